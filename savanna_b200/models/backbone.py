@@ -1,0 +1,154 @@
+"""Whole model: embedding -> N blocks -> final norm -> (tied) logits.
+
+Module indices reproduce the reference's sequential layout so state-dict keys match its checkpoints
+(savanna/model/backbone.py:312-434): `sequential.0` embedding, `.1` placeholder, layer i at
+`.{i+2}`, placeholder, final norm at `.{N+3}`, and (untied only) the lm head at `.{N+4}`.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint as ckpt
+
+from .. import ops
+from ..parallel import mappings, state
+from .block import ParallelBlock
+from .embedding import Embedding
+from .init_functions import get_init_methods
+from .mlp import ParallelLinear
+from .norms import get_norm
+
+
+class _Placeholder(nn.Module):
+    """Parameter-free slot (the reference puts layout lambdas here)."""
+
+    def forward(self, x, *a):
+        return x
+
+
+class NormPipe(nn.Module):
+    def __init__(self, cfg, dtype=None, device=None):
+        super().__init__()
+        self.norm = get_norm(cfg, dtype, device)
+
+    def forward(self, x):
+        return self.norm(x)
+
+
+class Backbone(nn.Module):
+    def __init__(self, cfg, device=None, dtype=None, layer_range: Optional[range] = None):
+        super().__init__()
+        self.cfg = cfg
+        dtype = dtype or cfg.params_dtype
+        init_m, out_init_m = get_init_methods(cfg)
+        N = cfg.num_layers
+        self.num_layers = N
+        self.layer_range = layer_range if layer_range is not None else range(N)
+        first = self.layer_range.start == 0
+        last = self.layer_range.stop == N
+        self.has_embedding, self.has_head = first or not cfg.no_weight_tying and last, last
+        mods: List[nn.Module] = []
+        mods.append(Embedding(cfg, init_m, dtype, device) if self.has_embedding else _Placeholder())
+        mods.append(_Placeholder())
+        for i in range(N):
+            mods.append(ParallelBlock(cfg, init_m, out_init_m, i, dtype, device) if i in self.layer_range else _Placeholder())
+        mods.append(_Placeholder())
+        mods.append(NormPipe(cfg, dtype, device) if last else _Placeholder())
+        if cfg.no_weight_tying and last:
+            mods.append(ParallelLinear(cfg, init_m, parallel_output=True, dtype=dtype, device=device))
+        self.sequential = nn.ModuleList(mods)
+        self.checkpoint_activations = cfg.checkpoint_activations
+        self.checkpoint_num_layers = max(1, cfg.checkpoint_num_layers)
+        self.sequence_parallel = cfg.sequence_parallel and state.get_model_parallel_world_size() > 1
+        self.mup_output_mult = (1.0 / cfg.mup_width_scale * cfg.mup_output_temp) if cfg.use_mup else 1.0
+
+    # -- pieces -------------------------------------------------------------------
+    @property
+    def embedding(self) -> Embedding:
+        return self.sequential[0]
+
+    def blocks(self):
+        return [self.sequential[i + 2] for i in self.layer_range]
+
+    @property
+    def final_norm(self):
+        return self.sequential[self.num_layers + 3]
+
+    def _run_blocks(self, x, positions):
+        blocks = self.blocks()
+        if not (self.checkpoint_activations and self.training):
+            for b in blocks:
+                x = b(x, positions)
+            return x
+        n = self.checkpoint_num_layers
+
+        def chunk_fn(start, end):
+            def fn(h, pos):
+                for b in blocks[start:end]:
+                    h = b(h, pos)
+                return h
+            return fn
+        for s in range(0, len(blocks), n):
+            x = ckpt.checkpoint(chunk_fn(s, min(s + n, len(blocks))), x, positions, use_reentrant=False)
+        return x
+
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        h = self.final_norm(h)
+        if self.cfg.no_weight_tying:
+            out, _ = self.sequential[self.num_layers + 4](h)
+            return out
+        w = self.embedding.word_embeddings.weight
+        if self.sequence_parallel:
+            h = mappings.gather_from_sequence_parallel_region(h, 1, True)
+        elif state.get_model_parallel_world_size() > 1:
+            h = mappings.copy_to_model_parallel_region(h)
+        out = ops.linear(h, w)
+        if self.mup_output_mult != 1.0:
+            out = out * self.mup_output_mult
+        return out
+
+    def forward(self, tokens: torch.Tensor, positions: Optional[torch.Tensor] = None,
+                hidden_in: Optional[torch.Tensor] = None, return_hidden: bool = False) -> torch.Tensor:
+        """tokens [B, L_local] -> logits [B, L_local, V/tp] (vocab-parallel when tp > 1).
+        Pipeline stages pass `hidden_in` instead of tokens and set `return_hidden`."""
+        if positions is None:
+            positions = torch.arange(tokens.shape[1], device=tokens.device)
+        x = self.embedding(tokens, positions) if hidden_in is None else hidden_in
+        x = self._run_blocks(x, positions)
+        if return_hidden or not self.has_head:
+            return x
+        return self.logits(x)
+
+
+def build_model(cfg, device=None) -> Backbone:
+    if cfg.padded_vocab_size is None:
+        raise ValueError("padded_vocab_size is unset: build the tokenizer first (cfg.build_tokenizer())")
+    return Backbone(cfg, device=device)
+
+
+def param_groups(model: nn.Module, cfg):
+    """Weight-decay / no-weight-decay (+ optional per-group lr) parameter groups
+    (reference: savanna/model/utils.py:28-109): no decay for norms, biases and Hyena filter
+    parameters; optional own lr for Hyena-MR filters (`lr_medium_hyena`) and for the no-decay group
+    (`wd_free_lr`)."""
+    decay, no_decay, medium = [], [], []
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        if cfg.lr_medium_hyena is not None and ".filter.h" in name:
+            medium.append(p)
+        elif getattr(p, "is_norm_param", False) or getattr(p, "is_filter_param", False) or name.endswith(".bias") \
+                or p.dim() == 1:
+            no_decay.append(p)
+        else:
+            decay.append(p)
+    wd = cfg.weight_decay
+    groups = [{"params": decay, "weight_decay": wd, "name": "decay"},
+              {"params": no_decay, "weight_decay": 0.0, "name": "no_decay"}]
+    if cfg.wd_free_lr is not None:
+        groups[1]["lr"] = cfg.wd_free_lr
+    if medium:
+        groups.append({"params": medium, "weight_decay": 0.0, "lr": cfg.lr_medium_hyena, "name": "medium_hyena"})
+    return [g for g in groups if g["params"]]

@@ -1,0 +1,182 @@
+"""Hyena filter parametrisations.
+
+ExplicitSingleDecayFilter (Hyena-MR): h[g,t] = h_hat[g,t] * exp(-alpha_g * t/(L_cache-1)),
+alpha = logspace(r_min, r_max, G_global) sliced by tensor-parallel rank
+(reference: parametrization/explicit.py:15-75).
+ImplicitModalFilter (Hyena-LI): h[d,t] = sum_o R[d,o] exp(-exp(p) exp(gamma) t)
+(parametrization/implicit_modal.py:220-282).  The modal form is an order-`order` diagonal linear
+recurrence, which is what the CUDA kernel evaluates; `forward(L)` materialises h only for the oracle,
+for filter inspection and for checkpoint tools.
+Other classes of the reference (real modal, complex modal, free-form sine MLP) are provided for
+configuration parity and evaluate through the generic FFT long-convolution path.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ..ops import reference as ref
+from ..parallel import state
+
+_PRESETS = {"strong": (0, 2), "normal": (-1, 2), "weak": (-2, 2)}
+
+
+class ExplicitSingleDecayFilter(nn.Module):
+    def __init__(self, d_model: int, L_cache: int, decay_preset: str = "strong", num_decay_repeats: int = 1,
+                 small_init: bool = True, unit_passthrough: bool = False, device=None):
+        super().__init__()
+        if decay_preset not in _PRESETS:
+            raise ValueError(f"decay preset {decay_preset!r} unknown")
+        r_min, r_max = _PRESETS[decay_preset]
+        h = torch.randn(d_model, L_cache, device=device) / math.sqrt(L_cache)
+        if small_init:
+            h = h * 1e-5
+        if unit_passthrough:
+            h[:, :1] = 1.0
+        self.h = nn.Parameter(h)
+        self.h.is_filter_param = True
+        tp, rank = state.get_model_parallel_world_size(), state.get_model_parallel_rank()
+        global_d = d_model * tp // num_decay_repeats
+        alpha = torch.logspace(r_min, r_max, global_d)[:, None].repeat(num_decay_repeats, 1)
+        alpha = alpha[rank * d_model:(rank + 1) * d_model]
+        t = torch.linspace(0, 1, L_cache)[None]
+        self.register_buffer("decay", torch.exp(-alpha * t).to(device))
+
+    def forward(self, L: int):
+        return self.h[:, :L] * self.decay[:, :L]
+
+    filter = forward
+
+
+class ImplicitModalFilter(nn.Module):
+    def __init__(self, d_model: int, order: int = 64, L_cache: int = None, gamma_min: float = 0.01,
+                 gamma_max: float = 0.1, device=None):
+        super().__init__()
+        self.order, self.d_model = order, d_model
+        self.register_buffer("t", torch.arange(L_cache or 1, dtype=torch.float32, device=device).view(1, 1, -1))
+        gamma = torch.rand(d_model, order, dtype=torch.float32, device=device) * (gamma_max - gamma_min) + gamma_min
+        self.gamma = nn.Parameter(gamma.log())
+        self.R = nn.Parameter(1e-1 * torch.randn(d_model, order, dtype=torch.float32, device=device) / math.sqrt(order))
+        self.p = nn.Parameter(-torch.ones(d_model, order, dtype=torch.float32, device=device))
+        for q in (self.gamma, self.R, self.p):
+            q.is_filter_param = True
+
+    def forward(self, L: int):
+        return ref.modal_filter(self.gamma, self.R, self.p, L)
+
+    filter = forward
+
+
+class ImplicitRealModalFilter(nn.Module):
+    """h[d,t] = sum_o residue[d,o] * pole[d,o]^t with real poles in (r_min, r_max)
+    (parametrization/implicit_modal.py:11-83)."""
+
+    def __init__(self, d_model, order=64, L_cache=None, r_min=0.5, r_max=0.99, residue_factors=3, pole_factors=3,
+                 device=None):
+        super().__init__()
+        self.order = order
+        poles = torch.rand(d_model, order, device=device) * (r_max - r_min) + r_min
+        self.log_poles = nn.Parameter(poles.log())
+        self.residues = nn.Parameter(torch.randn(d_model, order, device=device) / math.sqrt(order))
+        self.log_poles.is_filter_param = True
+        self.residues.is_filter_param = True
+
+    def forward(self, L: int):
+        t = torch.arange(L, device=self.log_poles.device, dtype=torch.float32)
+        return (self.residues.float().unsqueeze(-1) * torch.exp(self.log_poles.float().unsqueeze(-1) * t)).sum(1)
+
+    filter = forward
+
+
+class ParallelComplexModalFilter(nn.Module):
+    """S4D-style complex diagonal filter: h[t] = Re( sum_o C_o exp(dt*A_o t) * (exp(dt*A_o)-1)/A_o )
+    (parametrization/implicit_complex.py:35-97)."""
+
+    def __init__(self, d_model, order=64, dt_min=0.001, dt_max=0.1, device=None):
+        super().__init__()
+        half = max(1, order // 2)
+        log_dt = torch.rand(d_model, device=device) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min)
+        self.log_dt = nn.Parameter(log_dt)
+        self.C = nn.Parameter(torch.view_as_real(torch.randn(d_model, half, dtype=torch.cfloat, device=device)))
+        self.log_A_real = nn.Parameter(torch.log(0.5 * torch.ones(d_model, half, device=device)))
+        self.A_imag = nn.Parameter(math.pi * torch.arange(half, device=device, dtype=torch.float32).repeat(d_model, 1))
+        for q in (self.log_dt, self.C, self.log_A_real, self.A_imag):
+            q.is_filter_param = True
+
+    def forward(self, L: int):
+        dt = torch.exp(self.log_dt.float())
+        C = torch.view_as_complex(self.C.float())
+        A = -torch.exp(self.log_A_real.float()) + 1j * self.A_imag.float()
+        dtA = A * dt.unsqueeze(-1)
+        t = torch.arange(L, device=dt.device)
+        K = dtA.unsqueeze(-1) * t
+        Cb = C * (torch.exp(dtA) - 1.0) / A
+        return 2 * torch.einsum("dn,dnl->dl", Cb, torch.exp(K)).real
+
+    filter = forward
+
+
+class ParallelImplicitFreeformFilter(nn.Module):
+    """Sine-activated MLP over a positional embedding, modulated by an exponential decay window
+    (parametrization/implicit_freeform.py:15-122, implicit_utils.py:12-111)."""
+
+    def __init__(self, d_model, emb_dim=33, order=64, num_inner_mlps=2, w=14, L_cache=8192, fast_decay=0.3,
+                 slow_decay=1.2, modulate=True, device=None):
+        super().__init__()
+        if emb_dim % 2 == 0 or emb_dim < 3:
+            raise ValueError("emb_dim must be odd and >= 3 (time + sine/cosine pairs)")
+        self.w, self.modulate = w, modulate
+        bands = (emb_dim - 1) // 2
+        t = torch.linspace(0, 1, L_cache, device=device)[:, None]
+        tr = torch.linspace(0, L_cache - 1, L_cache, device=device)[:, None]
+        f = torch.linspace(1e-4, bands - 1, bands, device=device)[None]
+        ang = 2 * math.pi * tr * f / L_cache
+        self.register_buffer("z", torch.cat([t, torch.cos(ang), torch.sin(ang)], dim=-1))
+        self.register_buffer("t", t)
+        layers = [nn.Linear(emb_dim, order, device=device)]
+        for _ in range(num_inner_mlps):
+            layers.append(nn.Linear(order, order, device=device))
+        layers.append(nn.Linear(order, d_model, bias=False, device=device))
+        self.layers = nn.ModuleList(layers)
+        self.freq = nn.Parameter(w * torch.ones(1, order, device=device))
+        max_decay = math.log(1e-2) / fast_decay
+        min_decay = math.log(1e-2) / slow_decay
+        self.register_buffer("deltas", torch.linspace(min_decay, max_decay, d_model, device=device)[None])
+        for q in self.parameters():
+            q.is_filter_param = True
+
+    def forward(self, L: int):
+        x = self.z[:L]
+        for lin in self.layers[:-1]:
+            x = torch.sin(self.freq * lin(x))
+        h = self.layers[-1](x)
+        if self.modulate:
+            h = h * torch.exp(-self.t[:L] * self.deltas.abs())
+        return h.transpose(0, 1).float()
+
+    filter = forward
+
+
+def build_filter(cfg, operator_type: str, num_groups: int, device=None) -> nn.Module:
+    cls = cfg.hyena_filter_cls
+    if operator_type == "hyena_mr" and cfg.hyena_medium_filter_cls is not None:
+        cls = cfg.hyena_medium_filter_cls
+    if cls == "explicit_single_decay":
+        return ExplicitSingleDecayFilter(num_groups, cfg.seq_length, decay_preset=cfg.explicit_filter_decay_preset,
+                                         num_decay_repeats=cfg.explicit_filter_num_decay_repeats, device=device)
+    if cls == "implicit_modal":
+        return ImplicitModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length, cfg.modal_gamma_min,
+                                   cfg.modal_gamma_max, device=device)
+    if cls == "implicit_real_modal":
+        return ImplicitRealModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length, cfg.hyena_filter_r_min,
+                                       cfg.hyena_filter_r_max, cfg.modal_residue_factors, cfg.modal_pole_factors,
+                                       device=device)
+    if cls == "implicit_complex_modal":
+        return ParallelComplexModalFilter(num_groups, cfg.hyena_filter_order, device=device)
+    if cls in ("implicit", "implicit_freeform"):
+        return ParallelImplicitFreeformFilter(num_groups, cfg.hyena_filter_emb_dim, cfg.hyena_filter_order,
+                                              cfg.hyena_filter_num_inner_mlps, cfg.hyena_filter_w, cfg.seq_length,
+                                              cfg.hyena_filter_fast_decay, cfg.hyena_filter_slow_decay, device=device)
+    raise ValueError(f"hyena filter class {cls!r} unknown")

@@ -1,0 +1,115 @@
+"""Sequence mixer: projection -> (Hyena featuriser conv + Hyena operator | attention) -> out-projection.
+
+Reference: savanna/model/block.py:82-1003.  Parameter names: `dense_projection`, `hyena_proj_conv`,
+`mixer`, `rotary_emb`, `dense`.  The out-projection returns its bias un-added (the block fuses it
+into bias-dropout-add).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..parallel import halo as halo_mod, state
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
+from .hyena import CausalDepthwiseConv1d, HyenaOperator, ShortHyenaOperator, _as_two_chunks
+from .rope import RotaryEmbedding
+
+HYENA_OPS = ("hyena", "hyena_mr", "hyena_se")
+ATTENTION_OPS = ("flash_v2", "flash", "global", "ring", "flash_te")
+
+
+class SelfAttention(nn.Module):
+    """Causal multi-head attention on [B, L, heads/tp, 3*hd] projections with rotate-half RoPE.
+
+    Context parallelism: `ring` / `flash_te` operators run the zigzag ring algorithm
+    (parallel/ring_attention.py): KV shards travel around the context-parallel group and partial
+    outputs are merged by log-sum-exp (reference: operators/attention/flash.py:523-597).
+    """
+
+    def __init__(self, cfg, operator_type: str, device=None):
+        super().__init__()
+        tp = state.get_model_parallel_world_size()
+        self.heads = cfg.num_attention_heads // tp
+        self.hd = cfg.hidden_size // cfg.num_attention_heads
+        self.causal = cfg.causal
+        self.operator_type = operator_type
+        self._rotary = []          # the module itself is registered by the owning mixer as `rotary_emb`
+        if cfg.pos_emb in ("rotary", "rotary_linear_scaled", "rotary_ntk_scaled", "rotary2"):
+            rd = int(self.hd * cfg.rotary_pct)
+            self._rotary.append(RotaryEmbedding(rd, cfg.rotary_emb_base, cfg.rotary_emb_scaling_factor,
+                                                "rotary" if cfg.pos_emb == "rotary2" else cfg.pos_emb,
+                                                cfg.rotary_emb_max_unscaled_seq_len, device=device))
+
+    def forward(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        B, L, _ = qkv.shape
+        qkv = qkv.view(B, L, self.heads, 3 * self.hd)
+        q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+        if self._rotary:
+            cos, sin = self._rotary[0](positions)
+            q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+        cp = state.get_context_parallel_world_size()
+        if cp > 1 and self.operator_type in ("ring", "flash_te"):
+            from ..parallel.ring_attention import ring_attention
+            o = ring_attention(q, k, v, positions, causal=self.causal)
+        else:
+            o = ops.attention(q, k, v, causal=self.causal)
+        return o.reshape(B, L, self.heads * self.hd)
+
+
+class ParallelSequenceMixer(nn.Module):
+    def __init__(self, cfg, init_method, output_layer_init_method, layer_number: int,
+                 operator_type: Optional[str] = None, is_mlp: bool = False, dtype=None, device=None):
+        super().__init__()
+        self.cfg, self.layer_number, self.is_mlp = cfg, layer_number, is_mlp
+        self.operator_type = operator_type or cfg.operator_config[layer_number]
+        D = cfg.hidden_size
+        tp = state.get_model_parallel_world_size()
+        sp = cfg.sequence_parallel
+        if is_mlp:
+            fp8_in = cfg.use_fp8_linears and cfg.use_fp8_hyena_mlp_input_projections
+            fp8_out = cfg.use_fp8_linears and cfg.use_fp8_hyena_mlp_output_projections
+        else:
+            fp8_in = cfg.use_fp8_linears and cfg.use_fp8_input_projections
+            fp8_out = cfg.use_fp8_linears and cfg.use_fp8_output_projections
+        self.dense_projection = ColumnParallelLinear(D, 3 * D, bias=False, gather_output=False, init_method=init_method,
+                                                     skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device,
+                                                     fp8=fp8_in)
+        if self.operator_type in HYENA_OPS:
+            width = 3 * D // tp
+            self.short_conv_L = cfg.short_conv_L
+            self.hyena_proj_conv = CausalDepthwiseConv1d(width, cfg, cfg.short_conv_L, num_groups=width,
+                                                         fast=cfg.fast_conv_proj, dtype=dtype, device=device)
+            if self.operator_type == "hyena_se":
+                self.mixer = ShortHyenaOperator(D, cfg, is_mlp=is_mlp, dtype=dtype, device=device)
+            else:
+                self.mixer = HyenaOperator(D, cfg, layer_number, self.operator_type, dtype=dtype, device=device)
+            if not cfg.interleave_projections:
+                raise NotImplementedError("non-interleaved projections: convert the checkpoint with "
+                                          "tools/interleave_model_states.py and set interleave_projections")
+        elif self.operator_type in ATTENTION_OPS:
+            self.mixer = SelfAttention(cfg, self.operator_type, device=device)
+            if self.mixer._rotary:
+                self.rotary_emb = self.mixer._rotary[0]
+        else:
+            raise NotImplementedError(f"operator {self.operator_type!r} has no implementation in this framework")
+        self.dense = RowParallelLinear(D, D, bias=True, input_is_parallel=True, init_method=output_layer_init_method,
+                                       skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device, fp8=fp8_out)
+
+    def forward(self, x: torch.Tensor, positions: torch.Tensor):
+        proj, _ = self.dense_projection(x)
+        if self.operator_type in HYENA_OPS:
+            cp = state.get_context_parallel_world_size() if self.cfg.use_cp_hyena else 1
+            if cp > 1:
+                B, L, C = proj.shape
+                k = self.short_conv_L
+                h = halo_mod.zigzag_halo(proj, k - 1)
+                feat = self.hyena_proj_conv(_as_two_chunks(proj), h.reshape(B * 2, k - 1, C)).reshape(B, L, C)
+            else:
+                feat = self.hyena_proj_conv(proj)
+            z = self.mixer(feat)
+        else:
+            z = self.mixer(proj, positions)
+        return self.dense(z)

@@ -1,0 +1,233 @@
+"""ZeRO stage-1 optimizer: flat low-precision parameters and gradients, fp32 master weights and Adam
+moments partitioned over the data-parallel (x context-parallel) group.
+
+Step = gradient reduce-scatter -> global-norm clip -> Adam on the owned shard -> parameter
+all-gather.  Layout follows DeepSpeed's stage-1 so checkpoints carry the same objects
+(`single_partition_of_fp32_groups`, one flat partition per parameter group; reference usage:
+savanna/training.py:1329-1337 and the `zero_optimization` block of its configs):
+each parameter group is flattened in parameter order, padded so that every rank owns an equal,
+aligned slice, and rank i of the partition group owns slice i.
+
+Two communication paths: "nccl" issues reduce_scatter_tensor / all_gather_into_tensor on the flat
+buffers; "symm" runs the fused peer-memory kernels (parallel/fused_zero.py) when the buffers live in
+a symmetric-memory workspace.  With one rank both degenerate to the fused Adam kernel alone.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from . import state
+
+ALIGN = 256  # elements; keeps every shard 512-byte aligned for vector loads and bulk copies
+
+
+def _pad_to(n: int, m: int) -> int:
+    return m * ((n + m - 1) // m)
+
+
+class FlatGroup:
+    """One parameter group flattened into a parameter buffer and a gradient buffer."""
+
+    def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, allocator=None):
+        self.params = params
+        self.hyper = dict(hyper)
+        dtype, device = params[0].dtype, params[0].device
+        if any(p.dtype != dtype for p in params):
+            raise ValueError("all parameters of a group must share a dtype")
+        self.numel = sum(p.numel() for p in params)
+        self.padded = _pad_to(self.numel, ALIGN * world)
+        self.shard = self.padded // world
+        self.world, self.rank = world, rank
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
+        self.flat_param = alloc(self.padded, dtype)
+        self.flat_grad = alloc(self.padded, dtype)
+        self.offsets = []
+        off = 0
+        with torch.no_grad():
+            for p in params:
+                n = p.numel()
+                view = self.flat_param[off:off + n].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = self.flat_grad[off:off + n].view(p.shape)
+                self.offsets.append(off)
+                off += n
+        lo, hi = rank * self.shard, (rank + 1) * self.shard
+        self.master = self.flat_param[lo:hi].float().clone()
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.norm_weight: Optional[torch.Tensor] = None
+
+    def shard_slice(self, t: torch.Tensor) -> torch.Tensor:
+        return t[self.rank * self.shard:(self.rank + 1) * self.shard]
+
+    def build_norm_weight(self, tp: int) -> None:
+        """Per-element weight of the squared-norm sum on this shard: replicated (non tensor-parallel)
+        parameters count once over the tensor-parallel group."""
+        if tp == 1 or all(getattr(p, "model_parallel", False) for p in self.params):
+            return
+        w = torch.ones(self.padded, dtype=torch.float32, device=self.flat_param.device)
+        for p, off in zip(self.params, self.offsets):
+            if not getattr(p, "model_parallel", False):
+                w[off:off + p.numel()] = 1.0 / tp
+        self.norm_weight = self.shard_slice(w).clone()
+
+
+class ZeroOptimizer:
+    """Adam(W) with ZeRO-1 partitioning.  `param_groups` as for torch optimizers (dicts with `params`,
+    optional `lr`, `weight_decay`, `name`)."""
+
+    def __init__(self, param_groups: List[Dict], lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0, adamw: bool = True, clip_grad: float = 0.0,
+                 group=None, group_ranks: Optional[List[int]] = None, comm_path: str = "nccl",
+                 grad_divisor: Optional[float] = None, partition: bool = True):
+        self.group = group
+        ranks = group_ranks or [0]
+        self.world = len(ranks) if partition else 1
+        me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+        self.rank = ranks.index(me) if (partition and me in ranks) else 0
+        self.reduce_world = len(ranks)
+        self.partition = partition
+        self.betas, self.eps, self.adamw = betas, eps, adamw
+        self.clip_grad = clip_grad or 0.0
+        self.comm_path = comm_path
+        self.step_count = 0
+        self.defaults = {"lr": lr, "weight_decay": weight_decay}
+        self.groups: List[FlatGroup] = []
+        self.param_groups: List[Dict] = []
+        tp = state.get_model_parallel_world_size()
+        for g in param_groups:
+            params = [p for p in g["params"] if p.requires_grad]
+            if not params:
+                continue
+            hyper = {"lr": g.get("lr", lr), "weight_decay": g.get("weight_decay", weight_decay),
+                     "name": g.get("name", f"group{len(self.groups)}"), "lr_mult": g.get("lr", lr) / lr if lr else 1.0,
+                     "fixed_lr": "lr" in g}
+            fg = FlatGroup(params, self.world, self.rank, hyper)
+            fg.build_norm_weight(tp)
+            self.groups.append(fg)
+            self.param_groups.append(fg.hyper)      # lr schedulers write `lr` here
+        self.grad_divisor = grad_divisor
+        self.last_grad_norm: Optional[torch.Tensor] = None
+        self.fused = None                          # set by parallel.fused_zero.attach() on CUDA with symmetric memory
+
+    # ------------------------------------------------------------------ gradients
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        for g in self.groups:
+            g.flat_grad.zero_()
+
+    def _reduce_scatter(self, g: FlatGroup) -> torch.Tensor:
+        """Average gradients over the partition group; returns this rank's gradient shard."""
+        shard = g.shard_slice(g.flat_grad)
+        if self.reduce_world == 1:
+            return shard
+        if not self.partition:
+            dist.all_reduce(g.flat_grad, group=self.group)
+            g.flat_grad.div_(self.reduce_world)
+            return g.flat_grad
+        backend = dist.get_backend(self.group)
+        if backend == "gloo":
+            dist.all_reduce(g.flat_grad, group=self.group)
+        else:
+            dist.reduce_scatter_tensor(shard, g.flat_grad, group=self.group)
+        return shard
+
+    def _all_gather(self, g: FlatGroup) -> None:
+        if self.world == 1:
+            return
+        shard = g.shard_slice(g.flat_param)
+        backend = dist.get_backend(self.group)
+        if backend == "gloo":
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.clone(), group=self.group)
+            g.flat_param.copy_(torch.cat(parts))
+        else:
+            dist.all_gather_into_tensor(g.flat_param, shard, group=self.group)
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        """Runs one optimizer step; returns the global gradient norm (0-dim fp32 tensor, on device)."""
+        if self.fused is not None:
+            return self.fused.step(self)
+        self.step_count += 1
+        shards = [self._reduce_scatter(g) for g in self.groups]
+        inv = 1.0 / self.reduce_world if (self.reduce_world > 1 and self.partition) else 1.0
+        if self.grad_divisor:
+            inv = inv / self.grad_divisor
+        sq = None
+        for g, s in zip(self.groups, shards):
+            part = ops.sq_norm(s, g.norm_weight)
+            sq = part if sq is None else sq + part
+        sq = sq * (inv * inv)
+        if self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        tp = state.get_model_parallel_world_size()
+        if tp > 1:
+            dist.all_reduce(sq, group=state.get_model_parallel_group())
+        norm = sq.sqrt()
+        self.last_grad_norm = norm
+        if self.clip_grad > 0.0:
+            coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0) * inv
+        else:
+            coef = torch.full_like(norm, inv)
+        b1, b2 = self.betas
+        for g, s in zip(self.groups, shards):
+            ops.adam_step(g.master, g.exp_avg, g.exp_avg_sq, s, g.hyper["lr"], b1, b2, self.eps,
+                          g.hyper["weight_decay"], self.step_count, self.adamw, coef, g.shard_slice(g.flat_param))
+            self._all_gather(g)
+        return norm
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> Dict:
+        """DeepSpeed stage-1 shaped state."""
+        base_state = {}
+        for i, g in enumerate(self.groups):
+            base_state[i] = {"step": self.step_count, "exp_avg": g.exp_avg, "exp_avg_sq": g.exp_avg_sq}
+        return {
+            "zero_stage": 1,
+            "partition_count": [self.world] * len(self.groups),
+            "loss_scaler": None,
+            "dynamic_loss_scale": False,
+            "overflow": False,
+            "clip_grad": self.clip_grad,
+            "single_partition_of_fp32_groups": [g.master for g in self.groups],
+            "group_paddings": [g.padded - g.numel if self.rank == self.world - 1 else 0 for g in self.groups],
+            "base_optimizer_state": {
+                "state": base_state,
+                "param_groups": [{"lr": g.hyper["lr"], "betas": list(self.betas), "eps": self.eps,
+                                  "weight_decay": g.hyper["weight_decay"], "name": g.hyper["name"],
+                                  "params": [i]} for i, g in enumerate(self.groups)],
+            },
+        }
+
+    def load_state_dict(self, sd: Dict, load_master: bool = True) -> None:
+        masters = sd["single_partition_of_fp32_groups"]
+        if len(masters) != len(self.groups):
+            raise ValueError("optimizer state has a different number of parameter groups")
+        st = sd["base_optimizer_state"]["state"]
+        for i, g in enumerate(self.groups):
+            if masters[i].numel() != g.master.numel():
+                raise ValueError(f"optimizer partition size mismatch in group {i}: checkpoint was written with a "
+                                 "different partition count; reshard it with tools/reshard_zero.py")
+            if load_master:
+                g.master.copy_(masters[i])
+            g.exp_avg.copy_(st[i]["exp_avg"])
+            g.exp_avg_sq.copy_(st[i]["exp_avg_sq"])
+            self.step_count = int(st[i]["step"])
+            pg = sd["base_optimizer_state"]["param_groups"][i]
+            g.hyper["lr"] = pg["lr"]
+
+    def refresh_master_from_params(self) -> None:
+        for g in self.groups:
+            g.master.copy_(g.shard_slice(g.flat_param))
+
+    def sync_params_from_master(self) -> None:
+        for g in self.groups:
+            g.shard_slice(g.flat_param).copy_(g.master)
+            self._all_gather(g)

@@ -1,0 +1,295 @@
+"""Training program: distributed set-up, model + optimizer construction, the step and the loop.
+
+Role of the reference's savanna/training.py (pretrain :340, setup_model_and_optimizer :1243,
+forward_step :930, train_step :1410, train :1549, evaluate :1801) and savanna/initialize.py, without
+DeepSpeed: the engine pieces (ZeRO-1 optimizer, gradient accumulation, activation checkpointing,
+checkpoint I/O) are this package's own.
+
+Public API:
+    trainer = Trainer(cfg)                      # builds groups, model, optimizer, scheduler; loads a checkpoint
+    loss = trainer.train_step(data_iterator)    # one optimizer step (all accumulation micro-steps)
+    trainer.train(train_iter, valid_iter)       # the full loop with logging / eval / checkpoints
+    pretrain(cfg)                               # what train.py calls
+"""
+from __future__ import annotations
+
+import gc
+import math
+import os
+import random
+import time
+from typing import Dict, Iterator, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import print_rank_0
+from ..models import build_model, losses, param_groups
+from ..parallel import state
+from ..parallel.zero import ZeroOptimizer
+from . import batch as batch_mod
+from .lr import build_lr_scheduler
+
+
+# ----------------------------------------------------------------------------- distributed set-up
+
+
+def check_distributed_vars() -> None:
+    """Environment sanity of a multi-process launch (reference: savanna/distributed.py:6-30)."""
+    need = ("MASTER_ADDR", "MASTER_PORT", "RANK", "LOCAL_RANK", "WORLD_SIZE")
+    missing = [k for k in need if k not in os.environ]
+    if missing:
+        raise RuntimeError(f"distributed launch needs the environment variables {missing}")
+
+
+def set_random_seed(seed: int) -> None:
+    """Same seed on every rank for parameters (tensor-parallel weights are sliced from a master draw);
+    dropout and data order are offset by the data-parallel rank where they are used."""
+    if seed is None or seed < 0:
+        raise ValueError(f"seed must be a non-negative integer, got {seed}")
+    random.seed(seed)
+    np.random.seed(seed)
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed(seed)
+
+
+def initialize_distributed(cfg) -> torch.device:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    use_cuda = torch.cuda.is_available() and cfg.distributed_backend != "gloo"
+    if use_cuda:
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local % max(1, torch.cuda.device_count()))
+        device = torch.device("cuda", torch.cuda.current_device())
+    else:
+        device = torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        check_distributed_vars()
+        backend = cfg.distributed_backend if use_cuda else "gloo"
+        kw = {}
+        if backend == "nccl":
+            kw["device_id"] = device
+        dist.init_process_group(backend=backend, **kw)
+    if world > 1 or not state.model_parallel_is_initialized():
+        state.initialize_model_parallel(cfg.model_parallel_size, cfg.context_parallel_size,
+                                        max(1, cfg.pipe_parallel_size or 0), fp32_allreduce=cfg.fp32_allreduce)
+    cfg.rank = dist.get_rank() if dist.is_initialized() else 0
+    cfg.world_size = world
+    set_random_seed(cfg.seed)
+    return device
+
+
+# ----------------------------------------------------------------------------- trainer
+
+
+class Trainer:
+    def __init__(self, cfg, device: Optional[torch.device] = None, load: bool = True):
+        self.cfg = cfg
+        self.device = device if device is not None else initialize_distributed(cfg)
+        if cfg.tokenizer is None:
+            cfg.build_tokenizer()
+        if cfg.disable_gc:
+            gc.disable()
+        self.iteration = 0
+        self.tokens_seen = 0
+        self.model, self.optimizer, self.lr_scheduler = self._setup_model_and_optimizer()
+        self.gas = cfg.gradient_accumulation_steps
+        self.micro_batch = cfg.train_micro_batch_size_per_gpu
+        self.skipped_iters = 0
+        self.nan_iters = 0
+        self.profiler = None
+        self.timers = None
+        self.watchdog = None
+        if load and cfg.load is not None:
+            from ..ckpt import load_checkpoint
+            self.iteration = load_checkpoint(self)
+
+    # ------------------------------------------------------------------ construction
+    def _setup_model_and_optimizer(self):
+        cfg = self.cfg
+        if (cfg.pipe_parallel_size or 0) > 1:
+            from ..parallel.pipeline import build_pipeline_stage
+            model = build_pipeline_stage(cfg, self.device)
+        else:
+            model = build_model(cfg, device=self.device)
+        nparams = sum(p.numel() for p in model.parameters())
+        total = torch.tensor([float(nparams)], device=self.device)
+        if dist.is_initialized() and state.get_model_parallel_world_size() > 1:
+            dist.all_reduce(total, group=state.get_model_parallel_group())
+        print_rank_0(f" > parameters on tensor-parallel rank 0: {nparams:,} (model total ~{int(total.item()):,})")
+        self.num_params = int(total.item())
+        groups = param_groups(model, cfg)
+        opt_cfg = cfg.optimizer or {"type": "Adam", "params": {}}
+        p = dict(opt_cfg.get("params", {}))
+        otype = cfg.optimizer_type
+        if otype in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
+            optimizer = ZeroOptimizer(
+                groups, lr=cfg.lr, betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8),
+                weight_decay=cfg.weight_decay, adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
+                group=state.get_sequence_data_parallel_group(), group_ranks=state.get_sequence_data_parallel_ranks(),
+                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1)
+            if self.device.type == "cuda" and cfg.comm_path == "symm" and optimizer.reduce_world > 1:
+                from ..parallel import fused_zero
+                fused_zero.attach(optimizer, cfg)
+        else:
+            from .optimizers import build_generic_optimizer
+            optimizer = build_generic_optimizer(otype, groups, cfg, p)
+        sched = build_lr_scheduler(optimizer, cfg)
+        return model, optimizer, sched
+
+    # ------------------------------------------------------------------ forward
+    def compute_loss(self, logits: torch.Tensor, b: Dict[str, torch.Tensor]) -> torch.Tensor:
+        cfg = self.cfg
+        vp = state.get_model_parallel_world_size() > 1
+        labels, mask = b["labels"], b["loss_mask"]
+        if cfg.to_upper == "upper":
+            labels = batch_mod.to_upper_bytes(labels)
+        if cfg.pretraining_strategy == "OADM":
+            return losses.oadm_loss(logits, labels, mask, None)
+        if cfg.to_upper in ("weighted", "normalized_weighted"):
+            return losses.reweighted_cross_entropy(logits, labels, mask, cfg.lowercase_loss_reweighting,
+                                                   normalize_per_batch=cfg.to_upper == "normalized_weighted",
+                                                   vocab_parallel=vp)
+        return losses.cross_entropy(logits, labels, mask, vocab_parallel=vp)
+
+    def forward_step(self, b: Dict[str, torch.Tensor], return_logits: bool = False):
+        tokens = b["tokens"]
+        if self.cfg.to_upper in ("upper", "weighted", "normalized_weighted"):
+            tokens = batch_mod.to_upper_bytes(tokens)
+        logits = self.model(tokens, b["positions"])
+        loss = self.compute_loss(logits, b)
+        return (loss, logits) if return_logits else loss
+
+    # ------------------------------------------------------------------ step
+    def _mark(self, name: str):
+        if self.profiler is not None:
+            return self.profiler.mark(name)
+        import contextlib
+        return contextlib.nullcontext()
+
+    def train_step(self, data_iterator: Iterator) -> torch.Tensor:
+        """One optimizer step over `gradient_accumulation_steps` micro-batches.  Returns the mean loss
+        (0-dim device tensor; no host synchronisation happens inside the step)."""
+        cfg = self.cfg
+        if getattr(self.model, "is_pipeline_stage", False):
+            from ..parallel.pipeline import pipeline_train_step
+            return pipeline_train_step(self, data_iterator)
+        self.model.train()
+        self.optimizer.zero_grad()
+        total = None
+        for micro in range(self.gas):
+            with self._mark("TRAIN_STEP_FORWARD"):
+                b = batch_mod.get_batch(cfg, data_iterator, self.device)
+                loss = self.forward_step(b)
+            with self._mark("TRAIN_STEP_BACKWARD"):
+                (loss / self.gas).backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        self._sync_replicated_grads()
+        with self._mark("TRAIN_STEP_OPTIMIZER_STEP"):
+            self.grad_norm = self.optimizer.step()
+            self.lr_scheduler.step()
+        self.iteration += 1
+        self.tokens_seen += cfg.train_batch_size * cfg.seq_length
+        if self.watchdog is not None:
+            self.watchdog.beat(self.iteration)
+        return total / self.gas
+
+    def _sync_replicated_grads(self) -> None:
+        """Sequence parallelism: parameters replicated over the tensor-parallel group (norm gains, row
+        biases) see only a sequence slice per rank, so their gradients are summed over the group in ONE
+        flat all-reduce (the reference registers a hook per norm weight, model/utils.py:329-368)."""
+        cfg = self.cfg
+        tp = state.get_model_parallel_world_size()
+        if tp == 1 or not cfg.sequence_parallel:
+            return
+        grads = [p.grad for p in self.model.parameters()
+                 if p.grad is not None and not getattr(p, "model_parallel", False)]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=state.get_model_parallel_group())
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+
+    # ------------------------------------------------------------------ evaluation
+    @torch.no_grad()
+    def evaluate(self, data_iterator: Iterator, iters: Optional[int] = None) -> Dict[str, float]:
+        cfg = self.cfg
+        self.model.eval()
+        n = iters if iters is not None else cfg.eval_iters
+        acc = torch.zeros((), device=self.device)
+        for _ in range(n):
+            b = batch_mod.get_batch(cfg, data_iterator, self.device)
+            acc += self.forward_step(b).float()
+        self.model.train()
+        acc = acc / max(1, n)
+        if dist.is_initialized() and state.get_data_parallel_world_size() > 1:
+            dist.all_reduce(acc, group=state.get_data_parallel_group())
+            acc = acc / state.get_data_parallel_world_size()
+        lm = float(acc)
+        out = {"lm_loss": lm, "lm_loss_ppl": math.exp(min(20.0, lm))}
+        if cfg.char_level_ppl:
+            out["lm_loss_char_lvl_ppl"] = out["lm_loss_ppl"]
+        return out
+
+    # ------------------------------------------------------------------ loop
+    def train(self, train_iter: Iterator, valid_iter: Optional[Iterator] = None) -> None:
+        from ..ckpt import save_checkpoint
+        from ..utils.logging import TrainingLogger
+        from ..utils.profiler import setup_profiler
+        from ..utils.watchdog import Watchdog
+        cfg = self.cfg
+        logger = TrainingLogger(cfg, self)
+        self.profiler = setup_profiler(cfg)
+        if cfg.watchdog_step_timeout and cfg.watchdog_step_timeout > 0:
+            self.watchdog = Watchdog(cfg.watchdog_step_timeout, cfg.watchdog_heartbeat_dir, rank=cfg.rank or 0)
+            self.watchdog.start()
+        self.profiler.start()
+        if cfg.save and self.iteration == 0 and cfg.save_iters and 0 in cfg.save_iters:
+            save_checkpoint(self)
+        try:
+            while self.iteration < cfg.train_iters:
+                t0 = time.time()
+                loss = self.train_step(train_iter)
+                self.profiler.step()
+                logger.log_step(loss, time.time() - t0)
+                it = self.iteration
+                if cfg.save and cfg.save_iters and it in cfg.save_iters:
+                    save_checkpoint(self)
+                if valid_iter is not None and cfg.eval_interval and it % cfg.eval_interval == 0 and cfg.do_valid != 0:
+                    res = self.evaluate(valid_iter)
+                    logger.log_eval(res, it)
+                if cfg.exit_interval and it % cfg.exit_interval == 0:
+                    print_rank_0(f"exit_interval reached at iteration {it}")
+                    break
+                if cfg.disable_gc and it % 100 == 0:
+                    gc.collect(cfg.gc_collect_generation)
+        finally:
+            self.profiler.stop()
+            if self.watchdog is not None:
+                self.watchdog.stop()
+        if cfg.save and self.iteration > 0 and (not cfg.save_iters or self.iteration not in cfg.save_iters):
+            save_checkpoint(self)
+
+
+# ----------------------------------------------------------------------------- entry
+
+
+def pretrain(cfg) -> Trainer:
+    """Entry used by train.py: set up, build data iterators, train, final evaluation."""
+    from ..data.loaders import build_train_valid_test_data_iterators
+    trainer = Trainer(cfg)
+    cfg.iteration = trainer.iteration
+    train_it, valid_it, test_it = build_train_valid_test_data_iterators(cfg, trainer)
+    if cfg.do_train is None or cfg.do_train:
+        trainer.train(train_it, valid_it)
+    if valid_it is not None and cfg.do_valid:
+        res = trainer.evaluate(valid_it)
+        print_rank_0(f"final validation: {res}")
+    if test_it is not None and cfg.do_test:
+        res = trainer.evaluate(test_it)
+        print_rank_0(f"final test: {res}")
+    return trainer
