@@ -1,0 +1,300 @@
+// bf16 GEMM on 5th-generation tensor cores (sm_100a): C[M,N] = A * B^T (+ bias) (+ C), fp32 accumulation in TMEM.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0   : TMA producer  (one elected lane issues cp.async.bulk.tensor loads, 128-byte swizzle, no multicast)
+//   warp 1   : MMA issuer    (one elected lane issues tcgen05.mma; owns the TMEM allocation)
+//   warps 2-5: epilogue      (tcgen05.ld TMEM -> registers -> bf16 -> global), one TMEM lane quarter each
+// Tile 128 x 256 x 64, 4-stage shared-memory ring (48 KB per stage), two 256-column TMEM accumulators so
+// the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts ("major" = which dim is contiguous in global memory):
+//   A K-major : A[M, K]   (activations in a forward projection, dY in dgrad)
+//   A MN-major: A^T[K, M] (dY in wgrad: the reduction dim T is the row index)
+//   B K-major : B[N, K]   (weights in a forward projection)
+//   B MN-major: B^T[K, N] (weights in dgrad, X in wgrad)
+// MN-major tiles are fetched as 64x64 boxes so that the shared-memory image is the canonical
+// MN-major 128B-swizzle layout (64-element blocks LBO apart, 8-row groups SBO apart).
+//
+// All waits are bounded (sm100.cuh); on a timeout the kernel records a status word, every role unwinds,
+// TMEM is freed and the kernel returns.
+#include "sm100.cuh"
+
+namespace sb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE = BM * BK * 2;              // 16 KB
+constexpr int B_STAGE = BN * BK * 2;              // 32 KB
+constexpr int STAGE_BYTES = A_STAGE + B_STAGE;    // 48 KB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 16;                       // raster: 16 m-tiles share the concurrently running n-tiles
+constexpr int NUM_THREADS = 192;
+
+struct GemmParams {
+  __nv_bfloat16* C;
+  const __nv_bfloat16* bias;   // [N] or null
+  int M, N, K, ldc;
+  int beta;                    // 1: C += result (bf16 read-modify-write)
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_group = GROUP_M * n_tiles;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsz = min(GROUP_M, m_tiles - first_m);
+  const int r = tile - g * per_group;
+  mt = first_m + r % gsz;
+  nt = r / gsz;
+}
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  // barrier block after the stages
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mt, nt; tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(a_dst, &tmA, k0, m0, full_bar(stage));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, m0 + 64 * j, k0, full_bar(stage));
+          }
+          if (B_MN == 0) {
+            tma_load_2d(b_dst, &tmB, k0, n0, full_bar(stage));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, n0 + 64 * j, k0, full_bar(stage));
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let loads that are still in flight land before the CTA exits
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { __nanosleep(1000); }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, a_step = A_MN ? (UMMA_K * 128u) >> 4 : (UMMA_K * 2u) >> 4;
+      constexpr uint32_t b_lbo = B_MN ? 8192u : 16u, b_step = B_MN ? (UMMA_K * 128u) >> 4 : (UMMA_K * 2u) >> 4;
+      int stage = 0; uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0u, 0u};
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        acc_phase[acc] ^= 1u;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+          const uint64_t adesc = umma_smem_desc(a_addr, a_lbo, 1024u);
+          const uint64_t bdesc = umma_smem_desc(a_addr + A_STAGE, b_lbo, 1024u);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_bf16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                         // TMEM lane quarter this warp may access
+    uint32_t acc_phase[2] = {0u, 0u};
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      int mt, nt; tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      acc_phase[acc] ^= 1u;
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const int n0 = nt * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      __nv_bfloat16* crow = p.C + size_t(row) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col + 8 <= p.N) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (p.bias) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(b2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+              }
+              if (p.beta) {
+                const uint4 ov = *reinterpret_cast<const uint4*>(crow + col);
+                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(o2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+              }
+              uint4 out;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *reinterpret_cast<uint4*>(crow + col) = out;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride `ld` elements.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+
+}  // namespace sb
+
+// C = A * B^T (+bias) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
+// transposed as [K, M] with leading dim lda.  b_mn likewise for B ([N, K] or [K, N]).  All leading dims and
+// base addresses must be 16-byte aligned; N and K multiples of 8.  Returns 0 on a successful launch.
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                            int ldb, int ldc, int a_mn, int b_mn, int beta, unsigned int* status, int max_ctas,
+                            cudaStream_t stream) {
+  using namespace sb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (a_mn && (M % 8))) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, BM);
+  else       rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, BN);
+  else       rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK);
+  if (rc) return rc;
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, beta, status};
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);
+  if (!a_mn && !b_mn) kern = gemm_bf16_kernel<0, 0>;
+  else if (!a_mn && b_mn) kern = gemm_bf16_kernel<0, 1>;
+  else if (a_mn && b_mn) kern = gemm_bf16_kernel<1, 1>;
+  else kern = gemm_bf16_kernel<1, 0>;
+  static bool attr_set[4] = {false, false, false, false};
+  const int idx = a_mn * 2 + b_mn;
+  if (!attr_set[idx]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -5;
+    attr_set[idx] = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}

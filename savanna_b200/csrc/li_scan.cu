@@ -1,0 +1,313 @@
+// Hyena-LI with the implicit modal filter, evaluated as what it is: an order-O diagonal linear recurrence.
+//
+//   h[d,t] = sum_o R[d,o] lam[d,o]^t          =>   s_o[t] = lam_o s_o[t-1] + u[t],   y[t] = sum_o R_o s_o[t] + bias u[t]
+//   u = x2 * v,  z = x1 * y                        (features interleaved (x1,x2,v), channel-last bf16, fp32 state)
+//
+// The sequence is cut into chunks of TC steps that run in parallel (chunked scan):
+//   1. local   : every chunk runs from a zero state and stores its end state          [B, NC, D, O]
+//   2. prefix  : per (b, d, o) a serial pass over the NC chunk states turns them into the state ENTERING each chunk
+//   3. apply   : every chunk reruns from its entering state and writes z
+// so the cost is two streaming reads of the features and one write of z, instead of the size-2L fp32 FFTs the
+// filter's materialised form needs.  The backward pass uses the same structure twice: a forward scan that
+// carries the state s and its sensitivity w = ds/dlam (gradients of R, lam, bias and dx1), and a reverse scan of
+// the adjoint a[t] = R dy[t] + lam a[t+1] (gradients of x2 and v).  `state_in` / `state_out` expose the recurrence
+// state at the shard boundaries, which is all context parallelism needs to hand over.
+//
+// One thread owns one channel (its O states live in registers); a warp reads 32 channels x 3 features = 192
+// contiguous bytes per time step.  O is padded to 16 (lam = 0, R = 0 beyond the real order).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sb {
+typedef __nv_bfloat16 bf16;
+constexpr int LO = 16;            // padded filter order
+constexpr int LI_THREADS = 128;
+
+__device__ __forceinline__ float b2f(const bf16 v) { return __bfloat162float(v); }
+
+struct LiDims { int B, L, D, TC, NC; };
+
+__device__ __forceinline__ void load_vec16(const float* p, float (&r)[LO]) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < LO / 4; ++i) { float4 t = q[i]; r[4 * i] = t.x; r[4 * i + 1] = t.y; r[4 * i + 2] = t.z; r[4 * i + 3] = t.w; }
+}
+__device__ __forceinline__ void store_vec16(float* p, const float (&r)[LO]) {
+  float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+  for (int i = 0; i < LO / 4; ++i) q[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+}
+
+// ------------------------------------------------------------------------------------ forward
+// pass 1: chunk-local end state from a zero state
+__global__ void __launch_bounds__(LI_THREADS)
+li_local_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam, float* __restrict__ Sloc, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); s[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t, f += 3 * d.D) {
+    const float u = b2f(f[1]) * b2f(f[2]);
+#pragma unroll
+    for (int o = 0; o < LO; ++o) s[o] = lam[o] * s[o] + u;
+  }
+  store_vec16(Sloc + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+}
+
+// pass 2: exclusive prefix over chunks, in place: S[n] <- state entering chunk n.  One thread per (b, ch, o).
+// Chunks are full (TC steps) except possibly the last one, whose end state only feeds state_out.
+__global__ void li_prefix_kernel(float* __restrict__ S, const float* __restrict__ loglam, const float* __restrict__ state_in,
+                                 float* __restrict__ state_out, LiDims d) {
+  const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t per_b = (size_t)d.D * LO;
+  if (idx >= (size_t)d.B * per_b) return;
+  const int b = idx / per_b;
+  const size_t r = idx - (size_t)b * per_b;               // ch * LO + o
+  const float ll = loglam[r];
+  const float step = __expf(ll * d.TC);
+  float carry = state_in ? state_in[idx] : 0.f;
+  float* p = S + (size_t)b * d.NC * per_b + r;
+  for (int n = 0; n < d.NC; ++n) {
+    const float loc = p[(size_t)n * per_b];
+    p[(size_t)n * per_b] = carry;
+    const int len = min(d.TC, d.L - n * d.TC);
+    const float st = len == d.TC ? step : __expf(ll * len);
+    carry = st * carry + loc;
+  }
+  if (state_out) state_out[idx] = carry;
+}
+
+// pass 3: rerun each chunk from its entering state and emit z
+__global__ void __launch_bounds__(LI_THREADS)
+li_apply_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam, const float* __restrict__ R,
+                const float* __restrict__ bias, const float* __restrict__ Sin, bf16* __restrict__ z, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], rr[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Sin + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) lam[o] = __expf(lam[o]);
+  const float be = bias[ch];
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
+  bf16* zo = z + ((size_t)b * d.L + t0) * d.D + ch;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t, f += 3 * d.D, zo += d.D) {
+    const float x1 = b2f(f[0]);
+    const float u = b2f(f[1]) * b2f(f[2]);
+    float y = be * u;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { s[o] = lam[o] * s[o] + u; y += rr[o] * s[o]; }
+    *zo = __float2bfloat16_rn(x1 * y);
+  }
+}
+
+// ------------------------------------------------------------------------------------ backward
+// pass B1: chunk-local quantities from zero states:
+//   Sloc  end state;  Wloc end sensitivity (w[t] = s[t-1] + lam w[t-1]);
+//   Aloc  adjoint leaving the chunk on its left edge: sum_t lam^(t-t0) R dy[t], dy = dz * x1
+__global__ void __launch_bounds__(LI_THREADS)
+li_bwd_local_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
+                    const float* __restrict__ R, float* __restrict__ Sloc, float* __restrict__ Wloc,
+                    float* __restrict__ Aloc, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], w[LO], pw[LO], a[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); s[o] = 0.f; w[o] = 0.f; pw[o] = 1.f; a[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
+  const bf16* g = dz + ((size_t)b * d.L + t0) * d.D + ch;
+#pragma unroll 2
+  for (int t = t0; t < t1; ++t, f += 3 * d.D, g += d.D) {
+    const float u = b2f(f[1]) * b2f(f[2]);
+    const float dy = b2f(*g) * b2f(f[0]);
+#pragma unroll
+    for (int o = 0; o < LO; ++o) {
+      w[o] = s[o] + lam[o] * w[o];
+      s[o] = lam[o] * s[o] + u;
+      a[o] += pw[o] * dy;
+      pw[o] *= lam[o];
+    }
+  }
+  float rr[LO];
+  load_vec16(R + (size_t)ch * LO, rr);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) a[o] *= rr[o];
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  store_vec16(Sloc + off, s);
+  store_vec16(Wloc + off, w);
+  store_vec16(Aloc + off, a);
+}
+
+// pass B2: (S, W) exclusive prefix (forward), A exclusive suffix (reverse), in place.
+//   S_in[n+1] = lam^len S_in[n] + Sloc[n]
+//   W_in[n+1] = lam^len W_in[n] + len lam^(len-1) S_in[n] + Wloc[n]
+//   A_in[n-1] = lam^len(n) A_in[n] + Aloc[n]          (A_in[n] = adjoint at the right edge of chunk n)
+// Also: w_end (sensitivity of the final state), dstate_in = lam * (adjoint at t = 0).
+__global__ void li_bwd_prefix_kernel(float* __restrict__ S, float* __restrict__ W, float* __restrict__ A,
+                                     const float* __restrict__ loglam, const float* __restrict__ state_in,
+                                     const float* __restrict__ dstate_out, float* __restrict__ w_end,
+                                     float* __restrict__ dstate_in, LiDims d) {
+  const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t per_b = (size_t)d.D * LO;
+  if (idx >= (size_t)d.B * per_b) return;
+  const int b = idx / per_b;
+  const size_t r = idx - (size_t)b * per_b;
+  const float ll = loglam[r];
+  const size_t base = (size_t)b * d.NC * per_b + r;
+  float cs = state_in ? state_in[idx] : 0.f, cw = 0.f;
+  for (int n = 0; n < d.NC; ++n) {
+    const size_t o = base + (size_t)n * per_b;
+    const float ls = S[o], lw = W[o];
+    S[o] = cs; W[o] = cw;
+    const int len = min(d.TC, d.L - n * d.TC);
+    const float st = __expf(ll * len);
+    const float stm1 = __expf(ll * (len - 1));
+    cw = st * cw + len * stm1 * cs + lw;
+    cs = st * cs + ls;
+  }
+  if (w_end) w_end[idx] = cw;
+  float ca = dstate_out ? dstate_out[idx] : 0.f;
+  for (int n = d.NC - 1; n >= 0; --n) {
+    const size_t o = base + (size_t)n * per_b;
+    const float la = A[o];
+    A[o] = ca;
+    const int len = min(d.TC, d.L - n * d.TC);
+    ca = __expf(ll * len) * ca + la;
+  }
+  if (dstate_in) dstate_in[idx] = __expf(ll) * ca;
+}
+
+// pass B3 (forward direction): y, dx1 = dz*y (into tmp), and per-chunk partial sums of dR, dlam, dbias
+__global__ void __launch_bounds__(LI_THREADS)
+li_bwd_apply_fwd_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
+                        const float* __restrict__ R, const float* __restrict__ bias, const float* __restrict__ Sin,
+                        const float* __restrict__ Win, bf16* __restrict__ dx1, float* __restrict__ dRp,
+                        float* __restrict__ dLp, float* __restrict__ dBp, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], w[LO], rr[LO], dr[LO], dl[LO];
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Sin + off, s);
+  load_vec16(Win + off, w);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); dr[o] = 0.f; dl[o] = 0.f; }
+  const float be = bias[ch];
+  float db = 0.f;
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
+  const bf16* g = dz + ((size_t)b * d.L + t0) * d.D + ch;
+  bf16* o1 = dx1 + ((size_t)b * d.L + t0) * d.D + ch;
+#pragma unroll 2
+  for (int t = t0; t < t1; ++t, f += 3 * d.D, g += d.D, o1 += d.D) {
+    const float x1 = b2f(f[0]);
+    const float u = b2f(f[1]) * b2f(f[2]);
+    const float gz = b2f(*g);
+    const float dy = gz * x1;
+    float y = be * u;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) {
+      w[o] = s[o] + lam[o] * w[o];
+      s[o] = lam[o] * s[o] + u;
+      y += rr[o] * s[o];
+      dr[o] += dy * s[o];
+      dl[o] += dy * w[o];
+    }
+    db += dy * u;
+    *o1 = __float2bfloat16_rn(gz * y);
+  }
+#pragma unroll
+  for (int o = 0; o < LO; ++o) dl[o] *= rr[o];
+  store_vec16(dRp + off, dr);
+  store_vec16(dLp + off, dl);
+  dBp[((size_t)b * d.NC + n) * d.D + ch] = db;
+}
+
+// pass R3 (reverse direction): adjoint scan, writes the full interleaved gradient (dx1 from tmp)
+__global__ void __launch_bounds__(LI_THREADS)
+li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
+                        const float* __restrict__ R, const float* __restrict__ bias, const float* __restrict__ Ain,
+                        const bf16* __restrict__ dx1, bf16* __restrict__ dfeat, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], a[LO], rr[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Ain + (((size_t)b * d.NC + n) * d.D + ch) * LO, a);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) lam[o] = __expf(lam[o]);
+  const float be = bias[ch];
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = feat + ((size_t)b * d.L + (t1 - 1)) * 3 * d.D + 3 * ch;
+  const bf16* g = dz + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
+  const bf16* i1 = dx1 + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
+  bf16* df = dfeat + ((size_t)b * d.L + (t1 - 1)) * 3 * d.D + 3 * ch;
+#pragma unroll 4
+  for (int t = t1 - 1; t >= t0; --t, f -= 3 * d.D, g -= d.D, i1 -= d.D, df -= 3 * d.D) {
+    const float x1 = b2f(f[0]), x2 = b2f(f[1]), v = b2f(f[2]);
+    const float dy = b2f(*g) * x1;
+    float du = be * dy;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { a[o] = rr[o] * dy + lam[o] * a[o]; du += a[o]; }
+    df[0] = *i1;
+    df[1] = __float2bfloat16_rn(du * v);
+    df[2] = __float2bfloat16_rn(du * x2);
+  }
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+static inline LiDims li_dims(int B, int L, int D, int TC) { return LiDims{B, L, D, TC, (L + TC - 1) / TC}; }
+
+// Scratch sizes (floats): S = B*NC*D*16.  Callers allocate and pass them.
+extern "C" int sb_li_num_chunks(int L, int TC) { return (L + TC - 1) / TC; }
+
+extern "C" int sb_li_fwd(const void* feat, const float* loglam, const float* R, const float* bias, const float* state_in,
+                         float* state_out, float* S_scratch, void* z, int B, int L, int D, int TC, cudaStream_t st) {
+  if (B * L == 0) return 0;
+  LiDims d = li_dims(B, L, D, TC);
+  dim3 grid((D + LI_THREADS - 1) / LI_THREADS, d.NC, B);
+  li_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, S_scratch, d);
+  const size_t n = (size_t)B * D * LO;
+  li_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S_scratch, loglam, state_in, state_out, d);
+  li_apply_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, R, bias, S_scratch, (bf16*)z, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Scratch: S, W, A, dRp, dLp each B*NC*D*16 floats; dBp B*NC*D floats; dx1_tmp B*L*D bf16.
+// Outputs: dfeat; per-chunk partials dRp/dLp/dBp (the caller sums over B and NC); w_end, dstate_in optional.
+extern "C" int sb_li_bwd(const void* feat, const void* dz, const float* loglam, const float* R, const float* bias,
+                         const float* state_in, const float* dstate_out, float* S, float* W, float* A, float* dRp,
+                         float* dLp, float* dBp, void* dx1_tmp, void* dfeat, float* w_end, float* dstate_in, int B, int L,
+                         int D, int TC, cudaStream_t st) {
+  if (B * L == 0) return 0;
+  LiDims d = li_dims(B, L, D, TC);
+  dim3 grid((D + LI_THREADS - 1) / LI_THREADS, d.NC, B);
+  li_bwd_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, S, W, A, d);
+  const size_t n = (size_t)B * D * LO;
+  li_bwd_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, W, A, loglam, state_in, dstate_out, w_end, dstate_in, d);
+  li_bwd_apply_fwd_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, S, W,
+                                                      (bf16*)dx1_tmp, dRp, dLp, dBp, d);
+  li_bwd_apply_rev_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, A,
+                                                      (const bf16*)dx1_tmp, (bf16*)dfeat, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

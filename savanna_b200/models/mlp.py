@@ -29,38 +29,65 @@ def gate_activation(cfg, layer_number: int) -> str:
 
 
 class ParallelGLU(nn.Module):
+    """Gated MLP.  `w12` stacks the local rows of w1 and w2 ([2F/tp, D]) so both run as one GEMM; state
+    dicts still carry `w1.weight` and `w2.weight` (hooks below), which keeps checkpoints and the
+    tensor-parallel reshard tools unchanged."""
+
     def __init__(self, cfg, init_method, output_layer_init_method, layer_number: int = 0, dtype=None, device=None):
         super().__init__()
+        from ..parallel.layers import _master_init, mark_tp
         self.act = gate_activation(cfg, layer_number)
         D, Fh = cfg.hidden_size, cfg.ffn_size
         tp = state.get_model_parallel_world_size()
         if cfg.pad_mlp_weights:
             m = 16 * tp
             Fh = m * ((Fh + m - 1) // m)
-        fp8 = cfg.use_fp8_linears or cfg.use_fp8_mlp_projections
+        if Fh % tp:
+            raise ValueError(f"MLP inner size {Fh} not divisible by the tensor-parallel size {tp}")
+        self.ffn_local = Fh // tp
+        self.fp8 = bool(cfg.use_fp8_linears or cfg.use_fp8_mlp_projections)
         sp = cfg.sequence_parallel
-        kw = dict(bias=False, gather_output=False, init_method=init_method, skip_bias_add=True,
-                  sequence_parallel=sp, dtype=dtype, device=device, fp8=fp8)
-        self.w1 = ColumnParallelLinear(D, Fh, **kw)
-        self.w2 = ColumnParallelLinear(D, Fh, **kw)
+        w1 = _master_init((Fh, D), init_method, 0, dtype, device)
+        w2 = _master_init((Fh, D), init_method, 0, dtype, device)
+        self.w12 = nn.Parameter(torch.cat([w1, w2], dim=0))
+        mark_tp(self.w12, True, 0)
+        self.w12.glu_packed = True
         self.w3 = RowParallelLinear(Fh, D, bias=False, input_is_parallel=True, init_method=output_layer_init_method,
                                     skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device,
-                                    fp8=fp8 and not cfg.disable_fp8_w3)
+                                    fp8=self.fp8 and not cfg.disable_fp8_w3)
         self.sequence_parallel = sp and tp > 1
-        self._w12 = None
+        self._register_state_dict_hook(self._split_hook)
+        self._register_load_state_dict_pre_hook(self._merge_hook)
 
-    def _packed_weight(self):
-        # [2F/tp, D]: w1 rows then w2 rows.  Built by autograd-visible concatenation so both parameters get grads.
-        return torch.cat([self.w1.weight, self.w2.weight], dim=0)
+    @staticmethod
+    def _split_hook(module, sd, prefix, local_metadata):
+        w = sd.pop(prefix + "w12")
+        sd[prefix + "w1.weight"], sd[prefix + "w2.weight"] = w[: module.ffn_local], w[module.ffn_local:]
+        # keep the reference's key order: w1, w2, w3
+        w3 = {k: sd.pop(k) for k in [k for k in sd if k.startswith(prefix + "w3.")]}
+        sd.update(w3)
+        return sd
+
+    def _merge_hook(self, sd, prefix, local_metadata, strict, missing, unexpected, errors):
+        k1, k2 = prefix + "w1.weight", prefix + "w2.weight"
+        if k1 in sd and k2 in sd:
+            sd[prefix + "w12"] = torch.cat([sd.pop(k1), sd.pop(k2)], dim=0)
+
+    @property
+    def w1_weight(self):
+        return self.w12[: self.ffn_local]
+
+    @property
+    def w2_weight(self):
+        return self.w12[self.ffn_local:]
 
     def forward(self, x):
-        w12 = self._packed_weight()
         if self.sequence_parallel:
-            ab = ops.linear_allgather(x, w12, None, 1, fp8=self.w1.fp8)
+            ab = ops.linear_allgather(x, self.w12, None, 1, fp8=self.fp8)
         else:
             from ..parallel import mappings
             xin = mappings.copy_to_model_parallel_region(x) if state.get_model_parallel_world_size() > 1 else x
-            ab = ops.linear(xin, w12, None, fp8=self.w1.fp8)
+            ab = ops.linear(xin, self.w12, None, fp8=self.fp8)
         h = ops.glu_act_packed(ab, self.act)
         return self.w3(h)
 

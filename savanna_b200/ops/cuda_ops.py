@@ -1,0 +1,610 @@
+"""CUDA operator implementations: autograd Functions over the in-tree sm_100a library.
+
+The library (`savanna_b200/libsavanna_b200.so`, built by `python -m savanna_b200.csrc.build`) exposes C
+symbols; they are called through ctypes with raw device pointers and the current CUDA stream, so the
+kernels run in PyTorch's stream order and under its caching allocator.  All kernels take bf16
+activations and accumulate in fp32.  Tensors of another dtype run the PyTorch statement of the op
+(reference.py) — a debugging configuration, not a performance path.
+
+`launch_count()` counts launches of this library's kernels (incremented at every call site by the
+number of kernels the C entry point launches).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+
+_LIB = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "libsavanna_b200.so")
+_LAUNCHES = 0
+_STATUS = {}
+
+_ACT = {"silu": 0, "swish": 0, "gelu": 1, "relu": 2, "identity": 3}
+bf16 = torch.bfloat16
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def require():
+    """Load the native library; raise if it is missing (never fall back silently on a GPU)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build the CUDA kernels with `python -m savanna_b200.csrc.build` "
+            "(CUDA tensors never fall back to PyTorch ops silently; set SAVANNA_B200_BACKEND=torch to ask for that)")
+    _LIB = ctypes.CDLL(_LIB_PATH)
+    for name in dir(_Sig):
+        if name.startswith("sb_"):
+            fn = getattr(_LIB, name)
+            fn.restype = c_int
+            fn.argtypes = getattr(_Sig, name)
+    return _LIB
+
+
+class _Sig:
+    P, I, F, LL = c_void_p, c_int, c_float, c_ll
+    sb_gemm_bf16 = [P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, P]
+    sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
+    sb_rmsnorm_bwd = [P, P, P, P, P, P, I, I, F, I, P]
+    sb_glu_fwd = [P, P, LL, I, I, P]
+    sb_glu_bwd = [P, P, P, LL, I, I, P]
+    sb_rope = [P, P, P, P, I, I, I, I, I, LL, LL, I, P]
+    sb_ce_fwd = [P, P, P, P, LL, I, P]
+    sb_ce_bwd = [P, P, P, P, P, LL, I, P]
+    sb_sqnorm = [P, P, P, LL, I, P]
+    sb_adam = [P, P, P, P, P, LL, F, F, F, F, F, F, F, I, P, F, I, P]
+    sb_dwconv_fwd = [P, P, P, P, I, I, I, I, P]
+    sb_dwconv_bwd = [P, P, P, P, P, P, P, I, I, I, I, P]
+    sb_se_fwd = [P, P, P, P, I, I, I, I, I, I, I, P]
+    sb_se_bwd = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
+    sb_mr_fwd = [P, P, P, P, P, P, I, I, I, I, I, P]
+    sb_mr_bwd = [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
+    sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
+    sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def _count(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"savanna_b200 kernel `{what}` rejected its arguments or failed to launch (code {rc})")
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device uint32 word the bounded waits of the kernels write when they give up."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device=None) -> int:
+    """Read (and clear) the status word; raises if a kernel recorded a timed-out wait.  Synchronises."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise RuntimeError(f"a kernel gave up on a bounded wait: code {(v >> 24) & 0xff}, detail {v & 0xffffff}")
+    return v
+
+
+def _is_bf16(*ts) -> bool:
+    return all(t is None or t.dtype == bf16 for t in ts)
+
+
+# ----------------------------------------------------------------------------- GEMM
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
+         bias: Optional[torch.Tensor] = None, accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """out[M,N] = A * B^T (+bias) (+out).  `a` is [M,K] (a_mn False) or the transposed storage [K,M]
+    (a_mn True); `b` is [N,K] or [K,N].  2-D tensors with unit inner stride."""
+    lib = require()
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    for t in (a, b, out):
+        if t.dim() != 2 or t.stride(1) != 1 or t.dtype != bf16:
+            raise ValueError("gemm operands must be 2-D bf16 with unit inner stride")
+    rc = lib.sb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), M, N, K, a.stride(0), b.stride(0),
+                          out.stride(0), int(a_mn), int(b_mn), int(accumulate), status_word(out.device).data_ptr(),
+                          max_ctas, _stream())
+    _check(rc, "gemm_bf16")
+    _count()
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or (x2.stride(0) % 8):
+            x2 = x2.contiguous()
+        out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
+        gemm(x2, w, out, bias=bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.xshape = x.shape
+        return out.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if g2.stride(1) != 1 or (g2.stride(0) % 8):
+            g2 = g2.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.empty_like(x2)
+            gemm(g2, w, gx, a_mn=False, b_mn=True)                 # dX[T,K] = dY[T,N] . W[N,K]
+            gx = gx.view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            gw = torch.empty_like(w)
+            gemm(g2, x2, gw, a_mn=True, b_mn=True)                 # dW[N,K] = dY^T[N,T] . X[T,K]
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.float().sum(0).to(gy.dtype)
+        return gx, gw, gb
+
+
+def linear(x, w, bias=None, fp8: bool = False):
+    if not _is_bf16(x, w, bias) or (w.shape[0] % 8) or (w.shape[1] % 8):
+        return ref.linear(x, w, bias)
+    return _Linear.apply(x, w, bias)
+
+
+def linear_allgather(x, w, bias, seq_dim, fp8):
+    from ..parallel import fused_tp
+    return fused_tp.linear_allgather(x, w, bias, seq_dim)
+
+
+def linear_reducescatter(x, w, seq_dim, fp8):
+    from ..parallel import fused_tp
+    return fused_tp.linear_reducescatter(x, w, seq_dim)
+
+
+# ----------------------------------------------------------------------------- RMSNorm
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, form):
+        lib = require()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        T, D = x2.shape
+        y = torch.empty_like(x2)
+        a = torch.empty(T, dtype=torch.float32, device=x.device)
+        wc = w.contiguous()
+        _check(lib.sb_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), a.data_ptr(), T, D, eps, form, _stream()),
+               "rmsnorm_fwd")
+        _count()
+        ctx.save_for_backward(x2, wc, a)
+        ctx.meta = (eps, form, x.shape)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        lib = require()
+        x2, w, a = ctx.saved_tensors
+        eps, form, shape = ctx.meta
+        T, D = x2.shape
+        g2 = gy.reshape(T, D).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.zeros(D, dtype=torch.float32, device=x2.device)
+        _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                  T, D, eps, form, _stream()), "rmsnorm_bwd")
+        _count()
+        return dx.view(shape), dw.to(w.dtype), None, None
+
+
+def rmsnorm(x, weight, eps, form="te"):
+    if not _is_bf16(x, weight) or x.shape[-1] % 8 or x.shape[-1] > 16384:
+        return ref.rmsnorm(x, weight, eps, form)
+    return _RMSNorm.apply(x, weight, float(eps), 0 if form == "te" else 1)
+
+
+# ----------------------------------------------------------------------------- gated activation
+
+
+class _GluPacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ab, act):
+        lib = require()
+        ab2 = ab.reshape(-1, ab.shape[-1]).contiguous()
+        T, F2 = ab2.shape
+        Fh = F2 // 2
+        h = torch.empty((T, Fh), dtype=bf16, device=ab.device)
+        _check(lib.sb_glu_fwd(ab2.data_ptr(), h.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
+        _count()
+        ctx.save_for_backward(ab2)
+        ctx.meta = (act, ab.shape)
+        return h.view(*ab.shape[:-1], Fh)
+
+    @staticmethod
+    def backward(ctx, gh):
+        lib = require()
+        (ab2,) = ctx.saved_tensors
+        act, shape = ctx.meta
+        T, F2 = ab2.shape
+        g2 = gh.reshape(T, F2 // 2).contiguous()
+        dab = torch.empty_like(ab2)
+        _check(lib.sb_glu_bwd(ab2.data_ptr(), g2.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
+        _count()
+        return dab.view(shape), None
+
+
+def glu_act_packed(ab, act="silu"):
+    if not _is_bf16(ab) or (ab.shape[-1] // 2) % 8 or act not in _ACT:
+        a, b = ab.chunk(2, dim=-1)
+        return ref.glu_act(a, b, act)
+    return _GluPacked.apply(ab, _ACT[act])
+
+
+def glu_act(a, b, act="silu"):
+    return glu_act_packed(torch.cat([a, b], dim=-1), act)
+
+
+# ----------------------------------------------------------------------------- RoPE
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        y = _rope_launch(x, cos, sin, 0)
+        ctx.save_for_backward(cos, sin)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        cos, sin = ctx.saved_tensors
+        return _rope_launch(gy, cos, sin, 1), None, None
+
+
+def _rope_launch(x, cos, sin, inverse):
+    lib = require()
+    B, L, H, hd = x.shape
+    # rows (b,l,h) must be addressable with one stride: true for a slice of the packed [B,L,H,3*hd] projection
+    rs = x.stride(2)
+    if x.stride(3) != 1 or x.stride(1) != H * rs or x.stride(0) != L * H * rs or rs % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+        rs = hd
+    y = torch.empty((B, L, H, hd), dtype=bf16, device=x.device)
+    _check(lib.sb_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, L, H, hd, cos.shape[-1], rs, hd,
+                       inverse, _stream()), "rope")
+    _count()
+    return y
+
+
+def apply_rope(x, cos, sin):
+    if not _is_bf16(x) or x.shape[-1] % 8 or cos.shape[-1] % 16:
+        return ref.apply_rope(x, cos, sin)
+    return _Rope.apply(x, cos.float().contiguous(), sin.float().contiguous())
+
+
+# ----------------------------------------------------------------------------- attention
+
+
+def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False):
+    from . import attention_cuda
+    return attention_cuda.attention(q, k, v, causal, q_pos, k_pos, return_lse)
+
+
+# ----------------------------------------------------------------------------- cross entropy
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels):
+        lib = require()
+        V = logits.shape[-1]
+        l2 = logits.reshape(-1, V).contiguous()
+        lab = labels.reshape(-1).contiguous()
+        T = l2.shape[0]
+        loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+        lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+        _check(lib.sb_ce_fwd(l2.data_ptr(), lab.data_ptr(), loss.data_ptr(), lse.data_ptr(), T, V, _stream()), "ce_fwd")
+        _count()
+        ctx.save_for_backward(l2, lab, lse)
+        ctx.shape = logits.shape
+        return loss.view(labels.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        lib = require()
+        l2, lab, lse = ctx.saved_tensors
+        T, V = l2.shape
+        gc = g.reshape(-1).float().contiguous()
+        dl = torch.empty_like(l2)
+        _check(lib.sb_ce_bwd(l2.data_ptr(), lab.data_ptr(), lse.data_ptr(), gc.data_ptr(), dl.data_ptr(), T, V, _stream()),
+               "ce_bwd")
+        _count()
+        return dl.view(ctx.shape), None
+
+
+def cross_entropy(logits, labels):
+    if not _is_bf16(logits) or logits.shape[-1] % 8 or labels.dtype != torch.int64:
+        return ref.cross_entropy(logits, labels)
+    return _CrossEntropy.apply(logits, labels)
+
+
+# ----------------------------------------------------------------------------- optimizer pieces
+
+
+def sq_norm(x, weight=None):
+    if x.dtype not in (bf16, torch.float32) or not x.is_contiguous():
+        xf = x.float()
+        return (xf * xf * weight).sum() if weight is not None else (xf * xf).sum()
+    lib = require()
+    out = torch.zeros((), dtype=torch.float32, device=x.device)
+    _check(lib.sb_sqnorm(x.data_ptr(), _ptr(weight), out.data_ptr(), x.numel(), int(x.dtype == bf16), _stream()), "sqnorm")
+    _count()
+    return out
+
+
+def adam_step(master, exp_avg, exp_avg_sq, grad, lr, beta1, beta2, eps, weight_decay, step, adamw=True, grad_scale=1.0,
+              param_out=None):
+    ok = (master.dtype == torch.float32 and grad.dtype in (bf16, torch.float32) and grad.is_contiguous()
+          and (param_out is None or param_out.dtype == bf16))
+    if not ok:
+        return ref.adam_step(master, exp_avg, exp_avg_sq, grad, lr, beta1, beta2, eps, weight_decay, step, adamw,
+                             grad_scale, param_out)
+    lib = require()
+    if isinstance(grad_scale, torch.Tensor):
+        sp, sh = grad_scale.float().reshape(1), 1.0
+    else:
+        sp, sh = None, float(grad_scale)
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    _check(lib.sb_adam(master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(), _ptr(param_out),
+                       master.numel(), lr, beta1, beta2, eps, weight_decay, bc1, bc2, int(adamw), _ptr(sp), sh,
+                       int(grad.dtype == bf16), _stream()), "adam")
+    _count()
+
+
+# ----------------------------------------------------------------------------- short convolutions
+
+
+def _f32c(t):
+    return t.detach().float().contiguous()
+
+
+class _DwConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, halo):
+        lib = require()
+        B, L, C = x.shape
+        K = w.shape[-1]
+        xc = x.contiguous()
+        hc = halo.contiguous() if halo is not None else None
+        wf = _f32c(w)
+        y = torch.empty_like(xc)
+        _check(lib.sb_dwconv_fwd(xc.data_ptr(), _ptr(hc), wf.data_ptr(), y.data_ptr(), B, L, C, K, _stream()), "dwconv_fwd")
+        _count()
+        ctx.save_for_backward(xc, wf, hc if hc is not None else torch.empty(0, device=x.device))
+        ctx.meta = (halo is not None, w.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        lib = require()
+        xc, wf, hc = ctx.saved_tensors
+        has_halo, wdtype = ctx.meta
+        B, L, C = xc.shape
+        K = wf.shape[-1]
+        g = gy.contiguous()
+        dx = torch.empty_like(xc)
+        dh = torch.empty_like(hc) if has_halo else None
+        dw = torch.zeros_like(wf)
+        _check(lib.sb_dwconv_bwd(xc.data_ptr(), hc.data_ptr() if has_halo else None, wf.data_ptr(), g.data_ptr(),
+                                 dx.data_ptr(), _ptr(dh), dw.data_ptr(), B, L, C, K, _stream()), "dwconv_bwd")
+        _count()
+        return dx, dw.to(wdtype), dh
+
+
+def causal_conv1d(x, w, halo=None):
+    K = w.shape[-1]
+    if not _is_bf16(x, halo) or x.shape[-1] % 8 or not 2 <= K <= 8:
+        return ref.causal_conv1d(x, w, halo)
+    return _DwConv.apply(x, w, halo)
+
+
+class _HyenaSE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, feat, w, halo, pregate, postgate):
+        lib = require()
+        B, L, C3 = feat.shape
+        D = C3 // 3
+        G, K = w.shape
+        fc = feat.contiguous()
+        hc = halo.contiguous() if halo is not None else None
+        wf = _f32c(w)
+        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        _check(lib.sb_se_fwd(fc.data_ptr(), _ptr(hc), wf.data_ptr(), z.data_ptr(), B, L, D, G, K, int(pregate),
+                             int(postgate), _stream()), "se_fwd")
+        _count()
+        ctx.save_for_backward(fc, wf, hc if hc is not None else torch.empty(0, device=feat.device))
+        ctx.meta = (halo is not None, w.dtype, pregate, postgate)
+        return z
+
+    @staticmethod
+    def backward(ctx, gz):
+        lib = require()
+        fc, wf, hc = ctx.saved_tensors
+        has_halo, wdtype, pregate, postgate = ctx.meta
+        B, L, C3 = fc.shape
+        D = C3 // 3
+        G, K = wf.shape
+        g = gz.contiguous()
+        df = torch.empty_like(fc)
+        dh = torch.empty_like(hc) if has_halo else None
+        dw = torch.zeros_like(wf)
+        _check(lib.sb_se_bwd(fc.data_ptr(), hc.data_ptr() if has_halo else None, wf.data_ptr(), g.data_ptr(), df.data_ptr(),
+                             _ptr(dh), dw.data_ptr(), B, L, D, G, K, int(pregate), int(postgate), _stream()), "se_bwd")
+        _count()
+        return df, dw.to(wdtype), dh, None, None
+
+
+def hyena_se_inner(feat, w, halo=None, pregate=True, postgate=True):
+    K = w.shape[-1]
+    D = feat.shape[-1] // 3
+    if not _is_bf16(feat, halo) or D % 8 or not 2 <= K <= 8:
+        return ref.hyena_se_inner(feat, w, halo, pregate, postgate)
+    return _HyenaSE.apply(feat, w, halo, pregate, postgate)
+
+
+class _HyenaMR(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, feat, h, bias, halo):
+        lib = require()
+        B, L, C3 = feat.shape
+        D = C3 // 3
+        G, K = h.shape
+        fc = feat.contiguous()
+        hc = halo.contiguous() if halo is not None else None
+        hf, bf = _f32c(h), _f32c(bias)
+        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        need = any(ctx.needs_input_grad)
+        y = torch.empty_like(z) if need else None
+        _check(lib.sb_mr_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), _ptr(y), B, L, D, G, K,
+                             _stream()), "mr_fwd")
+        _count()
+        ctx.save_for_backward(fc, hf, bf, y if y is not None else torch.empty(0, device=feat.device),
+                              hc if hc is not None else torch.empty(0, device=feat.device))
+        ctx.meta = (halo is not None, h.dtype, bias.dtype)
+        return z
+
+    @staticmethod
+    def backward(ctx, gz):
+        lib = require()
+        fc, hf, bf, y, hc = ctx.saved_tensors
+        has_halo, hdtype, bdtype = ctx.meta
+        B, L, C3 = fc.shape
+        D = C3 // 3
+        G, K = hf.shape
+        g = gz.contiguous()
+        df = torch.empty_like(fc)
+        dhalo = torch.zeros_like(hc) if has_halo else None
+        dh = torch.zeros_like(hf)
+        db = torch.zeros_like(bf)
+        _check(lib.sb_mr_bwd(fc.data_ptr(), hc.data_ptr() if has_halo else None, hf.data_ptr(), bf.data_ptr(), g.data_ptr(),
+                             y.data_ptr(), df.data_ptr(), _ptr(dhalo), dh.data_ptr(), db.data_ptr(), B, L, D, G, K,
+                             _stream()), "mr_bwd")
+        _count(2)
+        return df, dh.to(hdtype), db.to(bdtype), dhalo
+
+
+def hyena_mr_inner(feat, h, bias, halo=None):
+    G, K = h.shape
+    D = feat.shape[-1] // 3
+    dg = D // G
+    if not _is_bf16(feat, halo) or K > 128 or D % G or ((64 % dg) and (dg % 64)):
+        return ref.hyena_mr_inner(feat, h, bias, halo)
+    return _HyenaMR.apply(feat, h, bias, halo)
+
+
+# ----------------------------------------------------------------------------- Hyena-LI (modal scan)
+
+LI_ORDER = 16
+LI_CHUNK = 128
+
+
+def _pad_order(t, fill):
+    D, O = t.shape
+    if O == LI_ORDER:
+        return t.contiguous()
+    out = torch.full((D, LI_ORDER), fill, dtype=torch.float32, device=t.device)
+    out[:, :O] = t
+    return out
+
+
+class _HyenaLI(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, feat, gamma, R, p, bias, state_in, want_state):
+        lib = require()
+        B, L, C3 = feat.shape
+        D = C3 // 3
+        O = gamma.shape[1]
+        fc = feat.contiguous()
+        loglam = -torch.exp(p.detach().float()) * torch.exp(gamma.detach().float())
+        ll = _pad_order(loglam, -1.0e30)
+        Rp = _pad_order(R.detach().float(), 0.0)
+        bf = _f32c(bias)
+        sin = None
+        if state_in is not None:
+            sin = torch.zeros((B, D, LI_ORDER), dtype=torch.float32, device=feat.device)
+            sin[..., :O] = state_in.detach().float()
+        NC = (L + LI_CHUNK - 1) // LI_CHUNK
+        S = torch.empty((B, NC, D, LI_ORDER), dtype=torch.float32, device=feat.device)
+        sout = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=feat.device) if want_state else None
+        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        _check(lib.sb_li_fwd(fc.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(), _ptr(sin), _ptr(sout), S.data_ptr(),
+                             z.data_ptr(), B, L, D, LI_CHUNK, _stream()), "li_fwd")
+        _count(3)
+        ctx.save_for_backward(fc, ll, Rp, bf, sin if sin is not None else torch.empty(0, device=feat.device))
+        ctx.meta = (O, state_in is not None, gamma.dtype, R.dtype, p.dtype, bias.dtype, want_state)
+        if want_state:
+            return z, sout[..., :O].contiguous()
+        return z, None
+
+    @staticmethod
+    def backward(ctx, gz, gstate):
+        lib = require()
+        fc, ll, Rp, bf, sin = ctx.saved_tensors
+        O, has_sin, gdt, rdt, pdt, bdt, want_state = ctx.meta
+        B, L, C3 = fc.shape
+        D = C3 // 3
+        dev = fc.device
+        NC = (L + LI_CHUNK - 1) // LI_CHUNK
+        g = gz.contiguous()
+        shape = (B, NC, D, LI_ORDER)
+        S, W, A, dRp, dLp = (torch.empty(shape, dtype=torch.float32, device=dev) for _ in range(5))
+        dBp = torch.empty((B, NC, D), dtype=torch.float32, device=dev)
+        tmp = torch.empty((B, L, D), dtype=bf16, device=dev)
+        df = torch.empty_like(fc)
+        dso = None
+        if want_state and gstate is not None:
+            dso = torch.zeros((B, D, LI_ORDER), dtype=torch.float32, device=dev)
+            dso[..., :O] = gstate.float()
+        w_end = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=dev) if dso is not None else None
+        dsi = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=dev) if has_sin else None
+        _check(lib.sb_li_bwd(fc.data_ptr(), g.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(),
+                             sin.data_ptr() if has_sin else None, _ptr(dso), S.data_ptr(), W.data_ptr(), A.data_ptr(),
+                             dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), tmp.data_ptr(), df.data_ptr(), _ptr(w_end),
+                             _ptr(dsi), B, L, D, LI_CHUNK, _stream()), "li_bwd")
+        _count(4)
+        dR = dRp.sum((0, 1))[:, :O]
+        dlam = dLp.sum((0, 1))
+        if dso is not None:
+            dlam = dlam + (dso * w_end).sum(0)
+        lam = torch.exp(ll)
+        dll = (dlam * lam * ll)[:, :O]          # d/dp = d/dgamma = dloglam * loglam
+        dll = torch.nan_to_num(dll, nan=0.0, posinf=0.0, neginf=0.0)
+        db = dBp.sum((0, 1))
+        return (df, dll.to(gdt), dR.to(rdt), dll.to(pdt), db.to(bdt), dsi[..., :O].contiguous() if has_sin else None, None)
+
+
+def hyena_li_modal(feat, gamma, R, p, bias, state_in=None, return_state=False):
+    if not _is_bf16(feat) or gamma.shape[1] > LI_ORDER:
+        return ref.hyena_li_modal(feat, gamma, R, p, bias, state_in, return_state)
+    z, s = _HyenaLI.apply(feat, gamma, R, p, bias, state_in, return_state)
+    return (z, s) if return_state else z

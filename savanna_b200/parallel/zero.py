@@ -35,7 +35,7 @@ class FlatGroup:
 
     def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, allocator=None):
         self.params = params
-        self.hyper = dict(hyper)
+        self.hyper = hyper
         dtype, device = params[0].dtype, params[0].device
         if any(p.dtype != dtype for p in params):
             raise ValueError("all parameters of a group must share a dtype")
@@ -58,7 +58,9 @@ class FlatGroup:
                 self.offsets.append(off)
                 off += n
         lo, hi = rank * self.shard, (rank + 1) * self.shard
-        self.master = self.flat_param[lo:hi].float().clone()
+        # fp32 parameters are their own master copy (the shard view is updated in place)
+        self.master = self.flat_param[lo:hi] if dtype == torch.float32 else self.flat_param[lo:hi].float().clone()
+        self.master_is_view = dtype == torch.float32
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.norm_weight: Optional[torch.Tensor] = None
@@ -106,12 +108,18 @@ class ZeroOptimizer:
             if not params:
                 continue
             hyper = {"lr": g.get("lr", lr), "weight_decay": g.get("weight_decay", weight_decay),
-                     "name": g.get("name", f"group{len(self.groups)}"), "lr_mult": g.get("lr", lr) / lr if lr else 1.0,
+                     "name": g.get("name", f"group{len(self.param_groups)}"), "lr_mult": g.get("lr", lr) / lr if lr else 1.0,
                      "fixed_lr": "lr" in g}
-            fg = FlatGroup(params, self.world, self.rank, hyper)
-            fg.build_norm_weight(tp)
-            self.groups.append(fg)
-            self.param_groups.append(fg.hyper)      # lr schedulers write `lr` here
+            self.param_groups.append(hyper)         # lr schedulers write `lr` here
+            # one flat buffer per dtype (low-precision weights and fp32 filter parameters share hyper-parameters)
+            by_dtype: Dict[torch.dtype, List] = {}
+            for q in params:
+                by_dtype.setdefault(q.dtype, []).append(q)
+            for dt, plist in by_dtype.items():
+                fg = FlatGroup(plist, self.world, self.rank, hyper)
+                fg.hyper = hyper                    # shared object: both flats follow the schedule
+                fg.build_norm_weight(tp)
+                self.groups.append(fg)
         self.grad_divisor = grad_divisor
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.fused = None                          # set by parallel.fused_zero.attach() on CUDA with symmetric memory
@@ -179,7 +187,8 @@ class ZeroOptimizer:
         b1, b2 = self.betas
         for g, s in zip(self.groups, shards):
             ops.adam_step(g.master, g.exp_avg, g.exp_avg_sq, s, g.hyper["lr"], b1, b2, self.eps,
-                          g.hyper["weight_decay"], self.step_count, self.adamw, coef, g.shard_slice(g.flat_param))
+                          g.hyper["weight_decay"], self.step_count, self.adamw, coef,
+                          None if g.master_is_view else g.shard_slice(g.flat_param))
             self._all_gather(g)
         return norm
 
@@ -225,9 +234,11 @@ class ZeroOptimizer:
 
     def refresh_master_from_params(self) -> None:
         for g in self.groups:
-            g.master.copy_(g.shard_slice(g.flat_param))
+            if not g.master_is_view:
+                g.master.copy_(g.shard_slice(g.flat_param))
 
     def sync_params_from_master(self) -> None:
         for g in self.groups:
-            g.shard_slice(g.flat_param).copy_(g.master)
+            if not g.master_is_view:
+                g.shard_slice(g.flat_param).copy_(g.master)
             self._all_gather(g)

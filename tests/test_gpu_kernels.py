@@ -1,0 +1,291 @@
+"""CUDA kernels against the fp32 PyTorch statement of the same operator (ops/reference.py).
+
+Tolerances follow the reference's kernel tests (bf16: 1e-3 relative on saved intermediates is too tight
+for outputs that are themselves rounded to bf16, so outputs are compared with the bf16 rounding error
+of the oracle result: atol/rtol 2e-2 on O(1) values; fp32 quantities (filter gradients, losses) use 1e-3
+relative to their scale)."""
+import math
+
+import pytest
+import torch
+
+from savanna_b200 import ops
+from savanna_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    scale = b.abs().max().clamp(min=1e-6)
+    err = (a - b).abs().max()
+    assert err <= atol * scale + rtol * scale, f"{what}: max err {err.item():.4g} vs scale {scale.item():.4g}"
+
+
+def _rel(a, b, tol, what=""):
+    a, b = a.float(), b.float()
+    denom = b.norm().clamp(min=1e-12)
+    r = (a - b).norm() / denom
+    assert r <= tol, f"{what}: relative L2 error {r.item():.4g} > {tol}"
+
+
+def _status_ok():
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 136), (1024, 768, 512), (8192, 512, 1024)])
+def test_gemm_tn(M, N, K):
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=BF)
+    b = torch.randn(N, K, device=DEV, dtype=BF)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=BF)
+    cuda_ops.gemm(a, b, out)
+    _status_ok()
+    _rel(out, a.float() @ b.float().t(), 1e-2, "gemm TN")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 520, 200)])
+def test_gemm_bias_accumulate(M, N, K):
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device=DEV, dtype=BF)
+    b = torch.randn(N, K, device=DEV, dtype=BF)
+    bias = torch.randn(N, device=DEV, dtype=BF)
+    c0 = torch.randn(M, N, device=DEV, dtype=BF)
+    out = c0.clone()
+    cuda_ops.gemm(a, b, out, bias=bias, accumulate=True)
+    _status_ok()
+    _rel(out, a.float() @ b.float().t() + bias.float() + c0.float(), 1e-2, "gemm bias+acc")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 320), (264, 136, 520)])
+def test_gemm_dgrad_layout(M, N, K):
+    """B given as its transpose storage [K, N] (weights in dgrad)."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device=DEV, dtype=BF)
+    bt = torch.randn(K, N, device=DEV, dtype=BF)
+    out = torch.empty(M, N, device=DEV, dtype=BF)
+    cuda_ops.gemm(a, bt, out, b_mn=True)
+    _status_ok()
+    _rel(out, a.float() @ bt.float(), 1e-2, "gemm A K-major, B MN-major")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 1000), (136, 264, 4096)])
+def test_gemm_wgrad_layout(M, N, K):
+    """Both operands stored with the reduction dim as the row index."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(3)
+    at = torch.randn(K, M, device=DEV, dtype=BF)
+    bt = torch.randn(K, N, device=DEV, dtype=BF)
+    out = torch.empty(M, N, device=DEV, dtype=BF)
+    cuda_ops.gemm(at, bt, out, a_mn=True, b_mn=True)
+    _status_ok()
+    _rel(out, at.float().t() @ bt.float(), 1e-2, "gemm both MN-major")
+
+
+def test_linear_autograd():
+    torch.manual_seed(4)
+    x = torch.randn(2, 96, 256, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(384, 256, device=DEV) * 0.05).to(BF).requires_grad_()
+    b = torch.randn(384, device=DEV, dtype=BF, requires_grad=True)
+    y = ops.linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = ref.linear(xr, wr, br)
+    yr.backward(g.float())
+    _status_ok()
+    _rel(y, yr, 1e-2, "linear fwd")
+    _rel(x.grad, xr.grad, 1e-2, "linear dx")
+    _rel(w.grad, wr.grad, 1e-2, "linear dw")
+    _rel(b.grad, br.grad, 1e-2, "linear db")
+
+
+@pytest.mark.parametrize("form", ["te", "classic"])
+@pytest.mark.parametrize("D", [256, 4096])
+def test_rmsnorm(form, D):
+    torch.manual_seed(5)
+    x = torch.randn(3, 50, D, device=DEV, dtype=BF, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(BF).requires_grad_()
+    y = ops.rmsnorm(x, w, 1e-6, form)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6, form)
+    yr.backward(g.float())
+    _close(y, yr, what="rmsnorm fwd")
+    _close(x.grad, xr.grad, what="rmsnorm dx")
+    _rel(w.grad, wr.grad, 2e-2, "rmsnorm dw")
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "identity"])
+def test_glu(act):
+    torch.manual_seed(6)
+    ab = torch.randn(4, 33, 2 * 688, device=DEV, dtype=BF, requires_grad=True)
+    h = ops.glu_act_packed(ab, act)
+    g = torch.randn_like(h)
+    h.backward(g)
+    abr = ab.detach().float().requires_grad_()
+    a, b = abr.chunk(2, -1)
+    hr = ref.glu_act(a, b, act)
+    hr.backward(g.float())
+    _close(h, hr, what="glu fwd")
+    _close(ab.grad, abr.grad, what="glu bwd")
+
+
+def test_rope():
+    torch.manual_seed(7)
+    B, L, H, hd = 2, 64, 4, 64
+    qkv = torch.randn(B, L, H, 3 * hd, device=DEV, dtype=BF, requires_grad=True)
+    pos = torch.arange(L, device=DEV)
+    cos, sin = ref.rope_tables(pos, hd)
+    q = qkv[..., :hd]
+    y = ops.apply_rope(q, cos, sin)
+    g = torch.randn_like(y)
+    y.backward(g)
+    qr = qkv.detach().float().requires_grad_()
+    yr = ref.apply_rope(qr[..., :hd], cos, sin)
+    yr.backward(g.float())
+    _close(y, yr, what="rope fwd")
+    _close(qkv.grad, qr.grad, what="rope bwd")
+
+
+def test_cross_entropy():
+    torch.manual_seed(8)
+    logits = (torch.randn(2, 100, 512, device=DEV) * 3).to(BF).requires_grad_()
+    labels = torch.randint(0, 512, (2, 100), device=DEV)
+    l = ops.cross_entropy(logits, labels)
+    w = torch.rand_like(l)
+    (l * w).sum().backward()
+    lr_ = logits.detach().float().requires_grad_()
+    lref = ref.cross_entropy(lr_, labels)
+    (lref * w).sum().backward()
+    _rel(l, lref, 1e-3, "ce fwd")
+    _close(logits.grad, lr_.grad, what="ce bwd")
+
+
+def test_sqnorm_adam():
+    torch.manual_seed(9)
+    n = 100_003
+    g = torch.randn(n, device=DEV).to(BF)
+    wgt = torch.rand(n, device=DEV)
+    _rel(ops.sq_norm(g), (g.float() ** 2).sum(), 1e-4, "sqnorm")
+    _rel(ops.sq_norm(g, wgt), (g.float() ** 2 * wgt).sum(), 1e-4, "weighted sqnorm")
+    master = torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p = torch.empty(n, device=DEV, dtype=BF)
+    mr, mm, vv = master.clone(), m.clone(), v.clone()
+    pr = torch.empty(n, device=DEV, dtype=BF)
+    scale = torch.tensor(0.5, device=DEV)
+    for step in (1, 2, 3):
+        ops.adam_step(master, m, v, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, True, scale, p)
+        ref.adam_step(mr, mm, vv, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, True, 0.5, pr)
+    _rel(master, mr, 1e-5, "adam master")
+    _rel(v, vv, 1e-5, "adam v")
+    assert torch.equal(p, master.to(BF))
+
+
+@pytest.mark.parametrize("K", [3, 4, 7])
+@pytest.mark.parametrize("halo", [False, True])
+def test_dwconv(K, halo):
+    torch.manual_seed(10)
+    B, L, C = 2, 300, 96
+    x = torch.randn(B, L, C, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(C, K, device=DEV) * 0.5).requires_grad_()
+    h = torch.randn(B, K - 1, C, device=DEV, dtype=BF, requires_grad=True) if halo else None
+    y = ops.causal_conv1d(x, w, h)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    hr = h.detach().float().requires_grad_() if halo else None
+    yr = ref.causal_conv1d(xr, wr, hr)
+    yr.backward(g.float())
+    _close(y, yr, what="dwconv fwd")
+    _close(x.grad, xr.grad, what="dwconv dx")
+    _rel(w.grad, wr.grad, 2e-2, "dwconv dw")
+    if halo:
+        _close(h.grad, hr.grad, what="dwconv dhalo")
+
+
+@pytest.mark.parametrize("K,G", [(7, 16), (3, 64), (7, 256)])
+@pytest.mark.parametrize("halo", [False, True])
+def test_hyena_se(K, G, halo):
+    torch.manual_seed(11)
+    B, L, D = 2, 200, 256
+    feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(G, K, device=DEV) * 0.4).requires_grad_()
+    h = torch.randn(B, K - 1, 3 * D, device=DEV, dtype=BF, requires_grad=True) if halo else None
+    z = ops.hyena_se_inner(feat, w, h)
+    g = torch.randn_like(z)
+    z.backward(g)
+    fr, wr = feat.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    hr = h.detach().float().requires_grad_() if halo else None
+    zr = ref.hyena_se_inner(fr, wr, hr)
+    zr.backward(g.float())
+    _close(z, zr, what="se fwd")
+    _close(feat.grad, fr.grad, what="se dfeat")
+    _rel(w.grad, wr.grad, 2e-2, "se dw")
+    if halo:
+        _close(h.grad, hr.grad, what="se dhalo")
+
+
+@pytest.mark.parametrize("K,G,L", [(128, 16, 400), (32, 16, 130), (128, 4, 256)])
+@pytest.mark.parametrize("halo", [False, True])
+def test_hyena_mr(K, G, L, halo):
+    torch.manual_seed(12)
+    B, D = 2, 256
+    feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
+    hflt = (torch.randn(G, K, device=DEV) * (1.0 / math.sqrt(K))).requires_grad_()
+    bias = torch.randn(D, device=DEV).requires_grad_()
+    h = torch.randn(B, K - 1, 3 * D, device=DEV, dtype=BF, requires_grad=True) if halo else None
+    z = ops.hyena_mr_inner(feat, hflt, bias, h)
+    g = torch.randn_like(z)
+    z.backward(g)
+    fr, hr_, br = feat.detach().float().requires_grad_(), hflt.detach().clone().requires_grad_(), bias.detach().clone().requires_grad_()
+    hh = h.detach().float().requires_grad_() if halo else None
+    zr = ref.hyena_mr_inner(fr, hr_, br, hh)
+    zr.backward(g.float())
+    _close(z, zr, what="mr fwd")
+    _close(feat.grad, fr.grad, what="mr dfeat")
+    _rel(hflt.grad, hr_.grad, 2e-2, "mr dh")
+    _rel(bias.grad, br.grad, 2e-2, "mr dbias")
+    if halo:
+        _close(h.grad, hh.grad, what="mr dhalo")
+
+
+@pytest.mark.parametrize("L,O,state", [(512, 16, False), (300, 8, False), (384, 16, True)])
+def test_hyena_li(L, O, state):
+    torch.manual_seed(13)
+    B, D = 2, 128
+    feat = (torch.randn(B, L, 3 * D, device=DEV) * 0.7).to(BF).requires_grad_()
+    gamma = (torch.rand(D, O, device=DEV) * 0.09 + 0.01).log().requires_grad_()
+    R = (0.1 * torch.randn(D, O, device=DEV) / math.sqrt(O)).requires_grad_()
+    p = (-torch.ones(D, O, device=DEV)).requires_grad_()
+    bias = torch.randn(D, device=DEV).requires_grad_()
+    s_in = torch.randn(B, D, O, device=DEV).requires_grad_() if state else None
+    out = ops.hyena_li_modal(feat, gamma, R, p, bias, s_in, state)
+    z, s_out = out if state else (out, None)
+    g = torch.randn_like(z)
+    gs = torch.randn_like(s_out) if state else None
+    loss = (z.float() * g.float()).sum() + ((s_out * gs).sum() if state else 0.0)
+    loss.backward()
+    leaves = [t.detach().float().requires_grad_() for t in (feat, gamma, R, p, bias)]
+    sr = s_in.detach().clone().requires_grad_() if state else None
+    outr = ref.hyena_li_modal(*leaves, sr, state)
+    zr, sor = outr if state else (outr, None)
+    lossr = (zr.float() * g.float()).sum() + ((sor * gs).sum() if state else 0.0)
+    lossr.backward()
+    _close(z, zr, what="li fwd")
+    _close(feat.grad, leaves[0].grad, rtol=3e-2, atol=3e-2, what="li dfeat")
+    _rel(R.grad, leaves[2].grad, 3e-2, "li dR")
+    _rel(gamma.grad, leaves[1].grad, 3e-2, "li dgamma")
+    _rel(p.grad, leaves[3].grad, 3e-2, "li dp")
+    _rel(bias.grad, leaves[4].grad, 3e-2, "li dbias")
+    if state:
+        _rel(s_out, sor, 1e-3, "li state_out")
+        _rel(s_in.grad, sr.grad, 3e-2, "li dstate_in")
