@@ -1,0 +1,203 @@
+"""Operator benchmark (BASELINE config 2 and the per-kernel roofline table): times this framework's CUDA
+kernels and, beside each, the PyTorch/library statement of the same operator, on the Evo-2-7B shapes
+(hidden 4096, 256 groups of 16 channels, filter lengths 3 / 7 / 128, modal order 16).
+
+    python bench_ops.py [--seq 8192] [--ops gemm,dwconv,se,mr,li,norm,glu,ce,adam] [--iters 10]
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB buffer write)
+between timed launches.  Rooflines use MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 throughput) when
+present, else the fallback figures 6.65 TB/s / 1.59 PFLOP/s.  One JSON line per measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from savanna_b200 import ops  # noqa: E402
+from savanna_b200.ops import reference as ref  # noqa: E402
+from savanna_b200.utils.mfu import measured_peaks  # noqa: E402
+
+BF = torch.bfloat16
+
+
+def peaks():
+    m = measured_peaks() or {}
+    return float(m.get("hbm_gbs", 6650.0)) * 1e9, float(m.get("bf16_tflops", 1590.0)) * 1e12, ("measured" if m else "fallback")
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def timeit(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(name, ms, flops=None, bytes_=None, **kw):
+    bw, tf, src = peaks()
+    rec = {"op": name, "ms": round(ms, 4)}
+    if flops:
+        rec["tflops"] = round(flops / ms / 1e9, 1)
+        rec["frac_of_gemm_peak"] = round(flops / (ms / 1e3) / tf, 3)
+    if bytes_:
+        rec["gbs"] = round(bytes_ / ms / 1e6, 1)
+        rec["frac_of_copy_bw"] = round(bytes_ / (ms / 1e3) / bw, 3)
+    rec["peaks"] = src
+    rec.update(kw)
+    print(json.dumps(rec), flush=True)
+
+
+def bench_gemm(T, iters):
+    from savanna_b200.ops import cuda_ops
+    D, F = 4096, 11264
+    shapes = [("in_proj", T, 3 * D, D), ("out_proj", T, D, D), ("mlp_w12", T, 2 * F, D), ("mlp_w3", T, D, F), ("logits", T, 512, D)]
+    for name, M, N, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=BF)
+        w = torch.randn(N, K, device="cuda", dtype=BF) * 0.02
+        gy = torch.randn(M, N, device="cuda", dtype=BF)
+        out = torch.empty(M, N, device="cuda", dtype=BF)
+        gx, gw = torch.empty_like(x), torch.empty_like(w)
+        fl = 2.0 * M * N * K
+        report(f"gemm.{name}.fwd.ours", timeit(lambda: cuda_ops.gemm(x, w, out), iters), fl, M=M, N=N, K=K)
+        report(f"gemm.{name}.fwd.cublas", timeit(lambda: torch.matmul(x, w.t(), out=out), iters), fl)
+        report(f"gemm.{name}.dgrad.ours", timeit(lambda: cuda_ops.gemm(gy, w, gx, b_mn=True), iters), fl)
+        report(f"gemm.{name}.dgrad.cublas", timeit(lambda: torch.matmul(gy, w, out=gx), iters), fl)
+        report(f"gemm.{name}.wgrad.ours", timeit(lambda: cuda_ops.gemm(gy, x, gw, a_mn=True, b_mn=True), iters), fl)
+        report(f"gemm.{name}.wgrad.cublas", timeit(lambda: torch.matmul(gy.t(), x, out=gw), iters), fl)
+        cuda_ops.check_status()
+
+
+def _fwd_bwd(fn, inputs, iters):
+    outs = fn(*inputs)
+    out = outs[0] if isinstance(outs, tuple) else outs
+    g = torch.randn_like(out)
+    f_ms = timeit(lambda: fn(*inputs), iters)
+
+    def fb():
+        for t in inputs:
+            if isinstance(t, torch.Tensor) and t.grad is not None:
+                t.grad = None
+        o = fn(*inputs)
+        o = o[0] if isinstance(o, tuple) else o
+        o.backward(g)
+    fb_ms = timeit(fb, iters)
+    return f_ms, fb_ms - f_ms
+
+
+def bench_convs(L, iters, which):
+    D, G = 4096, 256
+    B = 1
+    feat = torch.randn(B, L, 3 * D, device="cuda", dtype=BF, requires_grad=True)
+    proj = torch.randn(B, L, 3 * D, device="cuda", dtype=BF, requires_grad=True)
+    nb = B * L * D * 2
+    for backend in ("auto", "torch"):
+        ops.set_backend(backend)
+        tag = "ours" if backend == "auto" else "torch"
+        if backend == "torch" and L > 32768:
+            continue
+        if "dwconv" in which:
+            w = torch.randn(3 * D, 3, device="cuda", requires_grad=True)
+            f, b = _fwd_bwd(lambda x, w_: ops.causal_conv1d(x, w_), (proj, w), iters)
+            report(f"featurizer_conv3.fwd.{tag}", f, None, 6 * nb, L=L)
+            report(f"featurizer_conv3.bwd.{tag}", b, None, 9 * nb, L=L)
+        if "se" in which:
+            w = torch.randn(G, 7, device="cuda", requires_grad=True)
+            f, b = _fwd_bwd(lambda x, w_: ops.hyena_se_inner(x, w_), (feat, w), iters)
+            report(f"hyena_se_k7.fwd.{tag}", f, None, 4 * nb, L=L)
+            report(f"hyena_se_k7.bwd.{tag}", b, None, 7 * nb, L=L)
+        if "mr" in which:
+            h = (torch.randn(G, 128, device="cuda") / 11.3).requires_grad_()
+            bias = torch.randn(D, device="cuda", requires_grad=True)
+            f, b = _fwd_bwd(lambda x, h_, b_: ops.hyena_mr_inner(x, h_, b_), (feat, h, bias), iters)
+            fl = 2.0 * 128 * B * L * D
+            report(f"hyena_mr_k128.fwd.{tag}", f, fl, 4 * nb, L=L)
+            report(f"hyena_mr_k128.bwd.{tag}", b, 2 * fl, 8 * nb, L=L)
+        if "li" in which:
+            O = 16
+            gamma = (torch.rand(D, O, device="cuda") * 0.09 + 0.01).log().requires_grad_()
+            R = (0.1 * torch.randn(D, O, device="cuda") / 4).requires_grad_()
+            p = (-torch.ones(D, O, device="cuda")).requires_grad_()
+            bias = torch.randn(D, device="cuda", requires_grad=True)
+            f, b = _fwd_bwd(lambda x, g_, r_, p_, b_: ops.hyena_li_modal(x, g_, r_, p_, b_), (feat, gamma, R, p, bias), iters)
+            report(f"hyena_li_modal16.fwd.{tag}", f, None, 7 * nb, L=L)
+            report(f"hyena_li_modal16.bwd.{tag}", b, None, 17 * nb, L=L)
+    ops.set_backend("auto")
+
+
+def bench_elementwise(T, iters, which):
+    D, F = 4096, 11264
+    for backend in ("auto", "torch"):
+        ops.set_backend(backend)
+        tag = "ours" if backend == "auto" else "torch"
+        if "norm" in which:
+            x = torch.randn(T, D, device="cuda", dtype=BF, requires_grad=True)
+            w = torch.ones(D, device="cuda", dtype=BF, requires_grad=True)
+            f, b = _fwd_bwd(lambda x_, w_: ops.rmsnorm(x_, w_, 1e-6, "te"), (x, w), iters)
+            report(f"rmsnorm.fwd.{tag}", f, None, 2 * T * D * 2)
+            report(f"rmsnorm.bwd.{tag}", b, None, 3 * T * D * 2)
+        if "glu" in which:
+            ab = torch.randn(T, 2 * F, device="cuda", dtype=BF, requires_grad=True)
+            f, b = _fwd_bwd(lambda t: ops.glu_act_packed(t, "silu"), (ab,), iters)
+            report(f"swiglu.fwd.{tag}", f, None, 3 * T * F * 2)
+            report(f"swiglu.bwd.{tag}", b, None, 5 * T * F * 2)
+        if "ce" in which:
+            lg = torch.randn(T, 512, device="cuda", dtype=BF, requires_grad=True)
+            lab = torch.randint(0, 512, (T,), device="cuda")
+            f, b = _fwd_bwd(lambda t: ops.cross_entropy(t, lab), (lg,), iters)
+            report(f"cross_entropy.fwd.{tag}", f, None, T * 512 * 2)
+            report(f"cross_entropy.bwd.{tag}", b, None, 2 * T * 512 * 2)
+    ops.set_backend("auto")
+    if "adam" in which:
+        n = 256 * 1024 * 1024
+        master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+        g = torch.randn(n, device="cuda", dtype=BF)
+        p = torch.empty(n, device="cuda", dtype=BF)
+        ms = timeit(lambda: ops.adam_step(master, m, v, g, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, True, 1.0, p), iters)
+        report("adam.ours", ms, None, n * 28, n=n)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--ops", type=str, default="gemm,dwconv,se,mr,li,norm,glu,ce,adam")
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    which = set(a.ops.split(","))
+    torch.cuda.set_device(0)
+    if "gemm" in which:
+        bench_gemm(a.seq, a.iters)
+    if which & {"dwconv", "se", "mr", "li"}:
+        bench_convs(a.seq, a.iters, which)
+    if which & {"norm", "glu", "ce", "adam"}:
+        bench_elementwise(a.seq, a.iters, which)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,343 @@
+"""Checkpoint save / load in the DeepSpeed directory layout the reference produces, so its tools
+(tensor-parallel reshard, projection interleave, filter extension, zero_to_fp32, vortex export) keep
+working on files written here and its checkpoints load here.
+
+    <save>/latest                                   text: "global_step<N>"
+    <save>/global_step<N>/mp_rank_<TP:02d>_model_states.pt
+        module (state dict, keys `sequential.<i>...`), param_shapes, buffer_names, shared_params,
+        frozen_param_shapes, ds_config, ds_version, dp_world_size, mp_world_size, lr_scheduler,
+        + client state: iteration, args, data_loading, RNG states, optional validation logits
+    <save>/global_step<N>/[bf16_]zero_pp_rank_<DP>_mp_rank_<TP:02d>_optim_states.pt
+        optimizer_state_dict (ZeRO stage-1 shaped, see parallel/zero.py), ds_config, ds_version
+    <save>/global_step<N>/configs/*.yml             the raw YAML files of the run
+
+Behaviour (reference: savanna/checkpointing.py:153-571): tag `global_step<N>`; `latest` is reconciled
+with the directories on disk (the older of the two wins, so a half-written newest checkpoint is
+skipped); keep-last-N deletion; optional background (async) writing finalised at the next step;
+finetune = module only and iteration 0; `no_load_optim` / `no_load_rng`; strict toggle; optional
+forward-pass logits validation; data cursor (`train_data_token_index`) and LR-scheduler restore.
+"""
+from __future__ import annotations
+
+import glob
+import os
+import random
+import re
+import shutil
+import threading
+import time
+from collections import OrderedDict
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import __version__, print_rank_0
+from ..parallel import state
+
+DS_VERSION = "0.14.0+savanna_b200." + __version__
+_ASYNC: Dict[str, threading.Thread] = {}
+
+ARGS_TO_CHECK = ("num_layers", "hidden_size", "num_attention_heads", "max_position_embeddings", "make_vocab_size_divisible_by",
+                 "padded_vocab_size", "tokenizer_type", "model_parallel_size")
+
+
+def checkpoint_dir(root: str, iteration: int) -> str:
+    return os.path.join(root, f"global_step{iteration}")
+
+
+def model_states_name(tp_rank: int) -> str:
+    return f"mp_rank_{tp_rank:02d}_model_states.pt"
+
+
+def optim_states_name(dp_rank: int, tp_rank: int, bf16: bool) -> str:
+    return f"{'bf16_' if bf16 else ''}zero_pp_rank_{dp_rank}_mp_rank_{tp_rank:02d}_optim_states.pt"
+
+
+def _barrier():
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+def _rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+# ----------------------------------------------------------------------------- global step resolution
+
+
+def read_global_step(load_dir: str) -> Optional[int]:
+    """Iteration to resume from: min(latest file, newest global_step directory), None if nothing usable."""
+    latest = None
+    p = os.path.join(load_dir, "latest")
+    if os.path.isfile(p):
+        m = re.match(r"global_step(\d+)", open(p).read().strip())
+        if m:
+            latest = int(m.group(1))
+    on_disk = []
+    for d in glob.glob(os.path.join(load_dir, "global_step*")):
+        m = re.match(r"global_step(\d+)$", os.path.basename(d))
+        if m and os.path.isdir(d):
+            on_disk.append(int(m.group(1)))
+    if latest is None and not on_disk:
+        return None
+    if latest is None:
+        return max(on_disk)
+    if not on_disk:
+        return None
+    newest = max(on_disk)
+    step = min(latest, newest)
+    if step not in on_disk:
+        older = [s for s in on_disk if s <= step]
+        return max(older) if older else None
+    return step
+
+
+# ----------------------------------------------------------------------------- save
+
+
+def _client_state(trainer) -> Dict:
+    cfg = trainer.cfg
+    sd = {
+        "iteration": trainer.iteration,
+        "args": {k: getattr(cfg, k) for k in ARGS_TO_CHECK},
+        "data_loading": {
+            "train_data_token_index": trainer.tokens_seen,
+            "train_val_test_num_samples": cfg.train_val_test_num_samples,
+        },
+    }
+    if not cfg.no_save_rng:
+        sd["random_rng_state"] = random.getstate()
+        sd["np_rng_state"] = np.random.get_state()
+        sd["torch_rng_state"] = torch.get_rng_state()
+        sd["cuda_rng_state"] = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
+        sd["rng_tracker_states"] = {}
+    return sd
+
+
+def _param_shapes(trainer):
+    names = {id(p): n for n, p in trainer.model.named_parameters()}
+    out = []
+    opt = trainer.optimizer
+    if hasattr(opt, "groups"):
+        for g in opt.groups:
+            out.append(OrderedDict((names[id(p)], p.shape) for p in g.params))
+    else:
+        out.append(OrderedDict((n, p.shape) for n, p in trainer.model.named_parameters()))
+    return out
+
+
+def _write(obj, path: str) -> None:
+    tmp = path + ".tmp"
+    torch.save(obj, tmp)
+    os.replace(tmp, path)
+
+
+def _to_cpu(obj):
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().to("cpu", copy=True)
+    if isinstance(obj, dict):
+        return type(obj)((k, _to_cpu(v)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_cpu(v) for v in obj)
+    return obj
+
+
+def finalize_async_save(blocking: bool = True) -> None:
+    for tag, th in list(_ASYNC.items()):
+        if blocking or not th.is_alive():
+            th.join()
+            _ASYNC.pop(tag, None)
+
+
+def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
+    cfg = trainer.cfg
+    it = trainer.iteration if iteration is None else iteration
+    root = cfg.save
+    d = checkpoint_dir(root, it)
+    tp_rank = state.get_model_parallel_rank()
+    zero_rank = state.get_sequence_data_parallel_rank()
+    bf16 = cfg.precision == "bfloat16"
+    finalize_async_save(True)
+    if _rank() == 0:
+        os.makedirs(d, exist_ok=True)
+    _barrier()
+    files = {}
+    if zero_rank == 0:
+        ms = {
+            "module": trainer.model.state_dict(),
+            "buffer_names": [n for n, _ in trainer.model.named_buffers()],
+            "param_shapes": _param_shapes(trainer),
+            "frozen_param_shapes": None,
+            "shared_params": {},
+            "frozen_param_fragments": None,
+            "lr_scheduler": trainer.lr_scheduler.state_dict() if trainer.lr_scheduler is not None else None,
+            "optimizer": None,
+            "sparse_tensor_module_names": [],
+            "skipped_steps": trainer.skipped_iters,
+            "global_steps": it,
+            "global_samples": it * cfg.train_batch_size,
+            "dp_world_size": state.get_sequence_data_parallel_world_size(),
+            "mp_world_size": state.get_model_parallel_world_size(),
+            "ds_config": cfg.engine_config,
+            "ds_version": DS_VERSION,
+        }
+        ms.update(_client_state(trainer))
+        files[os.path.join(d, model_states_name(tp_rank))] = ms
+    if not cfg.no_save_optim and hasattr(trainer.optimizer, "state_dict"):
+        files[os.path.join(d, optim_states_name(zero_rank, tp_rank, bf16))] = {
+            "optimizer_state_dict": trainer.optimizer.state_dict(),
+            "ds_config": cfg.engine_config,
+            "ds_version": DS_VERSION,
+        }
+
+    def write_all(objs):
+        for path, obj in objs.items():
+            _write(obj, path)
+
+    if cfg.async_save:
+        snap = {p: _to_cpu(o) for p, o in files.items()}
+        th = threading.Thread(target=write_all, args=(snap,), daemon=False)
+        th.start()
+        _ASYNC[f"global_step{it}"] = th
+    else:
+        write_all(files)
+    if _rank() == 0:
+        if cfg.config_files:
+            cdir = os.path.join(d, "configs")
+            os.makedirs(cdir, exist_ok=True)
+            for name, text in cfg.config_files.items():
+                with open(os.path.join(cdir, name), "w") as fh:
+                    fh.write(text)
+    if not cfg.async_save:
+        _barrier()
+    else:
+        finalize_async_save(True)
+        _barrier()
+    if _rank() == 0:
+        with open(os.path.join(root, "latest"), "w") as fh:
+            fh.write(f"global_step{it}")
+        if cfg.keep_last_n_checkpoints:
+            _delete_old(root, cfg.keep_last_n_checkpoints)
+        if cfg.checkpoint_stores:
+            _upload(cfg, d)
+    _barrier()
+    print_rank_0(f"  saved checkpoint at iteration {it} to {d}")
+    return d
+
+
+def _delete_old(root: str, keep: int) -> None:
+    steps = sorted(int(re.match(r"global_step(\d+)$", os.path.basename(p)).group(1))
+                   for p in glob.glob(os.path.join(root, "global_step*")) if re.match(r"global_step(\d+)$", os.path.basename(p)))
+    for s in steps[:-keep] if keep > 0 else []:
+        shutil.rmtree(os.path.join(root, f"global_step{s}"), ignore_errors=True)
+
+
+def _upload(cfg, ckpt_dir: str, retries: int = 3) -> None:
+    """Copy a finished checkpoint to every configured store.  A `.uploading` marker is written first and
+    replaced by `.uploaded` on success, so deletion never removes a checkpoint that is not safely stored
+    (reference: checkpointing.py:187-291).  Only the "posix" store type is built in; "s3" needs boto3."""
+    for store in cfg.checkpoint_stores or []:
+        kind = store.get("storage_type", "posix")
+        dst_root = store.get("location")
+        if kind != "posix":
+            try:
+                import boto3  # noqa: F401
+            except ImportError:
+                print_rank_0(f"  checkpoint store {kind!r} needs boto3, which is not installed; skipping upload")
+                continue
+        dst = os.path.join(dst_root, os.path.basename(ckpt_dir))
+        marker = os.path.join(ckpt_dir, ".uploading")
+        open(marker, "w").close()
+        delay = 1.0
+        for attempt in range(retries):
+            try:
+                shutil.copytree(ckpt_dir, dst, dirs_exist_ok=True, ignore=shutil.ignore_patterns(".uploading", ".uploaded"))
+                os.replace(marker, os.path.join(ckpt_dir, ".uploaded"))
+                break
+            except OSError as exc:
+                print_rank_0(f"  upload attempt {attempt + 1} failed: {exc}")
+                time.sleep(delay)
+                delay *= 2
+
+
+# ----------------------------------------------------------------------------- load
+
+
+def _check_args(cfg, saved: Dict) -> None:
+    for k, v in (saved or {}).items():
+        mine = getattr(cfg, k, None)
+        if mine != v:
+            print_rank_0(f"  WARNING: checkpoint was written with {k}={v!r}, current configuration has {mine!r}")
+
+
+def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
+    cfg = trainer.cfg
+    load_dir = cfg.load
+    it = iteration if iteration is not None else (cfg.iteration if cfg.iteration is not None else read_global_step(load_dir))
+    if it is None:
+        print_rank_0(f"  no checkpoint found in {load_dir}; starting from scratch")
+        return 0
+    d = checkpoint_dir(load_dir, it)
+    tp_rank = state.get_model_parallel_rank()
+    zero_rank = state.get_sequence_data_parallel_rank()
+    path = os.path.join(d, model_states_name(tp_rank))
+    if not os.path.isfile(path):
+        raise FileNotFoundError(f"checkpoint file {path} not found")
+    dev = trainer.device
+    ms = torch.load(path, map_location="cpu", weights_only=False)
+    _check_args(cfg, ms.get("args"))
+    missing, unexpected = trainer.model.load_state_dict(ms["module"], strict=False)
+    # buffers that are recomputed (rotary tables, filter time index) may be absent in foreign checkpoints
+    missing = [k for k in missing if not k.endswith((".inv_freq", ".filter.t", ".decay"))]
+    if cfg.checkpoint_strict_load and (missing or unexpected):
+        raise RuntimeError(f"checkpoint does not match the model: missing {missing[:8]}, unexpected {unexpected[:8]}")
+    module_only = cfg.finetune or cfg.no_load_optim
+    opt = trainer.optimizer
+    bf16 = cfg.precision == "bfloat16"
+    if not module_only and hasattr(opt, "load_state_dict"):
+        opath = os.path.join(d, optim_states_name(zero_rank, tp_rank, bf16))
+        if os.path.isfile(opath):
+            osd = torch.load(opath, map_location=dev, weights_only=False)
+            opt.load_state_dict(osd["optimizer_state_dict"])
+        else:
+            print_rank_0(f"  optimizer state {opath} not found; master weights are rebuilt from the module")
+            if hasattr(opt, "refresh_master_from_params"):
+                opt.refresh_master_from_params()
+    elif hasattr(opt, "refresh_master_from_params"):
+        opt.refresh_master_from_params()
+    if cfg.finetune:
+        it_out = 0
+    else:
+        it_out = int(ms.get("iteration", it))
+        if trainer.lr_scheduler is not None and ms.get("lr_scheduler") is not None and not cfg.no_load_optim:
+            trainer.lr_scheduler.load_state_dict(ms["lr_scheduler"])
+        dl = ms.get("data_loading") or {}
+        if dl.get("train_data_token_index") is not None:
+            trainer.tokens_seen = int(dl["train_data_token_index"])
+            cfg.train_data_token_index = trainer.tokens_seen
+        if cfg.use_checkpoint_num_samples and dl.get("train_val_test_num_samples") is not None:
+            cfg.train_val_test_num_samples = dl["train_val_test_num_samples"]
+        if not cfg.no_load_rng and "torch_rng_state" in ms:
+            random.setstate(ms["random_rng_state"])
+            np.random.set_state(ms["np_rng_state"])
+            torch.set_rng_state(ms["torch_rng_state"])
+            if torch.cuda.is_available() and ms.get("cuda_rng_state") is not None and dev.type == "cuda":
+                torch.cuda.set_rng_state(ms["cuda_rng_state"])
+    if cfg.checkpoint_validation_with_forward_pass and "checkpoint_validation_logits" in ms:
+        _validate_logits(trainer, ms)
+    _barrier()
+    print_rank_0(f"  loaded checkpoint {d} (iteration {it_out})")
+    return it_out
+
+
+@torch.no_grad()
+def _validate_logits(trainer, ms) -> None:
+    tokens = ms["checkpoint_validation_input"].to(trainer.device)
+    ref_logits = ms["checkpoint_validation_logits"].to(trainer.device)
+    trainer.model.eval()
+    out = trainer.model(tokens)
+    trainer.model.train()
+    if not torch.allclose(out.float(), ref_logits.float(), atol=1e-2, rtol=1e-2):
+        raise RuntimeError("forward pass after loading does not reproduce the logits stored with the checkpoint")

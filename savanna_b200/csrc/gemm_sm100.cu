@@ -238,6 +238,8 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
+static int g_last_encode_result = 0;
+
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride `ld` elements.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer) {
@@ -250,12 +252,16 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_last_encode_result = (int)r;
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
 static int g_num_sms = 0;
+static int g_last_detail = 0;   // (which operand << 16) | CUresult of the last failed tensor-map encode
 
 }  // namespace sb
+
+extern "C" int sb_gemm_last_error_detail() { return sb::g_last_detail; }
 
 // C = A * B^T (+bias) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
 // transposed as [K, M] with leading dim lda.  b_mn likewise for B ([N, K] or [K, N]).  All leading dims and
@@ -271,10 +277,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   int rc;
   if (!a_mn) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, BM);
   else       rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, 64, BK);
-  if (rc) return rc;
+  if (rc) { g_last_detail = (1 << 16) | (g_last_encode_result & 0xffff); return rc; }
   if (!b_mn) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, BN);
   else       rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK);
-  if (rc) return rc;
+  if (rc) { g_last_detail = (2 << 16) | (g_last_encode_result & 0xffff); return rc; }
   if (!g_num_sms) {
     int dev = 0;
     cudaGetDevice(&dev);

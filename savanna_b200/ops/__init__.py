@@ -131,8 +131,10 @@ def apply_rope(x, cos, sin):
 
 
 def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False):
-    if _k(q):
-        return _co().attention(q, k, v, causal, q_pos, k_pos, return_lse)
+    if q.is_cuda:
+        # CUDA tensors never materialise the score matrix: own flash kernel, or (backend "torch") PyTorch's
+        from . import attention_cuda
+        return attention_cuda.attention(q, k, v, causal, q_pos, k_pos, return_lse, own_kernels=_k(q))
     return ref.attention(q, k, v, causal, q_pos, k_pos, return_lse)
 
 

@@ -131,7 +131,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False
     rc = lib.sb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), M, N, K, a.stride(0), b.stride(0),
                           out.stride(0), int(a_mn), int(b_mn), int(accumulate), status_word(out.device).data_ptr(),
                           max_ctas, _stream())
-    _check(rc, "gemm_bf16")
+    if rc != 0:
+        detail = lib.sb_gemm_last_error_detail()
+        raise RuntimeError(f"gemm_bf16 failed (code {rc}, operand {detail >> 16}, driver result {detail & 0xffff}): "
+                           f"M={M} N={N} K={K} a{tuple(a.shape)}/{a.stride()} b{tuple(b.shape)}/{b.stride()} "
+                           f"out{tuple(out.shape)}/{out.stride()} a_mn={a_mn} b_mn={b_mn} "
+                           f"ptrs {a.data_ptr():#x} {b.data_ptr():#x} {out.data_ptr():#x}")
     _count()
     return out
 
@@ -305,9 +310,6 @@ def apply_rope(x, cos, sin):
 # ----------------------------------------------------------------------------- attention
 
 
-def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False):
-    from . import attention_cuda
-    return attention_cuda.attention(q, k, v, causal, q_pos, k_pos, return_lse)
 
 
 # ----------------------------------------------------------------------------- cross entropy
