@@ -139,6 +139,7 @@ class GlobalConfig:
         self.causal = True
         self.tokenizer = None
         self.tensorboard_writer = None
+        self.validate_types()          # user-supplied values first, so derivation never sees a wrong type
         self.calculate_derived()
         self.validate_types()
         self.validate_values()

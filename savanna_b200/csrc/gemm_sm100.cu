@@ -271,6 +271,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
                             cudaStream_t stream) {
   using namespace sb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // The tensor-map encoder is a driver call and needs a current context; a thread that has made no runtime call
+  // yet (e.g. an autograd worker on its first launch) has none until the runtime binds the primary context.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
   if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (a_mn && (M % 8))) return -3;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
   CUtensorMap tmA, tmB;

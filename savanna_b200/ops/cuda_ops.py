@@ -66,6 +66,8 @@ class _Sig:
     sb_se_bwd = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
     sb_mr_fwd = [P, P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_bwd = [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
+    sb_mr_tc_fwd = [P, P, P, P, P, I, I, I, I, I, P]
+    sb_mr_tc_bwd = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
     sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
 
@@ -475,6 +477,9 @@ def hyena_se_inner(feat, w, halo=None, pregate=True, postgate=True):
 
 
 class _HyenaMR(torch.autograd.Function):
+    """Tensor-core kernels (csrc/mr_conv_tc.cu) when a 16-channel slab shares one filter (dg % 16 == 0), else the
+    CUDA-core kernels (csrc/mr_conv.cu)."""
+
     @staticmethod
     def forward(ctx, feat, h, bias, halo):
         lib = require()
@@ -485,21 +490,26 @@ class _HyenaMR(torch.autograd.Function):
         hc = halo.contiguous() if halo is not None else None
         hf, bf = _f32c(h), _f32c(bias)
         z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
-        need = any(ctx.needs_input_grad)
-        y = torch.empty_like(z) if need else None
-        _check(lib.sb_mr_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), _ptr(y), B, L, D, G, K,
-                             _stream()), "mr_fwd")
+        tc = (D // G) % 16 == 0 and D % 8 == 0
+        y = None
+        if tc:
+            _check(lib.sb_mr_tc_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), B, L, D, G, K,
+                                    _stream()), "mr_tc_fwd")
+        else:
+            y = torch.empty_like(z) if any(ctx.needs_input_grad) else None
+            _check(lib.sb_mr_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), _ptr(y), B, L, D, G, K,
+                                 _stream()), "mr_fwd")
         _count()
-        ctx.save_for_backward(fc, hf, bf, y if y is not None else torch.empty(0, device=feat.device),
-                              hc if hc is not None else torch.empty(0, device=feat.device))
-        ctx.meta = (halo is not None, h.dtype, bias.dtype)
+        empty = torch.empty(0, device=feat.device)
+        ctx.save_for_backward(fc, hf, bf, y if y is not None else empty, hc if hc is not None else empty)
+        ctx.meta = (halo is not None, h.dtype, bias.dtype, tc)
         return z
 
     @staticmethod
     def backward(ctx, gz):
         lib = require()
         fc, hf, bf, y, hc = ctx.saved_tensors
-        has_halo, hdtype, bdtype = ctx.meta
+        has_halo, hdtype, bdtype, tc = ctx.meta
         B, L, C3 = fc.shape
         D = C3 // 3
         G, K = hf.shape
@@ -508,10 +518,15 @@ class _HyenaMR(torch.autograd.Function):
         dhalo = torch.zeros_like(hc) if has_halo else None
         dh = torch.zeros_like(hf)
         db = torch.zeros_like(bf)
-        _check(lib.sb_mr_bwd(fc.data_ptr(), hc.data_ptr() if has_halo else None, hf.data_ptr(), bf.data_ptr(), g.data_ptr(),
-                             y.data_ptr(), df.data_ptr(), _ptr(dhalo), dh.data_ptr(), db.data_ptr(), B, L, D, G, K,
-                             _stream()), "mr_bwd")
-        _count(2)
+        hp = hc.data_ptr() if has_halo else None
+        if tc:
+            _check(lib.sb_mr_tc_bwd(fc.data_ptr(), hp, hf.data_ptr(), bf.data_ptr(), g.data_ptr(), df.data_ptr(), _ptr(dhalo),
+                                    dh.data_ptr(), db.data_ptr(), B, L, D, G, K, _stream()), "mr_tc_bwd")
+            _count()
+        else:
+            _check(lib.sb_mr_bwd(fc.data_ptr(), hp, hf.data_ptr(), bf.data_ptr(), g.data_ptr(), y.data_ptr(), df.data_ptr(),
+                                 _ptr(dhalo), dh.data_ptr(), db.data_ptr(), B, L, D, G, K, _stream()), "mr_bwd")
+            _count(2)
         return df, dh.to(hdtype), db.to(bdtype), dhalo
 
 

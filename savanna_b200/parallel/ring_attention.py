@@ -16,15 +16,19 @@ from .. import ops
 from . import state
 
 
+def _acc(t):
+    return t.float() if t.dtype in (torch.bfloat16, torch.float16) else t
+
+
 def _merge(o_acc, lse_acc, o, lse):
-    """Merge two partial attention results (o [B,L,H,hd], lse [B,H,L])."""
+    """Merge two partial attention results (o [B,L,H,hd], lse [B,H,L]); accumulation in fp32 or wider."""
     if o_acc is None:
-        return o.float(), lse.float()
-    lse = lse.float()
+        return _acc(o), _acc(lse)
+    lse = _acc(lse).to(lse_acc.dtype)
     new = torch.logaddexp(lse_acc, lse)
     wa = torch.exp(lse_acc - new).transpose(1, 2).unsqueeze(-1)
     wb = torch.exp(lse - new).transpose(1, 2).unsqueeze(-1)
-    return o_acc * wa + o.float() * wb, new
+    return o_acc * wa + _acc(o) * wb, new
 
 
 def _exchange(t: torch.Tensor, dst: int, src: int, group) -> torch.Tensor:

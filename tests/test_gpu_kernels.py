@@ -234,7 +234,7 @@ def test_hyena_se(K, G, halo):
         _close(h.grad, hr.grad, what="se dhalo")
 
 
-@pytest.mark.parametrize("K,G,L", [(128, 16, 400), (32, 16, 130), (128, 4, 256)])
+@pytest.mark.parametrize("K,G,L", [(128, 16, 400), (32, 16, 130), (128, 4, 256), (128, 32, 200), (100, 16, 333)])
 @pytest.mark.parametrize("halo", [False, True])
 def test_hyena_mr(K, G, L, halo):
     torch.manual_seed(12)

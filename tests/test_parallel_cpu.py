@@ -1,0 +1,212 @@
+"""Host-side logic of the parallel runtime on CPU processes (gloo): topology, zigzag sharding, the
+context-parallel all-to-all and halo exchange, ring attention, ZeRO-1 partitioning and tensor /
+sequence / context-parallel equivalence of the whole model."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from savanna_b200.parallel.topology import build_topology
+from savanna_b200.parallel.zigzag import inverse_zigzag_permutation, zigzag_indices, zigzag_merge, zigzag_split
+from tests.dist_utils import run_distributed
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = os.path.join(ROOT, "configs", "baseline", "tiny_sh2_cpu.yml")
+
+
+def test_topology_rank_order():
+    topo = build_topology(16, pp=1, cp=2, tp=2)
+    assert topo.get_coord(0) == {"pipe": 0, "data": 0, "context": 0, "model": 0}
+    assert topo.get_coord(1)["model"] == 1 and topo.get_coord(2)["context"] == 1 and topo.get_coord(4)["data"] == 1
+    assert topo.get_axis_comm_lists("model")[0] == [0, 1]
+    assert topo.get_axis_comm_lists("context")[0] == [0, 2]
+    assert topo.get_axis_comm_lists("data")[0] == [0, 4, 8, 12]
+    assert topo.get_multi_axis_comm_lists(["data", "context"])[0] == [0, 2, 4, 6, 8, 10, 12, 14]
+
+
+def test_zigzag_roundtrip():
+    x = torch.arange(2 * 32 * 3).view(2, 32, 3)
+    for cp in (1, 2, 4):
+        parts = [zigzag_split(x, cp, r) for r in range(cp)]
+        assert torch.equal(zigzag_merge(parts), x)
+    idx = zigzag_indices(16, 2, 0)
+    assert idx.tolist() == [0, 1, 2, 3, 12, 13, 14, 15]
+    inv = inverse_zigzag_permutation(16, 2)
+    order = torch.cat([zigzag_indices(16, 2, r) for r in range(2)])
+    assert torch.equal(order[inv], torch.arange(16))
+
+
+# ----------------------------------------------------------------------------- multi-process workers
+
+
+def _w_groups(rank, world):
+    from savanna_b200.parallel import state
+    state.initialize_model_parallel(2, 2, 1)
+    assert state.get_model_parallel_world_size() == 2 and state.get_context_parallel_world_size() == 2
+    assert state.get_data_parallel_world_size() == world // 4
+    assert state.get_sequence_data_parallel_world_size() == world // 2
+    t = torch.ones(1)
+    dist.all_reduce(t, group=state.get_model_parallel_group())
+    assert t.item() == 2
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=state.get_context_parallel_group())
+    coord = state.get_topology().get_coord(rank)
+    partner = state.get_topology().get_rank(**{**coord, "context": 1 - coord["context"]})
+    assert t.item() == rank + partner
+
+
+def test_process_groups():
+    run_distributed(_w_groups, 8)
+
+
+def _w_a2a_halo(rank, world):
+    from savanna_b200.parallel import a2a, halo, state
+    state.initialize_model_parallel(1, world, 1)
+    torch.manual_seed(0)
+    B, L, D = 2, 16 * world, 4 * world
+    full = torch.randn(B, L, D, dtype=torch.float64)
+    local = zigzag_split(full, world, rank).clone().requires_grad_()
+    # split_to_full gives the natural-order sequence with this rank's channel block
+    sf = a2a.split_to_full(local)
+    d = D // world
+    assert torch.allclose(sf, full[..., rank * d:(rank + 1) * d])
+    back = a2a.full_to_split(sf)
+    assert torch.allclose(back, local)
+    back.sum().backward()
+    assert torch.allclose(local.grad, torch.ones_like(local))
+    # halo rows equal the rows that precede each chunk in the full sequence
+    H = 3
+    h = halo.zigzag_halo(local.detach(), H)
+    c = L // (2 * world)
+    a_id, b_id = rank, 2 * world - 1 - rank
+    exp_a = full[:, a_id * c - H:a_id * c] if a_id > 0 else torch.zeros(B, H, D, dtype=torch.float64)
+    exp_b = full[:, b_id * c - H:b_id * c]
+    assert torch.allclose(h[:, 0], exp_a) and torch.allclose(h[:, 1], exp_b)
+
+
+def test_a2a_and_halo():
+    run_distributed(_w_a2a_halo, 4)
+
+
+def _w_halo_grad(rank, world):
+    """Gradient of a causal conv through the halo exchange equals the gradient on the full sequence."""
+    from savanna_b200.ops import reference as ref
+    from savanna_b200.parallel import halo, state
+    state.initialize_model_parallel(1, world, 1)
+    torch.manual_seed(1)
+    B, L, C, K = 1, 8 * 2 * world, 6, 4
+    full = torch.randn(B, L, C, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(C, K, dtype=torch.float64)
+    g = torch.randn(B, L, C, dtype=torch.float64)
+    ref.causal_conv1d(full, w).backward(g)
+    local = zigzag_split(full.detach(), world, rank).clone().requires_grad_()
+    h = halo.zigzag_halo(local, K - 1)
+    y = ref.causal_conv1d(local.reshape(B * 2, -1, C), w, h.reshape(B * 2, K - 1, C)).reshape(B, -1, C)
+    y.backward(zigzag_split(g, world, rank))
+    assert torch.allclose(local.grad, zigzag_split(full.grad, world, rank), atol=1e-10)
+
+
+def test_halo_gradient():
+    run_distributed(_w_halo_grad, 4)
+
+
+def _w_ring_attention(rank, world):
+    from savanna_b200.ops import reference as ref
+    from savanna_b200.parallel import state
+    from savanna_b200.parallel.ring_attention import ring_attention
+    state.initialize_model_parallel(1, world, 1)
+    torch.manual_seed(2)
+    B, L, H, hd = 1, 8 * 2 * world, 2, 8
+    q, k, v = (torch.randn(B, L, H, hd, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    g = torch.randn(B, L, H, hd, dtype=torch.float64)
+    o = ref.attention(q, k, v, causal=True)
+    o.backward(g)
+    ql, kl, vl = (zigzag_split(t.detach(), world, rank).clone().requires_grad_() for t in (q, k, v))
+    pos = zigzag_indices(L, world, rank)
+    ol = ring_attention(ql, kl, vl, pos, causal=True)
+    assert torch.allclose(ol, zigzag_split(o.detach(), world, rank), atol=1e-9)
+    ol.backward(zigzag_split(g, world, rank))
+    for a, b in ((ql, q), (kl, k), (vl, v)):
+        assert torch.allclose(a.grad, zigzag_split(b.grad, world, rank), atol=1e-9)
+
+
+def test_ring_attention():
+    run_distributed(_w_ring_attention, 4)
+
+
+def _tiny_cfg(world, **over):
+    from savanna_b200.config import GlobalConfig
+    base = {"global_num_gpus": world, "hidden_dropout": 0.0, "train_micro_batch_size_per_gpu": 2}
+    base.update(over)
+    cfg = GlobalConfig.from_ymls([TINY], base)
+    return cfg
+
+
+def _run_steps(cfg, n=3, seed_offset=0, global_batch=None):
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    tr = Trainer(cfg, load=False)
+    dp, dr = state.get_data_parallel_world_size(), state.get_data_parallel_rank()
+    mb = cfg.train_micro_batch_size_per_gpu
+
+    def it():
+        i = 0
+        while True:
+            full = acgt_batch(mb * dp, cfg.seq_length, seed=i)
+            yield {"text": full[dr * mb:(dr + 1) * mb]}
+            i += 1
+    d = it()
+    losses = [float(tr.train_step(d)) for _ in range(n)]
+    return tr, losses
+
+
+def _w_equiv(rank, world, over, ref_losses):
+    cfg = _tiny_cfg(world, **over)
+    _, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+
+
+def _reference_losses(mb=2):
+    cfg = _tiny_cfg(1, train_micro_batch_size_per_gpu=mb)
+    _, losses = _run_steps(cfg)
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    return losses
+
+
+@pytest.mark.slow
+def test_tensor_parallel_equivalence():
+    ref_losses = _reference_losses()
+    run_distributed(_w_equiv, 2, {"model_parallel_size": 2}, ref_losses)
+
+
+@pytest.mark.slow
+def test_sequence_parallel_equivalence():
+    ref_losses = _reference_losses()
+    run_distributed(_w_equiv, 2, {"model_parallel_size": 2, "sequence_parallel": True}, ref_losses)
+
+
+@pytest.mark.slow
+def test_context_parallel_equivalence_a2a():
+    ref_losses = _reference_losses()
+    over = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True,
+            "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
+    run_distributed(_w_equiv, 2, over, ref_losses)
+
+
+@pytest.mark.slow
+def test_context_parallel_equivalence_p2p_state():
+    ref_losses = _reference_losses()
+    over = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True, "cp_hyena_mr_algo": "p2p",
+            "cp_hyena_li_algo": "state", "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
+    run_distributed(_w_equiv, 2, over, ref_losses)
+
+
+@pytest.mark.slow
+def test_zero1_data_parallel_equivalence():
+    """dp=2 with micro batch 1 and ZeRO-1 partitioning == one process with micro batch 2."""
+    ref_losses = _reference_losses(mb=2)
+    run_distributed(_w_equiv, 2, {"train_micro_batch_size_per_gpu": 1, "zero_optimization": {"stage": 1}}, ref_losses)
