@@ -23,6 +23,13 @@ from ..parallel import state
 _PRESETS = {"strong": (0, 2), "normal": (-1, 2), "weak": (-2, 2)}
 
 
+def _tp_slice(full: torch.Tensor) -> torch.Tensor:
+    """Rows of a tensor drawn at the global (all tensor-parallel ranks) size that belong to this rank.
+    Drawing globally and slicing keeps the initial model identical for every tensor-parallel size."""
+    tp, rank = state.get_model_parallel_world_size(), state.get_model_parallel_rank()
+    return full.chunk(tp, dim=0)[rank].contiguous() if tp > 1 else full
+
+
 class ExplicitSingleDecayFilter(nn.Module):
     def __init__(self, d_model: int, L_cache: int, decay_preset: str = "strong", num_decay_repeats: int = 1,
                  small_init: bool = True, unit_passthrough: bool = False, device=None):
@@ -30,7 +37,8 @@ class ExplicitSingleDecayFilter(nn.Module):
         if decay_preset not in _PRESETS:
             raise ValueError(f"decay preset {decay_preset!r} unknown")
         r_min, r_max = _PRESETS[decay_preset]
-        h = torch.randn(d_model, L_cache, device=device) / math.sqrt(L_cache)
+        tp_ = state.get_model_parallel_world_size()
+        h = _tp_slice(torch.randn(d_model * tp_, L_cache, device=device)) / math.sqrt(L_cache)
         if small_init:
             h = h * 1e-5
         if unit_passthrough:
@@ -56,9 +64,10 @@ class ImplicitModalFilter(nn.Module):
         super().__init__()
         self.order, self.d_model = order, d_model
         self.register_buffer("t", torch.arange(L_cache or 1, dtype=torch.float32, device=device).view(1, 1, -1))
-        gamma = torch.rand(d_model, order, dtype=torch.float32, device=device) * (gamma_max - gamma_min) + gamma_min
+        tp_ = state.get_model_parallel_world_size()
+        gamma = _tp_slice(torch.rand(d_model * tp_, order, dtype=torch.float32, device=device)) * (gamma_max - gamma_min) + gamma_min
         self.gamma = nn.Parameter(gamma.log())
-        self.R = nn.Parameter(1e-1 * torch.randn(d_model, order, dtype=torch.float32, device=device) / math.sqrt(order))
+        self.R = nn.Parameter(1e-1 * _tp_slice(torch.randn(d_model * tp_, order, dtype=torch.float32, device=device)) / math.sqrt(order))
         self.p = nn.Parameter(-torch.ones(d_model, order, dtype=torch.float32, device=device))
         for q in (self.gamma, self.R, self.p):
             q.is_filter_param = True
@@ -77,9 +86,10 @@ class ImplicitRealModalFilter(nn.Module):
                  device=None):
         super().__init__()
         self.order = order
-        poles = torch.rand(d_model, order, device=device) * (r_max - r_min) + r_min
+        tp_ = state.get_model_parallel_world_size()
+        poles = _tp_slice(torch.rand(d_model * tp_, order, device=device)) * (r_max - r_min) + r_min
         self.log_poles = nn.Parameter(poles.log())
-        self.residues = nn.Parameter(torch.randn(d_model, order, device=device) / math.sqrt(order))
+        self.residues = nn.Parameter(_tp_slice(torch.randn(d_model * tp_, order, device=device)) / math.sqrt(order))
         self.log_poles.is_filter_param = True
         self.residues.is_filter_param = True
 

@@ -193,7 +193,17 @@ class Trainer:
         self.tokens_seen += cfg.train_batch_size * cfg.seq_length
         if self.watchdog is not None:
             self.watchdog.beat(self.iteration)
-        return total / self.gas
+        return self._reduce_loss(total / self.gas)
+
+    def _reduce_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        """Mean of the step's loss over the data-parallel replicas (what gets logged; the reference's
+        `reduce_losses`, savanna/utils.py:47-52).  One scalar all-reduce, no host synchronisation."""
+        dp = state.get_data_parallel_world_size()
+        if dp == 1 or not dist.is_initialized():
+            return loss
+        loss = loss.clone()
+        dist.all_reduce(loss, group=state.get_data_parallel_group())
+        return loss / dp
 
     def _sync_replicated_grads(self) -> None:
         """Sequence parallelism: parameters replicated over the tensor-parallel group (norm gains, row

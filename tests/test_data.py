@@ -1,0 +1,115 @@
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from savanna_b200.data import helpers
+from savanna_b200.data.blendable_dataset import BlendableDataset
+from savanna_b200.data.indexed_dataset import MMapIndexedDataset, MMapIndexedDatasetBuilder
+from savanna_b200.data.samplers import DistributedBatchSampler
+from savanna_b200.data.sequence_dataset import SequenceDataset
+from savanna_b200.data.synthetic import ACGT, SyntheticACGTDataset
+from savanna_b200.data.tokenizer import CharLevelTokenizer, pad_vocab_size
+
+
+def _make_dataset(tmp_path, ndocs=50, seed=0):
+    rng = np.random.default_rng(seed)
+    prefix = str(tmp_path / "ds")
+    b = MMapIndexedDatasetBuilder(prefix + ".bin", dtype=np.uint16)
+    docs = []
+    for _ in range(ndocs):
+        n = int(rng.integers(5, 200))
+        toks = rng.integers(0, 512, size=n)
+        docs.append(toks)
+        b.add_item(toks)
+        b.end_document()
+    b.finalize(prefix + ".idx")
+    return prefix, docs
+
+
+def test_indexed_dataset_roundtrip(tmp_path):
+    prefix, docs = _make_dataset(tmp_path)
+    ds = MMapIndexedDataset(prefix)
+    assert len(ds) == len(docs)
+    for i in (0, 7, len(docs) - 1):
+        assert np.array_equal(ds[i], docs[i])
+    assert np.array_equal(ds.get(3, offset=2, length=3), docs[3][2:5])
+    assert ds.doc_idx[-1] == len(docs)
+
+
+def test_sample_idx_native_matches_python():
+    rng = np.random.default_rng(1)
+    sizes = rng.integers(1, 300, size=400).astype(np.int32)
+    doc_idx = np.tile(np.arange(400, dtype=np.int32), 3)
+    rng.shuffle(doc_idx)
+    tokens = int(sizes.sum())
+    a = helpers.build_sample_idx(sizes, doc_idx, 64, 3, tokens, force_python=True)
+    if helpers.native_available():
+        b = helpers.build_sample_idx(sizes, doc_idx, 64, 3, tokens)
+        assert np.array_equal(a, b)
+    # every sample spans exactly seq_length + 1 tokens, consecutive samples overlap by one token
+    flat_off = np.concatenate([[0], np.cumsum(sizes[doc_idx])])
+    starts = flat_off[a[:, 0]] + a[:, 1]
+    assert np.all(np.diff(starts) == 64)
+
+
+def test_blending_indices():
+    w = [0.5, 0.3, 0.2]
+    ds, dss = helpers.build_blending_indices(w, 1000, force_python=True)
+    if helpers.native_available():
+        ds2, dss2 = helpers.build_blending_indices(w, 1000)
+        assert np.array_equal(ds, ds2) and np.array_equal(dss, dss2)
+    counts = np.bincount(ds, minlength=3) / 1000.0
+    assert np.allclose(counts, w, atol=0.01)
+    for d in range(3):
+        assert np.array_equal(dss[ds == d], np.arange((ds == d).sum()))
+
+
+def test_sequence_dataset_samples(tmp_path):
+    prefix, docs = _make_dataset(tmp_path)
+    ids = MMapIndexedDataset(prefix)
+    sd = SequenceDataset("train", prefix, np.arange(len(docs), dtype=np.int32), ids, num_samples=40, seq_length=32, seed=3)
+    assert len(sd) >= 40
+    for i in range(0, 40, 7):
+        s = sd[i]["text"]
+        assert s.shape == (33,) and s.dtype == np.int64
+    # the index caches are written once and reused
+    files = [f for f in os.listdir(tmp_path) if f.endswith("_idx.npy")]
+    assert len(files) == 3
+    sd2 = SequenceDataset("train", prefix, np.arange(len(docs), dtype=np.int32), ids, 40, 32, 3)
+    assert np.array_equal(sd[5]["text"], sd2[5]["text"])
+
+
+def test_blendable_dataset():
+    a = SyntheticACGTDataset(100, 8, seed=1)
+    b = SyntheticACGTDataset(50, 8, seed=2)
+    bl = BlendableDataset([a, b], [0.7, 0.3])
+    assert len(bl) == 150
+    assert set(np.unique(bl[0]["text"])) <= set(ACGT.tolist())
+
+
+def test_distributed_batch_sampler_partitions():
+    data = list(range(64))
+    seen = []
+    for rank in range(4):
+        s = DistributedBatchSampler(torch.utils.data.SequentialSampler(data), 8, True, rank=rank, world_size=4)
+        batches = list(s)
+        assert all(len(b) == 2 for b in batches)
+        seen.append([i for b in batches for i in b])
+    assert sorted(i for r in seen for i in r) == data
+    s = DistributedBatchSampler(torch.utils.data.SequentialSampler(data), 8, True, rank=1, world_size=4)
+    s.start_iter = 3
+    assert list(s)[0] == [26, 27]
+
+
+def test_char_tokenizer_and_padding():
+    t = CharLevelTokenizer(512)
+    ids = t.tokenize("ACGT")
+    assert ids == [65, 67, 71, 84] and t.detokenize(ids) == "ACGT"
+    assert pad_vocab_size(512, 8, 2) == 512 and pad_vocab_size(500, 128, 2) == 512
+
+
+def test_synthetic_is_deterministic():
+    a, b = SyntheticACGTDataset(10, 16, seed=5), SyntheticACGTDataset(10, 16, seed=5)
+    assert np.array_equal(a[3]["text"], b[3]["text"]) and not np.array_equal(a[3]["text"], a[4]["text"])

@@ -1,0 +1,84 @@
+"""Algebraic checks of the oracle operators themselves (the kernels are tested against these)."""
+import math
+
+import torch
+
+from savanna_b200.ops import reference as ref
+
+
+def test_causal_conv_matches_explicit_sum():
+    torch.manual_seed(0)
+    x = torch.randn(2, 20, 3, dtype=torch.float64)
+    w = torch.randn(3, 4, dtype=torch.float64)
+    y = ref.causal_conv1d(x, w)
+    t, c = 7, 1
+    exp = sum(w[c, j] * x[0, t - 3 + j, c] for j in range(4))
+    assert abs(y[0, t, c] - exp) < 1e-6
+    # halo == explicit left context
+    y2 = ref.causal_conv1d(x[:, 5:], w, x[:, 2:5])
+    assert torch.allclose(y2, y[:, 5:], atol=1e-6)
+
+
+def test_fft_conv_equals_direct():
+    torch.manual_seed(1)
+    u = torch.randn(1, 64, 4)
+    h = torch.randn(4, 64)
+    y = ref.fft_causal_conv(u, h)
+    yd = ref.fir_causal(u, h)
+    assert torch.allclose(y, yd, atol=1e-4)
+
+
+def test_modal_state_splits_sequence():
+    """Running two halves with the state hand-off equals running the whole sequence."""
+    torch.manual_seed(2)
+    B, L, D, O = 2, 64, 6, 4
+    feat = torch.randn(B, L, 3 * D)
+    gamma = (torch.rand(D, O) * 0.09 + 0.01).log()
+    R = torch.randn(D, O) * 0.1
+    p = -torch.ones(D, O)
+    bias = torch.randn(D)
+    full = ref.hyena_li_modal(feat, gamma, R, p, bias)
+    a, s = ref.hyena_li_modal(feat[:, :32], gamma, R, p, bias, None, True)
+    b = ref.hyena_li_modal(feat[:, 32:], gamma, R, p, bias, s)
+    assert torch.allclose(torch.cat([a, b], 1), full, atol=1e-4)
+
+
+def test_rope_is_rotation():
+    pos = torch.arange(16)
+    cos, sin = ref.rope_tables(pos, 8)
+    x = torch.randn(1, 16, 2, 8)
+    y = ref.apply_rope(x, cos, sin)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+    back = ref.apply_rope(y, cos, -sin)
+    assert torch.allclose(back, x, atol=1e-5)
+
+
+def test_attention_matches_sdpa():
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(2, 12, 3, 8) for _ in range(3))
+    o = ref.attention(q, k, v, causal=True)
+    exp = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+    assert torch.allclose(o, exp.transpose(1, 2), atol=1e-5)
+
+
+def test_rmsnorm_forms():
+    x = torch.randn(4, 32)
+    w = torch.rand(32) + 0.5
+    a = ref.rmsnorm(x, w, 1e-6, "te")
+    b = ref.rmsnorm(x, w, 1e-6, "classic")
+    assert torch.allclose(a, b, atol=1e-4)      # the forms differ only in where eps enters
+    assert torch.allclose(a, w * x / x.pow(2).mean(-1, keepdim=True).sqrt(), atol=1e-4)
+
+
+def test_adam_matches_torch():
+    torch.manual_seed(4)
+    p0 = torch.randn(100)
+    g = torch.randn(100)
+    q = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.AdamW([q], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v, master = torch.zeros(100), torch.zeros(100), p0.clone()
+    for step in (1, 2, 3):
+        q.grad = g.clone()
+        opt.step()
+        ref.adam_step(master, m, v, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, True)
+    assert torch.allclose(master, q.detach(), atol=1e-6)
