@@ -311,3 +311,47 @@ extern "C" int sb_li_bwd(const void* feat, const void* dz, const float* loglam, 
                                                       (const bf16*)dx1_tmp, (bf16*)dfeat, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ------------------------------------------------------------------------------------ allocation-free variant
+// See li_scan_noalloc.h for who needs this and for the contract.
+#include <stdio.h>
+
+#include "li_scan_noalloc.h"
+
+// The chunk-state scratch of the forward scan, resident in the library's device image (one copy per GPU).
+static __device__ __align__(256) float g_li_noalloc_scratch[SB_LI_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+// In host code the symbol above is only a handle; the kernels need its device address, looked up once per device.
+static float* g_li_noalloc_ptr[64] = {nullptr};
+
+extern "C" int sb_li_fwd_noalloc(const void* feat, const float* loglam, const float* R, const float* bias,
+                                 const float* state_in, float* state_out, void* z, int B, int L, int D, int TC,
+                                 cudaStream_t st) {
+  if (B <= 0 || L <= 0 || D <= 0 || TC <= 0) return 0;
+  LiDims d = li_dims(B, L, D, TC);
+  const unsigned long long need = (unsigned long long)B * d.NC * D * LO * sizeof(float);
+  if (need > SB_LI_NOALLOC_SCRATCH_BYTES) {
+    fprintf(stderr,
+            "sb_li_fwd_noalloc: B=%d L=%d D=%d TC=%d needs %llu bytes of chunk-state scratch, the built-in buffer holds "
+            "%u; use sb_li_fwd with a caller-provided buffer\n", B, L, D, TC, need, SB_LI_NOALLOC_SCRATCH_BYTES);
+    return SB_LI_NOALLOC_TOO_LARGE;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SB_LI_NOALLOC_SETUP_FAILED;
+  if (g_li_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_li_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "sb_li_fwd_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
+      return SB_LI_NOALLOC_SETUP_FAILED;
+    }
+    g_li_noalloc_ptr[dev] = p;
+  }
+  float* S = g_li_noalloc_ptr[dev];
+  dim3 grid((D + LI_THREADS - 1) / LI_THREADS, d.NC, B);
+  li_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, S, d);
+  const size_t n = (size_t)B * D * LO;
+  li_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, loglam, state_in, state_out, d);
+  li_apply_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, R, bias, S, (bf16*)z, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
