@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is then not the named config)")
     ap.add_argument("--accum", type=int, default=None, help="debug only: accumulation steps per optimizer step")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm", type=str, default=None, choices=["symm", "nccl"], help="ZeRO collective path (default: config)")
     return ap.parse_args()
 
 
@@ -134,6 +135,8 @@ def main():
         over["num_layers"] = args.layers
     if args.accum:
         over["gradient_accumulation_steps"] = args.accum
+    if args.comm:
+        over["comm_path"] = args.comm
     if args.layers:
         import yaml
         doc = yaml.load(open(args.config), Loader=yaml.FullLoader)
@@ -236,7 +239,7 @@ def main():
             "config": {"model": "evo2-7b-style-sh2 (32L, D4096, 32 heads, ffn 11264, vocab 512)" if not args.layers
                        else f"DEBUG {args.layers}-layer truncation (not the named config)",
                        "global_batch": cfg.train_batch_size, "seq_len": L, "micro_batch": B, "grad_accum": gas,
-                       "parallelism": f"dp{world} zero1", "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
+                       "parallelism": f"dp{world} zero1", "zero_path": ("fused peer-memory kernels" if getattr(trainer.optimizer, "fused", None) is not None else ("nccl" if world > 1 else "single rank")), "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
             "mfu_of_measured_peak": mfu, "model_flops_per_token": fpt, "loss": final_loss,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

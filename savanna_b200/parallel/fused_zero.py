@@ -1,0 +1,165 @@
+"""ZeRO-1 step over NVLink peer memory (the "symm" communication path).
+
+The flat bf16 gradient and parameter buffers of every rank are allocated in symmetric memory
+(torch.distributed._symmetric_memory: each rank maps all peers' buffers).  One optimizer step is then
+
+    barrier (stream-ordered)                         every rank's backward has finished writing gradients
+    zero_rs_kernel      per flat group               peer loads -> fp32 sum -> own shard + squared-norm partial
+    all-reduce of one scalar                         global gradient norm (also orders the ranks)
+    zero_adam_kernel    per flat group               Adam on the shard + peer stores of the new bf16 params
+    barrier (stream-ordered)                         all parameter stores have landed before the next forward
+
+(csrc/zero_fused.cu).  Barriers are tiny NCCL all-reduces on the compute stream, so the kernels themselves
+never wait on a peer.  fp32 flat groups (filter parameters, a few MB) stay on the NCCL path.
+Reference behaviour replaced: DeepSpeed stage-1 reduce-scatter, fused Adam and all-gather
+(savanna/training.py:1329-1337, 1391-1400, 1497).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import print_rank_0
+from . import state
+
+
+class SymmAllocator:
+    """Allocates flat buffers in symmetric memory and remembers the handles for the later rendezvous."""
+
+    def __init__(self, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.symm_mem = symm_mem
+        self.group = group
+        self.tensors: List[torch.Tensor] = []
+
+    def __call__(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        dev = torch.device("cuda", torch.cuda.current_device())
+        if dtype != torch.bfloat16:
+            return torch.zeros(n, dtype=dtype, device=dev)
+        t = self.symm_mem.empty(n, dtype=dtype, device=dev)
+        t.zero_()
+        self.tensors.append(t)
+        return t
+
+    def rendezvous(self, t: torch.Tensor):
+        group = self.group if self.group is not None else dist.group.WORLD
+        return self.symm_mem.rendezvous(t, group)
+
+
+class FusedZeroStep:
+    def __init__(self, opt, allocator: SymmAllocator):
+        from ..ops import cuda_ops
+        self.lib = cuda_ops.require()
+        self.cuda_ops = cuda_ops
+        P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        self.lib.sb_zero_reduce_scatter.restype = I
+        self.lib.sb_zero_reduce_scatter.argtypes = [P, I, I, LL, LL, P, P, P, P]
+        self.lib.sb_zero_adam_allgather.restype = I
+        self.lib.sb_zero_adam_allgather.argtypes = [P, P, P, P, P, I, I, LL, LL, F, F, F, F, F, F, F, I, P, P]
+        self.world, self.rank = opt.world, opt.rank
+        self.handles = {}
+        for g in opt.groups:
+            if g.flat_param.dtype != torch.bfloat16:
+                continue
+            hg = allocator.rendezvous(g.flat_grad)
+            hp = allocator.rendezvous(g.flat_param)
+            gp = (ctypes.c_void_p * self.world)(*[int(p) for p in hg.buffer_ptrs])
+            pp = (ctypes.c_void_p * self.world)(*[int(p) for p in hp.buffer_ptrs])
+            self.handles[id(g)] = (hg, hp, gp, pp)
+        dev = opt.groups[0].flat_param.device
+        self._token = torch.zeros(1, device=dev)
+        self._sq = torch.zeros((), dtype=torch.float32, device=dev)
+
+    def _barrier(self, group) -> None:
+        dist.all_reduce(self._token, group=group)          # stream-ordered: completes once every rank has arrived
+
+    @torch.no_grad()
+    def step(self, opt) -> torch.Tensor:
+        opt.step_count += 1
+        st = torch.cuda.current_stream().cuda_stream
+        self._barrier(opt.group)
+        self._sq.zero_()
+        shards = []
+        for g in opt.groups:
+            h = self.handles.get(id(g))
+            if h is None:
+                s = opt._reduce_scatter(g)
+                self._sq += self.cuda_ops.sq_norm(s, g.norm_weight) if s.is_cuda else (s.float() ** 2).sum()
+                shards.append(s)
+                continue
+            _, _, gp, _ = h
+            lo = g.rank * g.shard
+            out = g.shard_slice(g.flat_grad)
+            rc = self.lib.sb_zero_reduce_scatter(gp, self.world, self.rank, lo, g.shard, out.data_ptr(),
+                                                 None if g.norm_weight is None else g.norm_weight.data_ptr(),
+                                                 self._sq.data_ptr(), st)
+            if rc != 0:
+                raise RuntimeError(f"zero_reduce_scatter failed ({rc})")
+            self.cuda_ops._count()
+            shards.append(out)
+        inv = 1.0 / opt.reduce_world
+        sq = self._sq * (inv * inv)
+        dist.all_reduce(sq, group=opt.group)
+        tp = state.get_model_parallel_world_size()
+        if tp > 1:
+            dist.all_reduce(sq, group=state.get_model_parallel_group())
+        norm = sq.sqrt()
+        opt.last_grad_norm = norm
+        if opt.clip_grad > 0.0:
+            coef = (torch.clamp(opt.clip_grad / (norm + 1e-6), max=1.0) * inv).reshape(1).float()
+        else:
+            coef = torch.full((1,), inv, dtype=torch.float32, device=norm.device)
+        b1, b2 = opt.betas
+        bc1, bc2 = 1.0 - b1 ** opt.step_count, 1.0 - b2 ** opt.step_count
+        for g, s in zip(opt.groups, shards):
+            h = self.handles.get(id(g))
+            if h is None:
+                from .. import ops
+                ops.adam_step(g.master, g.exp_avg, g.exp_avg_sq, s, g.hyper["lr"], b1, b2, opt.eps, g.hyper["weight_decay"],
+                              opt.step_count, opt.adamw, coef, None if g.master_is_view else g.shard_slice(g.flat_param))
+                opt._all_gather(g)
+                continue
+            _, _, _, pp = h
+            rc = self.lib.sb_zero_adam_allgather(g.master.data_ptr(), g.exp_avg.data_ptr(), g.exp_avg_sq.data_ptr(),
+                                                 s.data_ptr(), pp, self.world, self.rank, g.rank * g.shard, g.shard,
+                                                 g.hyper["lr"], b1, b2, opt.eps, g.hyper["weight_decay"], bc1, bc2,
+                                                 int(opt.adamw), coef.data_ptr(), st)
+            if rc != 0:
+                raise RuntimeError(f"zero_adam_allgather failed ({rc})")
+            self.cuda_ops._count()
+        self._barrier(opt.group)
+        return norm
+
+
+def make_allocator(group) -> Optional[SymmAllocator]:
+    try:
+        return SymmAllocator(group)
+    except Exception as exc:  # noqa: BLE001
+        print_rank_0(f"symmetric memory unavailable ({exc}); ZeRO uses the NCCL path")
+        return None
+
+
+def attach(opt, allocator: Optional[SymmAllocator]) -> bool:
+    """Switch `opt.step` to the fused path.  Every rank must reach the same decision: the outcome of the
+    rendezvous is agreed on with an all-reduce, and a failure anywhere keeps everyone on the NCCL path."""
+    ok = 1
+    fused = None
+    if allocator is None or opt.world > 16 or not opt.partition:
+        ok = 0
+    else:
+        try:
+            fused = FusedZeroStep(opt, allocator)
+        except Exception as exc:  # noqa: BLE001
+            print(f"[rank {dist.get_rank()}] fused ZeRO set-up failed: {exc}", flush=True)
+            ok = 0
+    flag = torch.tensor([ok], device=opt.groups[0].flat_param.device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=opt.group)
+    if int(flag.item()) == 1:
+        opt.fused = fused
+        print_rank_0(" > ZeRO-1 step: fused peer-memory kernels (reduce-scatter + Adam + all-gather)")
+        return True
+    print_rank_0(" > ZeRO-1 step: NCCL reduce-scatter / all-gather path")
+    return False

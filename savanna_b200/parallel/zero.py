@@ -87,7 +87,7 @@ class ZeroOptimizer:
     def __init__(self, param_groups: List[Dict], lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, adamw: bool = True, clip_grad: float = 0.0,
                  group=None, group_ranks: Optional[List[int]] = None, comm_path: str = "nccl",
-                 grad_divisor: Optional[float] = None, partition: bool = True):
+                 grad_divisor: Optional[float] = None, partition: bool = True, allocator=None):
         self.group = group
         ranks = group_ranks or [0]
         self.world = len(ranks) if partition else 1
@@ -116,7 +116,7 @@ class ZeroOptimizer:
             for q in params:
                 by_dtype.setdefault(q.dtype, []).append(q)
             for dt, plist in by_dtype.items():
-                fg = FlatGroup(plist, self.world, self.rank, hyper)
+                fg = FlatGroup(plist, self.world, self.rank, hyper, allocator)
                 fg.hyper = hyper                    # shared object: both flats follow the schedule
                 fg.build_norm_weight(tp)
                 self.groups.append(fg)

@@ -124,14 +124,20 @@ class Trainer:
         p = dict(opt_cfg.get("params", {}))
         otype = cfg.optimizer_type
         if otype in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
+            zranks = state.get_sequence_data_parallel_ranks()
+            use_symm = (self.device.type == "cuda" and cfg.comm_path == "symm" and len(zranks) > 1
+                        and cfg.zero_stage >= 1 and cfg.precision == "bfloat16")
+            allocator = None
+            if use_symm:
+                from ..parallel import fused_zero
+                allocator = fused_zero.make_allocator(state.get_sequence_data_parallel_group())
             optimizer = ZeroOptimizer(
                 groups, lr=cfg.lr, betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8),
                 weight_decay=cfg.weight_decay, adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
-                group=state.get_sequence_data_parallel_group(), group_ranks=state.get_sequence_data_parallel_ranks(),
-                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1)
-            if self.device.type == "cuda" and cfg.comm_path == "symm" and optimizer.reduce_world > 1:
-                from ..parallel import fused_zero
-                fused_zero.attach(optimizer, cfg)
+                group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
+                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator)
+            if use_symm:
+                fused_zero.attach(optimizer, allocator)
         else:
             from .optimizers import build_generic_optimizer
             optimizer = build_generic_optimizer(otype, groups, cfg, p)
