@@ -318,6 +318,42 @@ __global__ void adam_kernel(float* __restrict__ master, float* __restrict__ m, f
   }
 }
 
+// ------------------------------------------------------------------------------------ column sums (bias gradients)
+// out[c] += sum_rows x[r, c]; each block owns 64 columns x a slab of rows, one fp32 atomic per column per block.
+__global__ void __launch_bounds__(256)
+colsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, int T, int N, int rows_per_block) {
+  __shared__ float part[64];
+  const int cv = threadIdx.x & 7;                 // 8 column-vectors of 8 = 64 columns
+  const int rl = threadIdx.x >> 3;                // 32 row lanes
+  const int c0 = blockIdx.x * 64 + cv * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(r0 + rows_per_block, T);
+  if (threadIdx.x < 64) part[threadIdx.x] = 0.f;
+  __syncthreads();
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c0 < N) {
+    for (int r = r0 + rl; r < r1; r += 32) {
+      float f[8]; unpack8(*reinterpret_cast<const uint4*>(x + (size_t)r * N + c0), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+  // a warp holds 4 row lanes x 8 column vectors: fold the row lanes, then one shared atomic per column per warp
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 8);
+    acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 16);
+  }
+  if ((threadIdx.x & 31) < 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&part[cv * 8 + j], acc[j]);
+  }
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < N) atomicAdd(out + c, part[threadIdx.x]);
+  }
+}
+
 static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
@@ -393,6 +429,20 @@ extern "C" int sb_ce_bwd(const void* logits, const long long* labels, const floa
   if (T == 0) return 0;
   const int wpb = 8;
   ce_bwd_kernel<<<(unsigned)((T + wpb - 1) / wpb), wpb * 32, 0, st>>>((const bf16*)logits, (const int64_t*)labels, lse, g, (bf16*)dlogits, (size_t)T, V);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// out [N] fp32 must be zeroed by the caller (it is accumulated into); N % 8 == 0
+extern "C" int sb_colsum(const void* x, float* out, int T, int N, cudaStream_t st) {
+  if (N % 8) return -1;
+  if (T == 0 || N == 0) return 0;
+  const int cblocks = (N + 63) / 64;
+  int rsplit = (148 * 4 + cblocks - 1) / cblocks;
+  if (rsplit > (T + 63) / 64) rsplit = (T + 63) / 64;
+  if (rsplit < 1) rsplit = 1;
+  const int rows_per_block = (T + rsplit - 1) / rsplit;
+  dim3 grid(cblocks, (T + rows_per_block - 1) / rows_per_block);
+  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, out, T, N, rows_per_block);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -34,7 +34,8 @@ constexpr int NUM_THREADS = 192;
 struct GemmParams {
   __nv_bfloat16* C;
   const __nv_bfloat16* bias;   // [N] or null
-  int M, N, K, ldc;
+  const __nv_bfloat16* residual;  // [M, N] (leading dim ldr) added in the epilogue, or null
+  int M, N, K, ldc, ldr;
   int beta;                    // 1: C += result (bf16 read-modify-write)
   uint32_t* status;
 };
@@ -190,6 +191,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(b2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
               }
+              if (p.residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldr + col);
+                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(r2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+              }
               if (p.beta) {
                 const uint4 ov = *reinterpret_cast<const uint4*>(crow + col);
                 const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
@@ -263,12 +270,12 @@ static int g_last_detail = 0;   // (which operand << 16) | CUresult of the last 
 
 extern "C" int sb_gemm_last_error_detail() { return sb::g_last_detail; }
 
-// C = A * B^T (+bias) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
+// C = A * B^T (+bias) (+residual) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
 // transposed as [K, M] with leading dim lda.  b_mn likewise for B ([N, K] or [K, N]).  All leading dims and
 // base addresses must be 16-byte aligned; N and K multiples of 8.  Returns 0 on a successful launch.
-extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
-                            int ldb, int ldc, int a_mn, int b_mn, int beta, unsigned int* status, int max_ctas,
-                            cudaStream_t stream) {
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                            int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int beta, unsigned int* status,
+                            int max_ctas, cudaStream_t stream) {
   using namespace sb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // The tensor-map encoder is a driver call and needs a current context; a thread that has made no runtime call
@@ -290,7 +297,9 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, beta, status};
+  if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
+  GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
+               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;

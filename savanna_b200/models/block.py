@@ -47,12 +47,18 @@ class ParallelBlock(nn.Module):
             return F.dropout(x, self.hidden_dropout, True)
         return x
 
-    def _mlp(self, x, positions):
+    def _mlp(self, x, positions, residual=None):
         if isinstance(self.mlp, nn.Identity):
-            return x, None
+            return (x if residual is None else residual + x), None
         if isinstance(self.mlp, ParallelSequenceMixer):
-            return self.mlp(x, positions)
-        return self.mlp(x)
+            return self.mlp(x, positions, residual)
+        if isinstance(self.mlp, ParallelGLU):
+            return self.mlp(x, residual)
+        y, b = self.mlp(x)
+        if residual is not None:
+            y = residual + (y + b if b is not None else y)
+            b = None
+        return y, b
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         if self.gpt_j_residual:
@@ -66,6 +72,13 @@ class ParallelBlock(nn.Module):
             return x + self._drop(out)
         residual = x
         u = self.input_layernorm(x) if self.prenorm else x
+        no_drop = not (self.hidden_dropout > 0.0 and self.training)
+        if no_drop and not self.postnorm and not self.outer_mlp_norm:
+            # residual and bias additions ride in the epilogues of the out-projection and w3 GEMMs
+            a, _ = self.mixer(u, positions, residual)
+            u = self.pre_mlp_layernorm(a) if self.pre_mlp_norm else a
+            y, _ = self._mlp(u, positions, a)
+            return y
         m, mb = self.mixer(u, positions)
         if mb is not None:
             m = m + mb

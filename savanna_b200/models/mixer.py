@@ -98,7 +98,9 @@ class ParallelSequenceMixer(nn.Module):
         self.dense = RowParallelLinear(D, D, bias=True, input_is_parallel=True, init_method=output_layer_init_method,
                                        skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device, fp8=fp8_out)
 
-    def forward(self, x: torch.Tensor, positions: torch.Tensor):
+    def forward(self, x: torch.Tensor, positions: torch.Tensor, residual: Optional[torch.Tensor] = None):
+        """Returns (output, out-projection bias to be added by the caller).  With `residual` the
+        out-projection adds bias and residual itself and the bias slot is None."""
         proj, _ = self.dense_projection(x)
         if self.operator_type in HYENA_OPS:
             cp = state.get_context_parallel_world_size() if self.cfg.use_cp_hyena else 1
@@ -112,4 +114,4 @@ class ParallelSequenceMixer(nn.Module):
             z = self.mixer(feat)
         else:
             z = self.mixer(proj, positions)
-        return self.dense(z)
+        return self.dense(z, residual)

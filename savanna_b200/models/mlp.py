@@ -81,7 +81,7 @@ class ParallelGLU(nn.Module):
     def w2_weight(self):
         return self.w12[self.ffn_local:]
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         if self.sequence_parallel:
             ab = ops.linear_allgather(x, self.w12, None, 1, fp8=self.fp8)
         else:
@@ -89,7 +89,7 @@ class ParallelGLU(nn.Module):
             xin = mappings.copy_to_model_parallel_region(x) if state.get_model_parallel_world_size() > 1 else x
             ab = ops.linear(xin, self.w12, None, fp8=self.fp8)
         h = ops.glu_act_packed(ab, self.act)
-        return self.w3(h)
+        return self.w3(h, residual)
 
 
 class ParallelMLP(nn.Module):

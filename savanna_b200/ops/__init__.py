@@ -57,8 +57,12 @@ def rmsnorm(x, weight, eps: float, form: str = "te"):
     return _co().rmsnorm(x, weight, eps, form) if _k(x) else ref.rmsnorm(x, weight, eps, form)
 
 
-def linear(x, w, bias=None, fp8: bool = False):
-    return _co().linear(x, w, bias, fp8) if _k(x) else ref.linear(x, w, bias)
+def linear(x, w, bias=None, fp8: bool = False, residual=None):
+    """x w^T (+ bias) (+ residual).  On CUDA bias and residual are added in the GEMM epilogue."""
+    if _k(x):
+        return _co().linear(x, w, bias, fp8, residual)
+    y = ref.linear(x, w, bias)
+    return y if residual is None else y + residual
 
 
 def linear_allgather(x, w, bias=None, seq_dim: int = 1, fp8: bool = False):

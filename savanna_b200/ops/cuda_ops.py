@@ -50,7 +50,8 @@ def require():
 
 class _Sig:
     P, I, F, LL = c_void_p, c_int, c_float, c_ll
-    sb_gemm_bf16 = [P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, P]
+    sb_gemm_bf16 = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P]
+    sb_colsum = [P, P, I, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd = [P, P, P, P, P, P, I, I, F, I, P]
     sb_glu_fwd = [P, P, LL, I, I, P]
@@ -121,8 +122,9 @@ def _is_bf16(*ts) -> bool:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
-         bias: Optional[torch.Tensor] = None, accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
-    """out[M,N] = A * B^T (+bias) (+out).  `a` is [M,K] (a_mn False) or the transposed storage [K,M]
+         bias: Optional[torch.Tensor] = None, accumulate: bool = False, max_ctas: int = 0,
+         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = A * B^T (+bias) (+residual) (+out).  `a` is [M,K] (a_mn False) or the transposed storage [K,M]
     (a_mn True); `b` is [N,K] or [K,N].  2-D tensors with unit inner stride."""
     lib = require()
     M, N = out.shape
@@ -130,9 +132,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False
     for t in (a, b, out):
         if t.dim() != 2 or t.stride(1) != 1 or t.dtype != bf16:
             raise ValueError("gemm operands must be 2-D bf16 with unit inner stride")
-    rc = lib.sb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), M, N, K, a.stride(0), b.stride(0),
-                          out.stride(0), int(a_mn), int(b_mn), int(accumulate), status_word(out.device).data_ptr(),
-                          max_ctas, _stream())
+    if residual is not None and (residual.dim() != 2 or residual.stride(1) != 1 or residual.dtype != bf16
+                                 or tuple(residual.shape) != (M, N)):
+        raise ValueError("gemm residual must be a [M, N] bf16 matrix with unit inner stride")
+    rc = lib.sb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual), M, N, K, a.stride(0),
+                          b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, int(a_mn),
+                          int(b_mn), int(accumulate), status_word(out.device).data_ptr(), max_ctas, _stream())
     if rc != 0:
         detail = lib.sb_gemm_last_error_detail()
         raise RuntimeError(f"gemm_bf16 failed (code {rc}, operand {detail >> 16}, driver result {detail & 0xffff}): "
@@ -143,42 +148,69 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False
     return out
 
 
+def colsum(x2: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a [T, N] bf16 matrix (bias gradients) without an fp32 copy of the matrix."""
+    lib = require()
+    T, N = x2.shape
+    out = torch.zeros(N, dtype=torch.float32, device=x2.device)
+    _check(lib.sb_colsum(x2.data_ptr(), out.data_ptr(), T, N, _stream()), "colsum")
+    _count()
+    return out
+
+
+def _rows(x):
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    return x2
+
+
 class _Linear(torch.autograd.Function):
+    """y = x w^T (+ bias) (+ residual).  The weight gradient is accumulated by the GEMM epilogue directly into
+    `w.grad` when the parameter lives in a persistent flat gradient buffer (marked `_fuse_grad_accum` by the
+    ZeRO optimizer): no temporary gradient, no separate accumulation pass."""
+
     @staticmethod
-    def forward(ctx, x, w, bias):
-        x2 = x.reshape(-1, x.shape[-1])
-        if x2.stride(1) != 1 or (x2.stride(0) % 8):
-            x2 = x2.contiguous()
+    def forward(ctx, x, w, bias, residual):
+        x2 = _rows(x)
         out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
-        gemm(x2, w, out, bias=bias)
+        r2 = _rows(residual) if residual is not None else None
+        gemm(x2, w, out, bias=bias, residual=r2)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
         ctx.xshape = x.shape
+        ctx.wref = w
         return out.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, gy):
         x2, w = ctx.saved_tensors
-        g2 = gy.reshape(-1, gy.shape[-1])
-        if g2.stride(1) != 1 or (g2.stride(0) % 8):
-            g2 = g2.contiguous()
+        g2 = _rows(gy)
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             gx = torch.empty_like(x2)
             gemm(g2, w, gx, a_mn=False, b_mn=True)                 # dX[T,K] = dY[T,N] . W[N,K]
             gx = gx.view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            gw = torch.empty_like(w)
-            gemm(g2, x2, gw, a_mn=True, b_mn=True)                 # dW[N,K] = dY^T[N,T] . X[T,K]
+            wp = ctx.wref
+            tgt = wp.grad if getattr(wp, "_fuse_grad_accum", False) else None
+            if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == w.shape:
+                gemm(g2, x2, tgt, a_mn=True, b_mn=True, accumulate=True)   # dW += dY^T X, straight into the flat buffer
+            else:
+                gw = torch.empty_like(w)
+                gemm(g2, x2, gw, a_mn=True, b_mn=True)             # dW[N,K] = dY^T[N,T] . X[T,K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = g2.float().sum(0).to(gy.dtype)
-        return gx, gw, gb
+            gb = colsum(g2).to(gy.dtype) if g2.shape[1] % 8 == 0 else g2.float().sum(0).to(gy.dtype)
+        gr = gy if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        return gx, gw, gb, gr
 
 
-def linear(x, w, bias=None, fp8: bool = False):
-    if not _is_bf16(x, w, bias) or (w.shape[0] % 8) or (w.shape[1] % 8):
-        return ref.linear(x, w, bias)
-    return _Linear.apply(x, w, bias)
+def linear(x, w, bias=None, fp8: bool = False, residual=None):
+    if not _is_bf16(x, w, bias, residual) or (w.shape[0] % 8) or (w.shape[1] % 8):
+        y = ref.linear(x, w, bias)
+        return y if residual is None else y + residual
+    return _Linear.apply(x, w, bias, residual)
 
 
 def linear_allgather(x, w, bias, seq_dim, fp8):

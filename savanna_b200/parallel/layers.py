@@ -113,8 +113,16 @@ class RowParallelLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):
+        """With `residual` the layer returns (residual + x A^T + bias, None): on one tensor-parallel rank both
+        additions happen in the GEMM epilogue."""
         tp = state.get_model_parallel_world_size()
+        if residual is not None:
+            if tp == 1 and self.input_is_parallel:
+                return ops.linear(x, self.weight, self.bias, fp8=self.fp8, residual=residual), None
+            y, b = self.forward(x, None)
+            y = y + b if b is not None else y
+            return residual + y, None
         if not self.input_is_parallel:
             x = mappings.scatter_to_model_parallel_region(x)
         if self.sequence_parallel and not self.parallel_output:

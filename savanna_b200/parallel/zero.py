@@ -55,6 +55,7 @@ class FlatGroup:
                 view.copy_(p.data)
                 p.data = view
                 p.grad = self.flat_grad[off:off + n].view(p.shape)
+                p._fuse_grad_accum = True           # GEMM epilogues may accumulate weight gradients in place
                 self.offsets.append(off)
                 off += n
         lo, hi = rank * self.shard, (rank + 1) * self.shard

@@ -289,3 +289,30 @@ def test_hyena_li(L, O, state):
     if state:
         _rel(s_out, sor, 1e-3, "li state_out")
         _rel(s_in.grad, sr.grad, 3e-2, "li dstate_in")
+
+
+def test_linear_residual_epilogue_and_inplace_grad_accumulation():
+    torch.manual_seed(20)
+    x = torch.randn(3, 100, 256, device=DEV, dtype=BF, requires_grad=True)
+    res = torch.randn(3, 100, 384, device=DEV, dtype=BF, requires_grad=True)
+    w = torch.nn.Parameter((torch.randn(384, 256, device=DEV) * 0.05).to(BF))
+    b = torch.nn.Parameter(torch.randn(384, device=DEV, dtype=BF))
+    w.grad = torch.zeros_like(w)
+    w._fuse_grad_accum = True                       # what the ZeRO flat buffer sets
+    grad_buffer = w.grad
+    g1, g2 = torch.randn(3, 100, 384, device=DEV, dtype=BF), torch.randn(3, 100, 384, device=DEV, dtype=BF)
+    for g in (g1, g2):                              # two micro-steps accumulate into the same buffer
+        y = ops.linear(x, w, b, residual=res)
+        y.backward(g)
+    _status_ok()
+    assert w.grad is grad_buffer
+    xr, rr = x.detach().float().requires_grad_(), res.detach().float().requires_grad_()
+    wr, br = w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    for g in (g1, g2):
+        yr = ref.linear(xr, wr, br) + rr
+        yr.backward(g.float())
+    _rel(y, yr, 1e-2, "linear+residual fwd")
+    _rel(w.grad, wr.grad, 2e-2, "in-place accumulated dW")
+    _rel(b.grad, br.grad, 1e-2, "bias grad (colsum)")
+    _rel(x.grad, xr.grad, 1e-2, "dx")
+    _rel(res.grad, rr.grad, 1e-2, "dresidual")
