@@ -272,7 +272,7 @@ extern "C" int sb_gemm_last_error_detail() { return sb::g_last_detail; }
 
 // C = A * B^T (+bias) (+residual) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
 // transposed as [K, M] with leading dim lda.  b_mn likewise for B ([N, K] or [K, N]).  All leading dims and
-// base addresses must be 16-byte aligned; N and K multiples of 8.  Returns 0 on a successful launch.
+// base addresses must be 16-byte aligned; N a multiple of 8, and K too unless both operands are MN-major.  Returns 0 on a successful launch.
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
                             int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int beta, unsigned int* status,
                             int max_ctas, cudaStream_t stream) {
@@ -282,7 +282,8 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   // yet (e.g. an autograd worker on its first launch) has none until the runtime binds the primary context.
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
-  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || (a_mn && (M % 8))) return -3;
+  // K only has to be a multiple of 8 where it is the contiguous dim of an operand (a K-major one)
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldc % 8) || ((!a_mn || !b_mn) && (K % 8))) return -3;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
   CUtensorMap tmA, tmB;
   int rc;
