@@ -49,15 +49,33 @@ class Backbone(nn.Module):
         first = self.layer_range.start == 0
         last = self.layer_range.stop == N
         self.has_embedding, self.has_head = first or not cfg.no_weight_tying and last, last
+        # Every component draws its initial weights from its own seeded stream (seed + component index), so a
+        # layer is initialised identically whichever pipeline stage builds it and whatever else that stage holds.
+        def seeded(idx):
+            s = (cfg.seed or 0) + 7919 * (idx + 1)
+            torch.manual_seed(s)
+            if torch.cuda.is_available():
+                torch.cuda.manual_seed(s)
+        cpu_state = torch.get_rng_state()
+        cuda_state = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
         mods: List[nn.Module] = []
+        seeded(0)
         mods.append(Embedding(cfg, init_m, dtype, device) if self.has_embedding else _Placeholder())
         mods.append(_Placeholder())
         for i in range(N):
-            mods.append(ParallelBlock(cfg, init_m, out_init_m, i, dtype, device) if i in self.layer_range else _Placeholder())
+            if i in self.layer_range:
+                seeded(i + 1)
+                mods.append(ParallelBlock(cfg, init_m, out_init_m, i, dtype, device))
+            else:
+                mods.append(_Placeholder())
         mods.append(_Placeholder())
         mods.append(NormPipe(cfg, dtype, device) if last else _Placeholder())
         if cfg.no_weight_tying and last:
+            seeded(N + 1)
             mods.append(ParallelLinear(cfg, init_m, parallel_output=True, dtype=dtype, device=device))
+        torch.set_rng_state(cpu_state)
+        if cuda_state is not None:
+            torch.cuda.set_rng_state(cuda_state)
         self.sequential = nn.ModuleList(mods)
         self.checkpoint_activations = cfg.checkpoint_activations
         self.checkpoint_num_layers = max(1, cfg.checkpoint_num_layers)
@@ -114,7 +132,8 @@ class Backbone(nn.Module):
         """tokens [B, L_local] -> logits [B, L_local, V/tp] (vocab-parallel when tp > 1).
         Pipeline stages pass `hidden_in` instead of tokens and set `return_hidden`."""
         if positions is None:
-            positions = torch.arange(tokens.shape[1], device=tokens.device)
+            ref_t = tokens if tokens is not None else hidden_in
+            positions = torch.arange(ref_t.shape[1], device=ref_t.device)
         x = self.embedding(tokens, positions) if hidden_in is None else hidden_in
         x = self._run_blocks(x, positions)
         if return_hidden or not self.has_head:

@@ -106,6 +106,8 @@ class FusedZeroStep:
         tp = state.get_model_parallel_world_size()
         if tp > 1:
             dist.all_reduce(sq, group=state.get_model_parallel_group())
+        if state.get_pipe_parallel_world_size() > 1:
+            dist.all_reduce(sq, group=state.get_pipe_parallel_group())
         norm = sq.sqrt()
         opt.last_grad_norm = norm
         if opt.clip_grad > 0.0:

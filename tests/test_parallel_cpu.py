@@ -210,3 +210,10 @@ def test_zero1_data_parallel_equivalence():
     """dp=2 with micro batch 1 and ZeRO-1 partitioning == one process with micro batch 2."""
     ref_losses = _reference_losses(mb=2)
     run_distributed(_w_equiv, 2, {"train_micro_batch_size_per_gpu": 1, "zero_optimization": {"stage": 1}}, ref_losses)
+
+
+@pytest.mark.slow
+def test_pipeline_parallel_equivalence():
+    """Two pipeline stages (tied embedding on both ends) reproduce the single-process loss trace."""
+    ref_losses = _reference_losses()
+    run_distributed(_w_equiv, 2, {"pipe_parallel_size": 2, "gradient_accumulation_steps": 1}, ref_losses)
