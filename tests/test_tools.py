@@ -1,0 +1,99 @@
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from savanna_b200.config import GlobalConfig
+from savanna_b200.data.synthetic import acgt_batch
+from savanna_b200.train.trainer import Trainer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = os.path.join(ROOT, "configs", "baseline", "tiny_sh2_cpu.yml")
+
+
+@pytest.fixture()
+def tiny_ckpt(tmp_path):
+    from savanna_b200.ckpt import save_checkpoint
+    cfg = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1, "save": str(tmp_path / "ck"),
+                                          "zero_optimization": {"stage": 1}})
+    tr = Trainer(cfg, load=False)
+    tr.train_step(iter([{"text": acgt_batch(2, cfg.seq_length, 0)}]))
+    return tr, save_checkpoint(tr)
+
+
+def test_tp_reshard_roundtrip(tiny_ckpt, tmp_path):
+    from savanna_b200.tools.reshard_model_parallel import load_shards, reshard
+    tr, d = tiny_ckpt
+    reshard(d, str(tmp_path / "mp4"), 4)
+    parts = load_shards(str(tmp_path / "mp4"))
+    assert len(parts) == 4
+    assert parts[0]["module"]["sequential.2.mixer.dense_projection.weight"].shape == (192, 256)
+    assert parts[0]["module"]["sequential.2.mixer.dense.weight"].shape == (256, 64)
+    assert parts[0]["module"]["sequential.2.input_layernorm.weight"].shape == (256,)
+    reshard(str(tmp_path / "mp4"), str(tmp_path / "mp1"), 1)
+    back = load_shards(str(tmp_path / "mp1"))[0]["module"]
+    for k, v in tr.model.state_dict().items():
+        assert torch.equal(back[k], v.cpu()), k
+
+
+def test_interleave_roundtrip():
+    from savanna_b200.tools.interleave_model_states import deinterleave_rows, interleave_rows
+    w = torch.arange(12 * 2).view(12, 2)
+    i = interleave_rows(w)
+    assert i[0].tolist() == w[0].tolist() and i[1].tolist() == w[4].tolist() and i[2].tolist() == w[8].tolist()
+    assert torch.equal(deinterleave_rows(i), w)
+
+
+def test_extend_filter(tiny_ckpt):
+    from savanna_b200.tools.extend_filter import extend_module
+    tr, _ = tiny_ckpt
+    mod = {k: v.cpu() for k, v in tr.model.state_dict().items()}
+    out = extend_module(mod, 4096, taps=128)
+    h = out["sequential.3.mixer.mixer.filter.h"]
+    assert h.shape == (16, 4096) and torch.equal(h[:, :128], mod["sequential.3.mixer.mixer.filter.h"][:, :128])
+    assert out["sequential.3.mixer.mixer.filter.decay"].shape == (16, 4096)
+    assert out["sequential.4.mixer.mixer.filter.t"].shape == (1, 1, 4096)
+
+
+def test_zero_to_fp32_and_dp_reshard(tiny_ckpt, tmp_path):
+    from savanna_b200.tools.reshard_zero import reshard
+    from savanna_b200.tools.zero_to_fp32 import consolidate
+    tr, d = tiny_ckpt
+    sd = consolidate(d)
+    for k, v in tr.model.state_dict().items():
+        assert torch.allclose(sd[k].float(), v.float().cpu(), atol=1e-6), k
+    reshard(d, str(tmp_path / "dp4"), 4)
+    sd4 = consolidate(str(tmp_path / "dp4"))
+    for k in sd:
+        assert torch.equal(sd[k], sd4[k]), k
+
+
+def test_vortex_export(tiny_ckpt):
+    from savanna_b200.tools.convert_checkpoint_to_vortex import convert
+    tr, _ = tiny_ckpt
+    out = convert({k: v.cpu() for k, v in tr.model.state_dict().items()})
+    for k in ("blocks.0.filter.h", "blocks.1.filter.h", "blocks.2.filter.log_poles", "blocks.2.filter.residues",
+              "blocks.3.inner_mha_cls.Wqkv.weight", "blocks.0.mlp.l1.weight", "embedding_layer.weight", "norm.scale"):
+        assert k in out, k
+    assert out["blocks.1.filter.h"].shape == (16, 1, 128)
+
+
+def test_preprocess_and_load(tmp_path):
+    from savanna_b200.data.indexed_dataset import MMapIndexedDataset
+    from savanna_b200.tools.preprocess_data import main
+    src = tmp_path / "d.jsonl"
+    src.write_text("\n".join(json.dumps({"text": t}) for t in ("ACGT", "GGGTTTAAAC", "T")) + "\n")
+    main(["--input", str(src), "--output-prefix", str(tmp_path / "out"), "--append-eod"])
+    ds = MMapIndexedDataset(str(tmp_path / "out_text_document"))
+    assert len(ds) == 3 and ds[0].tolist() == [65, 67, 71, 84, 0] and ds[2].tolist() == [84, 0]
+
+
+def test_generation_greedy_is_deterministic():
+    from savanna_b200.inference import generate
+    cfg = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1})
+    tr = Trainer(cfg, load=False)
+    a = generate(tr.model, cfg.tokenizer, ["ACGT", "GG"], maximum_tokens=5)
+    b = generate(tr.model, cfg.tokenizer, ["ACGT", "GG"], maximum_tokens=5)
+    assert [r["text"] for r in a] == [r["text"] for r in b] and all(r["length"] >= 5 for r in a)
