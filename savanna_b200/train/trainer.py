@@ -93,6 +93,12 @@ class Trainer:
             gc.disable()
         self.iteration = 0
         self.tokens_seen = 0
+        if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.sequence_parallel
+                and state.get_model_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
+            from ..parallel import fused_tp
+            on = fused_tp.setup()
+            print_rank_0(" > tensor-parallel projections: " + ("fused all-gather->GEMM / GEMM->reduce-scatter kernels"
+                                                               if on else "NCCL collectives + GEMM"))
         self.model, self.optimizer, self.lr_scheduler = self._setup_model_and_optimizer()
         self.gas = cfg.gradient_accumulation_steps
         self.micro_batch = cfg.train_micro_batch_size_per_gpu
