@@ -28,7 +28,10 @@ namespace tp {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2, STAGE_BYTES = A_STAGE + B_STAGE;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_LD = 72;                                   // staged epilogue row: 64 columns + 8 pad (144 B)
+constexpr int EPI_BYTES = 4 * 32 * EPI_LD * 2;               // 4 epilogue warps x 32 rows
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_BYTES;
+constexpr int CP_NB = 5, CP_CHUNK = 32768, CP_LAG = 3;        // copy CTAs: ring of bulk-copy buffers
 constexpr int TMEM_COLS = 512, GROUP_M = 16, NUM_THREADS = 192, MAXR = 16;
 
 struct Params {
@@ -86,33 +89,82 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
     const int cid = blockIdx.x, n_copy = n_copy_ctas;
     const int n_remote = m_tiles - p.ag_tiles_per_rank;
     const int vec_per_row = p.K >> 3;
+    const bool contiguous = p.ag_src_ld == p.K && p.K * 2 <= CP_CHUNK;   // whole rows per bulk chunk
+    const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
+    const uint32_t cbar = ring + CP_NB * CP_CHUNK;                       // CP_NB mbarriers
+    __shared__ int copy_abort;
+    if (threadIdx.x == 0) {
+      copy_abort = 0;
+      for (int b = 0; b < CP_NB; ++b) mbar_init(cbar + 8u * b, 1);
+      fence_barrier_init();
+    }
+    __syncthreads();
+    uint32_t issued = 0, done = 0;                                       // chunk counters over the whole CTA lifetime
     for (int idx = cid; idx < n_remote; idx += n_copy) {
       const int mt = (first_local_tile + p.ag_tiles_per_rank + idx) % m_tiles;     // rotated order: next rank's shard first
       const int src_rank = mt / p.ag_tiles_per_rank;
       const int src_row0 = (mt - src_rank * p.ag_tiles_per_rank) * BM;
-      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld);
-      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * p.K);
       const int rows = min(BM, p.M - mt * BM);
-      const int total = rows * vec_per_row;
-      const int src_ld8 = p.ag_src_ld >> 3;
-      // 8 independent 16-byte peer loads in flight per thread
-      for (int i = threadIdx.x; i < total; i += NUM_THREADS * 8) {
-        uint4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int j = i + u * NUM_THREADS;
-          if (j < total) { const int r = j / vec_per_row, c = j - r * vec_per_row; v[u] = src[(size_t)r * src_ld8 + c]; }
+      if (contiguous) {
+        // one thread drives a ring of bulk copies: peer memory -> shared -> local gather buffer
+        if (threadIdx.x == 0) {
+          const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * p.K);
+          char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * p.K);
+          const uint32_t row_bytes = (uint32_t)p.K * 2u;
+          const uint32_t rows_per_chunk = max(1u, CP_CHUNK / row_bytes);
+          const uint32_t chunk = rows_per_chunk * row_bytes;
+          const uint32_t total = (uint32_t)rows * row_bytes;
+          const uint32_t n_chunks = (total + chunk - 1) / chunk;
+          bool ok = chunk <= (uint32_t)CP_CHUNK;
+          for (uint32_t i = 0; ok && i < n_chunks + CP_LAG; ++i) {
+            if (i < n_chunks) {
+              const uint32_t b = issued % CP_NB;
+              bulk_wait_read<CP_NB - CP_LAG - 1>();                      // the store that last used this buffer has read it
+              const uint32_t off = i * chunk, sz = min(chunk, total - off);
+              mbar_expect_tx(cbar + 8u * b, sz);
+              bulk_load(ring + b * CP_CHUNK, src + off, sz, cbar + 8u * b);
+              ++issued;
+            }
+            if (i >= (uint32_t)CP_LAG) {
+              const uint32_t j = i - CP_LAG;
+              const uint32_t b = done % CP_NB, par = (done / CP_NB) & 1u;
+              if (!mbar_wait(cbar + 8u * b, par, &copy_abort, p.status, ST_TIMEOUT_PEER)) { ok = false; break; }
+              const uint32_t off = j * chunk, sz = min(chunk, total - off);
+              bulk_store(dst + off, ring + b * CP_CHUNK, sz);
+              bulk_commit();
+              ++done;
+            }
+          }
+          bulk_wait<0>();                                                // all stores of this tile have landed
+          if (ok) {
+            __threadfence();
+            fence_proxy_async();
+            st_release(p.ag_flags + mt, p.ag_epoch);
+          }
         }
+      } else {
+        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld);
+        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * p.K);
+        const int total = rows * vec_per_row;
+        const int src_ld8 = p.ag_src_ld >> 3;
+        for (int i = threadIdx.x; i < total; i += NUM_THREADS * 8) {
+          uint4 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int j = i + u * NUM_THREADS;
-          if (j < total) dst[j] = v[u];
+          for (int u = 0; u < 8; ++u) {
+            const int j = i + u * NUM_THREADS;
+            if (j < total) { const int r = j / vec_per_row, c = j - r * vec_per_row; v[u] = src[(size_t)r * src_ld8 + c]; }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int j = i + u * NUM_THREADS;
+            if (j < total) dst[j] = v[u];
+          }
         }
+        __threadfence();
+        fence_proxy_async();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release(p.ag_flags + mt, p.ag_epoch);
       }
-      __threadfence();
-      fence_proxy_async();                      // the consumers read this tile through TMA (async proxy)
-      __syncthreads();
-      if (threadIdx.x == 0) st_release(p.ag_flags + mt, p.ag_epoch);
     }
     return;
   }
@@ -228,18 +280,48 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
       const int n0 = nt * BN;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       __nv_bfloat16* crow;
+      bool staged = false;
+      __nv_bfloat16* wbase = nullptr;                 // staged path: destination of row (mt*BM + q*32) of this warp
       if (rs) {
-        const int owner = row / p.rs_rows_per_owner, lr = row - owner * p.rs_rows_per_owner;
-        crow = p.rs_dst[owner < p.rs_world ? owner : 0] + ((size_t)p.rs_me * p.rs_rows_per_owner + lr) * p.N;
+        const int row_w = mt * BM + q * 32;           // rows of one warp never straddle owners (rows_per_owner % 128 == 0)
+        const int owner = row_w / p.rs_rows_per_owner, lr = row_w - owner * p.rs_rows_per_owner;
+        const int ow = owner < p.rs_world ? owner : 0;
+        wbase = p.rs_dst[ow] + ((size_t)p.rs_me * p.rs_rows_per_owner + lr) * p.N;
+        crow = wbase + (size_t)lane * p.N;
+        staged = ow != p.rs_me;                       // peer rows: coalesce through shared memory into 128-byte row segments
       } else {
         crow = p.C + (size_t)row * p.ldc;
       }
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem_gen + STAGES * STAGE_BYTES + 256) + q * 32 * EPI_LD;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_wait_ld();
         const int col0 = n0 + c * 32;
+        if (staged) {
+          __nv_bfloat16* srow = stg + lane * EPI_LD + (c & 1) * 32;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 out;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+            *reinterpret_cast<uint4*>(srow + v * 8) = out;
+          }
+          if (c & 1) {
+            __syncwarp();
+            const int cbase = n0 + (c - 1) * 32;      // first of the 64 staged columns
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3), cv = (lane & 7) * 8;
+              if (mt * BM + q * 32 + rr < p.M && cbase + cv + 8 <= p.N)
+                *reinterpret_cast<uint4*>(wbase + (size_t)rr * p.N + cbase + cv) = *reinterpret_cast<const uint4*>(stg + rr * EPI_LD + cv);
+            }
+            __syncwarp();
+          }
+          continue;
+        }
         if (row < p.M && col0 < p.N) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -368,7 +450,7 @@ extern "C" int sb_gemm_tp(const void* A, int lda, const void* B, int ldb, int b_
   else       rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK);
   if (rc) return rc;
   if (rs) {
-    if (rs_world > MAXR || (M % rs_world)) return -8;
+    if (rs_world > MAXR || (M % rs_world) || ((M / rs_world) % BM)) return -8;
     p.rs_world = rs_world; p.rs_me = rs_me; p.rs_rows_per_owner = M / rs_world;
     for (int r = 0; r < rs_world; ++r) p.rs_dst[r] = (__nv_bfloat16*)rs_dst[r];
   } else if (ldc % 8) return -3;

@@ -48,12 +48,28 @@ class TPWorkspace:
         self.token = torch.zeros(1, device=self.dev)
         self.flags = torch.zeros(8192, dtype=torch.int32, device=self.dev)
         self.epoch = 0
+        self.lib.sb_peer_barrier.restype = I
+        self.lib.sb_peer_barrier.argtypes = [P, I, I, I, P, P]
+        # signal words of the device-side barrier (int32[world] per rank, zeroed before anyone signals)
+        self.sig = symm_mem.empty(32, dtype=torch.int32, device=self.dev)
+        self.sig.zero_()
+        hs = symm_mem.rendezvous(self.sig, self.group)
+        self.sig_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hs.buffer_ptrs])
+        self.bar_epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)               # every rank's signal words are zero before the first device barrier
         self.symm: Dict[Tuple[str, int, int], Tuple[torch.Tensor, object]] = {}
         self.local: Dict[Tuple[str, int], torch.Tensor] = {}
         self.parity: Dict[str, int] = {}
 
     def barrier(self) -> None:
-        dist.all_reduce(self.token, group=self.group)
+        """Stream-ordered barrier over the group: one small kernel with bounded peer waits (csrc/peer_barrier.cu)."""
+        self.bar_epoch += 1
+        rc = self.lib.sb_peer_barrier(self.sig_ptrs, self.rank, self.world, self.bar_epoch,
+                                      self.cuda_ops.status_word(self.dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"sb_peer_barrier failed ({rc})")
+        self.cuda_ops._count()
 
     def symm_buffer(self, name: str, numel: int):
         """Next slot (of two) of a symmetric bf16 buffer; allocation + rendezvous happen once per (name, size, slot)."""
