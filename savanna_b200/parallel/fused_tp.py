@@ -11,7 +11,7 @@ savanna/mpu/layers.py:525-560 and :746-786 (NCCL all-gather / reduce-scatter nex
 
 Both entry points return None when the fused path does not apply (workspace not set up, tensor-parallel size 1,
 micro-batch > 1, shard not a multiple of 128 rows, non-bf16): the caller then runs the NCCL collective and the GEMM
-separately.  Cross-GPU ordering uses stream-ordered barriers (a one-element all-reduce); symmetric staging buffers are
+separately.  Cross-GPU ordering uses stream-ordered device barriers (csrc/peer_barrier.cu, bounded waits); symmetric staging buffers are
 double-buffered so that a rank can stage its next operand while a peer still reads the previous one.
 """
 from __future__ import annotations
