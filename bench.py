@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is then not the named config)")
     ap.add_argument("--accum", type=int, default=None, help="debug only: accumulation steps per optimizer step")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="fp8 (e4m3/e5m2, per-tensor scaling) projections, as the reference's 7B configs enable")
     ap.add_argument("--comm", type=str, default=None, choices=["symm", "nccl"], help="ZeRO collective path (default: config)")
     return ap.parse_args()
 
@@ -137,6 +138,9 @@ def main():
         over["gradient_accumulation_steps"] = args.accum
     if args.comm:
         over["comm_path"] = args.comm
+    if args.fp8:
+        over.update({"use_fp8_linears": True, "use_fp8_input_projections": True, "use_fp8_output_projections": True,
+                     "use_fp8_mlp_projections": True})
     if args.layers:
         import yaml
         doc = yaml.load(open(args.config), Loader=yaml.FullLoader)
@@ -234,7 +238,8 @@ def main():
         out = {
             "metric": "train tokens/sec (Evo2-7B-style StripedHyena 2 @8K, ZeRO-1 DP)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 (fp8 e4m3/e5m2 projection GEMMs, per-tensor scaling)" if args.fp8 else "bf16",
             "data": "synthetic uniform ACGT bytes; random-init weights", "impl": args.impl,
             "config": {"model": "evo2-7b-style-sh2 (32L, D4096, 32 heads, ffn 11264, vocab 512)" if not args.layers
                        else f"DEBUG {args.layers}-layer truncation (not the named config)",

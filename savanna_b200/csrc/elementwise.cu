@@ -3,6 +3,7 @@
 // All use 16-byte vector accesses; grids are sized from the problem, row kernels use one CTA per row
 // (forward) or a grid-stride over rows with per-thread column ownership (weight-gradient reductions).
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -354,6 +355,40 @@ colsum_kernel(const bf16* __restrict__ x, float* __restrict__ out, int T, int N,
   }
 }
 
+// ------------------------------------------------------------------------------------ fp8 quantisation (per tensor)
+// amax: max |x| over the tensor (atomicMax on the bit pattern of a non-negative float; zero `out` first)
+__global__ void amax_kernel(const bf16* __restrict__ x, float* __restrict__ out, size_t n8) {
+  float m = 0.f;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float f[8]; unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+}
+// q = saturate(x * fmax / amax) in e4m3 (fmt 0) or e5m2 (fmt 1); scale_inv[0] = amax / fmax (the de-quantisation factor)
+__global__ void quantize_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, size_t n8,
+                                    const float* __restrict__ amax, float* __restrict__ scale_inv, int fmt) {
+  const float fmax = fmt == 0 ? 448.f : 57344.f;
+  const float a = fmaxf(amax[0], 1e-12f);
+  const float scale = fmax / a;
+  if (blockIdx.x == 0 && threadIdx.x == 0) scale_inv[0] = a / fmax;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float f[8]; unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+    uint2 o;
+    unsigned short h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 v = make_float2(f[2 * j] * scale, f[2 * j + 1] * scale);
+      h[j] = fmt == 0 ? __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3) : __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E5M2);
+    }
+    o.x = (unsigned)h[0] | ((unsigned)h[1] << 16);
+    o.y = (unsigned)h[2] | ((unsigned)h[3] << 16);
+    reinterpret_cast<uint2*>(q)[i] = o;
+  }
+}
+
 static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
@@ -464,5 +499,17 @@ extern "C" int sb_adam(float* master, float* m, float* v, const void* grad, void
     adam_kernel<bf16><<<grid, 512, 0, st>>>(master, m, v, (const bf16*)grad, (bf16*)param_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr, scale_host);
   else
     adam_kernel<float><<<grid, 512, 0, st>>>(master, m, v, (const float*)grad, (bf16*)param_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr, scale_host);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// x: n bf16 values (n % 8 == 0) -> q: n bytes; amax and scale_inv are device floats (amax is zeroed here).
+extern "C" int sb_quantize_fp8(const void* x, void* q, float* amax, float* scale_inv, long long n, int fmt, cudaStream_t st) {
+  if (n % 8) return -1;
+  if (n == 0) return 0;
+  const size_t n8 = (size_t)n / 8;
+  const int grid = grid_for(n8, 512, 148 * 8);
+  if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return -2;
+  amax_kernel<<<grid, 512, 0, st>>>((const bf16*)x, amax, n8);
+  quantize_fp8_kernel<<<grid, 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, amax, scale_inv, fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -38,6 +38,8 @@ struct GemmParams {
   int M, N, K, ldc, ldr;
   int beta;                    // 1: C += result (bf16 read-modify-write)
   uint32_t* status;
+  const float* alpha;          // device scalar multiplied into the accumulator (fp8 de-quantisation), or null
+  int a_fmt, b_fmt;            // fp8 operand formats for the instruction descriptor: 0 = e4m3, 1 = e5m2
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
@@ -50,7 +52,9 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   nt = r / gsz;
 }
 
-template <int A_MN, int B_MN>
+// EB = bytes per operand element: 2 = bf16 (kind::f16), 1 = fp8 e4m3 / e5m2 (kind::f8f6f4).  A shared-memory row is
+// always 128 bytes, so a k-block holds 64 bf16 or 128 fp8 values and every MMA consumes 32 bytes of K.
+template <int A_MN, int B_MN, int EB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -69,7 +73,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = 128 / EB;                      // elements of K per k-block
+  constexpr int MNB = 128 / EB;                      // MN elements per 128-byte row of an MN-major box
+  constexpr int MN_BOX_BYTES = BKE * 128;            // one MN-major box: BKE k-rows of 128 bytes
+  const int num_kb = (p.K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -101,18 +108,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_STAGE;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           if (A_MN == 0) {
             tma_load_2d(a_dst, &tmA, k0, m0, full_bar(stage));
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, m0 + 64 * j, k0, full_bar(stage));
+            for (int j = 0; j < BM / MNB; ++j) tma_load_2d(a_dst + j * MN_BOX_BYTES, &tmA, m0 + MNB * j, k0, full_bar(stage));
           }
           if (B_MN == 0) {
             tma_load_2d(b_dst, &tmB, k0, n0, full_bar(stage));
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, n0 + 64 * j, k0, full_bar(stage));
+            for (int j = 0; j < BN / MNB; ++j) tma_load_2d(b_dst + j * MN_BOX_BYTES, &tmB, n0 + MNB * j, k0, full_bar(stage));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -126,9 +133,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
-      constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, a_step = A_MN ? (UMMA_K * 128u) >> 4 : (UMMA_K * 2u) >> 4;
-      constexpr uint32_t b_lbo = B_MN ? 8192u : 16u, b_step = B_MN ? (UMMA_K * 128u) >> 4 : (UMMA_K * 2u) >> 4;
+      constexpr int UK = 32 / EB;                       // K elements per MMA (32 bytes)
+      const uint32_t idesc = EB == 2 ? umma_idesc_bf16(BM, BN, A_MN, B_MN)
+                                     : umma_idesc_fp8(BM, BN, A_MN, B_MN, p.a_fmt, p.b_fmt);
+      constexpr uint32_t a_lbo = A_MN ? (uint32_t)MN_BOX_BYTES : 16u, a_step = A_MN ? (UK * 128u) >> 4 : 2u;
+      constexpr uint32_t b_lbo = B_MN ? (uint32_t)MN_BOX_BYTES : 16u, b_step = B_MN ? (UK * 128u) >> 4 : 2u;
       int stage = 0; uint32_t phase = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       int local = 0;
@@ -146,8 +155,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t adesc = umma_smem_desc(a_addr, a_lbo, 1024u);
           const uint64_t bdesc = umma_smem_desc(a_addr + A_STAGE, b_lbo, 1024u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            if (EB == 2) umma_bf16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_fp8(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -161,6 +171,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase[2] = {0u, 0u};
     int local = 0;
     bool ok = true;
+    const float alpha = p.alpha ? p.alpha[0] : 1.f;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       int mt, nt; tile_coords(tile, m_tiles, n_tiles, mt, nt);
@@ -184,7 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (col + 8 <= p.N) {
               float f[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * alpha;
               if (p.bias) {
                 const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
                 const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
@@ -263,6 +274,22 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// 2-D one-byte tensor map (fp8 operands)
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                    uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) g_last_encode_result = (int)r;
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 static int g_num_sms = 0;
 static int g_last_detail = 0;   // (which operand << 16) | CUresult of the last failed tensor-map encode
 
@@ -300,15 +327,56 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   }
   if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
   GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
-               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status};
+               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, nullptr, 0, 0};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);
-  if (!a_mn && !b_mn) kern = gemm_bf16_kernel<0, 0>;
-  else if (!a_mn && b_mn) kern = gemm_bf16_kernel<0, 1>;
-  else if (a_mn && b_mn) kern = gemm_bf16_kernel<1, 1>;
-  else kern = gemm_bf16_kernel<1, 0>;
+  if (!a_mn && !b_mn) kern = gemm_bf16_kernel<0, 0, 2>;
+  else if (!a_mn && b_mn) kern = gemm_bf16_kernel<0, 1, 2>;
+  else if (a_mn && b_mn) kern = gemm_bf16_kernel<1, 1, 2>;
+  else kern = gemm_bf16_kernel<1, 0, 2>;
+  static bool attr_set[4] = {false, false, false, false};
+  const int idx = a_mn * 2 + b_mn;
+  if (!attr_set[idx]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -5;
+    attr_set[idx] = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}
+
+// fp8 GEMM: C[M,N] (bf16) = alpha * A * B^T (+bias) (+residual) (+C) with one-byte operands (e4m3 = 0 / e5m2 = 1) and
+// fp32 accumulation; `alpha` is a device scalar (product of the operands' de-quantisation scales).  Leading dims and
+// contiguous extents must be multiples of 16 elements.
+extern "C" int sb_gemm_fp8(const void* A, const void* B, void* C, const void* bias, const void* residual, const float* alpha,
+                           int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int a_fmt, int b_fmt,
+                           int beta, unsigned int* status, cudaStream_t stream) {
+  using namespace sb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
+  if ((N % 8) || (lda % 16) || (ldb % 16) || (ldc % 8) || ((!a_mn || !b_mn) && (K % 16))) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d_u8(&tmA, A, K, M, lda, 128, BM);
+  else       rc = make_tmap_2d_u8(&tmA, A, M, K, lda, 128, 128);
+  if (rc) { g_last_detail = (1 << 16) | (g_last_encode_result & 0xffff); return rc; }
+  if (!b_mn) rc = make_tmap_2d_u8(&tmB, B, K, N, ldb, 128, BN);
+  else       rc = make_tmap_2d_u8(&tmB, B, N, K, ldb, 128, 128);
+  if (rc) { g_last_detail = (2 << 16) | (g_last_encode_result & 0xffff); return rc; }
+  if (!g_num_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev); }
+  if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
+  GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
+               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, alpha, a_fmt, b_fmt};
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);
+  if (!a_mn && !b_mn) kern = gemm_bf16_kernel<0, 0, 1>;
+  else if (!a_mn && b_mn) kern = gemm_bf16_kernel<0, 1, 1>;
+  else if (a_mn && b_mn) kern = gemm_bf16_kernel<1, 1, 1>;
+  else kern = gemm_bf16_kernel<1, 0, 1>;
   static bool attr_set[4] = {false, false, false, false};
   const int idx = a_mn * 2 + b_mn;
   if (!attr_set[idx]) {

@@ -52,6 +52,8 @@ class _Sig:
     P, I, F, LL = c_void_p, c_int, c_float, c_ll
     sb_gemm_bf16 = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P]
     sb_colsum = [P, P, I, I, P]
+    sb_gemm_fp8 = [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P]
+    sb_quantize_fp8 = [P, P, P, P, LL, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd = [P, P, P, P, P, P, I, I, F, I, P]
     sb_glu_fwd = [P, P, LL, I, I, P]
@@ -206,7 +208,96 @@ class _Linear(torch.autograd.Function):
         return gx, gw, gb, gr
 
 
+# ----------------------------------------------------------------------------- fp8 projections (per-tensor scaling)
+
+E4M3, E5M2 = 0, 1
+PARAM_EPOCH = 0          # bumped by the optimizer after every parameter update: invalidates cached fp8 weights
+
+
+def bump_param_epoch() -> None:
+    global PARAM_EPOCH
+    PARAM_EPOCH += 1
+
+
+def quantize_fp8(x2: torch.Tensor, fmt: int):
+    """Per-tensor current scaling: q = sat(x * fmax / amax(x)) as bytes, plus the de-quantisation factor (device scalar)."""
+    lib = require()
+    q = torch.empty(x2.shape, dtype=torch.uint8, device=x2.device)
+    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
+    sinv = torch.empty(1, dtype=torch.float32, device=x2.device)
+    _check(lib.sb_quantize_fp8(x2.data_ptr(), q.data_ptr(), amax.data_ptr(), sinv.data_ptr(), x2.numel(), fmt, _stream()),
+           "quantize_fp8")
+    _count(2)
+    return q, sinv
+
+
+def gemm_fp8(a, b, out, alpha, a_mn=False, b_mn=False, a_fmt=E4M3, b_fmt=E4M3, bias=None, residual=None, accumulate=False):
+    lib = require()
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    rc = lib.sb_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual), alpha.data_ptr(), M, N, K,
+                         a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                         int(a_mn), int(b_mn), a_fmt, b_fmt, int(accumulate), status_word(out.device).data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_fp8 failed (code {rc}): M={M} N={N} K={K} a{tuple(a.shape)} b{tuple(b.shape)} a_mn={a_mn} b_mn={b_mn}")
+    _count()
+    return out
+
+
+def _fp8_weight(w):
+    cache = getattr(w, "_fp8_cache", None)
+    if cache is None or cache[0] != PARAM_EPOCH:
+        wq, sw = quantize_fp8(w.detach(), E4M3)
+        cache = (PARAM_EPOCH, wq, sw)
+        w._fp8_cache = cache
+    return cache[1], cache[2]
+
+
+class _LinearFP8(torch.autograd.Function):
+    """Projection with fp8 tensor-core operands (e4m3 activations and weights, e5m2 output gradients — the HYBRID
+    recipe of the reference's TransformerEngine layers, savanna/model/tengine.py:17-20), per-tensor current scaling,
+    fp32 accumulation, bf16 results.  The quantised activation is reused by the weight-gradient GEMM; quantised
+    weights are cached until the optimizer updates the parameters."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = _rows(x)
+        xq, sx = quantize_fp8(x2, E4M3)
+        wq, sw = _fp8_weight(w)
+        out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
+        r2 = _rows(residual) if residual is not None else None
+        gemm_fp8(xq, wq, out, sx * sw, bias=bias, residual=r2)
+        ctx.save_for_backward(xq, sx, wq, sw)
+        ctx.has_bias, ctx.has_res, ctx.xshape, ctx.wref = bias is not None, residual is not None, x.shape, w
+        return out.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        xq, sx, wq, sw = ctx.saved_tensors
+        g2 = _rows(gy)
+        gq, sg = quantize_fp8(g2, E5M2)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.empty((g2.shape[0], wq.shape[1]), dtype=bf16, device=gy.device)
+            gemm_fp8(gq, wq, gx, sg * sw, b_mn=True, a_fmt=E5M2, b_fmt=E4M3)
+            gx = gx.view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            wp = ctx.wref
+            tgt = wp.grad if getattr(wp, "_fuse_grad_accum", False) else None
+            if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == wp.shape:
+                gemm_fp8(gq, xq, tgt, sg * sx, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True)
+            else:
+                gw = torch.empty(wp.shape, dtype=bf16, device=gy.device)
+                gemm_fp8(gq, xq, gw, sg * sx, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g2).to(gy.dtype)
+        gr = gy if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        return gx, gw, gb, gr
+
+
 def linear(x, w, bias=None, fp8: bool = False, residual=None):
+    if fp8 and _is_bf16(x, w, bias, residual) and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0:
+        return _LinearFP8.apply(x, w, bias, residual)
     if not _is_bf16(x, w, bias, residual) or (w.shape[0] % 8) or (w.shape[1] % 8):
         y = ref.linear(x, w, bias)
         return y if residual is None else y + residual

@@ -162,6 +162,9 @@ class ZeroOptimizer:
     @torch.no_grad()
     def step(self) -> torch.Tensor:
         """Runs one optimizer step; returns the global gradient norm (0-dim fp32 tensor, on device)."""
+        if self.groups and self.groups[0].flat_param.is_cuda:
+            from ..ops import cuda_ops
+            cuda_ops.bump_param_epoch()             # cached fp8 copies of the weights are stale after this step
         if self.fused is not None:
             return self.fused.step(self)
         self.step_count += 1

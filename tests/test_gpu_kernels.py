@@ -316,3 +316,64 @@ def test_linear_residual_epilogue_and_inplace_grad_accumulation():
     _rel(b.grad, br.grad, 1e-2, "bias grad (colsum)")
     _rel(x.grad, xr.grad, 1e-2, "dx")
     _rel(res.grad, rr.grad, 1e-2, "dresidual")
+
+
+@pytest.mark.parametrize("layout", ["tn", "dgrad", "wgrad"])
+def test_gemm_fp8_layouts(layout):
+    """fp8 operands, per-tensor scales: compare against the product of the DE-QUANTISED operands (exact fp32 math),
+    so only accumulation order and the bf16 output rounding remain."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(30)
+    M, N, K = 384, 512, 640
+
+    def deq(q, sinv, fmt):
+        dt = torch.float8_e4m3fn if fmt == 0 else torch.float8_e5m2
+        return q.view(dt).float() * sinv
+    if layout == "tn":
+        a = torch.randn(M, K, device=DEV, dtype=BF); b = torch.randn(N, K, device=DEV, dtype=BF)
+        aq, sa = cuda_ops.quantize_fp8(a, 0); bq, sb_ = cuda_ops.quantize_fp8(b, 0)
+        out = torch.empty(M, N, device=DEV, dtype=BF)
+        cuda_ops.gemm_fp8(aq, bq, out, sa * sb_)
+        want = deq(aq, sa, 0) @ deq(bq, sb_, 0).t()
+    elif layout == "dgrad":
+        a = torch.randn(M, K, device=DEV, dtype=BF); bt = torch.randn(K, N, device=DEV, dtype=BF)
+        aq, sa = cuda_ops.quantize_fp8(a, 1); bq, sb_ = cuda_ops.quantize_fp8(bt, 0)
+        out = torch.empty(M, N, device=DEV, dtype=BF)
+        cuda_ops.gemm_fp8(aq, bq, out, sa * sb_, b_mn=True, a_fmt=1, b_fmt=0)
+        want = deq(aq, sa, 1) @ deq(bq, sb_, 0)
+    else:
+        at = torch.randn(K, M, device=DEV, dtype=BF); bt = torch.randn(K, N, device=DEV, dtype=BF)
+        aq, sa = cuda_ops.quantize_fp8(at, 1); bq, sb_ = cuda_ops.quantize_fp8(bt, 0)
+        out = torch.empty(M, N, device=DEV, dtype=BF)
+        cuda_ops.gemm_fp8(aq, bq, out, sa * sb_, a_mn=True, b_mn=True, a_fmt=1, b_fmt=0)
+        want = deq(aq, sa, 1).t() @ deq(bq, sb_, 0)
+    _status_ok()
+    _rel(out, want, 1e-2, f"fp8 gemm {layout}")
+
+
+def test_quantize_fp8_matches_torch():
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(31)
+    x = (torch.randn(256, 512, device=DEV) * 3).to(BF)
+    q, sinv = cuda_ops.quantize_fp8(x, 0)
+    amax = x.float().abs().max()
+    assert abs(float(sinv) - float(amax) / 448.0) < 1e-6 * float(amax)
+    want = (x.float() * (448.0 / amax)).to(torch.float8_e4m3fn)
+    same = (q.view(torch.float8_e4m3fn).float() == want.float()).float().mean()
+    assert same > 0.999, f"only {same.item():.4f} of the fp8 codes agree"
+
+
+def test_linear_fp8_autograd():
+    torch.manual_seed(32)
+    x = torch.randn(2, 128, 512, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(768, 512, device=DEV) * 0.05).to(BF).requires_grad_()
+    y = ops.linear(x, w, None, fp8=True)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.linear(xr, wr)
+    yr.backward(g.float())
+    _status_ok()
+    _rel(y, yr, 6e-2, "fp8 linear fwd")          # e4m3 has 3 mantissa bits: a few percent relative error is the format
+    _rel(x.grad, xr.grad, 8e-2, "fp8 linear dx")
+    _rel(w.grad, wr.grad, 8e-2, "fp8 linear dw")
