@@ -377,3 +377,28 @@ def test_linear_fp8_autograd():
     _rel(y, yr, 6e-2, "fp8 linear fwd")          # e4m3 has 3 mantissa bits: a few percent relative error is the format
     _rel(x.grad, xr.grad, 8e-2, "fp8 linear dx")
     _rel(w.grad, wr.grad, 8e-2, "fp8 linear dw")
+
+
+def test_fp8_training_tracks_bf16():
+    """Same tiny model, same data: the loss trace with fp8 projections stays close to the bf16 one."""
+    import os
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    traces = []
+    for fp8 in (False, True):
+        over = {"global_num_gpus": 1}
+        if fp8:
+            over.update({"use_fp8_linears": True, "use_fp8_input_projections": True, "use_fp8_output_projections": True,
+                         "use_fp8_mlp_projections": True})
+        cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_gpu.yml")], over)
+        tr = Trainer(cfg, load=False)
+        batches = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i).cuda()} for i in range(30)])
+        traces.append([float(tr.train_step(batches)) for _ in range(30)])
+        state.destroy_model_parallel()
+    a, b = traces
+    assert b[-1] < b[0] - 1.5, b
+    assert abs(a[-1] - b[-1]) < 0.08 * a[-1], (a[-1], b[-1])
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.25, (a, b)
