@@ -91,6 +91,13 @@ def bench_gemm(T, iters):
         report(f"gemm.{name}.dgrad.cublas", timeit(lambda: torch.matmul(gy, w, out=gx), iters), fl)
         report(f"gemm.{name}.wgrad.ours", timeit(lambda: cuda_ops.gemm(gy, x, gw, a_mn=True, b_mn=True), iters), fl)
         report(f"gemm.{name}.wgrad.cublas", timeit(lambda: torch.matmul(gy.t(), x, out=gw), iters), fl)
+        # fp8 operands (quantisation excluded: it is timed separately below)
+        xq, sx = cuda_ops.quantize_fp8(x, 0); wq, sw = cuda_ops.quantize_fp8(w, 0); gq, sg = cuda_ops.quantize_fp8(gy, 1)
+        al = sx * sw
+        report(f"gemm.{name}.fwd.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(xq, wq, out, al), iters), fl)
+        report(f"gemm.{name}.dgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, wq, gx, al, b_mn=True, a_fmt=1), iters), fl)
+        report(f"gemm.{name}.wgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, xq, gw, al, a_mn=True, b_mn=True, a_fmt=1), iters), fl)
+        report(f"quantize_fp8.{name}.x", timeit(lambda: cuda_ops.quantize_fp8(x, 0), iters), None, M * K * 5)
         cuda_ops.check_status()
 
 
