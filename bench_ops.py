@@ -97,7 +97,9 @@ def bench_gemm(T, iters):
         report(f"gemm.{name}.fwd.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(xq, wq, out, al), iters), fl)
         report(f"gemm.{name}.dgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, wq, gx, al, b_mn=True, a_fmt=1), iters), fl)
         report(f"gemm.{name}.wgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, xq, gw, al, a_mn=True, b_mn=True, a_fmt=1), iters), fl)
-        report(f"quantize_fp8.{name}.x", timeit(lambda: cuda_ops.quantize_fp8(x, 0), iters), None, M * K * 5)
+        report(f"quantize_fp8.{name}.x.current", timeit(lambda: cuda_ops.quantize_fp8(x, 0), iters), None, M * K * 5)
+        site = torch.nn.Parameter(torch.zeros(1, device=x.device))
+        report(f"quantize_fp8.{name}.x.delayed", timeit(lambda: cuda_ops.quantize_fp8_site(x, 0, site, "x"), iters), None, M * K * 3)
         cuda_ops.check_status()
 
 
@@ -190,11 +192,53 @@ def bench_elementwise(T, iters, which):
         report("adam.ours", ms, None, n * 28, n=n)
 
 
+def bench_attention(L, iters, heads=32, small=False):
+    """Causal attention of one 7B layer (32 heads x 128): this framework's tcgen05 kernels and the flash kernels that
+    ship with PyTorch (library baseline).  FLOPs: 4 L^2 hd H / 2 forward, 2.5x that backward."""
+    from savanna_b200.ops import attention_cuda, flash_sm100
+    B, H, hd = 1, heads, 128
+    qkv = torch.randn(B, L, 3, H, hd, device="cuda", dtype=BF)
+    q, k, v = (qkv[:, :, i].detach().requires_grad_() for i in range(3))
+    fl = 4.0 * L * L * hd * H / 2 * B
+    o, lse = flash_sm100.forward(q, k, v, True, hd ** -0.5)
+    go = torch.randn_like(o)
+    report("attention.fwd.ours", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl, L=L, H=H)
+    report("attention.bwd.ours", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
+    if small:
+        return
+
+    def lib_fwd():
+        return attention_cuda._SdpaWithLse.apply(q, k, v, True)
+    report("attention.fwd.torch_flash", timeit(lib_fwd, iters), fl)
+    o2, _ = lib_fwd()
+    fwd_ms = timeit(lib_fwd, iters)
+
+    def lib_fb():
+        oo, _ = lib_fwd()
+        oo.backward(go)
+        q.grad = k.grad = v.grad = None
+    report("attention.bwd.torch_flash", timeit(lib_fb, iters) - fwd_ms, 2.5 * fl)
+    import torch.nn.functional as F
+    qt, kt, vt = (t.detach().transpose(1, 2).requires_grad_() for t in (q, k, v))
+    sd = lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+    sd_f = timeit(sd, iters)
+    report("attention.fwd.torch_sdpa", sd_f, fl)
+
+    def sd_fb():
+        sd().backward(go.transpose(1, 2))
+        qt.grad = kt.grad = vt.grad = None
+    report("attention.bwd.torch_sdpa", timeit(sd_fb, iters) - sd_f, 2.5 * fl)
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq", type=int, default=8192)
-    ap.add_argument("--ops", type=str, default="gemm,dwconv,se,mr,li,norm,glu,ce,adam")
+    ap.add_argument("--ops", type=str, default="gemm,dwconv,se,mr,li,norm,glu,ce,adam,attention")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--own-only", action="store_true", help="attention: time only this framework's kernels")
     a = ap.parse_args()
     which = set(a.ops.split(","))
     torch.cuda.set_device(0)
@@ -204,6 +248,8 @@ def main():
         bench_convs(a.seq, a.iters, which)
     if which & {"norm", "glu", "ce", "adam"}:
         bench_elementwise(a.seq, a.iters, which)
+    if "attention" in which:
+        bench_attention(a.seq, a.iters, a.heads, a.own_only)
 
 
 if __name__ == "__main__":

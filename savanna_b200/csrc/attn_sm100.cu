@@ -1,0 +1,740 @@
+// Flash attention for sm_100a: tcgen05 tensor-core products with TMEM accumulators, TMA-staged operands, online
+// softmax by one thread per query row.  Head dimension 128, bf16 in and out, fp32 accumulation and statistics.
+//
+// Tensors are addressed as [B, L, H, 128] with arbitrary (16-byte aligned) strides for B, L and H, so the q/k/v slices
+// of one fused projection output are read in place.  Both kernels load every operand tile the same way: 128 rows of
+// one head as two TMA boxes of [128 rows x 64 columns] (128-byte rows, 128-byte swizzle).  Such a tile serves as a
+// K-major operand when the contraction runs over the head dimension and as an MN-major operand when it runs over the
+// rows, so no tile is ever transposed in memory.
+//
+// Forward (one CTA = two 128-row query tiles of one head):
+//   warp 0      TMA producer   Q tiles once; per key block one K tile and one V tile (single-buffered, separate
+//                               barriers, so K[j+1] lands during softmax j and V[j+1] during softmax j+1)
+//   warp 1      MMA issuer     S_t = Q_t K^T (TMEM cols t*128), then O_t += P_t V (TMEM cols 256 + t*128); the next S of
+//                               a tile is issued right behind its P V product so the two tiles alternate on the tensor
+//                               pipe while the other one is in its softmax
+//   warps 2-5   softmax of tile 0, warps 6-9 of tile 1: row max, exp2, row sum, P as bf16 into swizzled shared
+//               memory, rescale of O in TMEM only when the running maximum grew by more than 2^8
+//
+// Every wait is bounded (sm100.cuh); on a timeout the CTA records a status code, frees TMEM and returns.
+#include "sm100.cuh"
+
+namespace sb {
+namespace attn {
+
+constexpr int HD = 128;                 // head dimension
+constexpr int BQ = 128;                 // query rows per tile
+constexpr int BK = 128;                 // keys per block
+constexpr int TILE_BYTES = 128 * HD * 2;   // 32 KB: two boxes of 16 KB
+constexpr int BOX_BYTES = 128 * 128;       // 16 KB: 128 rows of 128 bytes
+constexpr int FWD_THREADS = 320;
+constexpr int FWD_SMEM = 6 * TILE_BYTES + 256 + 1024;
+constexpr uint32_t ST_ATTN = 0x20;      // status codes 0x20.. identify attention waits
+
+struct FwdParams {
+  __nv_bfloat16* out;        // [B, Lq, H, 128]
+  float* lse;                // [B, H, Lq] natural-log sum of exp of the scaled scores
+  long long o_sb, o_sl, o_sh;   // element strides of out
+  int B, H, Lq, Lk;
+  int causal;
+  float scale_log2;          // softmax scale * log2(e)
+  float scale;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+// one 128-row tile of head h, batch b, rows l0.. : two boxes (columns 0-63 and 64-127)
+__device__ __forceinline__ void load_tile(uint32_t dst, const void* tmap, int l0, int h, int b, uint32_t bar) {
+  tma_load_4d(dst, tmap, 0, h, l0, b, bar);
+  tma_load_4d(dst + BOX_BYTES, tmap, 64, h, l0, b, bar);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Byte offset of the 16-byte chunk `cc` (8 bf16 columns, 0..15) of row `r` inside a swizzled [128 x 128] bf16 tile.
+__device__ __forceinline__ uint32_t swz_chunk(int r, int cc) {
+  return uint32_t(cc >> 3) * BOX_BYTES + uint32_t(r) * 128u + (uint32_t((cc & 7) ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// K-major operand (contraction over the 128 columns): MMA k-step kk (16 columns) of a tile
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kk) {
+  return umma_smem_desc(tile + uint32_t(kk >> 2) * BOX_BYTES + uint32_t(kk & 3) * 32u, 16u, 1024u);
+}
+// MN-major operand (contraction over the 128 rows; the two 64-column boxes are BOX_BYTES apart): k-step kk = 16 rows
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kk) {
+  return umma_smem_desc(tile + uint32_t(kk) * 2048u, BOX_BYTES, 1024u);
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base, sK = smem_base + 2 * TILE_BYTES, sV = sK + TILE_BYTES, sP = sV + TILE_BYTES;
+  const uint32_t bar_base = smem_base + 6 * TILE_BYTES;
+  const uint32_t q_full = bar_base, k_full = bar_base + 8, k_free = bar_base + 16, v_full = bar_base + 24,
+                 v_free = bar_base + 32;
+  auto s_full = [&](int t) { return bar_base + 40u + 8u * t; };
+  auto p_ready = [&](int t) { return bar_base + 56u + 8u * t; };
+  auto pv_done = [&](int t) { return bar_base + 72u + 8u * t; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + 6 * TILE_BYTES + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + 6 * TILE_BYTES + 104);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;          // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qblk * 2 * BQ;
+  const int kv_blocks = (p.Lk + BK - 1) / BK;
+  int nb[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = q0 + t * BQ;
+    if (r0 >= p.Lq) nb[t] = 0;
+    else if (p.causal) nb[t] = min(kv_blocks, r0 / BK + 1);
+    else nb[t] = kv_blocks;
+  }
+  const int n = max(nb[0], nb[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_free, 1); mbar_init(v_full, 1); mbar_init(v_free, 1);
+    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(pv_done(t), 1); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      bool ok = true;
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      load_tile(sQ, &tmQ, q0, h, b, q_full);
+      load_tile(sQ + TILE_BYTES, &tmQ, q0 + BQ, h, b, q_full);
+      for (int j = 0; j < n && ok; ++j) {
+        const uint32_t par = (uint32_t(j) & 1u) ^ 1u;
+        if (!mbar_wait(k_free, par, abort_flag, p.status, ST_ATTN + 1)) { ok = false; break; }
+        mbar_expect_tx(k_full, TILE_BYTES);
+        load_tile(sK, &tmK, j * BK, h, b, k_full);
+        if (!mbar_wait(v_free, par, abort_flag, p.status, ST_ATTN + 2)) { ok = false; break; }
+        mbar_expect_tx(v_full, TILE_BYTES);
+        load_tile(sV, &tmV, j * BK, h, b, v_full);
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { __nanosleep(1000); }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n > 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);     // S = Q K^T: both operands K-major
+      const uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);     // O += P V: P K-major, V MN-major
+      bool ok = mbar_wait(q_full, 0u, abort_flag, p.status, ST_ATTN + 3) &&
+                mbar_wait(k_full, 0u, abort_flag, p.status, ST_ATTN + 4);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (nb[t] > 0) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK, kk), idesc_s, kk ? 1u : 0u);
+            umma_commit(s_full(t));
+          }
+        }
+        umma_commit(k_free);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        const uint32_t par = uint32_t(j) & 1u;
+        if (!mbar_wait(v_full, par, abort_flag, p.status, ST_ATTN + 5)) { ok = false; break; }
+        const bool more = j + 1 < n;
+        if (more && !mbar_wait(k_full, par ^ 1u, abort_flag, p.status, ST_ATTN + 4)) { ok = false; break; }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < nb[t]) {
+            if (!mbar_wait(p_ready(t), par, abort_flag, p.status, ST_ATTN + 6)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
+                        (j | kk) ? 1u : 0u);
+            umma_commit(pv_done(t));
+            if (j + 1 < nb[t]) {
+#pragma unroll
+              for (int kk = 0; kk < 8; ++kk)
+                umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK, kk), idesc_s, kk ? 1u : 0u);
+              umma_commit(s_full(t));
+            }
+          }
+        }
+        if (!ok) break;
+        umma_commit(v_free);
+        if (more) umma_commit(k_free);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: one thread per query row
+    const int t = (warp - 2) >> 2;
+    const int quarter = warp & 3;                    // TMEM lane quarter this warp may access
+    const int r = quarter * 32 + lane;               // row inside the tile
+    const int row = q0 + t * BQ + r;                 // query position
+    const uint32_t t_s = tmem_base + (uint32_t(quarter * 32) << 16) + t * 128;
+    const uint32_t t_o = tmem_base + (uint32_t(quarter * 32) << 16) + 256 + t * 128;
+    const uint32_t p_tile = sP + t * TILE_BYTES;
+    const float sl2 = p.scale_log2;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb[t] && ok; ++j) {
+      const uint32_t par = uint32_t(j) & 1u;
+      if (!mbar_wait(s_full(t), par, abort_flag, p.status, ST_ATTN + 7)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * BK;
+      const bool edge = (p.causal && k0 + BK - 1 > q0 + t * BQ) || (k0 + BK > p.Lk);
+      const int limit = p.causal ? min(row, p.Lk - 1) : p.Lk - 1;      // last visible key of this row
+      // pass 1: row maximum
+      float bm = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (k0 + c * 32 + i <= limit) bm = fmaxf(bm, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(v[i]));
+        }
+      }
+      // keep the old reference maximum unless the new one exceeds it by more than 2^8 (P stays below 256)
+      float m_new = m;
+      if (bm > m && (m == -INFINITY || (bm - m) * sl2 > 8.f)) m_new = bm;
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = (m == -INFINITY) ? 0.f : ex2((m - m_ref) * sl2);
+      const bool rescale = (j > 0) && (m_new != m);
+      m = m_new;
+      if (j > 0) {
+        if (!mbar_wait(pv_done(t), par ^ 1u, abort_flag, p.status, ST_ATTN + 8)) { ok = false; break; }
+        tc_fence_after();
+      }
+      // pass 2: P = exp2((S - m) * scale), row sum, bf16 into the swizzled P tile
+      const float moff = -m_ref * sl2;
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_wait_ld();
+        float e[32];
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            e[i] = (k0 + c * 32 + i <= limit) ? ex2(fmaf(__uint_as_float(v[i]), sl2, moff)) : 0.f;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) e[i] = ex2(fmaf(__uint_as_float(v[i]), sl2, moff));
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // the row sum uses the rounded values that the tensor core will see
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(e[g * 8 + 2 * i], e[g * 8 + 2 * i + 1]);
+            const float2 back = __bfloat1622float2(pr);
+            rs += back.x + back.y;
+            w[i] = *reinterpret_cast<const uint32_t*>(&pr);
+          }
+          st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
+        }
+      }
+      l = l * alpha + rs;
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(t_o + c * 32, v);
+        }
+        tmem_wait_st();
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(p_ready(t));
+    }
+    if (ok && nb[t] > 0) {
+      const uint32_t par = uint32_t(nb[t] - 1) & 1u;
+      if (mbar_wait(pv_done(t), par, abort_flag, p.status, ST_ATTN + 9)) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)row * p.o_sl + (long long)h * p.o_sh;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_wait_ld();
+          if (row < p.Lq) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+              o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+              o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+              o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+            }
+          }
+        }
+        if (row < p.Lq)
+          p.lse[((long long)b * p.H + h) * p.Lq + row] = (m == -INFINITY ? 0.f : m) * p.scale + __logf(fmaxf(l, 1e-37f));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------ backward
+// One CTA owns a block of 128 keys of one head and walks over the query tiles (64 rows each) that see it.  All five
+// products run with M = 128 on the tensor cores, in the transposed form (keys or head dimension on the TMEM lanes):
+//   S^T  = K Q^T            [keys x q]   A = K  (K-major),   B = Q_i  (K-major)
+//   dP^T = V dO^T           [keys x q]   A = V  (K-major),   B = dO_i (K-major)
+//   dV  += P^T dO           [keys x d]   A = P^T (K-major, from shared memory), B = dO_i (MN-major)
+//   dK  += dS^T Q           [keys x d]   A = dS^T (K-major),                    B = Q_i  (MN-major)
+//   dQ^T = K^T dS^T         [d x q]      A = K (MN-major),   B = dS^T (MN-major)   -> fp32 atomics into dq_acc
+// with P = exp(S * scale - lse) and dS = P (dP - delta) * scale computed by one thread per key row and 32 query columns
+// (two warpgroups split the 64 columns).  TMEM: S^T (2 x 64 columns, the dQ^T of a tile reuses the S^T buffer of that
+// tile), dP^T (2 x 64), dV (128), dK (128).
+constexpr int BQ2 = 64;                          // query rows per backward tile
+constexpr int QTILE_BYTES = BQ2 * HD * 2;        // 16 KB: two boxes of 8 KB
+constexpr int QBOX_BYTES = BQ2 * 128;            // 8 KB
+constexpr int PT_BYTES = 128 * 128;              // P^T / dS^T tile: 128 key rows x 64 q columns bf16 = 16 KB
+constexpr int BWD_THREADS = 320;
+constexpr int BWD_SMEM = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + 256 + 1024;
+
+struct BwdParams {
+  const float* lse;          // [B, H, Lq]
+  const float* delta;        // [B, H, Lq]  rowsum(dO * O) - dlse
+  float* dq_acc;             // [B, Lq, H, 128] fp32, zero on entry
+  __nv_bfloat16* dk;         // [B, Lk, H, 128] contiguous
+  __nv_bfloat16* dv;
+  int B, H, Lq, Lk;
+  int causal;
+  float scale_log2, scale;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void load_qtile(uint32_t dst, const void* tmap, int l0, int h, int b, uint32_t bar) {
+  tma_load_4d(dst, tmap, 0, h, l0, b, bar);
+  tma_load_4d(dst + QBOX_BYTES, tmap, 64, h, l0, b, bar);
+}
+// 64-row tile as K-major operand (contraction over the 128 columns)
+__device__ __forceinline__ uint64_t qdesc_kmajor(uint32_t tile, int kk) {
+  return umma_smem_desc(tile + uint32_t(kk >> 2) * QBOX_BYTES + uint32_t(kk & 3) * 32u, 16u, 1024u);
+}
+// 64-row tile as MN-major operand (contraction over its 64 rows, N = 128 columns in two boxes)
+__device__ __forceinline__ uint64_t qdesc_mnmajor(uint32_t tile, int kk) {
+  return umma_smem_desc(tile + uint32_t(kk) * 2048u, QBOX_BYTES, 1024u);
+}
+// P^T / dS^T tile [128 rows x 64 columns]: K-major (contraction over the 64 columns) and MN-major (over the 128 rows)
+__device__ __forceinline__ uint64_t pdesc_kmajor(uint32_t tile, int kk) { return umma_smem_desc(tile + uint32_t(kk) * 32u, 16u, 1024u); }
+__device__ __forceinline__ uint64_t pdesc_mnmajor(uint32_t tile, int kk) { return umma_smem_desc(tile + uint32_t(kk) * 2048u, 16u, 1024u); }
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sK = smem_base, sV = sK + TILE_BYTES;
+  auto sQ = [&](int s) { return smem_base + 2u * TILE_BYTES + uint32_t(s) * 2u * QTILE_BYTES; };
+  auto sdO = [&](int s) { return sQ(s) + QTILE_BYTES; };
+  auto sP = [&](int s) { return smem_base + 2u * TILE_BYTES + 4u * QTILE_BYTES + uint32_t(s) * 2u * PT_BYTES; };
+  auto sdS = [&](int s) { return sP(s) + PT_BYTES; };
+  constexpr uint32_t BAR_OFF = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES;
+  const uint32_t bar_base = smem_base + BAR_OFF;
+  const uint32_t kv_full = bar_base, dkv_done = bar_base + 8;
+  auto qdo_full = [&](int s) { return bar_base + 16u + 8u * s; };
+  auto qdo_free = [&](int s) { return bar_base + 32u + 8u * s; };
+  auto s_full = [&](int s) { return bar_base + 48u + 8u * s; };
+  auto pds_ready = [&](int s) { return bar_base + 64u + 8u * s; };
+  auto dq_full = [&](int s) { return bar_base + 80u + 8u * s; };
+  auto dq_free = [&](int s) { return bar_base + 96u + 8u * s; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 112);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 120);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k0 = blockIdx.x * BK, h = blockIdx.y, b = blockIdx.z;
+  const int nq = (p.Lq + BQ2 - 1) / BQ2;
+  const int i_start = p.causal ? k0 / BQ2 : 0;          // first query tile that sees a key of this block
+  const int n = nq - i_start;                            // > 0: the grid only covers key blocks below Lk <= ... (host checks)
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(dkv_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(qdo_full(s), 1); mbar_init(qdo_free(s), 1); mbar_init(s_full(s), 1);
+      mbar_init(pds_ready(s), 256); mbar_init(dq_full(s), 1); mbar_init(dq_free(s), 256);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t T_S = 0, T_DP = 128, T_DV = 256, T_DK = 384;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && n > 0) {
+      bool ok = true;
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      load_tile(sK, &tmK, k0, h, b, kv_full);
+      load_tile(sV, &tmV, k0, h, b, kv_full);
+      for (int it = 0; it < n && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(qdo_free(s), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 17)) { ok = false; break; }
+        mbar_expect_tx(qdo_full(s), 2 * QTILE_BYTES);
+        const int i0 = (i_start + it) * BQ2;
+        load_qtile(sQ(s), &tmQ, i0, h, b, qdo_full(s));
+        load_qtile(sdO(s), &tmdO, i0, h, b, qdo_full(s));
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { __nanosleep(1000); }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n > 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_kv = umma_idesc_bf16(128, 128, 0, 1);
+      const uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);
+      auto issue_sdp = [&](int it) -> bool {
+        const int s = it & 1;
+        if (!mbar_wait(qdo_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 18)) return false;
+        // the S^T buffer of this parity last held dQ^T of tile it-2: wait until it has been read out
+        if (it >= 2 && !mbar_wait(dq_free(s), (uint32_t(it - 2) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 19)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + T_S + s * 64, desc_kmajor(sK, kk), qdesc_kmajor(sQ(s), kk), idesc_s, kk ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + T_DP + s * 64, desc_kmajor(sV, kk), qdesc_kmajor(sdO(s), kk), idesc_s, kk ? 1u : 0u);
+        umma_commit(s_full(s));
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0u, abort_flag, p.status, ST_ATTN + 20);
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < n && ok; ++it) {
+        const int s = it & 1;
+        // start the score products of the next tile before waiting for this tile's P and dS
+        if (it + 1 < n && !issue_sdp(it + 1)) { ok = false; break; }
+        if (!mbar_wait(pds_ready(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 21)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem_base + T_DV, pdesc_kmajor(sP(s), kk), qdesc_mnmajor(sdO(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem_base + T_DK, pdesc_kmajor(sdS(s), kk), qdesc_mnmajor(sQ(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
+        umma_commit(qdo_free(s));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + T_S + s * 64, desc_mnmajor(sK, kk), pdesc_mnmajor(sdS(s), kk), idesc_dq, kk ? 1u : 0u);
+        umma_commit(dq_full(s));
+      }
+      if (ok) umma_commit(dkv_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ P / dS, dQ read-out, dK / dV epilogue
+    const int wg = (warp - 2) >> 2;                  // which 32 query columns
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;               // key row of this thread; also head-dimension lane of dQ^T
+    const int key = k0 + r;
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    const float sl2 = p.scale_log2;
+    const long long stat_base = ((long long)b * p.H + h) * p.Lq;
+    bool ok = n > 0;
+    auto read_out_dq = [&](int it) -> bool {
+      const int s = it & 1;
+      if (!mbar_wait(dq_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 22)) return false;
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld_32x32(tmem_base + lane_off + T_S + s * 64 + wg * 32, v);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(dq_free(s));
+      const int qi = (i_start + it) * BQ2 + wg * 32;
+      float* dst = p.dq_acc + (((long long)b * p.Lq + qi) * p.H + h) * HD + r;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (qi + i < p.Lq) atomicAdd(dst + (long long)i * p.H * HD, __uint_as_float(v[i]));
+      return true;
+    };
+    for (int it = 0; it < n && ok; ++it) {
+      const int s = it & 1;
+      const int qi = (i_start + it) * BQ2 + wg * 32;   // first query of this thread's 32 columns
+      float nl[32], dl[32];                            // -lse * log2(e) and delta of the 32 queries
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const bool in = qi + i < p.Lq;
+        nl[i] = in ? -__ldg(p.lse + stat_base + qi + i) * 1.4426950408889634f : 0.f;
+        dl[i] = in ? __ldg(p.delta + stat_base + qi + i) : 0.f;
+      }
+      // dQ^T of the previous tile first: the issuer needs its TMEM buffer back for the scores of tile it+1
+      if (it >= 1 && !read_out_dq(it - 1)) { ok = false; break; }
+      if (!mbar_wait(s_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 23)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[32], dp[32];
+      tmem_ld_32x32(tmem_base + lane_off + T_S + s * 64 + wg * 32, sv);
+      tmem_ld_32x32(tmem_base + lane_off + T_DP + s * 64 + wg * 32, dp);
+      tmem_wait_ld();
+      const bool edge = (p.causal && key > qi) || key >= p.Lk;     // some of the 32 columns may be masked for this row
+      uint32_t pw[16], dw[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float pa = ex2(fmaf(__uint_as_float(sv[2 * i]), sl2, nl[2 * i]));
+        float pb = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), sl2, nl[2 * i + 1]));
+        if (edge) {
+          if (key >= p.Lk || (p.causal && key > qi + 2 * i)) pa = 0.f;
+          if (key >= p.Lk || (p.causal && key > qi + 2 * i + 1)) pb = 0.f;
+        }
+        const float da = pa * (__uint_as_float(dp[2 * i]) - dl[2 * i]) * p.scale;
+        const float db = pb * (__uint_as_float(dp[2 * i + 1]) - dl[2 * i + 1]) * p.scale;
+        pw[i] = pack_bf16(pa, pb);
+        dw[i] = pack_bf16(da, db);
+      }
+      // the P^T / dS^T buffers of this parity were last read by the products of tile it-2, which completed before
+      // dq_full(it-2), and this thread waited for that barrier in read_out_dq(it-2)
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t off = uint32_t(r) * 128u + (uint32_t((wg * 4 + g) ^ (r & 7)) << 4);
+        st_shared_v4(sP(s) + off, pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]);
+        st_shared_v4(sdS(s) + off, dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pds_ready(s));
+    }
+    if (ok && !read_out_dq(n - 1)) ok = false;
+    if (ok && mbar_wait(dkv_done, 0u, abort_flag, p.status, ST_ATTN + 24)) {
+      tc_fence_after();
+      // warpgroup 0 stores dV, warpgroup 1 stores dK: one key row (256 bytes) per thread
+      __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + (((long long)b * p.Lk + key) * p.H + h) * HD;
+      const uint32_t t_src = tmem_base + lane_off + (wg == 0 ? T_DV : T_DK);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_src + c * 32, v);
+        tmem_wait_ld();
+        if (key < p.Lk) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d] - dlse[b, h, i]; one warp per (b, i, h)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ go, const __nv_bfloat16* __restrict__ o,
+                                  const float* __restrict__ glse, float* __restrict__ delta, int B, int H, int L,
+                                  long long g_sb, long long g_sl, long long g_sh, long long o_sb, long long o_sl, long long o_sh) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)B * L * H) return;
+  const int hh = int(w % H);
+  const long long bl = w / H;
+  const int i = int(bl % L), bb = int(bl / L);
+  const uint2 a = *reinterpret_cast<const uint2*>(go + bb * g_sb + i * g_sl + hh * g_sh + lane * 4);
+  const uint2 c = *reinterpret_cast<const uint2*>(o + bb * o_sb + i * o_sl + hh * o_sh + lane * 4);
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 c0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.x));
+  const float2 c1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.y));
+  float sum = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+#pragma unroll
+  for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (lane == 0) {
+    const long long idx = ((long long)bb * H + hh) * L + i;
+    delta[idx] = sum - (glse ? glse[idx] : 0.f);
+  }
+}
+
+// dq[b, i, h, :] (bf16, strided) = dq_acc (fp32, contiguous [B, L, H, 128])
+__global__ void attn_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int H, int L,
+                                    long long sb_, long long sl_, long long sh_) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;     // one thread per 8 values
+  if (idx >= rows * 16) return;
+  const long long row = idx >> 4;
+  const int c = int(idx & 15) * 8;
+  const int hh = int(row % H);
+  const long long bl = row / H;
+  const int i = int(bl % L);
+  const long long bb = bl / L;
+  const float4 x = *reinterpret_cast<const float4*>(acc + row * HD + c);
+  const float4 y = *reinterpret_cast<const float4*>(acc + row * HD + c + 4);
+  uint4 o;
+  o.x = pack_bf16(x.x, x.y); o.y = pack_bf16(x.z, x.w); o.z = pack_bf16(y.x, y.y); o.w = pack_bf16(y.z, y.w);
+  *reinterpret_cast<uint4*>(dq + bb * sb_ + i * sl_ + hh * sh_ + c) = o;
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+static int g_last_encode = 0;
+
+// [B, L, H, 128] bf16 with element strides (sb, sl, sh); box = 64 columns x 1 head x box_rows rows x 1 batch
+static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, long long sb, long long sl, long long sh,
+                     int box_rows = 128) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (sb % 8) || (sl % 8) || (sh % 8)) return -4;
+  cuuint64_t dims[4] = {HD, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)sl * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_encode = (int)r; return -2; }
+  return 0;
+}
+
+}  // namespace attn
+}  // namespace sb
+
+extern "C" int sb_attn_last_encode_result() { return sb::attn::g_last_encode; }
+
+// Attention forward.  q [B, Lq, H, 128], k and v [B, Lk, H, 128], out like q: bf16, last dimension contiguous, the
+// other strides (in elements) multiples of 8.  lse [B, H, Lq] fp32.  causal needs Lq == Lk (row i sees keys 0..i).
+extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int Lq, int Lk,
+                           const long long* q_str, const long long* k_str, const long long* v_str, const long long* o_str,
+                           int causal, float scale, unsigned int* status, cudaStream_t stream) {
+  using namespace sb;
+  using namespace sb::attn;
+  if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0) return 0;
+  if (causal && Lq != Lk) return -3;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (o_str[0] % 8) || (o_str[1] % 8) || (o_str[2] % 8)) return -4;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap(&tq, q, B, Lq, H, q_str[0], q_str[1], q_str[2]))) return rc;
+  if ((rc = make_tmap(&tk, k, B, Lk, H, k_str[0], k_str[1], k_str[2]))) return rc;
+  if ((rc = make_tmap(&tv, v, B, Lk, H, v_str[0], v_str[1], v_str[2]))) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  FwdParams p{reinterpret_cast<__nv_bfloat16*>(out), lse, o_str[0], o_str[1], o_str[2], B, H, Lq, Lk, causal,
+              scale * 1.4426950408889634f, scale, status};
+  dim3 grid((Lq + 2 * BQ - 1) / (2 * BQ), H, B);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}
+
+// Attention backward.  go/q/out [B, Lq, H, 128], k/v [B, Lk, H, 128] (bf16, strided as in the forward); lse and the
+// optional dlse [B, H, Lq] fp32; scratch: delta [B, H, Lq] fp32 and dq_acc [B, Lq, H, 128] fp32 (zero on entry).
+// Results: dq (strided, bf16), dk and dv (contiguous [B, Lk, H, 128], bf16).  Three launches.
+extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                           const float* glse, float* delta, float* dq_acc, void* dq, void* dk, int B, int H, int Lq, int Lk,
+                           void* dv, const long long* g_str, const long long* q_str, const long long* k_str,
+                           const long long* v_str, const long long* o_str, const long long* dq_str, int causal, float scale,
+                           unsigned int* status, cudaStream_t stream) {
+  using namespace sb;
+  using namespace sb::attn;
+  if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0) return 0;
+  if (causal && Lq != Lk) return -3;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
+  if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(go)) & 15) return -4;
+  for (int i = 0; i < 3; ++i) if ((dq_str[i] % 8) || (o_str[i] % 8) || (g_str[i] % 8)) return -4;
+  CUtensorMap tq, tk, tv, tg;
+  int rc;
+  if ((rc = make_tmap(&tq, q, B, Lq, H, q_str[0], q_str[1], q_str[2], BQ2))) return rc;
+  if ((rc = make_tmap(&tg, go, B, Lq, H, g_str[0], g_str[1], g_str[2], BQ2))) return rc;
+  if ((rc = make_tmap(&tk, k, B, Lk, H, k_str[0], k_str[1], k_str[2]))) return rc;
+  if ((rc = make_tmap(&tv, v, B, Lk, H, v_str[0], v_str[1], v_str[2]))) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  const long long rows = (long long)B * Lq * H;
+  attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, glse, delta, B, H, Lq, g_str[0], g_str[1], g_str[2], o_str[0],
+      o_str[1], o_str[2]);
+  BwdParams p{lse, delta, dq_acc, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), B, H, Lq, Lk,
+              causal, scale * 1.4426950408889634f, scale, status};
+  dim3 grid((Lk + BK - 1) / BK, H, B);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
+  attn_dq_cast_kernel<<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, rows, H, Lq,
+                                                                              dq_str[0], dq_str[1], dq_str[2]);
+  return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}

@@ -389,6 +389,43 @@ __global__ void quantize_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restr
   }
 }
 
+// Delayed scaling in one pass over x.  `hist` is a ring of `slots` = history + 2 floats holding the amax of earlier
+// calls at this site: the scale comes from the maximum over the ring except slot `cur` (which collects this call's
+// amax by atomicMax and was zeroed by the previous call) and slot `cur + 1` (zeroed here for the next call).
+// Values beyond the stale range saturate.  A ring without a finite positive entry leaves x unscaled.
+__global__ void quantize_fp8_delayed_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, size_t n8,
+                                            float* __restrict__ hist, int slots, int cur,
+                                            float* __restrict__ scale_inv, int fmt) {
+  const float fmax = fmt == 0 ? 448.f : 57344.f;
+  const int nxt = cur + 1 == slots ? 0 : cur + 1;
+  float a = 0.f;
+  for (int j = 0; j < slots; ++j) {
+    if (j == cur || j == nxt) continue;
+    const float h = hist[j];
+    if (h > a && h < 3.0e38f) a = h;
+  }
+  if (!(a > 0.f)) a = fmax;
+  const float scale = fmax / a;
+  if (blockIdx.x == 0 && threadIdx.x == 0) { scale_inv[0] = a / fmax; hist[nxt] = 0.f; }
+  float m = 0.f;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float f[8]; unpack8(reinterpret_cast<const uint4*>(x)[i], f);
+    uint2 o;
+    unsigned short h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m = fmaxf(m, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
+      const float2 v = make_float2(f[2 * j] * scale, f[2 * j + 1] * scale);
+      h[j] = fmt == 0 ? __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3) : __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E5M2);
+    }
+    o.x = (unsigned)h[0] | ((unsigned)h[1] << 16);
+    o.y = (unsigned)h[2] | ((unsigned)h[3] << 16);
+    reinterpret_cast<uint2*>(q)[i] = o;
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
+}
+
 static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
@@ -511,5 +548,17 @@ extern "C" int sb_quantize_fp8(const void* x, void* q, float* amax, float* scale
   if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return -2;
   amax_kernel<<<grid, 512, 0, st>>>((const bf16*)x, amax, n8);
   quantize_fp8_kernel<<<grid, 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, amax, scale_inv, fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Delayed-scaling variant (one pass): see quantize_fp8_delayed_kernel.  `hist` has `slots` floats, all zero before the
+// first use of a site; the caller advances `cur` by one (mod slots) per call and primes slot 0 with sb_quantize_fp8.
+extern "C" int sb_quantize_fp8_delayed(const void* x, void* q, float* hist, int slots, int cur, float* scale_inv,
+                                       long long n, int fmt, cudaStream_t st) {
+  if ((n % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if (n == 0) return 0;
+  const size_t n8 = (size_t)n / 8;
+  const int grid = grid_for(n8, 512, 148 * 8);
+  quantize_fp8_delayed_kernel<<<grid, 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, hist, slots, cur, scale_inv, fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -39,6 +39,7 @@ struct GemmParams {
   int beta;                    // 1: C += result (bf16 read-modify-write)
   uint32_t* status;
   const float* alpha;          // device scalar multiplied into the accumulator (fp8 de-quantisation), or null
+  const float* alpha2;         // second device scalar (the other operand's de-quantisation factor), or null
   int a_fmt, b_fmt;            // fp8 operand formats for the instruction descriptor: 0 = e4m3, 1 = e5m2
 };
 
@@ -171,7 +172,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase[2] = {0u, 0u};
     int local = 0;
     bool ok = true;
-    const float alpha = p.alpha ? p.alpha[0] : 1.f;
+    const float alpha = (p.alpha ? p.alpha[0] : 1.f) * (p.alpha2 ? p.alpha2[0] : 1.f);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       int mt, nt; tile_coords(tile, m_tiles, n_tiles, mt, nt);
@@ -327,7 +328,7 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   }
   if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
   GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
-               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, nullptr, 0, 0};
+               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, nullptr, nullptr, 0, 0};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
@@ -347,10 +348,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 }
 
 // fp8 GEMM: C[M,N] (bf16) = alpha * A * B^T (+bias) (+residual) (+C) with one-byte operands (e4m3 = 0 / e5m2 = 1) and
-// fp32 accumulation; `alpha` is a device scalar (product of the operands' de-quantisation scales).  Leading dims and
-// contiguous extents must be multiples of 16 elements.
+// fp32 accumulation; `alpha` and `alpha2` are device scalars (the operands' de-quantisation factors; either may be
+// null) whose product scales the accumulator.  Leading dims and contiguous extents must be multiples of 16 elements.
 extern "C" int sb_gemm_fp8(const void* A, const void* B, void* C, const void* bias, const void* residual, const float* alpha,
-                           int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int a_fmt, int b_fmt,
+                           const float* alpha2, int M, int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int a_fmt, int b_fmt,
                            int beta, unsigned int* status, cudaStream_t stream) {
   using namespace sb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -369,7 +370,7 @@ extern "C" int sb_gemm_fp8(const void* A, const void* B, void* C, const void* bi
   if (!g_num_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev); }
   if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
   GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
-               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, alpha, a_fmt, b_fmt};
+               reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, alpha, alpha2, a_fmt, b_fmt};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
   void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);

@@ -52,8 +52,9 @@ class _Sig:
     P, I, F, LL = c_void_p, c_int, c_float, c_ll
     sb_gemm_bf16 = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P]
     sb_colsum = [P, P, I, I, P]
-    sb_gemm_fp8 = [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P]
+    sb_gemm_fp8 = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P]
     sb_quantize_fp8 = [P, P, P, P, LL, I, P]
+    sb_quantize_fp8_delayed = [P, P, P, I, I, P, LL, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd = [P, P, P, P, P, P, I, I, F, I, P]
     sb_glu_fwd = [P, P, LL, I, I, P]
@@ -231,11 +232,59 @@ def quantize_fp8(x2: torch.Tensor, fmt: int):
     return q, sinv
 
 
-def gemm_fp8(a, b, out, alpha, a_mn=False, b_mn=False, a_fmt=E4M3, b_fmt=E4M3, bias=None, residual=None, accumulate=False):
+class Fp8History:
+    """Amax ring of one quantisation site for delayed scaling (the recipe of the reference's TransformerEngine layers:
+    amax_history_len=16, amax_compute_algo="max", savanna/model/tengine.py:19).  The ring has two slots more than the
+    history: the one that collects the running call's amax and the one being cleared for the call after it."""
+
+    __slots__ = ("buf", "cur", "primed")
+
+    def __init__(self, device, history: int):
+        self.buf = torch.zeros(history + 2, dtype=torch.float32, device=device)
+        self.cur = 0
+        self.primed = False
+
+
+FP8_HISTORY = 16         # amax history length of the activation/gradient sites; 0 = current scaling (two passes)
+
+
+def set_fp8_history(n: int) -> None:
+    global FP8_HISTORY
+    FP8_HISTORY = int(n)
+
+
+def quantize_fp8_site(x2: torch.Tensor, fmt: int, owner, role: str):
+    """Quantise at a named site of `owner` (a parameter): delayed scaling from the site's amax history in one pass over
+    the data; the first call at a site has no history and uses current scaling."""
+    if FP8_HISTORY <= 0 or owner is None:
+        return quantize_fp8(x2, fmt)
+    sites = owner.__dict__.setdefault("_fp8_sites", {})
+    h = sites.get(role)
+    if h is None or h.buf.numel() != FP8_HISTORY + 2 or h.buf.device != x2.device:
+        h = sites[role] = Fp8History(x2.device, FP8_HISTORY)
+    lib = require()
+    q = torch.empty(x2.shape, dtype=torch.uint8, device=x2.device)
+    sinv = torch.empty(1, dtype=torch.float32, device=x2.device)
+    if not h.primed:
+        _check(lib.sb_quantize_fp8(x2.data_ptr(), q.data_ptr(), h.buf.data_ptr(), sinv.data_ptr(), x2.numel(), fmt, _stream()),
+               "quantize_fp8")
+        _count(2)
+        h.primed, h.cur = True, 1
+        return q, sinv
+    _check(lib.sb_quantize_fp8_delayed(x2.data_ptr(), q.data_ptr(), h.buf.data_ptr(), h.buf.numel(), h.cur, sinv.data_ptr(),
+                                       x2.numel(), fmt, _stream()), "quantize_fp8_delayed")
+    _count()
+    h.cur = (h.cur + 1) % h.buf.numel()
+    return q, sinv
+
+
+def gemm_fp8(a, b, out, alpha, a_mn=False, b_mn=False, a_fmt=E4M3, b_fmt=E4M3, bias=None, residual=None, accumulate=False,
+             alpha2=None):
     lib = require()
     M, N = out.shape
     K = a.shape[0] if a_mn else a.shape[1]
-    rc = lib.sb_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual), alpha.data_ptr(), M, N, K,
+    rc = lib.sb_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual), alpha.data_ptr(),
+                         _ptr(alpha2), M, N, K,
                          a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
                          int(a_mn), int(b_mn), a_fmt, b_fmt, int(accumulate), status_word(out.device).data_ptr(), _stream())
     if rc != 0:
@@ -255,18 +304,19 @@ def _fp8_weight(w):
 
 class _LinearFP8(torch.autograd.Function):
     """Projection with fp8 tensor-core operands (e4m3 activations and weights, e5m2 output gradients — the HYBRID
-    recipe of the reference's TransformerEngine layers, savanna/model/tengine.py:17-20), per-tensor current scaling,
-    fp32 accumulation, bf16 results.  The quantised activation is reused by the weight-gradient GEMM; quantised
-    weights are cached until the optimizer updates the parameters."""
+    recipe of the reference's TransformerEngine layers, savanna/model/tengine.py:17-20), per-tensor scaling (delayed
+    for activations and gradients, current for the weights), fp32 accumulation, bf16 results.  The quantised
+    activation is reused by the weight-gradient GEMM; quantised weights are cached until the optimizer updates the
+    parameters."""
 
     @staticmethod
     def forward(ctx, x, w, bias, residual):
         x2 = _rows(x)
-        xq, sx = quantize_fp8(x2, E4M3)
+        xq, sx = quantize_fp8_site(x2, E4M3, w, "x")
         wq, sw = _fp8_weight(w)
         out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
         r2 = _rows(residual) if residual is not None else None
-        gemm_fp8(xq, wq, out, sx * sw, bias=bias, residual=r2)
+        gemm_fp8(xq, wq, out, sx, bias=bias, residual=r2, alpha2=sw)
         ctx.save_for_backward(xq, sx, wq, sw)
         ctx.has_bias, ctx.has_res, ctx.xshape, ctx.wref = bias is not None, residual is not None, x.shape, w
         return out.view(*x.shape[:-1], w.shape[0])
@@ -275,20 +325,20 @@ class _LinearFP8(torch.autograd.Function):
     def backward(ctx, gy):
         xq, sx, wq, sw = ctx.saved_tensors
         g2 = _rows(gy)
-        gq, sg = quantize_fp8(g2, E5M2)
+        gq, sg = quantize_fp8_site(g2, E5M2, ctx.wref, "g")
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             gx = torch.empty((g2.shape[0], wq.shape[1]), dtype=bf16, device=gy.device)
-            gemm_fp8(gq, wq, gx, sg * sw, b_mn=True, a_fmt=E5M2, b_fmt=E4M3)
+            gemm_fp8(gq, wq, gx, sg, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sw)
             gx = gx.view(ctx.xshape)
         if ctx.needs_input_grad[1]:
             wp = ctx.wref
             tgt = wp.grad if getattr(wp, "_fuse_grad_accum", False) else None
             if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == wp.shape:
-                gemm_fp8(gq, xq, tgt, sg * sx, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True)
+                gemm_fp8(gq, xq, tgt, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
             else:
                 gw = torch.empty(wp.shape, dtype=bf16, device=gy.device)
-                gemm_fp8(gq, xq, gw, sg * sx, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3)
+                gemm_fp8(gq, xq, gw, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g2).to(gy.dtype)
         gr = gy if (ctx.has_res and ctx.needs_input_grad[3]) else None

@@ -93,6 +93,9 @@ class Trainer:
             gc.disable()
         self.iteration = 0
         self.tokens_seen = 0
+        if self.device.type == "cuda":
+            from ..ops import cuda_ops
+            cuda_ops.set_fp8_history(cfg.fp8_amax_history_len)
         if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.sequence_parallel
                 and state.get_model_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
             from ..parallel import fused_tp

@@ -1,0 +1,90 @@
+"""tcgen05 flash attention (csrc/attn_sm100.cu) against the fp32 PyTorch statement of the op: forward, log-sum-exp and
+all three gradients; causal and full; lengths that are not multiples of the tile sizes; q/k/v as strided slices of one
+fused projection output; a gradient arriving at the log-sum-exp output (the ring-attention merge)."""
+import pytest
+import torch
+
+from savanna_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def _rel(a, b, tol, what):
+    a, b = a.float(), b.float()
+    err = (a - b).norm() / b.norm().clamp_min(1e-12)
+    assert err < tol, f"{what}: relative error {err.item():.3e} (tolerance {tol})"
+
+
+def _status_ok():
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.check_status()
+
+
+def _case(B, Lq, Lk, H, causal, fused_qkv=False, lse_grad=False, seed=0):
+    from savanna_b200.ops import flash_sm100
+    torch.manual_seed(seed)
+    if fused_qkv:
+        assert Lq == Lk
+        qkv = torch.randn(B, Lq, 3, H, 128, device=DEV, dtype=BF, requires_grad=True)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    else:
+        q = torch.randn(B, Lq, H, 128, device=DEV, dtype=BF, requires_grad=True)
+        k = torch.randn(B, Lk, H, 128, device=DEV, dtype=BF, requires_grad=True)
+        v = torch.randn(B, Lk, H, 128, device=DEV, dtype=BF, requires_grad=True)
+    assert flash_sm100.supported(q, k, v, causal)
+    o, lse = flash_sm100.attention(q, k, v, causal, return_lse=True)
+    go = torch.randn_like(o)
+    gl = torch.randn_like(lse) if lse_grad else None
+    loss = (o.float() * go.float()).sum() + ((lse * gl).sum() if lse_grad else 0.0)
+    leaves = (qkv,) if fused_qkv else (q, k, v)
+    grads = torch.autograd.grad(loss, leaves)
+    _status_ok()
+
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf, lser = ref.attention(qr, kr, vr, causal, return_lse=True)
+    lossr = (orf * go.float()).sum() + ((lser * gl).sum() if lse_grad else 0.0)
+    gr = torch.autograd.grad(lossr, (qr, kr, vr))
+    _rel(o, orf, 1e-2, "out")
+    assert (lse - lser).abs().max() < 2e-2, (lse - lser).abs().max()
+    if fused_qkv:
+        got = (grads[0][:, :, 0], grads[0][:, :, 1], grads[0][:, :, 2])
+    else:
+        got = grads
+    for name, a, b in zip(("dq", "dk", "dv"), got, gr):
+        _rel(a, b, 2e-2, name)
+
+
+@pytest.mark.parametrize("L", [256, 1024, 333])
+def test_flash_causal(L):
+    _case(2, L, L, 3, True, seed=L)
+
+
+@pytest.mark.parametrize("Lq,Lk", [(256, 256), (192, 448), (100, 130)])
+def test_flash_full(Lq, Lk):
+    _case(1, Lq, Lk, 2, False, seed=Lq + Lk)
+
+
+def test_flash_fused_qkv_strides():
+    _case(2, 512, 512, 4, True, fused_qkv=True, seed=7)
+
+
+def test_flash_lse_gradient():
+    _case(1, 384, 384, 2, True, lse_grad=True, seed=8)
+    _case(1, 128, 256, 2, False, lse_grad=True, seed=9)
+
+
+def test_flash_long_sequence_statistics():
+    """Scores with a large spread exercise the lazy rescaling of the output accumulator."""
+    from savanna_b200.ops import flash_sm100
+    torch.manual_seed(11)
+    B, L, H = 1, 2048, 2
+    q = (torch.randn(B, L, H, 128, device=DEV) * 3).to(BF)
+    k = (torch.randn(B, L, H, 128, device=DEV) * 3).to(BF)
+    v = torch.randn(B, L, H, 128, device=DEV, dtype=BF)
+    o, lse = flash_sm100.attention(q, k, v, True, return_lse=True)
+    _status_ok()
+    orf, lser = ref.attention(q.float(), k.float(), v.float(), True, return_lse=True)
+    _rel(o, orf, 1.5e-2, "out")
+    assert (lse - lser).abs().max() < 5e-2

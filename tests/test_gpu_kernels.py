@@ -333,7 +333,7 @@ def test_gemm_fp8_layouts(layout):
         a = torch.randn(M, K, device=DEV, dtype=BF); b = torch.randn(N, K, device=DEV, dtype=BF)
         aq, sa = cuda_ops.quantize_fp8(a, 0); bq, sb_ = cuda_ops.quantize_fp8(b, 0)
         out = torch.empty(M, N, device=DEV, dtype=BF)
-        cuda_ops.gemm_fp8(aq, bq, out, sa * sb_)
+        cuda_ops.gemm_fp8(aq, bq, out, sa, alpha2=sb_)
         want = deq(aq, sa, 0) @ deq(bq, sb_, 0).t()
     elif layout == "dgrad":
         a = torch.randn(M, K, device=DEV, dtype=BF); bt = torch.randn(K, N, device=DEV, dtype=BF)
@@ -361,6 +361,32 @@ def test_quantize_fp8_matches_torch():
     want = (x.float() * (448.0 / amax)).to(torch.float8_e4m3fn)
     same = (q.view(torch.float8_e4m3fn).float() == want.float()).float().mean()
     assert same > 0.999, f"only {same.item():.4f} of the fp8 codes agree"
+
+
+def test_quantize_fp8_delayed_scaling():
+    """One-pass quantiser: the scale comes from the amax history (max over the last `history` calls), the running amax
+    lands in the ring, values beyond the stale range saturate, and the ring forgets after `history` calls."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(33)
+    old = cuda_ops.FP8_HISTORY
+    cuda_ops.set_fp8_history(3)
+    try:
+        owner = torch.nn.Parameter(torch.zeros(1, device=DEV))
+        amaxes, f8 = [], torch.float8_e4m3fn
+        for call, gain in enumerate([1.0, 4.0, 0.5, 0.5, 0.5, 0.5]):
+            x = (torch.randn(128, 512, device=DEV) * gain).to(BF)
+            q, sinv = cuda_ops.quantize_fp8_site(x, 0, owner, "x")
+            amaxes.append(float(x.float().abs().max()))
+            used = amaxes[0] if call == 0 else max(amaxes[max(0, call - 3):call])
+            assert abs(float(sinv) * 448.0 - used) < 1e-5 * used, (call, float(sinv) * 448.0, used)
+            want = (x.float() * (448.0 / used)).clamp(-448.0, 448.0).to(f8)
+            same = (q.view(f8).float() == want.float()).float().mean()
+            assert same > 0.999, (call, same.item())
+        hist = owner._fp8_sites["x"].buf
+        assert abs(float(hist.max()) - max(amaxes[-3:])) < 1e-6          # the gain-4 call has left the ring
+        _status_ok()
+    finally:
+        cuda_ops.set_fp8_history(old)
 
 
 def test_linear_fp8_autograd():

@@ -19,14 +19,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fn, errq):
+def _worker(rank, world, port, fn, errq, args=()):
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world),
                        "LOCAL_RANK": str(rank), "NCCL_NVLS_ENABLE": "0"})
     import torch.distributed as dist
     try:
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-        fn(rank, world)
+        fn(rank, world, *args)
         torch.cuda.synchronize()
         dist.barrier()
     except Exception:  # noqa: BLE001
@@ -36,12 +36,16 @@ def _worker(rank, world, port, fn, errq):
             dist.destroy_process_group()
 
 
-def _spawn(fn, world):
+def _spawn_args(fn, world, *args):
+    _spawn(fn, world, args)
+
+
+def _spawn(fn, world, args=()):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fn, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn, errq, args)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -216,3 +220,57 @@ def _w_tp_train(rank, world):
 @needs2
 def test_tensor_sequence_parallel_training_fused():
     _spawn(_w_tp_train, 2)
+
+
+# ------------------------------------------------------------------------------------------ context parallelism
+_CP_OVER = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True, "hidden_dropout": 0.0,
+            "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
+
+
+def _cp_losses(world, over, n=4):
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = {"global_num_gpus": world, "train_micro_batch_size_per_gpu": 1}
+    base.update(over)
+    cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_gpu.yml")], base)
+    tr = Trainer(cfg, load=False)
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(1, cfg.seq_length, seed=i, pin=True)}
+            i += 1
+    d = it()
+    return [float(tr.train_step(d)) for _ in range(n)]
+
+
+def _w_cp_train(rank, world, over, want):
+    from savanna_b200.ops import cuda_ops
+    got = _cp_losses(world, over, len(want))
+    cuda_ops.check_status()
+    for a, b in zip(got, want):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
+
+
+def _cp_reference():
+    from savanna_b200.parallel import state
+    want = _cp_losses(1, {"hidden_dropout": 0.0, "operator_config": ["hyena_se", "hyena_mr", "hyena", "flash_v2"]})
+    state.destroy_model_parallel()
+    return want
+
+
+@needs2
+def test_context_parallel_training_a2a_matches_single_gpu():
+    """cp=2 (zigzag split, all-to-all Hyena, ring attention) reproduces the single-GPU loss trace in bf16."""
+    want = _cp_reference()
+    _spawn_args(_w_cp_train, 2, dict(_CP_OVER), want)
+
+
+@needs2
+def test_context_parallel_training_halo_state_matches_single_gpu():
+    """cp=2 with the halo exchange (Hyena-SE/MR) and the modal-state hand-off (Hyena-LI)."""
+    want = _cp_reference()
+    over = dict(_CP_OVER, cp_hyena_mr_algo="p2p", cp_hyena_li_algo="state")
+    _spawn_args(_w_cp_train, 2, over, want)
