@@ -340,12 +340,11 @@ constexpr int QTILE_BYTES = BQ2 * HD * 2;        // 16 KB: two boxes of 8 KB
 constexpr int QBOX_BYTES = BQ2 * 128;            // 8 KB
 constexpr int PT_BYTES = 128 * 128;              // P^T / dS^T tile: 128 key rows x 64 q columns bf16 = 16 KB
 constexpr int BWD_THREADS = 320;
-constexpr int BWD_SMEM = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + 256 + 1024;
+constexpr int STAGE_BYTES = BQ2 * HD * 4;          // dQ^T staging tile: 64 query rows x 128 fp32
+constexpr int BWD_SMEM = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + STAGE_BYTES + 256 + 1024;
 
 struct BwdParams {
-  const float* lse;          // [B, H, Lq]
-  const float* delta;        // [B, H, Lq]  rowsum(dO * O) - dlse
-  float* dq_acc;             // [B, Lq, H, 128] fp32, zero on entry
+  const float* stats;        // [B, H, Lpad, 2]: (-lse * log2(e), scale * (rowsum(dO * O) - dlse)), Lpad = 64 * ceil(Lq / 64)
   __nv_bfloat16* dk;         // [B, Lk, H, 128] contiguous
   __nv_bfloat16* dv;
   int B, H, Lq, Lk;
@@ -357,6 +356,13 @@ struct BwdParams {
 __device__ __forceinline__ void load_qtile(uint32_t dst, const void* tmap, int l0, int h, int b, uint32_t bar) {
   tma_load_4d(dst, tmap, 0, h, l0, b, bar);
   tma_load_4d(dst + QBOX_BYTES, tmap, 64, h, l0, b, bar);
+}
+// shared -> global reduce-add (fp32) of one box of a 4-D tensor map; completion through the bulk group
+__device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(src)
+      : "memory");
 }
 // 64-row tile as K-major operand (contraction over the 128 columns)
 __device__ __forceinline__ uint64_t qdesc_kmajor(uint32_t tile, int kk) {
@@ -372,7 +378,8 @@ __device__ __forceinline__ uint64_t pdesc_mnmajor(uint32_t tile, int kk) { retur
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmDQ, BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -381,7 +388,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto sdO = [&](int s) { return sQ(s) + QTILE_BYTES; };
   auto sP = [&](int s) { return smem_base + 2u * TILE_BYTES + 4u * QTILE_BYTES + uint32_t(s) * 2u * PT_BYTES; };
   auto sdS = [&](int s) { return sP(s) + PT_BYTES; };
-  constexpr uint32_t BAR_OFF = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES;
+  const uint32_t sStage = smem_base + 2u * TILE_BYTES + 4u * QTILE_BYTES + 4u * PT_BYTES;
+  constexpr uint32_t BAR_OFF = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + STAGE_BYTES;
   const uint32_t bar_base = smem_base + BAR_OFF;
   const uint32_t kv_full = bar_base, dkv_done = bar_base + 8;
   auto qdo_full = [&](int s) { return bar_base + 16u + 8u * s; };
@@ -390,8 +398,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto pds_ready = [&](int s) { return bar_base + 64u + 8u * s; };
   auto dq_full = [&](int s) { return bar_base + 80u + 8u * s; };
   auto dq_free = [&](int s) { return bar_base + 96u + 8u * s; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 112);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 120);
+  const uint32_t stage_ready = bar_base + 112, stage_free = bar_base + 120;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 136);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = blockIdx.x * BK, h = blockIdx.y, b = blockIdx.z;
@@ -405,9 +414,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(qdo_full(s), 1); mbar_init(qdo_free(s), 1); mbar_init(s_full(s), 1);
       mbar_init(pds_ready(s), 256); mbar_init(dq_full(s), 1); mbar_init(dq_free(s), 256);
     }
+    mbar_init(stage_ready, 256); mbar_init(stage_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
-    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO); prefetch_tmap(&tmDQ);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -490,9 +500,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int key = k0 + r;
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
     const float sl2 = p.scale_log2;
-    const long long stat_base = ((long long)b * p.H + h) * p.Lq;
+    const int tid_c = threadIdx.x - 64;              // 0..255 among the compute threads
+    const int lpad = nq * BQ2;
+    const float4* stats = reinterpret_cast<const float4*>(p.stats + (((long long)b * p.H + h) * lpad) * 2);
     bool ok = n > 0;
-    auto read_out_dq = [&](int it) -> bool {
+    // dQ^T of tile `it` leaves through shared memory: every thread holds 32 query rows of one head-dimension column,
+    // writes them into a [64 x 128] fp32 staging tile, and one thread hands the tile to a TMA reduce-add into dq_acc
+    // (rows beyond Lq are clipped by the tensor map).  `cnt` counts the read-outs of this CTA.
+    auto read_out_dq = [&](int it, int cnt) -> bool {
       const int s = it & 1;
       if (!mbar_wait(dq_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 22)) return false;
       tc_fence_after();
@@ -501,45 +516,56 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(dq_free(s));
-      const int qi = (i_start + it) * BQ2 + wg * 32;
-      float* dst = p.dq_acc + (((long long)b * p.Lq + qi) * p.H + h) * HD + r;
+      if (cnt > 0) {
+        if (tid_c == 0) { bulk_wait_read<0>(); mbar_arrive(stage_free); }      // the previous reduce has read the tile
+        if (!mbar_wait(stage_free, uint32_t(cnt - 1) & 1u, abort_flag, p.status, ST_ATTN + 25)) return false;
+      }
+      const uint32_t dst = sStage + uint32_t(wg * 32) * 512u + uint32_t(r) * 4u;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (qi + i < p.Lq) atomicAdd(dst + (long long)i * p.H * HD, __uint_as_float(v[i]));
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst + uint32_t(i) * 512u), "r"(v[i]) : "memory");
+      fence_proxy_async();
+      mbar_arrive(stage_ready);
+      if (tid_c == 0) {
+        if (!mbar_wait(stage_ready, uint32_t(cnt) & 1u, abort_flag, p.status, ST_ATTN + 26)) return false;
+        tma_reduce_add_4d(&tmDQ, sStage, 0, h, (i_start + it) * BQ2, b);
+        bulk_commit();
+      }
       return true;
     };
     for (int it = 0; it < n && ok; ++it) {
       const int s = it & 1;
       const int qi = (i_start + it) * BQ2 + wg * 32;   // first query of this thread's 32 columns
-      float nl[32], dl[32];                            // -lse * log2(e) and delta of the 32 queries
+      // (-lse * log2(e), delta) pairs of the 32 queries: the same addresses in every lane (broadcast loads)
+      float4 st[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const bool in = qi + i < p.Lq;
-        nl[i] = in ? -__ldg(p.lse + stat_base + qi + i) * 1.4426950408889634f : 0.f;
-        dl[i] = in ? __ldg(p.delta + stat_base + qi + i) : 0.f;
-      }
+      for (int i = 0; i < 16; ++i) st[i] = __ldg(stats + (qi >> 1) + i);
       // dQ^T of the previous tile first: the issuer needs its TMEM buffer back for the scores of tile it+1
-      if (it >= 1 && !read_out_dq(it - 1)) { ok = false; break; }
+      if (it >= 1 && !read_out_dq(it - 1, it - 1)) { ok = false; break; }
       if (!mbar_wait(s_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 23)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[32], dp[32];
       tmem_ld_32x32(tmem_base + lane_off + T_S + s * 64 + wg * 32, sv);
       tmem_ld_32x32(tmem_base + lane_off + T_DP + s * 64 + wg * 32, dp);
       tmem_wait_ld();
-      const bool edge = (p.causal && key > qi) || key >= p.Lk;     // some of the 32 columns may be masked for this row
       uint32_t pw[16], dw[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        float pa = ex2(fmaf(__uint_as_float(sv[2 * i]), sl2, nl[2 * i]));
-        float pb = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), sl2, nl[2 * i + 1]));
-        if (edge) {
-          if (key >= p.Lk || (p.causal && key > qi + 2 * i)) pa = 0.f;
-          if (key >= p.Lk || (p.causal && key > qi + 2 * i + 1)) pb = 0.f;
-        }
-        const float da = pa * (__uint_as_float(dp[2 * i]) - dl[2 * i]) * p.scale;
-        const float db = pb * (__uint_as_float(dp[2 * i + 1]) - dl[2 * i + 1]) * p.scale;
+        const float pa = ex2(fmaf(__uint_as_float(sv[2 * i]), sl2, st[i].x));
+        const float pb = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), sl2, st[i].z));
+        const float da = pa * fmaf(__uint_as_float(dp[2 * i]), p.scale, -st[i].y);
+        const float db = pb * fmaf(__uint_as_float(dp[2 * i + 1]), p.scale, -st[i].w);
         pw[i] = pack_bf16(pa, pb);
         dw[i] = pack_bf16(da, db);
+      }
+      if ((p.causal && key > qi) || key >= p.Lk) {
+        // some of this row's 32 columns are masked (only the tiles on the diagonal, and the key rows beyond Lk)
+        const int vis = key >= p.Lk ? 32 : key - qi;      // columns 0..vis-1 are masked
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (2 * i + 1 < vis) { pw[i] = 0u; dw[i] = 0u; }
+          else if (2 * i < vis) { pw[i] &= 0xffff0000u; dw[i] &= 0xffff0000u; }
+        }
       }
       // the P^T / dS^T buffers of this parity were last read by the products of tile it-2, which completed before
       // dq_full(it-2), and this thread waited for that barrier in read_out_dq(it-2)
@@ -553,7 +579,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       mbar_arrive(pds_ready(s));
     }
-    if (ok && !read_out_dq(n - 1)) ok = false;
+    if (ok && !read_out_dq(n - 1, n - 1)) ok = false;
+    if (tid_c == 0) bulk_wait<0>();                     // the last reduce must have left shared memory
     if (ok && mbar_wait(dkv_done, 0u, abort_flag, p.status, ST_ATTN + 24)) {
       tc_fence_after();
       // warpgroup 0 stores dV, warpgroup 1 stores dK: one key row (256 bytes) per thread
@@ -586,16 +613,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d] - dlse[b, h, i]; one warp per (b, i, h)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ go, const __nv_bfloat16* __restrict__ o,
-                                  const float* __restrict__ glse, float* __restrict__ delta, int B, int H, int L,
-                                  long long g_sb, long long g_sl, long long g_sh, long long o_sb, long long o_sl, long long o_sh) {
+// stats[b, h, i] = (-lse * log2(e), scale * (sum_d dO[b, i, h, d] * O[b, i, h, d] - dlse[b, h, i])) for i < L and (0, 0)
+// for the padding rows L <= i < Lpad; one warp per (b, i, h)
+__global__ void attn_stats_kernel(const __nv_bfloat16* __restrict__ go, const __nv_bfloat16* __restrict__ o,
+                                  const float* __restrict__ lse, const float* __restrict__ glse, float* __restrict__ stats,
+                                  int B, int H, int L, int Lpad, float scale, long long g_sb, long long g_sl, long long g_sh,
+                                  long long o_sb, long long o_sl, long long o_sh) {
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * L * H) return;
+  if (w >= (long long)B * Lpad * H) return;
   const int hh = int(w % H);
   const long long bl = w / H;
-  const int i = int(bl % L), bb = int(bl / L);
+  const int i = int(bl % Lpad), bb = int(bl / Lpad);
+  float2* dst = reinterpret_cast<float2*>(stats) + ((long long)bb * H + hh) * Lpad + i;
+  if (i >= L) {
+    if (lane == 0) *dst = make_float2(0.f, 0.f);
+    return;
+  }
   const uint2 a = *reinterpret_cast<const uint2*>(go + bb * g_sb + i * g_sl + hh * g_sh + lane * 4);
   const uint2 c = *reinterpret_cast<const uint2*>(o + bb * o_sb + i * o_sl + hh * o_sh + lane * 4);
   const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
@@ -607,7 +641,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ go, const __
   for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
   if (lane == 0) {
     const long long idx = ((long long)bb * H + hh) * L + i;
-    delta[idx] = sum - (glse ? glse[idx] : 0.f);
+    *dst = make_float2(-lse[idx] * 1.4426950408889634f, scale * (sum - (glse ? glse[idx] : 0.f)));
   }
 }
 
@@ -699,10 +733,10 @@ extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* ou
 }
 
 // Attention backward.  go/q/out [B, Lq, H, 128], k/v [B, Lk, H, 128] (bf16, strided as in the forward); lse and the
-// optional dlse [B, H, Lq] fp32; scratch: delta [B, H, Lq] fp32 and dq_acc [B, Lq, H, 128] fp32 (zero on entry).
-// Results: dq (strided, bf16), dk and dv (contiguous [B, Lk, H, 128], bf16).  Three launches.
+// optional dlse [B, H, Lq] fp32; scratch: stats (2 * B * H * 64 * ceil(Lq / 64) floats) and dq_acc [B, Lq, H, 128] fp32
+// (zero on entry).  Results: dq (strided, bf16), dk and dv (contiguous [B, Lk, H, 128], bf16).  Three launches.
 extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const void* v, const void* out, const float* lse,
-                           const float* glse, float* delta, float* dq_acc, void* dq, void* dk, int B, int H, int Lq, int Lk,
+                           const float* glse, float* stats, float* dq_acc, void* dq, void* dk, int B, int H, int Lq, int Lk,
                            void* dv, const long long* g_str, const long long* q_str, const long long* k_str,
                            const long long* v_str, const long long* o_str, const long long* dq_str, int causal, float scale,
                            unsigned int* status, cudaStream_t stream) {
@@ -713,28 +747,43 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
   if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
-       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(go)) & 15) return -4;
+       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(dq_acc) |
+       reinterpret_cast<uintptr_t>(stats)) & 15) return -4;
   for (int i = 0; i < 3; ++i) if ((dq_str[i] % 8) || (o_str[i] % 8) || (g_str[i] % 8)) return -4;
-  CUtensorMap tq, tk, tv, tg;
+  CUtensorMap tq, tk, tv, tg, tdq;
   int rc;
   if ((rc = make_tmap(&tq, q, B, Lq, H, q_str[0], q_str[1], q_str[2], BQ2))) return rc;
   if ((rc = make_tmap(&tg, go, B, Lq, H, g_str[0], g_str[1], g_str[2], BQ2))) return rc;
   if ((rc = make_tmap(&tk, k, B, Lk, H, k_str[0], k_str[1], k_str[2]))) return rc;
   if ((rc = make_tmap(&tv, v, B, Lk, H, v_str[0], v_str[1], v_str[2]))) return rc;
+  {
+    // dq_acc: fp32 [B, Lq, H, 128] contiguous, box = 128 columns x 1 head x 64 rows, no swizzle (dense staging tile)
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return -1;
+    cuuint64_t dims[4] = {HD, (cuuint64_t)H, (cuuint64_t)Lq, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)HD * 4, (cuuint64_t)H * HD * 4, (cuuint64_t)Lq * H * HD * 4};
+    cuuint32_t box[4] = {HD, 1, BQ2, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { g_last_encode = (int)r; return -2; }
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
     attr_set = true;
   }
-  const long long rows = (long long)B * Lq * H;
-  attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, glse, delta, B, H, Lq, g_str[0], g_str[1], g_str[2], o_str[0],
-      o_str[1], o_str[2]);
-  BwdParams p{lse, delta, dq_acc, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), B, H, Lq, Lk,
+  const int lpad = (Lq + BQ2 - 1) / BQ2 * BQ2;
+  const long long rows = (long long)B * lpad * H;
+  attn_stats_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, lse, glse, stats, B, H, Lq, lpad, scale, g_str[0], g_str[1], g_str[2],
+      o_str[0], o_str[1], o_str[2]);
+  BwdParams p{stats, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), B, H, Lq, Lk,
               causal, scale * 1.4426950408889634f, scale, status};
   dim3 grid((Lk + BK - 1) / BK, H, B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, p);
-  attn_dq_cast_kernel<<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, rows, H, Lq,
-                                                                              dq_str[0], dq_str[1], dq_str[2]);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
+  const long long orows = (long long)B * Lq * H;
+  attn_dq_cast_kernel<<<(unsigned)((orows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, orows, H, Lq,
+                                                                               dq_str[0], dq_str[1], dq_str[2]);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;
 }

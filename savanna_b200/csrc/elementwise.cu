@@ -49,82 +49,151 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ------------------------------------------------------------------------------------ RMSNorm
 // form 0 ("te"):      y = w * x * rsqrt(mean(x^2) + eps);       saved a = rsqrt(mean + eps)
 // form 1 ("classic"): y = w * x / (sqrt(mean(x^2)) + eps);      saved a = 1 / (rms + eps)
-__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
-                                   float* __restrict__ a_out, int D, float eps, int form) {
-  __shared__ float red[32];
-  const size_t row = blockIdx.x;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
-  const uint4* wr = reinterpret_cast<const uint4*>(w);
-  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+// Persistent blocks walk over the rows; a row stays in registers (packed) between the sum of squares and the scaling,
+// and the next row is in flight meanwhile.
+template <int VPT>
+__global__ void __launch_bounds__(512, VPT == 1 ? 4 : 2)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                   float* __restrict__ a_out, int T, int D, float eps, int form) {
+  __shared__ float red[2][32];
   const int nv = D >> 3;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    float f[8]; unpack8(xr[i], f);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  uint4 wv[VPT], xn[VPT];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * blockDim.x;
+    wv[v] = i < nv ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0, 0, 0, 0);
+    xn[v] = make_uint4(0, 0, 0, 0);
   }
-  ss = block_sum(ss, red);
-  const float mean = ss / D;
-  const float a = form == 0 ? rsqrtf(mean + eps) : 1.f / (sqrtf(mean) + eps);
-  if (threadIdx.x == 0) a_out[row] = a;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    float f[8], g[8]; unpack8(xr[i], f); unpack8(wr[i], g);
+  size_t row = blockIdx.x;
+  if (row < (size_t)T) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = f[j] * a * g[j];
-    yr[i] = pack8(f);
+    for (int v = 0; v < VPT; ++v) {
+      const int i = threadIdx.x + v * blockDim.x;
+      if (i < nv) xn[v] = reinterpret_cast<const uint4*>(x + row * D)[i];
+    }
+  }
+  int it = 0;
+  for (; row < (size_t)T; row += gridDim.x, ++it) {
+    uint4 xc[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) xc[v] = xn[v];
+    const size_t nxt = row + gridDim.x;
+    if (nxt < (size_t)T) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        if (i < nv) xn[v] = reinterpret_cast<const uint4*>(x + nxt * D)[i];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float f[8]; unpack8(xc[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+    ss = warp_sum(ss);
+    float* rr = red[it & 1];
+    if (lane == 0) rr[wid] = ss;
+    __syncthreads();
+    float tot = lane < nw ? rr[lane] : 0.f;
+    tot = warp_sum(tot);
+    const float mean = tot / D;
+    const float a = form == 0 ? rsqrtf(mean + eps) : 1.f / (sqrtf(mean) + eps);
+    if (threadIdx.x == 0) a_out[row] = a;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int i = threadIdx.x + v * blockDim.x;
+      if (i < nv) {
+        float f[8], g[8]; unpack8(xc[v], f); unpack8(wv[v], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * a * g[j];
+        reinterpret_cast<uint4*>(y + row * D)[i] = pack8(f);
+      }
+    }
   }
 }
 
 // dx = a * g - x * c * mean(g * x), g = w * dy;  c = a^3 (form 0) or a^2 / rms (form 1)
-// dw[col] += sum_rows dy * x * a   (fp32 atomics, dw zeroed by the caller)
-// Each thread owns VPT fixed column-vectors so its dw partial sums stay in registers over the row loop.
+// partial[block, col] = sum over the block's rows of dy * x * a; rmsnorm_dw_reduce_kernel adds the blocks up.
+// Each thread owns VPT fixed column-vectors (8 columns each) so its weight-gradient sums stay in registers over the
+// row loop; the next row's x and dy are in flight (packed, 8 registers per vector) while this row is reduced and stored.
 template <int VPT>
-__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
-                                   const float* __restrict__ a_in, bf16* __restrict__ dx, float* __restrict__ dw,
-                                   int T, int D, float eps, int form) {
-  __shared__ float red[32];
+__global__ void __launch_bounds__(512, VPT == 1 ? 2 : 1)
+rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
+                   const float* __restrict__ a_in, bf16* __restrict__ dx, float* __restrict__ partial,
+                   int T, int D, float eps, int form) {
+  __shared__ float red[2][32];
   const int nv = D >> 3;
-  float wreg[VPT][8], dwacc[VPT][8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float dwacc[VPT][8];
+  uint4 wv[VPT];
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
     const int i = threadIdx.x + v * blockDim.x;
-    if (i < nv) unpack8(reinterpret_cast<const uint4*>(w)[i], wreg[v]);
+    wv[v] = i < nv ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[v][j] = 0.f;
   }
-  for (size_t row = blockIdx.x; row < (size_t)T; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
-    uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
+  uint4 xn[VPT], gn[VPT];
+  size_t row = blockIdx.x;
+  if (row < (size_t)T) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int i = threadIdx.x + v * blockDim.x;
+      if (i < nv) { xn[v] = reinterpret_cast<const uint4*>(x + row * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + row * D)[i]; }
+    }
+  }
+  int it = 0;
+  for (; row < (size_t)T; row += gridDim.x, ++it) {
+    uint4 xc[VPT], gc[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) { xc[v] = xn[v]; gc[v] = gn[v]; }
+    const size_t nxt = row + gridDim.x;
+    if (nxt < (size_t)T) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        if (i < nv) { xn[v] = reinterpret_cast<const uint4*>(x + nxt * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + nxt * D)[i]; }
+      }
+    }
     const float a = a_in[row];
-    float xf[VPT][8], gf[VPT][8];
     float dot = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < nv) {
-        unpack8(xr[i], xf[v]); unpack8(gr[i], gf[v]);
+        float xf[8], gf[8], wf[8];
+        unpack8(xc[v], xf); unpack8(gc[v], gf); unpack8(wv[v], wf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          dwacc[v][j] += gf[v][j] * xf[v][j] * a;
-          gf[v][j] *= wreg[v][j];
-          dot += gf[v][j] * xf[v][j];
+          const float gx = gf[j] * xf[j];
+          dwacc[v][j] += gx * a;
+          dot += gx * wf[j];
         }
       }
     }
-    dot = block_sum(dot, red);
+    // block sum with one barrier per row (two alternating scratch rows)
+    dot = warp_sum(dot);
+    float* rr = red[it & 1];
+    if (lane == 0) rr[wid] = dot;
+    __syncthreads();
+    float tot = lane < nw ? rr[lane] : 0.f;
+    tot = warp_sum(tot);
     float c;
     if (form == 0) c = a * a * a;
     else { const float rms = 1.f / a - eps; c = a * a / fmaxf(rms, 1e-30f); }
-    const float k = c * dot / D;
+    const float k = c * tot / D;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < nv) {
-        float o[8];
+        float xf[8], gf[8], wf[8], o[8];
+        unpack8(xc[v], xf); unpack8(gc[v], gf); unpack8(wv[v], wf);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = a * gf[v][j] - xf[v][j] * k;
-        dxr[i] = pack8(o);
+        for (int j = 0; j < 8; ++j) o[j] = a * gf[j] * wf[j] - xf[j] * k;
+        reinterpret_cast<uint4*>(dx + row * D)[i] = pack8(o);
       }
     }
   }
@@ -132,10 +201,23 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
   for (int v = 0; v < VPT; ++v) {
     const int i = threadIdx.x + v * blockDim.x;
     if (i < nv) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(dw + i * 8 + j, dwacc[v][j]);
+      float4* dst = reinterpret_cast<float4*>(partial + (size_t)blockIdx.x * D + (size_t)i * 8);
+      dst[0] = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+      dst[1] = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
     }
   }
+}
+// dw[col] += sum_b partial[b, col]: blockIdx.y splits the blocks, one thread per four columns
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nblk, int D) {
+  const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c4 * 4 >= D) return;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int b = blockIdx.y; b < nblk; b += gridDim.y) {
+    const float4 p = *reinterpret_cast<const float4*>(partial + (size_t)b * D + (size_t)c4 * 4);
+    s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+  }
+  atomicAdd(dw + c4 * 4 + 0, s.x); atomicAdd(dw + c4 * 4 + 1, s.y);
+  atomicAdd(dw + c4 * 4 + 2, s.z); atomicAdd(dw + c4 * 4 + 3, s.w);
 }
 
 // ------------------------------------------------------------------------------------ gated MLP activation
@@ -389,13 +471,23 @@ __global__ void quantize_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restr
   }
 }
 
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale, int fmt) {
+  unsigned short h[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = make_float2(f[2 * j] * scale, f[2 * j + 1] * scale);
+    h[j] = fmt == 0 ? __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3) : __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E5M2);
+  }
+  return make_uint2((unsigned)h[0] | ((unsigned)h[1] << 16), (unsigned)h[2] | ((unsigned)h[3] << 16));
+}
 // Delayed scaling in one pass over x.  `hist` is a ring of `slots` = history + 2 floats holding the amax of earlier
 // calls at this site: the scale comes from the maximum over the ring except slot `cur` (which collects this call's
 // amax by atomicMax and was zeroed by the previous call) and slot `cur + 1` (zeroed here for the next call).
 // Values beyond the stale range saturate.  A ring without a finite positive entry leaves x unscaled.
-__global__ void quantize_fp8_delayed_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, size_t n8,
-                                            float* __restrict__ hist, int slots, int cur,
-                                            float* __restrict__ scale_inv, int fmt) {
+// Each thread converts 16 consecutive values per step (two 16-byte loads, one 16-byte store), two steps in flight.
+__global__ void __launch_bounds__(256)
+quantize_fp8_delayed_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, size_t n16, size_t n8,
+                            float* __restrict__ hist, int slots, int cur, float* __restrict__ scale_inv, int fmt) {
   const float fmax = fmt == 0 ? 448.f : 57344.f;
   const int nxt = cur + 1 == slots ? 0 : cur + 1;
   float a = 0.f;
@@ -408,19 +500,54 @@ __global__ void quantize_fp8_delayed_kernel(const bf16* __restrict__ x, uint8_t*
   const float scale = fmax / a;
   if (blockIdx.x == 0 && threadIdx.x == 0) { scale_inv[0] = a / fmax; hist[nxt] = 0.f; }
   float m = 0.f;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
-    float f[8]; unpack8(reinterpret_cast<const uint4*>(x)[i], f);
-    uint2 o;
-    unsigned short h[4];
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  uint4* qv = reinterpret_cast<uint4*>(q);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (; i + stride < n16; i += 2 * stride) {
+    const uint4 a0 = xv[2 * i], a1 = xv[2 * i + 1], b0 = xv[2 * (i + stride)], b1 = xv[2 * (i + stride) + 1];
+    float f[8];
+    uint2 lo, hi;
+    unpack8(a0, f);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      m = fmaxf(m, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
-      const float2 v = make_float2(f[2 * j] * scale, f[2 * j + 1] * scale);
-      h[j] = fmt == 0 ? __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3) : __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E5M2);
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    lo = quant8(f, scale, fmt);
+    unpack8(a1, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    hi = quant8(f, scale, fmt);
+    qv[i] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    unpack8(b0, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    lo = quant8(f, scale, fmt);
+    unpack8(b1, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    hi = quant8(f, scale, fmt);
+    qv[i + stride] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  }
+  for (; i < n16; i += stride) {
+    float f[8];
+    unpack8(xv[2 * i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    const uint2 lo = quant8(f, scale, fmt);
+    unpack8(xv[2 * i + 1], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    const uint2 hi = quant8(f, scale, fmt);
+    qv[i] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+  }
+  // an odd trailing group of 8 values
+  if (n8 & 1) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      float f[8];
+      unpack8(xv[n8 - 1], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+      reinterpret_cast<uint2*>(q)[n8 - 1] = quant8(f, scale, fmt);
     }
-    o.x = (unsigned)h[0] | ((unsigned)h[1] << 16);
-    o.y = (unsigned)h[2] | ((unsigned)h[3] << 16);
-    reinterpret_cast<uint2*>(q)[i] = o;
   }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
@@ -441,26 +568,39 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* w, void* y, float* a_ou
                               cudaStream_t st) {
   if (D % 8) return -1;
   if (T == 0) return 0;
-  int threads = D / 8 >= 256 ? 256 : (D / 8 >= 128 ? 128 : 64);
-  rmsnorm_fwd_kernel<<<T, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, a_out, D, eps, form);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
-}
-
-extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, void* dx, float* dw,
-                              int T, int D, float eps, int form, cudaStream_t st) {
-  if (D % 8) return -1;
-  if (T == 0) return 0;
   const int nv = D / 8;
-  const int threads = 256;
+  const int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
   const int vpt = (nv + threads - 1) / threads;
-  int grid = T < 148 * 4 ? T : 148 * 4;
-#define LAUNCH(V) rmsnorm_bwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, a_in, (bf16*)dx, dw, T, D, eps, form)
+  const int grid = T < 148 * 4 ? T : 148 * 4;
+#define LAUNCH(V) rmsnorm_fwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, a_out, T, D, eps, form)
   if (vpt <= 1) LAUNCH(1);
   else if (vpt <= 2) LAUNCH(2);
   else if (vpt <= 4) LAUNCH(4);
-  else if (vpt <= 8) LAUNCH(8);
   else return -3;
 #undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Blocks of the backward kernel for T rows (also the number of rows of the `partial` scratch).
+extern "C" int sb_rmsnorm_bwd_blocks(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
+
+// dw (fp32 [D]) must be zero on entry; partial is scratch of sb_rmsnorm_bwd_blocks(T) * D floats.  Two launches.
+extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, void* dx, float* dw,
+                              float* partial, int T, int D, float eps, int form, cudaStream_t st) {
+  if (D % 8) return -1;
+  if (T == 0) return 0;
+  const int nv = D / 8;
+  int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
+  const int vpt = (nv + threads - 1) / threads;
+  const int grid = sb_rmsnorm_bwd_blocks(T);
+#define LAUNCH(V) rmsnorm_bwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, a_in, (bf16*)dx, partial, T, D, eps, form)
+  if (vpt <= 1) LAUNCH(1);
+  else if (vpt <= 2) LAUNCH(2);
+  else if (vpt <= 4) LAUNCH(4);
+  else return -3;
+#undef LAUNCH
+  const int ysplit = grid >= 16 ? 16 : 1;
+  rmsnorm_dw_reduce_kernel<<<dim3((D / 4 + 127) / 128, ysplit), 128, 0, st>>>(partial, dw, grid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -557,8 +697,8 @@ extern "C" int sb_quantize_fp8_delayed(const void* x, void* q, float* hist, int 
                                        long long n, int fmt, cudaStream_t st) {
   if ((n % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (n == 0) return 0;
-  const size_t n8 = (size_t)n / 8;
-  const int grid = grid_for(n8, 512, 148 * 8);
-  quantize_fp8_delayed_kernel<<<grid, 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, hist, slots, cur, scale_inv, fmt);
+  const size_t n8 = (size_t)n / 8, n16 = n8 / 2;
+  const int grid = grid_for((n16 + 1) / 2 + 1, 256, 148 * 8);
+  quantize_fp8_delayed_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (uint8_t*)q, n16, n8, hist, slots, cur, scale_inv, fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -56,7 +56,8 @@ class _Sig:
     sb_quantize_fp8 = [P, P, P, P, LL, I, P]
     sb_quantize_fp8_delayed = [P, P, P, I, I, P, LL, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
-    sb_rmsnorm_bwd = [P, P, P, P, P, P, I, I, F, I, P]
+    sb_rmsnorm_bwd = [P, P, P, P, P, P, P, I, I, F, I, P]
+    sb_rmsnorm_bwd_blocks = [I]
     sb_glu_fwd = [P, P, LL, I, I, P]
     sb_glu_bwd = [P, P, P, LL, I, I, P]
     sb_rope = [P, P, P, P, I, I, I, I, I, LL, LL, I, P]
@@ -392,14 +393,15 @@ class _RMSNorm(torch.autograd.Function):
         g2 = gy.reshape(T, D).contiguous()
         dx = torch.empty_like(x2)
         dw = torch.zeros(D, dtype=torch.float32, device=x2.device)
+        partial = torch.empty(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
         _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                                  T, D, eps, form, _stream()), "rmsnorm_bwd")
-        _count()
+                                  partial.data_ptr(), T, D, eps, form, _stream()), "rmsnorm_bwd")
+        _count(2)
         return dx.view(shape), dw.to(w.dtype), None, None
 
 
 def rmsnorm(x, weight, eps, form="te"):
-    if not _is_bf16(x, weight) or x.shape[-1] % 8 or x.shape[-1] > 16384:
+    if not _is_bf16(x, weight) or x.shape[-1] % 8 or x.shape[-1] > 16384 or x.shape[-1] < 64:
         return ref.rmsnorm(x, weight, eps, form)
     return _RMSNorm.apply(x, weight, float(eps), 0 if form == "te" else 1)
 

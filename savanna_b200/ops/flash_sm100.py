@@ -76,14 +76,14 @@ def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None):
     Lk = k.shape[1]
     go = go if _ok_layout(go) else go.contiguous()
     dq_acc = torch.zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
-    delta = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+    stats = torch.empty(2 * B * H * ((Lq + 63) // 64 * 64), dtype=torch.float32, device=q.device)
     dq = torch.empty((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
     dk = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     dv = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     if glse is not None:
         glse = glse.contiguous().float()
     rc = lib.sb_attn_bwd(go.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                         cuda_ops._ptr(glse), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                         cuda_ops._ptr(glse), stats.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
                          B, H, Lq, Lk, dv.data_ptr(), _str3(go), _str3(q), _str3(k), _str3(v), _str3(out),
                          _str3(dq), int(causal), float(scale), cuda_ops.status_word(q.device).data_ptr(),
                          cuda_ops._stream())
