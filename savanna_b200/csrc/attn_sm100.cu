@@ -28,7 +28,7 @@ constexpr int BK = 128;                 // keys per block
 constexpr int TILE_BYTES = 128 * HD * 2;   // 32 KB: two boxes of 16 KB
 constexpr int BOX_BYTES = 128 * 128;       // 16 KB: 128 rows of 128 bytes
 constexpr int FWD_THREADS = 320;
-constexpr int FWD_SMEM = 6 * TILE_BYTES + 256 + 1024;
+constexpr int FWD_SMEM = 7 * TILE_BYTES + 256 + 1024;
 constexpr uint32_t ST_ATTN = 0x20;      // status codes 0x20.. identify attention waits
 
 struct FwdParams {
@@ -85,15 +85,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sQ = smem_base, sK = smem_base + 2 * TILE_BYTES, sV = sK + TILE_BYTES, sP = sV + TILE_BYTES;
-  const uint32_t bar_base = smem_base + 6 * TILE_BYTES;
-  const uint32_t q_full = bar_base, k_full = bar_base + 8, k_free = bar_base + 16, v_full = bar_base + 24,
-                 v_free = bar_base + 32;
-  auto s_full = [&](int t) { return bar_base + 40u + 8u * t; };
-  auto p_ready = [&](int t) { return bar_base + 56u + 8u * t; };
-  auto pv_done = [&](int t) { return bar_base + 72u + 8u * t; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + 6 * TILE_BYTES + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + 6 * TILE_BYTES + 104);
+  const uint32_t sQ = smem_base, sK = smem_base + 2 * TILE_BYTES, sV = sK + 2 * TILE_BYTES, sP = sV + TILE_BYTES;
+  constexpr uint32_t BAR_OFF = 7 * TILE_BYTES;
+  const uint32_t bar_base = smem_base + BAR_OFF;
+  const uint32_t q_full = bar_base, v_full = bar_base + 8, v_free = bar_base + 16;
+  auto k_full = [&](int s) { return bar_base + 24u + 8u * s; };
+  auto k_free = [&](int s) { return bar_base + 40u + 8u * s; };
+  auto s_full = [&](int t) { return bar_base + 56u + 8u * t; };
+  auto s_free = [&](int t) { return bar_base + 72u + 8u * t; };
+  auto p_ready = [&](int t) { return bar_base + 88u + 8u * t; };
+  auto pv_done = [&](int t) { return bar_base + 104u + 8u * t; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 120);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = gridDim.x - 1 - blockIdx.x;          // longest rows first
@@ -111,8 +114,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int n = max(nb[0], nb[1]);
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_free, 1); mbar_init(v_full, 1); mbar_init(v_free, 1);
-    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(pv_done(t), 1); }
+    mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_free, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(k_full(t), 1); mbar_init(k_free(t), 1);
+      mbar_init(s_full(t), 1); mbar_init(s_free(t), 128); mbar_init(p_ready(t), 128); mbar_init(pv_done(t), 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
@@ -134,11 +140,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       load_tile(sQ, &tmQ, q0, h, b, q_full);
       load_tile(sQ + TILE_BYTES, &tmQ, q0 + BQ, h, b, q_full);
       for (int j = 0; j < n && ok; ++j) {
-        const uint32_t par = (uint32_t(j) & 1u) ^ 1u;
-        if (!mbar_wait(k_free, par, abort_flag, p.status, ST_ATTN + 1)) { ok = false; break; }
-        mbar_expect_tx(k_full, TILE_BYTES);
-        load_tile(sK, &tmK, j * BK, h, b, k_full);
-        if (!mbar_wait(v_free, par, abort_flag, p.status, ST_ATTN + 2)) { ok = false; break; }
+        const int ks = j & 1;
+        if (!mbar_wait(k_free(ks), ((uint32_t(j) >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 1)) { ok = false; break; }
+        mbar_expect_tx(k_full(ks), TILE_BYTES);
+        load_tile(sK + ks * TILE_BYTES, &tmK, j * BK, h, b, k_full(ks));
+        if (!mbar_wait(v_free, (uint32_t(j) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 2)) { ok = false; break; }
         mbar_expect_tx(v_full, TILE_BYTES);
         load_tile(sV, &tmV, j * BK, h, b, v_full);
       }
@@ -152,47 +158,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (elect_one() && n > 0) {
       const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);     // S = Q K^T: both operands K-major
       const uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);     // O += P V: P K-major, V MN-major
-      bool ok = mbar_wait(q_full, 0u, abort_flag, p.status, ST_ATTN + 3) &&
-                mbar_wait(k_full, 0u, abort_flag, p.status, ST_ATTN + 4);
-      if (ok) {
-        tc_fence_after();
+      bool ok = mbar_wait(q_full, 0u, abort_flag, p.status, ST_ATTN + 3);
+      // Event loop over both tiles: S_t(js) goes out as soon as K(js) has landed and the softmax warps have read S_t(js-1)
+      // out of TMEM; O_t += P_t(jp) V(jp) as soon as P_t(jp) and V(jp) are there.  Each tile's queue is served in order.
+      int s_idx[2] = {0, 0}, pv_idx[2] = {0, 0};
+      unsigned long long t0 = globaltimer();       // time of the last progress
+      uint32_t spins = 0;
+      while (ok && (s_idx[0] < nb[0] || s_idx[1] < nb[1] || pv_idx[0] < nb[0] || pv_idx[1] < nb[1])) {
+        bool progress = false;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-          if (nb[t] > 0) {
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK, kk), idesc_s, kk ? 1u : 0u);
-            umma_commit(s_full(t));
-          }
-        }
-        umma_commit(k_free);
-      }
-      for (int j = 0; j < n && ok; ++j) {
-        const uint32_t par = uint32_t(j) & 1u;
-        if (!mbar_wait(v_full, par, abort_flag, p.status, ST_ATTN + 5)) { ok = false; break; }
-        const bool more = j + 1 < n;
-        if (more && !mbar_wait(k_full, par ^ 1u, abort_flag, p.status, ST_ATTN + 4)) { ok = false; break; }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j < nb[t]) {
-            if (!mbar_wait(p_ready(t), par, abort_flag, p.status, ST_ATTN + 6)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
-                        (j | kk) ? 1u : 0u);
-            umma_commit(pv_done(t));
-            if (j + 1 < nb[t]) {
+          if (pv_idx[t] < nb[t]) {
+            const int jp = pv_idx[t];
+            if (mbar_test(p_ready(t), uint32_t(jp) & 1u) && mbar_test(v_full, uint32_t(jp) & 1u)) {
+              tc_fence_after();
 #pragma unroll
               for (int kk = 0; kk < 8; ++kk)
-                umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK, kk), idesc_s, kk ? 1u : 0u);
+                umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
+                          (jp | kk) ? 1u : 0u);
+              umma_commit(pv_done(t));
+              pv_idx[t] = jp + 1;
+              if (pv_idx[t ^ 1] > jp || jp >= nb[t ^ 1]) umma_commit(v_free);     // both tiles are through with V(jp)
+              progress = true;
+            }
+          }
+          if (s_idx[t] < nb[t]) {
+            const int js = s_idx[t];
+            if (mbar_test(k_full(js & 1), (uint32_t(js) >> 1) & 1u) &&
+                (js == 0 || mbar_test(s_free(t), uint32_t(js - 1) & 1u))) {
+              tc_fence_after();
+#pragma unroll
+              for (int kk = 0; kk < 8; ++kk)
+                umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK + (js & 1) * TILE_BYTES, kk),
+                          idesc_s, kk ? 1u : 0u);
               umma_commit(s_full(t));
+              s_idx[t] = js + 1;
+              if (s_idx[t ^ 1] > js || js >= nb[t ^ 1]) umma_commit(k_free(js & 1)); // both tiles are through with K(js)
+              progress = true;
             }
           }
         }
-        if (!ok) break;
-        umma_commit(v_free);
-        if (more) umma_commit(k_free);
+        if (progress) {
+          t0 = globaltimer();
+        } else {
+          __nanosleep(32);
+          if ((++spins & 63u) == 0u) {
+            if (*abort_flag) ok = false;
+            else if (globaltimer() - t0 > WAIT_BUDGET_NS) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0u, ((ST_ATTN + 6) << 24) | (blockIdx.x & 0xffffffu));
+              ok = false;
+            }
+          }
+        }
       }
     }
   } else {
@@ -214,20 +232,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int k0 = j * BK;
       const bool edge = (p.causal && k0 + BK - 1 > q0 + t * BQ) || (k0 + BK > p.Lk);
       const int limit = p.causal ? min(row, p.Lk - 1) : p.Lk - 1;      // last visible key of this row
-      // pass 1: row maximum
+      // the whole score row into registers, then hand the TMEM buffer back for the next block's scores
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, v[c]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(s_free(t));
       float bm = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_wait_ld();
-        if (edge) {
+      if (edge) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (k0 + c * 32 + i <= limit) bm = fmaxf(bm, __uint_as_float(v[i]));
-        } else {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(v[i]));
-        }
+          for (int i = 0; i < 32; ++i) {
+            if (k0 + c * 32 + i > limit) v[c][i] = 0xff800000u;      // -inf
+            bm = fmaxf(bm, __uint_as_float(v[c][i]));
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(v[c][i]));
       }
       // keep the old reference maximum unless the new one exceeds it by more than 2^8 (P stays below 256)
       float m_new = m;
@@ -237,36 +262,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool rescale = (j > 0) && (m_new != m);
       m = m_new;
       if (j > 0) {
+        // the previous P V product must have read the P tile (and left O consistent) before either is touched
         if (!mbar_wait(pv_done(t), par ^ 1u, abort_flag, p.status, ST_ATTN + 8)) { ok = false; break; }
         tc_fence_after();
       }
-      // pass 2: P = exp2((S - m) * scale), row sum, bf16 into the swizzled P tile
+      // P = exp2((S - m) * scale) as bf16 into the swizzled P tile; row sum in fp32
       const float moff = -m_ref * sl2;
       float rs = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_wait_ld();
-        float e[32];
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            e[i] = (k0 + c * 32 + i <= limit) ? ex2(fmaf(__uint_as_float(v[i]), sl2, moff)) : 0.f;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) e[i] = ex2(fmaf(__uint_as_float(v[i]), sl2, moff));
-        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint32_t w[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            // the row sum uses the rounded values that the tensor core will see
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(e[g * 8 + 2 * i], e[g * 8 + 2 * i + 1]);
-            const float2 back = __bfloat1622float2(pr);
-            rs += back.x + back.y;
-            w[i] = *reinterpret_cast<const uint32_t*>(&pr);
+            const float ea = ex2(fmaf(__uint_as_float(v[c][g * 8 + 2 * i]), sl2, moff));       // exp2(-inf) = 0 for masked keys
+            const float eb = ex2(fmaf(__uint_as_float(v[c][g * 8 + 2 * i + 1]), sl2, moff));
+            rs += ea + eb;
+            w[i] = pack_bf16(ea, eb);
           }
           st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
         }
@@ -333,8 +346,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //   dK  += dS^T Q           [keys x d]   A = dS^T (K-major),                    B = Q_i  (MN-major)
 //   dQ^T = K^T dS^T         [d x q]      A = K (MN-major),   B = dS^T (MN-major)   -> fp32 atomics into dq_acc
 // with P = exp(S * scale - lse) and dS = P (dP - delta) * scale computed by one thread per key row and 32 query columns
-// (two warpgroups split the 64 columns).  TMEM: S^T (2 x 64 columns, the dQ^T of a tile reuses the S^T buffer of that
-// tile), dP^T (2 x 64), dV (128), dK (128).
+// (two warpgroups split the 64 columns).  TMEM: S^T (2 x 64 columns, so the scores of the next tile are computed during
+// this tile's softmax), dP^T (64), dQ^T (64), dV (128), dK (128).
 constexpr int BQ2 = 64;                          // query rows per backward tile
 constexpr int QTILE_BYTES = BQ2 * HD * 2;        // 16 KB: two boxes of 8 KB
 constexpr int QBOX_BYTES = BQ2 * 128;            // 8 KB
@@ -396,8 +409,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto qdo_free = [&](int s) { return bar_base + 32u + 8u * s; };
   auto s_full = [&](int s) { return bar_base + 48u + 8u * s; };
   auto pds_ready = [&](int s) { return bar_base + 64u + 8u * s; };
-  auto dq_full = [&](int s) { return bar_base + 80u + 8u * s; };
-  auto dq_free = [&](int s) { return bar_base + 96u + 8u * s; };
+  const uint32_t dq_full = bar_base + 80u, dq_free = bar_base + 96u;
   const uint32_t stage_ready = bar_base + 112, stage_free = bar_base + 120;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 136);
@@ -412,8 +424,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(kv_full, 1); mbar_init(dkv_done, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(qdo_full(s), 1); mbar_init(qdo_free(s), 1); mbar_init(s_full(s), 1);
-      mbar_init(pds_ready(s), 256); mbar_init(dq_full(s), 1); mbar_init(dq_free(s), 256);
+      mbar_init(pds_ready(s), 256);
     }
+    mbar_init(dq_full, 1); mbar_init(dq_free, 256);
     mbar_init(stage_ready, 256); mbar_init(stage_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -427,7 +440,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t T_S = 0, T_DP = 128, T_DV = 256, T_DK = 384;
+  constexpr uint32_t T_S = 0, T_DP = 128, T_DQ = 192, T_DV = 256, T_DK = 384;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -455,29 +468,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
       const uint32_t idesc_kv = umma_idesc_bf16(128, 128, 0, 1);
       const uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);
-      auto issue_sdp = [&](int it) -> bool {
+      // S^T(it) needs Q(it) in shared memory and the S^T buffer of its parity, which the softmax warps finished reading
+      // before pds_ready(it-2), a barrier this thread has already passed
+      auto issue_s = [&](int it) -> bool {
         const int s = it & 1;
         if (!mbar_wait(qdo_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 18)) return false;
-        // the S^T buffer of this parity last held dQ^T of tile it-2: wait until it has been read out
-        if (it >= 2 && !mbar_wait(dq_free(s), (uint32_t(it - 2) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 19)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16(tmem_base + T_S + s * 64, desc_kmajor(sK, kk), qdesc_kmajor(sQ(s), kk), idesc_s, kk ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_base + T_DP + s * 64, desc_kmajor(sV, kk), qdesc_kmajor(sdO(s), kk), idesc_s, kk ? 1u : 0u);
-        umma_commit(s_full(s));
         return true;
       };
+      // dP^T(it) goes into the single dP^T buffer: only after the softmax warps have read dP^T(it-1) (pds_ready(it-1))
+      auto issue_dp = [&](int it) {
+        const int s = it & 1;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + T_DP, desc_kmajor(sV, kk), qdesc_kmajor(sdO(s), kk), idesc_s, kk ? 1u : 0u);
+        umma_commit(s_full(s));              // S^T(it) and dP^T(it) are complete
+      };
       bool ok = mbar_wait(kv_full, 0u, abort_flag, p.status, ST_ATTN + 20);
-      if (ok) ok = issue_sdp(0);
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
       for (int it = 0; it < n && ok; ++it) {
         const int s = it & 1;
-        // start the score products of the next tile before waiting for this tile's P and dS
-        if (it + 1 < n && !issue_sdp(it + 1)) { ok = false; break; }
+        // the scores of the next tile run while the softmax warps work on this one
+        if (it + 1 < n && !issue_s(it + 1)) { ok = false; break; }
         if (!mbar_wait(pds_ready(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 21)) { ok = false; break; }
         tc_fence_after();
+        if (it + 1 < n) issue_dp(it + 1);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_bf16(tmem_base + T_DV, pdesc_kmajor(sP(s), kk), qdesc_mnmajor(sdO(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
@@ -485,10 +504,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int kk = 0; kk < 4; ++kk)
           umma_bf16(tmem_base + T_DK, pdesc_kmajor(sdS(s), kk), qdesc_mnmajor(sQ(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
         umma_commit(qdo_free(s));
+        // dQ^T(it) into its own buffer once dQ^T(it-1) has been read out (the softmax warps do that after P/dS of tile it)
+        if (it >= 1 && !mbar_wait(dq_free, uint32_t(it - 1) & 1u, abort_flag, p.status, ST_ATTN + 19)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_base + T_S + s * 64, desc_mnmajor(sK, kk), pdesc_mnmajor(sdS(s), kk), idesc_dq, kk ? 1u : 0u);
-        umma_commit(dq_full(s));
+          umma_bf16(tmem_base + T_DQ, desc_mnmajor(sK, kk), pdesc_mnmajor(sdS(s), kk), idesc_dq, kk ? 1u : 0u);
+        umma_commit(dq_full);
       }
       if (ok) umma_commit(dkv_done);
     }
@@ -508,14 +530,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // writes them into a [64 x 128] fp32 staging tile, and one thread hands the tile to a TMA reduce-add into dq_acc
     // (rows beyond Lq are clipped by the tensor map).  `cnt` counts the read-outs of this CTA.
     auto read_out_dq = [&](int it, int cnt) -> bool {
-      const int s = it & 1;
-      if (!mbar_wait(dq_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 22)) return false;
+      if (!mbar_wait(dq_full, uint32_t(it) & 1u, abort_flag, p.status, ST_ATTN + 22)) return false;
       tc_fence_after();
       uint32_t v[32];
-      tmem_ld_32x32(tmem_base + lane_off + T_S + s * 64 + wg * 32, v);
+      tmem_ld_32x32(tmem_base + lane_off + T_DQ + wg * 32, v);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(dq_free(s));
+      mbar_arrive(dq_free);
       if (cnt > 0) {
         if (tid_c == 0) { bulk_wait_read<0>(); mbar_arrive(stage_free); }      // the previous reduce has read the tile
         if (!mbar_wait(stage_free, uint32_t(cnt - 1) & 1u, abort_flag, p.status, ST_ATTN + 25)) return false;
@@ -540,13 +561,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float4 st[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) st[i] = __ldg(stats + (qi >> 1) + i);
-      // dQ^T of the previous tile first: the issuer needs its TMEM buffer back for the scores of tile it+1
-      if (it >= 1 && !read_out_dq(it - 1, it - 1)) { ok = false; break; }
       if (!mbar_wait(s_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 23)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[32], dp[32];
       tmem_ld_32x32(tmem_base + lane_off + T_S + s * 64 + wg * 32, sv);
-      tmem_ld_32x32(tmem_base + lane_off + T_DP + s * 64 + wg * 32, dp);
+      tmem_ld_32x32(tmem_base + lane_off + T_DP + wg * 32, dp);
       tmem_wait_ld();
       uint32_t pw[16], dw[16];
 #pragma unroll
@@ -568,7 +587,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       // the P^T / dS^T buffers of this parity were last read by the products of tile it-2, which completed before
-      // dq_full(it-2), and this thread waited for that barrier in read_out_dq(it-2)
+      // dq_full of tile it-2, and this thread waited for that barrier in read_out_dq(it-2)
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint32_t off = uint32_t(r) * 128u + (uint32_t((wg * 4 + g) ^ (r & 7)) << 4);
@@ -578,6 +597,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(pds_ready(s));
+      // dQ^T of the previous tile: its product ran while this tile's P and dS were computed
+      if (it >= 1 && !read_out_dq(it - 1, it - 1)) { ok = false; break; }
     }
     if (ok && !read_out_dq(n - 1, n - 1)) ok = false;
     if (tid_c == 0) bulk_wait<0>();                     // the last reduce must have left shared memory
