@@ -204,6 +204,9 @@ def bench_attention(L, iters, heads=32, small=False):
     go = torch.randn_like(o)
     report("attention.fwd.ours", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl, L=L, H=H)
     report("attention.bwd.ours", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
+    flash_sm100.set_backward_variant(False)
+    report("attention.bwd.ours_p_in_smem", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
+    flash_sm100.set_backward_variant(True)
     if small:
         return
 

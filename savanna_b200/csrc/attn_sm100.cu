@@ -201,8 +201,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (progress) {
           t0 = globaltimer();
         } else {
-          __nanosleep(32);
-          if ((++spins & 63u) == 0u) {
+          if ((++spins & 255u) == 0u) {
             if (*abort_flag) ok = false;
             else if (globaltimer() - t0 > WAIT_BUDGET_NS) {
               *abort_flag = 1;
@@ -239,21 +238,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(s_free(t));
-      float bm = -INFINITY;
       if (edge) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 32; ++i)
             if (k0 + c * 32 + i > limit) v[c][i] = 0xff800000u;      // -inf
-            bm = fmaxf(bm, __uint_as_float(v[c][i]));
-          }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(v[c][i]));
       }
+      // four independent chains keep the dependent-issue latency of the row maximum short
+      float bm4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        bm4[c] = __uint_as_float(v[c][0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) bm4[c] = fmaxf(bm4[c], __uint_as_float(v[c][i]));
+      }
+      const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
       // keep the old reference maximum unless the new one exceeds it by more than 2^8 (P stays below 256)
       float m_new = m;
       if (bm > m && (m == -INFINITY || (bm - m) * sl2 > 8.f)) m_new = bm;
@@ -268,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // P = exp2((S - m) * scale) as bf16 into the swizzled P tile; row sum in fp32
       const float moff = -m_ref * sl2;
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -276,14 +276,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           uint32_t w[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float ea = ex2(fmaf(__uint_as_float(v[c][g * 8 + 2 * i]), sl2, moff));       // exp2(-inf) = 0 for masked keys
-            const float eb = ex2(fmaf(__uint_as_float(v[c][g * 8 + 2 * i + 1]), sl2, moff));
-            rs += ea + eb;
+            const float xa = fmaf(__uint_as_float(v[c][g * 8 + 2 * i]), sl2, moff);
+            const float xb = fmaf(__uint_as_float(v[c][g * 8 + 2 * i + 1]), sl2, moff);
+            const float ea = ex2(xa), eb = ex2(xb);        // exp2(-inf) = 0 for masked keys
+            rs4[i] += ea + eb;
             w[i] = pack_bf16(ea, eb);
           }
           st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
         }
       }
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l = l * alpha + rs;
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
@@ -389,6 +391,10 @@ __device__ __forceinline__ uint64_t qdesc_mnmajor(uint32_t tile, int kk) {
 __device__ __forceinline__ uint64_t pdesc_kmajor(uint32_t tile, int kk) { return umma_smem_desc(tile + uint32_t(kk) * 32u, 16u, 1024u); }
 __device__ __forceinline__ uint64_t pdesc_mnmajor(uint32_t tile, int kk) { return umma_smem_desc(tile + uint32_t(kk) * 2048u, 16u, 1024u); }
 
+// P_TMEM: P^T stays in tensor memory (written over the consumed S^T columns, two bf16 per 32-bit cell) and feeds the dV
+// product as the A operand from TMEM; the shared memory this frees holds a third Q/dO stage, which takes the tile loads
+// off the critical path.  Otherwise P^T goes through shared memory like dS^T and there are two Q/dO stages.
+template <bool P_TMEM>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -397,19 +403,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sK = smem_base, sV = sK + TILE_BYTES;
+  constexpr int NST = P_TMEM ? 3 : 2;                  // Q/dO stages
   auto sQ = [&](int s) { return smem_base + 2u * TILE_BYTES + uint32_t(s) * 2u * QTILE_BYTES; };
   auto sdO = [&](int s) { return sQ(s) + QTILE_BYTES; };
-  auto sP = [&](int s) { return smem_base + 2u * TILE_BYTES + 4u * QTILE_BYTES + uint32_t(s) * 2u * PT_BYTES; };
-  auto sdS = [&](int s) { return sP(s) + PT_BYTES; };
-  const uint32_t sStage = smem_base + 2u * TILE_BYTES + 4u * QTILE_BYTES + 4u * PT_BYTES;
-  constexpr uint32_t BAR_OFF = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + STAGE_BYTES;
+  const uint32_t pds_base = smem_base + 2u * TILE_BYTES + uint32_t(NST) * 2u * QTILE_BYTES;
+  auto sdS = [&](int s) { return pds_base + uint32_t(s) * PT_BYTES; };
+  auto sP = [&](int s) { return pds_base + 2u * PT_BYTES + uint32_t(s) * PT_BYTES; };     // only without P_TMEM
+  constexpr uint32_t STAGE_OFF = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES;          // both layouts end here
+  const uint32_t sStage = smem_base + STAGE_OFF;
+  constexpr uint32_t BAR_OFF = STAGE_OFF + STAGE_BYTES;
   const uint32_t bar_base = smem_base + BAR_OFF;
   const uint32_t kv_full = bar_base, dkv_done = bar_base + 8;
   auto qdo_full = [&](int s) { return bar_base + 16u + 8u * s; };
-  auto qdo_free = [&](int s) { return bar_base + 32u + 8u * s; };
-  auto s_full = [&](int s) { return bar_base + 48u + 8u * s; };
-  auto pds_ready = [&](int s) { return bar_base + 64u + 8u * s; };
-  const uint32_t dq_full = bar_base + 80u, dq_free = bar_base + 96u;
+  auto qdo_free = [&](int s) { return bar_base + 40u + 8u * s; };
+  auto s_full = [&](int s) { return bar_base + 64u + 8u * s; };
+  auto pds_ready = [&](int s) { return bar_base + 80u + 8u * s; };
+  const uint32_t dq_full = bar_base + 96u, dq_free = bar_base + 104u;
   const uint32_t stage_ready = bar_base + 112, stage_free = bar_base + 120;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 136);
@@ -422,10 +431,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(dkv_done, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(qdo_full(s), 1); mbar_init(qdo_free(s), 1); mbar_init(s_full(s), 1);
-      mbar_init(pds_ready(s), 256);
-    }
+    for (int s = 0; s < NST; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_free(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(s_full(s), 1); mbar_init(pds_ready(s), 256); }
     mbar_init(dq_full, 1); mbar_init(dq_free, 256);
     mbar_init(stage_ready, 256); mbar_init(stage_free, 1);
     *abort_flag = 0;
@@ -450,8 +457,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       load_tile(sK, &tmK, k0, h, b, kv_full);
       load_tile(sV, &tmV, k0, h, b, kv_full);
       for (int it = 0; it < n && ok; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(qdo_free(s), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 17)) { ok = false; break; }
+        const int s = it % NST;
+        if (!mbar_wait(qdo_free(s), (uint32_t(it / NST) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 17)) { ok = false; break; }
         mbar_expect_tx(qdo_full(s), 2 * QTILE_BYTES);
         const int i0 = (i_start + it) * BQ2;
         load_qtile(sQ(s), &tmQ, i0, h, b, qdo_full(s));
@@ -471,39 +478,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // S^T(it) needs Q(it) in shared memory and the S^T buffer of its parity, which the softmax warps finished reading
       // before pds_ready(it-2), a barrier this thread has already passed
       auto issue_s = [&](int it) -> bool {
-        const int s = it & 1;
-        if (!mbar_wait(qdo_full(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 18)) return false;
+        const int s = it & 1, qs = it % NST;
+        if (!mbar_wait(qdo_full(qs), uint32_t(it / NST) & 1u, abort_flag, p.status, ST_ATTN + 18)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_base + T_S + s * 64, desc_kmajor(sK, kk), qdesc_kmajor(sQ(s), kk), idesc_s, kk ? 1u : 0u);
+          umma_bf16(tmem_base + T_S + s * 64, desc_kmajor(sK, kk), qdesc_kmajor(sQ(qs), kk), idesc_s, kk ? 1u : 0u);
         return true;
       };
       // dP^T(it) goes into the single dP^T buffer: only after the softmax warps have read dP^T(it-1) (pds_ready(it-1))
       auto issue_dp = [&](int it) {
-        const int s = it & 1;
+        const int s = it & 1, qs = it % NST;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem_base + T_DP, desc_kmajor(sV, kk), qdesc_kmajor(sdO(s), kk), idesc_s, kk ? 1u : 0u);
+          umma_bf16(tmem_base + T_DP, desc_kmajor(sV, kk), qdesc_kmajor(sdO(qs), kk), idesc_s, kk ? 1u : 0u);
         umma_commit(s_full(s));              // S^T(it) and dP^T(it) are complete
       };
       bool ok = mbar_wait(kv_full, 0u, abort_flag, p.status, ST_ATTN + 20);
       if (ok) ok = issue_s(0);
       if (ok) issue_dp(0);
       for (int it = 0; it < n && ok; ++it) {
-        const int s = it & 1;
+        const int s = it & 1, qs = it % NST;
         // the scores of the next tile run while the softmax warps work on this one
         if (it + 1 < n && !issue_s(it + 1)) { ok = false; break; }
         if (!mbar_wait(pds_ready(s), (uint32_t(it) >> 1) & 1u, abort_flag, p.status, ST_ATTN + 21)) { ok = false; break; }
         tc_fence_after();
         if (it + 1 < n) issue_dp(it + 1);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + T_DV, pdesc_kmajor(sP(s), kk), qdesc_mnmajor(sdO(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {
+          if (P_TMEM)   // 16 queries = 8 packed columns; each warpgroup wrote its 32 queries over its own S^T columns
+            umma_bf16_ts(tmem_base + T_DV, tmem_base + T_S + s * 64 + (kk >> 1) * 32 + (kk & 1) * 8, qdesc_mnmajor(sdO(qs), kk),
+                         idesc_kv, (it | kk) ? 1u : 0u);
+          else
+            umma_bf16(tmem_base + T_DV, pdesc_kmajor(sP(s), kk), qdesc_mnmajor(sdO(qs), kk), idesc_kv, (it | kk) ? 1u : 0u);
+        }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem_base + T_DK, pdesc_kmajor(sdS(s), kk), qdesc_mnmajor(sQ(s), kk), idesc_kv, (it | kk) ? 1u : 0u);
-        umma_commit(qdo_free(s));
+          umma_bf16(tmem_base + T_DK, pdesc_kmajor(sdS(s), kk), qdesc_mnmajor(sQ(qs), kk), idesc_kv, (it | kk) ? 1u : 0u);
+        umma_commit(qdo_free(qs));
         // dQ^T(it) into its own buffer once dQ^T(it-1) has been read out (the softmax warps do that after P/dS of tile it)
         if (it >= 1 && !mbar_wait(dq_free, uint32_t(it - 1) & 1u, abort_flag, p.status, ST_ATTN + 19)) { ok = false; break; }
         tc_fence_after();
@@ -591,8 +603,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint32_t off = uint32_t(r) * 128u + (uint32_t((wg * 4 + g) ^ (r & 7)) << 4);
-        st_shared_v4(sP(s) + off, pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]);
+        if (!P_TMEM) st_shared_v4(sP(s) + off, pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]);
         st_shared_v4(sdS(s) + off, dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]);
+      }
+      if (P_TMEM) {
+        tmem_st_32x16(tmem_base + lane_off + T_S + s * 64 + wg * 32, pw);
+        tmem_wait_st();
       }
       fence_proxy_async();
       tc_fence_before();
@@ -701,6 +717,7 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 static int g_last_encode = 0;
+static int g_p_tmem = 1;       // backward variant: P^T in tensor memory (1) or in shared memory (0)
 
 // [B, L, H, 128] bf16 with element strides (sb, sl, sh); box = 64 columns x 1 head x box_rows rows x 1 batch
 static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, long long sb, long long sl, long long sh,
@@ -723,6 +740,7 @@ static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, lo
 }  // namespace sb
 
 extern "C" int sb_attn_last_encode_result() { return sb::attn::g_last_encode; }
+extern "C" int sb_attn_set_bwd_variant(int p_in_tmem) { sb::attn::g_p_tmem = p_in_tmem ? 1 : 0; return 0; }
 
 // Attention forward.  q [B, Lq, H, 128], k and v [B, Lk, H, 128], out like q: bf16, last dimension contiguous, the
 // other strides (in elements) multiples of 8.  lse [B, H, Lq] fp32.  causal needs Lq == Lk (row i sees keys 0..i).
@@ -791,7 +809,8 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
+    if (cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
+    if (cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
     attr_set = true;
   }
   const int lpad = (Lq + BQ2 - 1) / BQ2 * BQ2;
@@ -802,7 +821,8 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   BwdParams p{stats, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), B, H, Lq, Lk,
               causal, scale * 1.4426950408889634f, scale, status};
   dim3 grid((Lk + BK - 1) / BK, H, B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
+  if (g_p_tmem) attn_bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
+  else attn_bwd_kernel<false><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
   const long long orows = (long long)B * Lq * H;
   attn_dq_cast_kernel<<<(unsigned)((orows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, orows, H, Lq,
                                                                                dq_str[0], dq_str[1], dq_str[2]);

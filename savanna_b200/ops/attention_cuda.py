@@ -37,11 +37,20 @@ class _SdpaWithLse(torch.autograd.Function):
         return gq.transpose(1, 2), gk.transpose(1, 2), gv.transpose(1, 2), None
 
 
+_OWN = True
+
+
+def set_own_kernels(on: bool) -> None:
+    """Debug switch: False routes every call to the flash kernels shipped with PyTorch (the library baseline)."""
+    global _OWN
+    _OWN = bool(on)
+
+
 def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False, own_kernels=True):
     if q_pos is not None or k_pos is not None or q.dtype != torch.bfloat16:
         return ref.attention(q, k, v, causal, q_pos, k_pos, return_lse)
     from . import flash_sm100
-    if own_kernels and flash_sm100.supported(q, k, v, causal):
+    if _OWN and own_kernels and flash_sm100.supported(q, k, v, causal):
         return flash_sm100.attention(q, k, v, causal, return_lse)
     if return_lse:
         return _SdpaWithLse.apply(q, k, v, causal)

@@ -30,8 +30,16 @@ def _lib():
         lib.sb_attn_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P, P, P, P, P, P, I, F, P, P]
         lib.sb_attn_last_encode_result.restype = I
         lib.sb_attn_last_encode_result.argtypes = []
+        lib.sb_attn_set_bwd_variant.restype = I
+        lib.sb_attn_set_bwd_variant.argtypes = [I]
         _SIGS_SET = True
     return lib
+
+
+def set_backward_variant(p_in_tmem: bool) -> None:
+    """Backward kernel variant: P^T as the tensor-memory operand of the dV product with three Q/dO stages (default),
+    or P^T through shared memory with two stages."""
+    _lib().sb_attn_set_bwd_variant(int(bool(p_in_tmem)))
 
 
 def _ok_layout(t) -> bool:
