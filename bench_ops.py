@@ -85,6 +85,7 @@ def bench_gemm(T, iters):
         out = torch.empty(M, N, device="cuda", dtype=BF)
         gx, gw = torch.empty_like(x), torch.empty_like(w)
         fl = 2.0 * M * N * K
+        cuda_ops.set_gemm_pair_mode(0)
         report(f"gemm.{name}.fwd.ours", timeit(lambda: cuda_ops.gemm(x, w, out), iters), fl, M=M, N=N, K=K)
         report(f"gemm.{name}.fwd.cublas", timeit(lambda: torch.matmul(x, w.t(), out=out), iters), fl)
         report(f"gemm.{name}.dgrad.ours", timeit(lambda: cuda_ops.gemm(gy, w, gx, b_mn=True), iters), fl)
@@ -97,6 +98,13 @@ def bench_gemm(T, iters):
         report(f"gemm.{name}.fwd.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(xq, wq, out, al), iters), fl)
         report(f"gemm.{name}.dgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, wq, gx, al, b_mn=True, a_fmt=1), iters), fl)
         report(f"gemm.{name}.wgrad.ours_fp8", timeit(lambda: cuda_ops.gemm_fp8(gq, xq, gw, al, a_mn=True, b_mn=True, a_fmt=1), iters), fl)
+        cuda_ops.set_gemm_pair_mode(2)
+        report(f"gemm.{name}.fwd.ours_pair", timeit(lambda: cuda_ops.gemm(x, w, out), iters), fl)
+        report(f"gemm.{name}.dgrad.ours_pair", timeit(lambda: cuda_ops.gemm(gy, w, gx, b_mn=True), iters), fl)
+        report(f"gemm.{name}.wgrad.ours_pair", timeit(lambda: cuda_ops.gemm(gy, x, gw, a_mn=True, b_mn=True), iters), fl)
+        report(f"gemm.{name}.fwd.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(xq, wq, out, al), iters), fl)
+        report(f"gemm.{name}.dgrad.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(gq, wq, gx, al, b_mn=True, a_fmt=1), iters), fl)
+        report(f"gemm.{name}.wgrad.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(gq, xq, gw, al, a_mn=True, b_mn=True, a_fmt=1), iters), fl)
         report(f"quantize_fp8.{name}.x.current", timeit(lambda: cuda_ops.quantize_fp8(x, 0), iters), None, M * K * 5)
         site = torch.nn.Parameter(torch.zeros(1, device=x.device))
         report(f"quantize_fp8.{name}.x.delayed", timeit(lambda: cuda_ops.quantize_fp8_site(x, 0, site, "x"), iters), None, M * K * 3)

@@ -53,6 +53,45 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   nt = r / gsz;
 }
 
+// Epilogue of 32 accumulator columns of one row: scale, + bias, + residual, (+ C), bf16, 16-byte stores.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32], float alpha,
+                                            __nv_bfloat16* crow) {
+  if (row < p.M && col0 < p.N) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int col = col0 + v * 8;
+      if (col + 8 <= p.N) {
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * alpha;
+        if (p.bias) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+          const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(b2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+        }
+        if (p.residual) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldr + col);
+          const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(r2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+        }
+        if (p.beta) {
+          const uint4 ov = *reinterpret_cast<const uint4*>(crow + col);
+          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(o2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
+        }
+        uint4 out;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+        *reinterpret_cast<uint4*>(crow + col) = out;
+      }
+    }
+  }
+}
+
 // EB = bytes per operand element: 2 = bf16 (kind::f16), 1 = fp8 e4m3 / e5m2 (kind::f8f6f4).  A shared-memory row is
 // always 128 bytes, so a k-block holds 64 bf16 or 128 fp8 values and every MMA consumes 32 bytes of K.
 template <int A_MN, int B_MN, int EB>
@@ -188,41 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = col0 + v * 8;
-            if (col + 8 <= p.N) {
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * alpha;
-              if (p.bias) {
-                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(b2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
-              }
-              if (p.residual) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldr + col);
-                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(r2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
-              }
-              if (p.beta) {
-                const uint4 ov = *reinterpret_cast<const uint4*>(crow + col);
-                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(o2[j]); f[2 * j] += t.x; f[2 * j + 1] += t.y; }
-              }
-              uint4 out;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-              *reinterpret_cast<uint4*>(crow + col) = out;
-            }
-          }
-        }
+        store_chunk(p, row, n0 + c * 32, r, alpha, crow);
       }
       tc_fence_before();
       __syncwarp();
@@ -234,6 +239,186 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------ CTA-pair kernel (cta_group::2)
+// Two CTAs of a cluster (an SM pair) work on one 256 x 256 output tile.  CTA r of the pair stages rows [128 r, 128 r + 128)
+// of the A tile and rows [128 r, 128 r + 128) of the B tile (32 KB per stage instead of 48 KB: six stages, and a third
+// less shared-memory traffic per FLOP, which is what bounds one-byte operands on a single SM); its TMEM holds the 128
+// accumulator rows of its half.  The even CTA's MMA thread issues tcgen05.mma.cta_group::2 for both; its commits
+// arrive on the stage barriers of both CTAs.  Loads complete on the even CTA's `full` barrier.  No multicast loads.
+constexpr int P_STAGES = 6;
+constexpr int P_A_STAGE = 128 * 128;                 // 16 KB: this CTA's 128 rows of A (128-byte rows)
+constexpr int P_B_STAGE = 128 * 128;                 // 16 KB: this CTA's 128 rows of B
+constexpr int P_STAGE_BYTES = P_A_STAGE + P_B_STAGE;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_GROUP_M = 8;
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_group = P_GROUP_M * n_tiles;
+  const int g = tile / per_group;
+  const int first_m = g * P_GROUP_M;
+  const int gsz = min(P_GROUP_M, m_tiles - first_m);
+  const int r = tile - g * per_group;
+  mt = first_m + r % gsz;
+  nt = r / gsz;
+}
+
+template <int A_MN, int B_MN, int EB>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + P_STAGES * P_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (P_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + P_STAGES * P_STAGE_BYTES + 8 * (2 * P_STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + P_STAGES * P_STAGE_BYTES + 8 * (2 * P_STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();             // 0: issues the MMAs, 1: partner
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  constexpr int BKE = 128 / EB;
+  constexpr int MNB = 128 / EB;
+  constexpr int MN_BOX_BYTES = BKE * 128;
+  const int num_kb = (p.K + BKE - 1) / BKE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }   // 4 warps of each CTA
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // barriers of both CTAs are initialised before either signals the other
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+        int mt, nt; pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        const int m0 = mt * 256 + int(rank) * 128, n0 = nt * BN + int(rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t b_dst = a_dst + P_A_STAGE;
+          const uint32_t bar = map_to_cta(full_bar(stage), 0);         // the even CTA counts both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);
+          const int k0 = kb * BKE;
+          if (A_MN == 0) {
+            tma_load_2d_pair(a_dst, &tmA, k0, m0, bar);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128 / MNB; ++j) tma_load_2d_pair(a_dst + j * MN_BOX_BYTES, &tmA, m0 + MNB * j, k0, bar);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(b_dst, &tmB, k0, n0, bar);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128 / MNB; ++j) tma_load_2d_pair(b_dst + j * MN_BOX_BYTES, &tmB, n0 + MNB * j, k0, bar);
+          }
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { __nanosleep(1000); }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (rank == 0 && elect_one()) {
+      constexpr int UK = 32 / EB;
+      const uint32_t idesc = EB == 2 ? umma_idesc_bf16(256, BN, A_MN, B_MN)
+                                     : umma_idesc_fp8(256, BN, A_MN, B_MN, p.a_fmt, p.b_fmt);
+      constexpr uint32_t a_lbo = A_MN ? (uint32_t)MN_BOX_BYTES : 16u, a_step = A_MN ? (UK * 128u) >> 4 : 2u;
+      constexpr uint32_t b_lbo = B_MN ? (uint32_t)MN_BOX_BYTES : 16u, b_step = B_MN ? (UK * 128u) >> 4 : 2u;
+      int stage = 0; uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0u, 0u};
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        acc_phase[acc] ^= 1u;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * P_STAGE_BYTES;
+          const uint64_t adesc = umma_smem_desc(a_addr, a_lbo, 1024u);
+          const uint64_t bdesc = umma_smem_desc(a_addr + P_A_STAGE, b_lbo, 1024u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (EB == 2) umma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_fp8_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage));          // frees this stage in both CTAs
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(tfull_bar(acc));      // wakes the epilogue warps of both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;
+    uint32_t acc_phase[2] = {0u, 0u};
+    int local = 0;
+    bool ok = true;
+    const float alpha = (p.alpha ? p.alpha[0] : 1.f) * (p.alpha2 ? p.alpha2[0] : 1.f);
+    for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local) {
+      const int acc = local & 1;
+      int mt, nt; pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      acc_phase[acc] ^= 1u;
+      tc_fence_after();
+      const int row = mt * 256 + int(rank) * 128 + q * 32 + lane;
+      const int n0 = nt * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      __nv_bfloat16* crow = p.C + size_t(row) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_wait_ld();
+        store_chunk(p, row, n0 + c * 32, r, alpha, crow);
+      }
+      tc_fence_before();
+      __syncwarp();
+      // the MMA thread of the even CTA waits for the four epilogue warps of both CTAs
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  // neither CTA may free tensor memory or leave while its partner can still signal it or read its shared memory
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -294,9 +479,44 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t inner, uint64_t
 static int g_num_sms = 0;
 static int g_last_detail = 0;   // (which operand << 16) | CUresult of the last failed tensor-map encode
 
+static int g_pair_mode = 2;      // 1: CTA-pair kernel for one-byte operands, 2: for every GEMM, 0: never
+
+// Launch the CTA-pair kernel (cluster of 2) on tensor maps whose boxes are 128 rows (K-major) / 128-byte MN boxes.
+template <int EB>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int a_mn, int b_mn,
+                       cudaStream_t stream) {
+  void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);
+  if (!a_mn && !b_mn) kern = gemm_pair_kernel<0, 0, EB>;
+  else if (!a_mn && b_mn) kern = gemm_pair_kernel<0, 1, EB>;
+  else if (a_mn && b_mn) kern = gemm_pair_kernel<1, 1, EB>;
+  else kern = gemm_pair_kernel<1, 0, EB>;
+  static bool attr_set[4] = {false, false, false, false};
+  const int idx = a_mn * 2 + b_mn;
+  if (!attr_set[idx]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) return -5;
+    attr_set[idx] = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + BN - 1) / BN);
+  int pairs = g_num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? 0 : -6;
+}
+
 }  // namespace sb
 
 extern "C" int sb_gemm_last_error_detail() { return sb::g_last_detail; }
+// 0: single-CTA tiles only; 1: CTA pairs (cta_group::2) for fp8 operands; 2: CTA pairs for bf16 operands too
+extern "C" int sb_gemm_set_pair_mode(int mode) { sb::g_pair_mode = mode; return 0; }
 
 // C = A * B^T (+bias) (+residual) (+C).  a_mn = 0: A is [M, K] row-major with leading dim lda; a_mn = 1: A is stored
 // transposed as [K, M] with leading dim lda.  b_mn likewise for B ([N, K] or [K, N]).  All leading dims and
@@ -329,6 +549,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
   GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
                reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, nullptr, nullptr, 0, 0};
+  if (g_pair_mode >= 2 && max_ctas <= 0) {
+    if (!b_mn && (rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 128))) return rc;     // 128 B rows per CTA of the pair
+    return launch_pair<2>(tmA, tmB, p, a_mn, b_mn, stream);
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < g_num_sms ? tiles : g_num_sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
@@ -371,6 +595,10 @@ extern "C" int sb_gemm_fp8(const void* A, const void* B, void* C, const void* bi
   if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -4;
   GemmParams p{reinterpret_cast<__nv_bfloat16*>(C), reinterpret_cast<const __nv_bfloat16*>(bias),
                reinterpret_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, ldr, beta, status, alpha, alpha2, a_fmt, b_fmt};
+  if (g_pair_mode >= 1) {
+    if (!b_mn && (rc = make_tmap_2d_u8(&tmB, B, K, N, ldb, 128, 128))) return rc;      // 128 B rows per CTA of the pair
+    return launch_pair<1>(tmA, tmB, p, a_mn, b_mn, stream);
+  }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
   void (*kern)(const CUtensorMap, const CUtensorMap, GemmParams);

@@ -52,6 +52,7 @@ class _Sig:
     P, I, F, LL = c_void_p, c_int, c_float, c_ll
     sb_gemm_bf16 = [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P]
     sb_colsum = [P, P, I, I, P]
+    sb_gemm_set_pair_mode = [I]
     sb_gemm_fp8 = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P]
     sb_quantize_fp8 = [P, P, P, P, LL, I, P]
     sb_quantize_fp8_delayed = [P, P, P, I, I, P, LL, I, P]
@@ -150,6 +151,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False
                            f"ptrs {a.data_ptr():#x} {b.data_ptr():#x} {out.data_ptr():#x}")
     _count()
     return out
+
+
+def set_gemm_pair_mode(mode: int) -> None:
+    """0: one CTA per 128 x 256 tile; 1: CTA pairs (cta_group::2, 256 x 256 tiles) for fp8 operands; 2: for bf16 too."""
+    require().sb_gemm_set_pair_mode(int(mode))
 
 
 def colsum(x2: torch.Tensor) -> torch.Tensor:

@@ -36,8 +36,17 @@ def _status_ok():
     cuda_ops.check_status()
 
 
+@pytest.fixture(params=[0, 2], ids=["one_cta", "cta_pair"])
+def pair_mode(request):
+    """Runs a GEMM test with the single-CTA kernel and with the cta_group::2 kernel."""
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.set_gemm_pair_mode(request.param)
+    yield request.param
+    cuda_ops.set_gemm_pair_mode(2)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 136), (1024, 768, 512), (8192, 512, 1024)])
-def test_gemm_tn(M, N, K):
+def test_gemm_tn(M, N, K, pair_mode):
     from savanna_b200.ops import cuda_ops
     torch.manual_seed(0)
     a = torch.randn(M, K, device=DEV, dtype=BF)
@@ -49,7 +58,7 @@ def test_gemm_tn(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 520, 200)])
-def test_gemm_bias_accumulate(M, N, K):
+def test_gemm_bias_accumulate(M, N, K, pair_mode):
     from savanna_b200.ops import cuda_ops
     torch.manual_seed(1)
     a = torch.randn(M, K, device=DEV, dtype=BF)
@@ -63,7 +72,7 @@ def test_gemm_bias_accumulate(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 320), (264, 136, 520)])
-def test_gemm_dgrad_layout(M, N, K):
+def test_gemm_dgrad_layout(M, N, K, pair_mode):
     """B given as its transpose storage [K, N] (weights in dgrad)."""
     from savanna_b200.ops import cuda_ops
     torch.manual_seed(2)
@@ -76,7 +85,7 @@ def test_gemm_dgrad_layout(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 1000), (136, 264, 4096)])
-def test_gemm_wgrad_layout(M, N, K):
+def test_gemm_wgrad_layout(M, N, K, pair_mode):
     """Both operands stored with the reduction dim as the row index."""
     from savanna_b200.ops import cuda_ops
     torch.manual_seed(3)
@@ -319,7 +328,7 @@ def test_linear_residual_epilogue_and_inplace_grad_accumulation():
 
 
 @pytest.mark.parametrize("layout", ["tn", "dgrad", "wgrad"])
-def test_gemm_fp8_layouts(layout):
+def test_gemm_fp8_layouts(layout, pair_mode):
     """fp8 operands, per-tensor scales: compare against the product of the DE-QUANTISED operands (exact fp32 math),
     so only accumulation order and the bf16 output rounding remain."""
     from savanna_b200.ops import cuda_ops
@@ -349,6 +358,56 @@ def test_gemm_fp8_layouts(layout):
         want = deq(aq, sa, 1).t() @ deq(bq, sb_, 0)
     _status_ok()
     _rel(out, want, 1e-2, f"fp8 gemm {layout}")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 768, 640), (384, 264, 200), (1000, 520, 1032), (2048, 1024, 4096)])
+def test_gemm_cta_pair_bf16(M, N, K):
+    """cta_group::2 kernel (two CTAs per 256 x 256 tile): every operand layout, bias / residual / accumulate epilogue."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(40)
+    cuda_ops.set_gemm_pair_mode(2)
+    try:
+        a = torch.randn(M, K, device=DEV, dtype=BF); b = torch.randn(N, K, device=DEV, dtype=BF)
+        at, bt = a.t().contiguous(), b.t().contiguous()
+        want = a.float() @ b.float().t()
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=BF)
+        cuda_ops.gemm(a, b, out)
+        _status_ok(); _rel(out, want, 1e-2, "pair TN")
+        out.fill_(float("nan")); cuda_ops.gemm(a, bt, out, b_mn=True)
+        _status_ok(); _rel(out, want, 1e-2, "pair dgrad layout")
+        out.fill_(float("nan")); cuda_ops.gemm(at, bt, out, a_mn=True, b_mn=True)
+        _status_ok(); _rel(out, want, 1e-2, "pair wgrad layout")
+        out.fill_(float("nan")); cuda_ops.gemm(at, b, out, a_mn=True)
+        _status_ok(); _rel(out, want, 1e-2, "pair A MN-major, B K-major")
+        bias = torch.randn(N, device=DEV, dtype=BF); res = torch.randn(M, N, device=DEV, dtype=BF)
+        c0 = torch.randn(M, N, device=DEV, dtype=BF); out = c0.clone()
+        cuda_ops.gemm(a, b, out, bias=bias, residual=res, accumulate=True)
+        _status_ok(); _rel(out, want + bias.float() + res.float() + c0.float(), 1e-2, "pair epilogue")
+    finally:
+        cuda_ops.set_gemm_pair_mode(2)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 512, 640), (1008, 528, 1040)])
+def test_gemm_cta_pair_fp8(M, N, K):
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(41)
+
+    def deq(q, sinv, fmt):
+        return q.view(torch.float8_e4m3fn if fmt == 0 else torch.float8_e5m2).float() * sinv
+    cuda_ops.set_gemm_pair_mode(1)
+    try:
+        a = torch.randn(M, K, device=DEV, dtype=BF); b = torch.randn(N, K, device=DEV, dtype=BF)
+        aq, sa = cuda_ops.quantize_fp8(a, 1); bq, sb_ = cuda_ops.quantize_fp8(b, 0)
+        atq, sat = cuda_ops.quantize_fp8(a.t().contiguous(), 1); btq, sbt = cuda_ops.quantize_fp8(b.t().contiguous(), 0)
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=BF)
+        cuda_ops.gemm_fp8(aq, bq, out, sa, alpha2=sb_, a_fmt=1, b_fmt=0)
+        _status_ok(); _rel(out, deq(aq, sa, 1) @ deq(bq, sb_, 0).t(), 1e-2, "pair fp8 TN")
+        out.fill_(float("nan")); cuda_ops.gemm_fp8(aq, btq, out, sa, alpha2=sbt, b_mn=True, a_fmt=1, b_fmt=0)
+        _status_ok(); _rel(out, deq(aq, sa, 1) @ deq(btq, sbt, 0), 1e-2, "pair fp8 dgrad layout")
+        out.fill_(float("nan")); cuda_ops.gemm_fp8(atq, btq, out, sat, alpha2=sbt, a_mn=True, b_mn=True, a_fmt=1, b_fmt=0)
+        _status_ok(); _rel(out, deq(atq, sat, 1).t() @ deq(btq, sbt, 0), 1e-2, "pair fp8 wgrad layout")
+    finally:
+        cuda_ops.set_gemm_pair_mode(2)
 
 
 def test_quantize_fp8_matches_torch():
