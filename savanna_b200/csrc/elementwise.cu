@@ -207,17 +207,30 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     }
   }
 }
-// dw[col] += sum_b partial[b, col]: blockIdx.y splits the blocks, one thread per four columns
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nblk, int D) {
-  const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c4 * 4 >= D) return;
+// dw[col] = sum_b partial[b, col] as bf16: a block covers 32 groups of four columns, its 8 thread rows split the partial
+// rows and are combined through shared memory (no atomics, no zero-initialised output)
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dw, int nblk, int D) {
+  __shared__ float4 part[8][32];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c4 = blockIdx.x * 32 + cx;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int b = blockIdx.y; b < nblk; b += gridDim.y) {
-    const float4 p = *reinterpret_cast<const float4*>(partial + (size_t)b * D + (size_t)c4 * 4);
-    s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+  if (c4 * 4 < D) {
+    for (int b = ry; b < nblk; b += 8) {
+      const float4 p = *reinterpret_cast<const float4*>(partial + (size_t)b * D + (size_t)c4 * 4);
+      s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+    }
   }
-  atomicAdd(dw + c4 * 4 + 0, s.x); atomicAdd(dw + c4 * 4 + 1, s.y);
-  atomicAdd(dw + c4 * 4 + 2, s.z); atomicAdd(dw + c4 * 4 + 3, s.w);
+  part[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c4 * 4 < D) {
+#pragma unroll
+    for (int j = 1; j < 8; ++j) { const float4 p = part[j][cx]; s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w; }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dw + (size_t)c4 * 4) = o;
+  }
 }
 
 // ------------------------------------------------------------------------------------ gated MLP activation
@@ -584,8 +597,8 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* w, void* y, float* a_ou
 // Blocks of the backward kernel for T rows (also the number of rows of the `partial` scratch).
 extern "C" int sb_rmsnorm_bwd_blocks(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
 
-// dw (fp32 [D]) must be zero on entry; partial is scratch of sb_rmsnorm_bwd_blocks(T) * D floats.  Two launches.
-extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, void* dx, float* dw,
+// dw: bf16 [D], written (not accumulated); partial is scratch of sb_rmsnorm_bwd_blocks(T) * D floats.  Two launches.
+extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, void* dx, void* dw,
                               float* partial, int T, int D, float eps, int form, cudaStream_t st) {
   if (D % 8) return -1;
   if (T == 0) return 0;
@@ -599,8 +612,7 @@ extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
   else if (vpt <= 4) LAUNCH(4);
   else return -3;
 #undef LAUNCH
-  const int ysplit = grid >= 16 ? 16 : 1;
-  rmsnorm_dw_reduce_kernel<<<dim3((D / 4 + 127) / 128, ysplit), 128, 0, st>>>(partial, dw, grid, D);
+  rmsnorm_dw_reduce_kernel<<<(D / 4 + 31) / 32, 256, 0, st>>>(partial, (bf16*)dw, grid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -398,12 +398,12 @@ class _RMSNorm(torch.autograd.Function):
         T, D = x2.shape
         g2 = gy.reshape(T, D).contiguous()
         dx = torch.empty_like(x2)
-        dw = torch.zeros(D, dtype=torch.float32, device=x2.device)
+        dw = torch.empty(D, dtype=bf16, device=x2.device)
         partial = torch.empty(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
         _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), dx.data_ptr(), dw.data_ptr(),
                                   partial.data_ptr(), T, D, eps, form, _stream()), "rmsnorm_bwd")
         _count(2)
-        return dx.view(shape), dw.to(w.dtype), None, None
+        return dx.view(shape), dw, None, None
 
 
 def rmsnorm(x, weight, eps, form="te"):
