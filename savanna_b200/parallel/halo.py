@@ -72,6 +72,92 @@ class _ZigzagHalo(torch.autograd.Function):
         return gx, None
 
 
+# ------------------------------------------------------------------------------------------ peer-memory form
+_PEER_WS = None
+
+
+def setup_peer(group=None, ranks=None) -> bool:
+    """Collective over the context-parallel group: symmetric staging buffers and the device barrier for the
+    peer-memory halo exchange (csrc/halo_peer.cu).  Returns False (on every rank) if it cannot be brought up."""
+    global _PEER_WS
+    import ctypes
+    from . import fused_tp
+    group = group if group is not None else state.get_context_parallel_group()
+    ranks = ranks or state.get_context_parallel_ranks()
+    ok, ws = 1, None
+    try:
+        ws = fused_tp.TPWorkspace(group, ranks)
+        P, I = ctypes.c_void_p, ctypes.c_int
+        ws.lib.sb_halo_pull.restype = I
+        ws.lib.sb_halo_pull.argtypes = [P, P, P, P, I, I, I, P]
+        ws.lib.sb_halo_push_add.restype = I
+        ws.lib.sb_halo_push_add.argtypes = [P, P, P, P, I, I, I, I, P]
+    except Exception as exc:  # noqa: BLE001
+        print(f"[rank {dist.get_rank()}] peer-memory halo set-up failed: {exc}", flush=True)
+        ok = 0
+    flag = torch.tensor([ok], dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    _PEER_WS = ws if int(flag.item()) == 1 else None
+    return _PEER_WS is not None
+
+
+def teardown_peer() -> None:
+    global _PEER_WS
+    _PEER_WS = None
+
+
+def _peer_ptr(ptrs, idx, cp):
+    return ptrs[idx] if 0 <= idx < cp else None
+
+
+class _ZigzagHaloPeer(torch.autograd.Function):
+    """Same contract as _ZigzagHalo, with the neighbours' tails read from their symmetric buffers by this framework's
+    own kernels: stage the two tails -> device barrier -> pull; backward: stage the halo gradients -> device barrier ->
+    add the neighbours' parts onto the tail rows.  Staging buffers alternate between two slots, so one barrier per
+    exchange suffices (a slot is rewritten only after the barrier of the following exchange)."""
+
+    @staticmethod
+    def forward(ctx, x, H):
+        ws = _PEER_WS
+        B, L, C = x.shape
+        half = L // 2
+        if H > half:
+            raise ValueError(f"halo {H} exceeds the chunk length {half}")
+        me, cp = ws.rank, ws.world
+        stage, ptrs = ws.symm_buffer("halo_fwd", B * 2 * H * C)
+        sv = stage.view(B, 2, H, C)
+        sv[:, 0].copy_(x[:, half - H:half])
+        sv[:, 1].copy_(x[:, L - H:])
+        ws.barrier()
+        halo = torch.empty((B, 2, H, C), dtype=x.dtype, device=x.device)
+        rc = ws.lib.sb_halo_pull(halo.data_ptr(), _peer_ptr(ptrs, me - 1, cp), _peer_ptr(ptrs, me + 1, cp), stage.data_ptr(),
+                                 B, H, C, torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"sb_halo_pull failed ({rc})")
+        ws.cuda_ops._count()
+        ctx.meta = (H, L, C, B)
+        return halo
+
+    @staticmethod
+    def backward(ctx, g):
+        ws = _PEER_WS
+        H, L, C, B = ctx.meta
+        me, cp = ws.rank, ws.world
+        stage, ptrs = ws.symm_buffer("halo_bwd", B * 2 * H * C)
+        stage.view(B, 2, H, C).copy_(g)
+        ws.barrier()
+        gx = torch.zeros((B, L, C), dtype=g.dtype, device=g.device)
+        rc = ws.lib.sb_halo_push_add(gx.data_ptr(), _peer_ptr(ptrs, me - 1, cp), _peer_ptr(ptrs, me + 1, cp), stage.data_ptr(),
+                                     B, L, C, H, torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"sb_halo_push_add failed ({rc})")
+        ws.cuda_ops._count()
+        return gx, None
+
+
 def zigzag_halo(x: torch.Tensor, H: int) -> torch.Tensor:
     """Halo rows for both chunks of a zigzag shard: [B, 2, H, C]."""
+    if (_PEER_WS is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+            and x.shape[1] % 2 == 0):
+        return _ZigzagHaloPeer.apply(x, H)
     return _ZigzagHalo.apply(x, H)

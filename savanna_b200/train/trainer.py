@@ -102,6 +102,11 @@ class Trainer:
             on = fused_tp.setup()
             print_rank_0(" > tensor-parallel projections: " + ("fused all-gather->GEMM / GEMM->reduce-scatter kernels"
                                                                if on else "NCCL collectives + GEMM"))
+        if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.use_cp_hyena
+                and state.get_context_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
+            from ..parallel import halo as halo_mod
+            on = halo_mod.setup_peer()
+            print_rank_0(" > context-parallel halos: " + ("peer-memory pull kernels" if on else "NCCL send/recv"))
         self.model, self.optimizer, self.lr_scheduler = self._setup_model_and_optimizer()
         self.gas = cfg.gradient_accumulation_steps
         self.micro_batch = cfg.train_micro_batch_size_per_gpu

@@ -248,7 +248,9 @@ def _cp_losses(world, over, n=4):
 
 def _w_cp_train(rank, world, over, want):
     from savanna_b200.ops import cuda_ops
+    from savanna_b200.parallel import halo
     got = _cp_losses(world, over, len(want))
+    assert halo._PEER_WS is not None, "the peer-memory halo exchange was not brought up"
     cuda_ops.check_status()
     for a, b in zip(got, want):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
