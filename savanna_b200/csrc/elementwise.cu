@@ -115,14 +115,16 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
 }
 
-// dx = a * g - x * c * mean(g * x), g = w * dy;  c = a^3 (form 0) or a^2 / rms (form 1)
+// dx = a * g - x * c * mean(g * x) (+ gres), g = w * dy;  c = a^3 (form 0) or a^2 / rms (form 1); gres is the gradient
+// that reached x along the residual branch, added here instead of by a separate kernel
 // partial[block, col] = sum over the block's rows of dy * x * a; rmsnorm_dw_reduce_kernel adds the blocks up.
 // Each thread owns VPT fixed column-vectors (8 columns each) so its weight-gradient sums stay in registers over the
 // row loop; the next row's x and dy are in flight (packed, 8 registers per vector) while this row is reduced and stored.
 template <int VPT>
 __global__ void __launch_bounds__(512, VPT == 1 ? 2 : 1)
 rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
-                   const float* __restrict__ a_in, bf16* __restrict__ dx, float* __restrict__ partial,
+                   const float* __restrict__ a_in, const bf16* __restrict__ gres, bf16* __restrict__ dx,
+                   float* __restrict__ partial,
                    int T, int D, float eps, int form) {
   __shared__ float red[2][32];
   const int nv = D >> 3;
@@ -136,26 +138,32 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[v][j] = 0.f;
   }
-  uint4 xn[VPT], gn[VPT];
+  uint4 xn[VPT], gn[VPT], rn[VPT];                      // next row: x, dy and (optional) the gradient to add
   size_t row = blockIdx.x;
   if (row < (size_t)T) {
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
-      if (i < nv) { xn[v] = reinterpret_cast<const uint4*>(x + row * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + row * D)[i]; }
+      if (i < nv) {
+        xn[v] = reinterpret_cast<const uint4*>(x + row * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + row * D)[i];
+        if (gres) rn[v] = reinterpret_cast<const uint4*>(gres + row * D)[i];
+      }
     }
   }
   int it = 0;
   for (; row < (size_t)T; row += gridDim.x, ++it) {
-    uint4 xc[VPT], gc[VPT];
+    uint4 xc[VPT], gc[VPT], rc[VPT];
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) { xc[v] = xn[v]; gc[v] = gn[v]; }
+    for (int v = 0; v < VPT; ++v) { xc[v] = xn[v]; gc[v] = gn[v]; rc[v] = rn[v]; }
     const size_t nxt = row + gridDim.x;
     if (nxt < (size_t)T) {
 #pragma unroll
       for (int v = 0; v < VPT; ++v) {
         const int i = threadIdx.x + v * blockDim.x;
-        if (i < nv) { xn[v] = reinterpret_cast<const uint4*>(x + nxt * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + nxt * D)[i]; }
+        if (i < nv) {
+          xn[v] = reinterpret_cast<const uint4*>(x + nxt * D)[i]; gn[v] = reinterpret_cast<const uint4*>(dy + nxt * D)[i];
+          if (gres) rn[v] = reinterpret_cast<const uint4*>(gres + nxt * D)[i];
+        }
       }
     }
     const float a = a_in[row];
@@ -193,6 +201,11 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         unpack8(xc[v], xf); unpack8(gc[v], gf); unpack8(wv[v], wf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = a * gf[j] * wf[j] - xf[j] * k;
+        if (gres) {
+          float rf[8]; unpack8(rc[v], rf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rf[j];
+        }
         reinterpret_cast<uint4*>(dx + row * D)[i] = pack8(o);
       }
     }
@@ -390,27 +403,80 @@ __global__ void sqnorm_kernel(const T* __restrict__ x, const float* __restrict__
   acc = block_sum(acc, red);
   if (threadIdx.x == 0) atomicAdd(out, acc);
 }
+// bf16 input, 16-byte aligned arrays: eight values per thread and step, two steps in flight
+__global__ void __launch_bounds__(512)
+sqnorm_bf16_vec_kernel(const uint4* __restrict__ x, const float4* __restrict__ wgt, float* __restrict__ out, size_t n8) {
+  __shared__ float red[32];
+  float acc0 = 0.f, acc1 = 0.f;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  auto one = [&](size_t k, float& acc) {
+    float f[8]; unpack8(x[k], f);
+    if (wgt) {
+      const float4 w0 = wgt[2 * k], w1 = wgt[2 * k + 1];
+      acc += f[0] * f[0] * w0.x + f[1] * f[1] * w0.y + f[2] * f[2] * w0.z + f[3] * f[3] * w0.w +
+             f[4] * f[4] * w1.x + f[5] * f[5] * w1.y + f[6] * f[6] * w1.z + f[7] * f[7] * w1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += f[j] * f[j];
+    }
+  };
+  for (; i + stride < n8; i += 2 * stride) { one(i, acc0); one(i + stride, acc1); }
+  if (i < n8) one(i, acc0);
+  const float acc = block_sum(acc0 + acc1, red);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
 
 // ------------------------------------------------------------------------------------ fused Adam(W)
 // One pass: grad (bf16 or fp32) * scale[0] -> moments -> fp32 master -> low-precision parameter copy.
+struct AdamCoef { float lr, b1, b2, eps, wd, inv_bc1, inv_sqrt_bc2, scale; int adamw; };
+__device__ __forceinline__ float adam_one(float g, float& w, float& mi, float& vi, const AdamCoef& c) {
+  g *= c.scale;
+  if (!c.adamw && c.wd != 0.f) g += c.wd * w;
+  mi = c.b1 * mi + (1.f - c.b1) * g;
+  vi = c.b2 * vi + (1.f - c.b2) * g * g;
+  float upd = (mi * c.inv_bc1) / (sqrtf(vi) * c.inv_sqrt_bc2 + c.eps);
+  if (c.adamw && c.wd != 0.f) upd += c.wd * w;
+  w -= c.lr * upd;
+  return w;
+}
 template <typename G>
 __global__ void adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                             const G* __restrict__ grad, bf16* __restrict__ param_out, size_t n, float lr, float b1,
                             float b2, float eps, float wd, float bc1, float bc2, int adamw,
                             const float* __restrict__ scale_ptr, float scale_host) {
-  const float scale = scale_ptr ? scale_ptr[0] : scale_host;
-  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  const AdamCoef c{lr, b1, b2, eps, wd, 1.f / bc1, rsqrtf(bc2), scale_ptr ? scale_ptr[0] : scale_host, adamw};
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    float g = to_f<G>(grad[i]) * scale;
-    float w = master[i];
-    if (!adamw && wd != 0.f) g += wd * w;
-    const float mi = b1 * m[i] + (1.f - b1) * g;
-    const float vi = b2 * v[i] + (1.f - b2) * g * g;
-    float upd = (mi * inv_bc1) / (sqrtf(vi) * inv_sqrt_bc2 + eps);
-    if (adamw && wd != 0.f) upd += wd * w;
-    w -= lr * upd;
+    float w = master[i], mi = m[i], vi = v[i];
+    adam_one(to_f<G>(grad[i]), w, mi, vi, c);
     m[i] = mi; v[i] = vi; master[i] = w;
     if (param_out) param_out[i] = __float2bfloat16_rn(w);
+  }
+}
+// bf16 gradients, 16-byte aligned arrays, n a multiple of 4: four values per thread and step (16-byte accesses to the
+// fp32 state, 8-byte to the bf16 gradient and parameter)
+__global__ void __launch_bounds__(512)
+adam_bf16_vec_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
+                     const uint2* __restrict__ grad, uint2* __restrict__ param_out, size_t n4, float lr, float b1,
+                     float b2, float eps, float wd, float bc1, float bc2, int adamw,
+                     const float* __restrict__ scale_ptr, float scale_host) {
+  const AdamCoef c{lr, b1, b2, eps, wd, 1.f / bc1, rsqrtf(bc2), scale_ptr ? scale_ptr[0] : scale_host, adamw};
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    float4 w = master[i], mi = m[i], vi = v[i];
+    const uint2 gq = grad[i];
+    const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gq.x));
+    const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gq.y));
+    adam_one(g01.x, w.x, mi.x, vi.x, c);
+    adam_one(g01.y, w.y, mi.y, vi.y, c);
+    adam_one(g23.x, w.z, mi.z, vi.z, c);
+    adam_one(g23.y, w.w, mi.w, vi.w, c);
+    m[i] = mi; v[i] = vi; master[i] = w;
+    if (param_out) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+      param_out[i] = o;
+    }
   }
 }
 
@@ -598,15 +664,15 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* w, void* y, float* a_ou
 extern "C" int sb_rmsnorm_bwd_blocks(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
 
 // dw: bf16 [D], written (not accumulated); partial is scratch of sb_rmsnorm_bwd_blocks(T) * D floats.  Two launches.
-extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, void* dx, void* dw,
-                              float* partial, int T, int D, float eps, int form, cudaStream_t st) {
+extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, const void* gres, void* dx,
+                              void* dw, float* partial, int T, int D, float eps, int form, cudaStream_t st) {
   if (D % 8) return -1;
   if (T == 0) return 0;
   const int nv = D / 8;
   int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
   const int vpt = (nv + threads - 1) / threads;
   const int grid = sb_rmsnorm_bwd_blocks(T);
-#define LAUNCH(V) rmsnorm_bwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, a_in, (bf16*)dx, partial, T, D, eps, form)
+#define LAUNCH(V) rmsnorm_bwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, a_in, (const bf16*)gres, (bf16*)dx, partial, T, D, eps, form)
   if (vpt <= 1) LAUNCH(1);
   else if (vpt <= 2) LAUNCH(2);
   else if (vpt <= 4) LAUNCH(4);
@@ -673,6 +739,14 @@ extern "C" int sb_colsum(const void* x, float* out, int T, int N, cudaStream_t s
 // out must be zeroed by the caller (it is accumulated into)
 extern "C" int sb_sqnorm(const void* x, const float* wgt, float* out, long long n, int is_bf16, cudaStream_t st) {
   if (n == 0) return 0;
+  if (is_bf16 && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wgt)) & 15) && n >= 8) {
+    const size_t n8 = (size_t)n / 8;
+    sqnorm_bf16_vec_kernel<<<grid_for(n8, 512, 148 * 4), 512, 0, st>>>((const uint4*)x, (const float4*)wgt, out, n8);
+    const size_t done = n8 * 8;
+    if (done < (size_t)n)
+      sqnorm_kernel<bf16><<<1, 32, 0, st>>>((const bf16*)x + done, wgt ? wgt + done : nullptr, out, (size_t)n - done);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int grid = grid_for((size_t)n, 512, 148 * 4);
   if (is_bf16) sqnorm_kernel<bf16><<<grid, 512, 0, st>>>((const bf16*)x, wgt, out, (size_t)n);
   else sqnorm_kernel<float><<<grid, 512, 0, st>>>((const float*)x, wgt, out, (size_t)n);
@@ -683,6 +757,15 @@ extern "C" int sb_adam(float* master, float* m, float* v, const void* grad, void
                        float b1, float b2, float eps, float wd, float bc1, float bc2, int adamw, const float* scale_ptr,
                        float scale_host, int grad_is_bf16, cudaStream_t st) {
   if (n == 0) return 0;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         (reinterpret_cast<uintptr_t>(grad) << 1) | (reinterpret_cast<uintptr_t>(param_out) << 1);
+  if (grad_is_bf16 && !(bits & 15) && (n % 4) == 0) {
+    const size_t n4 = (size_t)n / 4;
+    adam_bf16_vec_kernel<<<grid_for(n4, 512, 148 * 8), 512, 0, st>>>((float4*)master, (float4*)m, (float4*)v, (const uint2*)grad,
+                                                                    (uint2*)param_out, n4, lr, b1, b2, eps, wd, bc1, bc2, adamw,
+                                                                    scale_ptr, scale_host);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int grid = grid_for((size_t)n, 512, 148 * 8);
   if (grad_is_bf16)
     adam_kernel<bf16><<<grid, 512, 0, st>>>(master, m, v, (const bf16*)grad, (bf16*)param_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr, scale_host);

@@ -17,6 +17,11 @@ from .mlp import ParallelGLU, ParallelMLP
 from .norms import get_norm
 
 
+def _norm_and_residual(norm, x):
+    fn = getattr(norm, "forward_with_residual", None)
+    return fn(x) if fn is not None else (norm(x), x)
+
+
 class ParallelBlock(nn.Module):
     def __init__(self, cfg, init_method, output_layer_init_method, layer_number: int, dtype=None, device=None):
         super().__init__()
@@ -71,14 +76,16 @@ class ParallelBlock(nn.Module):
                     out = out + b
             return x + self._drop(out)
         residual = x
-        u = self.input_layernorm(x) if self.prenorm else x
         no_drop = not (self.hidden_dropout > 0.0 and self.training)
         if no_drop and not self.postnorm and not self.outer_mlp_norm:
-            # residual and bias additions ride in the epilogues of the out-projection and w3 GEMMs
+            # residual and bias additions ride in the epilogues of the out-projection and w3 GEMMs; the norms hand the
+            # residual branch through so that its gradient is added inside their backward kernels
+            u, residual = _norm_and_residual(self.input_layernorm, x) if self.prenorm else (x, x)
             a, _ = self.mixer(u, positions, residual)
-            u = self.pre_mlp_layernorm(a) if self.pre_mlp_norm else a
-            y, _ = self._mlp(u, positions, a)
+            u, a_res = _norm_and_residual(self.pre_mlp_layernorm, a) if self.pre_mlp_norm else (a, a)
+            y, _ = self._mlp(u, positions, a_res)
             return y
+        u = self.input_layernorm(x) if self.prenorm else x
         m, mb = self.mixer(u, positions)
         if mb is not None:
             m = m + mb

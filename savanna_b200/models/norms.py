@@ -31,6 +31,10 @@ class RMSNorm(nn.Module):
     def forward(self, x):
         return ops.rmsnorm(x, self.gain, self.eps, self.form)
 
+    def forward_with_residual(self, x):
+        """(norm(x), x for the residual branch)."""
+        return ops.rmsnorm_residual(x, self.gain, self.eps, self.form)
+
 
 class ScaleNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5, dtype=None, device=None):

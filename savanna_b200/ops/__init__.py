@@ -57,6 +57,14 @@ def rmsnorm(x, weight, eps: float, form: str = "te"):
     return _co().rmsnorm(x, weight, eps, form) if _k(x) else ref.rmsnorm(x, weight, eps, form)
 
 
+def rmsnorm_residual(x, weight, eps: float, form: str = "te"):
+    """(rmsnorm(x), x): the second value is x as it continues down the residual branch.  On the kernel path the
+    gradient that comes back along that branch is added inside the norm's backward kernel."""
+    if _k(x):
+        return _co().rmsnorm_residual(x, weight, eps, form)
+    return ref.rmsnorm(x, weight, eps, form), x
+
+
 def linear(x, w, bias=None, fp8: bool = False, residual=None):
     """x w^T (+ bias) (+ residual).  On CUDA bias and residual are added in the GEMM epilogue."""
     if _k(x):

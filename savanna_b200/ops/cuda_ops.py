@@ -57,7 +57,7 @@ class _Sig:
     sb_quantize_fp8 = [P, P, P, P, LL, I, P]
     sb_quantize_fp8_delayed = [P, P, P, I, I, P, LL, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
-    sb_rmsnorm_bwd = [P, P, P, P, P, P, P, I, I, F, I, P]
+    sb_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd_blocks = [I]
     sb_glu_fwd = [P, P, LL, I, I, P]
     sb_glu_bwd = [P, P, P, LL, I, I, P]
@@ -374,36 +374,76 @@ def linear_reducescatter(x, w, seq_dim, fp8):
 # ----------------------------------------------------------------------------- RMSNorm
 
 
+def _rmsnorm_fwd(x, w, eps, form):
+    lib = require()
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    T, D = x2.shape
+    y = torch.empty_like(x2)
+    a = torch.empty(T, dtype=torch.float32, device=x.device)
+    wc = w.contiguous()
+    _check(lib.sb_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), a.data_ptr(), T, D, eps, form, _stream()),
+           "rmsnorm_fwd")
+    _count()
+    return x2, wc, a, y
+
+
+def _rmsnorm_bwd(x2, w, a, gy, gres, eps, form):
+    lib = require()
+    T, D = x2.shape
+    g2 = gy.reshape(T, D).contiguous()
+    r2 = gres.reshape(T, D).contiguous() if gres is not None else None
+    dx = torch.empty_like(x2)
+    dw = torch.empty(D, dtype=bf16, device=x2.device)
+    partial = torch.empty(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
+    _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), _ptr(r2), dx.data_ptr(),
+                              dw.data_ptr(), partial.data_ptr(), T, D, eps, form, _stream()), "rmsnorm_bwd")
+    _count(2)
+    return dx, dw
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps, form):
-        lib = require()
-        x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        T, D = x2.shape
-        y = torch.empty_like(x2)
-        a = torch.empty(T, dtype=torch.float32, device=x.device)
-        wc = w.contiguous()
-        _check(lib.sb_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), a.data_ptr(), T, D, eps, form, _stream()),
-               "rmsnorm_fwd")
-        _count()
+        x2, wc, a, y = _rmsnorm_fwd(x, w, eps, form)
         ctx.save_for_backward(x2, wc, a)
         ctx.meta = (eps, form, x.shape)
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, gy):
-        lib = require()
         x2, w, a = ctx.saved_tensors
         eps, form, shape = ctx.meta
-        T, D = x2.shape
-        g2 = gy.reshape(T, D).contiguous()
-        dx = torch.empty_like(x2)
-        dw = torch.empty(D, dtype=bf16, device=x2.device)
-        partial = torch.empty(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
-        _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                                  partial.data_ptr(), T, D, eps, form, _stream()), "rmsnorm_bwd")
-        _count(2)
+        dx, dw = _rmsnorm_bwd(x2, w, a, gy, None, eps, form)
         return dx.view(shape), dw, None, None
+
+
+class _RMSNormResidual(torch.autograd.Function):
+    """(norm(x), x): the second output carries x down the residual branch; the gradient arriving there is added inside
+    the norm's backward kernel instead of by a separate accumulation kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, form):
+        x2, wc, a, y = _rmsnorm_fwd(x, w, eps, form)
+        ctx.save_for_backward(x2, wc, a)
+        ctx.meta = (eps, form, x.shape)
+        ctx.set_materialize_grads(False)
+        return y.view(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, gy, gres):
+        x2, w, a = ctx.saved_tensors
+        eps, form, shape = ctx.meta
+        if gy is None:
+            return gres, None, None, None
+        dx, dw = _rmsnorm_bwd(x2, w, a, gy, gres, eps, form)
+        return dx.view(shape), dw, None, None
+
+
+def rmsnorm_residual(x, weight, eps, form="te"):
+    """(rmsnorm(x), x) with the two gradients combined in one backward kernel."""
+    if not _is_bf16(x, weight) or x.shape[-1] % 8 or x.shape[-1] > 16384 or x.shape[-1] < 64:
+        return ref.rmsnorm(x, weight, eps, form), x
+    return _RMSNormResidual.apply(x, weight, float(eps), 0 if form == "te" else 1)
 
 
 def rmsnorm(x, weight, eps, form="te"):

@@ -132,6 +132,28 @@ def test_rmsnorm(form, D):
     _rel(w.grad, wr.grad, 2e-2, "rmsnorm dw")
 
 
+def test_rmsnorm_residual_branch():
+    """(norm(x), x): the gradient of the residual branch is added inside the norm's backward kernel."""
+    torch.manual_seed(50)
+    x = torch.randn(3, 70, 4096, device=DEV, dtype=BF, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(4096, device=DEV)).to(BF).requires_grad_()
+    y, r = ops.rmsnorm_residual(x, w, 1e-6, "te")
+    g1, g2 = torch.randn_like(y), torch.randn_like(y)
+    ((y.float() * g1.float()).sum() + (r.float() * g2.float()).sum()).backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6, "te")
+    ((yr * g1.float()).sum() + (xr * g2.float()).sum()).backward()
+    _rel(y, yr, 1e-2, "y")
+    assert torch.equal(r, x)
+    _rel(x.grad, xr.grad, 1e-2, "dx with residual gradient")
+    _rel(w.grad, wr.grad, 2e-2, "dw")
+    # only the residual branch used: the gradient passes through unchanged
+    x2 = x.detach().clone().requires_grad_()
+    _, r2 = ops.rmsnorm_residual(x2, w, 1e-6, "te")
+    (r2.float() * g2.float()).sum().backward()
+    _rel(x2.grad, g2, 1e-3, "pass-through")
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu", "identity"])
 def test_glu(act):
     torch.manual_seed(6)
