@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--bf16-only", action="store_true", help="measure only the all-bf16 recipe (no fp8 projection GEMMs)")
     ap.add_argument("--skip-second", action="store_true", help="do not also measure the all-bf16 recipe")
     ap.add_argument("--comm", type=str, default=None, choices=["symm", "nccl"], help="ZeRO collective path (default: config)")
+    ap.add_argument("--override", action="append", default=[], metavar="KEY=VALUE",
+                    help="debug only: override a config key (YAML value); the result is then not the named config")
     return ap.parse_args()
 
 
@@ -187,6 +189,10 @@ def main():
         over["gradient_accumulation_steps"] = args.accum
     if args.comm:
         over["comm_path"] = args.comm
+    for kv in args.override:
+        import yaml
+        k, _, v = kv.partition("=")
+        over[k.replace("-", "_")] = yaml.safe_load(v)
     if args.layers:
         import yaml
         doc = yaml.load(open(args.config), Loader=yaml.FullLoader)
@@ -260,7 +266,13 @@ def main():
         if dist.is_initialized():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_per_step = float(t.item()) / args.steps
+        from savanna_b200.parallel import state as pstate
+        par = "".join(f"{n}{v} " for n, v in (("pp", pstate.get_pipe_parallel_world_size()),
+                                               ("tp", pstate.get_model_parallel_world_size()),
+                                               ("cp", pstate.get_context_parallel_world_size())) if v > 1)
+        par += f"dp{pstate.get_data_parallel_world_size()} zero{cfg.zero_stage}" + (" sp" if cfg.sequence_parallel else "")
         res = {"value": tokens_per_step / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "loss": float(loss),
+               "parallelism": par,
                "clocks": clocks, "gpu_launches": launches, "cfg": cfg, "e2e": None,
                "zero_path": ("fused peer-memory kernels" if getattr(trainer.optimizer, "fused", None) is not None
                              else ("nccl" if world > 1 else "single rank"))}
@@ -312,7 +324,7 @@ def main():
             "config": {"model": (f"{cfg.num_layers}L D{cfg.hidden_size} {cfg.num_attention_heads} heads ffn {cfg.ffn_size} vocab {cfg.padded_vocab_size} ({os.path.basename(args.config)})") if not args.layers
                        else f"DEBUG {args.layers}-layer truncation (not the named config)",
                        "global_batch": cfg.train_batch_size, "seq_len": L, "micro_batch": B, "grad_accum": gas,
-                       "parallelism": f"dp{world} zero1", "zero_path": zero_path, "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
+                       "parallelism": main_res["parallelism"], "zero_path": zero_path, "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
             "mfu_of_measured_bf16_peak": mfu, "mfu_note": "model FLOPs/s over the measured sustained cuBLAS bf16 peak; fp8 projection GEMMs can exceed 1.0 of a bf16 denominator", "model_flops_per_token": fpt, "loss": final_loss,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "bf16_only": None if other is None else {"value": other["value"], "ms_per_step": other["ms_per_step"],
