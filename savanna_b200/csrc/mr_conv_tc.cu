@@ -380,9 +380,253 @@ mr_tc_bwd_kernel(MrArgs a, const bf16* __restrict__ dz, bf16* __restrict__ dfeat
   }
 }
 
+// ------------------------------------------------------------------------------------ backward, streaming form
+// A CTA owns 64 channels and a segment of consecutive 64-row tiles.  The rows of u = x2*v and g = dz*x1 live in two
+// shared-memory rings of 320 rows (128 behind the current tile, the tile, 128 ahead); each tile step stages only the
+// 64 new rows at the front, so every input row is read once per CTA instead of five times, and the filter-gradient
+// accumulators stay in registers over the whole segment (one flush per CTA instead of one per tile).  Per tile: y and
+// du by Toeplitz MMAs into a bf16 staging tile, the filter-gradient MMAs (each warp keeps half of the nine block
+// diagonals for all 64 rows of its slab), then a coalesced pass that re-reads the tile's features and dz from global
+// memory (L2 hits), combines them with y and du and stores dfeat.
+constexpr int SB_TT = 64;                         // rows per tile step
+constexpr int SB_RING = TC_HALO + SB_TT + TC_HALO; // 320
+constexpr int SB_SMEM = (2 * SB_RING + 2 * SB_TT) * TC_LD * 2 + (4 * 128 + TC_CH) * 4;
+
+__device__ __forceinline__ int ring_pos(int p) { return p < 0 ? p + SB_RING : (p >= SB_RING ? p - SB_RING : p); }
+
+__global__ void __launch_bounds__(TC_THREADS, 2)
+mr_tc_bwd_stream_kernel(MrArgs a, const bf16* __restrict__ dz, bf16* __restrict__ dfeat, bf16* __restrict__ dhalo,
+                        float* __restrict__ dh, float* __restrict__ dbias, int n_halo_tiles, int n_tiles, int tiles_per_seg) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  bf16* sU = reinterpret_cast<bf16*>(smraw);
+  bf16* sG = sU + SB_RING * TC_LD;
+  bf16* sY = sG + SB_RING * TC_LD;                 // [64][LD] y (with the bias term) of the current tile
+  bf16* sDU = sY + SB_TT * TC_LD;                  // [64][LD] du
+  float* sdh = reinterpret_cast<float*>(sDU + SB_TT * TC_LD);       // [4 slabs][128]
+  float* sdb = sdh + 4 * 128;                                        // [64]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c_base = blockIdx.x * TC_CH, b = blockIdx.z;
+  const int k0 = blockIdx.y * tiles_per_seg, k1 = min(k0 + tiles_per_seg, n_tiles);
+  if (k0 >= k1) return;
+  const int seg_t0 = (k0 - n_halo_tiles) * SB_TT, seg_t1 = (k1 - n_halo_tiles) * SB_TT;
+  const int base_t = seg_t0 - TC_HALO;             // time of ring row 0 (the ring wraps modulo SB_RING from there)
+  for (int i = tid; i < 4 * 128 + TC_CH; i += TC_THREADS) sdh[i] = 0.f;
+
+  float db_part[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) db_part[j] = 0.f;
+  // rows [t_first, t_first + count) -> ring; u for every row that exists (sequence or halo), g inside the sequence
+  auto stage = [&](int t_first, int count) {
+    for (int i = tid; i < count * 8; i += TC_THREADS) {
+      const int r = i >> 3, cv = i & 7;
+      const int t = t_first + r, c0 = c_base + cv * 8;
+      const int pos = (t - base_t) % SB_RING;
+      float x1[8], x2[8], v[8], f[8], gg[8];
+      load_row8(a, b, t, c0, x1, x2, v);
+      const bool in_seq = t >= 0 && t < a.L && c0 < a.D;
+      if (in_seq) {
+        const uint4 q = *reinterpret_cast<const uint4*>(dz + ((size_t)b * a.L + t) * a.D + c0);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 pq = unpack2(w[j]); gg[2 * j] = pq.x * x1[2 * j]; gg[2 * j + 1] = pq.y * x1[2 * j + 1]; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gg[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = x2[j] * v[j];
+      st8(sU + pos * TC_LD + cv * 8, f);
+      st8(sG + pos * TC_LD + cv * 8, gg);
+      if (in_seq && t >= seg_t0 && t < seg_t1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) db_part[j] += gg[j] * f[j];
+      }
+    }
+  };
+  stage(base_t, SB_RING);
+
+  const int slab = warp & 3, half = warp >> 2;
+  const int ch0 = c_base + slab * 16;
+  const int grp = min(ch0, a.D - 1) / a.dg;
+  const float* hg = a.h + (size_t)grp * a.K;
+  const int nd = min(ND, (a.K - 1) / 16 + 2);
+  const int g = lane >> 2, tq = lane & 3;
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+  const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+  // filter-gradient accumulators: this warp covers diagonals d = half, half + 2, ... for all four row blocks of the tile
+  constexpr int NDH = (ND + 1) / 2;
+  float P[NDH][2][4];
+#pragma unroll
+  for (int dd = 0; dd < NDH; ++dd)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) P[dd][nt][q] = 0.f;
+  __syncthreads();
+
+  for (int k = k0; k < k1; ++k) {
+    const int t0 = (k - n_halo_tiles) * SB_TT;
+    const int rel0 = (t0 - base_t) % SB_RING;                 // ring row of the tile's first row
+    // ---- y (causal) and du (anticausal) for this warp's two row blocks -> staging tiles
+    {
+      uint32_t A[ND][4];
+      toeplitz_frags(A, hg, a.K, lane, false);
+      float acc[2][2][4];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        const int i0 = half * 32 + blk * 16;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) acc[blk][nt][q] = 0.f;
+#pragma unroll
+        for (int d = 0; d < ND; ++d) {
+          if (d < nd) {
+            uint32_t bf[4];
+            ldsm_x4_t(bf, smem_addr(sU + (ring_pos(rel0 + i0 - 16 * d) + lm_row) * TC_LD + slab * 16 + lm_col));
+            mma16816(acc[blk][0], A[d], bf[0], bf[1]);
+            mma16816(acc[blk][1], A[d], bf[2], bf[3]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int row = i0 + g + hh * 8, col = slab * 16 + nt * 8 + 2 * tq;
+            const float2 u = unpack2(*reinterpret_cast<const uint32_t*>(sU + ring_pos(rel0 + row) * TC_LD + col));
+            const int ca = c_base + col;
+            const float b0 = ca < a.D ? a.bias[ca] : 0.f, b1 = ca + 1 < a.D ? a.bias[ca + 1] : 0.f;
+            *reinterpret_cast<uint32_t*>(sY + row * TC_LD + col) = pack2(acc[blk][nt][hh * 2] + b0 * u.x, acc[blk][nt][hh * 2 + 1] + b1 * u.y);
+          }
+      }
+      toeplitz_frags(A, hg, a.K, lane, true);
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        const int i0 = half * 32 + blk * 16;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) acc[blk][nt][q] = 0.f;
+#pragma unroll
+        for (int d = 0; d < ND; ++d) {
+          if (d < nd) {
+            uint32_t bf[4];
+            ldsm_x4_t(bf, smem_addr(sG + (ring_pos(rel0 + i0 + 16 * d) + lm_row) * TC_LD + slab * 16 + lm_col));
+            mma16816(acc[blk][0], A[d], bf[0], bf[1]);
+            mma16816(acc[blk][1], A[d], bf[2], bf[3]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int row = i0 + g + hh * 8, col = slab * 16 + nt * 8 + 2 * tq;
+            const float2 gg = unpack2(*reinterpret_cast<const uint32_t*>(sG + ring_pos(rel0 + row) * TC_LD + col));
+            const int ca = c_base + col;
+            const float b0 = ca < a.D ? a.bias[ca] : 0.f, b1 = ca + 1 < a.D ? a.bias[ca + 1] : 0.f;
+            *reinterpret_cast<uint32_t*>(sDU + row * TC_LD + col) = pack2(acc[blk][nt][hh * 2] + b0 * gg.x, acc[blk][nt][hh * 2 + 1] + b1 * gg.y);
+          }
+      }
+    }
+    // ---- filter gradient: P_d[i][j] += sum_c G[i0+i][c] U[i0-16d+j][c] over the four row blocks, d = half, half+2, ..
+    if (t0 >= 0) {
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        const int i0 = blk * 16;
+        uint32_t af[4];
+        ldsm_x4(af, smem_addr(sG + (ring_pos(rel0 + i0) + a_row) * TC_LD + slab * 16 + a_col));
+#pragma unroll
+        for (int dd = 0; dd < NDH; ++dd) {
+          const int d = 2 * dd + half;
+          if (d < nd) {
+            uint32_t bf[4];
+            ldsm_x4(bf, smem_addr(sU + (ring_pos(rel0 + i0 - 16 * d) + b_row) * TC_LD + slab * 16 + b_col));
+            mma16816(P[dd][0], af, bf[0], bf[1]);
+            mma16816(P[dd][1], af, bf[2], bf[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();                                           // y / du tiles complete, ring reads of this tile done
+    // ---- coalesced output pass: (row, 8 channels) per thread and step
+    for (int i = tid; i < SB_TT * 8; i += TC_THREADS) {
+      const int r = i >> 3, cv = i & 7;
+      const int t = t0 + r, c0 = c_base + cv * 8;
+      if (c0 >= a.D) continue;
+      bf16* dst = nullptr;
+      if (t >= 0 && t < a.L) dst = dfeat + ((size_t)b * a.L + t) * 3 * a.D + 3 * c0;
+      else if (t < 0 && t >= -(a.K - 1) && dhalo) dst = dhalo + ((size_t)b * (a.K - 1) + (t + a.K - 1)) * 3 * a.D + 3 * c0;
+      if (!dst) continue;
+      float x1[8], x2[8], v[8], gz[8];
+      load_row8(a, b, t, c0, x1, x2, v);
+      if (t >= 0) {
+        const uint4 q = *reinterpret_cast<const uint4*>(dz + ((size_t)b * a.L + t) * a.D + c0);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 pq = unpack2(w[j]); gz[2 * j] = pq.x; gz[2 * j + 1] = pq.y; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gz[j] = 0.f;
+      }
+      const uint4 yq = *reinterpret_cast<const uint4*>(sY + r * TC_LD + cv * 8);
+      const uint4 dq = *reinterpret_cast<const uint4*>(sDU + r * TC_LD + cv * 8);
+      const uint32_t yw[4] = {yq.x, yq.y, yq.z, yq.w}, dw[4] = {dq.x, dq.y, dq.z, dq.w};
+      float o[24];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 y = unpack2(yw[j]), du = unpack2(dw[j]);
+        o[6 * j + 0] = gz[2 * j] * y.x;       o[6 * j + 1] = du.x * v[2 * j];       o[6 * j + 2] = du.x * x2[2 * j];
+        o[6 * j + 3] = gz[2 * j + 1] * y.y;   o[6 * j + 4] = du.y * v[2 * j + 1];   o[6 * j + 5] = du.y * x2[2 * j + 1];
+      }
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      d4[0] = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+      d4[1] = make_uint4(pack2(o[8], o[9]), pack2(o[10], o[11]), pack2(o[12], o[13]), pack2(o[14], o[15]));
+      d4[2] = make_uint4(pack2(o[16], o[17]), pack2(o[18], o[19]), pack2(o[20], o[21]), pack2(o[22], o[23]));
+    }
+    // ---- advance the rings: the 64 rows that fall out behind are replaced by the 64 rows ahead of the next tile
+    if (k + 1 < k1) stage(t0 + SB_TT + TC_HALO, SB_TT);
+    __syncthreads();
+  }
+
+  // ---- flush: filter gradient (once per CTA), bias gradient
+#pragma unroll
+  for (int dd = 0; dd < NDH; ++dd) {
+    const int d = 2 * dd + half;
+    if (d < nd) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = g + ((q & 2) ? 8 : 0), j = nt * 8 + 2 * tq + (q & 1);
+          const int s = 16 * d + i - j;
+          if (s >= 0 && s < a.K) atomicAdd(&sdh[slab * 128 + s], P[dd][nt][q]);
+        }
+    }
+  }
+  {
+    const int cv = tid & 7;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&sdb[cv * 8 + j], db_part[j]);
+  }
+  __syncthreads();
+  for (int i = tid; i < 4 * 128; i += TC_THREADS) {
+    const int sl = i >> 7, s = i & 127;
+    const int c = c_base + sl * 16;
+    if (s < a.K && c < a.D) atomicAdd(dh + (size_t)(c / a.dg) * a.K + s, sdh[i]);
+  }
+  for (int i = tid; i < TC_CH; i += TC_THREADS)
+    if (c_base + i < a.D) atomicAdd(dbias + c_base + i, sdb[i]);
+}
+
+static int g_mr_bwd_stream = 1;
+
 }  // namespace sb
 
 using namespace sb;
+
+// 1 (default): streaming backward kernel; 0: one independent CTA per 64-row tile
+extern "C" int sb_mr_tc_set_bwd_variant(int streaming) { sb::g_mr_bwd_stream = streaming ? 1 : 0; return 0; }
 
 extern "C" int sb_mr_tc_supported(int D, int G, int K) {
   const int dg = D / G;
@@ -416,6 +660,25 @@ extern "C" int sb_mr_tc_bwd(const void* feat, const void* halo, const float* h, 
   }
   MrArgs a{(const bf16*)feat, (const bf16*)halo, h, bias, L, D, K, D / G};
   const int n_halo = (halo && dhalo) ? (K - 1 + BWD_TT - 1) / BWD_TT : 0;
+  if (g_mr_bwd_stream) {
+    static bool attr2 = false;
+    if (!attr2) {
+      if (cudaFuncSetAttribute(mr_tc_bwd_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM) != cudaSuccess) return -5;
+      attr2 = true;
+    }
+    const int n_tiles = (L + SB_TT - 1) / SB_TT + n_halo;
+    const int ctiles = (D + TC_CH - 1) / TC_CH;
+    // as many segments as fit in one wave of two CTAs per SM (a partial second wave would double the run time),
+    // but no shorter than 8 tiles (the ring prologue costs 4 tiles)
+    int segs = (2 * 148) / (ctiles * B);
+    if (segs > (n_tiles + 7) / 8) segs = (n_tiles + 7) / 8;
+    if (segs < 1) segs = 1;
+    const int tps = (n_tiles + segs - 1) / segs;
+    dim3 sgrid(ctiles, (n_tiles + tps - 1) / tps, B);
+    mr_tc_bwd_stream_kernel<<<sgrid, TC_THREADS, SB_SMEM, st>>>(a, (const bf16*)dz, (bf16*)dfeat, (bf16*)dhalo, dh, dbias, n_halo,
+                                                               n_tiles, tps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   dim3 grid((D + TC_CH - 1) / TC_CH, (L + BWD_TT - 1) / BWD_TT + n_halo, B);
   mr_tc_bwd_kernel<<<grid, TC_THREADS, BWD_SMEM, st>>>(a, (const bf16*)dz, (bf16*)dfeat, (bf16*)dhalo, dh, dbias, n_halo);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -73,6 +73,7 @@ class _Sig:
     sb_mr_fwd = [P, P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_bwd = [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_tc_fwd = [P, P, P, P, P, I, I, I, I, I, P]
+    sb_mr_tc_set_bwd_variant = [I]
     sb_mr_tc_bwd = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
     sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
@@ -151,6 +152,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, a_mn: bool = False
                            f"ptrs {a.data_ptr():#x} {b.data_ptr():#x} {out.data_ptr():#x}")
     _count()
     return out
+
+
+def set_mr_backward_variant(streaming: bool) -> None:
+    """Hyena-MR tensor-core backward: the streaming kernel (rings of u and g rows, one filter-gradient flush per CTA;
+    default) or one independent CTA per 64-row tile."""
+    require().sb_mr_tc_set_bwd_variant(int(bool(streaming)))
 
 
 def set_gemm_pair_mode(mode: int) -> None:
@@ -763,7 +770,21 @@ def hyena_mr_inner(feat, h, bias, halo=None):
 # ----------------------------------------------------------------------------- Hyena-LI (modal scan)
 
 LI_ORDER = 16
-LI_CHUNK = 128
+
+
+LI_CHUNK_OVERRIDE = None      # tests set this to exercise a chunk length that their small shapes would not select
+
+
+def _li_chunk(B: int, L: int, D: int) -> int:
+    """Chunk length of the scan: as long as possible (the pass over the chunk states is serial in the number of
+    chunks) while the chunk grid still oversubscribes the GPU (>= 2048 blocks of 128 channels; with fewer blocks the
+    chunk kernels lose more than the shorter chunk-state pass gains: 0.37 ms against 0.28 ms forward at L = 8192)."""
+    if LI_CHUNK_OVERRIDE:
+        return int(LI_CHUNK_OVERRIDE)
+    tc = 1024
+    while tc > 128 and B * ((D + 127) // 128) * ((L + tc - 1) // tc) < 2048:
+        tc //= 2
+    return tc
 
 
 def _pad_order(t, fill):
@@ -791,12 +812,13 @@ class _HyenaLI(torch.autograd.Function):
         if state_in is not None:
             sin = torch.zeros((B, D, LI_ORDER), dtype=torch.float32, device=feat.device)
             sin[..., :O] = state_in.detach().float()
-        NC = (L + LI_CHUNK - 1) // LI_CHUNK
+        tc = _li_chunk(B, L, D)
+        NC = (L + tc - 1) // tc
         S = torch.empty((B, NC, D, LI_ORDER), dtype=torch.float32, device=feat.device)
         sout = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=feat.device) if want_state else None
         z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
         _check(lib.sb_li_fwd(fc.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(), _ptr(sin), _ptr(sout), S.data_ptr(),
-                             z.data_ptr(), B, L, D, LI_CHUNK, _stream()), "li_fwd")
+                             z.data_ptr(), B, L, D, tc, _stream()), "li_fwd")
         _count(3)
         ctx.save_for_backward(fc, ll, Rp, bf, sin if sin is not None else torch.empty(0, device=feat.device))
         ctx.meta = (O, state_in is not None, gamma.dtype, R.dtype, p.dtype, bias.dtype, want_state)
@@ -812,7 +834,8 @@ class _HyenaLI(torch.autograd.Function):
         B, L, C3 = fc.shape
         D = C3 // 3
         dev = fc.device
-        NC = (L + LI_CHUNK - 1) // LI_CHUNK
+        tc = _li_chunk(B, L, D)
+        NC = (L + tc - 1) // tc
         g = gz.contiguous()
         shape = (B, NC, D, LI_ORDER)
         S, W, A, dRp, dLp = (torch.empty(shape, dtype=torch.float32, device=dev) for _ in range(5))
@@ -828,7 +851,7 @@ class _HyenaLI(torch.autograd.Function):
         _check(lib.sb_li_bwd(fc.data_ptr(), g.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(),
                              sin.data_ptr() if has_sin else None, _ptr(dso), S.data_ptr(), W.data_ptr(), A.data_ptr(),
                              dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), tmp.data_ptr(), df.data_ptr(), _ptr(w_end),
-                             _ptr(dsi), B, L, D, LI_CHUNK, _stream()), "li_bwd")
+                             _ptr(dsi), B, L, D, tc, _stream()), "li_bwd")
         _count(4)
         dR = dRp.sum((0, 1))[:, :O]
         dlam = dLp.sum((0, 1))

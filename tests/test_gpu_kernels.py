@@ -265,9 +265,17 @@ def test_hyena_se(K, G, halo):
         _close(h.grad, hr.grad, what="se dhalo")
 
 
-@pytest.mark.parametrize("K,G,L", [(128, 16, 400), (32, 16, 130), (128, 4, 256), (128, 32, 200), (100, 16, 333)])
+@pytest.fixture(params=[True, False], ids=["streaming", "per_tile"])
+def mr_bwd_variant(request):
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.set_mr_backward_variant(request.param)
+    yield request.param
+    cuda_ops.set_mr_backward_variant(True)
+
+
+@pytest.mark.parametrize("K,G,L", [(128, 16, 400), (32, 16, 130), (128, 4, 256), (128, 32, 200), (100, 16, 333), (128, 16, 2100)])
 @pytest.mark.parametrize("halo", [False, True])
-def test_hyena_mr(K, G, L, halo):
+def test_hyena_mr(K, G, L, halo, mr_bwd_variant):
     torch.manual_seed(12)
     B, D = 2, 256
     feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
@@ -289,8 +297,17 @@ def test_hyena_mr(K, G, L, halo):
         _close(h.grad, hh.grad, what="mr dhalo")
 
 
-@pytest.mark.parametrize("L,O,state", [(512, 16, False), (300, 8, False), (384, 16, True)])
-def test_hyena_li(L, O, state):
+@pytest.fixture(params=[None, 512], ids=["chunk_auto", "chunk_512"])
+def li_chunk(request):
+    """Chunk length of the scan: the automatic choice (128 at these sizes) and the 512 that the 7B shapes select."""
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.LI_CHUNK_OVERRIDE = request.param
+    yield request.param
+    cuda_ops.LI_CHUNK_OVERRIDE = None
+
+
+@pytest.mark.parametrize("L,O,state", [(512, 16, False), (300, 8, False), (384, 16, True), (1300, 16, True)])
+def test_hyena_li(L, O, state, li_chunk):
     torch.manual_seed(13)
     B, D = 2, 128
     feat = (torch.randn(B, L, 3 * D, device=DEV) * 0.7).to(BF).requires_grad_()
