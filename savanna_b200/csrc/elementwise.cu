@@ -632,6 +632,121 @@ quantize_fp8_delayed_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q,
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
 }
 
+// ------------------------------------------------------------------------------------ producers with fp8 output
+// The scale of a delayed-scaling site is known before its tensor exists, so the kernel that produces the tensor can
+// emit the e4m3 bytes for the next GEMM directly (and collect the amax for later calls) instead of writing bf16 that a
+// quantiser re-reads.  Ring protocol as in quantize_fp8_delayed_kernel.
+__device__ __forceinline__ float delayed_scale(float* hist, int slots, int cur, float* scale_inv, float fmax) {
+  const int nxt = cur + 1 == slots ? 0 : cur + 1;
+  float a = 0.f;
+  for (int j = 0; j < slots; ++j) {
+    if (j == cur || j == nxt) continue;
+    const float h = hist[j];
+    if (h > a && h < 3.0e38f) a = h;
+  }
+  if (!(a > 0.f)) a = fmax;
+  if (blockIdx.x == 0 && threadIdx.x == 0) { scale_inv[0] = a / fmax; hist[nxt] = 0.f; }
+  return fmax / a;
+}
+
+// RMSNorm whose output goes out as e4m3 (no bf16 copy): q = sat(w * x * a * scale)
+template <int VPT>
+__global__ void __launch_bounds__(512, VPT == 1 ? 4 : 2)
+rmsnorm_fwd_fp8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, uint8_t* __restrict__ q,
+                       float* __restrict__ a_out, int T, int D, float eps, int form, float* __restrict__ hist, int slots,
+                       int cur, float* __restrict__ scale_inv) {
+  __shared__ float red[2][32];
+  const float scale = delayed_scale(hist, slots, cur, scale_inv, 448.f);
+  const int nv = D >> 3;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  uint4 wv[VPT], xn[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * blockDim.x;
+    wv[v] = i < nv ? reinterpret_cast<const uint4*>(w)[i] : make_uint4(0, 0, 0, 0);
+    xn[v] = make_uint4(0, 0, 0, 0);
+  }
+  size_t row = blockIdx.x;
+  if (row < (size_t)T) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int i = threadIdx.x + v * blockDim.x;
+      if (i < nv) xn[v] = reinterpret_cast<const uint4*>(x + row * D)[i];
+    }
+  }
+  float m = 0.f;
+  int it = 0;
+  for (; row < (size_t)T; row += gridDim.x, ++it) {
+    uint4 xc[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) xc[v] = xn[v];
+    const size_t nxt = row + gridDim.x;
+    if (nxt < (size_t)T) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        if (i < nv) xn[v] = reinterpret_cast<const uint4*>(x + nxt * D)[i];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float f[8]; unpack8(xc[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+    ss = warp_sum(ss);
+    float* rr = red[it & 1];
+    if (lane == 0) rr[wid] = ss;
+    __syncthreads();
+    float tot = lane < nw ? rr[lane] : 0.f;
+    tot = warp_sum(tot);
+    const float mean = tot / D;
+    const float a = form == 0 ? rsqrtf(mean + eps) : 1.f / (sqrtf(mean) + eps);
+    if (threadIdx.x == 0) a_out[row] = a;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int i = threadIdx.x + v * blockDim.x;
+      if (i < nv) {
+        float f[8], g[8]; unpack8(xc[v], f); unpack8(wv[v], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // the value the un-fused path would have stored as bf16
+          f[j] = __bfloat162float(__float2bfloat16_rn(f[j] * a * g[j]));
+          m = fmaxf(m, fabsf(f[j]));
+        }
+        reinterpret_cast<uint2*>(q + row * D)[i] = quant8(f, scale, 0);
+      }
+    }
+  }
+  m = warp_max(m);
+  if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
+}
+
+// gated activation with e4m3 output: q [T, F] = sat(act(a) * b * scale) for ab [T, 2F] = [a | b]
+__global__ void __launch_bounds__(256)
+glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t T, int F, int act, float* __restrict__ hist,
+                   int slots, int cur, float* __restrict__ scale_inv) {
+  const float scale = delayed_scale(hist, slots, cur, scale_inv, 448.f);
+  const int nvF = F >> 3;
+  const size_t total = T * nvF;
+  float m = 0.f;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / nvF; const int i = idx - row * nvF;
+    const uint4* r = reinterpret_cast<const uint4*>(ab + row * 2 * F);
+    float a[8], b[8], o[8];
+    unpack8(r[i], a); unpack8(r[nvF + i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j]));
+      m = fmaxf(m, fabsf(o[j]));
+    }
+    reinterpret_cast<uint2*>(q + row * F)[i] = quant8(o, scale, 0);
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
+}
+
 static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
@@ -795,5 +910,33 @@ extern "C" int sb_quantize_fp8_delayed(const void* x, void* q, float* hist, int 
   const size_t n8 = (size_t)n / 8, n16 = n8 / 2;
   const int grid = grid_for((n16 + 1) / 2 + 1, 256, 148 * 8);
   quantize_fp8_delayed_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (uint8_t*)q, n16, n8, hist, slots, cur, scale_inv, fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// RMSNorm with e4m3 output under delayed scaling (ring protocol of sb_quantize_fp8_delayed); a_out as in sb_rmsnorm_fwd.
+extern "C" int sb_rmsnorm_fwd_fp8(const void* x, const void* w, void* q, float* a_out, int T, int D, float eps, int form,
+                                  float* hist, int slots, int cur, float* scale_inv, cudaStream_t st) {
+  if ((D % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if (T == 0) return 0;
+  const int nv = D / 8;
+  const int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
+  const int vpt = (nv + threads - 1) / threads;
+  const int grid = T < 148 * 4 ? T : 148 * 4;
+#define LAUNCH(V) rmsnorm_fwd_fp8_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (uint8_t*)q, a_out, T, D, eps, form, hist, slots, cur, scale_inv)
+  if (vpt <= 1) LAUNCH(1);
+  else if (vpt <= 2) LAUNCH(2);
+  else if (vpt <= 4) LAUNCH(4);
+  else return -3;
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Gated activation with e4m3 output under delayed scaling.
+extern "C" int sb_glu_fwd_fp8(const void* ab, void* q, long long T, int F, int act, float* hist, int slots, int cur,
+                              float* scale_inv, cudaStream_t st) {
+  if ((F % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if (T == 0) return 0;
+  glu_fwd_fp8_kernel<<<grid_for((size_t)T * (F / 8), 256), 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist,
+                                                                        slots, cur, scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

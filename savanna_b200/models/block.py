@@ -80,8 +80,14 @@ class ParallelBlock(nn.Module):
         if no_drop and not self.postnorm and not self.outer_mlp_norm:
             # residual and bias additions ride in the epilogues of the out-projection and w3 GEMMs; the norms hand the
             # residual branch through so that its gradient is added inside their backward kernels
-            u, residual = _norm_and_residual(self.input_layernorm, x) if self.prenorm else (x, x)
-            a, _ = self.mixer(u, positions, residual)
+            if self.prenorm:
+                a, _ = self.mixer(x, positions, None, pre_norm=self.input_layernorm)
+            else:
+                a, _ = self.mixer(x, positions, x)
+            if self.pre_mlp_norm and isinstance(self.mlp, (ParallelGLU, ParallelSequenceMixer)):
+                y, _ = (self.mlp(a, None, pre_norm=self.pre_mlp_layernorm) if isinstance(self.mlp, ParallelGLU)
+                        else self.mlp(a, positions, None, pre_norm=self.pre_mlp_layernorm))
+                return y
             u, a_res = _norm_and_residual(self.pre_mlp_layernorm, a) if self.pre_mlp_norm else (a, a)
             y, _ = self._mlp(u, positions, a_res)
             return y

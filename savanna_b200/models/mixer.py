@@ -98,10 +98,14 @@ class ParallelSequenceMixer(nn.Module):
         self.dense = RowParallelLinear(D, D, bias=True, input_is_parallel=True, init_method=output_layer_init_method,
                                        skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device, fp8=fp8_out)
 
-    def forward(self, x: torch.Tensor, positions: torch.Tensor, residual: Optional[torch.Tensor] = None):
+    def forward(self, x: torch.Tensor, positions: torch.Tensor, residual: Optional[torch.Tensor] = None, pre_norm=None):
         """Returns (output, out-projection bias to be added by the caller).  With `residual` the
-        out-projection adds bias and residual itself and the bias slot is None."""
-        proj, _ = self.dense_projection(x)
+        out-projection adds bias and residual itself and the bias slot is None.  With `pre_norm` (the block's input
+        norm) x is the un-normalised stream: the norm is fused with the in-projection and x becomes the residual."""
+        if pre_norm is not None:
+            proj, _, residual = self.dense_projection.forward_normed(x, pre_norm)
+        else:
+            proj, _ = self.dense_projection(x)
         if self.operator_type in HYENA_OPS:
             cp = state.get_context_parallel_world_size() if self.cfg.use_cp_hyena else 1
             if cp > 1:

@@ -81,15 +81,24 @@ class ParallelGLU(nn.Module):
     def w2_weight(self):
         return self.w12[self.ffn_local:]
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, pre_norm=None):
+        """With `pre_norm` (the block's pre-MLP norm) x is the un-normalised stream: the norm is applied here so that
+        it can be fused with the w1|w2 projection, and x itself becomes the residual."""
+        tp = state.get_model_parallel_world_size()
+        if pre_norm is not None:
+            gain = getattr(pre_norm, "gain", None)
+            if gain is not None and tp == 1:
+                ab, residual = ops.norm_linear(x, gain, pre_norm.eps, pre_norm.form, self.w12, None, fp8=self.fp8)
+                return self.w3.forward_glu(ab, self.act, residual)
+            fn = getattr(pre_norm, "forward_with_residual", None)
+            x, residual = fn(x) if fn is not None else (pre_norm(x), x)
         if self.sequence_parallel:
             ab = ops.linear_allgather(x, self.w12, None, 1, fp8=self.fp8)
         else:
             from ..parallel import mappings
-            xin = mappings.copy_to_model_parallel_region(x) if state.get_model_parallel_world_size() > 1 else x
+            xin = mappings.copy_to_model_parallel_region(x) if tp > 1 else x
             ab = ops.linear(xin, self.w12, None, fp8=self.fp8)
-        h = ops.glu_act_packed(ab, self.act)
-        return self.w3(h, residual)
+        return self.w3.forward_glu(ab, self.act, residual)
 
 
 class ParallelMLP(nn.Module):

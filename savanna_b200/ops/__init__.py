@@ -57,6 +57,20 @@ def rmsnorm(x, weight, eps: float, form: str = "te"):
     return _co().rmsnorm(x, weight, eps, form) if _k(x) else ref.rmsnorm(x, weight, eps, form)
 
 
+def norm_linear(x, norm_weight, eps: float, form: str, w, bias=None, fp8: bool = False):
+    """(linear(rmsnorm(x)), x for the residual branch)."""
+    if _k(x):
+        return _co().norm_linear(x, norm_weight, eps, form, w, bias, fp8)
+    return linear(ref.rmsnorm(x, norm_weight, eps, form), w, bias, fp8), x
+
+
+def glu_linear(ab, act: str, w, bias=None, residual=None, fp8: bool = False):
+    """linear(act(a) * b) (+ bias) (+ residual) for the packed gate input ab = [a | b]."""
+    if _k(ab):
+        return _co().glu_linear(ab, act, w, bias, residual, fp8)
+    return linear(glu_act_packed(ab, act), w, bias, fp8, residual)
+
+
 def rmsnorm_residual(x, weight, eps: float, form: str = "te"):
     """(rmsnorm(x), x): the second value is x as it continues down the residual branch.  On the kernel path the
     gradient that comes back along that branch is added inside the norm's backward kernel."""

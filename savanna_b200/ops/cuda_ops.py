@@ -57,6 +57,8 @@ class _Sig:
     sb_quantize_fp8 = [P, P, P, P, LL, I, P]
     sb_quantize_fp8_delayed = [P, P, P, I, I, P, LL, I, P]
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
+    sb_rmsnorm_fwd_fp8 = [P, P, P, P, I, I, F, I, P, I, I, P, P]
+    sb_glu_fwd_fp8 = [P, P, LL, I, I, P, I, I, P, P]
     sb_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd_blocks = [I]
     sb_glu_fwd = [P, P, LL, I, I, P]
@@ -267,15 +269,20 @@ def set_fp8_history(n: int) -> None:
     FP8_HISTORY = int(n)
 
 
+def _site(owner, role: str, device) -> Fp8History:
+    sites = owner.__dict__.setdefault("_fp8_sites", {})
+    h = sites.get(role)
+    if h is None or h.buf.numel() != FP8_HISTORY + 2 or h.buf.device != device:
+        h = sites[role] = Fp8History(device, FP8_HISTORY)
+    return h
+
+
 def quantize_fp8_site(x2: torch.Tensor, fmt: int, owner, role: str):
     """Quantise at a named site of `owner` (a parameter): delayed scaling from the site's amax history in one pass over
     the data; the first call at a site has no history and uses current scaling."""
     if FP8_HISTORY <= 0 or owner is None:
         return quantize_fp8(x2, fmt)
-    sites = owner.__dict__.setdefault("_fp8_sites", {})
-    h = sites.get(role)
-    if h is None or h.buf.numel() != FP8_HISTORY + 2 or h.buf.device != x2.device:
-        h = sites[role] = Fp8History(x2.device, FP8_HISTORY)
+    h = _site(owner, role, x2.device)
     lib = require()
     q = torch.empty(x2.shape, dtype=torch.uint8, device=x2.device)
     sinv = torch.empty(1, dtype=torch.float32, device=x2.device)
@@ -444,6 +451,135 @@ class _RMSNormResidual(torch.autograd.Function):
             return gres, None, None, None
         dx, dw = _rmsnorm_bwd(x2, w, a, gy, gres, eps, form)
         return dx.view(shape), dw, None, None
+
+
+def _fp8_backward_gemms(ctx_w, gy2, xq, sx, wq, sw, need_gx, need_gw):
+    """Shared by the fp8 projections: quantise the output gradient (e5m2), then dgrad and (in-place) wgrad."""
+    gq, sg = quantize_fp8_site(gy2, E5M2, ctx_w, "g")
+    gx = gw = None
+    if need_gx:
+        gx = torch.empty((gy2.shape[0], wq.shape[1]), dtype=bf16, device=gy2.device)
+        gemm_fp8(gq, wq, gx, sg, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sw)
+    if need_gw:
+        tgt = ctx_w.grad if getattr(ctx_w, "_fuse_grad_accum", False) else None
+        if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == ctx_w.shape:
+            gemm_fp8(gq, xq, tgt, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
+        else:
+            gw = torch.empty(ctx_w.shape, dtype=bf16, device=gy2.device)
+            gemm_fp8(gq, xq, gw, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
+    return gx, gw
+
+
+class _NormLinearFP8(torch.autograd.Function):
+    """(linear(rmsnorm(x)), x): the norm kernel emits the e4m3 operand of the projection directly (delayed scaling: the
+    scale is known before the tensor exists), so the normalised activations never exist in bf16; the second output
+    carries x down the residual branch and its gradient is added inside the norm's backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, wn, eps, form, w, bias):
+        lib = require()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        T, D = x2.shape
+        h = _site(w, "x", x.device)
+        wnc = wn.contiguous()
+        if not h.primed:
+            _, _, a, y = _rmsnorm_fwd(x, wn, eps, form)
+            xq, sx = quantize_fp8_site(y, E4M3, w, "x")
+        else:
+            xq = torch.empty((T, D), dtype=torch.uint8, device=x.device)
+            a = torch.empty(T, dtype=torch.float32, device=x.device)
+            sx = torch.empty(1, dtype=torch.float32, device=x.device)
+            _check(lib.sb_rmsnorm_fwd_fp8(x2.data_ptr(), wnc.data_ptr(), xq.data_ptr(), a.data_ptr(), T, D, eps, form,
+                                          h.buf.data_ptr(), h.buf.numel(), h.cur, sx.data_ptr(), _stream()), "rmsnorm_fwd_fp8")
+            _count()
+            h.cur = (h.cur + 1) % h.buf.numel()
+        wq, sw = _fp8_weight(w)
+        out = torch.empty((T, w.shape[0]), dtype=bf16, device=x.device)
+        gemm_fp8(xq, wq, out, sx, bias=bias, alpha2=sw)
+        ctx.save_for_backward(x2, wnc, a, xq, sx, wq, sw)
+        ctx.meta = (eps, form, x.shape, bias is not None)
+        ctx.wref = w
+        ctx.set_materialize_grads(False)
+        return out.view(*x.shape[:-1], w.shape[0]), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, gy, gres):
+        x2, wn, a, xq, sx, wq, sw = ctx.saved_tensors
+        eps, form, shape, has_bias = ctx.meta
+        if gy is None:
+            return gres, None, None, None, None, None
+        g2 = _rows(gy)
+        gxn, gw = _fp8_backward_gemms(ctx.wref, g2, xq, sx, wq, sw, True, ctx.needs_input_grad[4])
+        gb = colsum(g2).to(gy.dtype) if (has_bias and ctx.needs_input_grad[5]) else None
+        dx, dwn = _rmsnorm_bwd(x2, wn, a, gxn, gres, eps, form)
+        return dx.view(shape), dwn, None, None, gw, gb
+
+
+class _GluLinearFP8(torch.autograd.Function):
+    """linear(act(a) * b) (+ bias, + residual) for ab = [a | b]: the gate kernel emits the e4m3 operand directly."""
+
+    @staticmethod
+    def forward(ctx, ab, act, w, bias, residual):
+        lib = require()
+        ab2 = ab.reshape(-1, ab.shape[-1]).contiguous()
+        T, F2 = ab2.shape
+        Fh = F2 // 2
+        h = _site(w, "x", ab.device)
+        if not h.primed:
+            hb = torch.empty((T, Fh), dtype=bf16, device=ab.device)
+            _check(lib.sb_glu_fwd(ab2.data_ptr(), hb.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
+            _count()
+            xq, sx = quantize_fp8_site(hb, E4M3, w, "x")
+        else:
+            xq = torch.empty((T, Fh), dtype=torch.uint8, device=ab.device)
+            sx = torch.empty(1, dtype=torch.float32, device=ab.device)
+            _check(lib.sb_glu_fwd_fp8(ab2.data_ptr(), xq.data_ptr(), T, Fh, act, h.buf.data_ptr(), h.buf.numel(), h.cur,
+                                      sx.data_ptr(), _stream()), "glu_fwd_fp8")
+            _count()
+            h.cur = (h.cur + 1) % h.buf.numel()
+        wq, sw = _fp8_weight(w)
+        out = torch.empty((T, w.shape[0]), dtype=bf16, device=ab.device)
+        r2 = _rows(residual) if residual is not None else None
+        gemm_fp8(xq, wq, out, sx, bias=bias, residual=r2, alpha2=sw)
+        ctx.save_for_backward(ab2, xq, sx, wq, sw)
+        ctx.meta = (act, ab.shape, bias is not None, residual is not None)
+        ctx.wref = w
+        return out.view(*ab.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        lib = require()
+        ab2, xq, sx, wq, sw = ctx.saved_tensors
+        act, shape, has_bias, has_res = ctx.meta
+        g2 = _rows(gy)
+        gh, gw = _fp8_backward_gemms(ctx.wref, g2, xq, sx, wq, sw, True, ctx.needs_input_grad[2])
+        gb = colsum(g2).to(gy.dtype) if (has_bias and ctx.needs_input_grad[3]) else None
+        T, F2 = ab2.shape
+        dab = torch.empty_like(ab2)
+        _check(lib.sb_glu_bwd(ab2.data_ptr(), gh.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
+        _count()
+        gr = gy if (has_res and ctx.needs_input_grad[4]) else None
+        return dab.view(shape), None, gw, gb, gr
+
+
+def _fp8_fusable(x, w, *others) -> bool:
+    return (FP8_HISTORY > 0 and _is_bf16(x, w, *others) and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0
+            and x.shape[-1] % 16 == 0)
+
+
+def norm_linear(x, norm_weight, eps, form, w, bias, fp8):
+    """(linear(rmsnorm(x)), x).  With fp8 projections and delayed scaling the norm emits the fp8 operand itself."""
+    if fp8 and _fp8_fusable(x, w, norm_weight, bias) and 64 <= x.shape[-1] <= 16384:
+        return _NormLinearFP8.apply(x, norm_weight, float(eps), 0 if form == "te" else 1, w, bias)
+    y, res = rmsnorm_residual(x, norm_weight, eps, form)
+    return linear(y, w, bias, fp8), res
+
+
+def glu_linear(ab, act, w, bias, residual, fp8):
+    """linear(act(a) * b) + bias + residual for ab = [a | b]."""
+    if fp8 and act in _ACT and _fp8_fusable(ab, w, bias, residual) and (ab.shape[-1] // 2) % 16 == 0:
+        return _GluLinearFP8.apply(ab, _ACT[act], w, bias, residual)
+    return linear(glu_act_packed(ab, act), w, bias, fp8, residual)
 
 
 def rmsnorm_residual(x, weight, eps, form="te"):

@@ -91,6 +91,20 @@ class ColumnParallelLinear(nn.Module):
             y = mappings.gather_from_model_parallel_region(y)
         return y, (self.bias if self.skip_bias_add else None)
 
+    def forward_normed(self, x: torch.Tensor, norm: nn.Module):
+        """Projection of norm(x).  Returns (output, bias-or-None, x for the residual branch).  On one tensor-parallel
+        rank an RMSNorm and the projection go through one fused op (ops.norm_linear): with fp8 projections the norm
+        kernel writes the fp8 operand itself, and the residual branch's gradient is added in the norm's backward."""
+        gain = getattr(norm, "gain", None)
+        if gain is not None and state.get_model_parallel_world_size() == 1 and not self.gather_output:
+            bias = None if self.skip_bias_add else self.bias
+            y, res = ops.norm_linear(x, gain, norm.eps, norm.form, self.weight, bias, fp8=self.fp8)
+            return y, (self.bias if self.skip_bias_add else None), res
+        fn = getattr(norm, "forward_with_residual", None)
+        u, res = fn(x) if fn is not None else (norm(x), x)
+        y, b = self.forward(u)
+        return y, b, res
+
 
 class RowParallelLinear(nn.Module):
     """Y = X A^T with A [out, in] split along `in`; partial products are summed over the group."""
@@ -136,3 +150,10 @@ class RowParallelLinear(nn.Module):
         if self.bias is not None:
             y = y + self.bias
         return y, None
+
+    def forward_glu(self, ab: torch.Tensor, act: str, residual: Optional[torch.Tensor] = None):
+        """Projection of the gated activation act(a) * b for ab = [a | b]; on one tensor-parallel rank the gate and
+        the projection are one fused op (with fp8 projections the gate kernel writes the fp8 operand)."""
+        if state.get_model_parallel_world_size() == 1 and self.input_is_parallel and (residual is not None or not self.skip_bias_add):
+            return ops.glu_linear(ab, act, self.weight, self.bias, residual, fp8=self.fp8), None
+        return self.forward(ops.glu_act_packed(ab, act), residual)

@@ -503,6 +503,46 @@ def test_linear_fp8_autograd():
     _rel(w.grad, wr.grad, 8e-2, "fp8 linear dw")
 
 
+def test_fused_fp8_producers_match_unfused():
+    """RMSNorm -> fp8 projection and gate -> fp8 projection with the producing kernel writing the fp8 operand: from the
+    second call at a site on (the first call has no amax history) outputs and gradients equal those of the separate
+    norm / gate, quantise and GEMM kernels, which see the same scale."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(60)
+    T, D, N, Fh = 384, 512, 768, 640
+    wn = (1 + 0.1 * torch.randn(D, device=DEV)).to(BF)
+    w0 = (torch.randn(N, D, device=DEV) * 0.05).to(BF)
+    w3_0 = (torch.randn(D, Fh, device=DEV) * 0.05).to(BF)
+    b3_0 = torch.randn(D, device=DEV, dtype=BF)
+    results = []
+    for fused in (True, False):
+        w, w3, b3 = (torch.nn.Parameter(t.clone()) for t in (w0, w3_0, b3_0))
+        wnp = torch.nn.Parameter(wn.clone())
+        outs = None
+        for call in range(3):
+            torch.manual_seed(100 + call)
+            x = torch.randn(2, T // 2, D, device=DEV, dtype=BF, requires_grad=True)
+            ab = torch.randn(2, T // 2, 2 * Fh, device=DEV, dtype=BF, requires_grad=True)
+            res = torch.randn(2, T // 2, D, device=DEV, dtype=BF, requires_grad=True)
+            for p in (w, w3, b3, wnp):
+                p.grad = None
+            if fused:
+                y, r = cuda_ops.norm_linear(x, wnp, 1e-6, "te", w, None, True)
+                z = cuda_ops.glu_linear(ab, "silu", w3, b3, res, True)
+            else:
+                u, r = cuda_ops.rmsnorm_residual(x, wnp, 1e-6, "te")
+                y = cuda_ops.linear(u, w, None, True)
+                z = cuda_ops.linear(cuda_ops.glu_act_packed(ab, "silu"), w3, b3, True, res)
+            g1, g2, g3 = torch.randn_like(y), torch.randn_like(z), torch.randn_like(r)
+            ((y.float() * g1.float()).sum() + (z.float() * g2.float()).sum() + (r.float() * g3.float()).sum()).backward()
+            outs = [t.detach().float().clone() for t in (y, z, x.grad, ab.grad, res.grad, w.grad, w3.grad, b3.grad, wnp.grad)]
+        results.append(outs)
+        _status_ok()
+    names = ["y", "z", "dx", "dab", "dres", "dw", "dw3", "db3", "dwn"]
+    for name, a, b in zip(names, *results):
+        _rel(a, b, 2e-3, f"fused vs unfused {name}")
+
+
 def test_fp8_training_tracks_bf16():
     """Same tiny model, same data: the loss trace with fp8 projections stays close to the bf16 one."""
     import os
