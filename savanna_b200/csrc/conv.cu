@@ -79,6 +79,7 @@ __global__ void dwconv_fwd_kernel(const bf16* __restrict__ x, const bf16* __rest
     }
   }
   const int t1 = min(t0 + TL, L);
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
 #pragma unroll
     for (int j = 0; j < K - 1; ++j)
@@ -191,6 +192,7 @@ __global__ void se_fwd_kernel(const bf16* __restrict__ feat, const bf16* __restr
     }
   }
   const int t1 = min(t0 + TL, L);
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
 #pragma unroll
     for (int j = 0; j < K - 1; ++j)

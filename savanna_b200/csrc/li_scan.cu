@@ -52,7 +52,7 @@ li_local_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam,
   for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); s[o] = 0.f; }
   const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
   const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
-#pragma unroll 4
+#pragma unroll 8
   for (int t = t0; t < t1; ++t, f += 3 * d.D) {
     const float u = b2f(f[1]) * b2f(f[2]);
 #pragma unroll
@@ -74,12 +74,21 @@ __global__ void li_prefix_kernel(float* __restrict__ S, const float* __restrict_
   const float step = __expf(ll * d.TC);
   float carry = state_in ? state_in[idx] : 0.f;
   float* p = S + (size_t)b * d.NC * per_b + r;
-  for (int n = 0; n < d.NC; ++n) {
-    const float loc = p[(size_t)n * per_b];
-    p[(size_t)n * per_b] = carry;
-    const int len = min(d.TC, d.L - n * d.TC);
-    const float st = len == d.TC ? step : __expf(ll * len);
-    carry = st * carry + loc;
+  // the chunk states are independent loads: fetch eight ahead, then run the serial carry over them
+  for (int n0 = 0; n0 < d.NC; n0 += 8) {
+    float loc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) loc[j] = n0 + j < d.NC ? p[(size_t)(n0 + j) * per_b] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j;
+      if (n < d.NC) {
+        p[(size_t)n * per_b] = carry;
+        const int len = min(d.TC, d.L - n * d.TC);
+        const float st = len == d.TC ? step : __expf(ll * len);
+        carry = st * carry + loc[j];
+      }
+    }
   }
   if (state_out) state_out[idx] = carry;
 }
@@ -101,7 +110,7 @@ li_apply_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam,
   const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
   const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
   bf16* zo = z + ((size_t)b * d.L + t0) * d.D + ch;
-#pragma unroll 4
+#pragma unroll 8
   for (int t = t0; t < t1; ++t, f += 3 * d.D, zo += d.D) {
     const float x1 = b2f(f[0]);
     const float u = b2f(f[1]) * b2f(f[2]);
@@ -130,7 +139,7 @@ li_bwd_local_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, 
   const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
   const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
   const bf16* g = dz + ((size_t)b * d.L + t0) * d.D + ch;
-#pragma unroll 2
+#pragma unroll 4
   for (int t = t0; t < t1; ++t, f += 3 * d.D, g += d.D) {
     const float u = b2f(f[1]) * b2f(f[2]);
     const float dy = b2f(*g) * b2f(f[0]);
@@ -169,24 +178,45 @@ __global__ void li_bwd_prefix_kernel(float* __restrict__ S, float* __restrict__ 
   const float ll = loglam[r];
   const size_t base = (size_t)b * d.NC * per_b + r;
   float cs = state_in ? state_in[idx] : 0.f, cw = 0.f;
-  for (int n = 0; n < d.NC; ++n) {
-    const size_t o = base + (size_t)n * per_b;
-    const float ls = S[o], lw = W[o];
-    S[o] = cs; W[o] = cw;
-    const int len = min(d.TC, d.L - n * d.TC);
-    const float st = __expf(ll * len);
-    const float stm1 = __expf(ll * (len - 1));
-    cw = st * cw + len * stm1 * cs + lw;
-    cs = st * cs + ls;
+  const float st_full = __expf(ll * d.TC), stm1_full = __expf(ll * (d.TC - 1));
+  // independent loads of eight chunks ahead of the serial carries (forward for S and W, backward for A)
+  for (int n0 = 0; n0 < d.NC; n0 += 8) {
+    float ls[8], lw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const size_t o = base + (size_t)(n0 + j) * per_b;
+      ls[j] = n0 + j < d.NC ? S[o] : 0.f;
+      lw[j] = n0 + j < d.NC ? W[o] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j;
+      if (n < d.NC) {
+        const size_t o = base + (size_t)n * per_b;
+        S[o] = cs; W[o] = cw;
+        const int len = min(d.TC, d.L - n * d.TC);
+        const float st = len == d.TC ? st_full : __expf(ll * len);
+        const float stm1 = len == d.TC ? stm1_full : __expf(ll * (len - 1));
+        cw = st * cw + len * stm1 * cs + lw[j];
+        cs = st * cs + ls[j];
+      }
+    }
   }
   if (w_end) w_end[idx] = cw;
   float ca = dstate_out ? dstate_out[idx] : 0.f;
-  for (int n = d.NC - 1; n >= 0; --n) {
-    const size_t o = base + (size_t)n * per_b;
-    const float la = A[o];
-    A[o] = ca;
-    const int len = min(d.TC, d.L - n * d.TC);
-    ca = __expf(ll * len) * ca + la;
+  for (int n0 = d.NC - 1; n0 >= 0; n0 -= 8) {
+    float la[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) la[j] = n0 - j >= 0 ? A[base + (size_t)(n0 - j) * per_b] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 - j;
+      if (n >= 0) {
+        A[base + (size_t)n * per_b] = ca;
+        const int len = min(d.TC, d.L - n * d.TC);
+        ca = (len == d.TC ? st_full : __expf(ll * len)) * ca + la[j];
+      }
+    }
   }
   if (dstate_in) dstate_in[idx] = __expf(ll) * ca;
 }
@@ -214,7 +244,7 @@ li_bwd_apply_fwd_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
   const bf16* f = feat + ((size_t)b * d.L + t0) * 3 * d.D + 3 * ch;
   const bf16* g = dz + ((size_t)b * d.L + t0) * d.D + ch;
   bf16* o1 = dx1 + ((size_t)b * d.L + t0) * d.D + ch;
-#pragma unroll 2
+#pragma unroll 4
   for (int t = t0; t < t1; ++t, f += 3 * d.D, g += d.D, o1 += d.D) {
     const float x1 = b2f(f[0]);
     const float u = b2f(f[1]) * b2f(f[2]);
@@ -259,7 +289,7 @@ li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
   const bf16* g = dz + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
   const bf16* i1 = dx1 + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
   bf16* df = dfeat + ((size_t)b * d.L + (t1 - 1)) * 3 * d.D + 3 * ch;
-#pragma unroll 4
+#pragma unroll 8
   for (int t = t1 - 1; t >= t0; --t, f -= 3 * d.D, g -= d.D, i1 -= d.D, df -= 3 * d.D) {
     const float x1 = b2f(f[0]), x2 = b2f(f[1]), v = b2f(f[2]);
     const float dy = b2f(*g) * x1;
