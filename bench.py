@@ -274,7 +274,8 @@ def main():
         res = {"value": tokens_per_step / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "loss": float(loss),
                "parallelism": par,
                "clocks": clocks, "gpu_launches": launches, "cfg": cfg, "e2e": None,
-               "zero_path": ("fused peer-memory kernels" if getattr(trainer.optimizer, "fused", None) is not None
+               "zero_path": (("fused peer-memory kernels" + (" (NVLS multimem)" if getattr(trainer.optimizer.fused, "nvls", False) else ""))
+                             if getattr(trainer.optimizer, "fused", None) is not None
                              else ("nccl" if world > 1 else "single rank"))}
         if with_e2e:
             hit = host_iter()

@@ -72,10 +72,22 @@ zero_rs_kernel(PeerPtrs grads, int world, int me, size_t lo8, size_t n8, bf16* _
   }
 }
 
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void mm_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                 "f"(__uint_as_float(v.w)) : "memory");
+}
+
 __global__ void __launch_bounds__(512)
 zero_adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, const bf16* __restrict__ grad,
-                 PeerPtrsW params, int world, int me, size_t lo8, size_t n8, float lr, float b1, float b2, float eps,
-                 float wd, float bc1, float bc2, int adamw, const float* __restrict__ scale_ptr) {
+                 PeerPtrsW params, void* mc_params, int world, int me, size_t lo8, size_t n8, float lr, float b1, float b2,
+                 float eps, float wd, float bc1, float bc2, int adamw, const float* __restrict__ scale_ptr) {
   const float scale = scale_ptr[0];
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
@@ -112,18 +124,69 @@ zero_adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
     __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(w[2 * j], w[2 * j + 1]);
+    if (mc_params) {
+      mm_st_16(reinterpret_cast<uint4*>(mc_params) + lo8 + i, o);        // one store, replicated by the switch
+    } else {
 #pragma unroll
-    for (int r = 0; r < ZMAX; ++r)
-      if (r < world) {
-        const int dst = (me + r) % world;
-        reinterpret_cast<uint4*>(params.p[dst])[lo8 + i] = o;
-      }
+      for (int r = 0; r < ZMAX; ++r)
+        if (r < world) {
+          const int dst = (me + r) % world;
+          reinterpret_cast<uint4*>(params.p[dst])[lo8 + i] = o;
+        }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- NVLS (multimem) variants
+// With the buffers bound to an NVLink multicast object the switch does the work: one multimem.ld_reduce returns the
+// sum of all ranks' gradients for 16 bytes (fp32 accumulation in the switch, so each rank pulls only its own shard
+// across NVLink instead of world-1 copies of it), and one multimem.st writes the updated parameters into every rank.
+__global__ void __launch_bounds__(512)
+zero_rs_mm_kernel(const uint4* __restrict__ mc_grad, size_t lo8, size_t n8, bf16* __restrict__ out,
+                  const float* __restrict__ norm_weight, float* __restrict__ sqnorm) {
+  __shared__ float red[32];
+  float local = 0.f;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 o = mm_ld_reduce_bf16x8(mc_grad + lo8 + i);
+    reinterpret_cast<uint4*>(out)[i] = o;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    add8(acc, o);
+    if (norm_weight) {
+      const float4 w0 = reinterpret_cast<const float4*>(norm_weight)[2 * i], w1 = reinterpret_cast<const float4*>(norm_weight)[2 * i + 1];
+      local += acc[0] * acc[0] * w0.x + acc[1] * acc[1] * w0.y + acc[2] * acc[2] * w0.z + acc[3] * acc[3] * w0.w +
+               acc[4] * acc[4] * w1.x + acc[5] * acc[5] * w1.y + acc[6] * acc[6] * w1.z + acc[7] * acc[7] * w1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local += acc[j] * acc[j];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) atomicAdd(sqnorm, t);
   }
 }
 
 }  // namespace sb
 
 using namespace sb;
+
+// NVLS reduce-scatter: mc_grad = multicast address of the flat gradient buffer (the same object on every rank).
+extern "C" int sb_zero_reduce_scatter_mm(const void* mc_grad, long long lo, long long n, void* out, const float* norm_weight,
+                                         float* sqnorm, cudaStream_t st) {
+  if (!mc_grad || (lo % 8) || (n % 8) || (reinterpret_cast<uintptr_t>(mc_grad) & 15)) return -1;
+  if (n == 0) return 0;
+  const size_t n8 = (size_t)n / 8;
+  size_t g = (n8 + 511) / 512;
+  if (g > 148 * 4) g = 148 * 4;
+  zero_rs_mm_kernel<<<(unsigned)g, 512, 0, st>>>((const uint4*)mc_grad, (size_t)lo / 8, n8, (bf16*)out, norm_weight, sqnorm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 // grads[r]: base address of rank r's flat bf16 gradient buffer as mapped in THIS process.  lo / n in elements,
 // both multiples of 8; `out` = own gradient buffer + lo.  sqnorm is accumulated into (zero it first).
@@ -141,9 +204,10 @@ extern "C" int sb_zero_reduce_scatter(const void* const* grads, int world, int m
 }
 
 // params[r]: base address of rank r's flat bf16 parameter buffer as mapped in this process.
-extern "C" int sb_zero_adam_allgather(float* master, float* m, float* v, const void* grad, void* const* params, int world,
-                                      int me, long long lo, long long n, float lr, float b1, float b2, float eps, float wd,
-                                      float bc1, float bc2, int adamw, const float* scale_ptr, cudaStream_t st) {
+// mc_params: multicast address of the flat parameter buffer (NVLS: one multimem.st per 16 bytes), or null (peer stores).
+extern "C" int sb_zero_adam_allgather(float* master, float* m, float* v, const void* grad, void* const* params, void* mc_params,
+                                      int world, int me, long long lo, long long n, float lr, float b1, float b2, float eps,
+                                      float wd, float bc1, float bc2, int adamw, const float* scale_ptr, cudaStream_t st) {
   if (world < 1 || world > ZMAX || (lo % 8) || (n % 8) || !scale_ptr) return -1;
   if (n == 0) return 0;
   PeerPtrsW pp;
@@ -151,7 +215,7 @@ extern "C" int sb_zero_adam_allgather(float* master, float* m, float* v, const v
   const size_t n8 = (size_t)n / 8;
   size_t g = (n8 + 511) / 512;
   if (g > 148 * 4) g = 148 * 4;
-  zero_adam_kernel<<<(unsigned)g, 512, 0, st>>>(master, m, v, (const bf16*)grad, pp, world, me, (size_t)lo / 8, n8, lr, b1, b2,
+  zero_adam_kernel<<<(unsigned)g, 512, 0, st>>>(master, m, v, (const bf16*)grad, pp, mc_params, world, me, (size_t)lo / 8, n8, lr, b1, b2,
                                                eps, wd, bc1, bc2, adamw, scale_ptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

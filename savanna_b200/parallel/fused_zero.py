@@ -10,7 +10,8 @@ The flat bf16 gradient and parameter buffers of every rank are allocated in symm
     barrier (stream-ordered)                         all parameter stores have landed before the next forward
 
 (csrc/zero_fused.cu).  Barriers are tiny NCCL all-reduces on the compute stream, so the kernels themselves
-never wait on a peer.  fp32 flat groups (filter parameters, a few MB) stay on the NCCL path.
+never wait on a peer.  When the symmetric buffers carry an NVLink multicast mapping (`use_nvls`), the reduce-scatter
+reads the in-switch sum with multimem.ld_reduce and the parameter all-gather is one multimem.st per 16 bytes.  fp32 flat groups (filter parameters, a few MB) stay on the NCCL path.
 Reference behaviour replaced: DeepSpeed stage-1 reduce-scatter, fused Adam and all-gather
 (savanna/training.py:1329-1337, 1391-1400, 1497).
 """
@@ -50,7 +51,7 @@ class SymmAllocator:
 
 
 class FusedZeroStep:
-    def __init__(self, opt, allocator: SymmAllocator):
+    def __init__(self, opt, allocator: SymmAllocator, use_nvls: bool = True):
         from ..ops import cuda_ops
         self.lib = cuda_ops.require()
         self.cuda_ops = cuda_ops
@@ -58,7 +59,9 @@ class FusedZeroStep:
         self.lib.sb_zero_reduce_scatter.restype = I
         self.lib.sb_zero_reduce_scatter.argtypes = [P, I, I, LL, LL, P, P, P, P]
         self.lib.sb_zero_adam_allgather.restype = I
-        self.lib.sb_zero_adam_allgather.argtypes = [P, P, P, P, P, I, I, LL, LL, F, F, F, F, F, F, F, I, P, P]
+        self.lib.sb_zero_adam_allgather.argtypes = [P, P, P, P, P, P, I, I, LL, LL, F, F, F, F, F, F, F, I, P, P]
+        self.lib.sb_zero_reduce_scatter_mm.restype = I
+        self.lib.sb_zero_reduce_scatter_mm.argtypes = [P, LL, LL, P, P, P, P]
         self.world, self.rank = opt.world, opt.rank
         self.handles = {}
         for g in opt.groups:
@@ -68,7 +71,11 @@ class FusedZeroStep:
             hp = allocator.rendezvous(g.flat_param)
             gp = (ctypes.c_void_p * self.world)(*[int(p) for p in hg.buffer_ptrs])
             pp = (ctypes.c_void_p * self.world)(*[int(p) for p in hp.buffer_ptrs])
-            self.handles[id(g)] = (hg, hp, gp, pp)
+            # NVLS: the buffers' multicast addresses (0 when the fabric offers none)
+            mcg = int(getattr(hg, "multicast_ptr", 0) or 0) if use_nvls else 0
+            mcp = int(getattr(hp, "multicast_ptr", 0) or 0) if use_nvls else 0
+            self.handles[id(g)] = (hg, hp, gp, pp, mcg, mcp)
+        self.nvls = bool(self.handles) and all(h[4] and h[5] for h in self.handles.values())
         dev = opt.groups[0].flat_param.device
         self._token = torch.zeros(1, device=dev)
         self._sq = torch.zeros((), dtype=torch.float32, device=dev)
@@ -90,12 +97,15 @@ class FusedZeroStep:
                 self._sq += self.cuda_ops.sq_norm(s, g.norm_weight) if s.is_cuda else (s.float() ** 2).sum()
                 shards.append(s)
                 continue
-            _, _, gp, _ = h
+            gp, mcg = h[2], h[4]
             lo = g.rank * g.shard
             out = g.shard_slice(g.flat_grad)
-            rc = self.lib.sb_zero_reduce_scatter(gp, self.world, self.rank, lo, g.shard, out.data_ptr(),
-                                                 None if g.norm_weight is None else g.norm_weight.data_ptr(),
-                                                 self._sq.data_ptr(), st)
+            nw = None if g.norm_weight is None else g.norm_weight.data_ptr()
+            if self.nvls:
+                rc = self.lib.sb_zero_reduce_scatter_mm(mcg, lo, g.shard, out.data_ptr(), nw, self._sq.data_ptr(), st)
+            else:
+                rc = self.lib.sb_zero_reduce_scatter(gp, self.world, self.rank, lo, g.shard, out.data_ptr(), nw,
+                                                     self._sq.data_ptr(), st)
             if rc != 0:
                 raise RuntimeError(f"zero_reduce_scatter failed ({rc})")
             self.cuda_ops._count()
@@ -124,9 +134,10 @@ class FusedZeroStep:
                               opt.step_count, opt.adamw, coef, None if g.master_is_view else g.shard_slice(g.flat_param))
                 opt._all_gather(g)
                 continue
-            _, _, _, pp = h
+            pp, mcp = h[3], h[5]
             rc = self.lib.sb_zero_adam_allgather(g.master.data_ptr(), g.exp_avg.data_ptr(), g.exp_avg_sq.data_ptr(),
-                                                 s.data_ptr(), pp, self.world, self.rank, g.rank * g.shard, g.shard,
+                                                 s.data_ptr(), pp, mcp if self.nvls else None, self.world, self.rank,
+                                                 g.rank * g.shard, g.shard,
                                                  g.hyper["lr"], b1, b2, opt.eps, g.hyper["weight_decay"], bc1, bc2,
                                                  int(opt.adamw), coef.data_ptr(), st)
             if rc != 0:
@@ -144,7 +155,7 @@ def make_allocator(group) -> Optional[SymmAllocator]:
         return None
 
 
-def attach(opt, allocator: Optional[SymmAllocator]) -> bool:
+def attach(opt, allocator: Optional[SymmAllocator], use_nvls: bool = True) -> bool:
     """Switch `opt.step` to the fused path.  Every rank must reach the same decision: the outcome of the
     rendezvous is agreed on with an all-reduce, and a failure anywhere keeps everyone on the NCCL path."""
     ok = 1
@@ -153,15 +164,18 @@ def attach(opt, allocator: Optional[SymmAllocator]) -> bool:
         ok = 0
     else:
         try:
-            fused = FusedZeroStep(opt, allocator)
+            fused = FusedZeroStep(opt, allocator, use_nvls)
         except Exception as exc:  # noqa: BLE001
             print(f"[rank {dist.get_rank()}] fused ZeRO set-up failed: {exc}", flush=True)
             ok = 0
-    flag = torch.tensor([ok], device=opt.groups[0].flat_param.device, dtype=torch.int32)
+    nv = 1 if (fused is not None and fused.nvls) else 0
+    flag = torch.tensor([ok, nv], device=opt.groups[0].flat_param.device, dtype=torch.int32)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=opt.group)
-    if int(flag.item()) == 1:
+    if int(flag[0].item()) == 1:
+        fused.nvls = bool(int(flag[1].item()))           # multimem only if every rank has the multicast mapping
         opt.fused = fused
-        print_rank_0(" > ZeRO-1 step: fused peer-memory kernels (reduce-scatter + Adam + all-gather)")
+        print_rank_0(" > ZeRO-1 step: fused peer-memory kernels (reduce-scatter + Adam + all-gather)"
+                     + (", NVLS multimem.ld_reduce / multimem.st" if fused.nvls else ", plain peer loads / stores"))
         return True
     print_rank_0(" > ZeRO-1 step: NCCL reduce-scatter / all-gather path")
     return False

@@ -151,7 +151,7 @@ class Trainer:
                 group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
                 comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator)
             if use_symm:
-                fused_zero.attach(optimizer, allocator)
+                fused_zero.attach(optimizer, allocator, use_nvls=bool(cfg.use_nvls))
         else:
             from .optimizers import build_generic_optimizer
             optimizer = build_generic_optimizer(otype, groups, cfg, p)

@@ -60,7 +60,7 @@ def _spawn(fn, world, args=()):
     assert not errs, "\n".join(f"[rank {r}]\n{t}" for r, t in errs)
 
 
-def _w_fused_zero(rank, world):
+def _w_fused_zero(rank, world, use_nvls=False):
     import torch.distributed as dist
     from savanna_b200.parallel import fused_zero, state
     from savanna_b200.parallel.zero import ZeroOptimizer
@@ -79,7 +79,9 @@ def _w_fused_zero(rank, world):
     alloc = fused_zero.make_allocator(state.get_sequence_data_parallel_group())
     assert alloc is not None
     pa, oa = make(alloc)
-    assert fused_zero.attach(oa, alloc), "fused path did not come up"
+    assert fused_zero.attach(oa, alloc, use_nvls=use_nvls), "fused path did not come up"
+    if use_nvls and not oa.fused.nvls:
+        print("no NVLink multicast mapping on this box: the multimem variant was not exercised", flush=True)
     pb, ob = make(None)
     for step in range(3):
         g = torch.Generator(device=dev).manual_seed(100 * step + rank)
@@ -105,6 +107,13 @@ def _w_fused_zero(rank, world):
 @needs2
 def test_fused_zero_matches_nccl():
     _spawn(_w_fused_zero, 2)
+
+
+@needs2
+def test_fused_zero_nvls_multimem_matches_nccl():
+    """Same step with the NVLS kernels (multimem.ld_reduce reduce-scatter, multimem.st all-gather) where the symmetric
+    buffers have a multicast mapping; falls back to plain peer access (and says so) where they do not."""
+    _spawn_args(_w_fused_zero, 2, True)
 
 
 def _w_dp_train(rank, world):
