@@ -747,6 +747,33 @@ glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t 
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
 }
 
+// gate backward with e5m2 output: dab [T, 2F] = (dh * b * act'(a) | dh * act(a)) as fp8 for the w1|w2 gradient GEMMs
+__global__ void __launch_bounds__(256)
+glu_bwd_fp8_kernel(const bf16* __restrict__ ab, const bf16* __restrict__ dh, uint8_t* __restrict__ dq, size_t T, int F,
+                   int act, float* __restrict__ hist, int slots, int cur, float* __restrict__ scale_inv) {
+  const float scale = delayed_scale(hist, slots, cur, scale_inv, 57344.f);
+  const int nvF = F >> 3;
+  const size_t total = T * nvF;
+  float m = 0.f;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / nvF; const int i = idx - row * nvF;
+    const uint4* r = reinterpret_cast<const uint4*>(ab + row * 2 * F);
+    float a[8], b[8], g[8], da[8], db[8];
+    unpack8(r[i], a); unpack8(r[nvF + i], b);
+    unpack8(reinterpret_cast<const uint4*>(dh + row * F)[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      da[j] = __bfloat162float(__float2bfloat16_rn(g[j] * b[j] * act_grad(a[j], act)));
+      db[j] = __bfloat162float(__float2bfloat16_rn(g[j] * act_fwd(a[j], act)));
+      m = fmaxf(m, fmaxf(fabsf(da[j]), fabsf(db[j])));
+    }
+    uint2* o = reinterpret_cast<uint2*>(dq + row * 2 * F);
+    o[i] = quant8(da, scale, 1); o[nvF + i] = quant8(db, scale, 1);
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
+}
+
 static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
@@ -938,5 +965,15 @@ extern "C" int sb_glu_fwd_fp8(const void* ab, void* q, long long T, int F, int a
   if (T == 0) return 0;
   glu_fwd_fp8_kernel<<<grid_for((size_t)T * (F / 8), 256), 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist,
                                                                         slots, cur, scale_inv);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Gate backward with e5m2 output under delayed scaling (the gradient operand of the w1|w2 dgrad / wgrad GEMMs).
+extern "C" int sb_glu_bwd_fp8(const void* ab, const void* dh, void* dq, long long T, int F, int act, float* hist, int slots,
+                              int cur, float* scale_inv, cudaStream_t st) {
+  if ((F % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if (T == 0) return 0;
+  glu_bwd_fp8_kernel<<<grid_for((size_t)T * (F / 8), 256), 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F,
+                                                                        act, hist, slots, cur, scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

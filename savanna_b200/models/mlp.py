@@ -88,6 +88,10 @@ class ParallelGLU(nn.Module):
         if pre_norm is not None:
             gain = getattr(pre_norm, "gain", None)
             if gain is not None and tp == 1:
+                w3 = self.w3
+                if w3.input_is_parallel and w3.fp8 == self.fp8:
+                    return ops.mlp_gated(x, gain, pre_norm.eps, pre_norm.form, self.w12, w3.weight, w3.bias, self.act,
+                                         fp8=self.fp8), None
                 ab, residual = ops.norm_linear(x, gain, pre_norm.eps, pre_norm.form, self.w12, None, fp8=self.fp8)
                 return self.w3.forward_glu(ab, self.act, residual)
             fn = getattr(pre_norm, "forward_with_residual", None)

@@ -71,6 +71,14 @@ def glu_linear(ab, act: str, w, bias=None, residual=None, fp8: bool = False):
     return linear(glu_act_packed(ab, act), w, bias, fp8, residual)
 
 
+def mlp_gated(x, norm_weight, eps: float, form: str, w12, w3, b3=None, act: str = "silu", fp8: bool = False):
+    """x + w3(act(a) * b) + b3 with [a | b] = w12(rmsnorm(x)) on one tensor-parallel rank."""
+    if _k(x):
+        return _co().mlp_gated(x, norm_weight, eps, form, w12, w3, b3, act, fp8)
+    ab = linear(ref.rmsnorm(x, norm_weight, eps, form), w12, None, fp8)
+    return linear(glu_act_packed(ab, act), w3, b3, fp8, x)
+
+
 def rmsnorm_residual(x, weight, eps: float, form: str = "te"):
     """(rmsnorm(x), x): the second value is x as it continues down the residual branch.  On the kernel path the
     gradient that comes back along that branch is added inside the norm's backward kernel."""

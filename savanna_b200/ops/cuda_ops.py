@@ -59,6 +59,7 @@ class _Sig:
     sb_rmsnorm_fwd = [P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_fwd_fp8 = [P, P, P, P, I, I, F, I, P, I, I, P, P]
     sb_glu_fwd_fp8 = [P, P, LL, I, I, P, I, I, P, P]
+    sb_glu_bwd_fp8 = [P, P, P, LL, I, I, P, I, I, P, P]
     sb_rmsnorm_bwd = [P, P, P, P, P, P, P, P, I, I, F, I, P]
     sb_rmsnorm_bwd_blocks = [I]
     sb_glu_fwd = [P, P, LL, I, I, P]
@@ -560,6 +561,104 @@ class _GluLinearFP8(torch.autograd.Function):
         _count()
         gr = gy if (has_res and ctx.needs_input_grad[4]) else None
         return dab.view(shape), None, gw, gb, gr
+
+
+class _MlpFP8(torch.autograd.Function):
+    """x + w3(act(a) * b) + b3 with [a | b] = w12(rmsnorm(x)): the whole gated MLP of a block as one autograd node, all
+    three GEMMs on fp8 operands.  Every fp8 operand is written by the kernel that produces the tensor (norm, gate, gate
+    backward), so neither the normalised input, nor the gated activation, nor the gradient of [a | b] exists in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, wn, eps, form, w12, w3, b3, act):
+        lib = require()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        T, D = x2.shape
+        F2 = w12.shape[0]
+        Fh = F2 // 2
+        dev = x.device
+        wnc = wn.contiguous()
+        hx, hh = _site(w12, "x", dev), _site(w3, "x", dev)
+        if not (hx.primed and hh.primed):
+            # first call: no amax history yet, take the separate kernels (they prime the sites)
+            _, _, a, y = _rmsnorm_fwd(x, wn, eps, form)
+            xq, sx = quantize_fp8_site(y, E4M3, w12, "x")
+        else:
+            xq = torch.empty((T, D), dtype=torch.uint8, device=dev)
+            a = torch.empty(T, dtype=torch.float32, device=dev)
+            sx = torch.empty(1, dtype=torch.float32, device=dev)
+            _check(lib.sb_rmsnorm_fwd_fp8(x2.data_ptr(), wnc.data_ptr(), xq.data_ptr(), a.data_ptr(), T, D, eps, form,
+                                          hx.buf.data_ptr(), hx.buf.numel(), hx.cur, sx.data_ptr(), _stream()), "rmsnorm_fwd_fp8")
+            _count()
+            hx.cur = (hx.cur + 1) % hx.buf.numel()
+        w12q, s12 = _fp8_weight(w12)
+        ab = torch.empty((T, F2), dtype=bf16, device=dev)
+        gemm_fp8(xq, w12q, ab, sx, alpha2=s12)
+        if not hh.primed:
+            hb = torch.empty((T, Fh), dtype=bf16, device=dev)
+            _check(lib.sb_glu_fwd(ab.data_ptr(), hb.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
+            _count()
+            hq, sh = quantize_fp8_site(hb, E4M3, w3, "x")
+        else:
+            hq = torch.empty((T, Fh), dtype=torch.uint8, device=dev)
+            sh = torch.empty(1, dtype=torch.float32, device=dev)
+            _check(lib.sb_glu_fwd_fp8(ab.data_ptr(), hq.data_ptr(), T, Fh, act, hh.buf.data_ptr(), hh.buf.numel(), hh.cur,
+                                      sh.data_ptr(), _stream()), "glu_fwd_fp8")
+            _count()
+            hh.cur = (hh.cur + 1) % hh.buf.numel()
+        w3q, s3 = _fp8_weight(w3)
+        out = torch.empty((T, w3.shape[0]), dtype=bf16, device=dev)
+        gemm_fp8(hq, w3q, out, sh, bias=b3, residual=x2, alpha2=s3)
+        ctx.save_for_backward(x2, wnc, a, xq, sx, w12q, s12, ab, hq, sh, w3q, s3)
+        ctx.meta = (eps, form, x.shape, act, b3 is not None)
+        ctx.w12, ctx.w3 = w12, w3
+        return out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        lib = require()
+        x2, wn, a, xq, sx, w12q, s12, ab, hq, sh, w3q, s3 = ctx.saved_tensors
+        eps, form, shape, act, has_b3 = ctx.meta
+        w12, w3 = ctx.w12, ctx.w3
+        g2 = _rows(gy)
+        T, F2 = ab.shape
+        dev = gy.device
+        gh, gw3 = _fp8_backward_gemms(w3, g2, hq, sh, w3q, s3, True, ctx.needs_input_grad[5])
+        gb3 = colsum(g2).to(gy.dtype) if (has_b3 and ctx.needs_input_grad[6]) else None
+        hg = _site(w12, "g", dev)
+        if not hg.primed:
+            dab = torch.empty_like(ab)
+            _check(lib.sb_glu_bwd(ab.data_ptr(), gh.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
+            _count()
+            dq, sd = quantize_fp8_site(dab, E5M2, w12, "g")
+        else:
+            dq = torch.empty((T, F2), dtype=torch.uint8, device=dev)
+            sd = torch.empty(1, dtype=torch.float32, device=dev)
+            _check(lib.sb_glu_bwd_fp8(ab.data_ptr(), gh.data_ptr(), dq.data_ptr(), T, F2 // 2, act, hg.buf.data_ptr(),
+                                      hg.buf.numel(), hg.cur, sd.data_ptr(), _stream()), "glu_bwd_fp8")
+            _count()
+            hg.cur = (hg.cur + 1) % hg.buf.numel()
+        gxn = torch.empty((T, x2.shape[1]), dtype=bf16, device=dev)
+        gemm_fp8(dq, w12q, gxn, sd, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=s12)
+        gw12 = None
+        if ctx.needs_input_grad[4]:
+            tgt = w12.grad if getattr(w12, "_fuse_grad_accum", False) else None
+            if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == w12.shape:
+                gemm_fp8(dq, xq, tgt, sd, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
+            else:
+                gw12 = torch.empty(w12.shape, dtype=bf16, device=dev)
+                gemm_fp8(dq, xq, gw12, sd, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
+        # the residual branch's gradient (gy itself) is added inside the norm's backward kernel
+        dx, dwn = _rmsnorm_bwd(x2, wn, a, gxn, g2, eps, form)
+        return dx.view(shape), dwn, None, None, gw12, gw3, gb3, None
+
+
+def mlp_gated(x, norm_weight, eps, form, w12, w3, b3, act, fp8):
+    """x + w3(act(a) * b) + b3, [a | b] = w12(rmsnorm(x)): one node on the fp8 path, the composed ops otherwise."""
+    if (fp8 and act in _ACT and _fp8_fusable(x, w12, norm_weight, b3) and _is_bf16(w3) and 64 <= x.shape[-1] <= 16384
+            and w3.shape[0] % 16 == 0 and w3.shape[1] % 16 == 0 and (w12.shape[0] // 2) % 16 == 0):
+        return _MlpFP8.apply(x, norm_weight, float(eps), 0 if form == "te" else 1, w12, w3, b3, _ACT[act])
+    ab, res = norm_linear(x, norm_weight, eps, form, w12, None, fp8)
+    return glu_linear(ab, act, w3, b3, res, fp8)
 
 
 def _fp8_fusable(x, w, *others) -> bool:

@@ -543,6 +543,39 @@ def test_fused_fp8_producers_match_unfused():
         _rel(a, b, 2e-3, f"fused vs unfused {name}")
 
 
+def test_mlp_fp8_single_node_matches_composed_ops():
+    """The whole gated MLP as one autograd node (fp8 operands written by the norm, gate and gate-backward kernels) against
+    the composition of the separate ops, from the third call on (amax histories primed on both sides)."""
+    from savanna_b200.ops import cuda_ops
+    torch.manual_seed(61)
+    T, D, Fh = 256, 512, 640
+    wn0 = (1 + 0.1 * torch.randn(D, device=DEV)).to(BF)
+    w12_0 = (torch.randn(2 * Fh, D, device=DEV) * 0.05).to(BF)
+    w3_0 = (torch.randn(D, Fh, device=DEV) * 0.05).to(BF)
+    b3_0 = torch.randn(D, device=DEV, dtype=BF)
+    results = []
+    for fused in (True, False):
+        wn, w12, w3, b3 = (torch.nn.Parameter(t.clone()) for t in (wn0, w12_0, w3_0, b3_0))
+        for call in range(3):
+            torch.manual_seed(200 + call)
+            x = torch.randn(2, T // 2, D, device=DEV, dtype=BF, requires_grad=True)
+            for p in (wn, w12, w3, b3):
+                p.grad = None
+            if fused:
+                y = cuda_ops.mlp_gated(x, wn, 1e-6, "te", w12, w3, b3, "silu", True)
+            else:
+                u, r = cuda_ops.rmsnorm_residual(x, wn, 1e-6, "te")
+                ab = cuda_ops.linear(u, w12, None, True)
+                y = cuda_ops.linear(cuda_ops.glu_act_packed(ab, "silu"), w3, b3, True, r)
+            g = torch.randn_like(y)
+            (y.float() * g.float()).sum().backward()
+            outs = [t.detach().float().clone() for t in (y, x.grad, wn.grad, w12.grad, w3.grad, b3.grad)]
+        results.append(outs)
+        _status_ok()
+    for name, a, b in zip(["y", "dx", "dwn", "dw12", "dw3", "db3"], *results):
+        _rel(a, b, 2e-3, f"mlp node vs composed {name}")
+
+
 def test_fp8_training_tracks_bf16():
     """Same tiny model, same data: the loss trace with fp8 projections stays close to the bf16 one."""
     import os
