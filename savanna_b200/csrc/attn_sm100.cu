@@ -773,7 +773,8 @@ extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* ou
 
 // Attention backward.  go/q/out [B, Lq, H, 128], k/v [B, Lk, H, 128] (bf16, strided as in the forward); lse and the
 // optional dlse [B, H, Lq] fp32; scratch: stats (2 * B * H * 64 * ceil(Lq / 64) floats) and dq_acc [B, Lq, H, 128] fp32
-// (zero on entry).  Results: dq (strided, bf16), dk and dv (contiguous [B, Lk, H, 128], bf16).  Three launches.
+// (the kernel adds into it: zero it before the first of the calls that share it).  Results: dq (strided, bf16; null =
+// leave the sum in dq_acc), dk and dv (contiguous [B, Lk, H, 128], bf16).  Three launches (two without dq).
 extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const void* v, const void* out, const float* lse,
                            const float* glse, float* stats, float* dq_acc, void* dq, void* dk, int B, int H, int Lq, int Lk,
                            void* dv, const long long* g_str, const long long* q_str, const long long* k_str,
@@ -824,7 +825,154 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   if (g_p_tmem) attn_bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
   else attn_bwd_kernel<false><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);
   const long long orows = (long long)B * Lq * H;
-  attn_dq_cast_kernel<<<(unsigned)((orows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, orows, H, Lq,
-                                                                               dq_str[0], dq_str[1], dq_str[2]);
+  // dq == null: the caller keeps accumulating into dq_acc over several calls (ring attention) and casts at the end
+  if (dq)
+    attn_dq_cast_kernel<<<(unsigned)((orows * 16 + 255) / 256), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, orows, H, Lq,
+                                                                                 dq_str[0], dq_str[1], dq_str[2]);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}
+
+// ------------------------------------------------------------------------------------ merging partial attention results
+// Ring attention computes, per query row, S partial results (o_s, lse_s) over disjoint key sets.  Their combination is
+//     lse = log sum_s exp(lse_s),   w_s = exp(lse_s - lse),   o = sum_s w_s o_s
+// and its backward  do_s = w_s do,  dlse_s = w_s (do . o_s - do . o).  One warp per (batch, row, head); partials are
+// addressed through element strides, so slices of larger attention outputs are read in place.
+namespace sb {
+namespace attn {
+constexpr int MERGE_MAX = 16;
+struct MergeArgs {
+  const __nv_bfloat16* o[MERGE_MAX];      // [B, L, H, 128] with strides (osb, osl, osh)
+  const float* lse[MERGE_MAX];            // [B, H, L] with strides (lsb, lsh, lsl)
+  long long osb[MERGE_MAX], osl[MERGE_MAX], osh[MERGE_MAX];
+  long long lsb[MERGE_MAX], lsh[MERGE_MAX], lsl[MERGE_MAX];
+  int S, B, L, H;
+};
+struct MergeGrads {
+  __nv_bfloat16* go[MERGE_MAX];           // contiguous [B, L, H, 128]
+  float* glse[MERGE_MAX];                 // contiguous [B, H, L]
+};
+
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&f)[4]) {
+  const uint2 q = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&f)[4]) {
+  uint2 q;
+  q.x = pack_bf16(f[0], f[1]); q.y = pack_bf16(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = q;
+}
+
+__global__ void __launch_bounds__(256)
+attn_merge_fwd_kernel(MergeArgs a, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)a.B * a.L * a.H) return;
+  const int h = int(w % a.H);
+  const long long bl = w / a.H;
+  const int l = int(bl % a.L), b = int(bl / a.L);
+  float ls[MERGE_MAX], m = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < MERGE_MAX; ++s)
+    if (s < a.S) { ls[s] = a.lse[s][b * a.lsb[s] + h * a.lsh[s] + l * a.lsl[s]]; m = fmaxf(m, ls[s]); }
+  float den = 0.f;
+#pragma unroll
+  for (int s = 0; s < MERGE_MAX; ++s)
+    if (s < a.S) den += __expf(ls[s] - m);
+  const float lse = m + __logf(den);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < MERGE_MAX; ++s)
+    if (s < a.S) {
+      const float wgt = __expf(ls[s] - lse);
+      float f[4];
+      ld4(a.o[s] + b * a.osb[s] + l * a.osl[s] + h * a.osh[s] + lane * 4, f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] += wgt * f[j];
+    }
+  st4(out + ((long long)(b * a.L + l) * a.H + h) * HD + lane * 4, acc);
+  if (lane == 0) lse_out[((long long)b * a.H + h) * a.L + l] = lse;
+}
+
+__global__ void __launch_bounds__(256)
+attn_merge_bwd_kernel(MergeArgs a, MergeGrads g, const __nv_bfloat16* __restrict__ out, const float* __restrict__ lse_out,
+                      const __nv_bfloat16* __restrict__ gout, long long g_sb, long long g_sl, long long g_sh) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)a.B * a.L * a.H) return;
+  const int h = int(w % a.H);
+  const long long bl = w / a.H;
+  const int l = int(bl % a.L), b = int(bl / a.L);
+  const long long row = ((long long)(b * a.L + l) * a.H + h) * HD + lane * 4;
+  const long long stat = ((long long)b * a.H + h) * a.L + l;
+  float go[4], o[4];
+  ld4(gout + b * g_sb + l * g_sl + h * g_sh + lane * 4, go);
+  ld4(out + row, o);
+  float dot_o = go[0] * o[0] + go[1] * o[1] + go[2] * o[2] + go[3] * o[3];
+#pragma unroll
+  for (int off = 16; off; off >>= 1) dot_o += __shfl_xor_sync(0xffffffffu, dot_o, off);
+  const float lse = lse_out[stat];
+#pragma unroll
+  for (int s = 0; s < MERGE_MAX; ++s)
+    if (s < a.S) {
+      const float wgt = __expf(a.lse[s][b * a.lsb[s] + h * a.lsh[s] + l * a.lsl[s]] - lse);
+      float f[4], d[4];
+      ld4(a.o[s] + b * a.osb[s] + l * a.osl[s] + h * a.osh[s] + lane * 4, f);
+      float dot = go[0] * f[0] + go[1] * f[1] + go[2] * f[2] + go[3] * f[3];
+#pragma unroll
+      for (int off = 16; off; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) d[j] = wgt * go[j];
+      st4(g.go[s] + row, d);
+      if (lane == 0) g.glse[s][stat] = wgt * (dot - dot_o);
+    }
+}
+}  // namespace attn
+}  // namespace sb
+
+// S partial results -> merged output (bf16, contiguous [B, L, H, 128]) and merged lse (contiguous [B, H, L]).
+// o_ptrs / lse_ptrs: S device pointers; o_str: S x 3 element strides (b, l, h); lse_str: S x 3 element strides (b, h, l).
+extern "C" int sb_attn_merge_fwd(const void* const* o_ptrs, const void* const* lse_ptrs, const long long* o_str,
+                                 const long long* lse_str, int S, int B, int L, int H, void* out, float* lse_out,
+                                 cudaStream_t st) {
+  using namespace sb::attn;
+  if (S < 1 || S > MERGE_MAX) return -1;
+  if ((long long)B * L * H == 0) return 0;
+  MergeArgs a{};
+  for (int s = 0; s < S; ++s) {
+    a.o[s] = (const __nv_bfloat16*)o_ptrs[s]; a.lse[s] = (const float*)lse_ptrs[s];
+    a.osb[s] = o_str[3 * s]; a.osl[s] = o_str[3 * s + 1]; a.osh[s] = o_str[3 * s + 2];
+    a.lsb[s] = lse_str[3 * s]; a.lsh[s] = lse_str[3 * s + 1]; a.lsl[s] = lse_str[3 * s + 2];
+    if ((reinterpret_cast<uintptr_t>(o_ptrs[s]) & 7) || (a.osb[s] % 4) || (a.osl[s] % 4) || (a.osh[s] % 4)) return -4;
+  }
+  a.S = S; a.B = B; a.L = L; a.H = H;
+  const long long rows = (long long)B * L * H;
+  attn_merge_fwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(a, (__nv_bfloat16*)out, lse_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Backward of the merge: go_ptrs[s] (bf16, contiguous [B, L, H, 128]) and glse_ptrs[s] (fp32, contiguous [B, H, L]).
+extern "C" int sb_attn_merge_bwd(const void* const* o_ptrs, const void* const* lse_ptrs, const long long* o_str,
+                                 const long long* lse_str, int S, int B, int L, int H, const void* out, const float* lse_out,
+                                 const void* gout, const long long* g_str, void* const* go_ptrs, void* const* glse_ptrs,
+                                 cudaStream_t st) {
+  using namespace sb::attn;
+  if (S < 1 || S > MERGE_MAX) return -1;
+  if ((long long)B * L * H == 0) return 0;
+  MergeArgs a{};
+  MergeGrads g{};
+  for (int s = 0; s < S; ++s) {
+    a.o[s] = (const __nv_bfloat16*)o_ptrs[s]; a.lse[s] = (const float*)lse_ptrs[s];
+    a.osb[s] = o_str[3 * s]; a.osl[s] = o_str[3 * s + 1]; a.osh[s] = o_str[3 * s + 2];
+    a.lsb[s] = lse_str[3 * s]; a.lsh[s] = lse_str[3 * s + 1]; a.lsl[s] = lse_str[3 * s + 2];
+    g.go[s] = (__nv_bfloat16*)go_ptrs[s]; g.glse[s] = (float*)glse_ptrs[s];
+    if ((reinterpret_cast<uintptr_t>(o_ptrs[s]) & 7) || (a.osb[s] % 4) || (a.osl[s] % 4) || (a.osh[s] % 4)) return -4;
+  }
+  if ((reinterpret_cast<uintptr_t>(gout) & 7) || (g_str[0] % 4) || (g_str[1] % 4) || (g_str[2] % 4)) return -4;
+  a.S = S; a.B = B; a.L = L; a.H = H;
+  const long long rows = (long long)B * L * H;
+  attn_merge_bwd_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(a, g, (const __nv_bfloat16*)out, lse_out,
+                                                                            (const __nv_bfloat16*)gout, g_str[0], g_str[1], g_str[2]);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -75,7 +75,25 @@ __global__ void halo_push_add_kernel(uint4* __restrict__ gx, const uint4* __rest
   }
 }
 
+// plain 16-byte copy (peer -> local when `src` is a peer mapping)
+__global__ void peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long n16) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace sb
+
+// Copy `bytes` (a multiple of 16, both addresses 16-byte aligned) with this framework's own kernel; `src` may be a
+// peer GPU's memory.  `max_blocks` bounds the grid so that the copy leaves SMs to a kernel running beside it.
+extern "C" int sb_peer_copy(void* dst, const void* src, long long bytes, int max_blocks, cudaStream_t st) {
+  if ((bytes % 16) || ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15)) return -1;
+  if (bytes == 0) return 0;
+  const long long n16 = bytes / 16;
+  long long g = (n16 + 255) / 256;
+  const long long cap = max_blocks > 0 ? max_blocks : 592;
+  if (g > cap) g = cap;
+  sb::peer_copy_kernel<<<(unsigned)g, 256, 0, st>>>((uint4*)dst, (const uint4*)src, n16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int sb_halo_pull(void* dst, const void* prev, const void* next, const void* own, int B, int H, int C, cudaStream_t st) {
   if (C % 8) return -1;

@@ -32,6 +32,10 @@ def _lib():
         lib.sb_attn_last_encode_result.argtypes = []
         lib.sb_attn_set_bwd_variant.restype = I
         lib.sb_attn_set_bwd_variant.argtypes = [I]
+        lib.sb_attn_merge_fwd.restype = I
+        lib.sb_attn_merge_fwd.argtypes = [P, P, P, P, I, I, I, I, P, P, P]
+        lib.sb_attn_merge_bwd.restype = I
+        lib.sb_attn_merge_bwd.argtypes = [P, P, P, P, I, I, I, I, P, P, P, P, P, P, P]
         _SIGS_SET = True
     return lib
 
@@ -76,24 +80,31 @@ def forward(q, k, v, causal: bool, scale: float):
     return out, lse
 
 
-def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None):
+def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_acc=None, dk=None, dv=None):
     """Gradients (dq, dk, dv) in bf16.  `glse` [B, H, Lq] is the gradient that arrived at the log-sum-exp output (the
-    merge step of ring attention differentiates through it); it enters as a shift of the row term delta."""
+    merge step of ring attention differentiates through it); it enters as a shift of the row term delta.
+    With `dq_acc` (fp32, contiguous [B, Lq, H, 128]) the query gradient is ADDED into that accumulator and no bf16 dq is
+    produced (returned as None): several calls over different key blocks share one accumulator.  `dk` / `dv` may be
+    given as contiguous [B, Lk, H, 128] bf16 destinations."""
     lib = _lib()
     B, Lq, H, _ = q.shape
     Lk = k.shape[1]
     go = go if _ok_layout(go) else go.contiguous()
-    dq_acc = torch.zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
+    shared = dq_acc is not None
+    if not shared:
+        dq_acc = torch.zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
     stats = torch.empty(2 * B * H * ((Lq + 63) // 64 * 64), dtype=torch.float32, device=q.device)
-    dq = torch.empty((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
-    dk = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
+    dq = None if shared else torch.empty((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
+    if dk is None:
+        dk = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
+    if dv is None:
+        dv = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     if glse is not None:
         glse = glse.contiguous().float()
     rc = lib.sb_attn_bwd(go.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                         cuda_ops._ptr(glse), stats.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                         cuda_ops._ptr(glse), stats.data_ptr(), dq_acc.data_ptr(), cuda_ops._ptr(dq), dk.data_ptr(),
                          B, H, Lq, Lk, dv.data_ptr(), _str3(go), _str3(q), _str3(k), _str3(v), _str3(out),
-                         _str3(dq), int(causal), float(scale), cuda_ops.status_word(q.device).data_ptr(),
+                         _str3(dq if dq is not None else out), int(causal), float(scale), cuda_ops.status_word(q.device).data_ptr(),
                          cuda_ops._stream())
     if rc != 0:
         raise RuntimeError(f"attention backward failed (code {rc}, encode {lib.sb_attn_last_encode_result()})")
@@ -125,3 +136,95 @@ def attention(q, k, v, causal, return_lse=False):
     if return_lse:
         return out, lse
     return out
+
+
+# ------------------------------------------------------------------------------------------ merging partial results
+MERGE_MAX = 16
+
+
+def _merge_args(os_, lses):
+    S = len(os_)
+    optr = (ctypes.c_void_p * S)(*[t.data_ptr() for t in os_])
+    lptr = (ctypes.c_void_p * S)(*[t.data_ptr() for t in lses])
+    ostr = (ctypes.c_longlong * (3 * S))(*[v for t in os_ for v in (t.stride(0), t.stride(1), t.stride(2))])
+    lstr = (ctypes.c_longlong * (3 * S))(*[v for t in lses for v in (t.stride(0), t.stride(1), t.stride(2))])
+    return optr, lptr, ostr, lstr
+
+
+def merge_supported(os_, lses) -> bool:
+    if not (1 <= len(os_) <= MERGE_MAX and len(os_) == len(lses)):
+        return False
+    shp = os_[0].shape
+    for o, l in zip(os_, lses):
+        if not (o.is_cuda and o.dtype == torch.bfloat16 and o.dim() == 4 and o.shape == shp and o.shape[-1] == 128
+                and o.stride(-1) == 1 and all(st % 4 == 0 for st in o.stride()[:3]) and o.data_ptr() % 8 == 0):
+            return False
+        if not (l.dtype == torch.float32 and l.shape == (shp[0], shp[2], shp[1])):
+            return False
+    return True
+
+
+def merge_forward(os_, lses):
+    """The merge without autograd: (o [B, L, H, 128] bf16, lse [B, H, L] fp32)."""
+    lib = _lib()
+    S = len(os_)
+    B, L, H, _ = os_[0].shape
+    out = torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
+    lse = torch.empty((B, H, L), dtype=torch.float32, device=os_[0].device)
+    optr, lptr, ostr, lstr = _merge_args(os_, lses)
+    rc = lib.sb_attn_merge_fwd(optr, lptr, ostr, lstr, S, B, L, H, out.data_ptr(), lse.data_ptr(), cuda_ops._stream())
+    if rc != 0:
+        raise RuntimeError(f"attention merge failed ({rc})")
+    cuda_ops._count()
+    return out, lse
+
+
+class _Merge(torch.autograd.Function):
+    """Combine partial attention results over disjoint key sets: o = sum_s exp(lse_s - lse) o_s, lse = logsumexp_s lse_s
+    (one kernel forward, one backward; csrc/attn_sm100.cu)."""
+
+    @staticmethod
+    def forward(ctx, S, *ts):
+        os_, lses = ts[:S], ts[S:]
+        lib = _lib()
+        B, L, H, _ = os_[0].shape
+        out = torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
+        lse = torch.empty((B, H, L), dtype=torch.float32, device=os_[0].device)
+        optr, lptr, ostr, lstr = _merge_args(os_, lses)
+        rc = lib.sb_attn_merge_fwd(optr, lptr, ostr, lstr, S, B, L, H, out.data_ptr(), lse.data_ptr(), cuda_ops._stream())
+        if rc != 0:
+            raise RuntimeError(f"attention merge failed ({rc})")
+        cuda_ops._count()
+        ctx.save_for_backward(out, lse, *ts)
+        ctx.S = S
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, gout, _glse):
+        S = ctx.S
+        saved = ctx.saved_tensors              # one access only (activation checkpointing unpacks on access)
+        out, lse = saved[:2]
+        ts = saved[2:]
+        os_, lses = ts[:S], ts[S:]
+        lib = _lib()
+        B, L, H, _ = out.shape
+        if gout.stride(-1) != 1 or any(st % 4 for st in gout.stride()[:3]) or gout.data_ptr() % 8:
+            gout = gout.contiguous()
+        gos = [torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=out.device) for _ in range(S)]
+        gls = [torch.empty((B, H, L), dtype=torch.float32, device=out.device) for _ in range(S)]
+        optr, lptr, ostr, lstr = _merge_args(os_, lses)
+        gstr = _LL3(gout.stride(0), gout.stride(1), gout.stride(2))
+        goptr = (ctypes.c_void_p * S)(*[t.data_ptr() for t in gos])
+        glptr = (ctypes.c_void_p * S)(*[t.data_ptr() for t in gls])
+        rc = lib.sb_attn_merge_bwd(optr, lptr, ostr, lstr, S, B, L, H, out.data_ptr(), lse.data_ptr(), gout.data_ptr(), gstr,
+                                   goptr, glptr, cuda_ops._stream())
+        if rc != 0:
+            raise RuntimeError(f"attention merge backward failed ({rc})")
+        cuda_ops._count()
+        return (None, *gos, *gls)
+
+
+def merge_partials(os_, lses):
+    """os_: list of [B, L, H, 128] bf16 partial outputs (views allowed), lses: list of [B, H, L] fp32 -> (o, lse)."""
+    return _Merge.apply(len(os_), *os_, *lses)

@@ -92,6 +92,11 @@ def setup_peer(group=None, ranks=None) -> bool:
         ws.lib.sb_halo_pull.argtypes = [P, P, P, P, I, I, I, P]
         ws.lib.sb_halo_push_add.restype = I
         ws.lib.sb_halo_push_add.argtypes = [P, P, P, P, I, I, I, I, P]
+        LL = ctypes.c_longlong
+        ws.lib.sb_peer_copy.restype = I
+        ws.lib.sb_peer_copy.argtypes = [P, P, LL, I, P]
+        ws.lib.sb_zero_reduce_scatter.restype = I
+        ws.lib.sb_zero_reduce_scatter.argtypes = [P, I, I, LL, LL, P, P, P, P]
     except Exception as exc:  # noqa: BLE001
         print(f"[rank {dist.get_rank()}] peer-memory halo set-up failed: {exc}", flush=True)
         ok = 0

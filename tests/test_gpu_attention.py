@@ -132,3 +132,32 @@ def test_model_training_own_attention_tracks_library_attention():
         attention_cuda.set_own_kernels(True)
     a, b = traces
     assert max(abs(x - y) for x, y in zip(a, b)) < 0.05, (a, b)
+
+
+def test_merge_partials_matches_pairwise_merge():
+    """Fused merge of partial attention results (and its backward) against the pairwise log-sum-exp merge in PyTorch,
+    with partials that are strided slices of larger tensors."""
+    from savanna_b200.ops import flash_sm100
+    from savanna_b200.parallel.ring_attention import _merge
+    torch.manual_seed(70)
+    B, L, H, S = 2, 96, 3, 5
+    big_o = [torch.randn(B, 2 * L, H, 128, device=DEV, dtype=BF, requires_grad=True) for _ in range(S)]
+    big_l = [(torch.randn(B, H, 2 * L, device=DEV) * 3).requires_grad_() for _ in range(S)]
+    os_ = [t[:, L:] if i % 2 else t[:, :L] for i, t in enumerate(big_o)]
+    ls_ = [t[..., L:] if i % 2 else t[..., :L] for i, t in enumerate(big_l)]
+    assert flash_sm100.merge_supported(os_, ls_)
+    out, lse = flash_sm100.merge_partials(os_, ls_)
+    g = torch.randn_like(out)
+    grads = torch.autograd.grad((out.float() * g.float()).sum(), big_o + big_l)
+    ro = [t.detach().float().requires_grad_() for t in big_o]
+    rl = [t.detach().clone().requires_grad_() for t in big_l]
+    oa = la = None
+    for i in range(S):
+        o_i = ro[i][:, L:] if i % 2 else ro[i][:, :L]
+        l_i = rl[i][..., L:] if i % 2 else rl[i][..., :L]
+        oa, la = _merge(oa, la, o_i, l_i)
+    rgrads = torch.autograd.grad((oa * g.float()).sum(), ro + rl)
+    _rel(out, oa, 1e-2, "merged output")
+    assert (lse - la).abs().max() < 1e-4
+    for i, (a, b) in enumerate(zip(grads, rgrads)):
+        _rel(a, b, 2e-2, f"merge grad {i}")

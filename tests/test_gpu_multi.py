@@ -232,8 +232,11 @@ def test_tensor_sequence_parallel_training_fused():
 
 
 # ------------------------------------------------------------------------------------------ context parallelism
-_CP_OVER = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True, "hidden_dropout": 0.0,
-            "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
+# 128-wide heads so that the tcgen05 attention kernels and the peer-memory ring are the ones that run
+_WIDE = {"hidden_size": 512, "num_attention_heads": 4, "num_groups_hyena": 512, "num_groups_hyena_medium": 32,
+         "num_groups_hyena_short": 32, "hidden_dropout": 0.0}
+_CP_OVER = dict(_WIDE, context_parallel_size=2, use_cp_hyena=True, use_cp_ring=True,
+                operator_config=["hyena_se", "ring", "hyena_mr", "hyena", "ring"], num_layers=5)
 
 
 def _cp_losses(world, over, n=4):
@@ -260,6 +263,8 @@ def _w_cp_train(rank, world, over, want):
     from savanna_b200.parallel import halo
     got = _cp_losses(world, over, len(want))
     assert halo._PEER_WS is not None, "the peer-memory halo exchange was not brought up"
+    from savanna_b200.parallel import ring_attention
+    assert ring_attention._SIDE, "the peer-memory ring attention did not run"
     cuda_ops.check_status()
     for a, b in zip(got, want):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
@@ -267,7 +272,7 @@ def _w_cp_train(rank, world, over, want):
 
 def _cp_reference():
     from savanna_b200.parallel import state
-    want = _cp_losses(1, {"hidden_dropout": 0.0, "operator_config": ["hyena_se", "hyena_mr", "hyena", "flash_v2"]})
+    want = _cp_losses(1, dict(_WIDE, operator_config=["hyena_se", "flash_v2", "hyena_mr", "hyena", "flash_v2"], num_layers=5))
     state.destroy_model_parallel()
     return want
 
