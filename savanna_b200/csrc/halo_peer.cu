@@ -80,7 +80,35 @@ __global__ void peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restric
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+// 2-D copy of `rows` rows of `row16` 16-byte vectors between pitched buffers (pitches in 16-byte units)
+__global__ void peer_copy_2d_kernel(uint4* __restrict__ dst, long long dst_pitch, const uint4* __restrict__ src,
+                                    long long src_pitch, int row16, long long rows) {
+  const long long total = rows * row16;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / row16;
+    const int c = int(i - r * row16);
+    dst[r * dst_pitch + c] = src[r * src_pitch + c];
+  }
+}
+
 }  // namespace sb
+
+// Pitched copy (all byte counts multiples of 16, addresses 16-byte aligned); `src` may be a peer GPU's memory.  The
+// context-parallel all-to-all is 2*cp of these per rank: every rank pulls its channel block of each sequence chunk
+// (or its sequence chunks of each channel block) straight into the final layout.
+extern "C" int sb_peer_copy_2d(void* dst, long long dst_pitch, const void* src, long long src_pitch, long long row_bytes,
+                               long long rows, int max_blocks, cudaStream_t st) {
+  if ((row_bytes % 16) || (dst_pitch % 16) || (src_pitch % 16) ||
+      ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15)) return -1;
+  if (rows == 0 || row_bytes == 0) return 0;
+  const long long total = rows * (row_bytes / 16);
+  long long g = (total + 255) / 256;
+  const long long cap = max_blocks > 0 ? max_blocks : 592;
+  if (g > cap) g = cap;
+  sb::peer_copy_2d_kernel<<<(unsigned)g, 256, 0, st>>>((uint4*)dst, dst_pitch / 16, (const uint4*)src, src_pitch / 16,
+                                                      (int)(row_bytes / 16), rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 // Copy `bytes` (a multiple of 16, both addresses 16-byte aligned) with this framework's own kernel; `src` may be a
 // peer GPU's memory.  `max_blocks` bounds the grid so that the copy leaves SMs to a kernel running beside it.

@@ -4,8 +4,10 @@
     full_to_split : the inverse
 
 This is the channel-last restatement of the reference's AllToAllSingleFunction
-(savanna/model/operators/hyena/distributed_a2a.py:45-168).  The collective itself is NCCL/gloo
-here; the fused CUDA long-convolution path pulls the peer slices itself.
+(savanna/model/operators/hyena/distributed_a2a.py:45-168).  Two forms: NCCL/gloo all_to_all_single with the
+permutes around it, and (CUDA bf16 with the context-parallel peer workspace up) a pull over NVSwitch peer memory: the
+tensor is staged once in a symmetric buffer and every rank copies its blocks from their owners straight into the final
+layout with this framework's pitched-copy kernel, zigzag addressing included.
 """
 from __future__ import annotations
 
@@ -63,17 +65,90 @@ def _full_to_split(x: torch.Tensor, zigzag: bool) -> torch.Tensor:
     return recv.permute(1, 2, 0, 3).reshape(B, l, cp * d).contiguous()
 
 
+# ------------------------------------------------------------------------------------------ peer-memory form
+def _peer_ws(x: torch.Tensor, zigzag: bool):
+    """The context-parallel peer workspace when this tensor can take the pull path (CUDA bf16, zigzag, 16-byte rows)."""
+    from . import halo
+    ws = halo._PEER_WS
+    if ws is None or not zigzag or not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 3:
+        return None
+    return ws if ws.world == state.get_context_parallel_world_size() else None
+
+
+def _pull(ws, dst, dst_pitch, src_ptr, src_off, src_pitch, row_bytes, rows):
+    rc = ws.lib.sb_peer_copy_2d(dst, dst_pitch, src_ptr + src_off, src_pitch, row_bytes, rows, 0,
+                                torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"sb_peer_copy_2d failed ({rc})")
+
+
+def _split_to_full_peer(ws, x: torch.Tensor) -> torch.Tensor:
+    """[B, l (zigzag shard), D] -> [B, l*cp (natural order), D/cp]: stage x in symmetric memory, one device barrier, then
+    pull this rank's channel block of every sequence chunk from its owner straight into its natural position."""
+    cp, me = ws.world, ws.rank
+    B, l, D = x.shape
+    d, c = D // cp, l // 2
+    stage, ptrs = ws.symm_buffer("a2a_s2f", x.numel())
+    stage.view(B, l, D).copy_(x)
+    ws.barrier()
+    full = torch.empty((B, cp * l, d), dtype=x.dtype, device=x.device)
+    for j in range(2 * cp):                               # natural chunk j lives on rank j (first half) or 2cp-1-j
+        owner, loc = (j, 0) if j < cp else (2 * cp - 1 - j, c)
+        for b in range(B):
+            _pull(ws, full[b, j * c].data_ptr(), d * 2, ptrs[owner], ((b * l + loc) * D + me * d) * 2, D * 2, d * 2, c)
+    ws.cuda_ops._count(2 * cp * B)
+    return full
+
+
+def _full_to_split_peer(ws, x: torch.Tensor) -> torch.Tensor:
+    """[B, L (natural order), d] -> [B, L/cp (zigzag shard), d*cp]: the inverse pull."""
+    cp, me = ws.world, ws.rank
+    B, L, d = x.shape
+    l = L // cp
+    c = l // 2
+    stage, ptrs = ws.symm_buffer("a2a_f2s", x.numel())
+    stage.view(B, L, d).copy_(x)
+    ws.barrier()
+    out = torch.empty((B, l, cp * d), dtype=x.dtype, device=x.device)
+    for r in range(cp):                                   # channel block r comes from rank r
+        for loc, j in ((0, me), (c, 2 * cp - 1 - me)):
+            for b in range(B):
+                _pull(ws, out[b, loc, r * d:].data_ptr(), cp * d * 2, ptrs[r], ((b * L + j * c) * d) * 2, d * 2, d * 2, c)
+    ws.cuda_ops._count(2 * cp * B)
+    return out
+
+
+def _peer_shapes_ok(x, direction, cp) -> bool:
+    if direction == "split_to_full":
+        B, l, D = x.shape
+        return D % cp == 0 and l % 2 == 0 and ((D // cp) * 2) % 16 == 0
+    B, L, d = x.shape
+    return L % (2 * cp) == 0 and (d * 2) % 16 == 0
+
+
 class AllToAllSingle(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, direction, zigzag):
         ctx.direction, ctx.zigzag = direction, zigzag
-        return _split_to_full(x, zigzag) if direction == "split_to_full" else _full_to_split(x, zigzag)
+        return _run(x, direction, zigzag)
 
     @staticmethod
     def backward(ctx, g):
-        g = g.contiguous()
-        out = _full_to_split(g, ctx.zigzag) if ctx.direction == "split_to_full" else _split_to_full(g, ctx.zigzag)
-        return out, None, None
+        inverse = "full_to_split" if ctx.direction == "split_to_full" else "split_to_full"
+        return _run(g.contiguous(), inverse, ctx.zigzag), None, None
+
+
+PEER_CALLS = 0        # number of all-to-alls that took the peer-memory pull path (tests read it)
+
+
+def _run(x, direction, zigzag):
+    global PEER_CALLS
+    ws = _peer_ws(x, zigzag)
+    if ws is not None and _peer_shapes_ok(x, direction, ws.world):
+        PEER_CALLS += 1
+        x = x.contiguous()
+        return _split_to_full_peer(ws, x) if direction == "split_to_full" else _full_to_split_peer(ws, x)
+    return _split_to_full(x, zigzag) if direction == "split_to_full" else _full_to_split(x, zigzag)
 
 
 def split_to_full(x, zigzag: bool = True):

@@ -95,6 +95,8 @@ def setup_peer(group=None, ranks=None) -> bool:
         LL = ctypes.c_longlong
         ws.lib.sb_peer_copy.restype = I
         ws.lib.sb_peer_copy.argtypes = [P, P, LL, I, P]
+        ws.lib.sb_peer_copy_2d.restype = I
+        ws.lib.sb_peer_copy_2d.argtypes = [P, LL, P, LL, LL, LL, I, P]
         ws.lib.sb_zero_reduce_scatter.restype = I
         ws.lib.sb_zero_reduce_scatter.argtypes = [P, I, I, LL, LL, P, P, P, P]
     except Exception as exc:  # noqa: BLE001

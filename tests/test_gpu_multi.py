@@ -265,6 +265,9 @@ def _w_cp_train(rank, world, over, want):
     assert halo._PEER_WS is not None, "the peer-memory halo exchange was not brought up"
     from savanna_b200.parallel import ring_attention
     assert ring_attention._SIDE, "the peer-memory ring attention did not run"
+    if over.get("cp_hyena_li_algo", "a2a") == "a2a":
+        from savanna_b200.parallel import a2a
+        assert a2a.PEER_CALLS > 0, "the peer-memory all-to-all did not run"
     cuda_ops.check_status()
     for a, b in zip(got, want):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
