@@ -90,12 +90,17 @@ def test_engine_config_has_zero_and_batch():
     assert cfg.ffn_size == 11264
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/configs"), reason="reference configs not mounted")
+# a checkout of the reference next to this repository (or SAVANNA_REFERENCE_DIR) provides its YAMLs
+REFERENCE = os.environ.get("SAVANNA_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "configs")), reason="reference configs not available")
 def test_reference_model_configs_load():
     """Every current Evo 2 model YAML of the reference parses with this schema."""
-    paths = glob.glob("/root/reference/configs/7b-context-ext/model_configs/*.yml") + \
-        glob.glob("/root/reference/configs/40b/model_configs/pretrain/*.yml") + \
-        glob.glob("/root/reference/configs/quickstart/*.yml") + glob.glob("/root/reference/configs/test/*.yml")
+    rc = os.path.join(REFERENCE, "configs")
+    paths = glob.glob(os.path.join(rc, "7b-context-ext/model_configs/*.yml")) + \
+        glob.glob(os.path.join(rc, "40b/model_configs/pretrain/*.yml")) + \
+        glob.glob(os.path.join(rc, "quickstart/*.yml")) + glob.glob(os.path.join(rc, "test/*.yml"))
     assert paths
     bad = []
     for p in paths:
