@@ -110,10 +110,47 @@ def build_batch(cfg, text: torch.Tensor, generator=None) -> Dict[str, torch.Tens
     return batch
 
 
+def build_batch_dpo(cfg, rows: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """Preference pairs (reference: training.py:637-724).  `rows` [B, n] float32 in the format written by
+    tools/preprocess_data_dpo.py: accept tokens, pad, reject tokens, pad, ref logprob accept, pad, ref logprob reject.
+    Returns 2B sequences (all accepted first, then all rejected) padded with eod to `seq_length`, next-token labels, a
+    loss mask without the eod padding, and the reference log-probabilities [2B]."""
+    if state.get_context_parallel_world_size() > 1:
+        raise ValueError("direct-preference batches do not support context parallelism")
+    tok = cfg.tokenizer
+    pad, eod = tok.pad, tok.eod
+    acc, rej, lp_a, lp_r = [], [], [], []
+    for row in rows:
+        pads = (row == pad).nonzero(as_tuple=True)[0]
+        if pads.numel() < 3:
+            raise ValueError("malformed preference row: fewer than three pad separators")
+        acc.append(row[: pads[0]].long())
+        rej.append(row[pads[0] + 1: pads[1]].long())
+        lp_a.append(row[pads[1] + 1])
+        lp_r.append(row[pads[2] + 1])
+    L = cfg.seq_length
+    seqs = acc + rej
+    if max(int(t.numel()) for t in seqs) > L + 1:
+        raise ValueError(f"a preference text is longer than seq_length + 1 = {L + 1}")
+    full = torch.full((len(seqs), L + 1), eod, dtype=torch.long, device=rows.device)
+    for i, t in enumerate(seqs):
+        full[i, : t.numel()] = t
+    tokens, labels = full[:, :-1].contiguous(), full[:, 1:].contiguous()
+    loss_mask, positions = ltor_masks_and_position_ids(tokens, eod, True, pad, cfg.pad_mask_loss)
+    return {"tokens": tokens, "labels": labels, "loss_mask": loss_mask, "positions": positions,
+            "ref_logps": torch.stack(lp_a + lp_r).float()}
+
+
 def get_batch(cfg, data_iterator, device) -> Dict[str, torch.Tensor]:
     """Fetch from the iterator on the data-reading rank, broadcast to tensor/context peers, build."""
     tp, cp = state.get_model_parallel_world_size(), state.get_context_parallel_world_size()
     data = next(data_iterator) if data_iterator is not None else None
+    if cfg.alignment_method == "dpo":
+        if tp == 1 and cp == 1:
+            rows = data["text"].to(device, non_blocking=True).float()
+        else:
+            rows = broadcast_data(["text"], data, torch.float32)["text"].float()
+        return build_batch_dpo(cfg, rows)
     if tp == 1 and cp == 1:
         text = data["text"].to(device, non_blocking=True).long()
     else:

@@ -165,6 +165,13 @@ class Trainer:
         labels, mask = b["labels"], b["loss_mask"]
         if cfg.to_upper == "upper":
             labels = batch_mod.to_upper_bytes(labels)
+        if cfg.alignment_method == "dpo":
+            # rows 0..B-1 are the accepted texts, B..2B-1 the rejected ones (train/batch.py:build_batch_dpo)
+            lp = losses.sequence_logps(logits, labels, mask)
+            B = lp.shape[0] // 2
+            ref = b["ref_logps"]
+            loss, _, _ = losses.dpo_loss(lp[:B], lp[B:], ref[:B], ref[B:], beta=cfg.dpo_beta)
+            return loss
         if cfg.pretraining_strategy == "OADM":
             return losses.oadm_loss(logits, labels, mask, None)
         if cfg.to_upper in ("weighted", "normalized_weighted"):
