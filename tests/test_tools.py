@@ -97,3 +97,19 @@ def test_generation_greedy_is_deterministic():
     a = generate(tr.model, cfg.tokenizer, ["ACGT", "GG"], maximum_tokens=5)
     b = generate(tr.model, cfg.tokenizer, ["ACGT", "GG"], maximum_tokens=5)
     assert [r["text"] for r in a] == [r["text"] for r in b] and all(r["length"] >= 5 for r in a)
+
+
+def test_convert_checkpoint_to_torch(tiny_ckpt, tmp_path):
+    from savanna_b200.tools.convert_checkpoint_to_torch import convert
+    tr, d = tiny_ckpt
+    plain = convert(d, str(tmp_path / "model.pt"))
+    assert os.path.exists(tmp_path / "model.pt")
+    for k, v in tr.model.state_dict().items():
+        assert torch.equal(plain[k], v.cpu()), k
+    named = convert(d, str(tmp_path / "standalone.pt"), strip_prefix=True)
+    assert "embedding.word_embeddings.weight" in named and "blocks.0.mixer.dense_projection.weight" in named
+    assert any(k.startswith("final_norm.") for k in named)
+    assert len(named) == len(plain)
+    fp32 = convert(d, str(tmp_path / "fp32.pt"), fp32=True)
+    k = "sequential.2.mixer.dense_projection.weight"
+    assert fp32[k].dtype == torch.float32 and torch.allclose(fp32[k], plain[k].float(), atol=1e-2)
