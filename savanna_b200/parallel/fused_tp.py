@@ -10,7 +10,7 @@ and run the plain GEMM.  Reference call sites replaced: savanna/mpu/mappings.py:
 savanna/mpu/layers.py:525-560 and :746-786 (NCCL all-gather / reduce-scatter next to cuBLAS GEMMs).
 
 Both entry points return None when the fused path does not apply (workspace not set up, tensor-parallel size 1,
-micro-batch > 1, shard not a multiple of 128 rows, non-bf16): the caller then runs the NCCL collective and the GEMM
+shard not a multiple of 128 rows, non-bf16; a micro-batch > 1 runs one sequence at a time): the caller then runs the NCCL collective and the GEMM
 separately.  Cross-GPU ordering uses stream-ordered device barriers (csrc/peer_barrier.cu, bounded waits); symmetric staging buffers are
 double-buffered so that a rank can stage its next operand while a peer still reads the previous one.
 """
@@ -268,14 +268,20 @@ class _LinearReduceScatter(torch.autograd.Function):
 
 
 def linear_allgather(x, w, bias, seq_dim):
-    if _WS is None or seq_dim != 1 or x.dim() != 3 or x.shape[0] != 1 or not _eligible(x, w, x.shape[1]):
+    if _WS is None or seq_dim != 1 or x.dim() != 3 or not _eligible(x, w, x.shape[1]):
         return None
-    return _LinearAllGather.apply(x, w, bias)
+    if x.shape[0] == 1:
+        return _LinearAllGather.apply(x, w, bias)
+    # the kernels take one sequence at a time (a rank's shard must be one block of rows): loop over the micro-batch
+    return torch.cat([_LinearAllGather.apply(x[b:b + 1], w, bias) for b in range(x.shape[0])], dim=0)
 
 
 def linear_reducescatter(x, w, seq_dim, bias=None, residual=None):
-    if _WS is None or seq_dim != 1 or x.dim() != 3 or x.shape[0] != 1:
+    if _WS is None or seq_dim != 1 or x.dim() != 3:
         return None
     if x.shape[1] % _WS.world or not _eligible(x, w, x.shape[1] // _WS.world):
         return None
-    return _LinearReduceScatter.apply(x, w, bias, residual)
+    if x.shape[0] == 1:
+        return _LinearReduceScatter.apply(x, w, bias, residual)
+    return torch.cat([_LinearReduceScatter.apply(x[b:b + 1], w, bias, None if residual is None else residual[b:b + 1])
+                      for b in range(x.shape[0])], dim=0)

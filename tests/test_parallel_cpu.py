@@ -217,3 +217,31 @@ def test_pipeline_parallel_equivalence():
     """Two pipeline stages (tied embedding on both ends) reproduce the single-process loss trace."""
     ref_losses = _reference_losses()
     run_distributed(_w_equiv, 2, {"pipe_parallel_size": 2, "gradient_accumulation_steps": 1}, ref_losses)
+
+
+def test_ring_block_plan_covers_the_causal_mask():
+    """The (query part, key part, causal) blocks of every ring step add up to exactly the causal mask between the local
+    zigzag query chunks and each rank's zigzag key chunks."""
+    import torch
+    from savanna_b200.parallel.ring_attention import _block_plan
+    cp, c = 4, 3                                   # 8 chunks of 3 positions
+    L = 2 * cp * c
+
+    def positions(rank):
+        return list(range(rank * c, (rank + 1) * c)) + list(range((2 * cp - 1 - rank) * c, (2 * cp - rank) * c))
+
+    def rows(part):
+        return {"lo": range(0, c), "hi": range(c, 2 * c), "all": range(0, 2 * c)}[part]
+    for me in range(cp):
+        for src in range(cp):
+            qpos, kpos = positions(me), positions(src)
+            want = torch.tensor([[int(kp <= qp) for kp in kpos] for qp in qpos])
+            got = torch.zeros_like(want)
+            for qp, kp, causal in _block_plan(me, src, True):
+                for i_local, i in enumerate(rows(qp)):
+                    for j_local, j in enumerate(rows(kp)):
+                        visible = (j_local <= i_local) if causal else True
+                        got[i, j] += int(visible)
+            assert torch.equal(got, want), (me, src, got, want)
+    # without causality a step is one dense block
+    assert _block_plan(1, 2, False) == [("all", "all", False)]
