@@ -113,3 +113,20 @@ def test_convert_checkpoint_to_torch(tiny_ckpt, tmp_path):
     fp32 = convert(d, str(tmp_path / "fp32.pt"), fp32=True)
     k = "sequential.2.mixer.dense_projection.weight"
     assert fp32[k].dtype == torch.float32 and torch.allclose(fp32[k], plain[k].float(), atol=1e-2)
+
+
+def test_load_for_inference_roundtrip(tiny_ckpt):
+    """A saved checkpoint rebuilds the model from its stored configs and reproduces the trainer's logits."""
+    from savanna_b200.inference.load import load_for_inference
+    from savanna_b200.parallel import state
+    tr, d = tiny_ckpt
+    tokens = acgt_batch(1, 64, 5)[:, :64]
+    tr.model.eval()
+    with torch.no_grad():
+        want = tr.model(tokens, torch.arange(64))
+    state.destroy_model_parallel()
+    model, tok, cfg = load_for_inference(os.path.dirname(d), config_files=[TINY])
+    with torch.no_grad():
+        got = model(tokens, torch.arange(64))
+    assert torch.allclose(got, want, atol=1e-5)
+    assert tok is not None and cfg.hidden_size == 256
