@@ -723,52 +723,68 @@ rmsnorm_fwd_fp8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, u
   if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
 }
 
-// gated activation with e4m3 output: q [T, F] = sat(act(a) * b * scale) for ab [T, 2F] = [a | b]
+// gated activation with e4m3 output: q [T, F] = sat(act(a) * b * scale) for ab [T, 2F] = [a | b]; F % 16 == 0, each
+// thread handles 16 columns per step (two 16-byte loads per operand, one 16-byte store)
 __global__ void __launch_bounds__(256)
 glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t T, int F, int act, float* __restrict__ hist,
                    int slots, int cur, float* __restrict__ scale_inv) {
   const float scale = delayed_scale(hist, slots, cur, scale_inv, 448.f);
-  const int nvF = F >> 3;
-  const size_t total = T * nvF;
+  const int nv = F >> 4;                          // 16-column groups per row
+  const size_t total = T * nv;
   float m = 0.f;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const size_t row = idx / nvF; const int i = idx - row * nvF;
-    const uint4* r = reinterpret_cast<const uint4*>(ab + row * 2 * F);
-    float a[8], b[8], o[8];
-    unpack8(r[i], a); unpack8(r[nvF + i], b);
+    const size_t row = idx / nv; const int i = idx - row * nv;
+    const uint4* ra = reinterpret_cast<const uint4*>(ab + row * 2 * F) + 2 * i;
+    const uint4* rb = reinterpret_cast<const uint4*>(ab + row * 2 * F + F) + 2 * i;
+    const uint4 a0 = ra[0], a1 = ra[1], b0 = rb[0], b1 = rb[1];
+    uint2 lo, hi;
+    {
+      float a[8], b[8], o[8];
+      unpack8(a0, a); unpack8(b0, b);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j]));
-      m = fmaxf(m, fabsf(o[j]));
+      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
+      lo = quant8(o, scale, 0);
+      unpack8(a1, a); unpack8(b1, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
+      hi = quant8(o, scale, 0);
     }
-    reinterpret_cast<uint2*>(q + row * F)[i] = quant8(o, scale, 0);
+    reinterpret_cast<uint4*>(q + row * F)[i] = make_uint4(lo.x, lo.y, hi.x, hi.y);
   }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
 }
 
-// gate backward with e5m2 output: dab [T, 2F] = (dh * b * act'(a) | dh * act(a)) as fp8 for the w1|w2 gradient GEMMs
+// gate backward with e5m2 output: dab [T, 2F] = (dh * b * act'(a) | dh * act(a)) as fp8 for the w1|w2 gradient GEMMs;
+// F % 16 == 0, 16 columns per thread and step
 __global__ void __launch_bounds__(256)
 glu_bwd_fp8_kernel(const bf16* __restrict__ ab, const bf16* __restrict__ dh, uint8_t* __restrict__ dq, size_t T, int F,
                    int act, float* __restrict__ hist, int slots, int cur, float* __restrict__ scale_inv) {
   const float scale = delayed_scale(hist, slots, cur, scale_inv, 57344.f);
-  const int nvF = F >> 3;
-  const size_t total = T * nvF;
+  const int nv = F >> 4;
+  const size_t total = T * nv;
   float m = 0.f;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const size_t row = idx / nvF; const int i = idx - row * nvF;
-    const uint4* r = reinterpret_cast<const uint4*>(ab + row * 2 * F);
-    float a[8], b[8], g[8], da[8], db[8];
-    unpack8(r[i], a); unpack8(r[nvF + i], b);
-    unpack8(reinterpret_cast<const uint4*>(dh + row * F)[i], g);
+    const size_t row = idx / nv; const int i = idx - row * nv;
+    const uint4* ra = reinterpret_cast<const uint4*>(ab + row * 2 * F) + 2 * i;
+    const uint4* rb = reinterpret_cast<const uint4*>(ab + row * 2 * F + F) + 2 * i;
+    const uint4* rg = reinterpret_cast<const uint4*>(dh + row * F) + 2 * i;
+    const uint4 av[2] = {ra[0], ra[1]}, bv[2] = {rb[0], rb[1]}, gv[2] = {rg[0], rg[1]};
+    uint2 qa[2], qb[2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      da[j] = __bfloat162float(__float2bfloat16_rn(g[j] * b[j] * act_grad(a[j], act)));
-      db[j] = __bfloat162float(__float2bfloat16_rn(g[j] * act_fwd(a[j], act)));
-      m = fmaxf(m, fmaxf(fabsf(da[j]), fabsf(db[j])));
+    for (int h = 0; h < 2; ++h) {
+      float a[8], b[8], g[8], da[8], db[8];
+      unpack8(av[h], a); unpack8(bv[h], b); unpack8(gv[h], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        da[j] = __bfloat162float(__float2bfloat16_rn(g[j] * b[j] * act_grad(a[j], act)));
+        db[j] = __bfloat162float(__float2bfloat16_rn(g[j] * act_fwd(a[j], act)));
+        m = fmaxf(m, fmaxf(fabsf(da[j]), fabsf(db[j])));
+      }
+      qa[h] = quant8(da, scale, 1); qb[h] = quant8(db, scale, 1);
     }
-    uint2* o = reinterpret_cast<uint2*>(dq + row * 2 * F);
-    o[i] = quant8(da, scale, 1); o[nvF + i] = quant8(db, scale, 1);
+    reinterpret_cast<uint4*>(dq + row * 2 * F)[i] = make_uint4(qa[0].x, qa[0].y, qa[1].x, qa[1].y);
+    reinterpret_cast<uint4*>(dq + row * 2 * F + F)[i] = make_uint4(qb[0].x, qb[0].y, qb[1].x, qb[1].y);
   }
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
@@ -961,9 +977,9 @@ extern "C" int sb_rmsnorm_fwd_fp8(const void* x, const void* w, void* q, float* 
 // Gated activation with e4m3 output under delayed scaling.
 extern "C" int sb_glu_fwd_fp8(const void* ab, void* q, long long T, int F, int act, float* hist, int slots, int cur,
                               float* scale_inv, cudaStream_t st) {
-  if ((F % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if ((F % 16) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (T == 0) return 0;
-  glu_fwd_fp8_kernel<<<grid_for((size_t)T * (F / 8), 256), 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist,
+  glu_fwd_fp8_kernel<<<grid_for((size_t)T * (F / 16), 256), 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist,
                                                                         slots, cur, scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -971,9 +987,9 @@ extern "C" int sb_glu_fwd_fp8(const void* ab, void* q, long long T, int F, int a
 // Gate backward with e5m2 output under delayed scaling (the gradient operand of the w1|w2 dgrad / wgrad GEMMs).
 extern "C" int sb_glu_bwd_fp8(const void* ab, const void* dh, void* dq, long long T, int F, int act, float* hist, int slots,
                               int cur, float* scale_inv, cudaStream_t st) {
-  if ((F % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
+  if ((F % 16) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (T == 0) return 0;
-  glu_bwd_fp8_kernel<<<grid_for((size_t)T * (F / 8), 256), 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F,
+  glu_bwd_fp8_kernel<<<grid_for((size_t)T * (F / 16), 256), 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F,
                                                                         act, hist, slots, cur, scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
