@@ -20,6 +20,7 @@ forward-pass logits validation; data cursor (`train_data_token_index`) and LR-sc
 from __future__ import annotations
 
 import glob
+import contextlib
 import os
 import random
 import re
@@ -164,9 +165,13 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
         os.makedirs(d, exist_ok=True)
     _barrier()
     files = {}
+    full = getattr(trainer.optimizer, "full_params", None)          # ZeRO-3: the gather is collective, all ranks enter
+    with (full() if full is not None else contextlib.nullcontext()):
+        module_sd = {k: v.detach().clone() for k, v in trainer.model.state_dict().items()} \
+            if (full is not None and zero_rank == 0) else (trainer.model.state_dict() if zero_rank == 0 else None)
     if zero_rank == 0:
         ms = {
-            "module": trainer.model.state_dict(),
+            "module": module_sd,
             "buffer_names": [n for n, _ in trainer.model.named_buffers()],
             "param_shapes": _param_shapes(trainer),
             "frozen_param_shapes": None,
@@ -288,7 +293,9 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
     dev = trainer.device
     ms = torch.load(path, map_location="cpu", weights_only=False)
     _check_args(cfg, ms.get("args"))
-    missing, unexpected = trainer.model.load_state_dict(ms["module"], strict=False)
+    full = getattr(trainer.optimizer, "full_params", None)          # ZeRO-3: load into whole parameters, re-shard after
+    with (full(writeback=True) if full is not None else contextlib.nullcontext()):
+        missing, unexpected = trainer.model.load_state_dict(ms["module"], strict=False)
     # buffers that are recomputed (rotary tables, filter time index) may be absent in foreign checkpoints
     missing = [k for k in missing if not k.endswith((".inv_freq", ".filter.t", ".decay"))]
     if cfg.checkpoint_strict_load and (missing or unexpected):

@@ -27,49 +27,67 @@ __device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
   for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(q[i]); acc[2 * i] += t.x; acc[2 * i + 1] += t.y; }
 }
 
-// n8 = number of 8-element vectors of the shard; `lo8` = shard offset in vectors inside every rank's buffer.
-__global__ void __launch_bounds__(512)
-zero_rs_kernel(PeerPtrs grads, int world, int me, size_t lo8, size_t n8, bf16* __restrict__ out,
-               const float* __restrict__ norm_weight, float* __restrict__ sqnorm) {
-  __shared__ float red[32];
-  float local = 0.f;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    uint4 v[ZMAX];
-#pragma unroll
-    for (int r = 0; r < ZMAX; ++r)
-      if (r < world) {
-        const int src = (me + r) % world;                      // start at the own copy, then walk the peers: spreads the load over links
-        v[r] = reinterpret_cast<const uint4*>(grads.p[src])[lo8 + i];
-      }
-#pragma unroll
-    for (int r = 0; r < ZMAX; ++r)
-      if (r < world) add8(acc, v[r]);
-    uint4 o;
-    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    reinterpret_cast<uint4*>(out)[i] = o;
-    if (norm_weight) {
-      const float4 w0 = reinterpret_cast<const float4*>(norm_weight)[2 * i], w1 = reinterpret_cast<const float4*>(norm_weight)[2 * i + 1];
-      local += acc[0] * acc[0] * w0.x + acc[1] * acc[1] * w0.y + acc[2] * acc[2] * w0.z + acc[3] * acc[3] * w0.w +
-               acc[4] * acc[4] * w1.x + acc[5] * acc[5] * w1.y + acc[6] * acc[6] * w1.z + acc[7] * acc[7] * w1.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) local += acc[j] * acc[j];
-    }
-  }
-  // block reduction -> one atomic per block
+__device__ __forceinline__ float block_sum_to(float local, float* red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
   __syncthreads();
+  float t = 0.f;
   if (threadIdx.x < 32) {
-    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (threadIdx.x == 0) atomicAdd(sqnorm, t);
   }
+  return t;
+}
+
+// n8 = number of 8-element vectors of the shard; `lo8` = shard offset in vectors inside every rank's buffer.
+// `grads` arrives ROTATED by the host (p[0] is this rank's own buffer, p[r] rank me+r), so the unrolled loops index it
+// statically and the walk over the peers starts at a different link on every rank.  W = compiled rank slots (>= world),
+// U = vectors per thread and pass: W * U 16-byte loads are in flight per thread before the first add.
+template <int W, int U>
+__global__ void __launch_bounds__(512, (W * U <= 8) ? 2 : 1)
+zero_rs_kernel(PeerPtrs grads, int world, size_t lo8, size_t n8, bf16* __restrict__ out,
+               const float* __restrict__ norm_weight, float* __restrict__ sqnorm) {
+  __shared__ float red[32];
+  float local = 0.f;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < n8; i0 += stride * U) {
+    uint4 v[U][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i < n8) {
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < world) v[u][r] = reinterpret_cast<const uint4*>(grads.p[r])[lo8 + i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i >= n8) continue;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < W; ++r)
+        if (r < world) add8(acc, v[u][r]);
+      uint4 o;
+      __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      reinterpret_cast<uint4*>(out)[i] = o;
+      if (norm_weight) {
+        const float4 w0 = reinterpret_cast<const float4*>(norm_weight)[2 * i], w1 = reinterpret_cast<const float4*>(norm_weight)[2 * i + 1];
+        local += acc[0] * acc[0] * w0.x + acc[1] * acc[1] * w0.y + acc[2] * acc[2] * w0.z + acc[3] * acc[3] * w0.w +
+                 acc[4] * acc[4] * w1.x + acc[5] * acc[5] * w1.y + acc[6] * acc[6] * w1.z + acc[7] * acc[7] * w1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) local += acc[j] * acc[j];
+      }
+    }
+  }
+  const float t = block_sum_to(local, red);                   // one atomic per block
+  if (threadIdx.x == 0) atomicAdd(sqnorm, t);
 }
 
 __device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc_addr) {
@@ -84,9 +102,11 @@ __device__ __forceinline__ void mm_st_16(void* mc_addr, const uint4& v) {
                  "f"(__uint_as_float(v.w)) : "memory");
 }
 
+// `params` arrives rotated like the gradient pointers above (p[0] = own buffer).
+template <int W>
 __global__ void __launch_bounds__(512)
 zero_adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, const bf16* __restrict__ grad,
-                 PeerPtrsW params, void* mc_params, int world, int me, size_t lo8, size_t n8, float lr, float b1, float b2,
+                 PeerPtrsW params, void* mc_params, int world, size_t lo8, size_t n8, float lr, float b1, float b2,
                  float eps, float wd, float bc1, float bc2, int adamw, const float* __restrict__ scale_ptr) {
   const float scale = scale_ptr[0];
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
@@ -128,11 +148,8 @@ zero_adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
       mm_st_16(reinterpret_cast<uint4*>(mc_params) + lo8 + i, o);        // one store, replicated by the switch
     } else {
 #pragma unroll
-      for (int r = 0; r < ZMAX; ++r)
-        if (r < world) {
-          const int dst = (me + r) % world;
-          reinterpret_cast<uint4*>(params.p[dst])[lo8 + i] = o;
-        }
+      for (int r = 0; r < W; ++r)
+        if (r < world) reinterpret_cast<uint4*>(params.p[r])[lo8 + i] = o;
     }
   }
 }
@@ -141,35 +158,39 @@ zero_adam_kernel(float* __restrict__ master, float* __restrict__ m, float* __res
 // With the buffers bound to an NVLink multicast object the switch does the work: one multimem.ld_reduce returns the
 // sum of all ranks' gradients for 16 bytes (fp32 accumulation in the switch, so each rank pulls only its own shard
 // across NVLink instead of world-1 copies of it), and one multimem.st writes the updated parameters into every rank.
+constexpr int MM_U = 4;       // multimem.ld_reduce operations in flight per thread
 __global__ void __launch_bounds__(512)
 zero_rs_mm_kernel(const uint4* __restrict__ mc_grad, size_t lo8, size_t n8, bf16* __restrict__ out,
                   const float* __restrict__ norm_weight, float* __restrict__ sqnorm) {
   __shared__ float red[32];
   float local = 0.f;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
-    const uint4 o = mm_ld_reduce_bf16x8(mc_grad + lo8 + i);
-    reinterpret_cast<uint4*>(out)[i] = o;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    add8(acc, o);
-    if (norm_weight) {
-      const float4 w0 = reinterpret_cast<const float4*>(norm_weight)[2 * i], w1 = reinterpret_cast<const float4*>(norm_weight)[2 * i + 1];
-      local += acc[0] * acc[0] * w0.x + acc[1] * acc[1] * w0.y + acc[2] * acc[2] * w0.z + acc[3] * acc[3] * w0.w +
-               acc[4] * acc[4] * w1.x + acc[5] * acc[5] * w1.y + acc[6] * acc[6] * w1.z + acc[7] * acc[7] * w1.w;
-    } else {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < n8; i0 += stride * MM_U) {
+    uint4 v[MM_U];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) local += acc[j] * acc[j];
+    for (int u = 0; u < MM_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i < n8) v[u] = mm_ld_reduce_bf16x8(mc_grad + lo8 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < MM_U; ++u) {
+      const size_t i = i0 + u * stride;
+      if (i >= n8) continue;
+      reinterpret_cast<uint4*>(out)[i] = v[u];
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8(acc, v[u]);
+      if (norm_weight) {
+        const float4 w0 = reinterpret_cast<const float4*>(norm_weight)[2 * i], w1 = reinterpret_cast<const float4*>(norm_weight)[2 * i + 1];
+        local += acc[0] * acc[0] * w0.x + acc[1] * acc[1] * w0.y + acc[2] * acc[2] * w0.z + acc[3] * acc[3] * w0.w +
+                 acc[4] * acc[4] * w1.x + acc[5] * acc[5] * w1.y + acc[6] * acc[6] * w1.z + acc[7] * acc[7] * w1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) local += acc[j] * acc[j];
+      }
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (threadIdx.x == 0) atomicAdd(sqnorm, t);
-  }
+  const float t = block_sum_to(local, red);
+  if (threadIdx.x == 0) atomicAdd(sqnorm, t);
 }
 
 }  // namespace sb
@@ -182,7 +203,7 @@ extern "C" int sb_zero_reduce_scatter_mm(const void* mc_grad, long long lo, long
   if (!mc_grad || (lo % 8) || (n % 8) || (reinterpret_cast<uintptr_t>(mc_grad) & 15)) return -1;
   if (n == 0) return 0;
   const size_t n8 = (size_t)n / 8;
-  size_t g = (n8 + 511) / 512;
+  size_t g = (n8 + 512 * MM_U - 1) / (512 * MM_U);
   if (g > 148 * 4) g = 148 * 4;
   zero_rs_mm_kernel<<<(unsigned)g, 512, 0, st>>>((const uint4*)mc_grad, (size_t)lo / 8, n8, (bf16*)out, norm_weight, sqnorm);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -195,11 +216,17 @@ extern "C" int sb_zero_reduce_scatter(const void* const* grads, int world, int m
   if (world < 1 || world > ZMAX || (lo % 8) || (n % 8)) return -1;
   if (n == 0) return 0;
   PeerPtrs pp;
-  for (int r = 0; r < ZMAX; ++r) pp.p[r] = r < world ? grads[r] : nullptr;
+  for (int r = 0; r < ZMAX; ++r) pp.p[r] = r < world ? grads[(me + r) % world] : nullptr;
   const size_t n8 = (size_t)n / 8;
-  size_t g = (n8 + 511) / 512;
-  if (g > 148 * 4) g = 148 * 4;
-  zero_rs_kernel<<<(unsigned)g, 512, 0, st>>>(pp, world, me, (size_t)lo / 8, n8, (bf16*)out, norm_weight, sqnorm);
+  auto grid = [&](int u, int per_sm) {
+    size_t g = (n8 + 512 * (size_t)u - 1) / (512 * (size_t)u);
+    return (unsigned)(g > 148 * (size_t)per_sm ? 148 * per_sm : g);
+  };
+  bf16* o = (bf16*)out;
+  if (world <= 2)      zero_rs_kernel<2, 4><<<grid(4, 2), 512, 0, st>>>(pp, world, (size_t)lo / 8, n8, o, norm_weight, sqnorm);
+  else if (world <= 4) zero_rs_kernel<4, 2><<<grid(2, 2), 512, 0, st>>>(pp, world, (size_t)lo / 8, n8, o, norm_weight, sqnorm);
+  else if (world <= 8) zero_rs_kernel<8, 1><<<grid(1, 2), 512, 0, st>>>(pp, world, (size_t)lo / 8, n8, o, norm_weight, sqnorm);
+  else                 zero_rs_kernel<16, 1><<<grid(1, 1), 512, 0, st>>>(pp, world, (size_t)lo / 8, n8, o, norm_weight, sqnorm);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -211,11 +238,13 @@ extern "C" int sb_zero_adam_allgather(float* master, float* m, float* v, const v
   if (world < 1 || world > ZMAX || (lo % 8) || (n % 8) || !scale_ptr) return -1;
   if (n == 0) return 0;
   PeerPtrsW pp;
-  for (int r = 0; r < ZMAX; ++r) pp.p[r] = r < world ? params[r] : nullptr;
+  for (int r = 0; r < ZMAX; ++r) pp.p[r] = r < world ? params[(me + r) % world] : nullptr;
   const size_t n8 = (size_t)n / 8;
   size_t g = (n8 + 511) / 512;
   if (g > 148 * 4) g = 148 * 4;
-  zero_adam_kernel<<<(unsigned)g, 512, 0, st>>>(master, m, v, (const bf16*)grad, pp, mc_params, world, me, (size_t)lo / 8, n8, lr, b1, b2,
-                                               eps, wd, bc1, bc2, adamw, scale_ptr);
+#define SB_ADAM(W) zero_adam_kernel<W><<<(unsigned)g, 512, 0, st>>>(master, m, v, (const bf16*)grad, pp, mc_params, world, \
+                                                                     (size_t)lo / 8, n8, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr)
+  if (world <= 2) SB_ADAM(2); else if (world <= 4) SB_ADAM(4); else if (world <= 8) SB_ADAM(8); else SB_ADAM(16);
+#undef SB_ADAM
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -2,7 +2,7 @@
 
 Role of the reference's savanna/training.py (pretrain :340, setup_model_and_optimizer :1243,
 forward_step :930, train_step :1410, train :1549, evaluate :1801) and savanna/initialize.py, without
-DeepSpeed: the engine pieces (ZeRO-1 optimizer, gradient accumulation, activation checkpointing,
+DeepSpeed: the engine pieces (ZeRO-1/2/3 optimizers, gradient accumulation, activation checkpointing,
 checkpoint I/O) are this package's own.
 
 Public API:
@@ -108,6 +108,7 @@ class Trainer:
             on = halo_mod.setup_peer()
             print_rank_0(" > context-parallel halos: " + ("peer-memory pull kernels" if on else "NCCL send/recv"))
         self.model, self.optimizer, self.lr_scheduler = self._setup_model_and_optimizer()
+        self.partitioned = hasattr(self.optimizer, "finish_backward")      # ZeRO stage 2 / 3
         self.gas = cfg.gradient_accumulation_steps
         self.micro_batch = cfg.train_micro_batch_size_per_gpu
         self.skipped_iters = 0
@@ -145,6 +146,20 @@ class Trainer:
             if use_symm:
                 from ..parallel import fused_zero
                 allocator = fused_zero.make_allocator(state.get_sequence_data_parallel_group())
+            if cfg.zero_stage >= 2 and len(zranks) >= 1 and hasattr(model, "blocks") \
+                    and not getattr(model, "is_pipeline_stage", False):
+                from ..parallel.zero_partitioned import PartitionedZeroOptimizer
+                optimizer = PartitionedZeroOptimizer(
+                    groups, model.blocks(), stage=min(3, cfg.zero_stage), lr=cfg.lr,
+                    betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8), weight_decay=cfg.weight_decay,
+                    adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
+                    group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
+                    sync_replicated=bool(cfg.sequence_parallel))
+                rep = optimizer.memory_report()
+                print_rank_0(f" > ZeRO stage {optimizer.stage}: {rep['persistent_bytes'] / 2**20:.0f} MiB of shards and "
+                             f"optimizer state per rank, largest unit {rep['largest_unit_param_bytes'] / 2**20:.0f} MiB "
+                             f"of {rep['full_model_param_bytes'] / 2**20:.0f} MiB of parameters")
+                return model, optimizer, build_lr_scheduler(optimizer, cfg)
             optimizer = ZeroOptimizer(
                 groups, lr=cfg.lr, betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8),
                 weight_decay=cfg.weight_decay, adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
@@ -211,8 +226,11 @@ class Trainer:
                 loss = self.forward_step(b)
             with self._mark("TRAIN_STEP_BACKWARD"):
                 (loss / self.gas).backward()
+                if self.partitioned:
+                    self.optimizer.finish_backward()
             total = loss.detach() if total is None else total + loss.detach()
-        self._sync_replicated_grads()
+        if not self.partitioned:
+            self._sync_replicated_grads()
         with self._mark("TRAIN_STEP_OPTIMIZER_STEP"):
             self.grad_norm = self.optimizer.step()
             self.lr_scheduler.step()
