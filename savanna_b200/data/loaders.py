@@ -159,3 +159,32 @@ def build_train_valid_test_data_iterators(cfg, trainer=None):
     valid = _cycle(make_data_loader(valid_ds, cfg))
     test = _cycle(make_data_loader(test_ds, cfg))
     return train, valid, test
+
+
+def dataset_chart_name(path: str) -> str:
+    """Short name of a validation set for logs: the reference names a chart after the third-last path component
+    (savanna/training.py:1920-1936, `.../<name>/<split>/<file>`); shorter paths fall back to the file stem."""
+    parts = [q for q in path.replace("\\", "/").split("/") if q]
+    return parts[-3] if len(parts) >= 3 else (parts[-1] if parts else path)
+
+
+def build_per_dataset_val_iterators(cfg):
+    """One validation iterator per file of `per_ds_valid_data_paths` (else `valid_data_paths`), so that the loss of
+    every data source is tracked on its own (reference: savanna/data/data_utils.py:732-844).  Returns a list of
+    (name, path, iterator); ranks that do not read data get iterators that yield None."""
+    paths = cfg.per_ds_valid_data_paths or cfg.valid_data_paths or []
+    iters = cfg.eval_per_ds_iters or cfg.eval_iters
+    reader = state.get_model_parallel_rank() == 0 and state.get_context_parallel_rank() == 0
+    out = []
+    for i, path in enumerate(paths):
+        name = dataset_chart_name(path)
+        if not reader:
+            def nones():
+                while True:
+                    yield None
+            out.append((name, path, nones()))
+            continue
+        n = max(1, iters) * cfg.train_batch_size
+        ds = build_the_dataset(path, f"valid_per_ds_{i}", cfg, n, cfg.seed, not cfg.mmap_warmup)
+        out.append((name, path, _cycle(make_data_loader(ds, cfg))))
+    return out

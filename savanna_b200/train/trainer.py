@@ -290,6 +290,15 @@ class Trainer:
             out["lm_loss_char_lvl_ppl"] = out["lm_loss_ppl"]
         return out
 
+    def evaluate_per_dataset(self, iters: Optional[int] = None) -> Dict[str, Dict[str, float]]:
+        """Validation loss of every data source on its own (reference: savanna/training.py:1897-1940); the iterators
+        are built on first use and keep their position between calls."""
+        from ..data.loaders import build_per_dataset_val_iterators
+        if getattr(self, "_per_ds_iters", None) is None:
+            self._per_ds_iters = build_per_dataset_val_iterators(self.cfg)
+        n = iters if iters is not None else (self.cfg.eval_per_ds_iters or self.cfg.eval_iters)
+        return {name: self.evaluate(it, n) for name, _path, it in self._per_ds_iters}
+
     # ------------------------------------------------------------------ loop
     def train(self, train_iter: Iterator, valid_iter: Optional[Iterator] = None) -> None:
         from ..ckpt import save_checkpoint
@@ -317,6 +326,9 @@ class Trainer:
                 if valid_iter is not None and cfg.eval_interval and it % cfg.eval_interval == 0 and cfg.do_valid != 0:
                     res = self.evaluate(valid_iter)
                     logger.log_eval(res, it)
+                if cfg.do_per_ds_valid and cfg.eval_per_ds_interval and it % cfg.eval_per_ds_interval == 0:
+                    for name, res in self.evaluate_per_dataset().items():
+                        logger.log_eval(res, it, prefix=f"validation/{name}")
                 if cfg.exit_interval and it % cfg.exit_interval == 0:
                     print_rank_0(f"exit_interval reached at iteration {it}")
                     break

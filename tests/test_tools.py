@@ -130,3 +130,71 @@ def test_load_for_inference_roundtrip(tiny_ckpt):
         got = model(tokens, torch.arange(64))
     assert torch.allclose(got, want, atol=1e-5)
     assert tok is not None and cfg.hidden_size == 256
+
+
+def _byte_dataset(path, ndocs, seed, low, high):
+    import numpy as np
+    from savanna_b200.data.indexed_dataset import MMapIndexedDatasetBuilder
+    rng = np.random.default_rng(seed)
+    b = MMapIndexedDatasetBuilder(path + ".bin", dtype=np.uint16)
+    for _ in range(ndocs):
+        b.add_item(rng.integers(low, high, size=int(rng.integers(100, 400))))
+        b.end_document()
+    b.finalize(path + ".idx")
+    return path
+
+
+def test_evaluate_per_dataset_tool(tmp_path):
+    """Two validation files give two separately reported losses; the in-training hook logs them under their names."""
+    import os
+    from savanna_b200.parallel import state
+    from savanna_b200.tools import evaluate_per_ds
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tiny = os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")
+    d1, d2 = tmp_path / "genomes" / "valid", tmp_path / "plasmids" / "valid"
+    d1.mkdir(parents=True); d2.mkdir(parents=True)
+    p1 = _byte_dataset(str(d1 / "data_text_document"), 40, 0, 65, 69)
+    p2 = _byte_dataset(str(d2 / "data_text_document"), 40, 1, 97, 123)
+    out = tmp_path / "res.json"
+    state.destroy_model_parallel()
+    res = evaluate_per_ds.main([tiny, "--iters", "2", "--json", str(out), "--override", "global_num_gpus=1",
+                                "--override", f"per_ds_valid_data_paths=[{p1}, {p2}]", "--override", "synthetic_data=null",
+                                "--override", f"train_data_paths=[{p1}]", "--override", "train_data_weights=[1.0]"])
+    assert list(res) == ["genomes", "plasmids"]
+    assert all(r["lm_loss"] == r["lm_loss"] and r["lm_loss"] > 0 for r in res.values())
+    import json
+    assert set(json.load(open(out))) == {"genomes", "plasmids"}
+    assert "genomes" in evaluate_per_ds.format_table(res)
+    state.destroy_model_parallel()
+
+
+def test_parquet_to_json(tmp_path):
+    import json
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from savanna_b200.tools import parquet_to_json
+    src, dst = str(tmp_path / "a.parquet"), str(tmp_path / "a.jsonl")
+    pq.write_table(pa.table({"text": ["ACGT", "GGCC", "TTAA"], "id": [1, 2, 3]}), src)
+    assert parquet_to_json.main([src, dst, "--columns", "text"]) == 3
+    rows = [json.loads(l) for l in open(dst)]
+    assert rows == [{"text": "ACGT"}, {"text": "GGCC"}, {"text": "TTAA"}]
+
+
+def test_ds_to_universal(tiny_ckpt, tmp_path):
+    """Per-parameter export: every parameter's fp32 master and Adam moments come back whole, with a step file."""
+    import os
+    from savanna_b200.tools.ds_to_universal import convert, load_universal_param
+    tr, d = tiny_ckpt
+    out = str(tmp_path / "universal")
+    names = convert(d, out, write_latest=False)
+    sd = {n: p.detach() for n, p in tr.model.named_parameters()}
+    assert set(names) == {n for n, p in tr.model.named_parameters() if p.requires_grad}
+    for n in names:
+        w = load_universal_param(out, n)
+        assert w.shape == sd[n].shape and w.dtype == torch.float32
+        assert torch.allclose(w, sd[n].float().cpu(), atol=1e-2, rtol=1e-2), n
+        m = load_universal_param(out, n, "exp_avg")
+        assert m.shape == sd[n].shape
+        assert os.path.isfile(os.path.join(out, "zero", n, "step.pt"))
+    assert os.path.isfile(os.path.join(out, "zero", "optimizer_state.pt"))
+    assert os.path.isfile(os.path.join(out, "mp_rank_00_model_states.pt"))
