@@ -348,6 +348,9 @@ class Trainer:
 def pretrain(cfg) -> Trainer:
     """Entry used by train.py: set up, build data iterators, train, final evaluation."""
     from ..data.loaders import build_train_valid_test_data_iterators
+    if cfg.use_mup and cfg.coord_check:
+        raise SystemExit("coord_check: run `python -m savanna_b200.train.mup_coord_check <model configs>`; it builds the "
+                         "model at several widths itself (the reference also exits after its coordinate check)")
     trainer = Trainer(cfg)
     cfg.iteration = trainer.iteration
     train_it, valid_it, test_it = build_train_valid_test_data_iterators(cfg, trainer)
