@@ -211,6 +211,12 @@ def bench_attention(L, iters, heads=32, small=False):
     o, lse = flash_sm100.forward(q, k, v, True, hd ** -0.5)
     go = torch.randn_like(o)
     report("attention.fwd.ours", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl, L=L, H=H)
+    qn, kn, vn = (torch.randn(B, L, H, hd, device="cuda", dtype=BF) for _ in range(3))
+    report("attention.fwd.ours_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
+    flash_sm100.set_forward_variant(True)
+    report("attention.fwd.ours_pingpong", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
+    report("attention.fwd.ours_pingpong_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
+    flash_sm100.set_forward_variant(False)
     report("attention.bwd.ours", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
     flash_sm100.set_backward_variant(False)
     report("attention.bwd.ours_p_in_smem", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)

@@ -40,6 +40,7 @@ struct FwdParams {
   float scale_log2;          // softmax scale * log2(e)
   float scale;
   uint32_t* status;
+  int pingpong;              // 1: the two softmax warpgroups take turns on the exponentials (see the kernel)
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -97,6 +98,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto pv_done = [&](int t) { return bar_base + 104u + 8u * t; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFF + 120);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + BAR_OFF + 128);
+  // turn(t): "warpgroup t may run its exponentials".  The special-function unit is the shared resource of the two
+  // softmax warpgroups: left alone they fall into phase (both in the exponentials, then both waiting on TMEM loads,
+  // row maxima and the P V product) and the unit idles half of the time.  Taking turns keeps one warpgroup in its
+  // exponentials while the other loads and reduces its next score row.
+  auto turn = [&](int t) { return bar_base + 136u + 8u * t; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = gridDim.x - 1 - blockIdx.x;          // longest rows first
@@ -118,6 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int t = 0; t < 2; ++t) {
       mbar_init(k_full(t), 1); mbar_init(k_free(t), 1);
       mbar_init(s_full(t), 1); mbar_init(s_free(t), 128); mbar_init(p_ready(t), 128); mbar_init(pv_done(t), 1);
+      mbar_init(turn(t), 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -266,6 +273,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(pv_done(t), par ^ 1u, abort_flag, p.status, ST_ATTN + 8)) { ok = false; break; }
         tc_fence_after();
       }
+      // my turn on the special-function unit: tile 0 goes first; tile 0's block j follows tile 1's block j-1, tile 1's
+      // block j follows tile 0's block j.  A warpgroup whose partner has no such block left does not wait.
+      if (p.pingpong) {
+        if (t == 0) {
+          if (j > 0 && j - 1 < nb[1] &&
+              !mbar_wait(turn(0), uint32_t(j - 1) & 1u, abort_flag, p.status, ST_ATTN + 10)) { ok = false; break; }
+        } else {
+          if (j < nb[0] && !mbar_wait(turn(1), par, abort_flag, p.status, ST_ATTN + 11)) { ok = false; break; }
+        }
+      }
       // P = exp2((S - m) * scale) as bf16 into the swizzled P tile; row sum in fp32
       const float moff = -m_ref * sl2;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -285,6 +302,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
         }
       }
+      if (p.pingpong) mbar_arrive(turn(t ^ 1));               // hand the unit to the other warpgroup
       const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l = l * alpha + rs;
       if (__any_sync(0xffffffffu, rescale)) {
@@ -717,6 +735,7 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 static int g_last_encode = 0;
+static int g_pingpong = 0;     // forward variant: softmax warpgroups take turns on the exponentials (1) or run freely (0)
 static int g_p_tmem = 1;       // backward variant: P^T in tensor memory (1) or in shared memory (0)
 
 // [B, L, H, 128] bf16 with element strides (sb, sl, sh); box = 64 columns x 1 head x box_rows rows x 1 batch
@@ -741,6 +760,7 @@ static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, lo
 
 extern "C" int sb_attn_last_encode_result() { return sb::attn::g_last_encode; }
 extern "C" int sb_attn_set_bwd_variant(int p_in_tmem) { sb::attn::g_p_tmem = p_in_tmem ? 1 : 0; return 0; }
+extern "C" int sb_attn_set_fwd_variant(int pingpong) { sb::attn::g_pingpong = pingpong ? 1 : 0; return 0; }
 
 // Attention forward.  q [B, Lq, H, 128], k and v [B, Lk, H, 128], out like q: bf16, last dimension contiguous, the
 // other strides (in elements) multiples of 8.  lse [B, H, Lq] fp32.  causal needs Lq == Lk (row i sees keys 0..i).
@@ -765,7 +785,7 @@ extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* ou
     attr_set = true;
   }
   FwdParams p{reinterpret_cast<__nv_bfloat16*>(out), lse, o_str[0], o_str[1], o_str[2], B, H, Lq, Lk, causal,
-              scale * 1.4426950408889634f, scale, status};
+              scale * 1.4426950408889634f, scale, status, g_pingpong};
   dim3 grid((Lq + 2 * BQ - 1) / (2 * BQ), H, B);
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;

@@ -32,6 +32,8 @@ def _lib():
         lib.sb_attn_last_encode_result.argtypes = []
         lib.sb_attn_set_bwd_variant.restype = I
         lib.sb_attn_set_bwd_variant.argtypes = [I]
+        lib.sb_attn_set_fwd_variant.restype = I
+        lib.sb_attn_set_fwd_variant.argtypes = [I]
         lib.sb_attn_merge_fwd.restype = I
         lib.sb_attn_merge_fwd.argtypes = [P, P, P, P, I, I, I, I, P, P, P]
         lib.sb_attn_merge_bwd.restype = I
@@ -44,6 +46,12 @@ def set_backward_variant(p_in_tmem: bool) -> None:
     """Backward kernel variant: P^T as the tensor-memory operand of the dV product with three Q/dO stages (default),
     or P^T through shared memory with two stages."""
     _lib().sb_attn_set_bwd_variant(int(bool(p_in_tmem)))
+
+
+def set_forward_variant(pingpong: bool) -> None:
+    """Forward kernel variant: the two softmax warpgroups of a CTA take turns on the exponentials (default), or run
+    without coordination."""
+    _lib().sb_attn_set_fwd_variant(int(bool(pingpong)))
 
 
 def _ok_layout(t) -> bool:

@@ -77,6 +77,20 @@ def test_flash_backward_variant_shared_memory_p():
         flash_sm100.set_backward_variant(True)
 
 
+@pytest.mark.parametrize("pingpong", [False, True])
+@pytest.mark.parametrize("Lq,Lk,causal", [(1024, 1024, True), (333, 333, True), (128, 128, True), (640, 896, False),
+                                           (130, 130, True)])
+def test_flash_forward_variants(pingpong, Lq, Lk, causal):
+    """Both forward schedules (softmax warpgroups taking turns on the exponentials, or free running) on shapes where
+    the two query tiles of a CTA see equal and unequal numbers of key blocks, and where the second tile is empty."""
+    from savanna_b200.ops import flash_sm100
+    flash_sm100.set_forward_variant(pingpong)
+    try:
+        _case(2, Lq, Lk, 2, causal, seed=5)
+    finally:
+        flash_sm100.set_forward_variant(False)
+
+
 def test_flash_fused_qkv_strides():
     _case(2, 512, 512, 4, True, fused_qkv=True, seed=7)
 
