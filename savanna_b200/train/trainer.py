@@ -113,6 +113,12 @@ class Trainer:
         self.micro_batch = cfg.train_micro_batch_size_per_gpu
         self.skipped_iters = 0
         self.nan_iters = 0
+        self.noise_scale = None
+        if cfg.log_gradient_noise_scale and not self.partitioned:
+            from .critical_batch import CriticalBatchEstimator
+            self.noise_scale = CriticalBatchEstimator(cfg.train_micro_batch_size_per_gpu * cfg.gradient_accumulation_steps,
+                                                      cfg.gradient_noise_scale_n_batches,
+                                                      cpu_offload=bool(cfg.gradient_noise_scale_cpu_offload))
         self.profiler = None
         self.timers = None
         self.watchdog = None
@@ -231,6 +237,9 @@ class Trainer:
             total = loss.detach() if total is None else total + loss.detach()
         if not self.partitioned:
             self._sync_replicated_grads()
+        if self.noise_scale is not None:
+            # this rank's accumulated gradient, before the data-parallel reduction, is the "small batch" sample
+            self.noise_scale.update([p for p in self.model.parameters() if p.requires_grad])
         with self._mark("TRAIN_STEP_OPTIMIZER_STEP"):
             self.grad_norm = self.optimizer.step()
             self.lr_scheduler.step()

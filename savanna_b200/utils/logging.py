@@ -8,6 +8,7 @@ utils/mfu.py).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 import sys
@@ -102,9 +103,42 @@ def init_wandb(cfg) -> bool:
         return False
 
 
+class ActivationNormRecorder:
+    """Per-layer activation norms of the sequence mixers (`log_attn_norms`, `log_hyena_norms`; the reference logs
+    `x.norm(2, -1).max(1).mean(0)` of the attention / Hyena outputs from rank 0, savanna/model/block.py:60-79,
+    1122-1192, operators/hyena/hyena.py:383-402).  Forward hooks keep the latest value per layer as a device scalar;
+    the logger reads them at the logging interval only."""
+
+    def __init__(self, model, cfg):
+        self.values: Dict[str, torch.Tensor] = {}
+        self.handles = []
+        if not (cfg.log_attn_norms or cfg.log_hyena_norms) or not hasattr(model, "blocks"):
+            return
+        for b in model.blocks():
+            op = getattr(b, "operator_type", "")
+            hyena = op.startswith("hyena")
+            if (hyena and not cfg.log_hyena_norms) or (not hyena and not cfg.log_attn_norms):
+                continue
+            key = f"{'hyena' if hyena else 'attention'}_output_norm_{b.layer_number}" if hasattr(b, "layer_number") \
+                else f"{'hyena' if hyena else 'attention'}_output_norm_{len(self.handles)}"
+            self.handles.append(b.mixer.register_forward_hook(self._hook(key)))
+
+    def _hook(self, key):
+        def fn(_m, _a, out):
+            t = out[0] if isinstance(out, (tuple, list)) else out
+            if isinstance(t, torch.Tensor) and t.dim() == 3:
+                with torch.no_grad():
+                    self.values[key] = t.detach().float().norm(2, dim=-1).max(1).values.mean(0)
+        return fn
+
+    def read(self) -> Dict[str, float]:
+        return {k: float(v) for k, v in self.values.items()}
+
+
 class TrainingLogger:
     def __init__(self, cfg, trainer):
         self.cfg, self.trainer = cfg, trainer
+        self.act_norms = ActivationNormRecorder(trainer.model, cfg)
         self.interval = max(1, cfg.log_interval or 1)
         self.t_acc, self.n_acc, self.loss_acc = 0.0, 0, 0.0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
@@ -162,12 +196,28 @@ class TrainingLogger:
                 self._log(f"memory/{k}", v, it)
         if cfg.log_memory_alloc_counts and torch.cuda.is_available():
             line += f" | alloc counts {mem.gather_alloc_counts()}"
+        for k, v in self.act_norms.read().items():
+            self._log(f"activations/{k}", v, it)
+        ns = getattr(tr, "noise_scale", None)
+        if cfg.log_gradient_noise_scale and ns is not None and ns.noise_scale is not None:
+            self._log("train/noise_scale", ns.noise_scale, it)
+            line += f" | noise scale: {ns.noise_scale:.3E}"
+        if cfg.log_optimizer_states and hasattr(tr.optimizer, "groups"):
+            for i, g in enumerate(tr.optimizer.groups):
+                name = getattr(g, "name", None) or g.hyper.get("name", str(i))
+                self._log(f"optimizer_state_norms/{name}_{i}/exp_avg", float(g.exp_avg.float().norm()), it)
+                self._log(f"optimizer_state_norms/{name}_{i}/exp_avg_sq", float(g.exp_avg_sq.float().norm()), it)
         if cfg.log_param_norm or cfg.log_grad_norm:
-            for name, p in tr.model.named_parameters():
-                if cfg.log_param_norm:
-                    self._log(f"param_norm/{name}", float(p.detach().float().norm()), it)
-                if cfg.log_grad_norm and p.grad is not None:
-                    self._log(f"grad_norm/{name}", float(p.grad.detach().float().norm()), it)
+            # ZeRO stage 2 / 3 keep no whole gradients after the step and (stage 3) no whole parameters: gather the
+            # parameters for the read, skip the per-parameter gradient norms
+            part = getattr(tr, "partitioned", False)
+            ctx = tr.optimizer.full_params() if part else contextlib.nullcontext()
+            with ctx:
+                for name, p in tr.model.named_parameters():
+                    if cfg.log_param_norm:
+                        self._log(f"param_norm/{name}", float(p.detach().float().norm()), it)
+                    if cfg.log_grad_norm and not part and p.grad is not None:
+                        self._log(f"grad_norm/{name}", float(p.grad.detach().float().norm()), it)
         print_rank_0(line)
 
     def log_eval(self, results: Dict[str, float], it: int, prefix: str = "validation") -> None:

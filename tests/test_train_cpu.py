@@ -1,4 +1,11 @@
+"""Training-loop helpers on CPU: muP coordinate check, optional logging (activation norms, gradient noise scale,
+optimizer-state norms, parameter norms under ZeRO stage 3)."""
+import os
 
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = os.path.join(ROOT, "configs", "baseline", "tiny_sh2_cpu.yml")
 
 def test_mup_coord_check(tmp_path):
     """Three widths, with and without muP: every block is recorded at every step; the CSV and the slopes come out."""
@@ -17,3 +24,39 @@ def test_mup_coord_check(tmp_path):
     assert len(open(tmp_path / "cc.csv").read().splitlines()) == len(recs) + 1
     s = cc.summarise(recs)
     assert set(s) == {"mup", "sp"} and "logits" in s["mup"] and all(v == v for v in s["sp"].values())
+
+
+@pytest.mark.parametrize("stage", [1, 3])
+def test_optional_logging(monkeypatch, stage):
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    from savanna_b200.utils import logging as lg
+    state.destroy_model_parallel()
+    cfg = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1, "log_attn_norms": True, "log_hyena_norms": True,
+                                          "log_gradient_noise_scale": True, "gradient_noise_scale_n_batches": 2,
+                                          "log_optimizer_states": True, "log_param_norm": True, "log_grad_norm": True,
+                                          "log_interval": 1, "zero_optimization": {"stage": stage}})
+    tr = Trainer(cfg, load=False)
+    seen = {}
+    monkeypatch.setattr(lg, "tb_wandb_log", lambda key, value, it, *a, **k: seen.__setitem__(key, value))
+    logger = lg.TrainingLogger(cfg, tr)
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    d = it()
+    for _ in range(3):
+        loss = tr.train_step(d)
+        logger.log_step(loss, 0.1)
+    n_layers = cfg.num_layers
+    acts = [k for k in seen if k.startswith("activations/")]
+    assert len(acts) == n_layers and any("hyena_output_norm" in k for k in acts) and any("attention_output_norm" in k for k in acts)
+    assert any(k.startswith("optimizer_state_norms/") for k in seen)
+    assert any(k.startswith("param_norm/") for k in seen)
+    if stage == 1:
+        assert "train/noise_scale" in seen and any(k.startswith("grad_norm/") for k in seen)
+    state.destroy_model_parallel()
