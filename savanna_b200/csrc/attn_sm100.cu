@@ -86,12 +86,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sQ = smem_base, sK = smem_base + 2 * TILE_BYTES, sV = sK + 2 * TILE_BYTES, sP = sV + TILE_BYTES;
+  // K and V tiles share one ring of three slots, filled in the order they are consumed: K(0) V(0) K(1) V(1) ...
+  // (tile number i of that sequence lives in slot i % 3).  K(j)'s slot is free as soon as both score products of block
+  // j are done, early in the block, so V(j+1) is already on its way while P V of block j runs; with the same 96 KB as
+  // two K stages and one V stage, no TMA latency is left exposed between consecutive P V products.
+  const uint32_t sQ = smem_base, sKV = smem_base + 2 * TILE_BYTES, sP = sKV + 3 * TILE_BYTES;
   constexpr uint32_t BAR_OFF = 7 * TILE_BYTES;
   const uint32_t bar_base = smem_base + BAR_OFF;
-  const uint32_t q_full = bar_base, v_full = bar_base + 8, v_free = bar_base + 16;
-  auto k_full = [&](int s) { return bar_base + 24u + 8u * s; };
-  auto k_free = [&](int s) { return bar_base + 40u + 8u * s; };
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u + 8u * s; };
+  auto kv_free = [&](int s) { return bar_base + 32u + 8u * s; };
   auto s_full = [&](int t) { return bar_base + 56u + 8u * t; };
   auto s_free = [&](int t) { return bar_base + 72u + 8u * t; };
   auto p_ready = [&](int t) { return bar_base + 88u + 8u * t; };
@@ -120,9 +124,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int n = max(nb[0], nb[1]);
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_free, 1);
+    mbar_init(q_full, 1);
+    for (int t = 0; t < 3; ++t) { mbar_init(kv_full(t), 1); mbar_init(kv_free(t), 1); }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(k_full(t), 1); mbar_init(k_free(t), 1);
       mbar_init(s_full(t), 1); mbar_init(s_free(t), 128); mbar_init(p_ready(t), 128); mbar_init(pv_done(t), 1);
       mbar_init(turn(t), 128);
     }
@@ -146,14 +150,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_expect_tx(q_full, 2 * TILE_BYTES);
       load_tile(sQ, &tmQ, q0, h, b, q_full);
       load_tile(sQ + TILE_BYTES, &tmQ, q0 + BQ, h, b, q_full);
-      for (int j = 0; j < n && ok; ++j) {
-        const int ks = j & 1;
-        if (!mbar_wait(k_free(ks), ((uint32_t(j) >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 1)) { ok = false; break; }
-        mbar_expect_tx(k_full(ks), TILE_BYTES);
-        load_tile(sK + ks * TILE_BYTES, &tmK, j * BK, h, b, k_full(ks));
-        if (!mbar_wait(v_free, (uint32_t(j) & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 2)) { ok = false; break; }
-        mbar_expect_tx(v_full, TILE_BYTES);
-        load_tile(sV, &tmV, j * BK, h, b, v_full);
+      for (int i = 0; i < 2 * n && ok; ++i) {            // i even: K(i/2), i odd: V(i/2)
+        const int slot = i % 3;
+        const uint32_t use = uint32_t(i / 3);
+        if (!mbar_wait(kv_free(slot), (use & 1u) ^ 1u, abort_flag, p.status, ST_ATTN + 1 + (i & 1))) { ok = false; break; }
+        mbar_expect_tx(kv_full(slot), TILE_BYTES);
+        load_tile(sKV + slot * TILE_BYTES, (i & 1) ? &tmV : &tmK, (i >> 1) * BK, h, b, kv_full(slot));
       }
       if (!ok) {
         const unsigned long long t0 = globaltimer();
@@ -177,30 +179,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int t = 0; t < 2; ++t) {
           if (pv_idx[t] < nb[t]) {
             const int jp = pv_idx[t];
-            if (mbar_test(p_ready(t), uint32_t(jp) & 1u) && mbar_test(v_full, uint32_t(jp) & 1u)) {
+            const int vslot = (2 * jp + 1) % 3;
+            if (mbar_test(p_ready(t), uint32_t(jp) & 1u) && mbar_test(kv_full(vslot), uint32_t((2 * jp + 1) / 3) & 1u)) {
               tc_fence_after();
+              const uint32_t sV = sKV + vslot * TILE_BYTES;
 #pragma unroll
               for (int kk = 0; kk < 8; ++kk)
                 umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
                           (jp | kk) ? 1u : 0u);
               umma_commit(pv_done(t));
               pv_idx[t] = jp + 1;
-              if (pv_idx[t ^ 1] > jp || jp >= nb[t ^ 1]) umma_commit(v_free);     // both tiles are through with V(jp)
+              if (pv_idx[t ^ 1] > jp || jp >= nb[t ^ 1]) umma_commit(kv_free(vslot));   // both tiles are through with V(jp)
               progress = true;
             }
           }
           if (s_idx[t] < nb[t]) {
             const int js = s_idx[t];
-            if (mbar_test(k_full(js & 1), (uint32_t(js) >> 1) & 1u) &&
+            const int kslot = (2 * js) % 3;
+            if (mbar_test(kv_full(kslot), uint32_t((2 * js) / 3) & 1u) &&
                 (js == 0 || mbar_test(s_free(t), uint32_t(js - 1) & 1u))) {
               tc_fence_after();
+              const uint32_t sK = sKV + kslot * TILE_BYTES;
 #pragma unroll
               for (int kk = 0; kk < 8; ++kk)
-                umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK + (js & 1) * TILE_BYTES, kk),
-                          idesc_s, kk ? 1u : 0u);
+                umma_bf16(tmem_base + t * 128, desc_kmajor(sQ + t * TILE_BYTES, kk), desc_kmajor(sK, kk), idesc_s, kk ? 1u : 0u);
               umma_commit(s_full(t));
               s_idx[t] = js + 1;
-              if (s_idx[t ^ 1] > js || js >= nb[t ^ 1]) umma_commit(k_free(js & 1)); // both tiles are through with K(js)
+              if (s_idx[t ^ 1] > js || js >= nb[t ^ 1]) umma_commit(kv_free(kslot));    // both tiles are through with K(js)
               progress = true;
             }
           }
