@@ -67,7 +67,7 @@ def emulate(a):
         ts.sort()
         return ts[len(ts) // 2]
 
-    for name, N, K in (("in_proj", 3 * D, D), ("mlp_w12", 2 * F_, D)):
+    for name, N, K in (() if a.only_zero else (("in_proj", 3 * D, D), ("mlp_w12", 2 * F_, D))):
         shards = [torch.randn(l, K, device=dev).to(torch.bfloat16) for _ in range(world)]
         w = (torch.randn(N // world, K, device=dev) * 0.02).to(torch.bfloat16)
         gather = torch.empty(L * K, dtype=torch.bfloat16, device=dev)
@@ -88,7 +88,7 @@ def emulate(a):
         print(json.dumps({"op": f"F1.ag_gemm.{name}.emulated_1gpu", "slots": world, "ms": round(ms, 4),
                           "tflops": round(fl / ms / 1e9, 1), "frac_of_gemm_peak": round(fl / (ms / 1e3) / peak, 3),
                           "rel_err": round(err, 5)}), flush=True)
-    for name, N, K in (("out_proj", D, D), ("mlp_w3", D, F_)):
+    for name, N, K in (() if a.only_zero else (("out_proj", D, D), ("mlp_w3", D, F_))):
         x = torch.randn(L, K // world, device=dev).to(torch.bfloat16)
         w = (torch.randn(N, K // world, device=dev) * 0.02).to(torch.bfloat16)
         stages = [torch.empty(world * l * N, dtype=torch.bfloat16, device=dev) for _ in range(world)]
@@ -103,8 +103,8 @@ def emulate(a):
         fl = 2.0 * L * N * (K // world)
         print(json.dumps({"op": f"F2.gemm_rs.{name}.emulated_1gpu", "slots": world, "ms": round(ms, 4),
                           "tflops": round(fl / ms / 1e9, 1), "frac_of_gemm_peak": round(fl / (ms / 1e3) / peak, 3)}), flush=True)
-    # ZeRO-1 step kernels on a 512M-element flat group: every slot's gradient / parameter buffer is local
-    n = 512 * 1024 * 1024
+    # ZeRO-1 step kernels on a flat group (512M elements by default): every slot's gradient / parameter buffer is local
+    n = (a.zero_elems // (8 * world)) * 8 * world
     shard = n // world
     grads = [torch.randn(n, device=dev, dtype=torch.bfloat16) for _ in range(world)]
     params = [torch.empty(n, device=dev, dtype=torch.bfloat16) for _ in range(world)]
@@ -135,6 +135,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--zero-elems", type=int, default=512 * 1024 * 1024,
+                    help="elements of the flat group of the emulated ZeRO kernels (smaller for profiler captures)")
+    ap.add_argument("--only-zero", action="store_true", help="emulation: run the ZeRO kernels only")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="single-GPU emulation with this many rank slots in local memory (for ncu captures)")
     a = ap.parse_args()
