@@ -128,7 +128,11 @@ def _fwd_bwd(fn, inputs, iters):
     return f_ms, fb_ms - f_ms
 
 
+TILED_DEFAULT = True      # which short-convolution backward variant the library starts with
+
+
 def bench_convs(L, iters, which):
+    from savanna_b200.ops import cuda_ops
     D, G = 4096, 256
     B = 1
     feat = torch.randn(B, L, 3 * D, device="cuda", dtype=BF, requires_grad=True)
@@ -144,11 +148,21 @@ def bench_convs(L, iters, which):
             f, b = _fwd_bwd(lambda x, w_: ops.causal_conv1d(x, w_), (proj, w), iters)
             report(f"featurizer_conv3.fwd.{tag}", f, None, 6 * nb, L=L)
             report(f"featurizer_conv3.bwd.{tag}", b, None, 9 * nb, L=L)
+            if backend == "auto":
+                cuda_ops.set_se_backward_variant(not TILED_DEFAULT)
+                _, b2 = _fwd_bwd(lambda x, w_: ops.causal_conv1d(x, w_), (proj, w), iters)
+                report("featurizer_conv3.bwd.ours_other_variant", b2, None, 9 * nb, L=L, tiled=not TILED_DEFAULT)
+                cuda_ops.set_se_backward_variant(TILED_DEFAULT)
         if "se" in which:
             w = torch.randn(G, 7, device="cuda", requires_grad=True)
             f, b = _fwd_bwd(lambda x, w_: ops.hyena_se_inner(x, w_), (feat, w), iters)
             report(f"hyena_se_k7.fwd.{tag}", f, None, 4 * nb, L=L)
             report(f"hyena_se_k7.bwd.{tag}", b, None, 7 * nb, L=L)
+            if backend == "auto":
+                cuda_ops.set_se_backward_variant(not TILED_DEFAULT)
+                _, b2 = _fwd_bwd(lambda x, w_: ops.hyena_se_inner(x, w_), (feat, w), iters)
+                report("hyena_se_k7.bwd.ours_other_variant", b2, None, 7 * nb, L=L, tiled=not TILED_DEFAULT)
+                cuda_ops.set_se_backward_variant(TILED_DEFAULT)
         if "mr" in which:
             h = (torch.randn(G, 128, device="cuda") / 11.3).requires_grad_()
             bias = torch.randn(D, device="cuda", requires_grad=True)

@@ -53,6 +53,14 @@ __device__ __forceinline__ void store_triple(bf16* p, const float (&x1)[CH], con
   store_ch<CH>(p, a); store_ch<CH>(p + CH, b); store_ch<CH>(p + 2 * CH, c);
 }
 
+// 16-byte asynchronous copy global -> shared; nbytes = 0 writes zeros without touching `src` (which must still be a
+// valid address).  Used to put a whole tile's loads in flight without holding them in registers.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, int nbytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(nbytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------ depthwise conv
 template <int K, int CH>
 __global__ void dwconv_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ halo, const float* __restrict__ w,
@@ -159,6 +167,78 @@ __global__ void dwconv_bwd_kernel(const bf16* __restrict__ x, const bf16* __rest
   for (int i = 0; i < CH; ++i)
 #pragma unroll
     for (int j = 0; j < K; ++j) atomicAdd(dw + (size_t)(c0 + i) * K + j, dwacc[i][j]);
+}
+
+// Backward through shared memory (same idea as se_bwd_tiled_kernel below): a CTA stages DW_T time steps x DW_CT channels
+// of x (with the K-1 rows before) and of dy (with the K-1 rows after) with 16-byte loads that are all in flight at once;
+// a thread then walks DW_SEG steps of two adjacent channels with both windows in registers.
+constexpr int DW_CT = 64, DW_SEG = 32, DW_NSEG = 4, DW_T = DW_SEG * DW_NSEG;
+
+template <int K>
+__global__ void __launch_bounds__(DW_CT / 2 * DW_NSEG)
+dwconv_bwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ halo, const float* __restrict__ w,
+                        const bf16* __restrict__ dy, bf16* __restrict__ dx, bf16* __restrict__ dhalo,
+                        float* __restrict__ dw, int L, int C) {
+  constexpr int H = K - 1, ROWS = DW_T + H, NT = DW_CT / 2 * DW_NSEG, CHK = DW_CT / 8;
+  __shared__ __align__(16) bf16 xS[ROWS][DW_CT];            // x_ext of times t0-H .. t0+DW_T-1
+  __shared__ __align__(16) bf16 gS[ROWS][DW_CT];            // dy of times t0 .. t0+DW_T+H-1
+  __shared__ float dwS[DW_CT][K];
+  const int tid = threadIdx.x, c0 = blockIdx.x * DW_CT, b = blockIdx.z;
+  const int t0 = blockIdx.y * DW_T - H;                     // the first tile also produces the halo rows' gradient
+  for (int idx = tid; idx < ROWS * CHK; idx += NT) {
+    const int row = idx / CHK, ch = idx % CHK;
+    int t = t0 - H + row;
+    const bf16* src = x;
+    int nb = 0;
+    if (t >= 0 && t < L) { src = x + ((size_t)b * L + t) * C + c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * C + c0 + ch * 8; nb = 16; }
+    cp_async16(&xS[row][ch * 8], src, nb);
+    t = t0 + row;
+    const bool in = t >= 0 && t < L;
+    cp_async16(&gS[row][ch * 8], in ? dy + ((size_t)b * L + t) * C + c0 + ch * 8 : dy, in ? 16 : 0);
+  }
+  for (int idx = tid; idx < DW_CT * K; idx += NT) (&dwS[0][0])[idx] = 0.f;
+  cp_async_wait_all();
+  __syncthreads();
+
+  const int cp = tid % (DW_CT / 2), seg = tid / (DW_CT / 2), r0 = seg * DW_SEG;
+  float wr[2][K], dwacc[2][K], xw[K][2], gw[K][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) { wr[i][j] = w[(size_t)(c0 + 2 * cp + i) * K + j]; dwacc[i][j] = 0.f; }
+  auto ld2 = [&](const bf16 (*tile)[DW_CT], int row, float (&f)[2]) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[row][2 * cp]));
+    f[0] = v.x; f[1] = v.y;
+  };
+#pragma unroll
+  for (int j = 0; j < H; ++j) { ld2(xS, r0 + j, xw[j + 1]); ld2(gS, r0 + j, gw[j + 1]); }
+#pragma unroll 4
+  for (int i = 0; i < DW_SEG; ++i) {
+    const int r = r0 + i, t = t0 + r;
+#pragma unroll
+    for (int j = 0; j < H; ++j) { xw[j][0] = xw[j + 1][0]; xw[j][1] = xw[j + 1][1]; gw[j][0] = gw[j + 1][0]; gw[j][1] = gw[j + 1][1]; }
+    ld2(xS, r + H, xw[K - 1]);
+    ld2(gS, r + H, gw[K - 1]);
+    float o[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) { acc += wr[q][j] * gw[K - 1 - j][q]; dwacc[q][j] += gw[0][q] * xw[j][q]; }
+      o[q] = acc;
+    }
+    bf16* dst = nullptr;
+    if (t >= 0 && t < L) dst = dx + ((size_t)b * L + t) * C + c0 + 2 * cp;
+    else if (t < 0 && t >= -H && dhalo) dst = dhalo + ((size_t)b * H + (t + H)) * C + c0 + 2 * cp;
+    if (dst) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(o[0], o[1]);
+  }
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+#pragma unroll
+    for (int j = 0; j < K; ++j) atomicAdd(&dwS[2 * cp + q][j], dwacc[q][j]);
+  __syncthreads();
+  for (int idx = tid; idx < DW_CT * K; idx += NT) atomicAdd(dw + (size_t)(c0 + idx / K) * K + idx % K, (&dwS[0][0])[idx]);
 }
 
 // ------------------------------------------------------------------------------------ Hyena-SE
@@ -314,6 +394,116 @@ __global__ void se_bwd_kernel(const bf16* __restrict__ feat, const bf16* __restr
     for (int j = 0; j < K; ++j) atomicAdd(dw + (size_t)((c0 + i) / dg) * K + j, dwacc[i][j]);
 }
 
+// Backward through shared memory.  A CTA stages a tile of SE_T time steps x SE_CT channels (plus K-1 rows before, for the
+// history of u, and K-1 rows after, for the look-ahead of dconv) with 16-byte loads that are all in flight at once, then
+// every thread walks SE_SEG consecutive steps of ONE channel with the two filter windows in registers, reading the tile
+// from shared memory.  The run-per-thread kernel above issues its global loads inside the serial time loop and is bound
+// by their latency; here the loop only touches shared memory.  Filter gradients are reduced over the lanes of a group
+// by shuffles, over the CTA in shared memory, and leave with one atomic per (group, tap) and CTA.
+constexpr int SE_CT = 32, SE_SEG = 32, SE_NSEG = 4, SE_T = SE_SEG * SE_NSEG;
+
+template <int K>
+__global__ void __launch_bounds__(SE_CT * SE_NSEG)
+se_bwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo, const float* __restrict__ w,
+                    const bf16* __restrict__ dz, bf16* __restrict__ dfeat, bf16* __restrict__ dhalo,
+                    float* __restrict__ dw, int L, int D, int dg, int pregate, int postgate) {
+  constexpr int H = K - 1, ROWS_F = SE_T + 2 * H, ROWS_G = SE_T + H;
+  __shared__ __align__(16) bf16 fS[ROWS_F][3 * SE_CT];      // features of times t0-H .. t0+SE_T+H-1
+  __shared__ __align__(16) bf16 gS[ROWS_G][SE_CT];          // dz of times t0 .. t0+SE_T+H-1
+  __shared__ float dwS[SE_CT][K];
+  const int tid = threadIdx.x, c0 = blockIdx.x * SE_CT, b = blockIdx.z;
+  const int t0 = blockIdx.y * SE_T - (halo ? H : 0);
+  constexpr int FCH = 3 * SE_CT / 8, GCH = SE_CT / 8;       // 16-byte chunks per staged row
+  for (int idx = tid; idx < ROWS_F * FCH; idx += SE_CT * SE_NSEG) {
+    const int row = idx / FCH, ch = idx % FCH, t = t0 - H + row;
+    const bf16* src = feat;
+    int nb = 0;
+    if (t >= 0 && t < L) { src = feat + ((size_t)b * L + t) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    cp_async16(&fS[row][ch * 8], src, nb);
+  }
+  for (int idx = tid; idx < ROWS_G * GCH; idx += SE_CT * SE_NSEG) {
+    const int row = idx / GCH, ch = idx % GCH, t = t0 + row;
+    const bool in = t >= 0 && t < L;
+    cp_async16(&gS[row][ch * 8], in ? dz + ((size_t)b * L + t) * D + c0 + ch * 8 : dz, in ? 16 : 0);
+  }
+  for (int idx = tid; idx < SE_CT * K; idx += SE_CT * SE_NSEG) (&dwS[0][0])[idx] = 0.f;
+  cp_async_wait_all();
+  __syncthreads();
+
+  const int c = tid % SE_CT, seg = tid / SE_CT;
+  const int r0 = seg * SE_SEG;                              // first step of this thread, relative to t0
+  float wr[K], dwacc[K], uw[K], gw[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) { wr[j] = w[(size_t)((c0 + c) / dg) * K + j]; dwacc[j] = 0.f; }
+  // u and dconv at relative step r (time t0 + r): feature row r + H, dz row r
+  auto u_at = [&](int r) -> float {
+    const float x2 = __bfloat162float(fS[r + H][3 * c + 1]), v = __bfloat162float(fS[r + H][3 * c + 2]);
+    return pregate ? x2 * v : v;
+  };
+  auto dconv_at = [&](int r) -> float {
+    const float g = __bfloat162float(gS[r][c]);
+    return postgate ? g * __bfloat162float(fS[r + H][3 * c]) : g;
+  };
+#pragma unroll
+  for (int j = 0; j < H; ++j) { uw[j + 1] = u_at(r0 - H + j); gw[j + 1] = dconv_at(r0 + j); }
+  // The results overwrite this thread's own (x1, x2, v) entries of the tile, so that they can leave with 16-byte
+  // stores.  Everything a thread needs from another segment's rows is therefore read before the barrier: the u history
+  // above and the dconv look-ahead past the end of the segment here.
+  float la[H > 0 ? H : 1];
+#pragma unroll
+  for (int j = 0; j < H; ++j) la[j] = dconv_at(r0 + SE_SEG + j);
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < SE_SEG; ++i) {
+    const int r = r0 + i;
+#pragma unroll
+    for (int j = 0; j < H; ++j) { uw[j] = uw[j + 1]; gw[j] = gw[j + 1]; }
+    const float x2 = __bfloat162float(fS[r + H][3 * c + 1]), v = __bfloat162float(fS[r + H][3 * c + 2]);
+    const float g = __bfloat162float(gS[r][c]);
+    uw[K - 1] = pregate ? x2 * v : v;
+    gw[K - 1] = (i + H < SE_SEG) ? dconv_at(r + H) : la[(i + H - SE_SEG) % (H > 0 ? H : 1)];
+    float conv = 0.f, du = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      conv += wr[j] * uw[j];
+      du += wr[j] * gw[K - 1 - j];
+      dwacc[j] += gw[0] * uw[j];
+    }
+    fS[r + H][3 * c] = __float2bfloat16(postgate ? g * conv : 0.f);
+    fS[r + H][3 * c + 1] = __float2bfloat16(pregate ? du * v : 0.f);
+    fS[r + H][3 * c + 2] = __float2bfloat16(pregate ? du * x2 : du);
+  }
+  // filter gradient: lanes of one group first (groups of 2..32 consecutive channels), then the CTA, then one atomic
+  const int span = dg % 32 == 0 ? 32 : (dg < 32 && (dg & (dg - 1)) == 0 ? dg : 0);
+  if (span > 0) {
+#pragma unroll
+    for (int j = 0; j < K; ++j)
+      for (int o = span >> 1; o > 0; o >>= 1) dwacc[j] += __shfl_xor_sync(0xffffffffu, dwacc[j], o);
+    if ((c & (span - 1)) == 0) {
+#pragma unroll
+      for (int j = 0; j < K; ++j) atomicAdd(&dwS[c][j], dwacc[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < K; ++j) atomicAdd(&dwS[c][j], dwacc[j]);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < SE_CT * K; idx += SE_CT * SE_NSEG) {
+    const float vsum = (&dwS[0][0])[idx];
+    if (vsum != 0.f) atomicAdd(dw + (size_t)((c0 + idx / K) / dg) * K + idx % K, vsum);
+  }
+  for (int idx = tid; idx < SE_T * FCH; idx += SE_CT * SE_NSEG) {
+    const int r = idx / FCH, ch = idx % FCH, t = t0 + r;
+    bf16* dst = nullptr;
+    if (t >= 0 && t < L) dst = dfeat + ((size_t)b * L + t) * 3 * D + 3 * c0 + ch * 8;
+    else if (t < 0 && t >= -H && dhalo) dst = dhalo + ((size_t)b * H + (t + H)) * 3 * D + 3 * c0 + ch * 8;
+    if (dst) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&fS[r + H][ch * 8]);
+  }
+}
+
+static int g_se_bwd_tiled = 1;
+
 static inline int pick_tl(int L, int B, int cvecs) {
   // enough CTAs to fill 148 SMs a few times over, runs long enough to amortise the K-1 overlap
   int tl = 64;
@@ -351,12 +541,21 @@ extern "C" int sb_dwconv_bwd(const void* x, const void* halo, const float* w, co
                              float* dw, int B, int L, int C, int K, cudaStream_t st) {
   if (C % 4) return -1;
   if (B * L == 0) return 0;
+  if (g_se_bwd_tiled && C % DW_CT == 0) {
+    dim3 grid(C / DW_CT, (L + K - 1 + DW_T - 1) / DW_T, B);
+    K_SWITCH(K, (dwconv_bwd_tiled_kernel<KK><<<grid, DW_CT / 2 * DW_NSEG, 0, st>>>((const bf16*)x, (const bf16*)halo, w,
+                                                                                 (const bf16*)dy, (bf16*)dx, (bf16*)dhalo, dw, L, C)));
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int cvecs = C / 4, threads = 128, tl = pick_tl(L, B, cvecs);
   dim3 grid((cvecs + threads - 1) / threads, (L + tl - 1) / tl, B);
   K_SWITCH(K, (dwconv_bwd_kernel<KK, 4><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)halo, w, (const bf16*)dy,
                                                                (bf16*)dx, (bf16*)dhalo, dw, L, C, tl)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// 1: Hyena-SE and depthwise-conv backward through shared-memory tiles; 0: one run per thread straight from global memory.
+extern "C" int sb_se_set_bwd_variant(int tiled) { sb::g_se_bwd_tiled = tiled ? 1 : 0; return 0; }
 
 extern "C" int sb_se_fwd(const void* feat, const void* halo, const float* w, void* z, int B, int L, int D, int G, int K,
                          int pregate, int postgate, cudaStream_t st) {
@@ -373,6 +572,14 @@ extern "C" int sb_se_bwd(const void* feat, const void* halo, const float* w, con
                          float* dw, int B, int L, int D, int G, int K, int pregate, int postgate, cudaStream_t st) {
   if ((D % 4) || (D % G)) return -1;
   if (B * L == 0) return 0;
+  if (g_se_bwd_tiled && D % SE_CT == 0) {
+    const int H = K - 1, steps = L + (halo ? H : 0);
+    dim3 grid(D / SE_CT, (steps + SE_T - 1) / SE_T, B);
+    K_SWITCH(K, (se_bwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (const bf16*)dz,
+                                                                         (bf16*)dfeat, (bf16*)dhalo, dw, L, D, D / G, pregate,
+                                                                         postgate)));
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int cvecs = D / 4, threads = 128, tl = pick_tl(L, B, cvecs);
   dim3 grid((cvecs + threads - 1) / threads, (L + tl - 1) / tl, B);
   K_SWITCH(K, (se_bwd_kernel<KK, 4><<<grid, threads, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (const bf16*)dz,

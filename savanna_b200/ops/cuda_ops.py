@@ -77,6 +77,7 @@ class _Sig:
     sb_mr_bwd = [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_tc_fwd = [P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_tc_set_bwd_variant = [I]
+    sb_se_set_bwd_variant = [I]
     sb_mr_tc_bwd = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
     sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
@@ -161,6 +162,11 @@ def set_mr_backward_variant(streaming: bool) -> None:
     """Hyena-MR tensor-core backward: the streaming kernel (rings of u and g rows, one filter-gradient flush per CTA;
     default) or one independent CTA per 64-row tile."""
     require().sb_mr_tc_set_bwd_variant(int(bool(streaming)))
+
+
+def set_se_backward_variant(tiled: bool) -> None:
+    """Hyena-SE backward: tiles staged through shared memory (default), or one run per thread reading global memory."""
+    require().sb_se_set_bwd_variant(int(bool(tiled)))
 
 
 def set_gemm_pair_mode(mode: int) -> None:

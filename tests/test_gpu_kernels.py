@@ -243,11 +243,19 @@ def test_dwconv(K, halo):
         _close(h.grad, hr.grad, what="dwconv dhalo")
 
 
-@pytest.mark.parametrize("K,G", [(7, 16), (3, 64), (7, 256)])
+@pytest.fixture(params=[True, False], ids=["tiled", "per_thread_run"])
+def se_bwd_variant(request):
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.set_se_backward_variant(request.param)
+    yield request.param
+    cuda_ops.set_se_backward_variant(True)
+
+
+@pytest.mark.parametrize("K,G,L", [(7, 16, 200), (3, 64, 200), (7, 256, 200), (7, 8, 515), (4, 4, 128), (7, 2, 130)])
 @pytest.mark.parametrize("halo", [False, True])
-def test_hyena_se(K, G, halo):
+def test_hyena_se(K, G, L, halo, se_bwd_variant):
     torch.manual_seed(11)
-    B, L, D = 2, 200, 256
+    B, D = 2, 256
     feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
     w = (torch.randn(G, K, device=DEV) * 0.4).requires_grad_()
     h = torch.randn(B, K - 1, 3 * D, device=DEV, dtype=BF, requires_grad=True) if halo else None

@@ -293,3 +293,18 @@ def test_context_parallel_training_halo_state_matches_single_gpu():
     want = _cp_reference()
     over = dict(_CP_OVER, cp_hyena_mr_algo="p2p", cp_hyena_li_algo="state")
     _spawn_args(_w_cp_train, 2, over, want)
+
+
+needs4 = pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
+
+
+@needs4
+@pytest.mark.parametrize("li_algo", ["a2a", "state"])
+def test_context_parallel_training_cp4_matches_single_gpu(li_algo):
+    """cp=4: distinct previous / next neighbours in the halo exchange, two staging buffers with the side-stream prefetch
+    in the ring attention, four-way pulls in the all-to-all and the per-owner dK/dV reduction."""
+    want = _cp_reference()
+    over = dict(_CP_OVER, context_parallel_size=4)
+    if li_algo == "state":
+        over.update(cp_hyena_mr_algo="p2p", cp_hyena_li_algo="state")
+    _spawn_args(_w_cp_train, 4, over, want)
