@@ -128,6 +128,7 @@ def _fwd_bwd(fn, inputs, iters):
     return f_ms, fb_ms - f_ms
 
 
+FWD_TILED_DEFAULT = False
 TILED_DEFAULT = True      # which short-convolution backward variant the library starts with
 
 
@@ -149,6 +150,10 @@ def bench_convs(L, iters, which):
             report(f"featurizer_conv3.fwd.{tag}", f, None, 6 * nb, L=L)
             report(f"featurizer_conv3.bwd.{tag}", b, None, 9 * nb, L=L)
             if backend == "auto":
+                cuda_ops.set_conv_forward_variant(not FWD_TILED_DEFAULT)
+                f2, _ = _fwd_bwd(lambda x, w_: ops.causal_conv1d(x, w_), (proj, w), iters)
+                report("featurizer_conv3.fwd.ours_other_variant", f2, None, 6 * nb, L=L, tiled=not FWD_TILED_DEFAULT)
+                cuda_ops.set_conv_forward_variant(FWD_TILED_DEFAULT)
                 cuda_ops.set_se_backward_variant(not TILED_DEFAULT)
                 _, b2 = _fwd_bwd(lambda x, w_: ops.causal_conv1d(x, w_), (proj, w), iters)
                 report("featurizer_conv3.bwd.ours_other_variant", b2, None, 9 * nb, L=L, tiled=not TILED_DEFAULT)
@@ -159,6 +164,10 @@ def bench_convs(L, iters, which):
             report(f"hyena_se_k7.fwd.{tag}", f, None, 4 * nb, L=L)
             report(f"hyena_se_k7.bwd.{tag}", b, None, 7 * nb, L=L)
             if backend == "auto":
+                cuda_ops.set_conv_forward_variant(not FWD_TILED_DEFAULT)
+                f2, _ = _fwd_bwd(lambda x, w_: ops.hyena_se_inner(x, w_), (feat, w), iters)
+                report("hyena_se_k7.fwd.ours_other_variant", f2, None, 4 * nb, L=L, tiled=not FWD_TILED_DEFAULT)
+                cuda_ops.set_conv_forward_variant(FWD_TILED_DEFAULT)
                 cuda_ops.set_se_backward_variant(not TILED_DEFAULT)
                 _, b2 = _fwd_bwd(lambda x, w_: ops.hyena_se_inner(x, w_), (feat, w), iters)
                 report("hyena_se_k7.bwd.ours_other_variant", b2, None, 7 * nb, L=L, tiled=not TILED_DEFAULT)

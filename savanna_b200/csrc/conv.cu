@@ -169,6 +169,52 @@ __global__ void dwconv_bwd_kernel(const bf16* __restrict__ x, const bf16* __rest
     for (int j = 0; j < K; ++j) atomicAdd(dw + (size_t)(c0 + i) * K + j, dwacc[i][j]);
 }
 
+constexpr int DW_CT_F = 64, DW_SEG_F = 32, DW_NSEG_F = 4;
+
+// Forward through shared memory: the x tile (DW_T steps + K-1 rows of history, DW_CT channels) is staged with
+// asynchronous 16-byte copies, a thread then produces DW_SEG steps of two adjacent channels from shared memory.
+template <int K>
+__global__ void __launch_bounds__(DW_CT_F / 2 * DW_NSEG_F)
+dwconv_fwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ halo, const float* __restrict__ w,
+                        bf16* __restrict__ y, int L, int C) {
+  constexpr int H = K - 1, T = DW_SEG_F * DW_NSEG_F, ROWS = T + H, NT = DW_CT_F / 2 * DW_NSEG_F, CHK = DW_CT_F / 8;
+  __shared__ __align__(16) bf16 xS[ROWS][DW_CT_F];          // x_ext of times t0-H .. t0+T-1
+  const int tid = threadIdx.x, c0 = blockIdx.x * DW_CT_F, b = blockIdx.z, t0 = blockIdx.y * T;
+  for (int idx = tid; idx < ROWS * CHK; idx += NT) {
+    const int row = idx / CHK, ch = idx % CHK, t = t0 - H + row;
+    const bf16* src = x;
+    int nb = 0;
+    if (t >= 0 && t < L) { src = x + ((size_t)b * L + t) * C + c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * C + c0 + ch * 8; nb = 16; }
+    cp_async16(&xS[row][ch * 8], src, nb);
+  }
+  const int cp = tid % (DW_CT_F / 2), seg = tid / (DW_CT_F / 2), r0 = seg * DW_SEG_F;
+  float wr[2][K], win[K][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) wr[i][j] = w[(size_t)(c0 + 2 * cp + i) * K + j];
+  cp_async_wait_all();
+  __syncthreads();
+  auto ld2 = [&](int row, float (&f)[2]) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xS[row][2 * cp]));
+    f[0] = v.x; f[1] = v.y;
+  };
+#pragma unroll
+  for (int j = 0; j < H; ++j) ld2(r0 + j, win[j + 1]);
+#pragma unroll 8
+  for (int i = 0; i < DW_SEG_F; ++i) {
+    const int r = r0 + i, t = t0 + r;
+#pragma unroll
+    for (int j = 0; j < H; ++j) { win[j][0] = win[j + 1][0]; win[j][1] = win[j + 1][1]; }
+    ld2(r + H, win[K - 1]);
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) { o0 += wr[0][j] * win[j][0]; o1 += wr[1][j] * win[j][1]; }
+    if (t < L) *reinterpret_cast<__nv_bfloat162*>(y + ((size_t)b * L + t) * C + c0 + 2 * cp) = __floats2bfloat162_rn(o0, o1);
+  }
+}
+
 // Backward through shared memory (same idea as se_bwd_tiled_kernel below): a CTA stages DW_T time steps x DW_CT channels
 // of x (with the K-1 rows before) and of dy (with the K-1 rows after) with 16-byte loads that are all in flight at once;
 // a thread then walks DW_SEG steps of two adjacent channels with both windows in registers.
@@ -394,13 +440,63 @@ __global__ void se_bwd_kernel(const bf16* __restrict__ feat, const bf16* __restr
     for (int j = 0; j < K; ++j) atomicAdd(dw + (size_t)((c0 + i) / dg) * K + j, dwacc[i][j]);
 }
 
+constexpr int SE_CT = 32, SE_SEG = 32, SE_NSEG = 4, SE_T = SE_SEG * SE_NSEG;
+
+// Forward through shared memory: features of SE_T steps (plus K-1 rows of history) x SE_CT channels staged with
+// asynchronous copies, one channel x SE_SEG steps per thread, outputs collected in shared memory and stored as
+// 16-byte chunks.
+template <int K>
+__global__ void __launch_bounds__(SE_CT * SE_NSEG)
+se_fwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo, const float* __restrict__ w,
+                    bf16* __restrict__ z, int L, int D, int dg, int pregate, int postgate) {
+  constexpr int H = K - 1, ROWS = SE_T + H, NT = SE_CT * SE_NSEG, FCH = 3 * SE_CT / 8, ZCH = SE_CT / 8;
+  __shared__ __align__(16) bf16 fS[ROWS][3 * SE_CT];        // features of times t0-H .. t0+SE_T-1
+  __shared__ __align__(16) bf16 zS[SE_T][SE_CT];
+  const int tid = threadIdx.x, c0 = blockIdx.x * SE_CT, b = blockIdx.z, t0 = blockIdx.y * SE_T;
+  for (int idx = tid; idx < ROWS * FCH; idx += NT) {
+    const int row = idx / FCH, ch = idx % FCH, t = t0 - H + row;
+    const bf16* src = feat;
+    int nb = 0;
+    if (t >= 0 && t < L) { src = feat + ((size_t)b * L + t) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    cp_async16(&fS[row][ch * 8], src, nb);
+  }
+  const int c = tid % SE_CT, seg = tid / SE_CT, r0 = seg * SE_SEG;
+  float wr[K], win[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) wr[j] = w[(size_t)((c0 + c) / dg) * K + j];
+  cp_async_wait_all();
+  __syncthreads();
+  auto u_row = [&](int row) -> float {
+    const float x2 = __bfloat162float(fS[row][3 * c + 1]), v = __bfloat162float(fS[row][3 * c + 2]);
+    return pregate ? x2 * v : v;
+  };
+#pragma unroll
+  for (int j = 0; j < H; ++j) win[j + 1] = u_row(r0 + j);
+#pragma unroll 8
+  for (int i = 0; i < SE_SEG; ++i) {
+    const int r = r0 + i;
+#pragma unroll
+    for (int j = 0; j < H; ++j) win[j] = win[j + 1];
+    win[K - 1] = u_row(r + H);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) acc += wr[j] * win[j];
+    zS[r][c] = __float2bfloat16(postgate ? __bfloat162float(fS[r + H][3 * c]) * acc : acc);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < SE_T * ZCH; idx += NT) {
+    const int r = idx / ZCH, ch = idx % ZCH, t = t0 + r;
+    if (t < L) *reinterpret_cast<uint4*>(z + ((size_t)b * L + t) * D + c0 + ch * 8) = *reinterpret_cast<const uint4*>(&zS[r][ch * 8]);
+  }
+}
+
 // Backward through shared memory.  A CTA stages a tile of SE_T time steps x SE_CT channels (plus K-1 rows before, for the
 // history of u, and K-1 rows after, for the look-ahead of dconv) with 16-byte loads that are all in flight at once, then
 // every thread walks SE_SEG consecutive steps of ONE channel with the two filter windows in registers, reading the tile
 // from shared memory.  The run-per-thread kernel above issues its global loads inside the serial time loop and is bound
 // by their latency; here the loop only touches shared memory.  Filter gradients are reduced over the lanes of a group
 // by shuffles, over the CTA in shared memory, and leave with one atomic per (group, tap) and CTA.
-constexpr int SE_CT = 32, SE_SEG = 32, SE_NSEG = 4, SE_T = SE_SEG * SE_NSEG;
 
 template <int K>
 __global__ void __launch_bounds__(SE_CT * SE_NSEG)
@@ -503,6 +599,7 @@ se_bwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo
 }
 
 static int g_se_bwd_tiled = 1;
+static int g_conv_fwd_tiled = 0;   // depthwise-conv forward through shared-memory tiles
 
 static inline int pick_tl(int L, int B, int cvecs) {
   // enough CTAs to fill 148 SMs a few times over, runs long enough to amortise the K-1 overlap
@@ -531,6 +628,13 @@ extern "C" int sb_dwconv_fwd(const void* x, const void* halo, const float* w, vo
                              cudaStream_t st) {
   if (C % 8) return -1;
   if (B * L == 0) return 0;
+  if (g_conv_fwd_tiled && C % DW_CT_F == 0) {
+    constexpr int T = DW_SEG_F * DW_NSEG_F;
+    dim3 grid(C / DW_CT_F, (L + T - 1) / T, B);
+    K_SWITCH(K, (dwconv_fwd_tiled_kernel<KK><<<grid, DW_CT_F / 2 * DW_NSEG_F, 0, st>>>((const bf16*)x, (const bf16*)halo, w,
+                                                                                     (bf16*)y, L, C)));
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int cvecs = C / 8, threads = 128, tl = pick_tl(L, B, cvecs);
   dim3 grid((cvecs + threads - 1) / threads, (L + tl - 1) / tl, B);
   K_SWITCH(K, (dwconv_fwd_kernel<KK, 8><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)halo, w, (bf16*)y, L, C, tl)));
@@ -556,11 +660,18 @@ extern "C" int sb_dwconv_bwd(const void* x, const void* halo, const float* w, co
 
 // 1: Hyena-SE and depthwise-conv backward through shared-memory tiles; 0: one run per thread straight from global memory.
 extern "C" int sb_se_set_bwd_variant(int tiled) { sb::g_se_bwd_tiled = tiled ? 1 : 0; return 0; }
+extern "C" int sb_conv_set_fwd_variant(int tiled) { sb::g_conv_fwd_tiled = tiled ? 1 : 0; return 0; }
 
 extern "C" int sb_se_fwd(const void* feat, const void* halo, const float* w, void* z, int B, int L, int D, int G, int K,
                          int pregate, int postgate, cudaStream_t st) {
   if ((D % 8) || (D % G)) return -1;
   if (B * L == 0) return 0;
+  if (g_conv_fwd_tiled && D % SE_CT == 0) {
+    dim3 grid(D / SE_CT, (L + SE_T - 1) / SE_T, B);
+    K_SWITCH(K, (se_fwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (bf16*)z, L, D,
+                                                                         D / G, pregate, postgate)));
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int cvecs = D / 8, threads = 128, tl = pick_tl(L, B, cvecs);
   dim3 grid((cvecs + threads - 1) / threads, (L + tl - 1) / tl, B);
   K_SWITCH(K, (se_fwd_kernel<KK, 8><<<grid, threads, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (bf16*)z, L, D, D / G, tl,

@@ -78,6 +78,7 @@ class _Sig:
     sb_mr_tc_fwd = [P, P, P, P, P, I, I, I, I, I, P]
     sb_mr_tc_set_bwd_variant = [I]
     sb_se_set_bwd_variant = [I]
+    sb_conv_set_fwd_variant = [I]
     sb_mr_tc_bwd = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
     sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
@@ -167,6 +168,11 @@ def set_mr_backward_variant(streaming: bool) -> None:
 def set_se_backward_variant(tiled: bool) -> None:
     """Hyena-SE backward: tiles staged through shared memory (default), or one run per thread reading global memory."""
     require().sb_se_set_bwd_variant(int(bool(tiled)))
+
+
+def set_conv_forward_variant(tiled: bool) -> None:
+    """Depthwise (featuriser) convolution forward: tiles staged through shared memory, or one run per thread."""
+    require().sb_conv_set_fwd_variant(int(bool(tiled)))
 
 
 def set_gemm_pair_mode(mode: int) -> None:

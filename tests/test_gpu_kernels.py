@@ -221,11 +221,22 @@ def test_sqnorm_adam():
     assert torch.equal(p, master.to(BF))
 
 
+@pytest.fixture(params=[(True, True), (False, False)], ids=["tiled", "per_thread_run"])
+def conv_variant(request):
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.set_conv_forward_variant(request.param[0])
+    cuda_ops.set_se_backward_variant(request.param[1])
+    yield request.param
+    cuda_ops.set_conv_forward_variant(False)
+    cuda_ops.set_se_backward_variant(True)
+
+
 @pytest.mark.parametrize("K", [3, 4, 7])
 @pytest.mark.parametrize("halo", [False, True])
-def test_dwconv(K, halo):
+@pytest.mark.parametrize("C,L", [(96, 300), (192, 300), (128, 128), (64, 517)])
+def test_dwconv(K, halo, C, L, conv_variant):
     torch.manual_seed(10)
-    B, L, C = 2, 300, 96
+    B = 2
     x = torch.randn(B, L, C, device=DEV, dtype=BF, requires_grad=True)
     w = (torch.randn(C, K, device=DEV) * 0.5).requires_grad_()
     h = torch.randn(B, K - 1, C, device=DEV, dtype=BF, requires_grad=True) if halo else None
@@ -247,8 +258,10 @@ def test_dwconv(K, halo):
 def se_bwd_variant(request):
     from savanna_b200.ops import cuda_ops
     cuda_ops.set_se_backward_variant(request.param)
+    cuda_ops.set_conv_forward_variant(request.param)
     yield request.param
     cuda_ops.set_se_backward_variant(True)
+    cuda_ops.set_conv_forward_variant(False)
 
 
 @pytest.mark.parametrize("K,G,L", [(7, 16, 200), (3, 64, 200), (7, 256, 200), (7, 8, 515), (4, 4, 128), (7, 2, 130)])
