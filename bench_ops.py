@@ -128,7 +128,7 @@ def _fwd_bwd(fn, inputs, iters):
     return f_ms, fb_ms - f_ms
 
 
-FWD_TILED_DEFAULT = False
+FWD_TILED_DEFAULT = True
 TILED_DEFAULT = True      # which short-convolution backward variant the library starts with
 
 

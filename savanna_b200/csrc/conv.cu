@@ -599,7 +599,7 @@ se_bwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo
 }
 
 static int g_se_bwd_tiled = 1;
-static int g_conv_fwd_tiled = 0;   // depthwise-conv forward through shared-memory tiles
+static int g_conv_fwd_tiled = 1;   // depthwise-conv forward through shared-memory tiles
 
 static inline int pick_tl(int L, int B, int cvecs) {
   // enough CTAs to fill 148 SMs a few times over, runs long enough to amortise the K-1 overlap

@@ -227,7 +227,7 @@ def conv_variant(request):
     cuda_ops.set_conv_forward_variant(request.param[0])
     cuda_ops.set_se_backward_variant(request.param[1])
     yield request.param
-    cuda_ops.set_conv_forward_variant(False)
+    cuda_ops.set_conv_forward_variant(True)
     cuda_ops.set_se_backward_variant(True)
 
 
@@ -261,7 +261,7 @@ def se_bwd_variant(request):
     cuda_ops.set_conv_forward_variant(request.param)
     yield request.param
     cuda_ops.set_se_backward_variant(True)
-    cuda_ops.set_conv_forward_variant(False)
+    cuda_ops.set_conv_forward_variant(True)
 
 
 @pytest.mark.parametrize("K,G,L", [(7, 16, 200), (3, 64, 200), (7, 256, 200), (7, 8, 515), (4, 4, 128), (7, 2, 130)])
