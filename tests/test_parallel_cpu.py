@@ -206,6 +206,18 @@ def test_context_parallel_equivalence_p2p_state():
 
 
 @pytest.mark.slow
+@pytest.mark.parametrize("algo", ["a2a", "p2p_state"])
+def test_context_parallel_equivalence_cp4(algo):
+    """cp=4: distinct previous / next neighbours in the halo exchange, three ring steps, four-way all-to-all."""
+    ref_losses = _reference_losses()
+    over = {"context_parallel_size": 4, "use_cp_hyena": True, "use_cp_ring": True,
+            "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
+    if algo == "p2p_state":
+        over.update({"cp_hyena_mr_algo": "p2p", "cp_hyena_li_algo": "state"})
+    run_distributed(_w_equiv, 4, over, ref_losses)
+
+
+@pytest.mark.slow
 def test_zero1_data_parallel_equivalence():
     """dp=2 with micro batch 1 and ZeRO-1 partitioning == one process with micro batch 2."""
     ref_losses = _reference_losses(mb=2)
