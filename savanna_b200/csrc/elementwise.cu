@@ -249,7 +249,7 @@ rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ d
 // ------------------------------------------------------------------------------------ gated MLP activation
 __device__ __forceinline__ float act_fwd(float a, int act) {
   switch (act) {
-    case 0: return a / (1.f + __expf(-a));                                         // silu
+    case 0: return a * __fdividef(1.f, 1.f + __expf(-a));                          // silu
     case 1: return 0.5f * a * (1.f + erff(a * 0.70710678118654752f));              // gelu (erf)
     case 2: return fmaxf(a, 0.f);                                                  // relu
     default: return a;                                                             // identity
@@ -257,12 +257,30 @@ __device__ __forceinline__ float act_fwd(float a, int act) {
 }
 __device__ __forceinline__ float act_grad(float a, int act) {
   switch (act) {
-    case 0: { const float s = 1.f / (1.f + __expf(-a)); return s * (1.f + a * (1.f - s)); }
+    case 0: { const float s = __fdividef(1.f, 1.f + __expf(-a)); return s * (1.f + a * (1.f - s)); }
     case 1: return 0.5f * (1.f + erff(a * 0.70710678118654752f)) + a * 0.3989422804014327f * __expf(-0.5f * a * a);
     case 2: return a > 0.f ? 1.f : 0.f;
     default: return 1.f;
   }
 }
+// act(a) and act'(a) together; SILU = true is the compile-time fast path (one exponential and one approximate reciprocal
+// for both values), otherwise the run-time `act` selects.
+template <bool SILU>
+__device__ __forceinline__ void act_both(float a, int act, float& f, float& g) {
+  if (SILU) {
+    const float s = __fdividef(1.f, 1.f + __expf(-a));
+    f = a * s;
+    g = s + f * (1.f - s);
+  } else {
+    f = act_fwd(a, act);
+    g = act_grad(a, act);
+  }
+}
+template <bool SILU>
+__device__ __forceinline__ float act_only(float a, int act) {
+  return SILU ? a * __fdividef(1.f, 1.f + __expf(-a)) : act_fwd(a, act);
+}
+
 // ab [T, 2F] = [a | b]  ->  h [T, F] = act(a) * b
 __global__ void glu_fwd_kernel(const bf16* __restrict__ ab, bf16* __restrict__ h, size_t T, int F, int act) {
   const int nvF = F >> 3;
@@ -725,6 +743,7 @@ rmsnorm_fwd_fp8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, u
 
 // gated activation with e4m3 output: q [T, F] = sat(act(a) * b * scale) for ab [T, 2F] = [a | b]; F % 16 == 0, each
 // thread handles 16 columns per step (two 16-byte loads per operand, one 16-byte store)
+template <bool SILU>
 __global__ void __launch_bounds__(256)
 glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t T, int F, int act, float* __restrict__ hist,
                    int slots, int cur, float* __restrict__ scale_inv) {
@@ -742,11 +761,11 @@ glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t 
       float a[8], b[8], o[8];
       unpack8(a0, a); unpack8(b0, b);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
+      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_only<SILU>(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
       lo = quant8(o, scale, 0);
       unpack8(a1, a); unpack8(b1, b);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_fwd(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
+      for (int j = 0; j < 8; ++j) { o[j] = __bfloat162float(__float2bfloat16_rn(act_only<SILU>(a[j], act) * b[j])); m = fmaxf(m, fabsf(o[j])); }
       hi = quant8(o, scale, 0);
     }
     reinterpret_cast<uint4*>(q + row * F)[i] = make_uint4(lo.x, lo.y, hi.x, hi.y);
@@ -757,6 +776,7 @@ glu_fwd_fp8_kernel(const bf16* __restrict__ ab, uint8_t* __restrict__ q, size_t 
 
 // gate backward with e5m2 output: dab [T, 2F] = (dh * b * act'(a) | dh * act(a)) as fp8 for the w1|w2 gradient GEMMs;
 // F % 16 == 0, 16 columns per thread and step
+template <bool SILU>
 __global__ void __launch_bounds__(256)
 glu_bwd_fp8_kernel(const bf16* __restrict__ ab, const bf16* __restrict__ dh, uint8_t* __restrict__ dq, size_t T, int F,
                    int act, float* __restrict__ hist, int slots, int cur, float* __restrict__ scale_inv) {
@@ -777,8 +797,10 @@ glu_bwd_fp8_kernel(const bf16* __restrict__ ab, const bf16* __restrict__ dh, uin
       unpack8(av[h], a); unpack8(bv[h], b); unpack8(gv[h], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        da[j] = __bfloat162float(__float2bfloat16_rn(g[j] * b[j] * act_grad(a[j], act)));
-        db[j] = __bfloat162float(__float2bfloat16_rn(g[j] * act_fwd(a[j], act)));
+        float f, dg;
+        act_both<SILU>(a[j], act, f, dg);
+        da[j] = __bfloat162float(__float2bfloat16_rn(g[j] * b[j] * dg));
+        db[j] = __bfloat162float(__float2bfloat16_rn(g[j] * f));
         m = fmaxf(m, fmaxf(fabsf(da[j]), fabsf(db[j])));
       }
       qa[h] = quant8(da, scale, 1); qb[h] = quant8(db, scale, 1);
@@ -979,8 +1001,9 @@ extern "C" int sb_glu_fwd_fp8(const void* ab, void* q, long long T, int F, int a
                               float* scale_inv, cudaStream_t st) {
   if ((F % 16) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (T == 0) return 0;
-  glu_fwd_fp8_kernel<<<grid_for((size_t)T * (F / 16), 256), 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist,
-                                                                        slots, cur, scale_inv);
+  const int g = grid_for((size_t)T * (F / 16), 256);
+  if (act == 0) glu_fwd_fp8_kernel<true><<<g, 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist, slots, cur, scale_inv);
+  else glu_fwd_fp8_kernel<false><<<g, 256, 0, st>>>((const bf16*)ab, (uint8_t*)q, (size_t)T, F, act, hist, slots, cur, scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -989,7 +1012,10 @@ extern "C" int sb_glu_bwd_fp8(const void* ab, const void* dh, void* dq, long lon
                               int cur, float* scale_inv, cudaStream_t st) {
   if ((F % 16) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (T == 0) return 0;
-  glu_bwd_fp8_kernel<<<grid_for((size_t)T * (F / 16), 256), 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F,
-                                                                        act, hist, slots, cur, scale_inv);
+  const int g = grid_for((size_t)T * (F / 16), 256);
+  if (act == 0) glu_bwd_fp8_kernel<true><<<g, 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F, act, hist, slots,
+                                                          cur, scale_inv);
+  else glu_bwd_fp8_kernel<false><<<g, 256, 0, st>>>((const bf16*)ab, (const bf16*)dh, (uint8_t*)dq, (size_t)T, F, act, hist, slots, cur,
+                                                   scale_inv);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
