@@ -11,6 +11,11 @@ working on files written here and its checkpoints load here.
         optimizer_state_dict (ZeRO stage-1 shaped, see parallel/zero.py), ds_config, ds_version
     <save>/global_step<N>/configs/*.yml             the raw YAML files of the run
 
+With pipeline stages (pipe_parallel_size > 1) the files follow DeepSpeed's pipeline engine: the module is written
+as one file per layer slot, `layer_<IDX:02d>-model_<TP:02d>-model_states.pt` (keys without the `sequential.<IDX>.`
+prefix; a tied embedding held by two stages is written by the first), and the `mp_rank_` number of the engine and
+optimizer files is the combined model rank `pipe_stage * tp + tp_rank`, so no two stages share a path.
+
 Behaviour (reference: savanna/checkpointing.py:153-571): tag `global_step<N>`; `latest` is reconciled
 with the directories on disk (the older of the two wins, so a half-written newest checkpoint is
 skipped); keep-last-N deletion; optional background (async) writing finalised at the next step;
@@ -39,6 +44,7 @@ from ..parallel import state
 
 DS_VERSION = "0.14.0+savanna_b200." + __version__
 _ASYNC: Dict[str, threading.Thread] = {}
+_PENDING: list = []          # (cfg, root, dir, iteration) of background saves whose `latest` is not yet written
 
 ARGS_TO_CHECK = ("num_layers", "hidden_size", "num_attention_heads", "max_position_embeddings", "make_vocab_size_divisible_by",
                  "padded_vocab_size", "tokenizer_type", "model_parallel_size")
@@ -54,6 +60,30 @@ def model_states_name(tp_rank: int) -> str:
 
 def optim_states_name(dp_rank: int, tp_rank: int, bf16: bool) -> str:
     return f"{'bf16_' if bf16 else ''}zero_pp_rank_{dp_rank}_mp_rank_{tp_rank:02d}_optim_states.pt"
+
+
+def layer_states_name(layer_idx: int, tp_rank: int) -> str:
+    return f"layer_{layer_idx:02d}-model_{tp_rank:02d}-model_states.pt"
+
+
+def _model_rank() -> int:
+    """Rank in the `mp_rank_XX` file names: the tensor-parallel rank, or with pipeline stages the combined
+    (stage, tensor-parallel) rank, as DeepSpeed's pipeline grid numbers its model-parallel ranks."""
+    pp = state.get_pipe_parallel_world_size()
+    tp_rank = state.get_model_parallel_rank()
+    if pp <= 1:
+        return tp_rank
+    return state.get_pipe_parallel_rank() * state.get_model_parallel_world_size() + tp_rank
+
+
+def _split_by_layer(module_sd: Dict) -> Dict[int, Dict]:
+    out: Dict[int, Dict] = {}
+    for k, v in module_sd.items():
+        m = re.match(r"sequential\.(\d+)\.(.+)$", k)
+        if m is None:
+            raise KeyError(f"module key {k!r} does not belong to a layer slot")
+        out.setdefault(int(m.group(1)), OrderedDict())[m.group(2)] = v
+    return out
 
 
 def _barrier():
@@ -113,7 +143,8 @@ def _client_state(trainer) -> Dict:
         sd["np_rng_state"] = np.random.get_state()
         sd["torch_rng_state"] = torch.get_rng_state()
         sd["cuda_rng_state"] = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
-        sd["rng_tracker_states"] = {}
+        from ..parallel.random import get_cuda_rng_tracker
+        sd["rng_tracker_states"] = get_cuda_rng_tracker().get_states()
     return sd
 
 
@@ -145,11 +176,30 @@ def _to_cpu(obj):
     return obj
 
 
-def finalize_async_save(blocking: bool = True) -> None:
+def finalize_async_save(blocking: bool = True) -> bool:
+    """Complete background checkpoint writes.  Non-blocking: returns False while any rank is still writing (the
+    ranks agree through one small all-reduce, so either all publish or none).  Blocking: joins the writers.
+    Returns True when nothing is pending any more."""
+    if not _ASYNC and not _PENDING:
+        return True
+    busy = any(th.is_alive() for th in _ASYNC.values())
+    if not blocking and dist.is_available() and dist.is_initialized():
+        flag = torch.tensor([1.0 if busy else 0.0])
+        if dist.get_backend() == "nccl":
+            flag = flag.cuda()
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        busy = bool(flag.item() > 0)
+    if busy and not blocking:
+        return False
     for tag, th in list(_ASYNC.items()):
-        if blocking or not th.is_alive():
-            th.join()
-            _ASYNC.pop(tag, None)
+        th.join()
+        _ASYNC.pop(tag, None)
+    pending = list(_PENDING)
+    _PENDING.clear()
+    for cfg, root, d, it in pending:
+        _barrier()
+        _publish(cfg, root, d, it)
+    return True
 
 
 def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
@@ -158,6 +208,8 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
     root = cfg.save
     d = checkpoint_dir(root, it)
     tp_rank = state.get_model_parallel_rank()
+    mp_rank = _model_rank()
+    pp = state.get_pipe_parallel_world_size()
     zero_rank = state.get_sequence_data_parallel_rank()
     bf16 = cfg.precision == "bfloat16"
     finalize_async_save(True)
@@ -170,6 +222,13 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
         module_sd = {k: v.detach().clone() for k, v in trainer.model.state_dict().items()} \
             if (full is not None and zero_rank == 0) else (trainer.model.state_dict() if zero_rank == 0 else None)
     if zero_rank == 0:
+        if pp > 1:
+            # one file per layer slot of this stage; a tied embedding copy on the last stage is not written again
+            for idx, sd in _split_by_layer(module_sd).items():
+                if idx == 0 and state.get_pipe_parallel_rank() != 0:
+                    continue
+                files[os.path.join(d, layer_states_name(idx, tp_rank))] = sd
+            module_sd = None
         ms = {
             "module": module_sd,
             "buffer_names": [n for n, _ in trainer.model.named_buffers()],
@@ -189,9 +248,9 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
             "ds_version": DS_VERSION,
         }
         ms.update(_client_state(trainer))
-        files[os.path.join(d, model_states_name(tp_rank))] = ms
+        files[os.path.join(d, model_states_name(mp_rank))] = ms
     if not cfg.no_save_optim and hasattr(trainer.optimizer, "state_dict"):
-        files[os.path.join(d, optim_states_name(zero_rank, tp_rank, bf16))] = {
+        files[os.path.join(d, optim_states_name(zero_rank, mp_rank, bf16))] = {
             "optimizer_state_dict": trainer.optimizer.state_dict(),
             "ds_config": cfg.engine_config,
             "ds_version": DS_VERSION,
@@ -215,11 +274,20 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
             for name, text in cfg.config_files.items():
                 with open(os.path.join(cdir, name), "w") as fh:
                     fh.write(text)
-    if not cfg.async_save:
-        _barrier()
-    else:
-        finalize_async_save(True)
-        _barrier()
+    if cfg.async_save:
+        # The writer threads keep running while training continues; `latest`, pruning and uploads wait until every
+        # rank's files are complete: at the trainer's next step (`finalize_async_save(False)` polls), at the next
+        # save, or at exit (`finalize_async_save(True)`).
+        _PENDING.append((cfg, root, d, it))
+        print_rank_0(f"  checkpoint at iteration {it}: writing {d} in the background")
+        return d
+    _barrier()
+    _publish(cfg, root, d, it)
+    return d
+
+
+def _publish(cfg, root: str, d: str, it: int) -> None:
+    """All ranks' files of checkpoint `d` are on disk: point `latest` at it, prune, upload."""
     if _rank() == 0:
         with open(os.path.join(root, "latest"), "w") as fh:
             fh.write(f"global_step{it}")
@@ -229,14 +297,16 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
             _upload(cfg, d)
     _barrier()
     print_rank_0(f"  saved checkpoint at iteration {it} to {d}")
-    return d
 
 
 def _delete_old(root: str, keep: int) -> None:
     steps = sorted(int(re.match(r"global_step(\d+)$", os.path.basename(p)).group(1))
                    for p in glob.glob(os.path.join(root, "global_step*")) if re.match(r"global_step(\d+)$", os.path.basename(p)))
     for s in steps[:-keep] if keep > 0 else []:
-        shutil.rmtree(os.path.join(root, f"global_step{s}"), ignore_errors=True)
+        d = os.path.join(root, f"global_step{s}")
+        if os.path.exists(os.path.join(d, ".uploading")):
+            continue                                 # an upload of this directory has not finished: keep it
+        shutil.rmtree(d, ignore_errors=True)
 
 
 def _upload(cfg, ckpt_dir: str, retries: int = 3) -> None:
@@ -286,13 +356,25 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
         return 0
     d = checkpoint_dir(load_dir, it)
     tp_rank = state.get_model_parallel_rank()
+    mp_rank = _model_rank()
     zero_rank = state.get_sequence_data_parallel_rank()
-    path = os.path.join(d, model_states_name(tp_rank))
+    path = os.path.join(d, model_states_name(mp_rank))
     if not os.path.isfile(path):
         raise FileNotFoundError(f"checkpoint file {path} not found")
     dev = trainer.device
     ms = torch.load(path, map_location="cpu", weights_only=False)
     _check_args(cfg, ms.get("args"))
+    if ms.get("module") is None:
+        # pipeline layout: collect this stage's layer slots from the per-layer files
+        module = OrderedDict()
+        slots = sorted({int(k.split(".")[1]) for k in trainer.model.state_dict().keys()})
+        for idx in slots:
+            lp = os.path.join(d, layer_states_name(idx, tp_rank))
+            if not os.path.isfile(lp):
+                raise FileNotFoundError(f"checkpoint file {lp} not found")
+            for k, v in torch.load(lp, map_location="cpu", weights_only=False).items():
+                module[f"sequential.{idx}.{k}"] = v
+        ms["module"] = module
     full = getattr(trainer.optimizer, "full_params", None)          # ZeRO-3: load into whole parameters, re-shard after
     with (full(writeback=True) if full is not None else contextlib.nullcontext()):
         missing, unexpected = trainer.model.load_state_dict(ms["module"], strict=False)
@@ -304,7 +386,7 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
     opt = trainer.optimizer
     bf16 = cfg.precision == "bfloat16"
     if not module_only and hasattr(opt, "load_state_dict"):
-        opath = os.path.join(d, optim_states_name(zero_rank, tp_rank, bf16))
+        opath = os.path.join(d, optim_states_name(zero_rank, mp_rank, bf16))
         if os.path.isfile(opath):
             osd = torch.load(opath, map_location=dev, weights_only=False)
             opt.load_state_dict(osd["optimizer_state_dict"])
@@ -332,6 +414,9 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
             torch.set_rng_state(ms["torch_rng_state"])
             if torch.cuda.is_available() and ms.get("cuda_rng_state") is not None and dev.type == "cuda":
                 torch.cuda.set_rng_state(ms["cuda_rng_state"])
+            if ms.get("rng_tracker_states"):
+                from ..parallel.random import get_cuda_rng_tracker
+                get_cuda_rng_tracker().set_states(ms["rng_tracker_states"])
     if cfg.checkpoint_validation_with_forward_pass and "checkpoint_validation_logits" in ms:
         _validate_logits(trainer, ms)
     _barrier()

@@ -110,7 +110,9 @@ class FusedZeroStep:
                 raise RuntimeError(f"zero_reduce_scatter failed ({rc})")
             self.cuda_ops._count()
             shards.append(out)
-        inv = 1.0 / opt.reduce_world
+        inv = opt.grad_scale()                      # mean over data-parallel replicas, sum over context-parallel ranks
+        if opt.grad_divisor:
+            inv = inv / opt.grad_divisor
         sq = self._sq * (inv * inv)
         dist.all_reduce(sq, group=opt.group)
         tp = state.get_model_parallel_world_size()

@@ -3,13 +3,14 @@
 Each stage owns a contiguous range of blocks (`Backbone(layer_range=...)`); the first stage also owns the
 embedding, the last stage the final norm and the logits (with tied embeddings it holds a copy of the
 embedding whose gradient is all-reduced with the first stage's after every step).  One optimizer step runs
-the `gradient_accumulation_steps` micro-batches through an all-forward / all-backward schedule; activations
-and their gradients travel as [B, L, D] tensors.  Role of the reference's DeepSpeed PipelineModule /
+the `gradient_accumulation_steps` micro-batches through the one-forward-one-backward (1F1B) schedule, so a stage
+holds the activations of at most `stages - stage` micro-batches; activations and their gradients travel as
+[B, L, D] tensors, the two directions of a steady-state exchange posted together.  Role of the reference's DeepSpeed PipelineModule /
 PipelineEngine use (savanna/model/backbone.py:219-284, savanna/training.py:1517-1546).
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -58,55 +59,101 @@ def _sync_tied_embedding_grads(model) -> None:
     w.grad.add_(other)
 
 
+def _exchange(send: Optional[torch.Tensor], send_to: int, recv_like: Optional[Tuple], recv_from: int):
+    """One batched point-to-point round: optionally send `send` to `send_to` and receive a tensor of shape / dtype
+    `recv_like` from `recv_from`.  Both directions are posted together (`batch_isend_irecv`), which is what lets two
+    neighbouring stages swap an activation and a gradient without ordering their blocking calls."""
+    ops, buf = [], None
+    if send is not None and send_to >= 0:
+        ops.append(dist.P2POp(dist.isend, send.contiguous(), send_to))
+    if recv_like is not None and recv_from >= 0:
+        shape, dtype, dev = recv_like
+        buf = torch.empty(shape, dtype=dtype, device=dev)
+        ops.append(dist.P2POp(dist.irecv, buf, recv_from))
+    if ops:
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+    return buf
+
+
 def pipeline_train_step(trainer, data_iterator) -> torch.Tensor:
+    """One optimizer step on the 1F1B schedule: stage s runs `pp - 1 - s` warm-up forwards, then alternates one
+    forward with one backward, then drains its remaining backwards.  At most `pp - s` micro-batches' activations are
+    alive on a stage, whatever the accumulation depth (the all-forward / all-backward order keeps all of them)."""
     cfg, model, dev = trainer.cfg, trainer.model, trainer.device
     prev, nxt = _neighbours()
     first, last = prev < 0, nxt < 0
     B, L, D = cfg.train_micro_batch_size_per_gpu, cfg.seq_length, cfg.hidden_size
+    if state.get_context_parallel_world_size() > 1:
+        L = L // state.get_context_parallel_world_size()
     if cfg.sequence_parallel and state.get_model_parallel_world_size() > 1:
         L = L // state.get_model_parallel_world_size()
-    dtype = cfg.params_dtype
+    act = ((B, L, D), cfg.params_dtype, dev)
     model.train()
     trainer.optimizer.zero_grad()
-    saved: List[Tuple[torch.Tensor, torch.Tensor]] = []
     total = torch.zeros((), device=dev)
     gas = trainer.gas
-    for _ in range(gas):
+    pp, stage = model.num_stages, model.stage
+    warmup = min(pp - stage - 1, gas)
+    steady = gas - warmup
+    live: List[Tuple[Optional[torch.Tensor], torch.Tensor]] = []      # (stage input, stage output) awaiting backward
+    trainer.pipeline_peak_live = 0
+
+    def forward(x_in):
+        nonlocal total
         b = batch_mod.get_batch(cfg, data_iterator, dev) if (first or last) else None
         if first:
             tokens = b["tokens"]
             if cfg.to_upper in ("upper", "weighted", "normalized_weighted"):
                 tokens = batch_mod.to_upper_bytes(tokens)
-            x_in = None
             out = model(tokens, b["positions"], return_hidden=not last)
         else:
-            x_in = torch.empty((B, L, D), dtype=dtype, device=dev)
-            dist.recv(x_in, prev)
             x_in.requires_grad_()
-            positions = b["positions"] if b is not None else torch.arange(cfg.seq_length, device=dev)
+            positions = b["positions"] if b is not None else torch.arange(L, device=dev)
             out = model(None, positions, hidden_in=x_in, return_hidden=not last)
         if last:
             loss = trainer.compute_loss(out, b)
             total += loss.detach()
             out = loss / gas
-        else:
-            dist.send(out.detach().contiguous(), nxt)
-        saved.append((x_in, out))
-    for x_in, out in reversed(saved):
+        live.append((x_in, out))
+        trainer.pipeline_peak_live = max(trainer.pipeline_peak_live, len(live))
+        return out
+
+    def backward(g):
+        x_in, out = live.pop(0)
         if last:
             out.backward()
         else:
-            g = torch.empty_like(out)
-            dist.recv(g, nxt)
             out.backward(g)
-        if not first:
-            dist.send(x_in.grad.contiguous(), prev)
+        return None if first else x_in.grad
+
+    x_in = None
+    for _ in range(warmup):
+        x_in = _exchange(None, -1, act, prev)
+        out = forward(x_in)
+        _exchange(out.detach(), nxt, None, -1)
+    if steady > 0:
+        x_in = _exchange(None, -1, act, prev)
+    for i in range(steady):
+        out = forward(x_in)
+        g = _exchange(None if last else out.detach(), nxt, None if last else act, nxt)
+        dx = backward(g)
+        if i == steady - 1:
+            _exchange(dx, prev, None, -1)
+        else:
+            x_in = _exchange(dx, prev, act, prev)
+    for _ in range(warmup):
+        g = _exchange(None, -1, act, nxt)
+        dx = backward(g)
+        _exchange(dx, prev, None, -1)
     _sync_tied_embedding_grads(model)
     trainer._sync_replicated_grads()
     trainer.grad_norm = trainer.optimizer.step()
     trainer.lr_scheduler.step()
     trainer.iteration += 1
     trainer.tokens_seen += cfg.train_batch_size * cfg.seq_length
+    if trainer.watchdog is not None:
+        trainer.watchdog.beat(trainer.iteration)
     # everyone reports the last stage's loss
     loss = total / gas
     ranks = state.get_pipe_parallel_ranks()

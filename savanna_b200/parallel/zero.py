@@ -88,13 +88,21 @@ class ZeroOptimizer:
     def __init__(self, param_groups: List[Dict], lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, adamw: bool = True, clip_grad: float = 0.0,
                  group=None, group_ranks: Optional[List[int]] = None, comm_path: str = "nccl",
-                 grad_divisor: Optional[float] = None, partition: bool = True, allocator=None):
+                 grad_divisor: Optional[float] = None, partition: bool = True, allocator=None,
+                 sum_ranks: Optional[int] = None):
         self.group = group
         ranks = group_ranks or [0]
         self.world = len(ranks) if partition else 1
         me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
         self.rank = ranks.index(me) if (partition and me in ranks) else 0
         self.reduce_world = len(ranks)
+        # The reduction group is data x context parallel.  The loss of a context-parallel rank is its local
+        # numerator over the GLOBAL token count (models/losses.py), so the ranks of one replica hold partial
+        # gradients that must be SUMMED; only the data-parallel replicas are averaged (DeepSpeed divides by
+        # dp_world / sequence_parallel_size for the same reason).
+        self.sum_ranks = int(sum_ranks) if sum_ranks else state.get_context_parallel_world_size()
+        if self.reduce_world % max(1, self.sum_ranks) != 0:
+            self.sum_ranks = 1
         self.partition = partition
         self.betas, self.eps, self.adamw = betas, eps, adamw
         self.clip_grad = clip_grad or 0.0
@@ -137,7 +145,7 @@ class ZeroOptimizer:
             return shard
         if not self.partition:
             dist.all_reduce(g.flat_grad, group=self.group)
-            g.flat_grad.div_(self.reduce_world)
+            g.flat_grad.mul_(self.grad_scale())
             return g.flat_grad
         backend = dist.get_backend(self.group)
         if backend == "gloo":
@@ -145,6 +153,11 @@ class ZeroOptimizer:
         else:
             dist.reduce_scatter_tensor(shard, g.flat_grad, group=self.group)
         return shard
+
+    def grad_scale(self) -> float:
+        """Factor that turns the SUM over the reduction group into the step's gradient: mean over the
+        data-parallel replicas, sum over the context-parallel ranks of a replica."""
+        return float(self.sum_ranks) / float(self.reduce_world)
 
     def _all_gather(self, g: FlatGroup) -> None:
         if self.world == 1:
@@ -169,7 +182,7 @@ class ZeroOptimizer:
             return self.fused.step(self)
         self.step_count += 1
         shards = [self._reduce_scatter(g) for g in self.groups]
-        inv = 1.0 / self.reduce_world if (self.reduce_world > 1 and self.partition) else 1.0
+        inv = self.grad_scale() if (self.reduce_world > 1 and self.partition) else 1.0
         if self.grad_divisor:
             inv = inv / self.grad_divisor
         sq = None

@@ -151,7 +151,8 @@ class PartitionedZeroOptimizer:
     def __init__(self, param_groups: List[Dict], unit_modules: Sequence[torch.nn.Module], stage: int, lr: float,
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = True,
                  clip_grad: float = 0.0, group=None, group_ranks: Optional[List[int]] = None,
-                 grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True):
+                 grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
+                 sum_ranks: Optional[int] = None):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
         self.stage = stage
@@ -161,6 +162,10 @@ class PartitionedZeroOptimizer:
         me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
         self.rank = ranks.index(me) if me in ranks else 0
         self.reduce_world = self.world
+        # context-parallel ranks hold partial gradients of one replica (summed); replicas are averaged
+        self.sum_ranks = int(sum_ranks) if sum_ranks else state.get_context_parallel_world_size()
+        if self.reduce_world % max(1, self.sum_ranks) != 0:
+            self.sum_ranks = 1
         self.betas, self.eps, self.adamw = betas, eps, adamw
         self.clip_grad = clip_grad or 0.0
         self.grad_divisor = grad_divisor
@@ -342,7 +347,7 @@ class PartitionedZeroOptimizer:
             self._start_reduce(f)
         self._drain(0)
         self.step_count += 1
-        inv = 1.0 / self.reduce_world
+        inv = float(self.sum_ranks) / float(self.reduce_world)
         if self.grad_divisor:
             inv = inv / self.grad_divisor
         sq = None

@@ -194,8 +194,11 @@ class AdamWScheduleFree(torch.optim.Optimizer):
 class DataParallelOptimizer:
     """Adapter: gradient averaging over the replica group + global-norm clipping around a torch-style optimizer."""
 
-    def __init__(self, inner: torch.optim.Optimizer, clip_grad: float, group, world: int):
+    def __init__(self, inner: torch.optim.Optimizer, clip_grad: float, group, world: int, sum_ranks: int = 1):
         self.inner, self.clip_grad, self.group, self.world = inner, clip_grad or 0.0, group, world
+        # `sum_ranks` ranks of the group (the context-parallel ranks of one replica) hold partial gradients that are
+        # summed; the remaining factor of the group (data-parallel replicas) is averaged
+        self.sum_ranks = sum_ranks if (sum_ranks and world % sum_ranks == 0) else 1
         self.param_groups = inner.param_groups
         for g in self.param_groups:
             g.setdefault("lr_mult", 1.0)
@@ -213,7 +216,7 @@ class DataParallelOptimizer:
         if self.world > 1 and params:
             flat = torch.cat([p.grad.reshape(-1).float() for p in params])
             dist.all_reduce(flat, group=self.group)
-            flat.div_(self.world)
+            flat.mul_(float(self.sum_ranks) / float(self.world))
             off = 0
             for p in params:
                 p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
@@ -259,4 +262,5 @@ def build_generic_optimizer(kind: str, groups: List[Dict], cfg, params: Dict) ->
     else:
         raise ValueError(f"optimizer type {kind!r} is not implemented")
     ranks = state.get_sequence_data_parallel_ranks()
-    return DataParallelOptimizer(inner, cfg.gradient_clipping, state.get_sequence_data_parallel_group(), len(ranks))
+    return DataParallelOptimizer(inner, cfg.gradient_clipping, state.get_sequence_data_parallel_group(), len(ranks),
+                                 sum_ranks=state.get_context_parallel_world_size())

@@ -210,6 +210,29 @@ class Trainer:
         return (loss, logits) if return_logits else loss
 
     # ------------------------------------------------------------------ step
+    def _unwatched(self):
+        """Context for host-side phases that are not steps (checkpoint save, evaluation): the watchdog's step
+        deadline is suspended inside it."""
+        import contextlib
+        return self.watchdog.paused() if self.watchdog is not None else contextlib.nullcontext()
+
+    def check_device_status(self) -> None:
+        """Raise if a device-side bounded wait (peer barrier, mbarrier, fused tensor-parallel pull) gave up since
+        the last check.  Those kernels record a code in a per-device status word and return instead of hanging; a
+        step that continued after one has used stale or partial peer data, so the run must stop and relaunch from
+        the last checkpoint.  Reading the word synchronises with the device, so this is called where the host
+        synchronises anyway: at the logging interval and before a checkpoint is written."""
+        reader = getattr(self, "status_reader", None)    # tests inject a host-side word here
+        if reader is None:
+            if self.device.type != "cuda":
+                return
+            from ..ops import cuda_ops
+            cuda_ops.check_status()
+            return
+        v = int(reader())
+        if v != 0:
+            raise RuntimeError(f"a kernel gave up on a bounded wait: code {(v >> 24) & 0xff}, detail {v & 0xffffff}")
+
     def _mark(self, name: str):
         if self.profiler is not None:
             return self.profiler.mark(name)
@@ -322,7 +345,8 @@ class Trainer:
             self.watchdog.start()
         self.profiler.start()
         if cfg.save and self.iteration == 0 and cfg.save_iters and 0 in cfg.save_iters:
-            save_checkpoint(self)
+            with self._unwatched():
+                save_checkpoint(self)
         try:
             while self.iteration < cfg.train_iters:
                 t0 = time.time()
@@ -330,13 +354,23 @@ class Trainer:
                 self.profiler.step()
                 logger.log_step(loss, time.time() - t0)
                 it = self.iteration
+                if cfg.async_save:
+                    from ..ckpt.io import finalize_async_save
+                    finalize_async_save(blocking=False)  # publishes `latest` once every rank's writer is done
+                if it % max(1, cfg.log_interval or 1) == 0:
+                    self.check_device_status()          # the logger has just read the loss: the device is idle
                 if cfg.save and cfg.save_iters and it in cfg.save_iters:
-                    save_checkpoint(self)
+                    self.check_device_status()          # never write a checkpoint of a corrupted run
+                    with self._unwatched():
+                        save_checkpoint(self)
                 if valid_iter is not None and cfg.eval_interval and it % cfg.eval_interval == 0 and cfg.do_valid != 0:
-                    res = self.evaluate(valid_iter)
+                    with self._unwatched():
+                        res = self.evaluate(valid_iter)
                     logger.log_eval(res, it)
                 if cfg.do_per_ds_valid and cfg.eval_per_ds_interval and it % cfg.eval_per_ds_interval == 0:
-                    for name, res in self.evaluate_per_dataset().items():
+                    with self._unwatched():
+                        per_ds = self.evaluate_per_dataset()
+                    for name, res in per_ds.items():
                         logger.log_eval(res, it, prefix=f"validation/{name}")
                 if cfg.exit_interval and it % cfg.exit_interval == 0:
                     print_rank_0(f"exit_interval reached at iteration {it}")
@@ -347,8 +381,15 @@ class Trainer:
             self.profiler.stop()
             if self.watchdog is not None:
                 self.watchdog.stop()
+            if cfg.async_save:
+                from ..ckpt.io import finalize_async_save
+                finalize_async_save(blocking=True)
         if cfg.save and self.iteration > 0 and (not cfg.save_iters or self.iteration not in cfg.save_iters):
+            self.check_device_status()
             save_checkpoint(self)
+        if cfg.async_save:
+            from ..ckpt.io import finalize_async_save
+            finalize_async_save(blocking=True)
 
 
 # ----------------------------------------------------------------------------- entry

@@ -158,23 +158,32 @@ def _run_steps(cfg, n=3, seed_offset=0, global_batch=None):
             yield {"text": full[dr * mb:(dr + 1) * mb]}
             i += 1
     d = it()
-    losses = [float(tr.train_step(d)) for _ in range(n)]
+    losses, norms = [], []
+    for _ in range(n):
+        losses.append(float(tr.train_step(d)))
+        norms.append(float(tr.grad_norm))
+    tr.grad_norms = norms
     return tr, losses
 
 
-def _w_equiv(rank, world, over, ref_losses):
+def _w_equiv(rank, world, over, ref_losses, ref_norms=None):
     cfg = _tiny_cfg(world, **over)
-    _, losses = _run_steps(cfg)
+    tr, losses = _run_steps(cfg)
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    if ref_norms is not None:
+        # Adam is invariant to the gradient's scale, so equal loss traces do not show a mis-scaled gradient:
+        # the logged global norm (what clipping acts on) must match the single-process value too
+        for a, b in zip(tr.grad_norms, ref_norms):
+            assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (tr.grad_norms, ref_norms)
 
 
-def _reference_losses(mb=2):
-    cfg = _tiny_cfg(1, train_micro_batch_size_per_gpu=mb)
-    _, losses = _run_steps(cfg)
+def _reference_losses(mb=2, with_norms=False, **over):
+    cfg = _tiny_cfg(1, train_micro_batch_size_per_gpu=mb, **over)
+    tr, losses = _run_steps(cfg)
     from savanna_b200.parallel import state
     state.destroy_model_parallel()
-    return losses
+    return (losses, tr.grad_norms) if with_norms else losses
 
 
 @pytest.mark.slow
@@ -191,10 +200,26 @@ def test_sequence_parallel_equivalence():
 
 @pytest.mark.slow
 def test_context_parallel_equivalence_a2a():
-    ref_losses = _reference_losses()
+    ref_losses, ref_norms = _reference_losses(with_norms=True)
     over = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True,
             "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
-    run_distributed(_w_equiv, 2, over, ref_losses)
+    run_distributed(_w_equiv, 2, over, ref_losses, ref_norms)
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("optimizer", ["adam", "sgd"])
+def test_context_parallel_gradient_scale_with_clipping(optimizer):
+    """cp=2 with clipping active (threshold far below the norm) and, for SGD, an optimizer whose step depends on
+    the gradient's scale: loss trace and gradient norm equal the single-process run."""
+    extra = {"gradient_clipping": 0.5}
+    if optimizer == "sgd":
+        extra["optimizer"] = {"type": "sgd", "params": {"lr": 0.05, "momentum": 0.0}}
+        extra["lr"] = 0.05
+    ref_losses, ref_norms = _reference_losses(with_norms=True, **extra)
+    assert min(ref_norms) > 1.0                      # clipping really is active
+    over = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_ring": True,
+            "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"], **extra}
+    run_distributed(_w_equiv, 2, over, ref_losses, ref_norms)
 
 
 @pytest.mark.slow
@@ -209,12 +234,12 @@ def test_context_parallel_equivalence_p2p_state():
 @pytest.mark.parametrize("algo", ["a2a", "p2p_state"])
 def test_context_parallel_equivalence_cp4(algo):
     """cp=4: distinct previous / next neighbours in the halo exchange, three ring steps, four-way all-to-all."""
-    ref_losses = _reference_losses()
+    ref_losses, ref_norms = _reference_losses(with_norms=True)
     over = {"context_parallel_size": 4, "use_cp_hyena": True, "use_cp_ring": True,
             "operator_config": ["hyena_se", "hyena_mr", "hyena", "ring"]}
     if algo == "p2p_state":
         over.update({"cp_hyena_mr_algo": "p2p", "cp_hyena_li_algo": "state"})
-    run_distributed(_w_equiv, 4, over, ref_losses)
+    run_distributed(_w_equiv, 4, over, ref_losses, ref_norms)
 
 
 @pytest.mark.slow
@@ -282,6 +307,73 @@ def test_pipeline_parallel_equivalence():
     """Two pipeline stages (tied embedding on both ends) reproduce the single-process loss trace."""
     ref_losses = _reference_losses()
     run_distributed(_w_equiv, 2, {"pipe_parallel_size": 2, "gradient_accumulation_steps": 1}, ref_losses)
+
+
+def _w_pipeline_1f1b(rank, world, ref_losses):
+    cfg = _tiny_cfg(world, pipe_parallel_size=world, gradient_accumulation_steps=4, train_micro_batch_size_per_gpu=1)
+    tr, losses = _run_steps(cfg, n=2)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    # 1F1B bound on live activations: stages - stage, not the accumulation depth
+    assert tr.pipeline_peak_live == world - rank, (rank, tr.pipeline_peak_live)
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_1f1b_schedule(stages):
+    """4 micro-batches through 2 and 3 stages: same loss trace as one process accumulating the same 4 micro-batches,
+    with the number of live micro-batch activations per stage bounded by the schedule."""
+    cfg = _tiny_cfg(1, gradient_accumulation_steps=4, train_micro_batch_size_per_gpu=1)
+    _, ref_losses = _run_steps(cfg, n=2)
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    run_distributed(_w_pipeline_1f1b, stages, ref_losses)
+
+
+def _w_pipeline_ckpt(rank, world, ref_losses, tmp):
+    """Two stages: 2 steps, save, fresh trainers load and run 2 more steps; the 4 losses equal the single-process trace."""
+    from savanna_b200.ckpt import load_checkpoint, save_checkpoint
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    over = {"pipe_parallel_size": 2, "gradient_accumulation_steps": 1, "save": tmp, "checkpoint_strict_load": True}
+    cfg = _tiny_cfg(world, **over)
+    tr = Trainer(cfg, load=False)
+    mb = cfg.train_micro_batch_size_per_gpu
+
+    def it(start):
+        i = start
+        while True:
+            yield {"text": acgt_batch(mb, cfg.seq_length, seed=i)}
+            i += 1
+    d = it(0)
+    first = [float(tr.train_step(d)) for _ in range(2)]
+    ck = save_checkpoint(tr)
+    names = sorted(os.listdir(ck))
+    if rank == 0:
+        # per-layer module files and one engine + optimizer file per stage: no path is shared by two stages
+        assert "mp_rank_00_model_states.pt" in names and "mp_rank_01_model_states.pt" in names, names
+        assert "zero_pp_rank_0_mp_rank_00_optim_states.pt" in names and "zero_pp_rank_0_mp_rank_01_optim_states.pt" in names, names
+        layers = [n for n in names if n.startswith("layer_")]
+        assert len(layers) == len(set(layers)) and "layer_00-model_00-model_states.pt" in layers, names
+        assert len(layers) == cfg.num_layers + 2, layers      # embedding + blocks + final norm
+    cfg2 = _tiny_cfg(world, load=tmp, **over)
+    state.destroy_model_parallel()
+    t2 = Trainer(cfg2, load=True)
+    assert t2.iteration == 2
+    d2 = it(2)
+    second = [float(t2.train_step(d2)) for _ in range(2)]
+    for a, b in zip(first + second, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (first + second, ref_losses)
+
+
+@pytest.mark.slow
+def test_pipeline_checkpoint_save_load_continue(tmp_path):
+    cfg = _tiny_cfg(1)
+    _, ref_losses = _run_steps(cfg, n=4)
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    run_distributed(_w_pipeline_ckpt, 2, ref_losses, str(tmp_path))
 
 
 def test_ring_block_plan_covers_the_causal_mask():
