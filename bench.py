@@ -1,8 +1,9 @@
-"""Headline benchmark: training tokens/s of the Evo-2-7B-style StripedHyena 2 at sequence length 8192,
-ZeRO-1 data parallel, bf16 (BASELINE.json config 3: 32 layers, hidden 4096, 32 heads, byte vocab 512,
-SwiGLU inner 11264, attention at layers 3/10/17/24/31, SE/MR/LI elsewhere; global batch 64 sequences on
-8 GPUs).  Weak scaling: every GPU processes 8 sequences of 8192 tokens per optimizer step (micro-batch 1,
-8 accumulation steps), so the global batch is 8 * N sequences.
+"""Training-throughput benchmark of the Evo-2-style StripedHyena 2 models (synthetic ACGT bytes, random-init weights).
+
+Headline (always): tokens/s of the 7B-style model at sequence length 8192 with ZeRO-1 data parallelism and the
+bf16 + fp8-projection recipe (32 layers, hidden 4096, 32 heads, byte vocab 512, SwiGLU inner 11264, attention at
+layers 3/10/17/24/31, SE/MR/LI elsewhere).  Weak scaling: every GPU processes 8 sequences of 8192 tokens per
+optimizer step (micro-batch 1, 8 accumulation steps), so the global batch is 8 * N sequences (64 on 8 GPUs).
 
     python bench.py --gpus N --steps K --warmup W          (N > 1: launched with torch.distributed.run)
     python bench.py --impl reference ...                   (the unmodified reference, when installable)
@@ -11,7 +12,16 @@ Two timed regions, each bracketed by barrier + synchronize:
   * device-timed (`value`): K optimizer steps on batches already resident on the GPU, CUDA events, max over ranks;
   * end to end (`e2e`): K calls of the public `Trainer.train_step` whose iterator yields pinned host batches
     (host->device copy inside the step) followed by a device->host read of the loss.
-Synthetic data: uniform random bytes of A, C, G, T; weights: random init of the named architecture.
+
+With N in {2, 4, 8} the same JSON line carries an `extra` block, measured in the same process group after the
+headline (1 warm-up + 2 timed steps each, device-timed, max over ranks):
+  * `cp`: the same 7B model with context parallelism over all N GPUs at 16384 tokens per GPU (N = 8 is
+    configs/baseline/evo2_7b_128k_cp8.yml unchanged: 131072 tokens, Hyena-LI all-to-all, SE/MR/featuriser halos,
+    ring attention, activation checkpointing), with the paths actually taken;
+  * `cp_loss_trace`: a 4-layer [SE, MR, LI, attention] slice of that model run for 3 steps with cp = N and with
+    cp = 1 on the same data; the two loss traces must agree;
+  * `tp40b` (N = 8): the 40B-style model with tensor parallel 8 + sequence parallelism (configs/baseline/evo2_40b_tp8.yml).
+A failure or a time-out inside `extra` is recorded there; the headline line is printed regardless.
 """
 from __future__ import annotations
 
@@ -26,6 +36,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+CFG_DIR = os.path.join(ROOT, "configs", "baseline")
 
 
 def parse():
@@ -43,13 +54,17 @@ def parse():
     ap.add_argument("--comm", type=str, default=None, choices=["symm", "nccl"], help="ZeRO collective path (default: config)")
     ap.add_argument("--override", action="append", default=[], metavar="KEY=VALUE",
                     help="debug only: override a config key (YAML value); the result is then not the named config")
+    ap.add_argument("--no-extra", action="store_true", help="skip the context-parallel / tensor-parallel extra block")
+    ap.add_argument("--extra-only", action="store_true", help="debug only: run just the extra block")
+    ap.add_argument("--extra-budget", type=float, default=520.0,
+                    help="seconds after which a still-running extra block is abandoned and the headline line is printed")
     return ap.parse_args()
 
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons while the timed region runs: NVML queries from a thread of this process
-    (three cheap reads every 250 ms).  An `nvidia-smi -lms 200` child, the first implementation, cost 6-10 % of the step
-    time it was meant to observe; it remains only as the fallback when the NVML binding is missing, at 1 s intervals."""
+    (three cheap reads every 250 ms).  An `nvidia-smi` child polling at 200 ms costs 6-10 % of the step time it is
+    meant to observe, so it is only the fallback when the NVML binding is missing, at 1 s intervals."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -163,6 +178,35 @@ def reference_arm(args):
     return 0
 
 
+def describe_metric(cfg, pstate, config_path: str) -> str:
+    """Metric label derived from the configuration that actually ran (model, context, parallel layout)."""
+    L = cfg.seq_length
+    ctx = f"{L // 1024}K" if L % 1024 == 0 else str(L)
+    tp, cp, pp = (pstate.get_model_parallel_world_size(), pstate.get_context_parallel_world_size(),
+                  pstate.get_pipe_parallel_world_size())
+    lay = []
+    if pp > 1:
+        lay.append(f"PP{pp}")
+    if tp > 1:
+        lay.append(f"TP{tp}" + ("+SP" if cfg.sequence_parallel else ""))
+    if cp > 1:
+        lay.append(f"CP{cp}")
+    lay.append(f"ZeRO-{cfg.zero_stage} DP{pstate.get_data_parallel_world_size()}" if cfg.zero_stage else
+               f"DP{pstate.get_data_parallel_world_size()}")
+    size = {(32, 4096): "Evo2-7B-style", (50, 8192): "Evo2-40B-style"}.get((cfg.num_layers, cfg.hidden_size),
+                                                                          f"{cfg.num_layers}L-D{cfg.hidden_size}")
+    return f"train tokens/sec ({size} StripedHyena 2 @{ctx}, {' '.join(lay)}; {os.path.basename(config_path)})"
+
+
+def describe_dtype(cfg, fused_tp_fp8) -> str:
+    if not cfg.use_fp8_linears:
+        return "bf16"
+    d = "bf16 + fp8 (e4m3/e5m2, per-tensor delayed scaling) projection GEMMs"
+    if fused_tp_fp8 is False:
+        d += " [tensor-parallel projections on the fused path run bf16]"
+    return d
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -175,7 +219,9 @@ def main():
     from savanna_b200 import ops
     from savanna_b200.config import GlobalConfig
     from savanna_b200.data.synthetic import ACGT
+    from savanna_b200.parallel import state as pstate
     from savanna_b200.train.trainer import Trainer
+    from savanna_b200.utils.mfu import model_flops_per_token, peak_flops
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -202,17 +248,54 @@ def main():
     fp8_over = {"use_fp8_linears": True, "use_fp8_input_projections": True, "use_fp8_output_projections": True,
                 "use_fp8_mlp_projections": True}
     acgt = torch.from_numpy(ACGT)
+    own = args.impl == "ours" and torch.cuda.is_available()
 
-    def measure(extra_over, with_e2e):
-        """Build the trainer for one precision recipe and time it; returns a dict of results."""
+    def sync(dev):
+        if dist.is_initialized():
+            dist.barrier()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+
+    def release(*objs):
+        """Drop a finished recipe's model, workspaces and parallel groups before the next one is built."""
+        import gc
+        from savanna_b200.parallel import fused_tp, halo
+        fused_tp.teardown()
+        halo.teardown_peer()
+        gc.collect()
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def paths_taken(trainer):
+        """Names of the communication paths this trainer's layout runs on."""
+        from savanna_b200.parallel import fused_tp, halo
+        out = {}
+        fused = getattr(trainer.optimizer, "fused", None)
+        out["zero"] = (("fused peer-memory kernels" + (" (NVLS multimem)" if getattr(fused, "nvls", False) else ""))
+                       if fused is not None else ("nccl" if world > 1 else "single rank"))
+        cfg = trainer.cfg
+        if pstate.get_context_parallel_world_size() > 1:
+            peer = halo._PEER_WS is not None
+            out["halo"] = "peer-memory" if peer else "nccl send/recv"
+            out["hyena_li"] = ("all-to-all " + ("(peer-memory)" if peer else "(nccl)")) if cfg.cp_hyena_li_algo == "a2a" \
+                else "modal-state hand-off"
+            out["attention"] = "ring " + ("(peer-memory K/V, tcgen05 kernels)" if peer else "(nccl)")
+        if pstate.get_model_parallel_world_size() > 1:
+            out["tensor_parallel"] = ("fused all-gather->GEMM / GEMM->reduce-scatter kernels" if fused_tp._WS is not None
+                                      else "nccl collectives + GEMM")
+        return out
+
+    def measure(config_path, extra_over, steps, warmup, with_e2e, same_data_on_all_ranks=False, keep_losses=False):
+        """Build the trainer for one configuration / precision recipe and time it; returns a dict of results."""
         o = dict(over)
         o.update(extra_over)
-        cfg = GlobalConfig.from_ymls([args.config], o)
+        cfg = GlobalConfig.from_ymls([config_path], o)
+        pstate.destroy_model_parallel()
         trainer = Trainer(cfg, load=False)
         dev = trainer.device
         B, L, gas = cfg.train_micro_batch_size_per_gpu, cfg.seq_length, cfg.gradient_accumulation_steps
         tokens_per_step = cfg.train_batch_size * L
-        gen = torch.Generator().manual_seed(1234 + rank)
+        gen = torch.Generator().manual_seed(1234 + (0 if same_data_on_all_ranks else rank))
 
         def host_batch():
             t = acgt[torch.randint(0, 4, (B, L + 1), generator=gen)]
@@ -231,33 +314,31 @@ def main():
             while True:
                 yield {"text": host_batch()}
 
-        def sync():
-            if dist.is_initialized():
-                dist.barrier()
-            if dev.type == "cuda":
-                torch.cuda.synchronize()
-
-        own = args.impl == "ours" and dev.type == "cuda"
         dit = device_iter(gas * 2)
-        for _ in range(args.warmup):
+        losses = []
+        for _ in range(warmup):
             loss = trainer.train_step(dit)
-        sync()
+            if keep_losses:
+                losses.append(float(loss))
+        sync(dev)
         if own:
             from savanna_b200.ops import cuda_ops
             cuda_ops.check_status()
         sampler = ClockSampler(local)
         launches0 = ops.kernel_launch_count() if own else 0
         sampler.start()
-        sync()
+        sync(dev)
         if dev.type == "cuda":
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
+        for _ in range(steps):
             loss = trainer.train_step(dit)
+            if keep_losses:
+                losses.append(float(loss))
         if dev.type == "cuda":
             e1.record()
-        sync()
+        sync(dev)
         wall = time.perf_counter() - t0
         ms = e0.elapsed_time(e1) if dev.type == "cuda" else wall * 1e3
         clocks = sampler.stop()
@@ -265,77 +346,164 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         if dist.is_initialized():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_per_step = float(t.item()) / args.steps
-        from savanna_b200.parallel import state as pstate
+        ms_per_step = float(t.item()) / steps
         par = "".join(f"{n}{v} " for n, v in (("pp", pstate.get_pipe_parallel_world_size()),
                                                ("tp", pstate.get_model_parallel_world_size()),
                                                ("cp", pstate.get_context_parallel_world_size())) if v > 1)
         par += f"dp{pstate.get_data_parallel_world_size()} zero{cfg.zero_stage}" + (" sp" if cfg.sequence_parallel else "")
-        res = {"value": tokens_per_step / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "loss": float(loss),
-               "parallelism": par,
-               "clocks": clocks, "gpu_launches": launches, "cfg": cfg, "e2e": None,
-               "zero_path": (("fused peer-memory kernels" + (" (NVLS multimem)" if getattr(trainer.optimizer.fused, "nvls", False) else ""))
-                             if getattr(trainer.optimizer, "fused", None) is not None
-                             else ("nccl" if world > 1 else "single rank"))}
+        value = tokens_per_step / (ms_per_step / 1e3)
+        peak = peak_flops(cfg)
+        paths = paths_taken(trainer)
+        from savanna_b200.parallel import fused_tp
+        res = {"value": value, "ms_per_step": ms_per_step, "loss": float(loss), "losses": losses,
+               "parallelism": par, "metric": describe_metric(cfg, pstate, config_path),
+               "dtype": describe_dtype(cfg, fused_tp.fp8_active() if pstate.get_model_parallel_world_size() > 1 else None),
+               "clocks": clocks, "gpu_launches": launches, "cfg": cfg, "e2e": None, "paths": paths,
+               "zero_path": paths["zero"], "tokens_per_step": tokens_per_step,
+               "mfu_reference_accounting": (value * model_flops_per_token(cfg) / (world * peak)) if peak else None,
+               "mfu_executed_flops": (value * model_flops_per_token(cfg, executed=True) / (world * peak)) if peak else None}
         if with_e2e:
             hit = host_iter()
-            sync()
+            sync(dev)
             t0 = time.perf_counter()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 loss = trainer.train_step(hit)
                 _ = float(loss)                     # device -> host read of the step's result
-            sync()
+            sync(dev)
             dt = time.perf_counter() - t0
             tt = torch.tensor([dt], dtype=torch.float64, device=dev)
             if dist.is_initialized():
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            res["e2e"] = {"value": tokens_per_step / (float(tt.item()) / args.steps), "unit": "tokens/s",
+            res["e2e"] = {"value": tokens_per_step / (float(tt.item()) / steps), "unit": "tokens/s",
                           "h2d_bytes_per_step": gas * B * (L + 1) * 8, "d2h_bytes_per_step": 4}
         if own:
             cuda_ops.check_status()
-        # release this recipe's model before the next one is built
         del trainer, dit
-        import gc
-        gc.collect()
-        if dev.type == "cuda":
-            torch.cuda.empty_cache()
+        release()
         return res
+
+    def brief(res):
+        keep = ("metric", "value", "ms_per_step", "loss", "parallelism", "dtype", "paths", "tokens_per_step",
+                "mfu_reference_accounting", "mfu_executed_flops", "gpu_launches")
+        d = {k: res[k] for k in keep}
+        d["unit"] = "tokens/s"
+        d["clocks"] = res["clocks"]
+        c = res["cfg"]
+        d["config"] = {"seq_len": c.seq_length, "global_batch": c.train_batch_size, "micro_batch": c.train_micro_batch_size_per_gpu,
+                       "grad_accum": c.gradient_accumulation_steps, "layers": c.num_layers, "hidden": c.hidden_size,
+                       "activation_checkpointing": bool(c.checkpoint_activations)}
+        return d
+
+    def run_extra(out):
+        """Context-parallel and tensor-parallel configurations measured after the headline in the same process group."""
+        def guarded(name, fn):
+            try:
+                out[name] = fn()
+            except Exception as exc:  # noqa: BLE001
+                out[name] = {"error": f"{type(exc).__name__}: {exc}".replace("\n", " ")[:400]}
+                release()
+        cp_cfg = os.path.join(CFG_DIR, "evo2_7b_128k_cp8.yml")
+        L = 16384 * world
+
+        def cp_run():
+            o = dict(fp8_over, context_parallel_size=world, seq_length=L, max_position_embeddings=L)
+            r = brief(measure(cp_cfg, o, 2, 1, False))
+            r["note"] = "7B-style model, context parallel over all GPUs, 16384 tokens per GPU" + \
+                        ("" if world == 8 else " (evo2_7b_128k_cp8.yml with the sequence length and cp size scaled down)")
+            return r
+
+        def trace_check():
+            ops4 = ["hyena_se", "hyena_mr", "hyena", "ring"]
+            Lc = 8192 * world
+            base = dict(fp8_over, num_layers=4, seq_length=Lc, max_position_embeddings=Lc, gradient_accumulation_steps=1,
+                        checkpoint_activations=False)
+            a = measure(cp_cfg, dict(base, context_parallel_size=world, operator_config=ops4), 2, 1, False,
+                        same_data_on_all_ranks=True, keep_losses=True)
+            b = measure(cp_cfg, dict(base, context_parallel_size=1, use_cp_hyena=False, use_cp_ring=False,
+                                     operator_config=["hyena_se", "hyena_mr", "hyena", "flash_v2"]), 2, 1, False,
+                        same_data_on_all_ranks=True, keep_losses=True)
+            gap = max(abs(x - y) / max(1.0, abs(y)) for x, y in zip(a["losses"], b["losses"]))
+            return {"seq_len": Lc, "layers": ops4, "steps": len(a["losses"]), "cp_losses": a["losses"],
+                    "single_shard_losses": b["losses"], "max_rel_gap": gap, "tolerance": 2e-2, "match": bool(gap < 2e-2),
+                    "paths": a["paths"]}
+
+        def tp_run():
+            r = brief(measure(os.path.join(CFG_DIR, "evo2_40b_tp8.yml"), dict(fp8_over), 2, 1, False))
+            r["note"] = "40B-style model, tensor parallel 8 with sequence parallelism, ZeRO-1"
+            return r
+
+        guarded("cp", cp_run)
+        guarded("cp_loss_trace", trace_check)
+        if world == 8:
+            guarded("tp40b", tp_run)
 
     # Headline recipe = the named configuration: bf16 with fp8 projection GEMMs (what the reference's Evo 2 7B configs
     # enable through use_fp8_linears).  The all-bf16 recipe is measured in the same run and reported beside it.
-    use_fp8 = not args.bf16_only and args.impl == "ours" and torch.cuda.is_available()
-    main_res = measure(fp8_over if use_fp8 else {}, not args.no_e2e)
-    other = measure({}, False) if (use_fp8 and not args.skip_second) else None
-    cfg = main_res["cfg"]
-    L, B, gas = cfg.seq_length, cfg.train_micro_batch_size_per_gpu, cfg.gradient_accumulation_steps
-    value, ms_per_step, final_loss = main_res["value"], main_res["ms_per_step"], main_res["loss"]
-    clocks, launches, e2e = main_res["clocks"], main_res["gpu_launches"], main_res["e2e"]
-    zero_path = main_res["zero_path"]
-    from savanna_b200.utils.mfu import model_flops_per_token, peak_flops
-    fpt = model_flops_per_token(cfg)
-    peak = peak_flops(cfg)
-    mfu = value * fpt / (world * peak) if peak else None
-    if rank == 0:
+    use_fp8 = not args.bf16_only and own
+    out = {}
+    if not args.extra_only:
+        main_res = measure(args.config, fp8_over if use_fp8 else {}, args.steps, args.warmup, not args.no_e2e)
+        other = measure(args.config, {}, args.steps, args.warmup, False) if (use_fp8 and not args.skip_second) else None
+        cfg = main_res["cfg"]
+        L, B, gas = cfg.seq_length, cfg.train_micro_batch_size_per_gpu, cfg.gradient_accumulation_steps
+        fpt = model_flops_per_token(cfg)
         out = {
-            "metric": "train tokens/sec (Evo2-7B-style StripedHyena 2 @8K, ZeRO-1 DP)", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "metric": main_res["metric"], "value": main_res["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 + fp8 (e4m3/e5m2, per-tensor scaling) projection GEMMs" if use_fp8 else "bf16",
+            "dtype": main_res["dtype"],
             "data": "synthetic uniform ACGT bytes; random-init weights", "impl": args.impl,
             "config": {"model": (f"{cfg.num_layers}L D{cfg.hidden_size} {cfg.num_attention_heads} heads ffn {cfg.ffn_size} vocab {cfg.padded_vocab_size} ({os.path.basename(args.config)})") if not args.layers
                        else f"DEBUG {args.layers}-layer truncation (not the named config)",
                        "global_batch": cfg.train_batch_size, "seq_len": L, "micro_batch": B, "grad_accum": gas,
-                       "parallelism": main_res["parallelism"], "zero_path": zero_path, "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
-            "mfu_of_measured_bf16_peak": mfu, "mfu_note": "model FLOPs/s over the measured sustained cuBLAS bf16 peak; fp8 projection GEMMs can exceed 1.0 of a bf16 denominator", "model_flops_per_token": fpt, "loss": final_loss,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+                       "parallelism": main_res["parallelism"], "zero_path": main_res["zero_path"],
+                       "l2": "inputs larger than L2 (per-step working set >> 126 MB)"},
+            "mfu_of_measured_bf16_peak": main_res["mfu_reference_accounting"],
+            "mfu_executed_flops": main_res["mfu_executed_flops"],
+            "mfu_note": "model FLOPs/s over the measured sustained cuBLAS bf16 peak; `mfu_of_measured_bf16_peak` uses the "
+                        "reference's accounting (full LxL attention, Hyena-LI as an FFT), `mfu_executed_flops` counts causal "
+                        "attention once and Hyena-LI as the modal recurrence; fp8 projection GEMMs can exceed 1.0 of a bf16 denominator",
+            "model_flops_per_token": fpt, "loss": main_res["loss"],
+            "clocks": main_res["clocks"], "e2e": main_res["e2e"], "gpu_launches": main_res["gpu_launches"],
             "bf16_only": None if other is None else {"value": other["value"], "ms_per_step": other["ms_per_step"],
                                                      "loss": other["loss"], "dtype": "bf16",
-                                                     "mfu_of_measured_peak": (other["value"] * fpt / (world * peak)) if peak else None},
+                                                     "mfu_of_measured_peak": other["mfu_reference_accounting"]},
         }
-        print(json.dumps(out))
+    printed = threading.Event()
+
+    def emit():
+        if rank == 0 and not printed.is_set():
+            printed.set()
+            print(json.dumps(out), flush=True)
+
+    want_extra = own and world in (2, 4, 8) and not args.no_extra and not args.layers and not args.override \
+        and os.path.abspath(args.config) == os.path.join(CFG_DIR, "evo2_7b_8k.yml")
+    if want_extra or (args.extra_only and own and world > 1):
+        extra = {}
+        out["extra"] = extra
+
+        def give_up():
+            # every rank runs this timer from the same barrier, so all leave together; nothing is waited for
+            extra["abandoned"] = f"extra block exceeded {args.extra_budget:.0f} s; partial results kept"
+            emit()
+            sys.stdout.flush()
+            os._exit(0)
+        if dist.is_initialized():
+            dist.barrier()
+        timer = threading.Timer(args.extra_budget, give_up)
+        timer.daemon = True
+        timer.start()
+        try:
+            run_extra(extra)
+        finally:
+            timer.cancel()
+    emit()
     if dist.is_initialized():
-        dist.barrier()
-        dist.destroy_process_group()
+        try:
+            dist.barrier()
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
     return 0
 
 

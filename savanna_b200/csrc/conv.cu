@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_info.h"
+
 namespace sb {
 typedef __nv_bfloat16 bf16;
 
@@ -604,7 +606,7 @@ static int g_conv_fwd_tiled = 1;   // depthwise-conv forward through shared-memo
 static inline int pick_tl(int L, int B, int cvecs) {
   // enough CTAs to fill 148 SMs a few times over, runs long enough to amortise the K-1 overlap
   int tl = 64;
-  while (tl > 16 && (long long)((L + tl - 1) / tl) * B * ((cvecs + 127) / 128) < 148 * 4) tl >>= 1;
+  while (tl > 16 && (long long)((L + tl - 1) / tl) * B * ((cvecs + 127) / 128) < sb::num_sms() * 4) tl >>= 1;
   return tl;
 }
 

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_info.h"
+
 namespace sb {
 
 typedef __nv_bfloat16 bf16;
@@ -812,7 +814,7 @@ glu_bwd_fp8_kernel(const bf16* __restrict__ ab, const bf16* __restrict__ dh, uin
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(hist + cur), __float_as_uint(m));
 }
 
-static inline int grid_for(size_t work, int threads, int cap = 148 * 16) {
+static inline int grid_for(size_t work, int threads, int cap = sb::num_sms() * 16) {
   size_t g = (work + threads - 1) / threads;
   if (g > (size_t)cap) g = cap;
   if (g < 1) g = 1;
@@ -830,7 +832,7 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* w, void* y, float* a_ou
   const int nv = D / 8;
   const int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
   const int vpt = (nv + threads - 1) / threads;
-  const int grid = T < 148 * 4 ? T : 148 * 4;
+  const int grid = T < sb::num_sms() * 4 ? T : sb::num_sms() * 4;
 #define LAUNCH(V) rmsnorm_fwd_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, a_out, T, D, eps, form)
   if (vpt <= 1) LAUNCH(1);
   else if (vpt <= 2) LAUNCH(2);
@@ -841,7 +843,7 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* w, void* y, float* a_ou
 }
 
 // Blocks of the backward kernel for T rows (also the number of rows of the `partial` scratch).
-extern "C" int sb_rmsnorm_bwd_blocks(int T) { return T < 148 * 2 ? (T < 1 ? 1 : T) : 148 * 2; }
+extern "C" int sb_rmsnorm_bwd_blocks(int T) { return T < sb::num_sms() * 2 ? (T < 1 ? 1 : T) : sb::num_sms() * 2; }
 
 // dw: bf16 [D], written (not accumulated); partial is scratch of sb_rmsnorm_bwd_blocks(T) * D floats.  Two launches.
 extern "C" int sb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* a_in, const void* gres, void* dx,
@@ -907,7 +909,7 @@ extern "C" int sb_colsum(const void* x, float* out, int T, int N, cudaStream_t s
   if (N % 8) return -1;
   if (T == 0 || N == 0) return 0;
   const int cblocks = (N + 63) / 64;
-  int rsplit = (148 * 4 + cblocks - 1) / cblocks;
+  int rsplit = (sb::num_sms() * 4 + cblocks - 1) / cblocks;
   if (rsplit > (T + 63) / 64) rsplit = (T + 63) / 64;
   if (rsplit < 1) rsplit = 1;
   const int rows_per_block = (T + rsplit - 1) / rsplit;
@@ -921,13 +923,13 @@ extern "C" int sb_sqnorm(const void* x, const float* wgt, float* out, long long 
   if (n == 0) return 0;
   if (is_bf16 && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wgt)) & 15) && n >= 8) {
     const size_t n8 = (size_t)n / 8;
-    sqnorm_bf16_vec_kernel<<<grid_for(n8, 512, 148 * 4), 512, 0, st>>>((const uint4*)x, (const float4*)wgt, out, n8);
+    sqnorm_bf16_vec_kernel<<<grid_for(n8, 512, sb::num_sms() * 4), 512, 0, st>>>((const uint4*)x, (const float4*)wgt, out, n8);
     const size_t done = n8 * 8;
     if (done < (size_t)n)
       sqnorm_kernel<bf16><<<1, 32, 0, st>>>((const bf16*)x + done, wgt ? wgt + done : nullptr, out, (size_t)n - done);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
-  const int grid = grid_for((size_t)n, 512, 148 * 4);
+  const int grid = grid_for((size_t)n, 512, sb::num_sms() * 4);
   if (is_bf16) sqnorm_kernel<bf16><<<grid, 512, 0, st>>>((const bf16*)x, wgt, out, (size_t)n);
   else sqnorm_kernel<float><<<grid, 512, 0, st>>>((const float*)x, wgt, out, (size_t)n);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -941,12 +943,12 @@ extern "C" int sb_adam(float* master, float* m, float* v, const void* grad, void
                          (reinterpret_cast<uintptr_t>(grad) << 1) | (reinterpret_cast<uintptr_t>(param_out) << 1);
   if (grad_is_bf16 && !(bits & 15) && (n % 4) == 0) {
     const size_t n4 = (size_t)n / 4;
-    adam_bf16_vec_kernel<<<grid_for(n4, 512, 148 * 8), 512, 0, st>>>((float4*)master, (float4*)m, (float4*)v, (const uint2*)grad,
+    adam_bf16_vec_kernel<<<grid_for(n4, 512, sb::num_sms() * 8), 512, 0, st>>>((float4*)master, (float4*)m, (float4*)v, (const uint2*)grad,
                                                                     (uint2*)param_out, n4, lr, b1, b2, eps, wd, bc1, bc2, adamw,
                                                                     scale_ptr, scale_host);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
-  const int grid = grid_for((size_t)n, 512, 148 * 8);
+  const int grid = grid_for((size_t)n, 512, sb::num_sms() * 8);
   if (grad_is_bf16)
     adam_kernel<bf16><<<grid, 512, 0, st>>>(master, m, v, (const bf16*)grad, (bf16*)param_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr, scale_host);
   else
@@ -959,7 +961,7 @@ extern "C" int sb_quantize_fp8(const void* x, void* q, float* amax, float* scale
   if (n % 8) return -1;
   if (n == 0) return 0;
   const size_t n8 = (size_t)n / 8;
-  const int grid = grid_for(n8, 512, 148 * 8);
+  const int grid = grid_for(n8, 512, sb::num_sms() * 8);
   if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return -2;
   amax_kernel<<<grid, 512, 0, st>>>((const bf16*)x, amax, n8);
   quantize_fp8_kernel<<<grid, 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, amax, scale_inv, fmt);
@@ -973,7 +975,7 @@ extern "C" int sb_quantize_fp8_delayed(const void* x, void* q, float* hist, int 
   if ((n % 8) || slots < 3 || cur < 0 || cur >= slots) return -1;
   if (n == 0) return 0;
   const size_t n8 = (size_t)n / 8, n16 = n8 / 2;
-  const int grid = grid_for((n16 + 1) / 2 + 1, 256, 148 * 8);
+  const int grid = grid_for((n16 + 1) / 2 + 1, 256, sb::num_sms() * 8);
   quantize_fp8_delayed_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (uint8_t*)q, n16, n8, hist, slots, cur, scale_inv, fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -986,7 +988,7 @@ extern "C" int sb_rmsnorm_fwd_fp8(const void* x, const void* w, void* q, float* 
   const int nv = D / 8;
   const int threads = nv >= 512 ? 512 : (nv >= 256 ? 256 : (nv >= 128 ? 128 : 64));
   const int vpt = (nv + threads - 1) / threads;
-  const int grid = T < 148 * 4 ? T : 148 * 4;
+  const int grid = T < sb::num_sms() * 4 ? T : sb::num_sms() * 4;
 #define LAUNCH(V) rmsnorm_fwd_fp8_kernel<V><<<grid, threads, 0, st>>>((const bf16*)x, (const bf16*)w, (uint8_t*)q, a_out, T, D, eps, form, hist, slots, cur, scale_inv)
   if (vpt <= 1) LAUNCH(1);
   else if (vpt <= 2) LAUNCH(2);

@@ -404,12 +404,6 @@ __global__ void gather_rows_kernel(Params p) {
   }
 }
 
-static int g_sms = 0;
-static int num_sms() {
-  if (!g_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev); }
-  return g_sms;
-}
-
 }  // namespace tp
 }  // namespace sb
 
@@ -455,7 +449,7 @@ extern "C" int sb_gemm_tp(const void* A, int lda, const void* B, int ldb, int b_
     for (int r = 0; r < rs_world; ++r) p.rs_dst[r] = (__nv_bfloat16*)rs_dst[r];
   } else if (ldc % 8) return -3;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int sms = num_sms();
+  const int sms = sb::num_sms();
   int n_copy = ag ? (n_copy_ctas > 0 ? n_copy_ctas : 16) : 0;
   int n_gemm = sms - n_copy;
   if (tiles < n_gemm) n_gemm = tiles;
@@ -476,7 +470,7 @@ extern "C" int sb_rs_reduce(const void* staging, const void* bias, const void* r
   if (rows == 0) return 0;
   size_t total = (size_t)rows * (N / 8);
   size_t g = (total + 255) / 256;
-  if (g > 148 * 8) g = 148 * 8;
+  if (g > sb::num_sms() * 8) g = sb::num_sms() * 8;
   rs_reduce_kernel<<<(unsigned)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, (const __nv_bfloat16*)bias,
                                                    (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, world, (size_t)rows, N);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -488,6 +482,6 @@ extern "C" int sb_gather_rows(const void* const* src, int world, void* gather, i
   Params p{};
   p.M = M; p.K = K; p.ag_tiles_per_rank = (M / world) / BM; p.ag_src_ld = ld; p.ag_dst = (__nv_bfloat16*)gather;
   for (int r = 0; r < world; ++r) p.ag_src[r] = (const __nv_bfloat16*)src[r];
-  gather_rows_kernel<<<148 * 4, 512, 0, stream>>>(p);
+  gather_rows_kernel<<<sb::num_sms() * 4, 512, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -19,6 +19,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_info.h"
+
 namespace sb {
 typedef __nv_bfloat16 bf16;
 
@@ -670,7 +672,7 @@ extern "C" int sb_mr_tc_bwd(const void* feat, const void* halo, const float* h, 
     const int ctiles = (D + TC_CH - 1) / TC_CH;
     // as many segments as fit in one wave of two CTAs per SM (a partial second wave would double the run time),
     // but no shorter than 8 tiles (the ring prologue costs 4 tiles)
-    int segs = (2 * 148) / (ctiles * B);
+    int segs = (2 * sb::num_sms()) / (ctiles * B);
     if (segs > (n_tiles + 7) / 8) segs = (n_tiles + 7) / 8;
     if (segs < 1) segs = 1;
     const int tps = (n_tiles + segs - 1) / segs;

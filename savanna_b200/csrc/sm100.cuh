@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_info.h"
+
 namespace sb {
 
 constexpr unsigned long long WAIT_BUDGET_NS = 1500ull * 1000ull * 1000ull;  // 1.5 s

@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_info.h"
+
 namespace sb {
 typedef __nv_bfloat16 bf16;
 constexpr int ZMAX = 16;      // max ranks of a partition group on one NVSwitch domain
@@ -204,7 +206,7 @@ extern "C" int sb_zero_reduce_scatter_mm(const void* mc_grad, long long lo, long
   if (n == 0) return 0;
   const size_t n8 = (size_t)n / 8;
   size_t g = (n8 + 512 * MM_U - 1) / (512 * MM_U);
-  if (g > 148 * 4) g = 148 * 4;
+  if (g > sb::num_sms() * 4) g = sb::num_sms() * 4;
   zero_rs_mm_kernel<<<(unsigned)g, 512, 0, st>>>((const uint4*)mc_grad, (size_t)lo / 8, n8, (bf16*)out, norm_weight, sqnorm);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -220,7 +222,7 @@ extern "C" int sb_zero_reduce_scatter(const void* const* grads, int world, int m
   const size_t n8 = (size_t)n / 8;
   auto grid = [&](int u, int per_sm) {
     size_t g = (n8 + 512 * (size_t)u - 1) / (512 * (size_t)u);
-    return (unsigned)(g > 148 * (size_t)per_sm ? 148 * per_sm : g);
+    return (unsigned)(g > sb::num_sms() * (size_t)per_sm ? sb::num_sms() * per_sm : g);
   };
   bf16* o = (bf16*)out;
   if (world <= 2)      zero_rs_kernel<2, 4><<<grid(4, 2), 512, 0, st>>>(pp, world, (size_t)lo / 8, n8, o, norm_weight, sqnorm);
@@ -241,7 +243,7 @@ extern "C" int sb_zero_adam_allgather(float* master, float* m, float* v, const v
   for (int r = 0; r < ZMAX; ++r) pp.p[r] = r < world ? params[(me + r) % world] : nullptr;
   const size_t n8 = (size_t)n / 8;
   size_t g = (n8 + 511) / 512;
-  if (g > 148 * 4) g = 148 * 4;
+  if (g > sb::num_sms() * 4) g = sb::num_sms() * 4;
 #define SB_ADAM(W) zero_adam_kernel<W><<<(unsigned)g, 512, 0, st>>>(master, m, v, (const bf16*)grad, pp, mc_params, world, \
                                                                      (size_t)lo / 8, n8, lr, b1, b2, eps, wd, bc1, bc2, adamw, scale_ptr)
   if (world <= 2) SB_ADAM(2); else if (world <= 4) SB_ADAM(4); else if (world <= 8) SB_ADAM(8); else SB_ADAM(16);

@@ -1,85 +1,91 @@
-"""Batch samplers (reference: savanna/data/samplers.py:6-143).
+"""Batch samplers for data-parallel loading.
 
-DistributedBatchSampler wraps a sequential sampler, groups `batch_size` (= micro batch x data-parallel
-size) indices and yields this rank's slice — contiguous or interleaved — with `start_iter` fast-forward
-for resume.
+`DistributedBatchSampler` cuts an index stream into global batches (micro batch x data-parallel size) and hands
+each rank its share of every batch; `start_iter` skips whole global batches so a resumed run continues where the
+token cursor of the checkpoint points.  `RandomSampler` is an epoch-seeded permutation every rank agrees on.
+Same role as the reference's savanna/data/samplers.py (batch slicing per rank, interleaved or contiguous, resume by
+iteration), written as plain index arithmetic: a batch is materialised with `itertools.islice`, the rank's share is
+one slice, and nothing is carried between epochs.
 """
 from __future__ import annotations
 
+import itertools
+from typing import Iterable, Iterator, List, Optional
+
 import torch
-from torch.utils import data
+from torch.utils.data import Sampler
 
 
-class RandomSampler(data.sampler.Sampler):
-    """Seeded random sampler whose order depends on (epoch, seed) only, so every rank agrees."""
+class RandomSampler(Sampler):
+    """Permutation (or draws with replacement) of `range(len(data_source))` that depends only on `seed + epoch`."""
 
-    def __init__(self, data_source, replacement=False, num_samples=None, seed: int = 0):
-        self.data_source, self.replacement, self._num_samples = data_source, replacement, num_samples
-        self.epoch, self.seed = -1, seed
+    def __init__(self, data_source, replacement: bool = False, num_samples: Optional[int] = None, seed: int = 0):
+        self.data_source = data_source
+        self.replacement = replacement
+        self.requested = num_samples
+        self.seed = seed
+        self.epoch = 0
 
-    @property
-    def num_samples(self):
-        return len(self.data_source) if self._num_samples is None else self._num_samples
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = max(0, int(epoch))
 
-    def __iter__(self):
-        n = len(self.data_source)
-        g = torch.Generator()
-        g.manual_seed(self.seed + max(self.epoch, 0))
+    def __len__(self) -> int:
+        return len(self.data_source) if self.requested is None else self.requested
+
+    def __iter__(self) -> Iterator[int]:
+        gen = torch.Generator().manual_seed(self.seed + self.epoch)
+        population = len(self.data_source)
         if self.replacement:
-            return iter(torch.randint(high=n, size=(self.num_samples,), dtype=torch.int64, generator=g).tolist())
-        return iter(torch.randperm(n, generator=g).tolist())
-
-    def __len__(self):
-        return self.num_samples
-
-    def set_epoch(self, epoch):
-        self.epoch = epoch
+            order = torch.randint(population, (len(self),), generator=gen)
+        else:
+            order = torch.randperm(population, generator=gen)[: len(self)]
+        return iter(order.tolist())
 
 
-class DistributedBatchSampler(data.sampler.BatchSampler):
-    def __init__(self, sampler, batch_size, drop_last, rank=-1, world_size=2, wrap_last=False, interleave=False):
-        super().__init__(sampler, batch_size, drop_last)
-        if rank == -1:
+class DistributedBatchSampler(Sampler):
+    """Yields, per global batch of `batch_size` indices drawn from `sampler`, the indices of data-parallel rank
+    `rank` of `world_size`: a contiguous block (default) or every `world_size`-th index (`interleave`).  The first
+    `start_iter` global batches are skipped without being yielded.  A trailing partial batch is dropped when
+    `drop_last`, otherwise its share for this rank (possibly shorter, possibly empty) is yielded."""
+
+    def __init__(self, sampler: Iterable[int], batch_size: int, drop_last: bool, rank: int = -1, world_size: int = 1,
+                 interleave: bool = False):
+        if batch_size % world_size != 0:
+            raise ValueError(f"global batch {batch_size} is not divisible by the data-parallel size {world_size}")
+        if rank < 0:
             rank = torch.distributed.get_rank()
+        if not 0 <= rank < world_size:
+            raise ValueError(f"rank {rank} outside the data-parallel group of size {world_size}")
+        self.sampler = sampler
+        self.batch_size = batch_size
+        self.drop_last = drop_last
         self.rank, self.world_size = rank, world_size
-        self.sampler.wrap_around = 0
-        self.wrap_around = 0
-        self.wrap_last = wrap_last
-        self.start_iter = 0
         self.interleave = interleave
+        self.start_iter = 0
 
-    def __iter__(self):
-        batch = []
-        i = 0
-        for idx in self.data_iterator(self.sampler, wrap_around=False):
-            batch.append(idx)
-            if len(batch) == self.batch_size:
-                tbatch = self._batch(batch)
-                if i >= self.start_iter:
-                    yield tbatch
-                    self.start_iter = 0
-                i += 1
-                batch = []
-        if len(batch) > 0 and not self.drop_last:
-            if self.wrap_last:
-                self.sampler.wrap_around -= self.batch_size
-                self.wrap_around += len(batch)
-                self.wrap_around %= self.batch_size
-            yield self._batch(batch)
-        if self.wrap_last:
-            self.sampler.wrap_around += self.batch_size
-
-    def data_iterator(self, _iter, wrap_around=False):
-        for i, idx in enumerate(_iter):
-            if i < self.wrap_around % self.batch_size:
-                continue
-            if wrap_around:
-                self.wrap_around += 1
-                self.wrap_around %= self.batch_size
-            yield idx
-
-    def _batch(self, batch):
+    def share(self, global_batch: List[int]) -> List[int]:
         if self.interleave:
-            return batch[self.rank:self.batch_size:self.world_size]
-        per = self.batch_size // self.world_size
-        return batch[self.rank * per:(self.rank + 1) * per]
+            return global_batch[self.rank::self.world_size]
+        per_rank = self.batch_size // self.world_size
+        return global_batch[self.rank * per_rank:(self.rank + 1) * per_rank]
+
+    def __len__(self) -> int:
+        n = len(self.sampler)                       # type: ignore[arg-type]
+        full, rest = divmod(n, self.batch_size)
+        total = full + (1 if rest and not self.drop_last else 0)
+        return max(0, total - self.start_iter)
+
+    def __iter__(self) -> Iterator[List[int]]:
+        stream = iter(self.sampler)
+        # resume: consume the indices of the batches that were already trained on
+        skipped = self.start_iter * self.batch_size
+        self.start_iter = 0                         # the skip applies to the pass that resumes, not to later epochs
+        if skipped:
+            next(itertools.islice(stream, skipped - 1, skipped), None)
+        while True:
+            global_batch = list(itertools.islice(stream, self.batch_size))
+            if len(global_batch) < self.batch_size:
+                if global_batch and not self.drop_last:
+                    yield self.share(global_batch)
+                return
+            yield self.share(global_batch)

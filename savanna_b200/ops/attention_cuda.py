@@ -46,12 +46,29 @@ def set_own_kernels(on: bool) -> None:
     _OWN = bool(on)
 
 
+_ALLOW_LIBRARY = False
+
+
+def set_allow_library(on: bool) -> None:
+    """Policy for shapes the tcgen05 kernels do not cover (head size other than 128, odd layouts): False (default)
+    raises, True runs them on the flash kernels shipped with PyTorch (config key `allow_library_attention`)."""
+    global _ALLOW_LIBRARY
+    _ALLOW_LIBRARY = bool(on)
+
+
 def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False, own_kernels=True):
     if q_pos is not None or k_pos is not None or q.dtype != torch.bfloat16:
+        # explicit positions (partial blocks of the NCCL ring) and fp32 inputs: the fp32 statement of the operator
         return ref.attention(q, k, v, causal, q_pos, k_pos, return_lse)
     from . import flash_sm100
-    if _OWN and own_kernels and flash_sm100.supported(q, k, v, causal):
-        return flash_sm100.attention(q, k, v, causal, return_lse)
+    if _OWN and own_kernels:
+        if flash_sm100.supported(q, k, v, causal):
+            return flash_sm100.attention(q, k, v, causal, return_lse)
+        if not _ALLOW_LIBRARY:
+            raise RuntimeError(
+                f"attention shape q{tuple(q.shape)} k{tuple(k.shape)} (strides {q.stride()}) is not covered by the "
+                "tcgen05 kernels (head size 128, bf16, unit inner stride); set `allow_library_attention: true` to run "
+                "it on PyTorch's flash kernels instead")
     if return_lse:
         return _SdpaWithLse.apply(q, k, v, causal)
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal)

@@ -145,6 +145,14 @@ def teardown() -> None:
     _WS = None
 
 
+def fp8_active():
+    """None: the fused projections are off.  False: they are on and run bf16 GEMMs even where the layer asks for fp8
+    (reported by bench.py next to the dtype).  True: they run fp8 operands."""
+    if _WS is None:
+        return None
+    return False
+
+
 def _eligible(x, w, rows_per_rank: int) -> bool:
     return (_WS is not None and x.is_cuda and x.dtype == bf16 and w.dtype == bf16 and rows_per_rank % 128 == 0
             and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0)

@@ -96,6 +96,8 @@ class Trainer:
         if self.device.type == "cuda":
             from ..ops import cuda_ops
             cuda_ops.set_fp8_history(cfg.fp8_amax_history_len)
+            from ..ops import attention_cuda
+            attention_cuda.set_allow_library(bool(cfg.allow_library_attention))
         if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.sequence_parallel
                 and state.get_model_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
             from ..parallel import fused_tp

@@ -27,7 +27,10 @@ DEVICE_PEAKS = {
 FALLBACK_MEASURED = 1.59e15
 
 
-def layer_flops_per_token(cfg, op: str) -> float:
+def layer_flops_per_token(cfg, op: str, executed: bool = False) -> float:
+    """`executed=False` reproduces the reference's accounting (full L x L attention, Hyena-LI as an FFT).
+    `executed=True` counts what a causal model has to do: attention over the lower triangle only (2*L*D) and
+    Hyena-LI as the order-`hyena_filter_order` modal recurrence (state update + read-out, 4*order*D)."""
     D, L = cfg.hidden_size, cfg.seq_length
     f = 2 * D * 3 * D + 2 * D * D
     if cfg.identity_mlp:
@@ -45,15 +48,17 @@ def layer_flops_per_token(cfg, op: str) -> float:
             f += 2 * cfg.hyena_se_len * D
         elif op == "hyena_mr":
             f += 2 * min(cfg.hyena_mr_len, L) * D
+        elif executed:
+            f += 4 * (cfg.hyena_filter_order or 16) * D
         else:
             f += 10 * math.log2(max(2, L)) * D
     else:
-        f += 4 * L * D
+        f += (2 if executed else 4) * L * D
     return float(f)
 
 
-def model_flops_per_token(cfg, backward: bool = True, recompute: bool = False) -> float:
-    fwd = sum(layer_flops_per_token(cfg, op) for op in cfg.operator_config)
+def model_flops_per_token(cfg, backward: bool = True, recompute: bool = False, executed: bool = False) -> float:
+    fwd = sum(layer_flops_per_token(cfg, op, executed) for op in cfg.operator_config)
     fwd += 2 * cfg.hidden_size * (cfg.padded_vocab_size or 512)
     mult = 1 + (2 if backward else 0) + (1 if recompute else 0)
     return fwd * mult
