@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "device_info.h"
+#include "halo_src.cuh"
 
 namespace sb {
 typedef __nv_bfloat16 bf16;
@@ -177,7 +178,7 @@ constexpr int DW_CT_F = 64, DW_SEG_F = 32, DW_NSEG_F = 4;
 // asynchronous 16-byte copies, a thread then produces DW_SEG steps of two adjacent channels from shared memory.
 template <int K>
 __global__ void __launch_bounds__(DW_CT_F / 2 * DW_NSEG_F)
-dwconv_fwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ halo, const float* __restrict__ w,
+dwconv_fwd_tiled_kernel(const bf16* __restrict__ x, const HaloSrc halo, const float* __restrict__ w,
                         bf16* __restrict__ y, int L, int C) {
   constexpr int H = K - 1, T = DW_SEG_F * DW_NSEG_F, ROWS = T + H, NT = DW_CT_F / 2 * DW_NSEG_F, CHK = DW_CT_F / 8;
   __shared__ __align__(16) bf16 xS[ROWS][DW_CT_F];          // x_ext of times t0-H .. t0+T-1
@@ -187,7 +188,10 @@ dwconv_fwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ hal
     const bf16* src = x;
     int nb = 0;
     if (t >= 0 && t < L) { src = x + ((size_t)b * L + t) * C + c0 + ch * 8; nb = 16; }
-    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * C + c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H) {
+      const bf16* hr = halo_row(halo, b, t + H, H, C);       // local halo tensor or a neighbour's staged tail (peer load)
+      if (hr) { src = hr + c0 + ch * 8; nb = 16; }
+    }
     cp_async16(&xS[row][ch * 8], src, nb);
   }
   const int cp = tid % (DW_CT_F / 2), seg = tid / (DW_CT_F / 2), r0 = seg * DW_SEG_F;
@@ -224,26 +228,38 @@ constexpr int DW_CT = 64, DW_SEG = 32, DW_NSEG = 4, DW_T = DW_SEG * DW_NSEG;
 
 template <int K>
 __global__ void __launch_bounds__(DW_CT / 2 * DW_NSEG)
-dwconv_bwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ halo, const float* __restrict__ w,
+dwconv_bwd_tiled_kernel(const bf16* __restrict__ x, const HaloSrc halo, const float* __restrict__ w,
                         const bf16* __restrict__ dy, bf16* __restrict__ dx, bf16* __restrict__ dhalo,
-                        float* __restrict__ dw, int L, int C) {
+                        float* __restrict__ dw, int L, int C, const int ahead_mode, const HaloSrc ahead) {
   constexpr int H = K - 1, ROWS = DW_T + H, NT = DW_CT / 2 * DW_NSEG, CHK = DW_CT / 8;
   __shared__ __align__(16) bf16 xS[ROWS][DW_CT];            // x_ext of times t0-H .. t0+DW_T-1
   __shared__ __align__(16) bf16 gS[ROWS][DW_CT];            // dy of times t0 .. t0+DW_T+H-1
   __shared__ float dwS[DW_CT][K];
   const int tid = threadIdx.x, c0 = blockIdx.x * DW_CT, b = blockIdx.z;
-  const int t0 = blockIdx.y * DW_T - H;                     // the first tile also produces the halo rows' gradient
+  // Two ways to account for the rows a neighbouring chunk convolved with this chunk's tail.  Default: the first tile
+  // starts H rows early and writes the gradient of the halo rows to `dhalo` (the caller routes it to their owner).
+  // `ahead_mode`: the H rows of dy that FOLLOW the chunk are read from `ahead` (the next chunk's staged head, peer
+  // memory), so dx of the tail rows is complete here and nothing is produced for the halo rows.
+  const int t0 = blockIdx.y * DW_T - (ahead_mode ? 0 : H);
   for (int idx = tid; idx < ROWS * CHK; idx += NT) {
     const int row = idx / CHK, ch = idx % CHK;
     int t = t0 - H + row;
     const bf16* src = x;
     int nb = 0;
     if (t >= 0 && t < L) { src = x + ((size_t)b * L + t) * C + c0 + ch * 8; nb = 16; }
-    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * C + c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H) {
+      const bf16* hr = halo_row(halo, b, t + H, H, C);
+      if (hr) { src = hr + c0 + ch * 8; nb = 16; }
+    }
     cp_async16(&xS[row][ch * 8], src, nb);
     t = t0 + row;
-    const bool in = t >= 0 && t < L;
-    cp_async16(&gS[row][ch * 8], in ? dy + ((size_t)b * L + t) * C + c0 + ch * 8 : dy, in ? 16 : 0);
+    src = dy; nb = 0;
+    if (t >= 0 && t < L) { src = dy + ((size_t)b * L + t) * C + c0 + ch * 8; nb = 16; }
+    else if (ahead_mode && t >= L && t < L + H) {
+      const bf16* ar = halo_row(ahead, b, t - L, H, C);
+      if (ar) { src = ar + c0 + ch * 8; nb = 16; }
+    }
+    cp_async16(&gS[row][ch * 8], src, nb);
   }
   for (int idx = tid; idx < DW_CT * K; idx += NT) (&dwS[0][0])[idx] = 0.f;
   cp_async_wait_all();
@@ -273,7 +289,9 @@ dwconv_bwd_tiled_kernel(const bf16* __restrict__ x, const bf16* __restrict__ hal
     for (int q = 0; q < 2; ++q) {
       float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < K; ++j) { acc += wr[q][j] * gw[K - 1 - j][q]; dwacc[q][j] += gw[0][q] * xw[j][q]; }
+      const float g0 = t < L ? gw[0][q] : 0.f;              // look-ahead rows belong to the next chunk's filter gradient
+#pragma unroll
+      for (int j = 0; j < K; ++j) { acc += wr[q][j] * gw[K - 1 - j][q]; dwacc[q][j] += g0 * xw[j][q]; }
       o[q] = acc;
     }
     bf16* dst = nullptr;
@@ -449,7 +467,7 @@ constexpr int SE_CT = 32, SE_SEG = 32, SE_NSEG = 4, SE_T = SE_SEG * SE_NSEG;
 // 16-byte chunks.
 template <int K>
 __global__ void __launch_bounds__(SE_CT * SE_NSEG)
-se_fwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo, const float* __restrict__ w,
+se_fwd_tiled_kernel(const bf16* __restrict__ feat, const HaloSrc halo, const float* __restrict__ w,
                     bf16* __restrict__ z, int L, int D, int dg, int pregate, int postgate) {
   constexpr int H = K - 1, ROWS = SE_T + H, NT = SE_CT * SE_NSEG, FCH = 3 * SE_CT / 8, ZCH = SE_CT / 8;
   __shared__ __align__(16) bf16 fS[ROWS][3 * SE_CT];        // features of times t0-H .. t0+SE_T-1
@@ -460,7 +478,10 @@ se_fwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo
     const bf16* src = feat;
     int nb = 0;
     if (t >= 0 && t < L) { src = feat + ((size_t)b * L + t) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
-    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H) {
+      const bf16* hr = halo_row(halo, b, t + H, H, (size_t)3 * D);   // local halo tensor or a neighbour's staged tail
+      if (hr) { src = hr + 3 * c0 + ch * 8; nb = 16; }
+    }
     cp_async16(&fS[row][ch * 8], src, nb);
   }
   const int c = tid % SE_CT, seg = tid / SE_CT, r0 = seg * SE_SEG;
@@ -502,28 +523,44 @@ se_fwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo
 
 template <int K>
 __global__ void __launch_bounds__(SE_CT * SE_NSEG)
-se_bwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo, const float* __restrict__ w,
+se_bwd_tiled_kernel(const bf16* __restrict__ feat, const HaloSrc halo, const int has_halo, const float* __restrict__ w,
                     const bf16* __restrict__ dz, bf16* __restrict__ dfeat, bf16* __restrict__ dhalo,
-                    float* __restrict__ dw, int L, int D, int dg, int pregate, int postgate) {
+                    float* __restrict__ dw, int L, int D, int dg, int pregate, int postgate,
+                    const int ahead_mode, const HaloSrc ahead_f, const HaloSrc ahead_g) {
   constexpr int H = K - 1, ROWS_F = SE_T + 2 * H, ROWS_G = SE_T + H;
   __shared__ __align__(16) bf16 fS[ROWS_F][3 * SE_CT];      // features of times t0-H .. t0+SE_T+H-1
   __shared__ __align__(16) bf16 gS[ROWS_G][SE_CT];          // dz of times t0 .. t0+SE_T+H-1
   __shared__ float dwS[SE_CT][K];
   const int tid = threadIdx.x, c0 = blockIdx.x * SE_CT, b = blockIdx.z;
-  const int t0 = blockIdx.y * SE_T - (halo ? H : 0);
+  // `ahead_mode`: the H rows after the chunk (features, for x1, and dz) come from the next chunk's staged head in peer
+  // memory, so the gradients of this chunk's tail rows are complete here; otherwise the first tile starts H rows early
+  // and the gradient of the halo rows goes to `dhalo`.
+  const int t0 = blockIdx.y * SE_T - ((has_halo && !ahead_mode) ? H : 0);
   constexpr int FCH = 3 * SE_CT / 8, GCH = SE_CT / 8;       // 16-byte chunks per staged row
   for (int idx = tid; idx < ROWS_F * FCH; idx += SE_CT * SE_NSEG) {
     const int row = idx / FCH, ch = idx % FCH, t = t0 - H + row;
     const bf16* src = feat;
     int nb = 0;
     if (t >= 0 && t < L) { src = feat + ((size_t)b * L + t) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
-    else if (t < 0 && t >= -H && halo) { src = halo + ((size_t)b * H + (t + H)) * 3 * D + 3 * c0 + ch * 8; nb = 16; }
+    else if (t < 0 && t >= -H) {
+      const bf16* hr = halo_row(halo, b, t + H, H, (size_t)3 * D);
+      if (hr) { src = hr + 3 * c0 + ch * 8; nb = 16; }
+    } else if (ahead_mode && t >= L && t < L + H) {
+      const bf16* ar = halo_row(ahead_f, b, t - L, H, (size_t)3 * D);
+      if (ar) { src = ar + 3 * c0 + ch * 8; nb = 16; }
+    }
     cp_async16(&fS[row][ch * 8], src, nb);
   }
   for (int idx = tid; idx < ROWS_G * GCH; idx += SE_CT * SE_NSEG) {
     const int row = idx / GCH, ch = idx % GCH, t = t0 + row;
-    const bool in = t >= 0 && t < L;
-    cp_async16(&gS[row][ch * 8], in ? dz + ((size_t)b * L + t) * D + c0 + ch * 8 : dz, in ? 16 : 0);
+    const bf16* src = dz;
+    int nb = 0;
+    if (t >= 0 && t < L) { src = dz + ((size_t)b * L + t) * D + c0 + ch * 8; nb = 16; }
+    else if (ahead_mode && t >= L && t < L + H) {
+      const bf16* ar = halo_row(ahead_g, b, t - L, H, (size_t)D);
+      if (ar) { src = ar + c0 + ch * 8; nb = 16; }
+    }
+    cp_async16(&gS[row][ch * 8], src, nb);
   }
   for (int idx = tid; idx < SE_CT * K; idx += SE_CT * SE_NSEG) (&dwS[0][0])[idx] = 0.f;
   cp_async_wait_all();
@@ -562,11 +599,12 @@ se_bwd_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ halo
     uw[K - 1] = pregate ? x2 * v : v;
     gw[K - 1] = (i + H < SE_SEG) ? dconv_at(r + H) : la[(i + H - SE_SEG) % (H > 0 ? H : 1)];
     float conv = 0.f, du = 0.f;
+    const float g0 = (t0 + r) < L ? gw[0] : 0.f;             // look-ahead rows count in the next chunk's filter gradient
 #pragma unroll
     for (int j = 0; j < K; ++j) {
       conv += wr[j] * uw[j];
       du += wr[j] * gw[K - 1 - j];
-      dwacc[j] += gw[0] * uw[j];
+      dwacc[j] += g0 * uw[j];
     }
     fS[r + H][3 * c] = __float2bfloat16(postgate ? g * conv : 0.f);
     fS[r + H][3 * c + 1] = __float2bfloat16(pregate ? du * v : 0.f);
@@ -633,7 +671,7 @@ extern "C" int sb_dwconv_fwd(const void* x, const void* halo, const float* w, vo
   if (g_conv_fwd_tiled && C % DW_CT_F == 0) {
     constexpr int T = DW_SEG_F * DW_NSEG_F;
     dim3 grid(C / DW_CT_F, (L + T - 1) / T, B);
-    K_SWITCH(K, (dwconv_fwd_tiled_kernel<KK><<<grid, DW_CT_F / 2 * DW_NSEG_F, 0, st>>>((const bf16*)x, (const bf16*)halo, w,
+    K_SWITCH(K, (dwconv_fwd_tiled_kernel<KK><<<grid, DW_CT_F / 2 * DW_NSEG_F, 0, st>>>((const bf16*)x, halo_local(halo), w,
                                                                                      (bf16*)y, L, C)));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
@@ -649,8 +687,9 @@ extern "C" int sb_dwconv_bwd(const void* x, const void* halo, const float* w, co
   if (B * L == 0) return 0;
   if (g_se_bwd_tiled && C % DW_CT == 0) {
     dim3 grid(C / DW_CT, (L + K - 1 + DW_T - 1) / DW_T, B);
-    K_SWITCH(K, (dwconv_bwd_tiled_kernel<KK><<<grid, DW_CT / 2 * DW_NSEG, 0, st>>>((const bf16*)x, (const bf16*)halo, w,
-                                                                                 (const bf16*)dy, (bf16*)dx, (bf16*)dhalo, dw, L, C)));
+    K_SWITCH(K, (dwconv_bwd_tiled_kernel<KK><<<grid, DW_CT / 2 * DW_NSEG, 0, st>>>((const bf16*)x, halo_local(halo), w,
+                                                                                 (const bf16*)dy, (bf16*)dx, (bf16*)dhalo, dw, L, C,
+                                                                                 0, halo_local(nullptr))));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   const int cvecs = C / 4, threads = 128, tl = pick_tl(L, B, cvecs);
@@ -670,7 +709,7 @@ extern "C" int sb_se_fwd(const void* feat, const void* halo, const float* w, voi
   if (B * L == 0) return 0;
   if (g_conv_fwd_tiled && D % SE_CT == 0) {
     dim3 grid(D / SE_CT, (L + SE_T - 1) / SE_T, B);
-    K_SWITCH(K, (se_fwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (bf16*)z, L, D,
+    K_SWITCH(K, (se_fwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, halo_local(halo), w, (bf16*)z, L, D,
                                                                          D / G, pregate, postgate)));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
@@ -688,14 +727,62 @@ extern "C" int sb_se_bwd(const void* feat, const void* halo, const float* w, con
   if (g_se_bwd_tiled && D % SE_CT == 0) {
     const int H = K - 1, steps = L + (halo ? H : 0);
     dim3 grid(D / SE_CT, (steps + SE_T - 1) / SE_T, B);
-    K_SWITCH(K, (se_bwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (const bf16*)dz,
-                                                                         (bf16*)dfeat, (bf16*)dhalo, dw, L, D, D / G, pregate,
-                                                                         postgate)));
+    K_SWITCH(K, (se_bwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, halo_local(halo), halo ? 1 : 0, w,
+                                                                         (const bf16*)dz, (bf16*)dfeat, (bf16*)dhalo, dw, L, D, D / G,
+                                                                         pregate, postgate, 0, halo_local(nullptr), halo_local(nullptr))));
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   const int cvecs = D / 4, threads = 128, tl = pick_tl(L, B, cvecs);
   dim3 grid((cvecs + threads - 1) / threads, (L + tl - 1) / tl, B);
   K_SWITCH(K, (se_bwd_kernel<KK, 4><<<grid, threads, 0, st>>>((const bf16*)feat, (const bf16*)halo, w, (const bf16*)dz,
                                                            (bf16*)dfeat, (bf16*)dhalo, dw, L, D, D / G, tl, pregate, postgate)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+
+// ------------------------------------------------------------------------------------ context-parallel entry points
+// The same tiled kernels with the edge rows read in place from the neighbours' staged chunk edges (peer memory, see
+// halo_src.cuh): x / feat are [2B, L, .] (two zigzag chunks per sequence as consecutive batch rows), `before` describes
+// the staged tails (rows preceding each chunk), `ahead*` the staged heads of the tensors whose look-ahead the backward
+// needs.  No halo tensor and no halo gradient exist on this path.  Return -9 when the shape has no tiled kernel.
+extern "C" int sb_dwconv_fwd_cp(const void* x, const HaloSrc* before, const float* w, void* y, int B2, int L, int C, int K,
+                                cudaStream_t st) {
+  if (C % DW_CT_F || !before) return -9;
+  if (B2 * L == 0) return 0;
+  constexpr int T = DW_SEG_F * DW_NSEG_F;
+  dim3 grid(C / DW_CT_F, (L + T - 1) / T, B2);
+  K_SWITCH(K, (dwconv_fwd_tiled_kernel<KK><<<grid, DW_CT_F / 2 * DW_NSEG_F, 0, st>>>((const bf16*)x, *before, w, (bf16*)y, L, C)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_dwconv_bwd_cp(const void* x, const HaloSrc* before, const float* w, const void* dy, const HaloSrc* ahead_dy,
+                                void* dx, float* dw, int B2, int L, int C, int K, cudaStream_t st) {
+  if (C % DW_CT || !before || !ahead_dy) return -9;
+  if (B2 * L == 0) return 0;
+  dim3 grid(C / DW_CT, (L + DW_T - 1) / DW_T, B2);
+  K_SWITCH(K, (dwconv_bwd_tiled_kernel<KK><<<grid, DW_CT / 2 * DW_NSEG, 0, st>>>((const bf16*)x, *before, w, (const bf16*)dy,
+                                                                               (bf16*)dx, nullptr, dw, L, C, 1, *ahead_dy)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_se_fwd_cp(const void* feat, const HaloSrc* before, const float* w, void* z, int B2, int L, int D, int G, int K,
+                            int pregate, int postgate, cudaStream_t st) {
+  if ((D % SE_CT) || (D % G) || !before) return -9;
+  if (B2 * L == 0) return 0;
+  dim3 grid(D / SE_CT, (L + SE_T - 1) / SE_T, B2);
+  K_SWITCH(K, (se_fwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, *before, w, (bf16*)z, L, D, D / G,
+                                                                       pregate, postgate)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_se_bwd_cp(const void* feat, const HaloSrc* before, const float* w, const void* dz, const HaloSrc* ahead_feat,
+                            const HaloSrc* ahead_dz, void* dfeat, float* dw, int B2, int L, int D, int G, int K, int pregate,
+                            int postgate, cudaStream_t st) {
+  if ((D % SE_CT) || (D % G) || !before || !ahead_feat || !ahead_dz) return -9;
+  if (B2 * L == 0) return 0;
+  dim3 grid(D / SE_CT, (L + SE_T - 1) / SE_T, B2);
+  K_SWITCH(K, (se_bwd_tiled_kernel<KK><<<grid, SE_CT * SE_NSEG, 0, st>>>((const bf16*)feat, *before, 1, w, (const bf16*)dz,
+                                                                       (bf16*)dfeat, nullptr, dw, L, D, D / G, pregate, postgate,
+                                                                       1, *ahead_feat, *ahead_dz)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -302,6 +302,267 @@ li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------------------------ context parallel: all-to-all inside the scan
+// Sequence-sharded ranks (zigzag: rank r holds natural chunks r and 2cp-1-r of `chunk_len` rows, [B, l, Dtot] with
+// l = 2 chunk_len) switch to a channel-sharded scan over the whole sequence (this rank: d = Dtot / cp channels) and back.
+// Only the pre-gated signal u = x2 v travels: every rank writes u into a symmetric staging buffer, and after one
+// stream-ordered barrier the scan's first pass reads its channel block of every chunk straight from the owner's
+// staging buffer (plain peer loads), keeping a local copy for the second pass.  The second pass stores y straight into
+// the owner's staging buffer (plain peer stores); after the second barrier the owner gates it with its own x1.  No
+// tensor is permuted or copied by a separate kernel, and a third of the bytes of exchanging (x1, x2, v) and z cross
+// NVLink.  `LiCpMap.base[j]`: row 0 of natural chunk j in its owner's staging buffer, already offset to this rank's
+// channel block.  The scan chunk length TC must divide chunk_len, so a scan chunk never straddles two owners.
+struct LiCpMap {
+  void* base[32];
+  long long batch_stride;   // elements between batches of a staging buffer (l * Dtot)
+  int row_stride;           // elements between rows (Dtot)
+  int chunk_len;
+  int n_chunks;             // 2 cp
+};
+
+__device__ __forceinline__ bf16* cp_row(const LiCpMap& m, int b, int t) {
+  const int j = t / m.chunk_len;
+  return reinterpret_cast<bf16*>(m.base[j]) + (size_t)b * m.batch_stride + (size_t)(t - j * m.chunk_len) * m.row_stride;
+}
+
+// pass 1: pull u from the owners, keep a local copy [B, L, d], chunk-local end state from a zero state
+__global__ void __launch_bounds__(LI_THREADS)
+li_cp_local_kernel(const LiCpMap u_in, bf16* __restrict__ ufull, const float* __restrict__ loglam, float* __restrict__ Sloc,
+                   LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); s[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* src = cp_row(u_in, b, t0) + ch;
+  bf16* dst = ufull + ((size_t)b * d.L + t0) * d.D + ch;
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t, src += u_in.row_stride, dst += d.D) {
+    const bf16 raw = *src;
+    *dst = raw;
+    const float u = b2f(raw);
+#pragma unroll
+    for (int o = 0; o < LO; ++o) s[o] = lam[o] * s[o] + u;
+  }
+  store_vec16(Sloc + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+}
+
+// pass 3: rerun each chunk from its entering state; y goes to the owner of the rows
+__global__ void __launch_bounds__(LI_THREADS)
+li_cp_apply_kernel(const bf16* __restrict__ ufull, const float* __restrict__ loglam, const float* __restrict__ R,
+                   const float* __restrict__ bias, const float* __restrict__ Sin, const LiCpMap y_out, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], rr[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Sin + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) lam[o] = __expf(lam[o]);
+  const float be = bias[ch];
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = ufull + ((size_t)b * d.L + t0) * d.D + ch;
+  bf16* yo = cp_row(y_out, b, t0) + ch;
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t, f += d.D, yo += y_out.row_stride) {
+    const float u = b2f(*f);
+    float y = be * u;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { s[o] = lam[o] * s[o] + u; y += rr[o] * s[o]; }
+    *yo = __float2bfloat16_rn(y);
+  }
+}
+
+// backward pass B1: pull dy = dz x1 from the owners (local copy [B, L, d]); Sloc, Wloc, Aloc as in li_bwd_local_kernel
+__global__ void __launch_bounds__(LI_THREADS)
+li_cp_bwd_local_kernel(const bf16* __restrict__ ufull, const LiCpMap dy_in, bf16* __restrict__ dyfull,
+                       const float* __restrict__ loglam, const float* __restrict__ R, float* __restrict__ Sloc,
+                       float* __restrict__ Wloc, float* __restrict__ Aloc, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], w[LO], pw[LO], a[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); s[o] = 0.f; w[o] = 0.f; pw[o] = 1.f; a[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = ufull + ((size_t)b * d.L + t0) * d.D + ch;
+  const bf16* g = cp_row(dy_in, b, t0) + ch;
+  bf16* gd = dyfull + ((size_t)b * d.L + t0) * d.D + ch;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t, f += d.D, g += dy_in.row_stride, gd += d.D) {
+    const float u = b2f(*f);
+    const bf16 raw = *g;
+    *gd = raw;
+    const float dy = b2f(raw);
+#pragma unroll
+    for (int o = 0; o < LO; ++o) {
+      w[o] = s[o] + lam[o] * w[o];
+      s[o] = lam[o] * s[o] + u;
+      a[o] += pw[o] * dy;
+      pw[o] *= lam[o];
+    }
+  }
+  float rr[LO];
+  load_vec16(R + (size_t)ch * LO, rr);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) a[o] *= rr[o];
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  store_vec16(Sloc + off, s);
+  store_vec16(Wloc + off, w);
+  store_vec16(Aloc + off, a);
+}
+
+// backward pass B3 (forward direction): y back to the owners (for dx1 = dz y), per-chunk partials of dR, dlam, dbias
+__global__ void __launch_bounds__(LI_THREADS)
+li_cp_bwd_apply_fwd_kernel(const bf16* __restrict__ ufull, const bf16* __restrict__ dyfull, const float* __restrict__ loglam,
+                           const float* __restrict__ R, const float* __restrict__ bias, const float* __restrict__ Sin,
+                           const float* __restrict__ Win, const LiCpMap y_out, float* __restrict__ dRp,
+                           float* __restrict__ dLp, float* __restrict__ dBp, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], s[LO], w[LO], rr[LO], dr[LO], dl[LO];
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Sin + off, s);
+  load_vec16(Win + off, w);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = __expf(lam[o]); dr[o] = 0.f; dl[o] = 0.f; }
+  const float be = bias[ch];
+  float db = 0.f;
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* f = ufull + ((size_t)b * d.L + t0) * d.D + ch;
+  const bf16* g = dyfull + ((size_t)b * d.L + t0) * d.D + ch;
+  bf16* yo = cp_row(y_out, b, t0) + ch;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t, f += d.D, g += d.D, yo += y_out.row_stride) {
+    const float u = b2f(*f);
+    const float dy = b2f(*g);
+    float y = be * u;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) {
+      w[o] = s[o] + lam[o] * w[o];
+      s[o] = lam[o] * s[o] + u;
+      y += rr[o] * s[o];
+      dr[o] += dy * s[o];
+      dl[o] += dy * w[o];
+    }
+    db += dy * u;
+    *yo = __float2bfloat16_rn(y);
+  }
+#pragma unroll
+  for (int o = 0; o < LO; ++o) dl[o] *= rr[o];
+  store_vec16(dRp + off, dr);
+  store_vec16(dLp + off, dl);
+  dBp[((size_t)b * d.NC + n) * d.D + ch] = db;
+}
+
+// backward pass R3 (reverse direction): adjoint scan, du back to the owners (for dx2 = du v, dv = du x2)
+__global__ void __launch_bounds__(LI_THREADS)
+li_cp_bwd_apply_rev_kernel(const bf16* __restrict__ dyfull, const float* __restrict__ loglam, const float* __restrict__ R,
+                           const float* __restrict__ bias, const float* __restrict__ Ain, const LiCpMap du_out, LiDims d) {
+  const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
+  if (ch >= d.D) return;
+  const int n = blockIdx.y, b = blockIdx.z;
+  float lam[LO], a[LO], rr[LO];
+  load_vec16(loglam + (size_t)ch * LO, lam);
+  load_vec16(R + (size_t)ch * LO, rr);
+  load_vec16(Ain + (((size_t)b * d.NC + n) * d.D + ch) * LO, a);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) lam[o] = __expf(lam[o]);
+  const float be = bias[ch];
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* g = dyfull + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
+  bf16* uo = cp_row(du_out, b, t1 - 1) + ch;
+#pragma unroll 8
+  for (int t = t1 - 1; t >= t0; --t, g -= d.D, uo -= du_out.row_stride) {
+    const float dy = b2f(*g);
+    float du = be * dy;
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { a[o] = rr[o] * dy + lam[o] * a[o]; du += a[o]; }
+    *uo = __float2bfloat16_rn(du);
+  }
+}
+
+// Local gate kernels around the exchange, 8 channels per thread (feat rows are 3D interleaved (x1, x2, v)).
+// mode 0: out[n, D] = x2 v                     (u, staged before the forward scan)
+// mode 1: out[n, D] = x1 a                     (z = x1 y after the forward scan;  dy = dz x1 before the backward scan)
+__global__ void li_cp_gate_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ a, bf16* __restrict__ out,
+                                  size_t n_vec, int mode) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4* fp = reinterpret_cast<const uint4*>(feat) + 3 * i;
+    const uint4 q0 = fp[0], q1 = fp[1], q2 = fp[2];
+    const uint32_t fw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
+    float all[24];
+#pragma unroll
+    for (int j = 0; j < 12; ++j) {
+      const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&fw[j]));
+      all[2 * j] = t.x; all[2 * j + 1] = t.y;
+    }
+    float r[8];
+    if (mode == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r[j] = all[3 * j + 1] * all[3 * j + 2];
+    } else {
+      const uint4 av = reinterpret_cast<const uint4*>(a)[i];
+      const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[j]));
+        r[2 * j] = all[6 * j] * t.x; r[2 * j + 1] = all[6 * j + 3] * t.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+// dfeat[n, 3D] = (dz y, du v, du x2) from the returned y and du
+__global__ void li_cp_finalize_bwd_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const bf16* __restrict__ y,
+                                          const bf16* __restrict__ du, bf16* __restrict__ dfeat, size_t n_vec) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4* fp = reinterpret_cast<const uint4*>(feat) + 3 * i;
+    const uint4 q0 = fp[0], q1 = fp[1], q2 = fp[2];
+    const uint32_t fw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
+    float all[24], gz[8], yy[8], dd[8], o[24];
+#pragma unroll
+    for (int j = 0; j < 12; ++j) {
+      const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&fw[j]));
+      all[2 * j] = t.x; all[2 * j + 1] = t.y;
+    }
+    const uint4 a = reinterpret_cast<const uint4*>(dz)[i], bq = reinterpret_cast<const uint4*>(y)[i],
+                c = reinterpret_cast<const uint4*>(du)[i];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[j])); gz[2 * j] = t.x; gz[2 * j + 1] = t.y;
+      t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[j])); yy[2 * j] = t.x; yy[2 * j + 1] = t.y;
+      t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cw[j])); dd[2 * j] = t.x; dd[2 * j + 1] = t.y;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[3 * j] = gz[j] * yy[j];
+      o[3 * j + 1] = dd[j] * all[3 * j + 2];
+      o[3 * j + 2] = dd[j] * all[3 * j + 1];
+    }
+    uint4 ov[3];
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(ov);
+#pragma unroll
+    for (int j = 0; j < 12; ++j) o2[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+    uint4* dp = reinterpret_cast<uint4*>(dfeat) + 3 * i;
+    dp[0] = ov[0]; dp[1] = ov[1]; dp[2] = ov[2];
+  }
+}
+
 }  // namespace sb
 
 using namespace sb;
@@ -339,6 +600,69 @@ extern "C" int sb_li_bwd(const void* feat, const void* dz, const float* loglam, 
                                                       (bf16*)dx1_tmp, dRp, dLp, dBp, d);
   li_bwd_apply_rev_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, A,
                                                       (const bf16*)dx1_tmp, (bf16*)dfeat, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+static inline unsigned li_gate_grid(size_t n_vec) {
+  size_t g = (n_vec + 255) / 256;
+  const size_t cap = 2048;
+  return (unsigned)(g > cap ? cap : (g < 1 ? 1 : g));
+}
+
+// out[n, D] = x2 v (mode 0) or x1 a (mode 1) for feat [n, 3D]; D % 8 == 0, 16-byte aligned rows.
+extern "C" int sb_li_cp_gate(const void* feat, const void* a, void* out, long long n_rows, int D, int mode, cudaStream_t st) {
+  if ((D % 8) || (mode == 1 && !a)) return -1;
+  const size_t n_vec = (size_t)n_rows * (D / 8);
+  if (n_vec == 0) return 0;
+  li_cp_gate_kernel<<<li_gate_grid(n_vec), 256, 0, st>>>((const bf16*)feat, (const bf16*)a, (bf16*)out, n_vec, mode);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_li_cp_finalize_bwd(const void* feat, const void* dz, const void* y, const void* du, void* dfeat,
+                                     long long n_rows, int D, cudaStream_t st) {
+  if (D % 8) return -1;
+  const size_t n_vec = (size_t)n_rows * (D / 8);
+  if (n_vec == 0) return 0;
+  li_cp_finalize_bwd_kernel<<<li_gate_grid(n_vec), 256, 0, st>>>((const bf16*)feat, (const bf16*)dz, (const bf16*)y,
+                                                                (const bf16*)du, (bf16*)dfeat, n_vec);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+static inline bool li_cp_map_ok(const LiCpMap* m, int L, int TC) {
+  return m && m->n_chunks >= 1 && m->n_chunks <= 32 && m->chunk_len > 0 && (long long)m->chunk_len * m->n_chunks == L &&
+         (m->chunk_len % TC) == 0;
+}
+
+// Channel-sharded forward scan of this rank (d channels, whole sequence L) with the exchange inside: u pulled from the
+// owners' staging (u_in) into ufull [B, L, d], y stored into the owners' staging (y_out).  S: B*NC*d*16 floats.
+extern "C" int sb_li_cp_fwd(const LiCpMap* u_in, const LiCpMap* y_out, const float* loglam, const float* R, const float* bias,
+                            float* S, void* ufull, int B, int L, int d, int TC, cudaStream_t st) {
+  if (B * L == 0) return 0;
+  if (!li_cp_map_ok(u_in, L, TC) || !li_cp_map_ok(y_out, L, TC)) return -9;
+  LiDims dm = li_dims(B, L, d, TC);
+  dim3 grid((d + LI_THREADS - 1) / LI_THREADS, dm.NC, B);
+  li_cp_local_kernel<<<grid, LI_THREADS, 0, st>>>(*u_in, (bf16*)ufull, loglam, S, dm);
+  const size_t n = (size_t)B * d * LO;
+  li_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, loglam, nullptr, nullptr, dm);
+  li_cp_apply_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)ufull, loglam, R, bias, S, *y_out, dm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Backward of the above: dy pulled from the owners (dy_in) into dyfull, y and du stored into the owners' staging.
+// Scratch S, W, A, dRp, dLp: B*NC*d*16 floats each; dBp: B*NC*d floats (the caller sums the partials over B and NC).
+extern "C" int sb_li_cp_bwd(const LiCpMap* dy_in, const LiCpMap* y_out, const LiCpMap* du_out, const void* ufull, void* dyfull,
+                            const float* loglam, const float* R, const float* bias, float* S, float* W, float* A, float* dRp,
+                            float* dLp, float* dBp, int B, int L, int d, int TC, cudaStream_t st) {
+  if (B * L == 0) return 0;
+  if (!li_cp_map_ok(dy_in, L, TC) || !li_cp_map_ok(y_out, L, TC) || !li_cp_map_ok(du_out, L, TC)) return -9;
+  LiDims dm = li_dims(B, L, d, TC);
+  dim3 grid((d + LI_THREADS - 1) / LI_THREADS, dm.NC, B);
+  li_cp_bwd_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)ufull, *dy_in, (bf16*)dyfull, loglam, R, S, W, A, dm);
+  const size_t n = (size_t)B * d * LO;
+  li_bwd_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, W, A, loglam, nullptr, nullptr, nullptr, nullptr, dm);
+  li_cp_bwd_apply_fwd_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)ufull, (const bf16*)dyfull, loglam, R, bias, S, W, *y_out,
+                                                         dRp, dLp, dBp, dm);
+  li_cp_bwd_apply_rev_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)dyfull, loglam, R, bias, A, *du_out, dm);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

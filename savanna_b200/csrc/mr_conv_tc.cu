@@ -19,6 +19,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "halo_src.cuh"
+
 #include "device_info.h"
 
 namespace sb {
@@ -69,15 +71,17 @@ __device__ __forceinline__ void toeplitz_frags(uint32_t (&a)[ND][4], const float
 }
 
 struct MrArgs {
-  const bf16* feat; const bf16* halo; const float* h; const float* bias;
+  const bf16* feat; HaloSrc halo; const float* h; const float* bias;
   int L, D, K, dg;
+  // context-parallel backward: rows [L, L + K - 1) of x1 and dz come from the next chunk's staged head (peer memory)
+  int ahead_mode; HaloSrc ahead_f, ahead_g;
 };
 
 // Loads 8 channels (c0..c0+7) of feature row t (halo-aware): returns false (zeros) outside the sequence.
 __device__ __forceinline__ bool load_row8(const MrArgs& a, int b, int t, int c0, float (&x1)[8], float (&x2)[8], float (&v)[8]) {
   const bf16* row = nullptr;
   if (t >= 0 && t < a.L) row = a.feat + ((size_t)b * a.L + t) * 3 * a.D;
-  else if (t < 0 && t >= -(a.K - 1) && a.halo) row = a.halo + ((size_t)b * (a.K - 1) + (t + a.K - 1)) * 3 * a.D;
+  else if (t < 0 && t >= -(a.K - 1)) row = halo_row(a.halo, b, t + a.K - 1, a.K - 1, (size_t)3 * a.D);
   if (!row || c0 >= a.D) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { x1[i] = 0.f; x2[i] = 0.f; v[i] = 0.f; }
@@ -434,6 +438,23 @@ mr_tc_bwd_stream_kernel(MrArgs a, const bf16* __restrict__ dz, bf16* __restrict_
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) gg[j] = 0.f;
+        if (a.ahead_mode && t >= a.L && t < a.L + a.K - 1 && c0 < a.D) {
+          // look-ahead of g = dz * x1 past the end of the chunk: the next chunk's first rows, staged by their owner
+          const bf16* fr = halo_row(a.ahead_f, b, t - a.L, a.K - 1, (size_t)3 * a.D);
+          const bf16* gr = halo_row(a.ahead_g, b, t - a.L, a.K - 1, (size_t)a.D);
+          if (fr && gr) {
+            const uint4* fp = reinterpret_cast<const uint4*>(fr + 3 * c0);
+            const uint4 q0 = fp[0], q1 = fp[1], q2 = fp[2];
+            const uint32_t fw[12] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x, q2.y, q2.z, q2.w};
+            float all[24];
+#pragma unroll
+            for (int j = 0; j < 12; ++j) { float2 pq = unpack2(fw[j]); all[2 * j] = pq.x; all[2 * j + 1] = pq.y; }
+            const uint4 q = *reinterpret_cast<const uint4*>(gr + c0);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { float2 pq = unpack2(w[j]); gg[2 * j] = pq.x * all[6 * j]; gg[2 * j + 1] = pq.y * all[6 * j + 3]; }
+          }
+        }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] = x2[j] * v[j];
@@ -644,9 +665,51 @@ extern "C" int sb_mr_tc_fwd(const void* feat, const void* halo, const float* h, 
     if (cudaFuncSetAttribute(mr_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
     attr = true;
   }
-  MrArgs a{(const bf16*)feat, (const bf16*)halo, h, bias, L, D, K, D / G};
+  MrArgs a{(const bf16*)feat, halo_local(halo), h, bias, L, D, K, D / G, 0, halo_local(nullptr), halo_local(nullptr)};
   dim3 grid((D + TC_CH - 1) / TC_CH, (L + FWD_TT - 1) / FWD_TT, B);
   mr_tc_fwd_kernel<<<grid, TC_THREADS, FWD_SMEM, st>>>(a, (bf16*)z);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Context-parallel forward: feat [2B, L, 3D] (two zigzag chunks per sequence), rows before each chunk read in place
+// from the neighbours' staged tails (`before`, see halo_src.cuh).
+extern "C" int sb_mr_tc_fwd_cp(const void* feat, const HaloSrc* before, const float* h, const float* bias, void* z, int B2,
+                               int L, int D, int G, int K, cudaStream_t st) {
+  if (!sb_mr_tc_supported(D, G, K) || !before) return -9;
+  if (B2 * L == 0) return 0;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(mr_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
+    attr = true;
+  }
+  MrArgs a{(const bf16*)feat, *before, h, bias, L, D, K, D / G, 0, halo_local(nullptr), halo_local(nullptr)};
+  dim3 grid((D + TC_CH - 1) / TC_CH, (L + FWD_TT - 1) / FWD_TT, B2);
+  mr_tc_fwd_kernel<<<grid, TC_THREADS, FWD_SMEM, st>>>(a, (bf16*)z);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Context-parallel backward (streaming kernel): the look-ahead of dz * x1 past each chunk's end comes from the next
+// chunk's staged head (`ahead_feat`, `ahead_dz`), so the gradients of the chunk's tail rows are complete and no halo
+// gradient is produced.  L must be a multiple of 64 (whole tiles: a look-ahead row never shares a tile with chunk rows).
+extern "C" int sb_mr_tc_bwd_cp(const void* feat, const HaloSrc* before, const float* h, const float* bias, const void* dz,
+                               const HaloSrc* ahead_feat, const HaloSrc* ahead_dz, void* dfeat, float* dh, float* dbias, int B2,
+                               int L, int D, int G, int K, cudaStream_t st) {
+  if (!sb_mr_tc_supported(D, G, K) || !before || !ahead_feat || !ahead_dz || (L % SB_TT)) return -9;
+  if (B2 * L == 0) return 0;
+  static bool attr2 = false;
+  if (!attr2) {
+    if (cudaFuncSetAttribute(mr_tc_bwd_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM) != cudaSuccess) return -5;
+    attr2 = true;
+  }
+  MrArgs a{(const bf16*)feat, *before, h, bias, L, D, K, D / G, 1, *ahead_feat, *ahead_dz};
+  const int n_tiles = L / SB_TT;
+  const int ctiles = (D + TC_CH - 1) / TC_CH;
+  int segs = (2 * sb::num_sms()) / (ctiles * B2);
+  if (segs > (n_tiles + 7) / 8) segs = (n_tiles + 7) / 8;
+  if (segs < 1) segs = 1;
+  const int tps = (n_tiles + segs - 1) / segs;
+  dim3 sgrid(ctiles, (n_tiles + tps - 1) / tps, B2);
+  mr_tc_bwd_stream_kernel<<<sgrid, TC_THREADS, SB_SMEM, st>>>(a, (const bf16*)dz, (bf16*)dfeat, nullptr, dh, dbias, 0, n_tiles, tps);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -660,7 +723,7 @@ extern "C" int sb_mr_tc_bwd(const void* feat, const void* halo, const float* h, 
     if (cudaFuncSetAttribute(mr_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return -5;
     attr = true;
   }
-  MrArgs a{(const bf16*)feat, (const bf16*)halo, h, bias, L, D, K, D / G};
+  MrArgs a{(const bf16*)feat, halo_local(halo), h, bias, L, D, K, D / G, 0, halo_local(nullptr), halo_local(nullptr)};
   const int n_halo = (halo && dhalo) ? (K - 1 + BWD_TT - 1) / BWD_TT : 0;
   if (g_mr_bwd_stream) {
     static bool attr2 = false;

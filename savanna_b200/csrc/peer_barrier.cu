@@ -11,7 +11,8 @@
 namespace sb {
 struct SigPtrs { int* p[16]; };
 
-__global__ void peer_barrier_kernel(SigPtrs sig, int me, int world, int epoch, uint32_t* status) {
+__global__ void peer_barrier_kernel(SigPtrs sig, int me, int world, int epoch, uint32_t* status,
+                                    unsigned long long budget_ns) {
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();
@@ -23,7 +24,7 @@ __global__ void peer_barrier_kernel(SigPtrs sig, int me, int world, int epoch, u
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (v >= epoch) break;
-    if ((++it & 127u) == 0u && globaltimer() - t0 > WAIT_BUDGET_NS) {
+    if ((++it & 127u) == 0u && globaltimer() - t0 > budget_ns) {
       if (status) atomicCAS(status, 0u, (uint32_t(ST_TIMEOUT_PEER) << 24) | 0x800000u | uint32_t(r));
       break;
     }
@@ -32,11 +33,17 @@ __global__ void peer_barrier_kernel(SigPtrs sig, int me, int world, int epoch, u
 }
 }  // namespace sb
 
-// sig[r]: rank r's signal array (int32[world], zero-initialised once) as mapped in this process.
-extern "C" int sb_peer_barrier(int* const* sig, int me, int world, int epoch, unsigned int* status, cudaStream_t st) {
+// sig[r]: rank r's signal array (int32[world], zero-initialised once) as mapped in this process.  `budget_ns` bounds the
+// wait for each peer (0 = the library default of 1.5 s); when it runs out the kernel records ST_TIMEOUT_PEER and returns.
+extern "C" int sb_peer_barrier_budget(int* const* sig, int me, int world, int epoch, unsigned int* status,
+                                      unsigned long long budget_ns, cudaStream_t st) {
   if (world < 1 || world > 16) return -1;
   sb::SigPtrs s;
   for (int r = 0; r < 16; ++r) s.p[r] = r < world ? sig[r] : nullptr;
-  sb::peer_barrier_kernel<<<1, 32, 0, st>>>(s, me, world, epoch, status);
+  sb::peer_barrier_kernel<<<1, 32, 0, st>>>(s, me, world, epoch, status, budget_ns ? budget_ns : sb::WAIT_BUDGET_NS);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_peer_barrier(int* const* sig, int me, int world, int epoch, unsigned int* status, cudaStream_t st) {
+  return sb_peer_barrier_budget(sig, me, world, epoch, status, 0ull, st);
 }

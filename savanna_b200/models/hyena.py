@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..parallel import a2a, halo as halo_mod, state
+from ..parallel import a2a, halo as halo_mod, halo_fused, state
 from .filters import ExplicitSingleDecayFilter, ImplicitModalFilter, build_filter
 
 
@@ -65,6 +65,21 @@ class CausalDepthwiseConv1d(nn.Module):
             w = w.repeat_interleave(self.group_dim, dim=0)
         return ops.causal_conv1d(x, w, halo)
 
+    def forward_cp(self, x: torch.Tensor) -> torch.Tensor:
+        """x [B, L_local, C] holding two zigzag chunks of a context-parallel shard.  The kernel reads the rows before
+        each chunk from the neighbour ranks' memory itself when the peer workspace is up; otherwise the halo rows are
+        exchanged first (NCCL or a pull kernel) and passed as a tensor."""
+        w = self.taps()
+        if self.group_dim > 1:
+            w = w.repeat_interleave(self.group_dim, dim=0)
+        y = halo_fused.causal_conv1d_cp(x, w)
+        if y is not None:
+            return y
+        B, L, C = x.shape
+        k = self.kernel_size
+        h = halo_mod.zigzag_halo(x, k - 1)
+        return ops.causal_conv1d(_as_two_chunks(x), w, h.reshape(B * 2, k - 1, C)).reshape(B, L, C)
+
 
 class ShortHyenaOperator(nn.Module):
     """Hyena-SE: z = x1 * conv_k(x2 * v); also the `short_hyena` MLP replacement."""
@@ -93,6 +108,9 @@ class ShortHyenaOperator(nn.Module):
     def forward(self, feat: torch.Tensor) -> torch.Tensor:
         w = self.short_conv.taps()
         if self.use_cp and state.get_context_parallel_world_size() > 1:
+            z = halo_fused.hyena_se_inner_cp(feat, w, self.pregate, self.postgate)
+            if z is not None:
+                return z
             h = halo_mod.zigzag_halo(feat, self.kernel_size - 1)
             B, L, C = feat.shape
             z = ops.hyena_se_inner(_as_two_chunks(feat), w, h.reshape(B * 2, self.kernel_size - 1, C), self.pregate,
@@ -128,6 +146,9 @@ class HyenaOperator(nn.Module):
         k = min(self.hyena_mr_len, L * cp)
         h = self.filter(k)
         if cp > 1 and self.cfg.cp_hyena_mr_algo == "p2p":
+            z = halo_fused.hyena_mr_inner_cp(feat, h, self.conv_bias)
+            if z is not None:
+                return z
             hal = halo_mod.zigzag_halo(feat, k - 1)
             z = ops.hyena_mr_inner(_as_two_chunks(feat), h, self.conv_bias, hal.reshape(B * 2, k - 1, C))
             return z.reshape(B, L, -1)

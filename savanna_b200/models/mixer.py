@@ -109,10 +109,7 @@ class ParallelSequenceMixer(nn.Module):
         if self.operator_type in HYENA_OPS:
             cp = state.get_context_parallel_world_size() if self.cfg.use_cp_hyena else 1
             if cp > 1:
-                B, L, C = proj.shape
-                k = self.short_conv_L
-                h = halo_mod.zigzag_halo(proj, k - 1)
-                feat = self.hyena_proj_conv(_as_two_chunks(proj), h.reshape(B * 2, k - 1, C)).reshape(B, L, C)
+                feat = self.hyena_proj_conv.forward_cp(proj)
             else:
                 feat = self.hyena_proj_conv(proj)
             z = self.mixer(feat)

@@ -620,3 +620,33 @@ def test_fp8_training_tracks_bf16():
     assert b[-1] < b[0] - 1.5, b
     assert abs(a[-1] - b[-1]) < 0.08 * a[-1], (a[-1], b[-1])
     assert max(abs(x - y) for x, y in zip(a, b)) < 0.25, (a, b)
+
+
+def test_peer_barrier_wait_runs_out_and_reports():
+    """A bounded device-side wait that nothing satisfies: the barrier kernel of "rank 0 of 2" waits for a signal word
+    that no one writes, gives up after its budget (30 ms here), records the time-out code with the missing rank in the
+    status word and returns by itself; the host turns the word into an exception and the context stays usable."""
+    import ctypes
+    import time
+    from savanna_b200.ops import cuda_ops
+    lib = cuda_ops.require()
+    P, I = ctypes.c_void_p, ctypes.c_int
+    lib.sb_peer_barrier_budget.restype = I
+    lib.sb_peer_barrier_budget.argtypes = [P, I, I, I, P, ctypes.c_ulonglong, P]
+    cuda_ops.check_status()
+    sig = [torch.zeros(32, dtype=torch.int32, device=DEV) for _ in range(2)]        # both ranks' signal arrays, local
+    ptrs = (ctypes.c_void_p * 2)(sig[0].data_ptr(), sig[1].data_ptr())
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.cuda.synchronize()
+    t0 = time.time()
+    rc = lib.sb_peer_barrier_budget(ptrs, 0, 2, 1, cuda_ops.status_word(dev).data_ptr(), 30_000_000,
+                                    torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0                       # the kernel ended on its own, well inside the default 1.5 s
+    assert int(sig[1][0]) == 1                          # rank 0 did signal its (absent) peer
+    with pytest.raises(RuntimeError, match="bounded wait: code 5"):
+        cuda_ops.check_status()
+    cuda_ops.check_status()                             # the word was cleared; the context still works
+    a = torch.ones(8, device=DEV)
+    assert float((a + a).sum()) == 16.0

@@ -265,6 +265,8 @@ def _w_cp_train(rank, world, over, want):
     assert halo._PEER_WS is not None, "the peer-memory halo exchange was not brought up"
     from savanna_b200.parallel import ring_attention
     assert ring_attention._SIDE, "the peer-memory ring attention did not run"
+    from savanna_b200.parallel import halo_fused
+    assert halo_fused.CALLS > 0, "the convolutions did not read their halo rows from peer memory themselves"
     if over.get("cp_hyena_li_algo", "a2a") == "a2a":
         from savanna_b200.parallel import a2a
         assert a2a.PEER_CALLS > 0, "the peer-memory all-to-all did not run"
