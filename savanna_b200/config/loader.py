@@ -261,6 +261,7 @@ class GlobalConfig:
         if z["stage"] not in (0, 1, 2, 3):
             raise ConfigError(f"zero stage must be 0..3, got {z['stage']!r}")
         self.zero_stage = z["stage"]
+        self.zero_overlap_comm = bool(z.get("overlap_comm", ZERO_DEFAULTS["overlap_comm"]))
         self.zero_reduce_scatter = z.get("reduce_scatter", ZERO_DEFAULTS["reduce_scatter"])
         self.zero_contiguous_gradients = z.get("contiguous_gradients", ZERO_DEFAULTS["contiguous_gradients"])
         self.zero_reduce_bucket_size = int(z.get("reduce_bucket_size", ZERO_DEFAULTS["reduce_bucket_size"]))

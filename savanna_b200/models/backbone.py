@@ -81,6 +81,9 @@ class Backbone(nn.Module):
         self.checkpoint_num_layers = max(1, cfg.checkpoint_num_layers)
         self.sequence_parallel = cfg.sequence_parallel and state.get_model_parallel_world_size() > 1
         self.mup_output_mult = (1.0 / cfg.mup_width_scale * cfg.mup_output_temp) if cfg.use_mup else 1.0
+        # Set by the trainer around the last micro-batch of a step: called as fn(i) from the backward pass once every
+        # parameter of the blocks with local index >= i has its final gradient (ZeRO reduce-scatter overlap).
+        self.grad_boundary_callback = None
 
     # -- pieces -------------------------------------------------------------------
     @property
@@ -94,11 +97,20 @@ class Backbone(nn.Module):
     def final_norm(self):
         return self.sequential[self.num_layers + 3]
 
+    def _watch(self, x, first_final_block: int):
+        """Report from the backward when the gradient of x (the input of block `first_final_block - 1`) is complete.
+        Autograd runs the nodes of later blocks first (they were created later), so at that moment every node of the
+        blocks >= `first_final_block` has run and their parameter gradients are final."""
+        cb = self.grad_boundary_callback
+        if cb is not None and x.requires_grad:
+            x.register_hook(lambda g, i=first_final_block: cb(i))
+        return x
+
     def _run_blocks(self, x, positions):
         blocks = self.blocks()
         if not (self.checkpoint_activations and self.training):
-            for b in blocks:
-                x = b(x, positions)
+            for i, b in enumerate(blocks):
+                x = b(self._watch(x, i + 1), positions)
             return x
         n = self.checkpoint_num_layers
 
@@ -109,7 +121,8 @@ class Backbone(nn.Module):
                 return h
             return fn
         for s in range(0, len(blocks), n):
-            x = ckpt.checkpoint(chunk_fn(s, min(s + n, len(blocks))), x, positions, use_reentrant=False)
+            e = min(s + n, len(blocks))
+            x = ckpt.checkpoint(chunk_fn(s, e), self._watch(x, e), positions, use_reentrant=False)
         return x
 
     def logits(self, h: torch.Tensor) -> torch.Tensor:

@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..parallel import a2a, halo as halo_mod, halo_fused, state
+from ..parallel import a2a, halo as halo_mod, halo_fused, li_fused, state
 from .filters import ExplicitSingleDecayFilter, ImplicitModalFilter, build_filter
 
 
@@ -186,9 +186,14 @@ class HyenaOperator(nn.Module):
         if modal is not None and self.cfg.cp_hyena_li_algo == "state":
             from ..parallel.modal_cp import hyena_li_modal_state_cp
             return hyena_li_modal_state_cp(feat, *modal, self.conv_bias)
-        full = a2a.split_to_full(feat)
         wl = self.width // cp
         sl = slice(r * wl, (r + 1) * wl)
+        if modal is not None:
+            # scan kernels that read / write the other ranks' staging buffers themselves (the all-to-all inside the scan)
+            z = li_fused.hyena_li_modal_cp(feat, modal[0][sl], modal[1][sl], modal[2][sl], self.conv_bias[sl])
+            if z is not None:
+                return z
+        full = a2a.split_to_full(feat)
         if modal is not None:
             z = ops.hyena_li_modal(full, modal[0][sl], modal[1][sl], modal[2][sl], self.conv_bias[sl])
         else:

@@ -111,6 +111,7 @@ class Trainer:
             print_rank_0(" > context-parallel halos: " + ("peer-memory pull kernels" if on else "NCCL send/recv"))
         self.model, self.optimizer, self.lr_scheduler = self._setup_model_and_optimizer()
         self.partitioned = hasattr(self.optimizer, "finish_backward")      # ZeRO stage 2 / 3
+        self._zero_overlap = self._setup_zero_overlap()
         self.gas = cfg.gradient_accumulation_steps
         self.micro_batch = cfg.train_micro_batch_size_per_gpu
         self.skipped_iters = 0
@@ -180,6 +181,23 @@ class Trainer:
             optimizer = build_generic_optimizer(otype, groups, cfg, p)
         sched = build_lr_scheduler(optimizer, cfg)
         return model, optimizer, sched
+
+    def _setup_zero_overlap(self):
+        """ZeRO-1 reduce-scatter overlapped with the last micro-batch's backward (`zero_optimization.overlap_comm`).
+        Needs the fused peer-memory step and gradients that are final when a block's backward ends: not with sequence
+        parallelism (replicated parameters' gradients are summed over the tensor-parallel group after the backward),
+        pipeline stages, or the gradient-noise-scale estimator (which reads the un-reduced gradients)."""
+        cfg = self.cfg
+        fused = getattr(self.optimizer, "fused", None)
+        if fused is None or not cfg.zero_overlap_comm or getattr(self.model, "is_pipeline_stage", False):
+            return None
+        if cfg.sequence_parallel and state.get_model_parallel_world_size() > 1:
+            return None
+        if cfg.log_gradient_noise_scale or not hasattr(self.model, "blocks"):
+            return None
+        fused.index_blocks(self.optimizer, [list(b.parameters()) for b in self.model.blocks()])
+        print_rank_0(" > ZeRO-1 reduce-scatter overlapped with the last micro-batch's backward")
+        return fused
 
     # ------------------------------------------------------------------ forward
     def compute_loss(self, logits: torch.Tensor, b: Dict[str, torch.Tensor]) -> torch.Tensor:
@@ -256,7 +274,14 @@ class Trainer:
                 b = batch_mod.get_batch(cfg, data_iterator, self.device)
                 loss = self.forward_step(b)
             with self._mark("TRAIN_STEP_BACKWARD"):
-                (loss / self.gas).backward()
+                overlap = self._zero_overlap if micro == self.gas - 1 else None
+                if overlap is not None and overlap.begin_overlap(self.optimizer):
+                    opt = self.optimizer
+                    self.model.grad_boundary_callback = lambda i: overlap.grads_final_from(opt, i)
+                try:
+                    (loss / self.gas).backward()
+                finally:
+                    self.model.grad_boundary_callback = None
                 if self.partitioned:
                     self.optimizer.finish_backward()
             total = loss.detach() if total is None else total + loss.detach()

@@ -185,3 +185,89 @@ def test_hyena_mr_cp_matches_full_sequence(cp, K):
     _close(_unshard(dfs, cp) / gscale, fr.grad / gscale, 2e-2, "mr cp dfeat")
     _rel(dh, hr.grad, 2e-2, "mr cp dh")
     _rel(db, br.grad, 2e-2, "mr cp dbias")
+
+
+@pytest.mark.parametrize("cp", [2, 3])
+def test_hyena_li_cp_scan_with_exchange_inside(cp):
+    """Hyena-LI with the all-to-all inside the scan kernels (csrc/li_scan.cu `sb_li_cp_*`), virtual ranks on one GPU:
+    every rank stages u = x2 v of its zigzag shard, the channel-sharded scans read it from the owners' staging buffers
+    and store y back; z and all gradients equal the fp32 statement of the operator on the unsplit sequence."""
+    from savanna_b200.parallel import li_fused as lf
+    ws = _WS()
+    lib = lf._lib(ws)
+    torch.manual_seed(3)
+    B, D, O, c = 1, 64 * cp, 8, 256
+    d, l, L = D // cp, 2 * c, 2 * cp * c
+    feat = (torch.randn(B, L, 3 * D, device=DEV) * 0.7).to(BF)
+    gamma = torch.randn(D, O, device=DEV) * 0.3 - 1.0
+    p = torch.randn(D, O, device=DEV) * 0.2 - 1.0
+    R = torch.randn(D, O, device=DEV) * 0.3
+    bias = torch.randn(D, device=DEV) * 0.5
+    gz = torch.randn(B, L, D, device=DEV, dtype=BF)
+    fr = feat.float().requires_grad_()
+    gr, Rr, pr, br = (t.clone().requires_grad_() for t in (gamma, R, p, bias))
+    z_ref = ref.hyena_li_modal(fr, gr, Rr, pr, br)
+    z_ref.backward(gz.float())
+    st = torch.cuda.current_stream().cuda_stream
+    fs = [_shard(feat, cp, r) for r in range(cp)]
+    gs = [_shard(gz, cp, r) for r in range(cp)]
+    tc = lf.scan_chunk(c, B, d, L)
+    assert tc > 0 and c % tc == 0
+    NC = L // tc
+    ll_all = lf._pad_order(-torch.exp(p) * torch.exp(gamma), -1.0e30)
+    R_all = lf._pad_order(R, 0.0)
+    ustage = [torch.empty(B, l, D, device=DEV, dtype=BF) for _ in range(cp)]
+    ystage = [torch.full((B, l, D), float("nan"), device=DEV, dtype=BF) for _ in range(cp)]
+    for r in range(cp):
+        assert lib.sb_li_cp_gate(fs[r].data_ptr(), None, ustage[r].data_ptr(), B * l, D, 0, st) == 0
+    ufull = []
+    for r in range(cp):
+        sl = slice(r * d, (r + 1) * d)
+        ll, Rp, bf = ll_all[sl].contiguous(), R_all[sl].contiguous(), bias[sl].contiguous()
+        S = torch.empty(B, NC, d, 16, device=DEV)
+        uf = torch.empty(B, L, d, device=DEV, dtype=BF)
+        um, ym = lf.make_map(_ptrs(ustage), r, cp, l, D), lf.make_map(_ptrs(ystage), r, cp, l, D)
+        assert lib.sb_li_cp_fwd(ctypes.byref(um), ctypes.byref(ym), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(), S.data_ptr(),
+                                uf.data_ptr(), B, L, d, tc, st) == 0
+        ufull.append(uf)
+    zs = []
+    for r in range(cp):
+        z = torch.empty(B, l, D, device=DEV, dtype=BF)
+        assert lib.sb_li_cp_gate(fs[r].data_ptr(), ystage[r].data_ptr(), z.data_ptr(), B * l, D, 1, st) == 0
+        zs.append(z)
+    torch.cuda.synchronize()
+    scale = float(z_ref.detach().abs().max())
+    _close(_unshard(zs, cp) / scale, z_ref.detach() / scale, 2e-2, "li cp z")
+    # backward
+    gstage = [torch.empty(B, l, D, device=DEV, dtype=BF) for _ in range(cp)]
+    ystage = [torch.full((B, l, D), float("nan"), device=DEV, dtype=BF) for _ in range(cp)]
+    dustage = [torch.full((B, l, D), float("nan"), device=DEV, dtype=BF) for _ in range(cp)]
+    for r in range(cp):
+        assert lib.sb_li_cp_gate(fs[r].data_ptr(), gs[r].data_ptr(), gstage[r].data_ptr(), B * l, D, 1, st) == 0
+    dR, dll, db = torch.zeros(D, O, device=DEV), torch.zeros(D, O, device=DEV), torch.zeros(D, device=DEV)
+    for r in range(cp):
+        sl = slice(r * d, (r + 1) * d)
+        ll, Rp, bf = ll_all[sl].contiguous(), R_all[sl].contiguous(), bias[sl].contiguous()
+        S, W, A, dRp, dLp = (torch.empty(B, NC, d, 16, device=DEV) for _ in range(5))
+        dBp = torch.empty(B, NC, d, device=DEV)
+        dyf = torch.empty(B, L, d, device=DEV, dtype=BF)
+        gm, ym, dm = (lf.make_map(_ptrs(x), r, cp, l, D) for x in (gstage, ystage, dustage))
+        assert lib.sb_li_cp_bwd(ctypes.byref(gm), ctypes.byref(ym), ctypes.byref(dm), ufull[r].data_ptr(), dyf.data_ptr(),
+                                ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(), S.data_ptr(), W.data_ptr(), A.data_ptr(),
+                                dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), B, L, d, tc, st) == 0
+        dR[sl] = dRp.sum((0, 1))[:, :O]
+        dll[sl] = (dLp.sum((0, 1)) * torch.exp(ll) * ll)[:, :O]
+        db[sl] = dBp.sum((0, 1))
+    dfs = []
+    for r in range(cp):
+        df = torch.empty_like(fs[r])
+        assert lib.sb_li_cp_finalize_bwd(fs[r].data_ptr(), gs[r].data_ptr(), ystage[r].data_ptr(), dustage[r].data_ptr(),
+                                         df.data_ptr(), B * l, D, st) == 0
+        dfs.append(df)
+    torch.cuda.synchronize()
+    gscale = float(fr.grad.abs().max())
+    _close(_unshard(dfs, cp) / gscale, fr.grad / gscale, 2e-2, "li cp dfeat")
+    _rel(dR, Rr.grad, 3e-2, "li cp dR")
+    _rel(dll, gr.grad, 3e-2, "li cp dgamma")
+    _rel(dll, pr.grad, 3e-2, "li cp dp")
+    _rel(db, br.grad, 3e-2, "li cp dbias")

@@ -143,6 +143,54 @@ def test_data_parallel_training_fused_zero():
     _spawn(_w_dp_train, 2)
 
 
+def _w_zero_overlap(rank, world, checkpointing):
+    """ZeRO-1 with the reduce-scatter launched from the last micro-batch's backward (side stream, device barrier per
+    block boundary) against the same run with the whole reduce-scatter inside the optimizer step: identical loss traces
+    and gradient norms (the same kernels reduce the same ranges; only the order of the squared-norm partials differs)."""
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.ops import cuda_ops
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(overlap):
+        cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_gpu.yml")],
+                                     {"global_num_gpus": world, "gradient_accumulation_steps": 2, "gradient_clipping": 0.3,
+                                      "checkpoint_activations": checkpointing, "checkpoint_num_layers": 2,
+                                      "zero_optimization": {"stage": 1, "overlap_comm": overlap}})
+        state.destroy_model_parallel()
+        tr = Trainer(cfg, load=False)
+        fused = tr.optimizer.fused
+        assert fused is not None and (tr._zero_overlap is not None) == overlap
+
+        def it():
+            i = 0
+            while True:
+                yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=1000 * rank + i, pin=True)}
+                i += 1
+        d = it()
+        out = []
+        for _ in range(5):
+            loss = float(tr.train_step(d))
+            out.append((loss, float(tr.grad_norm)))
+        cuda_ops.check_status()
+        return out, fused.overlap_launches
+
+    base, n0 = run(False)
+    over, n1 = run(True)
+    assert n0 == 0 and n1 > 0, (n0, n1)
+    for (la, na), (lb, nb) in zip(base, over):
+        assert abs(la - lb) < 1e-3 * max(1.0, abs(la)), (base, over)
+        assert abs(na - nb) < 2e-3 * max(1.0, abs(na)), (base, over)
+
+
+@needs2
+@pytest.mark.parametrize("checkpointing", [False, True])
+def test_zero_reduce_scatter_overlapped_with_backward(checkpointing):
+    _spawn_args(_w_zero_overlap, 2, checkpointing)
+
+
 def _w_fused_tp(rank, world):
     import torch.distributed as dist
     from savanna_b200 import ops
