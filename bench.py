@@ -203,7 +203,7 @@ def describe_dtype(cfg, fused_tp_fp8) -> str:
         return "bf16"
     d = "bf16 + fp8 (e4m3/e5m2, per-tensor delayed scaling) projection GEMMs"
     if fused_tp_fp8 is False:
-        d += " [tensor-parallel projections on the fused path run bf16]"
+        d += " [fused tensor-parallel projections ran bf16 operands]"
     return d
 
 

@@ -968,6 +968,27 @@ extern "C" int sb_quantize_fp8(const void* x, void* q, float* amax, float* scale
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// The two halves of sb_quantize_fp8 as separate calls, for operands that are sharded over several GPUs and need ONE
+// scale: every rank computes its amax, the ranks take the maximum (a collective on the same stream), every rank
+// quantises with the common value.
+extern "C" int sb_amax_bf16(const void* x, float* amax, long long n, cudaStream_t st) {
+  if (n % 8) return -1;
+  if (cudaMemsetAsync(amax, 0, sizeof(float), st) != cudaSuccess) return -2;
+  if (n == 0) return 0;
+  const size_t n8 = (size_t)n / 8;
+  amax_kernel<<<grid_for(n8, 512, sb::num_sms() * 8), 512, 0, st>>>((const bf16*)x, amax, n8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int sb_quantize_fp8_with_amax(const void* x, void* q, const float* amax, float* scale_inv, long long n, int fmt,
+                                         cudaStream_t st) {
+  if (n % 8) return -1;
+  if (n == 0) return 0;
+  const size_t n8 = (size_t)n / 8;
+  quantize_fp8_kernel<<<grid_for(n8, 512, sb::num_sms() * 8), 512, 0, st>>>((const bf16*)x, (uint8_t*)q, n8, amax, scale_inv, fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 // Delayed-scaling variant (one pass): see quantize_fp8_delayed_kernel.  `hist` has `slots` floats, all zero before the
 // first use of a site; the caller advances `cur` by one (mod slots) per call and primes slot 0 with sb_quantize_fp8.
 extern "C" int sb_quantize_fp8_delayed(const void* x, void* q, float* hist, int slots, int cur, float* scale_inv,

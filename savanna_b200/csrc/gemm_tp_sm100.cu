@@ -13,6 +13,11 @@
 //                        owner-side kernel then sums the `world` slots (+ bias, + residual).  Stores overlap the
 //                        remaining tiles' math; the summation order is fixed, so the result is deterministic.
 //
+// Operands are bf16 (EB = 2) or one-byte e4m3 / e5m2 (EB = 1, kind::f8f6f4; the result is scaled by two device scalars,
+// the operands' de-quantisation factors, in the epilogue): a gathered fp8 activation crosses NVLink with half the bytes.
+// A micro-batch of `batch` sequences is one launch: rank r's shard is [batch, Ms, K] and the gathered / scattered
+// tensor [batch, world, Ms, .], so row block (b, r) of the full tensor belongs to rank r.
+//
 // No kernel here waits on another GPU: flags are written and read by CTAs of the same grid (all co-resident: the
 // grid never exceeds the SM count and every CTA needs a full SM's shared memory), and the cross-GPU ordering
 // (peers' shards complete before the pull, stores landed before the reduction) is established by the caller with
@@ -23,6 +28,8 @@ namespace sb {
 
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                    uint32_t box_outer);
 
 namespace tp {
 
@@ -39,17 +46,35 @@ struct Params {
   // plain output (when rs_world == 0)
   __nv_bfloat16* C; int ldc;
   const __nv_bfloat16* bias;
-  // all-gather of A
-  int ag_world, ag_me, ag_tiles_per_rank, ag_epoch, n_gemm_ctas;
+  // all-gather of A (element size EB bytes)
+  int ag_world, ag_me, ag_tiles_per_rank, ag_batch, ag_epoch, n_gemm_ctas;   // tiles per (rank, sequence) block
   int* ag_flags;                          // [m_tiles], local; value == ag_epoch means "tile is in the gather buffer"
-  const __nv_bfloat16* ag_src[MAXR];      // peers' shards [Ms, K], leading dim ag_src_ld
+  const uint8_t* ag_src[MAXR];            // peers' shards [batch * Ms, K], leading dim ag_src_ld (elements)
   int ag_src_ld;
-  __nv_bfloat16* ag_dst;                  // local gather buffer [M, K], leading dim K
+  uint8_t* ag_dst;                        // local gather buffer [M, K], leading dim K
   // reduce-scatter of C
-  int rs_world, rs_me, rs_rows_per_owner;
-  __nv_bfloat16* rs_dst[MAXR];            // owners' staging buffers [world, Ms, N]
+  int rs_world, rs_me, rs_rows_per_block, rs_batch;
+  __nv_bfloat16* rs_dst[MAXR];            // owners' staging buffers [world, batch * Ms, N]
   uint32_t* status;
+  const float* alpha; const float* alpha2;  // de-quantisation factors of the two operands (fp8), or null
+  int a_fmt, b_fmt;                         // fp8 formats for the instruction descriptor: 0 = e4m3, 1 = e5m2
 };
+
+// Row-block bookkeeping of the gathered operand: m-tile `mt` of the full [batch, world, Ms] row space.
+__device__ __forceinline__ void ag_tile_source(const Params& p, int mt, int& src_rank, int& src_row0) {
+  const int block = mt / p.ag_tiles_per_rank, t = mt - block * p.ag_tiles_per_rank;
+  src_rank = block % p.ag_world;
+  const int b = block / p.ag_world;
+  src_row0 = (b * p.ag_tiles_per_rank + t) * BM;          // row inside the owner's shard [batch * Ms, K]
+}
+// Processing order: this rank's own blocks first, then the next rank's, ... (index -> m-tile of the full row space)
+__device__ __forceinline__ int ag_ordered_tile(const Params& p, int idx) {
+  const int per_rank = p.ag_batch * p.ag_tiles_per_rank;
+  const int rr = idx / per_rank, rem = idx - rr * per_rank;
+  const int b = rem / p.ag_tiles_per_rank, t = rem - b * p.ag_tiles_per_rank;
+  const int r = (rr + p.ag_me) % p.ag_world;
+  return (b * p.ag_world + r) * p.ag_tiles_per_rank + t;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
   const int per_group = GROUP_M * n_tiles;
@@ -70,26 +95,30 @@ __device__ __forceinline__ void st_release(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-template <int B_MN>
+template <int B_MN, int EB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_constant__ CUtensorMap tmA_gather,
                const __grid_constant__ CUtensorMap tmB, Params p) {
   extern __shared__ uint8_t smem_raw[];
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = 128 / EB;                          // K elements per k-block (a shared-memory row is 128 bytes)
+  constexpr int MNB = 128 / EB;                          // MN elements per 128-byte row of an MN-major box
+  constexpr int MN_BOX_BYTES = BKE * 128;
+  const int num_kb = (p.K + BKE - 1) / BKE;
   const bool ag = p.ag_world > 1;
   const int n_gemm = ag ? p.n_gemm_ctas : gridDim.x;
   const int n_copy_ctas = gridDim.x - n_gemm;            // copy CTAs take the lowest block indices: scheduled first
-  const int first_local_tile = ag ? p.ag_me * p.ag_tiles_per_rank : 0;
   const int gemm_id = (int)blockIdx.x - n_copy_ctas;
 
   if (ag && (int)blockIdx.x < n_copy_ctas) {
     // ------------------------------------------------------------------ copy CTAs: pull remote tiles, publish local flags
     const int cid = blockIdx.x, n_copy = n_copy_ctas;
-    const int n_remote = m_tiles - p.ag_tiles_per_rank;
-    const int vec_per_row = p.K >> 3;
-    const bool contiguous = p.ag_src_ld == p.K && p.K * 2 <= CP_CHUNK;   // whole rows per bulk chunk
+    const int n_local = p.ag_batch * p.ag_tiles_per_rank;
+    const int n_remote = m_tiles - n_local;
+    const int row_bytes_i = p.K * EB;
+    const int vec_per_row = row_bytes_i >> 4;
+    const bool contiguous = p.ag_src_ld == p.K && row_bytes_i <= CP_CHUNK;   // whole rows per bulk chunk
     const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
     const uint32_t cbar = ring + CP_NB * CP_CHUNK;                       // CP_NB mbarriers
     __shared__ int copy_abort;
@@ -101,16 +130,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
     __syncthreads();
     uint32_t issued = 0, done = 0;                                       // chunk counters over the whole CTA lifetime
     for (int idx = cid; idx < n_remote; idx += n_copy) {
-      const int mt = (first_local_tile + p.ag_tiles_per_rank + idx) % m_tiles;     // rotated order: next rank's shard first
-      const int src_rank = mt / p.ag_tiles_per_rank;
-      const int src_row0 = (mt - src_rank * p.ag_tiles_per_rank) * BM;
+      const int mt = ag_ordered_tile(p, n_local + idx);                   // rotated order: next rank's shard first
+      int src_rank, src_row0;
+      ag_tile_source(p, mt, src_rank, src_row0);
       const int rows = min(BM, p.M - mt * BM);
       if (contiguous) {
         // one thread drives a ring of bulk copies: peer memory -> shared -> local gather buffer
         if (threadIdx.x == 0) {
-          const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * p.K);
-          char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * p.K);
-          const uint32_t row_bytes = (uint32_t)p.K * 2u;
+          const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * row_bytes_i);
+          char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
+          const uint32_t row_bytes = (uint32_t)row_bytes_i;
           const uint32_t rows_per_chunk = max(1u, CP_CHUNK / row_bytes);
           const uint32_t chunk = rows_per_chunk * row_bytes;
           const uint32_t total = (uint32_t)rows * row_bytes;
@@ -143,10 +172,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
           }
         }
       } else {
-        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld);
-        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * p.K);
+        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld * EB);
+        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
         const int total = rows * vec_per_row;
-        const int src_ld8 = p.ag_src_ld >> 3;
+        const int src_ld8 = (p.ag_src_ld * EB) >> 4;
         for (int i = threadIdx.x; i < total; i += NUM_THREADS * 8) {
           uint4 v[8];
 #pragma unroll
@@ -196,7 +225,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
   // tile -> (actual m tile, n tile): local shard first when the A operand is being gathered
   auto coords = [&](int tile, int& mt, int& nt) {
     int mr; tile_coords(tile, m_tiles, n_tiles, mr, nt);
-    mt = ag ? (mr + first_local_tile) % m_tiles : mr;
+    mt = ag ? ag_ordered_tile(p, mr) : mr;
   };
 
   if (warp == 0) {
@@ -205,7 +234,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
       for (int tile = gemm_id; tile < num_tiles && ok; tile += n_gemm) {
         int mt, nt; coords(tile, mt, nt);
         const int n0 = nt * BN;
-        const bool local = !ag || (mt >= first_local_tile && mt < first_local_tile + p.ag_tiles_per_rank);
+        int src_rank = 0, src_row0 = mt * BM;
+        if (ag) ag_tile_source(p, mt, src_rank, src_row0);
+        const bool local = !ag || src_rank == p.ag_me;
         if (!local) {
           // bounded wait for the copy CTAs
           const unsigned long long t0 = globaltimer();
@@ -224,17 +255,17 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
           fence_proxy_async();
         }
         const CUtensorMap* tma = local && ag ? &tmA_local : (ag ? &tmA_gather : &tmA_local);
-        const int m0 = (local && ag) ? (mt - first_local_tile) * BM : mt * BM;
+        const int m0 = (local && ag) ? src_row0 : mt * BM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES, b_dst = a_dst + A_STAGE;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * BKE;
           tma_load_2d(a_dst, tma, k0, m0, full_bar(stage));
           if (B_MN == 0) tma_load_2d(b_dst, &tmB, k0, n0, full_bar(stage));
           else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, n0 + 64 * j, k0, full_bar(stage));
+            for (int j = 0; j < BN / MNB; ++j) tma_load_2d(b_dst + j * MN_BOX_BYTES, &tmB, n0 + MNB * j, k0, full_bar(stage));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -243,8 +274,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, B_MN);
-      constexpr uint32_t b_lbo = B_MN ? 8192u : 16u, b_step = B_MN ? (UMMA_K * 128u) >> 4 : (UMMA_K * 2u) >> 4;
+      constexpr int UK = 32 / EB;                       // K elements per MMA (32 bytes)
+      const uint32_t idesc = EB == 2 ? umma_idesc_bf16(BM, BN, 0, B_MN) : umma_idesc_fp8(BM, BN, 0, B_MN, p.a_fmt, p.b_fmt);
+      constexpr uint32_t b_lbo = B_MN ? (uint32_t)MN_BOX_BYTES : 16u, b_step = B_MN ? (UK * 128u) >> 4 : 2u;
       int stage = 0; uint32_t phase = 0; uint32_t acc_phase[2] = {0u, 0u}; int local = 0; bool ok = true;
       for (int tile = gemm_id; tile < num_tiles && ok; tile += n_gemm, ++local) {
         const int acc = local & 1;
@@ -259,7 +291,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
           const uint64_t adesc = umma_smem_desc(a_addr, 16u, 1024u);
           const uint64_t bdesc = umma_smem_desc(a_addr + A_STAGE, b_lbo, 1024u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16(d_tmem, adesc + k * 2, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            if (EB == 2) umma_bf16(d_tmem, adesc + k * 2, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_fp8(d_tmem, adesc + k * 2, bdesc + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -270,6 +305,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
     const int q = warp & 3;
     uint32_t acc_phase[2] = {0u, 0u}; int local = 0; bool ok = true;
     const bool rs = p.rs_world > 1;
+    const float alpha = (p.alpha ? p.alpha[0] : 1.f) * (p.alpha2 ? p.alpha2[0] : 1.f);
     for (int tile = gemm_id; tile < num_tiles && ok; tile += n_gemm, ++local) {
       const int acc = local & 1;
       int mt, nt; coords(tile, mt, nt);
@@ -283,10 +319,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
       bool staged = false;
       __nv_bfloat16* wbase = nullptr;                 // staged path: destination of row (mt*BM + q*32) of this warp
       if (rs) {
-        const int row_w = mt * BM + q * 32;           // rows of one warp never straddle owners (rows_per_owner % 128 == 0)
-        const int owner = row_w / p.rs_rows_per_owner, lr = row_w - owner * p.rs_rows_per_owner;
-        const int ow = owner < p.rs_world ? owner : 0;
-        wbase = p.rs_dst[ow] + ((size_t)p.rs_me * p.rs_rows_per_owner + lr) * p.N;
+        const int row_w = mt * BM + q * 32;           // rows of one warp never straddle blocks (rows_per_block % 128 == 0)
+        const int block = row_w / p.rs_rows_per_block, in_block = row_w - block * p.rs_rows_per_block;
+        const int owner = block % p.rs_world, b = block / p.rs_world;
+        const int ow = b < p.rs_batch ? owner : 0;
+        const int lr = (b < p.rs_batch ? b : 0) * p.rs_rows_per_block + in_block;      // row in the owner's [batch * Ms, N] slot
+        wbase = p.rs_dst[ow] + ((size_t)p.rs_me * p.rs_batch * p.rs_rows_per_block + lr) * p.N;
         crow = wbase + (size_t)lane * p.N;
         staged = ow != p.rs_me;                       // peer rows: coalesce through shared memory into 128-byte row segments
       } else {
@@ -306,7 +344,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
             uint4 out;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha, __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha);
             *reinterpret_cast<uint4*>(srow + v * 8) = out;
           }
           if (c & 1) {
@@ -329,7 +367,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
             if (col + 8 <= p.N) {
               float f[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]) * alpha;
               if (p.bias && !rs) {
                 const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
                 const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
@@ -390,17 +428,17 @@ __global__ void rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, cons
   }
 }
 
-// Plain peer gather (used where the gathered operand feeds a reduction dim: weight gradients)
-__global__ void gather_rows_kernel(Params p) {
-  const int vec_per_row = p.K >> 3;
-  const size_t rows_per_rank = (size_t)p.ag_tiles_per_rank * BM;
-  const size_t total = (size_t)p.M * vec_per_row;
-  const int src_ld8 = p.ag_src_ld >> 3;
+// Plain peer gather (used where the gathered operand feeds a reduction dim: weight gradients): the full
+// [batch, world, Ms, K] row space from the ranks' shards [batch * Ms, K]; `row16` = 16-byte vectors per row.
+__global__ void gather_rows_kernel(Params p, int row16, int src_ld16) {
+  const size_t total = (size_t)p.M * row16;
+  const int rows_per_block = p.ag_tiles_per_rank * BM;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = idx / vec_per_row; const int c = idx - r * vec_per_row;
-    const int src = r / rows_per_rank;
-    const size_t lr = r - src * rows_per_rank;
-    reinterpret_cast<uint4*>(p.ag_dst)[idx] = reinterpret_cast<const uint4*>(p.ag_src[src])[lr * src_ld8 + c];
+    const size_t r = idx / row16; const int c = idx - r * row16;
+    const int block = r / rows_per_block, in_block = r - (size_t)block * rows_per_block;
+    const int src = block % p.ag_world, bb = block / p.ag_world;
+    const size_t lr = (size_t)bb * rows_per_block + in_block;
+    reinterpret_cast<uint4*>(p.ag_dst)[idx] = reinterpret_cast<const uint4*>(p.ag_src[src])[lr * src_ld16 + c];
   }
 }
 
@@ -410,42 +448,54 @@ __global__ void gather_rows_kernel(Params p) {
 using namespace sb;
 using namespace sb::tp;
 
-// Fused projection.  A: own shard [Ms, K] (leading dim lda) when ag_world > 1, else the full [M, K].  B: [N, K]
-// (b_mn = 0) or [K, N] (b_mn = 1).  ag_src: `ag_world` shard base pointers (index = rank; entry `ag_me` = A);
-// gather: local workspace [M, K]; flags: [ceil(M/128)] ints (any contents; `epoch` must differ from the previous
-// call's on the same flags).  rs_dst: `rs_world` staging base pointers [rs_world, M/rs_world, N]; with rs_world <= 1
-// the result goes to C (ldc) with optional bias.
+// Fused projection.  A: own shard [batch * Ms, K] (leading dim lda) when ag_world > 1, else the full [M, K].  B: [N, K]
+// (b_mn = 0) or [K, N] (b_mn = 1).  elem_bytes: 2 = bf16 operands, 1 = fp8 (a_fmt / b_fmt: 0 = e4m3, 1 = e5m2; the result
+// is multiplied by alpha[0] * alpha2[0], device scalars, either may be null).  ag_src: `ag_world` shard base pointers
+// (index = rank; entry `ag_me` = A); gather: local workspace [M, K]; flags: [ceil(M/128)] ints (any contents; `epoch` must
+// differ from the previous call's on the same flags).  The full row space is [batch, world, Ms]: row block (b, r) is rank
+// r's.  rs_dst: `rs_world` staging base pointers [rs_world, batch * M / (batch * rs_world), N]; with rs_world <= 1 the
+// result goes to C (ldc) with optional bias.
 extern "C" int sb_gemm_tp(const void* A, int lda, const void* B, int ldb, int b_mn, void* C, int ldc, const void* bias,
-                          int M, int N, int K, int ag_world, int ag_me, const void* const* ag_src, void* gather, int* flags,
-                          int epoch, int n_copy_ctas, int rs_world, int rs_me, void* const* rs_dst, unsigned int* status,
+                          int M, int N, int K, int batch, int elem_bytes, const float* alpha, const float* alpha2, int a_fmt,
+                          int b_fmt, int ag_world, int ag_me, const void* const* ag_src, void* gather, int* flags, int epoch,
+                          int n_copy_ctas, int rs_world, int rs_me, void* const* rs_dst, unsigned int* status,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8)) return -3;
+  const int EBv = elem_bytes == 1 ? 1 : 2;
+  const int al = 16 / EBv;                                  // elements per 16 bytes
+  if ((N % 8) || (K % al) || (lda % al) || (ldb % al) || batch < 1 || (M % batch)) return -3;
+  if (EBv == 1 && b_mn && (N % 16)) return -3;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = (__nv_bfloat16*)C; p.ldc = ldc; p.bias = (const __nv_bfloat16*)bias; p.status = status;
+  p.alpha = alpha; p.alpha2 = alpha2; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   const bool ag = ag_world > 1, rs = rs_world > 1;
+  const uint32_t bke = 128 / EBv;
+  auto tmap = [&](CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t bi, uint32_t bo) {
+    return EBv == 2 ? make_tmap_2d_bf16(out, base, inner, outer, ld, bi, bo) : make_tmap_2d_u8(out, base, inner, outer, ld, bi, bo);
+  };
   CUtensorMap tmL, tmG, tmB;
   int rc;
   if (ag) {
-    if (ag_world > MAXR || (M % ag_world) || ((M / ag_world) % BM)) return -7;
-    const int Ms = M / ag_world;
-    p.ag_world = ag_world; p.ag_me = ag_me; p.ag_tiles_per_rank = Ms / BM; p.ag_epoch = epoch; p.ag_flags = flags;
-    for (int r = 0; r < ag_world; ++r) p.ag_src[r] = (const __nv_bfloat16*)ag_src[r];
-    p.ag_src_ld = lda; p.ag_dst = (__nv_bfloat16*)gather;
-    if ((rc = make_tmap_2d_bf16(&tmL, A, K, Ms, lda, BK, BM))) return rc;
-    if ((rc = make_tmap_2d_bf16(&tmG, gather, K, M, K, BK, BM))) return rc;
+    if (ag_world > MAXR || (M % (ag_world * batch)) || ((M / (ag_world * batch)) % BM)) return -7;
+    const int Ms = M / (ag_world * batch);
+    p.ag_world = ag_world; p.ag_me = ag_me; p.ag_tiles_per_rank = Ms / BM; p.ag_batch = batch; p.ag_epoch = epoch;
+    p.ag_flags = flags;
+    for (int r = 0; r < ag_world; ++r) p.ag_src[r] = (const uint8_t*)ag_src[r];
+    p.ag_src_ld = lda; p.ag_dst = (uint8_t*)gather;
+    if ((rc = tmap(&tmL, A, K, (uint64_t)Ms * batch, lda, bke, BM))) return rc;
+    if ((rc = tmap(&tmG, gather, K, M, K, bke, BM))) return rc;
   } else {
-    if ((rc = make_tmap_2d_bf16(&tmL, A, K, M, lda, BK, BM))) return rc;
+    if ((rc = tmap(&tmL, A, K, M, lda, bke, BM))) return rc;
     tmG = tmL;
   }
-  if (!b_mn) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, BN);
-  else       rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK);
+  if (!b_mn) rc = tmap(&tmB, B, K, N, ldb, bke, BN);
+  else       rc = tmap(&tmB, B, N, K, ldb, bke, bke);
   if (rc) return rc;
   if (rs) {
-    if (rs_world > MAXR || (M % rs_world) || ((M / rs_world) % BM)) return -8;
-    p.rs_world = rs_world; p.rs_me = rs_me; p.rs_rows_per_owner = M / rs_world;
+    if (rs_world > MAXR || (M % (rs_world * batch)) || ((M / (rs_world * batch)) % BM)) return -8;
+    p.rs_world = rs_world; p.rs_me = rs_me; p.rs_rows_per_block = M / (rs_world * batch); p.rs_batch = batch;
     for (int r = 0; r < rs_world; ++r) p.rs_dst[r] = (__nv_bfloat16*)rs_dst[r];
   } else if (ldc % 8) return -3;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -454,11 +504,14 @@ extern "C" int sb_gemm_tp(const void* A, int lda, const void* B, int ldb, int b_
   int n_gemm = sms - n_copy;
   if (tiles < n_gemm) n_gemm = tiles;
   p.n_gemm_ctas = n_gemm;
-  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, Params) = b_mn ? gemm_tp_kernel<1> : gemm_tp_kernel<0>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[b_mn ? 1 : 0]) {
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, Params);
+  if (EBv == 2) kern = b_mn ? gemm_tp_kernel<1, 2> : gemm_tp_kernel<0, 2>;
+  else          kern = b_mn ? gemm_tp_kernel<1, 1> : gemm_tp_kernel<0, 1>;
+  static bool attr_set[4] = {false, false, false, false};
+  const int ai = (EBv == 1 ? 2 : 0) + (b_mn ? 1 : 0);
+  if (!attr_set[ai]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -5;
-    attr_set[b_mn ? 1 : 0] = true;
+    attr_set[ai] = true;
   }
   kern<<<n_gemm + n_copy, NUM_THREADS, SMEM_BYTES, stream>>>(tmL, tmG, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;
@@ -476,12 +529,16 @@ extern "C" int sb_rs_reduce(const void* staging, const void* bias, const void* r
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// gather[M, K] <- concat over ranks of src[r][Ms, K] (leading dim ld)
-extern "C" int sb_gather_rows(const void* const* src, int world, void* gather, int M, int K, int ld, cudaStream_t stream) {
-  if ((K % 8) || (ld % 8) || world > MAXR || (M % world) || ((M / world) % BM)) return -1;
+// gather[M, K] <- the full [batch, world, Ms] row space from src[r] = rank r's shard [batch * Ms, K] (leading dim ld);
+// elem_bytes = 2 (bf16) or 1 (fp8)
+extern "C" int sb_gather_rows(const void* const* src, int world, void* gather, int M, int K, int ld, int batch, int elem_bytes,
+                              cudaStream_t stream) {
+  const int EBv = elem_bytes == 1 ? 1 : 2, al = 16 / EBv;
+  if ((K % al) || (ld % al) || world > MAXR || batch < 1 || (M % (world * batch)) || ((M / (world * batch)) % BM)) return -1;
   Params p{};
-  p.M = M; p.K = K; p.ag_tiles_per_rank = (M / world) / BM; p.ag_src_ld = ld; p.ag_dst = (__nv_bfloat16*)gather;
-  for (int r = 0; r < world; ++r) p.ag_src[r] = (const __nv_bfloat16*)src[r];
-  gather_rows_kernel<<<sb::num_sms() * 4, 512, 0, stream>>>(p);
+  p.M = M; p.K = K; p.ag_world = world; p.ag_batch = batch; p.ag_tiles_per_rank = (M / (world * batch)) / BM;
+  p.ag_dst = (uint8_t*)gather;
+  for (int r = 0; r < world; ++r) p.ag_src[r] = (const uint8_t*)src[r];
+  gather_rows_kernel<<<sb::num_sms() * 4, 512, 0, stream>>>(p, K * EBv / 16, ld * EBv / 16);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

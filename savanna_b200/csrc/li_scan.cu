@@ -203,7 +203,11 @@ __global__ void li_bwd_prefix_kernel(float* __restrict__ S, float* __restrict__ 
     }
   }
   if (w_end) w_end[idx] = cw;
-  float ca = dstate_out ? dstate_out[idx] : 0.f;
+  // The gradient of the returned state, g = dL/ds[L-1], enters the adjoint at the LAST step without a factor lam
+  // (a[L-1] = R dy[L-1] + g): the last chunk therefore starts from a zero adjoint, the reverse kernel adds g at its first
+  // step, and the carry into the chunk before it picks up lam^(len-1) g.
+  const float gout = dstate_out ? dstate_out[idx] : 0.f;
+  float ca = 0.f;
   for (int n0 = d.NC - 1; n0 >= 0; n0 -= 8) {
     float la[8];
 #pragma unroll
@@ -215,6 +219,7 @@ __global__ void li_bwd_prefix_kernel(float* __restrict__ S, float* __restrict__ 
         A[base + (size_t)n * per_b] = ca;
         const int len = min(d.TC, d.L - n * d.TC);
         ca = (len == d.TC ? st_full : __expf(ll * len)) * ca + la[j];
+        if (n == d.NC - 1 && gout != 0.f) ca += (len == d.TC ? stm1_full : __expf(ll * (len - 1))) * gout;
       }
     }
   }
@@ -273,7 +278,8 @@ li_bwd_apply_fwd_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
 __global__ void __launch_bounds__(LI_THREADS)
 li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
                         const float* __restrict__ R, const float* __restrict__ bias, const float* __restrict__ Ain,
-                        const bf16* __restrict__ dx1, bf16* __restrict__ dfeat, LiDims d) {
+                        const bf16* __restrict__ dx1, bf16* __restrict__ dfeat, const float* __restrict__ dstate_out,
+                        LiDims d) {
   const int ch = blockIdx.x * LI_THREADS + threadIdx.x;
   if (ch >= d.D) return;
   const int n = blockIdx.y, b = blockIdx.z;
@@ -289,13 +295,22 @@ li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
   const bf16* g = dz + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
   const bf16* i1 = dx1 + ((size_t)b * d.L + (t1 - 1)) * d.D + ch;
   bf16* df = dfeat + ((size_t)b * d.L + (t1 - 1)) * 3 * d.D + 3 * ch;
+  const bool tail = dstate_out != nullptr && n == d.NC - 1;       // the chunk that ends the sequence: see li_bwd_prefix_kernel
+  float gs[LO];
+  if (tail) load_vec16(dstate_out + ((size_t)b * d.D + ch) * LO, gs);
 #pragma unroll 8
   for (int t = t1 - 1; t >= t0; --t, f -= 3 * d.D, g -= d.D, i1 -= d.D, df -= 3 * d.D) {
     const float x1 = b2f(f[0]), x2 = b2f(f[1]), v = b2f(f[2]);
     const float dy = b2f(*g) * x1;
     float du = be * dy;
 #pragma unroll
-    for (int o = 0; o < LO; ++o) { a[o] = rr[o] * dy + lam[o] * a[o]; du += a[o]; }
+    for (int o = 0; o < LO; ++o) { a[o] = rr[o] * dy + lam[o] * a[o]; }
+    if (tail && t == t1 - 1) {
+#pragma unroll
+      for (int o = 0; o < LO; ++o) a[o] += gs[o];
+    }
+#pragma unroll
+    for (int o = 0; o < LO; ++o) du += a[o];
     df[0] = *i1;
     df[1] = __float2bfloat16_rn(du * v);
     df[2] = __float2bfloat16_rn(du * x2);
@@ -599,7 +614,7 @@ extern "C" int sb_li_bwd(const void* feat, const void* dz, const float* loglam, 
   li_bwd_apply_fwd_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, S, W,
                                                       (bf16*)dx1_tmp, dRp, dLp, dBp, d);
   li_bwd_apply_rev_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, A,
-                                                      (const bf16*)dx1_tmp, (bf16*)dfeat, d);
+                                                      (const bf16*)dx1_tmp, (bf16*)dfeat, dstate_out, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

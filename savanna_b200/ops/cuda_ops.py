@@ -388,34 +388,14 @@ def linear(x, w, bias=None, fp8: bool = False, residual=None):
     return _Linear.apply(x, w, bias, residual)
 
 
-_FP8_TP_WARNED = False
-
-
-def _note_fp8_on_fused_tp(fp8: bool) -> None:
-    """The fused tensor-parallel projections compute in bf16.  A layer that asks for fp8 there is told so once (the
-    benchmark's dtype label carries the same note) instead of being silently given another precision."""
-    global _FP8_TP_WARNED
-    if fp8 and not _FP8_TP_WARNED:
-        _FP8_TP_WARNED = True
-        from .. import print_rank_0
-        print_rank_0(" > note: fp8 was requested for tensor/sequence-parallel projections; the fused all-gather->GEMM / "
-                     "GEMM->reduce-scatter kernels run them in bf16 (set comm_path: nccl for fp8 GEMMs behind NCCL collectives)")
-
-
 def linear_allgather(x, w, bias, seq_dim, fp8):
     from ..parallel import fused_tp
-    y = fused_tp.linear_allgather(x, w, bias, seq_dim)
-    if y is not None:
-        _note_fp8_on_fused_tp(fp8)
-    return y
+    return fused_tp.linear_allgather(x, w, bias, seq_dim, fp8=bool(fp8) and _is_bf16(x, w, bias))
 
 
 def linear_reducescatter(x, w, seq_dim, fp8):
     from ..parallel import fused_tp
-    y = fused_tp.linear_reducescatter(x, w, seq_dim)
-    if y is not None:
-        _note_fp8_on_fused_tp(fp8)
-    return y
+    return fused_tp.linear_reducescatter(x, w, seq_dim, fp8=bool(fp8) and _is_bf16(x, w))
 
 
 # ----------------------------------------------------------------------------- RMSNorm

@@ -10,8 +10,9 @@ and run the plain GEMM.  Reference call sites replaced: savanna/mpu/mappings.py:
 savanna/mpu/layers.py:525-560 and :746-786 (NCCL all-gather / reduce-scatter next to cuBLAS GEMMs).
 
 Both entry points return None when the fused path does not apply (workspace not set up, tensor-parallel size 1,
-shard not a multiple of 128 rows, non-bf16; a micro-batch > 1 runs one sequence at a time): the caller then runs the NCCL collective and the GEMM
-separately.  Cross-GPU ordering uses stream-ordered device barriers (csrc/peer_barrier.cu, bounded waits); symmetric staging buffers are
+shard not a multiple of 128 rows, non-bf16): the caller then runs the NCCL collective and the GEMM separately.  A
+micro-batch of several sequences is one launch.  With `fp8` the operands are e4m3 / e5m2 bytes (per-tensor scaling;
+an operand that is sharded over the group is quantised with the group-wide amax so that all shards share one scale).  Cross-GPU ordering uses stream-ordered device barriers (csrc/peer_barrier.cu, bounded waits); symmetric staging buffers are
 double-buffered so that a rank can stage its next operand while a peer still reads the previous one.
 """
 from __future__ import annotations
@@ -26,6 +27,9 @@ from . import state
 
 _WS: Optional["TPWorkspace"] = None
 bf16 = torch.bfloat16
+FP8_CALLS = 0               # fused projections that ran on fp8 operands
+_SEEN_FP8_REQUEST = False   # a layer asked for fp8 on the fused path
+E4M3, E5M2 = 0, 1
 
 
 class TPWorkspace:
@@ -36,11 +40,16 @@ class TPWorkspace:
         self.lib = cuda_ops.require()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         self.lib.sb_gemm_tp.restype = I
-        self.lib.sb_gemm_tp.argtypes = [P, I, P, I, I, P, I, P, I, I, I, I, I, P, P, P, I, I, I, I, P, P, P]
+        self.lib.sb_gemm_tp.argtypes = [P, I, P, I, I, P, I, P, I, I, I, I, I, P, P, I, I, I, I, P, P, P, I, I, I, I, P, P, P]
         self.lib.sb_rs_reduce.restype = I
         self.lib.sb_rs_reduce.argtypes = [P, P, P, P, I, LL, I, P]
         self.lib.sb_gather_rows.restype = I
-        self.lib.sb_gather_rows.argtypes = [P, I, P, I, I, I, P]
+        self.lib.sb_gather_rows.argtypes = [P, I, P, I, I, I, I, I, P]
+        LLc = ctypes.c_longlong
+        self.lib.sb_amax_bf16.restype = I
+        self.lib.sb_amax_bf16.argtypes = [P, P, LLc, P]
+        self.lib.sb_quantize_fp8_with_amax.restype = I
+        self.lib.sb_quantize_fp8_with_amax.argtypes = [P, P, P, P, LLc, I, P]
         self.group = group if group is not None else dist.group.WORLD
         self.world = len(ranks)
         self.rank = ranks.index(dist.get_rank())
@@ -94,17 +103,20 @@ class TPWorkspace:
         return self.epoch
 
     # ---- kernel launchers -------------------------------------------------------------------------------
-    def gemm_tp(self, a, w, b_mn, out, M, N, K, ag=None, rs=None, bias=None):
-        """ag = (src_ptrs, gather, flags_epoch) or None; rs = staging ptr array or None."""
+    def gemm_tp(self, a, w, b_mn, out, M, N, K, ag=None, rs=None, bias=None, batch=1, fp8=None):
+        """ag = (src_ptrs, gather, flags_epoch) or None; rs = staging ptr array or None; fp8 = (alpha, alpha2, a_fmt,
+        b_fmt) for one-byte operands (a / w / gather are uint8 tensors then) or None for bf16."""
         st = torch.cuda.current_stream().cuda_stream
         ag_world, ag_src, gather, epoch = (self.world, ag[0], ag[1].data_ptr(), ag[2]) if ag else (0, None, None, 0)
+        al, al2, afmt, bfmt = (fp8[0].data_ptr(), fp8[1].data_ptr(), fp8[2], fp8[3]) if fp8 else (None, None, 0, 0)
         rc = self.lib.sb_gemm_tp(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), int(b_mn),
                                  None if out is None else out.data_ptr(), 0 if out is None else out.stride(0),
-                                 None if bias is None else bias.data_ptr(), M, N, K, ag_world, self.rank, ag_src, gather,
+                                 None if bias is None else bias.data_ptr(), M, N, K, batch, 1 if fp8 else 2, al, al2, afmt, bfmt,
+                                 ag_world, self.rank, ag_src, gather,
                                  self.flags.data_ptr(), epoch, 16, self.world if rs is not None else 0, self.rank, rs,
                                  self.cuda_ops.status_word(self.dev).data_ptr(), st)
         if rc != 0:
-            raise RuntimeError(f"sb_gemm_tp failed ({rc}) M={M} N={N} K={K}")
+            raise RuntimeError(f"sb_gemm_tp failed ({rc}) M={M} N={N} K={K} batch={batch} fp8={fp8 is not None}")
         self.cuda_ops._count()
 
     def rs_reduce(self, staging, out, rows, N, bias=None, residual=None):
@@ -115,12 +127,33 @@ class TPWorkspace:
             raise RuntimeError(f"sb_rs_reduce failed ({rc})")
         self.cuda_ops._count()
 
-    def gather_rows(self, src_ptrs, gather, M, K, ld):
+    def gather_rows(self, src_ptrs, gather, M, K, ld, batch=1, elem_bytes=2):
         st = torch.cuda.current_stream().cuda_stream
-        rc = self.lib.sb_gather_rows(src_ptrs, self.world, gather.data_ptr(), M, K, ld, st)
+        rc = self.lib.sb_gather_rows(src_ptrs, self.world, gather.data_ptr(), M, K, ld, batch, elem_bytes, st)
         if rc != 0:
             raise RuntimeError(f"sb_gather_rows failed ({rc})")
         self.cuda_ops._count()
+
+    # ---- fp8 operands sharded over the group: one scale for all ranks ------------------------------------
+    def quantize_shared(self, x2: torch.Tensor, fmt: int, name: str):
+        """Quantise this rank's shard x2 [rows, K] (bf16) into the next slot of the symmetric byte buffer `name` with
+        the scale of the whole gathered operand: local amax, maximum over the group (one small NCCL all-reduce on the
+        compute stream), quantise.  Returns (staged uint8 view, peers' pointers, de-quantisation factor)."""
+        lib, st = self.lib, torch.cuda.current_stream().cuda_stream
+        amax = torch.empty(1, dtype=torch.float32, device=self.dev)
+        if lib.sb_amax_bf16(x2.data_ptr(), amax.data_ptr(), x2.numel(), st) != 0:
+            raise RuntimeError("sb_amax_bf16 failed")
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
+        stage, ptrs = self.symm_buffer(name, (x2.numel() + 1) // 2)          # bytes = numel: half as many bf16 slots
+        q = stage.view(torch.uint8)[: x2.numel()].view(x2.shape)
+        sinv = torch.empty(1, dtype=torch.float32, device=self.dev)
+        if lib.sb_quantize_fp8_with_amax(x2.data_ptr(), q.data_ptr(), amax.data_ptr(), sinv.data_ptr(), x2.numel(), fmt, st) != 0:
+            raise RuntimeError("sb_quantize_fp8_with_amax failed")
+        self.cuda_ops._count(2)
+        return q, ptrs, sinv
+
+    def local_bytes(self, name: str, nbytes: int) -> torch.Tensor:
+        return self.local_buffer(name, (nbytes + 1) // 2).view(torch.uint8)[:nbytes]
 
 
 def setup(group=None, ranks=None) -> bool:
@@ -146,11 +179,13 @@ def teardown() -> None:
 
 
 def fp8_active():
-    """None: the fused projections are off.  False: they are on and run bf16 GEMMs even where the layer asks for fp8
-    (reported by bench.py next to the dtype).  True: they run fp8 operands."""
+    """None: the fused projections are off, or no layer has asked them for fp8.  True: fp8 requests ran on fp8 operands.
+    False: a layer asked for fp8 and got bf16 (shape not a multiple of 16; bench.py reports it next to the dtype)."""
     if _WS is None:
         return None
-    return False
+    if not _SEEN_FP8_REQUEST:
+        return None
+    return FP8_CALLS > 0
 
 
 def _eligible(x, w, rows_per_rank: int) -> bool:
@@ -171,102 +206,105 @@ def _accumulate_wgrad(ctx_w, g2, x2, a_mn=True):
 
 
 class _LinearAllGather(torch.autograd.Function):
-    """x [1, l, K] sequence shard -> y [1, l*tp, N]."""
+    """x [B, l, K] sequence shard -> y [B, l*tp, N] (bf16 operands)."""
 
     @staticmethod
     def forward(ctx, x, w, bias):
         ws = _WS
-        l, K = x.shape[1], x.shape[2]
-        N, M = w.shape[0], l * ws.world
-        x2 = x.reshape(l, K)
-        xs, ptrs = ws.symm_buffer("ag_x", l * K)
-        xs.view(l, K).copy_(x2)
+        Bn, l, K = x.shape
+        N, M = w.shape[0], Bn * l * ws.world
+        x2 = x.reshape(Bn * l, K)
+        xs, ptrs = ws.symm_buffer("ag_x", Bn * l * K)
+        xs.view(Bn * l, K).copy_(x2)
         ws.barrier()
         gather = ws.local_buffer("gather", M * K)
         out = torch.empty((M, N), dtype=bf16, device=x.device)
-        ws.gemm_tp(xs.view(l, K), w, False, out, M, N, K, ag=(ptrs, gather, ws.next_epoch()), bias=bias)
+        ws.gemm_tp(xs.view(Bn * l, K), w, False, out, M, N, K, ag=(ptrs, gather, ws.next_epoch()), bias=bias, batch=Bn)
         ctx.save_for_backward(x2.contiguous() if not x2.is_contiguous() else x2, w)
-        ctx.wref, ctx.has_bias = w, bias is not None
-        return out.view(1, M, N)
+        ctx.wref, ctx.has_bias, ctx.Bn = w, bias is not None, Bn
+        return out.view(Bn, l * ws.world, N)
 
     @staticmethod
     def backward(ctx, gy):
         ws = _WS
         x2, w = ctx.saved_tensors
-        l, K = x2.shape
-        N, M = w.shape[0], l * ws.world
+        Bn = ctx.Bn
+        rows, K = x2.shape                       # rows = Bn * l
+        N, M = w.shape[0], rows * ws.world
         g2 = gy.reshape(M, N)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
         gx = gw = gb = None
         # stage the operand of the weight gradient for the peers, then one barrier serves both products
-        xs, ptrs = ws.symm_buffer("ag_x", l * K)
-        xs.view(l, K).copy_(x2)
-        stage, sptrs = ws.symm_buffer("rs_stage", ws.world * l * K)
+        xs, ptrs = ws.symm_buffer("ag_x", rows * K)
+        xs.view(rows, K).copy_(x2)
+        stage, sptrs = ws.symm_buffer("rs_stage", ws.world * rows * K)
         ws.barrier()
         if ctx.needs_input_grad[0]:
             # dX = reduce_scatter(dY W): epilogue stores into the owners' staging buffers
-            ws.gemm_tp(g2, w, True, None, M, K, N, rs=sptrs)
+            ws.gemm_tp(g2, w, True, None, M, K, N, rs=sptrs, batch=Bn)
         if ctx.needs_input_grad[1]:
             gather = ws.local_buffer("gather", M * K)
-            ws.gather_rows(ptrs, gather, M, K, K)
+            ws.gather_rows(ptrs, gather, M, K, K, batch=Bn)
             gw = _accumulate_wgrad(ctx.wref, g2, gather.view(M, K))
         if ctx.has_bias and ctx.needs_input_grad[2]:
             from ..ops.cuda_ops import colsum
             gb = colsum(g2).to(gy.dtype)
         if ctx.needs_input_grad[0]:
             ws.barrier()
-            gx = torch.empty((l, K), dtype=bf16, device=gy.device)
-            ws.rs_reduce(stage, gx, l, K)
-            gx = gx.view(1, l, K)
+            gx = torch.empty((rows, K), dtype=bf16, device=gy.device)
+            ws.rs_reduce(stage, gx, rows, K)
+            gx = gx.view(Bn, rows // Bn, K)
         return gx, gw, gb
 
 
 class _LinearReduceScatter(torch.autograd.Function):
-    """x [1, L, K_local] -> y [1, L/tp, N] = reduce_scatter(x w^T) (+ bias + residual on the owner)."""
+    """x [B, L, K_local] -> y [B, L/tp, N] = reduce_scatter(x w^T) (+ bias + residual on the owner), bf16 operands."""
 
     @staticmethod
     def forward(ctx, x, w, bias, residual):
         ws = _WS
-        M, K = x.shape[1], x.shape[2]
-        N, l = w.shape[0], x.shape[1] // ws.world
+        Bn, L, K = x.shape
+        M = Bn * L
+        N, rows = w.shape[0], M // ws.world          # rows = Bn * l owned by this rank
         x2 = x.reshape(M, K)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        stage, sptrs = ws.symm_buffer("rs_stage", ws.world * l * N)
+        stage, sptrs = ws.symm_buffer("rs_stage", ws.world * rows * N)
         ws.barrier()
-        ws.gemm_tp(x2, w, False, None, M, N, K, rs=sptrs)
+        ws.gemm_tp(x2, w, False, None, M, N, K, rs=sptrs, batch=Bn)
         ws.barrier()
-        y = torch.empty((l, N), dtype=bf16, device=x.device)
-        r2 = residual.reshape(l, N).contiguous() if residual is not None else None
-        ws.rs_reduce(stage, y, l, N, bias=bias, residual=r2)
+        y = torch.empty((rows, N), dtype=bf16, device=x.device)
+        r2 = residual.reshape(rows, N).contiguous() if residual is not None else None
+        ws.rs_reduce(stage, y, rows, N, bias=bias, residual=r2)
         ctx.save_for_backward(x2, w)
-        ctx.wref, ctx.has_bias, ctx.has_res = w, bias is not None, residual is not None
-        return y.view(1, l, N)
+        ctx.wref, ctx.has_bias, ctx.has_res, ctx.Bn = w, bias is not None, residual is not None, Bn
+        return y.view(Bn, rows // Bn, N)
 
     @staticmethod
     def backward(ctx, gy):
         ws = _WS
         x2, w = ctx.saved_tensors
+        Bn = ctx.Bn
         M, K = x2.shape
-        N, l = w.shape[0], M // ws.world
-        g2 = gy.reshape(l, N)
-        gs, ptrs = ws.symm_buffer("ag_x", l * N)
-        gs.view(l, N).copy_(g2)
+        N, rows = w.shape[0], M // ws.world
+        g2 = gy.reshape(rows, N)
+        gs, ptrs = ws.symm_buffer("ag_x", rows * N)
+        gs.view(rows, N).copy_(g2)
         ws.barrier()
         gather = ws.local_buffer("gather", M * N)
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             # dX = allgather(dY) W : fused pull + GEMM, W [N, K] read as the [K_red = N, N_out = K] operand
             gx = torch.empty((M, K), dtype=bf16, device=gy.device)
-            ws.gemm_tp(gs.view(l, N), w, True, gx, M, K, N, ag=(ptrs, gather, ws.next_epoch()))
-            gx = gx.view(1, M, K)
+            ws.gemm_tp(gs.view(rows, N), w, True, gx, M, K, N, ag=(ptrs, gather, ws.next_epoch()), batch=Bn)
+            gx = gx.view(Bn, M // Bn, K)
         if ctx.needs_input_grad[1]:
             if ctx.needs_input_grad[0]:
-                # the fused kernel filled every remote tile of the gather buffer; add the local shard
-                gather.view(M, N)[ws.rank * l:(ws.rank + 1) * l].copy_(g2)
+                # the fused kernel filled every remote tile of the gather buffer; add the local blocks
+                gather.view(Bn, ws.world, rows // Bn, N)[:, ws.rank].copy_(g2.view(Bn, rows // Bn, N))
             else:
-                ws.gather_rows(ptrs, gather, M, N, N)
+                ws.gather_rows(ptrs, gather, M, N, N, batch=Bn)
             gw = _accumulate_wgrad(ctx.wref, gather.view(M, N), x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             from ..ops.cuda_ops import colsum
@@ -275,21 +313,159 @@ class _LinearReduceScatter(torch.autograd.Function):
         return gx, gw, gb, gr
 
 
-def linear_allgather(x, w, bias, seq_dim):
+# ------------------------------------------------------------------------------------------ fp8 operands
+def _wgrad_fp8(wref, gq, sg, xq, sx):
+    """dW = (gq^T xq) * sg * sx, into the flat gradient buffer when the parameter has one; gq [T, N] e5m2, xq [T, K] e4m3."""
+    from ..ops.cuda_ops import gemm_fp8
+    tgt = wref.grad if getattr(wref, "_fuse_grad_accum", False) else None
+    if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == wref.shape:
+        gemm_fp8(gq, xq, tgt, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
+        return None
+    gw = torch.empty(wref.shape, dtype=bf16, device=gq.device)
+    gemm_fp8(gq, xq, gw, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
+    return gw
+
+
+class _LinearAllGatherFP8(torch.autograd.Function):
+    """Column projection of a sequence-sharded activation with fp8 tensor-core operands: the shard is quantised to e4m3
+    with the scale of the whole gathered activation (group-wide amax) straight into the symmetric staging buffer, so
+    half the bytes of the bf16 path cross NVLink; weights are the cached e4m3 copy; gradients are e5m2."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        global FP8_CALLS
+        from ..ops.cuda_ops import _fp8_weight
+        ws = _WS
+        Bn, l, K = x.shape
+        N, M = w.shape[0], Bn * l * ws.world
+        x2 = x.reshape(Bn * l, K)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        xq, ptrs, sx = ws.quantize_shared(x2, E4M3, "ag_q")
+        wq, sw = _fp8_weight(w)
+        ws.barrier()
+        gather = ws.local_bytes("gather", M * K)
+        out = torch.empty((M, N), dtype=bf16, device=x.device)
+        ws.gemm_tp(xq, wq, False, out, M, N, K, ag=(ptrs, gather, ws.next_epoch()), bias=bias, batch=Bn,
+                   fp8=(sx, sw, E4M3, E4M3))
+        FP8_CALLS += 1
+        ctx.save_for_backward(xq.clone(), sx, wq, sw)
+        ctx.wref, ctx.has_bias, ctx.Bn = w, bias is not None, Bn
+        return out.view(Bn, l * ws.world, N)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..ops.cuda_ops import colsum, quantize_fp8_site
+        ws = _WS
+        xq, sx, wq, sw = ctx.saved_tensors
+        Bn = ctx.Bn
+        rows, K = xq.shape
+        N, M = wq.shape[0], rows * ws.world
+        g2 = gy.reshape(M, N)
+        g2 = g2 if g2.is_contiguous() else g2.contiguous()
+        gq, sg = quantize_fp8_site(g2, E5M2, ctx.wref, "g")            # dY is whole on every rank: local scale
+        gx = gw = gb = None
+        # stage the quantised shard again for the weight gradient's gather; one barrier serves both products
+        stage, ptrs = ws.symm_buffer("ag_q", (rows * K + 1) // 2)
+        stage.view(torch.uint8)[: rows * K].view(rows, K).copy_(xq)
+        rstage, sptrs = ws.symm_buffer("rs_stage", ws.world * rows * K)
+        ws.barrier()
+        if ctx.needs_input_grad[0]:
+            ws.gemm_tp(gq, wq, True, None, M, K, N, rs=sptrs, batch=Bn, fp8=(sg, sw, E5M2, E4M3))
+        if ctx.needs_input_grad[1]:
+            gather = ws.local_bytes("gather", M * K)
+            ws.gather_rows(ptrs, gather, M, K, K, batch=Bn, elem_bytes=1)
+            gw = _wgrad_fp8(ctx.wref, gq, sg, gather.view(M, K), sx)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g2).to(gy.dtype)
+        if ctx.needs_input_grad[0]:
+            ws.barrier()
+            gx = torch.empty((rows, K), dtype=bf16, device=gy.device)
+            ws.rs_reduce(rstage, gx, rows, K)
+            gx = gx.view(Bn, rows // Bn, K)
+        return gx, gw, gb
+
+
+class _LinearReduceScatterFP8(torch.autograd.Function):
+    """Row projection with fp8 operands followed by the reduce-scatter along the sequence (partial sums travel as bf16).
+    Backward: the sharded output gradient is quantised to e5m2 with the group-wide scale and gathered inside the GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        global FP8_CALLS
+        from ..ops.cuda_ops import _fp8_weight, quantize_fp8_site
+        ws = _WS
+        Bn, L, K = x.shape
+        M = Bn * L
+        N, rows = w.shape[0], M // ws.world
+        x2 = x.reshape(M, K)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        xq, sx = quantize_fp8_site(x2, E4M3, w, "x")                   # x is whole on this rank: local (delayed) scale
+        wq, sw = _fp8_weight(w)
+        stage, sptrs = ws.symm_buffer("rs_stage", ws.world * rows * N)
+        ws.barrier()
+        ws.gemm_tp(xq, wq, False, None, M, N, K, rs=sptrs, batch=Bn, fp8=(sx, sw, E4M3, E4M3))
+        ws.barrier()
+        y = torch.empty((rows, N), dtype=bf16, device=x.device)
+        r2 = residual.reshape(rows, N).contiguous() if residual is not None else None
+        ws.rs_reduce(stage, y, rows, N, bias=bias, residual=r2)
+        FP8_CALLS += 1
+        ctx.save_for_backward(xq, sx, wq, sw)
+        ctx.wref, ctx.has_bias, ctx.has_res, ctx.Bn = w, bias is not None, residual is not None, Bn
+        return y.view(Bn, rows // Bn, N)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..ops.cuda_ops import colsum
+        ws = _WS
+        xq, sx, wq, sw = ctx.saved_tensors
+        Bn = ctx.Bn
+        M, K = xq.shape
+        N, rows = wq.shape[0], M // ws.world
+        g2 = gy.reshape(rows, N)
+        g2 = g2 if g2.is_contiguous() else g2.contiguous()
+        gq, ptrs, sg = ws.quantize_shared(g2, E5M2, "ag_q")
+        ws.barrier()
+        gather = ws.local_bytes("gather", M * N)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.empty((M, K), dtype=bf16, device=gy.device)
+            ws.gemm_tp(gq, wq, True, gx, M, K, N, ag=(ptrs, gather, ws.next_epoch()), batch=Bn, fp8=(sg, sw, E5M2, E4M3))
+            gx = gx.view(Bn, M // Bn, K)
+        if ctx.needs_input_grad[1]:
+            if ctx.needs_input_grad[0]:
+                gather.view(Bn, ws.world, rows // Bn, N)[:, ws.rank].copy_(gq.view(Bn, rows // Bn, N))
+            else:
+                ws.gather_rows(ptrs, gather, M, N, N, batch=Bn, elem_bytes=1)
+            gw = _wgrad_fp8(ctx.wref, gather.view(M, N), sg, xq, sx)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g2).to(gy.dtype)
+        gr = gy if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        return gx, gw, gb, gr
+
+
+def _fp8_ok(x, w) -> bool:
+    return w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0
+
+
+def linear_allgather(x, w, bias, seq_dim, fp8: bool = False):
+    global _SEEN_FP8_REQUEST
     if _WS is None or seq_dim != 1 or x.dim() != 3 or not _eligible(x, w, x.shape[1]):
         return None
-    if x.shape[0] == 1:
-        return _LinearAllGather.apply(x, w, bias)
-    # the kernels take one sequence at a time (a rank's shard must be one block of rows): loop over the micro-batch
-    return torch.cat([_LinearAllGather.apply(x[b:b + 1], w, bias) for b in range(x.shape[0])], dim=0)
+    if fp8:
+        _SEEN_FP8_REQUEST = True
+        if _fp8_ok(x, w):
+            return _LinearAllGatherFP8.apply(x, w, bias)
+    return _LinearAllGather.apply(x, w, bias)
 
 
-def linear_reducescatter(x, w, seq_dim, bias=None, residual=None):
+def linear_reducescatter(x, w, seq_dim, bias=None, residual=None, fp8: bool = False):
+    global _SEEN_FP8_REQUEST
     if _WS is None or seq_dim != 1 or x.dim() != 3:
         return None
     if x.shape[1] % _WS.world or not _eligible(x, w, x.shape[1] // _WS.world):
         return None
-    if x.shape[0] == 1:
-        return _LinearReduceScatter.apply(x, w, bias, residual)
-    return torch.cat([_LinearReduceScatter.apply(x[b:b + 1], w, bias, None if residual is None else residual[b:b + 1])
-                      for b in range(x.shape[0])], dim=0)
+    if fp8:
+        _SEEN_FP8_REQUEST = True
+        if _fp8_ok(x, w):
+            return _LinearReduceScatterFP8.apply(x, w, bias, residual)
+    return _LinearReduceScatter.apply(x, w, bias, residual)

@@ -90,6 +90,7 @@ class FusedZeroStep:
         # ---- overlap of the reduce-scatter with the last micro-batch's backward
         self.overlap = False                 # armed by begin_overlap(), consumed by step()
         self.overlap_launches = 0            # reduce-scatter kernels launched from the backward (tests / bench read it)
+        self.overlap_rounds = 0              # barriers issued from the backward (same on every rank)
         self._watermark = {}                 # id(group) -> start of the range already handed to the side stream
         self._block_start = None             # per group: flat offset of the first parameter of every block
         self._side = None
@@ -173,6 +174,7 @@ class FusedZeroStep:
         if not todo:
             return
         side = self._side
+        self.overlap_rounds += 1
         side.wait_stream(torch.cuda.current_stream())
         # all ranks have finished these blocks' backward (every rank issues the same barriers in the same order)
         self._bar_epoch += 1

@@ -102,7 +102,8 @@ class Trainer:
                 and state.get_model_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
             from ..parallel import fused_tp
             on = fused_tp.setup()
-            print_rank_0(" > tensor-parallel projections: " + ("fused all-gather->GEMM / GEMM->reduce-scatter kernels"
+            print_rank_0(" > tensor-parallel projections: " + (("fused all-gather->GEMM / GEMM->reduce-scatter kernels"
+                                                                + (", fp8 operands" if cfg.use_fp8_linears else ""))
                                                                if on else "NCCL collectives + GEMM"))
         if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.use_cp_hyena
                 and state.get_context_parallel_world_size() > 1 and cfg.precision == "bfloat16"):
@@ -270,20 +271,23 @@ class Trainer:
         self.optimizer.zero_grad()
         total = None
         for micro in range(self.gas):
-            with self._mark("TRAIN_STEP_FORWARD"):
-                b = batch_mod.get_batch(cfg, data_iterator, self.device)
-                loss = self.forward_step(b)
-            with self._mark("TRAIN_STEP_BACKWARD"):
-                overlap = self._zero_overlap if micro == self.gas - 1 else None
-                if overlap is not None and overlap.begin_overlap(self.optimizer):
-                    opt = self.optimizer
-                    self.model.grad_boundary_callback = lambda i: overlap.grads_final_from(opt, i)
-                try:
+            # the last micro-batch's forward plants the hooks through which its backward reports finished blocks
+            overlap = self._zero_overlap if micro == self.gas - 1 else None
+            if overlap is not None:
+                opt = self.optimizer
+                self.model.grad_boundary_callback = lambda i: overlap.grads_final_from(opt, i)
+            try:
+                with self._mark("TRAIN_STEP_FORWARD"):
+                    b = batch_mod.get_batch(cfg, data_iterator, self.device)
+                    loss = self.forward_step(b)
+                with self._mark("TRAIN_STEP_BACKWARD"):
+                    if overlap is not None:
+                        overlap.begin_overlap(self.optimizer)
                     (loss / self.gas).backward()
-                finally:
-                    self.model.grad_boundary_callback = None
-                if self.partitioned:
-                    self.optimizer.finish_backward()
+                    if self.partitioned:
+                        self.optimizer.finish_backward()
+            finally:
+                self.model.grad_boundary_callback = None
             total = loss.detach() if total is None else total + loss.detach()
         if not self.partitioned:
             self._sync_replicated_grads()

@@ -1,9 +1,10 @@
 """CUDA kernels against the fp32 PyTorch statement of the same operator (ops/reference.py).
 
-Tolerances follow the reference's kernel tests (bf16: 1e-3 relative on saved intermediates is too tight
-for outputs that are themselves rounded to bf16, so outputs are compared with the bf16 rounding error
-of the oracle result: atol/rtol 2e-2 on O(1) values; fp32 quantities (filter gradients, losses) use 1e-3
-relative to their scale)."""
+Tolerances: bf16 tensors are compared element by element, |got - want| <= atol * rms(want) + rtol * |want|, with
+atol = rtol = 2e-2 by default: a few bf16 ulps (2^-8 relative) on the element itself plus a floor of 2 % of the tensor's
+typical magnitude for elements that are small because their terms cancel.  (The reference's kernel tests use 1e-3 on
+bf16 intermediates that are compared before the final rounding; outputs that are themselves rounded to bf16 cannot meet
+that.)  fp32 quantities (filter gradients, norms) are compared in relative L2 norm."""
 import math
 
 import pytest
@@ -19,9 +20,12 @@ BF = torch.bfloat16
 
 def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
     a, b = a.float(), b.float()
-    scale = b.abs().max().clamp(min=1e-6)
-    err = (a - b).abs().max()
-    assert err <= atol * scale + rtol * scale, f"{what}: max err {err.item():.4g} vs scale {scale.item():.4g}"
+    rms = b.pow(2).mean().sqrt().clamp(min=1e-12)
+    err = (a - b).abs()
+    bound = atol * rms + rtol * b.abs()
+    bad = err > bound
+    assert not bool(bad.any()), (f"{what}: {int(bad.sum())} of {bad.numel()} elements outside atol*rms + rtol*|ref| "
+                                 f"(worst excess {(err - bound).max().item():.4g}, rms {rms.item():.4g})")
 
 
 def _rel(a, b, tol, what=""):
@@ -310,12 +314,14 @@ def test_hyena_mr(K, G, L, halo, mr_bwd_variant):
     hh = h.detach().float().requires_grad_() if halo else None
     zr = ref.hyena_mr_inner(fr, hr_, br, hh)
     zr.backward(g.float())
-    _close(z, zr, what="mr fwd")
-    _close(feat.grad, fr.grad, what="mr dfeat")
+    # the Toeplitz products run on bf16 tensor-core operands (u = x2 v, the taps, and in the backward y and du are
+    # rounded to bf16 before the MMAs), one rounding more than the element-wise kernels: 3 % instead of 2 %
+    _close(z, zr, rtol=3e-2, atol=3e-2, what="mr fwd")
+    _close(feat.grad, fr.grad, rtol=3e-2, atol=3e-2, what="mr dfeat")
     _rel(hflt.grad, hr_.grad, 2e-2, "mr dh")
     _rel(bias.grad, br.grad, 2e-2, "mr dbias")
     if halo:
-        _close(h.grad, hh.grad, what="mr dhalo")
+        _close(h.grad, hh.grad, rtol=3e-2, atol=3e-2, what="mr dhalo")
 
 
 @pytest.fixture(params=[None, 512], ids=["chunk_auto", "chunk_512"])

@@ -1,0 +1,164 @@
+"""One case per convolution / scan / norm / gate / loss kernel at the shapes the 7B benchmark runs (B = 1, L = 8192,
+D = 4096, 256 filter groups, k in {3, 7, 128}, SwiGLU inner 11264), forward and backward, against the fp32 PyTorch
+statement of the operator (ops/reference.py) evaluated on the GPU.  The small-shape tests (tests/test_gpu_kernels.py)
+cover odd sizes and the fallback kernels; these cover the tile counts, grid sizes and chunk lengths that the real
+model selects.  Shapes follow the reference's kernel tests (cgcg/tests/test_fwd_refactor.py: L in {1024, 8192},
+D 4096, g 256, filter lengths 4 / 32 / 128)."""
+import math
+
+import pytest
+import torch
+
+from savanna_b200 import ops
+from savanna_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+B, L, D, G = 1, 8192, 4096, 256
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    rms = b.pow(2).mean().sqrt().clamp(min=1e-12)
+    err = (a - b).abs()
+    bound = atol * rms + rtol * b.abs()
+    bad = err > bound
+    assert not bool(bad.any()), (f"{what}: {int(bad.sum())} of {bad.numel()} elements outside atol*rms + rtol*|ref| "
+                                 f"(worst excess {(err - bound).max().item():.4g}, rms {rms.item():.4g})")
+
+
+def _rel(a, b, tol, what=""):
+    r = (a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12)
+    assert r <= tol, f"{what}: relative L2 error {r.item():.4g} > {tol}"
+
+
+def _done():
+    from savanna_b200.ops import cuda_ops
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+
+
+def test_featuriser_conv_k3():
+    torch.manual_seed(0)
+    C = 3 * D
+    x = torch.randn(B, L, C, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(C, 3, device=DEV) * 0.5).requires_grad_()
+    y = ops.causal_conv1d(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = ref.causal_conv1d(xr, wr)
+    yr.backward(g.float())
+    _done()
+    _close(y, yr, what="conv k3 fwd")
+    _close(x.grad, xr.grad, what="conv k3 dx")
+    _rel(w.grad, wr.grad, 1e-2, "conv k3 dw")
+
+
+def test_hyena_se_k7():
+    torch.manual_seed(1)
+    feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
+    w = (torch.randn(G, 7, device=DEV) * 0.4).requires_grad_()
+    z = ops.hyena_se_inner(feat, w)
+    g = torch.randn_like(z)
+    z.backward(g)
+    fr, wr = feat.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    zr = ref.hyena_se_inner(fr, wr)
+    zr.backward(g.float())
+    _done()
+    _close(z, zr, what="se k7 fwd")
+    _close(feat.grad, fr.grad, what="se k7 dfeat")
+    _rel(w.grad, wr.grad, 1e-2, "se k7 dw")
+
+
+@pytest.mark.parametrize("K", [32, 128])
+def test_hyena_mr(K):
+    torch.manual_seed(2)
+    feat = torch.randn(B, L, 3 * D, device=DEV, dtype=BF, requires_grad=True)
+    decay = torch.exp(-torch.logspace(-2, 2, G, device=DEV)[:, None] * torch.linspace(0, 1, K, device=DEV)[None])
+    h = (torch.randn(G, K, device=DEV) / math.sqrt(K) * decay).requires_grad_()
+    bias = torch.randn(D, device=DEV).requires_grad_()
+    z = ops.hyena_mr_inner(feat, h, bias)
+    g = torch.randn_like(z)
+    z.backward(g)
+    fr, hr, br = feat.detach().float().requires_grad_(), h.detach().clone().requires_grad_(), bias.detach().clone().requires_grad_()
+    zr = ref.hyena_mr_inner(fr, hr, br)
+    zr.backward(g.float())
+    _done()
+    # bf16 tensor-core operands (u, taps; y and du staged in bf16 in the backward): one rounding more than element-wise kernels
+    _close(z, zr, rtol=3e-2, atol=3e-2, what="mr fwd")
+    _close(feat.grad, fr.grad, rtol=4e-2, atol=4e-2, what="mr dfeat")
+    _rel(h.grad, hr.grad, 2e-2, "mr dh")
+    _rel(bias.grad, br.grad, 2e-2, "mr dbias")
+
+
+def test_hyena_li_order16():
+    torch.manual_seed(3)
+    O = 16
+    feat = (torch.randn(B, L, 3 * D, device=DEV) * 0.7).to(BF).requires_grad_()
+    gamma = (torch.rand(D, O, device=DEV) * 0.09 + 0.01).log().requires_grad_()
+    R = (0.1 * torch.randn(D, O, device=DEV) / math.sqrt(O)).requires_grad_()
+    p = (-torch.ones(D, O, device=DEV)).requires_grad_()
+    bias = torch.randn(D, device=DEV).requires_grad_()
+    z = ops.hyena_li_modal(feat, gamma, R, p, bias)
+    g = torch.randn_like(z)
+    z.backward(g)
+    leaves = [t.detach().float().requires_grad_() for t in (feat, gamma, R, p, bias)]
+    zr = ref.hyena_li_modal(*leaves)
+    zr.backward(g.float())
+    _done()
+    _close(z, zr, what="li fwd")
+    _close(feat.grad, leaves[0].grad, rtol=3e-2, atol=3e-2, what="li dfeat")
+    _rel(R.grad, leaves[2].grad, 3e-2, "li dR")
+    _rel(gamma.grad, leaves[1].grad, 3e-2, "li dgamma")
+    _rel(bias.grad, leaves[4].grad, 3e-2, "li dbias")
+
+
+@pytest.mark.parametrize("form", ["te", "classic"])
+def test_rmsnorm(form):
+    torch.manual_seed(4)
+    x = torch.randn(B, L, D, device=DEV, dtype=BF, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(BF).requires_grad_()
+    y = ops.rmsnorm(x, w, 1e-6, form)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6, form)
+    yr.backward(g.float())
+    _done()
+    _close(y, yr, what="rmsnorm fwd")
+    _close(x.grad, xr.grad, what="rmsnorm dx")
+    _rel(w.grad, wr.grad, 2e-2, "rmsnorm dw")
+
+
+def test_swiglu_gate_ffn_11264():
+    torch.manual_seed(5)
+    F_ = 11264
+    ab = torch.randn(B, L, 2 * F_, device=DEV, dtype=BF, requires_grad=True)
+    h = ops.glu_act_packed(ab, "silu")
+    g = torch.randn_like(h)
+    h.backward(g)
+    abr = ab.detach().float().requires_grad_()
+    a, b = abr.chunk(2, -1)
+    hr = ref.glu_act(a, b, "silu")
+    hr.backward(g.float())
+    _done()
+    _close(h, hr, what="glu fwd")
+    _close(ab.grad, abr.grad, what="glu bwd")
+
+
+def test_cross_entropy_vocab_512():
+    torch.manual_seed(6)
+    V = 512
+    logits = (torch.randn(B, L, V, device=DEV) * 2).to(BF).requires_grad_()
+    labels = torch.randint(0, V, (B, L), device=DEV)
+    loss = ops.cross_entropy(logits, labels)
+    w = torch.rand_like(loss)
+    (loss * w).sum().backward()
+    lr = logits.detach().float().requires_grad_()
+    lossr = ref.cross_entropy(lr, labels)
+    (lossr * w).sum().backward()
+    _done()
+    _rel(loss, lossr, 2e-3, "ce loss")
+    _close(logits.grad, lr.grad, what="ce dlogits")
