@@ -275,14 +275,22 @@ def main():
                        if fused is not None else ("nccl" if world > 1 else "single rank"))
         cfg = trainer.cfg
         if pstate.get_context_parallel_world_size() > 1:
+            from savanna_b200.parallel import halo_fused, li_fused
             peer = halo._PEER_WS is not None
-            out["halo"] = "peer-memory" if peer else "nccl send/recv"
-            out["hyena_li"] = ("all-to-all " + ("(peer-memory)" if peer else "(nccl)")) if cfg.cp_hyena_li_algo == "a2a" \
-                else "modal-state hand-off"
+            out["halo"] = ("halo rows read from peer memory inside the convolution kernels" if halo_fused.CALLS > 0 else
+                           ("peer-memory pull kernel" if peer else "nccl send/recv"))
+            if cfg.cp_hyena_li_algo == "a2a":
+                out["hyena_li"] = ("all-to-all inside the scan kernels (peer loads / stores)" if li_fused.CALLS > 0 else
+                                   ("all-to-all by peer-memory copy kernels" if peer else "all-to-all (nccl)"))
+            else:
+                out["hyena_li"] = "modal-state hand-off"
             out["attention"] = "ring " + ("(peer-memory K/V, tcgen05 kernels)" if peer else "(nccl)")
         if pstate.get_model_parallel_world_size() > 1:
-            out["tensor_parallel"] = ("fused all-gather->GEMM / GEMM->reduce-scatter kernels" if fused_tp._WS is not None
+            out["tensor_parallel"] = (("fused all-gather->GEMM / GEMM->reduce-scatter kernels"
+                                       + (" (fp8 operands)" if fused_tp.fp8_active() else "")) if fused_tp._WS is not None
                                       else "nccl collectives + GEMM")
+        if getattr(trainer, "_zero_overlap", None) is not None:
+            out["zero"] += ", reduce-scatter overlapped with backward"
         return out
 
     def measure(config_path, extra_over, steps, warmup, with_e2e, same_data_on_all_ranks=False, keep_losses=False):

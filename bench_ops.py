@@ -1,8 +1,19 @@
-"""Operator benchmark (BASELINE config 2 and the per-kernel roofline table): times this framework's CUDA
-kernels and, beside each, the PyTorch/library statement of the same operator, on the Evo-2-7B shapes
-(hidden 4096, 256 groups of 16 channels, filter lengths 3 / 7 / 128, modal order 16).
+"""Operator benchmark and per-kernel roofline table: times this framework's CUDA kernels and, beside each, the
+PyTorch/library statement of the same operator, on the Evo-2-7B shapes (hidden 4096, 256 groups of 16 channels, filter
+lengths 3 / 7 / 128, modal order 16).
 
     python bench_ops.py [--seq 8192] [--ops gemm,dwconv,se,mr,li,norm,glu,ce,adam] [--iters 10]
+
+Context-parallel operator sweep (one Hyena-MR block and one Hyena-LI block, batch 1, hidden 4096, forward and
+backward, the sequence split over the GPUs of the job; N(0,1) activations, seeded filters):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench_ops.py --cp-sweep \
+        [--seqs 8192,32768,131072,1048576]
+
+  MR block = featuriser conv (k = 3) + gated FIR (k = 128), halo rows read from the neighbour ranks inside the kernels;
+  LI block = featuriser conv + modal scan (order 16) with the all-to-all inside the scan kernels.
+Every row is device-timed (CUDA events, max over ranks) and carries the achieved fraction of its roofline, the slower of
+the algorithmic HBM bytes over the measured copy bandwidth and the bytes that must cross NVLink over 770 GB/s.
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB buffer write)
 between timed launches.  Rooflines use MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 throughput) when
@@ -272,14 +283,112 @@ def bench_attention(L, iters, heads=32, small=False):
     cuda_ops.check_status()
 
 
+NVLINK_BW = 770e9          # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900e9)
+
+
+def cp_sweep(seqs, iters):
+    """One Hyena-MR block and one Hyena-LI block under context parallelism over all ranks of the job."""
+    import torch.distributed as dist
+    from savanna_b200.parallel import halo, halo_fused, li_fused, state
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        state.initialize_model_parallel(1, world, 1)
+        if not halo.setup_peer():
+            raise RuntimeError("context-parallel peer workspace did not come up")
+    D, G, O = 4096, 256, 16
+    bw, _, src = peaks()
+    torch.manual_seed(1234)
+    w3 = torch.randn(3 * D, 3, device=dev, requires_grad=True)
+    h = (torch.randn(G, 128, device=dev) / 11.3 * torch.exp(-torch.linspace(0, 4, 128, device=dev))).requires_grad_()
+    bias = torch.randn(D, device=dev, requires_grad=True)
+    d = D // world
+    sl = slice(rank * d, (rank + 1) * d)
+    gamma = (torch.rand(D, O, device=dev) * 0.09 + 0.01).log()
+    Rm = 0.1 * torch.randn(D, O, device=dev) / 4
+    pm = -torch.ones(D, O, device=dev)
+    gam_l, R_l, p_l, b_l = (t[sl].clone().requires_grad_() for t in (gamma, Rm, pm, bias.detach()))
+
+    def mr_block(x):
+        if world > 1:
+            f = halo_fused.causal_conv1d_cp(x, w3)
+            return halo_fused.hyena_mr_inner_cp(f, h, bias)
+        return ops.hyena_mr_inner(ops.causal_conv1d(x, w3), h, bias)
+
+    def li_block(x):
+        if world > 1:
+            f = halo_fused.causal_conv1d_cp(x, w3)
+            return li_fused.hyena_li_modal_cp(f, gam_l, R_l, p_l, b_l)
+        return ops.hyena_li_modal(ops.causal_conv1d(x, w3), gam_l, R_l, p_l, b_l)
+
+    def timed(fn):
+        ms = timeit(fn, iters)
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for L in seqs:
+        l = L // world
+        if L % (2 * world) or (l // 2) % 64:
+            continue
+        need = l * 3 * D * 2 * 14                     # rough per-rank working set of a forward + backward, bytes
+        if need > 150e9:
+            if rank == 0:
+                print(json.dumps({"op": "skipped", "L": L, "cp": world, "why": "working set exceeds the GPU's memory"}), flush=True)
+            continue
+        torch.manual_seed(99 + rank)
+        x = torch.randn(1, l, 3 * D, device=dev, dtype=BF, requires_grad=True)
+        tok = l * D * 2                               # bytes of one [l, D] bf16 tensor on this rank
+        for name, blk, hbm_f, hbm_b, nv_f, nv_b in (
+                # MR: conv reads/writes 3D each way; FIR reads 3D writes D (+ bwd: reads 3D + D, writes 3D).  Halo rows only.
+                ("hyena_mr_block", mr_block, (6 + 4) * tok, (9 + 7) * tok, 0.0, 0.0),
+                # LI: conv; gate u (3D in, D out); scan pulls u and stores y (each D over NVLink, share (cp-1)/cp); gate z
+                ("hyena_li_block", li_block, (6 + 4 + 4 + 5) * tok, (9 + 5 + 8 + 9) * tok,
+                 2 * tok * (world - 1) / world, 3 * tok * (world - 1) / world)):
+            out = blk(x)
+            g = torch.randn_like(out)
+            f_ms = timed(lambda: blk(x))
+
+            def fb():
+                for t in (x, w3, h, bias, gam_l, R_l, p_l, b_l):
+                    t.grad = None
+                blk(x).backward(g)
+            b_ms = timed(fb) - f_ms
+            if rank == 0:
+                for tag, ms, hb, nb in (("fwd", f_ms, hbm_f, nv_f), ("bwd", b_ms, hbm_b, nv_b)):
+                    t_hbm, t_nv = hb / bw, nb / NVLINK_BW
+                    roof = max(t_hbm, t_nv)
+                    print(json.dumps({"op": f"{name}.{tag}", "L": L, "cp": world, "tokens_per_gpu": l, "ms": round(ms, 3),
+                                      "roofline_ms": round(roof * 1e3, 3), "bound": "nvlink" if t_nv > t_hbm else "hbm",
+                                      "frac_of_roofline": round(roof * 1e3 / ms, 3), "hbm_bytes": hb, "nvlink_bytes": nb,
+                                      "peaks": src}), flush=True)
+            del out, g
+        del x
+        torch.cuda.empty_cache()
+    from savanna_b200.ops import cuda_ops
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--cp-sweep", action="store_true", help="context-parallel operator sweep over the ranks of the job")
+    ap.add_argument("--seqs", type=str, default="8192,32768,131072,1048576")
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--ops", type=str, default="gemm,dwconv,se,mr,li,norm,glu,ce,adam,attention")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--own-only", action="store_true", help="attention: time only this framework's kernels")
     a = ap.parse_args()
+    if a.cp_sweep:
+        return cp_sweep([int(v) for v in a.seqs.split(",")], a.iters)
     which = set(a.ops.split(","))
     torch.cuda.set_device(0)
     if "gemm" in which:
