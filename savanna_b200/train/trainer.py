@@ -126,6 +126,7 @@ class Trainer:
         self.profiler = None
         self.timers = None
         self.watchdog = None
+        self.straggler = self.comms_logger = self.alloc_stats = None
         if load and cfg.load is not None:
             from ..ckpt import load_checkpoint
             self.iteration = load_checkpoint(self)
@@ -255,10 +256,16 @@ class Trainer:
             raise RuntimeError(f"a kernel gave up on a bounded wait: code {(v >> 24) & 0xff}, detail {v & 0xffffff}")
 
     def _mark(self, name: str):
-        if self.profiler is not None:
-            return self.profiler.mark(name)
         import contextlib
-        return contextlib.nullcontext()
+        det = getattr(self, "straggler", None)
+        if self.profiler is None and det is None:
+            return contextlib.nullcontext()
+        stack = contextlib.ExitStack()
+        if self.profiler is not None:
+            stack.enter_context(self.profiler.mark(name))
+        if det is not None:
+            stack.enter_context(det.section(name))
+        return stack
 
     def train_step(self, data_iterator: Iterator) -> torch.Tensor:
         """One optimizer step over `gradient_accumulation_steps` micro-batches.  Returns the mean loss
@@ -374,6 +381,9 @@ class Trainer:
         if cfg.watchdog_step_timeout and cfg.watchdog_step_timeout > 0:
             self.watchdog = Watchdog(cfg.watchdog_step_timeout, cfg.watchdog_heartbeat_dir, rank=cfg.rank or 0)
             self.watchdog.start()
+        from ..utils import observability
+        self.straggler, self.comms_logger, self.alloc_stats = observability.build_from_config(
+            cfg, cfg.rank or 0, int(os.environ.get("WORLD_SIZE", "1")))
         self.profiler.start()
         if cfg.save and self.iteration == 0 and cfg.save_iters and 0 in cfg.save_iters:
             with self._unwatched():
@@ -385,6 +395,14 @@ class Trainer:
                 self.profiler.step()
                 logger.log_step(loss, time.time() - t0)
                 it = self.iteration
+                if self.straggler is not None:
+                    self.straggler.step()
+                if self.alloc_stats is not None:
+                    self.alloc_stats.step(it)
+                if self.comms_logger is not None and it % max(1, cfg.deepspeed_comms_logging_interval or cfg.log_interval or 1) == 0:
+                    if cfg.deepspeed_comms_print_summary and (cfg.rank or 0) == 0:
+                        print_rank_0(f"comms summary at iteration {it}: {self.comms_logger.summary()}")
+                    self.comms_logger.serialize(cfg.deepspeed_comms_ops_to_log)
                 if cfg.async_save:
                     from ..ckpt.io import finalize_async_save
                     finalize_async_save(blocking=False)  # publishes `latest` once every rank's writer is done
@@ -412,6 +430,8 @@ class Trainer:
             self.profiler.stop()
             if self.watchdog is not None:
                 self.watchdog.stop()
+            if self.comms_logger is not None:
+                self.comms_logger.uninstall()
             if cfg.async_save:
                 from ..ckpt.io import finalize_async_save
                 finalize_async_save(blocking=True)

@@ -1,0 +1,81 @@
+"""Straggler detection, collective logging and the allocation watcher, on CPU (gloo ranks, injected slow rank)."""
+import time
+
+import torch
+import torch.distributed as dist
+
+from savanna_b200.utils.observability import AllocStats, CommsLogger, StragglerDetector, bus_bandwidth_factor
+from tests.dist_utils import run_distributed
+
+
+def _w_straggler(rank, world):
+    lines = []
+    det = StragglerDetector(world, rank, interval=4, minmax_count=2, rel_threshold=0.7, use_cuda_events=False, printer=lines.append)
+    rep = None
+    for step in range(4):
+        with det.section("TRAIN_STEP_FORWARD"):
+            time.sleep(0.06 if rank == 2 else 0.02)          # rank 2 is three times slower in this section
+        with det.section("TRAIN_STEP_BACKWARD"):
+            time.sleep(0.02)
+        rep = det.step()
+        dist.barrier()
+    assert rep is not None and rep["steps"] == 4
+    fwd = rep["sections"]["host/TRAIN_STEP_FORWARD"]
+    assert fwd["slowest_ranks"][0] == 2 and rep["stragglers"]["host/TRAIN_STEP_FORWARD"] == [2], rep
+    assert "host/TRAIN_STEP_BACKWARD" not in rep["stragglers"]
+    assert abs(fwd["relative_perf_scores"][0] - 1.0) < 0.3 and fwd["relative_perf_scores"][2] < 0.5
+    if rank == 0:
+        assert any("ranks [2]" in ln for ln in lines), lines
+
+
+def test_straggler_detector_names_the_slow_rank():
+    run_distributed(_w_straggler, 4)
+
+
+def test_straggler_individual_score_flags_a_rank_that_slows_down():
+    lines = []
+    det = StragglerDetector(1, 0, interval=2, use_cuda_events=False, individual_threshold=0.7, printer=lines.append)
+    for delay in (0.01, 0.01, 0.04, 0.04):
+        with det.section("step"):
+            time.sleep(delay)
+        rep = det.step()
+    assert rep["individual_perf_scores"]["host/step"] < 0.5 and "host/step" in rep["individual_stragglers"]
+
+
+def _w_comms(rank, world):
+    lines = []
+    lg = CommsLogger(rank, ops=["all_reduce", "broadcast"], rank_stride=2, world=world, printer=lines.append)
+    lg.install()
+    try:
+        lg.enabled = True
+        x = torch.ones(1024)
+        for _ in range(3):
+            dist.all_reduce(x)
+        dist.broadcast(x[:16].clone(), 0)
+        dist.all_gather([torch.empty(4) for _ in range(world)], torch.ones(4))       # not in the op list: not recorded
+        lg.enabled = False
+        dist.all_reduce(x)                                                             # disabled: not recorded
+        summ = lg.summary()
+        assert summ["all_reduce"][4096]["count"] == 3 and summ["broadcast"][64]["count"] == 1 and "all_gather" not in summ
+        assert summ["all_reduce"][4096]["busbw_gbs"] == summ["all_reduce"][4096]["algbw_gbs"] * bus_bandwidth_factor("all_reduce", world)
+        out = lg.serialize()
+        assert any(ln.startswith(f"COMMS:all_reduce,{rank},4096,") and ln.count(",") == 5 for ln in out), out
+        assert (len(lines) > 0) == (rank % 2 == 0)            # only every second rank prints
+    finally:
+        lg.uninstall()
+    assert not hasattr(dist.all_reduce, "_sb_comms_original")
+
+
+def test_comms_logger_records_selected_collectives():
+    run_distributed(_w_comms, 2)
+
+
+def test_alloc_stats_warns_when_the_allocator_goes_back_to_the_driver():
+    counters = {"num_alloc_retries": 0, "num_device_alloc": 10, "num_device_free": 2}
+    lines = []
+    w = AllocStats(rank=3, warmup_steps=7, reader=lambda: dict(counters), printer=lines.append)
+    for it in range(1, 10):
+        assert w.step(it) is False
+    counters["num_device_alloc"] = 12
+    assert w.step(10) is True and w.changes == 1 and "rank=3" in lines[0]
+    assert w.step(11) is False
