@@ -36,6 +36,8 @@ class SelfAttention(nn.Module):
         self.hd = cfg.hidden_size // cfg.num_attention_heads
         self.causal = cfg.causal
         self.operator_type = operator_type
+        # context-parallel exchange of `flash_te` layers: "p2p" = ring of K/V shards, "a2a" = head exchange, "all_gather"
+        self.cp_comm_type = cfg.flash_te_comm_type or "p2p"
         self._rotary = []          # the module itself is registered by the owning mixer as `rotary_emb`
         if cfg.pos_emb in ("rotary", "rotary_linear_scaled", "rotary_ntk_scaled", "rotary2"):
             rd = int(self.hd * cfg.rotary_pct)
@@ -51,7 +53,14 @@ class SelfAttention(nn.Module):
             cos, sin = self._rotary[0](positions)
             q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
         cp = state.get_context_parallel_world_size()
-        if cp > 1 and self.operator_type in ("ring", "flash_te"):
+        comm = self.cp_comm_type if self.operator_type == "flash_te" else "p2p"
+        if cp > 1 and self.operator_type in ("ring", "flash_te") and comm == "a2a":
+            from ..parallel.cp_attention import ulysses_attention
+            o = ulysses_attention(q, k, v, causal=self.causal)
+        elif cp > 1 and self.operator_type in ("ring", "flash_te") and comm == "all_gather":
+            from ..parallel.cp_attention import allgather_attention
+            o = allgather_attention(q, k, v, causal=self.causal)
+        elif cp > 1 and self.operator_type in ("ring", "flash_te"):
             from ..parallel.ring_attention import ring_attention
             o = ring_attention(q, k, v, positions, causal=self.causal)
         else:

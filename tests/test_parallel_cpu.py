@@ -243,6 +243,17 @@ def test_context_parallel_equivalence_cp4(algo):
 
 
 @pytest.mark.slow
+@pytest.mark.parametrize("comm", ["a2a", "all_gather"])
+def test_context_parallel_attention_comm_types(comm):
+    """`flash_te` layers with the head-exchange and the key/value all-gather forms of context-parallel attention at
+    cp=2 reproduce the single-process loss trace and gradient norm."""
+    ref_losses, ref_norms = _reference_losses(with_norms=True)
+    over = {"context_parallel_size": 2, "use_cp_hyena": True, "use_cp_flash_te": True, "flash_te_comm_type": comm,
+            "operator_config": ["hyena_se", "hyena_mr", "hyena", "flash_te"]}
+    run_distributed(_w_equiv, 2, over, ref_losses, ref_norms)
+
+
+@pytest.mark.slow
 def test_zero1_data_parallel_equivalence():
     """dp=2 with micro batch 1 and ZeRO-1 partitioning == one process with micro batch 2."""
     ref_losses = _reference_losses(mb=2)
