@@ -1,10 +1,10 @@
 """Autoregressive text generation for evaluation and sampling.
 
 `stream_tokens` re-runs the model on the growing context (the "recompute" mode of the reference,
-savanna/text_generation_utils.py:173-365 — constant-memory recurrent Hyena inference lives in the separate
-vortex project there as well) with temperature / top-k / top-p sampling; drivers for a single prompt, a
-prompt file and unconditional samples mirror savanna/text_generation_utils.py:368-774 and
-savanna/inference/generation.py.
+savanna/text_generation_utils.py:173-365) with temperature / top-k / top-p sampling; `generate(..., use_cache=True)`
+decodes with per-layer cached state instead (inference/cached.py: FIR tails, modal states, key/value cache), one
+constant-time step per token.  Drivers for a single prompt, a prompt file, unconditional samples and an interactive
+prompt loop mirror savanna/text_generation_utils.py:368-774 and savanna/inference/generation.py.
 """
 from __future__ import annotations
 
@@ -90,9 +90,41 @@ def stream_tokens(model, context_tokens: List[List[int]], eos_token_id: Optional
         model.train(was_training)
 
 
+def _generate_cached(model, tokenizer, prompts, ctx, maximum_tokens, temperature, top_k, top_p, eos_token_id, return_logits):
+    """Cached decoding; prompts are grouped by length so that each group shares one prefill."""
+    from .cached import stream_tokens_cached
+    out: List[Optional[Dict]] = [None] * len(prompts)
+    by_len: Dict[int, List[int]] = {}
+    for i, c in enumerate(ctx):
+        by_len.setdefault(len(c), []).append(i)
+    for n, idxs in by_len.items():
+        toks, steps, done_at = None, [], [None] * len(idxs)
+        for toks, logits, done in stream_tokens_cached(model, [ctx[i] for i in idxs], eos_token_id, maximum_tokens,
+                                                       temperature, top_k, top_p):
+            steps.append(logits.cpu() if return_logits else None)
+            for j in range(len(idxs)):
+                if done_at[j] is None and bool(done[j]):
+                    done_at[j] = toks.shape[1]
+        for j, i in enumerate(idxs):
+            end = done_at[j] if done_at[j] is not None else toks.shape[1]
+            gen = toks[j, n:end].tolist()
+            rec = {"context": prompts[i], "text": tokenizer.detokenize(gen), "length": len(gen)}
+            if return_logits:
+                rec["logits"] = torch.stack([l[j] for l in steps])
+            out[i] = rec
+    return out
+
+
 def generate(model, tokenizer, prompts: List[str], maximum_tokens: int = 64, temperature: float = 0.0, top_k: int = 0,
-             top_p: float = 0.0, eos_token_id: Optional[int] = None, return_logits: bool = False) -> List[Dict]:
+             top_p: float = 0.0, eos_token_id: Optional[int] = None, return_logits: bool = False,
+             use_cache: bool = False) -> List[Dict]:
     ctx = [tokenizer.tokenize(p) or [tokenizer.eod] for p in prompts]
+    if use_cache:
+        try:
+            return _generate_cached(model, tokenizer, prompts, ctx, maximum_tokens, temperature, top_k, top_p, eos_token_id,
+                                    return_logits)
+        except NotImplementedError as exc:
+            print(f"cached generation unavailable for this model ({exc}); recomputing the context every step")
     last = None
     all_logits = []
     for last in stream_tokens(model, ctx, eos_token_id, maximum_tokens, temperature, top_k, top_p,
@@ -117,7 +149,7 @@ def generate_samples_from_prompt(model, cfg, text, **kw) -> List[Dict]:
     return generate(model, cfg.tokenizer, prompts, maximum_tokens=kw.get("maximum_tokens", cfg.maximum_tokens),
                     temperature=kw.get("temperature", cfg.temperature), top_k=kw.get("top_k", cfg.top_k),
                     top_p=kw.get("top_p", cfg.top_p), eos_token_id=kw.get("eos_token_id"),
-                    return_logits=cfg.return_logits)
+                    return_logits=cfg.return_logits, use_cache=kw.get("use_cache", not bool(cfg.recompute)))
 
 
 def generate_samples_input_from_file(model, cfg, input_file: str, output_file: Optional[str] = None, **kw):
@@ -140,3 +172,39 @@ def generate_samples_unconditional(model, cfg, number_of_samples: int = 1, outpu
             for r in results:
                 fh.write(json.dumps({k: v for k, v in r.items() if k != "logits"}) + "\n")
     return results
+
+
+def generate_samples_interactive(model, cfg, input_fn=input, print_fn=print, **kw) -> None:
+    """Prompt loop on the terminal (reference: text_generation_utils.py:672-774): read a context, stream the
+    continuation as it is generated, repeat until an empty line, "stop" or end of input.  With several ranks only
+    rank 0 talks to the terminal; the others would need the prompt broadcast, so this driver runs single-process."""
+    tok = cfg.tokenizer
+    use_cache = kw.get("use_cache", not bool(cfg.recompute))
+    while True:
+        try:
+            text = input_fn("Context prompt >>> ")
+        except EOFError:
+            break
+        if not text.strip() or text.strip().lower() == "stop":
+            break
+        ctx = [tok.tokenize(text) or [tok.eod]]
+        shown = 0
+        stream = None
+        if use_cache:
+            try:
+                from .cached import CachedDecoder, stream_tokens_cached
+                CachedDecoder(model)                      # raises when the model has no cached form
+                stream = ((t, None, None, d) for t, _, d in stream_tokens_cached(
+                    model, ctx, kw.get("eos_token_id"), kw.get("maximum_tokens", cfg.maximum_tokens),
+                    kw.get("temperature", cfg.temperature), kw.get("top_k", cfg.top_k), kw.get("top_p", cfg.top_p)))
+            except NotImplementedError:
+                stream = None
+        if stream is None:
+            stream = stream_tokens(model, ctx, kw.get("eos_token_id"), kw.get("maximum_tokens", cfg.maximum_tokens),
+                                   kw.get("temperature", cfg.temperature), kw.get("top_k", cfg.top_k), kw.get("top_p", cfg.top_p))
+        for toks, _, _, _ in stream:
+            gen = toks[0, len(ctx[0]):].tolist()
+            piece = tok.detokenize(gen)
+            print_fn(piece[shown:], end="", flush=True)
+            shown = len(piece)
+        print_fn("")
