@@ -19,7 +19,8 @@ optimizer files is the combined model rank `pipe_stage * tp + tp_rank`, so no tw
 Behaviour (reference: savanna/checkpointing.py:153-571): tag `global_step<N>`; `latest` is reconciled
 with the directories on disk (the older of the two wins, so a half-written newest checkpoint is
 skipped); keep-last-N deletion; optional background (async) writing finalised at the next step;
-finetune = module only and iteration 0; `no_load_optim` / `no_load_rng`; strict toggle; optional
+finetune = module only and iteration 0; warmstart = everything but the iteration, data cursor and random streams;
+`no_load_optim` / `no_load_rng`; strict toggle; optional
 forward-pass logits validation; data cursor (`train_data_token_index`) and LR-scheduler restore.
 """
 from __future__ import annotations
@@ -309,32 +310,10 @@ def _delete_old(root: str, keep: int) -> None:
         shutil.rmtree(d, ignore_errors=True)
 
 
-def _upload(cfg, ckpt_dir: str, retries: int = 3) -> None:
-    """Copy a finished checkpoint to every configured store.  A `.uploading` marker is written first and
-    replaced by `.uploaded` on success, so deletion never removes a checkpoint that is not safely stored
-    (reference: checkpointing.py:187-291).  Only the "posix" store type is built in; "s3" needs boto3."""
-    for store in cfg.checkpoint_stores or []:
-        kind = store.get("storage_type", "posix")
-        dst_root = store.get("location")
-        if kind != "posix":
-            try:
-                import boto3  # noqa: F401
-            except ImportError:
-                print_rank_0(f"  checkpoint store {kind!r} needs boto3, which is not installed; skipping upload")
-                continue
-        dst = os.path.join(dst_root, os.path.basename(ckpt_dir))
-        marker = os.path.join(ckpt_dir, ".uploading")
-        open(marker, "w").close()
-        delay = 1.0
-        for attempt in range(retries):
-            try:
-                shutil.copytree(ckpt_dir, dst, dirs_exist_ok=True, ignore=shutil.ignore_patterns(".uploading", ".uploaded"))
-                os.replace(marker, os.path.join(ckpt_dir, ".uploaded"))
-                break
-            except OSError as exc:
-                print_rank_0(f"  upload attempt {attempt + 1} failed: {exc}")
-                time.sleep(delay)
-                delay *= 2
+def _upload(cfg, ckpt_dir: str) -> None:
+    """Copy a finished checkpoint to every configured store (ckpt/stores.py: posix directories, S3 buckets)."""
+    from .stores import build_stores, upload_checkpoint
+    upload_checkpoint(ckpt_dir, build_stores(cfg.checkpoint_stores))
 
 
 # ----------------------------------------------------------------------------- load
@@ -398,6 +377,12 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
         opt.refresh_master_from_params()
     if cfg.finetune:
         it_out = 0
+    elif cfg.warmstart:
+        # weights, optimizer state and LR schedule come from the checkpoint, but the run counts from iteration 0 with a
+        # fresh data cursor and fresh random streams (reference: checkpointing.py:445, :495)
+        it_out = 0
+        if trainer.lr_scheduler is not None and ms.get("lr_scheduler") is not None and not cfg.no_load_optim:
+            trainer.lr_scheduler.load_state_dict(ms["lr_scheduler"])
     else:
         it_out = int(ms.get("iteration", it))
         if trainer.lr_scheduler is not None and ms.get("lr_scheduler") is not None and not cfg.no_load_optim:

@@ -170,3 +170,22 @@ def test_finetune_loads_module_only(tmp_path):
     for a, b in zip(tr.model.parameters(), t2.model.parameters()):
         assert torch.equal(a, b)
     assert t2.optimizer.step_count == 0
+
+
+def test_warmstart_loads_state_but_restarts_the_count(tmp_path):
+    """`warmstart`: module and optimizer state come from the checkpoint, the iteration and the data cursor start at 0."""
+    save = str(tmp_path / "c")
+    cfg = _cfg(save=save)
+    tr = Trainer(cfg, load=False)
+    d = _iter(cfg)
+    for _ in range(2):
+        tr.train_step(d)
+    from savanna_b200.ckpt import save_checkpoint
+    save_checkpoint(tr)
+    t2 = Trainer(_cfg(load=save, warmstart=True), load=True)
+    assert t2.iteration == 0 and t2.tokens_seen == 0
+    for a, b in zip(tr.model.parameters(), t2.model.parameters()):
+        assert torch.equal(a, b)
+    assert t2.optimizer.step_count == tr.optimizer.step_count == 2
+    for ga, gb in zip(tr.optimizer.groups, t2.optimizer.groups):
+        assert torch.equal(ga.exp_avg, gb.exp_avg) and torch.equal(ga.master, gb.master)

@@ -237,3 +237,44 @@ def test_cached_generation_matches_recompute():
     generate_samples_interactive(model, cfg, input_fn=lambda _: next(prompts), print_fn=lambda *x, **k: said.append(x[0]),
                                  maximum_tokens=5)
     assert "".join(said) == generate(model, cfg.tokenizer, ["ACGTACGT"], maximum_tokens=5)[0]["text"]
+
+
+def test_checkpoint_stores_posix_and_s3(tmp_path):
+    """Uploads to a posix store (with retention) and to an S3 store driven through a fake client: retries, markers, and
+    a failed upload that leaves `.uploading` in place so that pruning keeps the directory."""
+    from savanna_b200.ckpt.io import _delete_old
+    from savanna_b200.ckpt.stores import PosixStore, S3Store, upload_checkpoint
+    root = tmp_path / "run"
+    for step in (10, 20, 30):
+        d = root / f"global_step{step}"
+        (d / "configs").mkdir(parents=True)
+        (d / "mp_rank_00_model_states.pt").write_bytes(b"x" * step)
+        (d / "configs" / "a.yml").write_text("k: 1")
+
+    class FakeS3:
+        def __init__(self, fail_first=0, always_fail=False):
+            self.calls, self.fail_first, self.always_fail, self.objects = 0, fail_first, always_fail, {}
+
+        def upload_file(self, path, bucket, key):
+            self.calls += 1
+            if self.always_fail or self.calls <= self.fail_first:
+                raise OSError("connection reset")
+            self.objects[(bucket, key)] = open(path, "rb").read()
+
+    naps = []
+    posix = PosixStore({"location": str(tmp_path / "mirror"), "num_checkpoints": 2})
+    s3 = S3Store({"bucket": "b", "location": "runs/x", "max_retries": 2}, client=FakeS3(fail_first=1))
+    for step in (10, 20, 30):
+        assert upload_checkpoint(str(root / f"global_step{step}"), [posix, s3], sleep=naps.append)
+        assert (root / f"global_step{step}" / ".uploaded").exists() and not (root / f"global_step{step}" / ".uploading").exists()
+    assert sorted(os.listdir(tmp_path / "mirror")) == ["global_step20", "global_step30"]          # keep last 2
+    assert s3.client.objects[("b", "runs/x/global_step30/configs/a.yml")] == b"k: 1"
+    assert len(s3.client.objects) == 6 and naps == [10.0]                                         # one retry, one delay
+    bad = S3Store({"bucket": "b", "location": "", "max_retries": 1}, client=FakeS3(always_fail=True))
+    (root / "global_step40").mkdir()
+    (root / "global_step40" / "f.pt").write_bytes(b"y")
+    assert not upload_checkpoint(str(root / "global_step40"), [bad], sleep=naps.append)
+    assert (root / "global_step40" / ".uploading").exists() and not (root / "global_step40" / ".uploaded").exists()
+    (root / "global_step50").mkdir()
+    _delete_old(str(root), 1)                                  # would remove 10..40; 40 is still being uploaded
+    assert sorted(p for p in os.listdir(root)) == ["global_step40", "global_step50"]
