@@ -278,3 +278,51 @@ def test_checkpoint_stores_posix_and_s3(tmp_path):
     (root / "global_step50").mkdir()
     _delete_old(str(root), 1)                                  # would remove 10..40; 40 is still being uploaded
     assert sorted(p for p in os.listdir(root)) == ["global_step40", "global_step50"]
+
+
+def test_zero3_layout_round_trips(tmp_path):
+    """Stage-1 checkpoint -> stage-3 layout at dp=3 (a size that does not divide the parameters) -> re-partitioned to
+    dp=2 -> back to stage 1: master weights and Adam moments survive bit for bit, the files carry the stage-3 keys, and
+    the converted checkpoint loads into a trainer that continues the original loss trace."""
+    from savanna_b200.ckpt import save_checkpoint
+    from savanna_b200.tools import convert_zero3 as z3
+    cfg = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1, "save": str(tmp_path / "ck"), "hidden_dropout": 0.0})
+    tr = Trainer(cfg, load=False)
+
+    def it(start=0):
+        i = start
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    d = it()
+    for _ in range(2):
+        tr.train_step(d)
+    src = save_checkpoint(tr)
+    want_next = float(tr.train_step(d))
+    s3, s3b, s1 = str(tmp_path / "z3" / "global_step2"), str(tmp_path / "z3b" / "global_step2"), str(tmp_path / "z1" / "global_step2")
+    z3.from_zero1(src, s3, 3)
+    names = sorted(os.listdir(s3))
+    assert "zero_pp_rank_2_mp_rank_00_model_states.pt" in names and "zero_pp_rank_2_mp_rank_00_optim_states.pt" in names
+    o = torch.load(os.path.join(s3, "zero_pp_rank_1_mp_rank_00_optim_states.pt"), weights_only=False)["optimizer_state_dict"]
+    assert o["zero_stage"] == 3 and o["partition_count"] == 3 and "fp32_flat_groups" in o
+    shapes = torch.load(os.path.join(s3, "zero_pp_rank_0_mp_rank_00_model_states.pt"), weights_only=False)["param_shapes"]
+    want = sum(z3.partition_size(int(torch.Size(s).numel()), 3) for s in shapes[0].values())
+    assert o["fp32_flat_groups"][0].numel() == want                       # every parameter cut on its own
+    z3.repartition(s3, s3b, 2)
+    z3.to_zero1(s3b, s1, 1)
+    a = torch.load(os.path.join(src, "zero_pp_rank_0_mp_rank_00_optim_states.pt"), weights_only=False)["optimizer_state_dict"]
+    b = torch.load(os.path.join(s1, "zero_pp_rank_0_mp_rank_00_optim_states.pt"), weights_only=False)["optimizer_state_dict"]
+    for g in range(len(a["single_partition_of_fp32_groups"])):
+        assert torch.equal(a["single_partition_of_fp32_groups"][g], b["single_partition_of_fp32_groups"][g])
+        for key in ("exp_avg", "exp_avg_sq"):
+            assert torch.equal(a["base_optimizer_state"]["state"][g][key], b["base_optimizer_state"]["state"][g][key])
+    z3.to_fp32(s3, str(tmp_path / "w.pt"))
+    w = torch.load(str(tmp_path / "w.pt"), weights_only=False)
+    some = next(n for n in w if n.endswith("dense_projection.weight"))
+    assert w[some].dtype == torch.float32 and w[some].shape == dict(tr.model.named_parameters())[some].shape
+    with open(os.path.join(str(tmp_path / "z1"), "latest"), "w") as fh:
+        fh.write("global_step2")
+    cfg2 = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1, "load": str(tmp_path / "z1"), "hidden_dropout": 0.0})
+    t2 = Trainer(cfg2, load=True)
+    assert t2.iteration == 2
+    assert abs(float(t2.train_step(it(2))) - want_next) < 1e-6
