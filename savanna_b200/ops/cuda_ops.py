@@ -88,6 +88,87 @@ def launch_count() -> int:
     return _LAUNCHES
 
 
+# ----------------------------------------------------------------------------- guarded allocation (debug aid)
+# Every buffer a kernel of this library writes (outputs, gradients, scratch) is allocated through the four helpers
+# below.  Normally they are torch.empty / zeros.  Inside `guarded_allocations()` each buffer is instead a window into a
+# larger one whose margins (GUARD elements on either side) hold a byte pattern; `check_guards()` verifies the margins
+# after the kernels have run, so a kernel that stores outside its output - a wrong tile bound, a bad leading
+# dimension - is caught even when the stray store lands in memory the process owns (where no fault would show it).
+GUARD = 256                 # elements on each side; keeps the window 256-byte aligned for every dtype
+_GUARD_BYTE = 0x5B
+_GUARDED = None             # None = off; else list of (whole buffer, window numel, tag)
+
+
+def _numel(shape) -> int:
+    n = 1
+    for d in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)):
+        n *= int(d)
+    return n
+
+
+def _alloc(*shape, dtype=None, device=None):
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    if _GUARDED is None or (device is not None and torch.device(device).type != "cuda"):
+        return torch.empty(shape, dtype=dtype, device=device)
+    dtype = dtype or torch.get_default_dtype()
+    n = _numel(shape)
+    whole = torch.empty(n + 2 * GUARD, dtype=dtype, device=device)
+    whole.view(torch.uint8).fill_(_GUARD_BYTE)
+    _GUARDED.append((whole, n, f"{tuple(shape)} {dtype}"))
+    return whole[GUARD:GUARD + n].view(shape)
+
+
+def _alloc_like(t):
+    if _GUARDED is None or not t.is_cuda:
+        return torch.empty_like(t)
+    return _alloc(tuple(t.shape), dtype=t.dtype, device=t.device)
+
+
+def _zeros(*shape, dtype=None, device=None):
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    if _GUARDED is None or (device is not None and torch.device(device).type != "cuda"):
+        return torch.zeros(shape, dtype=dtype, device=device)
+    return _alloc(shape, dtype=dtype, device=device).zero_()
+
+
+def _zeros_like(t):
+    if _GUARDED is None or not t.is_cuda:
+        return torch.zeros_like(t)
+    return _alloc(tuple(t.shape), dtype=t.dtype, device=t.device).zero_()
+
+
+class guarded_allocations:
+    """Context manager: allocate this library's kernel outputs with guard margins (see above)."""
+
+    def __enter__(self):
+        global _GUARDED
+        self.prev, _GUARDED = _GUARDED, []
+        return self
+
+    def __exit__(self, *exc):
+        global _GUARDED
+        _GUARDED = self.prev
+        return False
+
+
+def check_guards() -> int:
+    """Verify the margins of every buffer allocated under `guarded_allocations()` so far; raises on the first damaged
+    one, naming its shape.  Returns the number of buffers checked."""
+    if _GUARDED is None:
+        return 0
+    torch.cuda.synchronize()
+    for whole, n, tag in _GUARDED:
+        b = whole.view(torch.uint8)
+        item = whole.element_size()
+        lo, hi = b[: GUARD * item], b[(GUARD + n) * item:]
+        if bool((lo != _GUARD_BYTE).any()) or bool((hi != _GUARD_BYTE).any()):
+            side = "before" if bool((lo != _GUARD_BYTE).any()) else "after"
+            raise RuntimeError(f"a kernel wrote outside its output buffer {tag} ({side} it)")
+    return len(_GUARDED)
+
+
 def _count(n: int = 1) -> None:
     global _LAUNCHES
     _LAUNCHES += n
@@ -110,7 +191,7 @@ def status_word(device) -> torch.Tensor:
     """Per-device uint32 word the bounded waits of the kernels write when they give up."""
     key = torch.device(device).index or 0
     if key not in _STATUS:
-        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[key] = _zeros(1, dtype=torch.int32, device=device)
     return _STATUS[key]
 
 
@@ -184,7 +265,7 @@ def colsum(x2: torch.Tensor) -> torch.Tensor:
     """fp32 column sums of a [T, N] bf16 matrix (bias gradients) without an fp32 copy of the matrix."""
     lib = require()
     T, N = x2.shape
-    out = torch.zeros(N, dtype=torch.float32, device=x2.device)
+    out = _zeros(N, dtype=torch.float32, device=x2.device)
     _check(lib.sb_colsum(x2.data_ptr(), out.data_ptr(), T, N, _stream()), "colsum")
     _count()
     return out
@@ -205,7 +286,7 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, residual):
         x2 = _rows(x)
-        out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
+        out = _alloc((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
         r2 = _rows(residual) if residual is not None else None
         gemm(x2, w, out, bias=bias, residual=r2)
         ctx.save_for_backward(x2, w)
@@ -221,7 +302,7 @@ class _Linear(torch.autograd.Function):
         g2 = _rows(gy)
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            gx = torch.empty_like(x2)
+            gx = _alloc_like(x2)
             gemm(g2, w, gx, a_mn=False, b_mn=True)                 # dX[T,K] = dY[T,N] . W[N,K]
             gx = gx.view(ctx.xshape)
         if ctx.needs_input_grad[1]:
@@ -230,7 +311,7 @@ class _Linear(torch.autograd.Function):
             if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == w.shape:
                 gemm(g2, x2, tgt, a_mn=True, b_mn=True, accumulate=True)   # dW += dY^T X, straight into the flat buffer
             else:
-                gw = torch.empty_like(w)
+                gw = _alloc_like(w)
                 gemm(g2, x2, gw, a_mn=True, b_mn=True)             # dW[N,K] = dY^T[N,T] . X[T,K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g2).to(gy.dtype) if g2.shape[1] % 8 == 0 else g2.float().sum(0).to(gy.dtype)
@@ -252,9 +333,9 @@ def bump_param_epoch() -> None:
 def quantize_fp8(x2: torch.Tensor, fmt: int):
     """Per-tensor current scaling: q = sat(x * fmax / amax(x)) as bytes, plus the de-quantisation factor (device scalar)."""
     lib = require()
-    q = torch.empty(x2.shape, dtype=torch.uint8, device=x2.device)
-    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
-    sinv = torch.empty(1, dtype=torch.float32, device=x2.device)
+    q = _alloc(x2.shape, dtype=torch.uint8, device=x2.device)
+    amax = _alloc(1, dtype=torch.float32, device=x2.device)
+    sinv = _alloc(1, dtype=torch.float32, device=x2.device)
     _check(lib.sb_quantize_fp8(x2.data_ptr(), q.data_ptr(), amax.data_ptr(), sinv.data_ptr(), x2.numel(), fmt, _stream()),
            "quantize_fp8")
     _count(2)
@@ -269,7 +350,7 @@ class Fp8History:
     __slots__ = ("buf", "cur", "primed")
 
     def __init__(self, device, history: int):
-        self.buf = torch.zeros(history + 2, dtype=torch.float32, device=device)
+        self.buf = _zeros(history + 2, dtype=torch.float32, device=device)
         self.cur = 0
         self.primed = False
 
@@ -297,8 +378,8 @@ def quantize_fp8_site(x2: torch.Tensor, fmt: int, owner, role: str):
         return quantize_fp8(x2, fmt)
     h = _site(owner, role, x2.device)
     lib = require()
-    q = torch.empty(x2.shape, dtype=torch.uint8, device=x2.device)
-    sinv = torch.empty(1, dtype=torch.float32, device=x2.device)
+    q = _alloc(x2.shape, dtype=torch.uint8, device=x2.device)
+    sinv = _alloc(1, dtype=torch.float32, device=x2.device)
     if not h.primed:
         _check(lib.sb_quantize_fp8(x2.data_ptr(), q.data_ptr(), h.buf.data_ptr(), sinv.data_ptr(), x2.numel(), fmt, _stream()),
                "quantize_fp8")
@@ -348,7 +429,7 @@ class _LinearFP8(torch.autograd.Function):
         x2 = _rows(x)
         xq, sx = quantize_fp8_site(x2, E4M3, w, "x")
         wq, sw = _fp8_weight(w)
-        out = torch.empty((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
+        out = _alloc((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
         r2 = _rows(residual) if residual is not None else None
         gemm_fp8(xq, wq, out, sx, bias=bias, residual=r2, alpha2=sw)
         ctx.save_for_backward(xq, sx, wq, sw)
@@ -362,7 +443,7 @@ class _LinearFP8(torch.autograd.Function):
         gq, sg = quantize_fp8_site(g2, E5M2, ctx.wref, "g")
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            gx = torch.empty((g2.shape[0], wq.shape[1]), dtype=bf16, device=gy.device)
+            gx = _alloc((g2.shape[0], wq.shape[1]), dtype=bf16, device=gy.device)
             gemm_fp8(gq, wq, gx, sg, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sw)
             gx = gx.view(ctx.xshape)
         if ctx.needs_input_grad[1]:
@@ -371,7 +452,7 @@ class _LinearFP8(torch.autograd.Function):
             if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == wp.shape:
                 gemm_fp8(gq, xq, tgt, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
             else:
-                gw = torch.empty(wp.shape, dtype=bf16, device=gy.device)
+                gw = _alloc(wp.shape, dtype=bf16, device=gy.device)
                 gemm_fp8(gq, xq, gw, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = colsum(g2).to(gy.dtype)
@@ -405,8 +486,8 @@ def _rmsnorm_fwd(x, w, eps, form):
     lib = require()
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     T, D = x2.shape
-    y = torch.empty_like(x2)
-    a = torch.empty(T, dtype=torch.float32, device=x.device)
+    y = _alloc_like(x2)
+    a = _alloc(T, dtype=torch.float32, device=x.device)
     wc = w.contiguous()
     _check(lib.sb_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), a.data_ptr(), T, D, eps, form, _stream()),
            "rmsnorm_fwd")
@@ -419,9 +500,9 @@ def _rmsnorm_bwd(x2, w, a, gy, gres, eps, form):
     T, D = x2.shape
     g2 = gy.reshape(T, D).contiguous()
     r2 = gres.reshape(T, D).contiguous() if gres is not None else None
-    dx = torch.empty_like(x2)
-    dw = torch.empty(D, dtype=bf16, device=x2.device)
-    partial = torch.empty(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
+    dx = _alloc_like(x2)
+    dw = _alloc(D, dtype=bf16, device=x2.device)
+    partial = _alloc(lib.sb_rmsnorm_bwd_blocks(T) * D, dtype=torch.float32, device=x2.device)
     _check(lib.sb_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), a.data_ptr(), _ptr(r2), dx.data_ptr(),
                               dw.data_ptr(), partial.data_ptr(), T, D, eps, form, _stream()), "rmsnorm_bwd")
     _count(2)
@@ -471,14 +552,14 @@ def _fp8_backward_gemms(ctx_w, gy2, xq, sx, wq, sw, need_gx, need_gw):
     gq, sg = quantize_fp8_site(gy2, E5M2, ctx_w, "g")
     gx = gw = None
     if need_gx:
-        gx = torch.empty((gy2.shape[0], wq.shape[1]), dtype=bf16, device=gy2.device)
+        gx = _alloc((gy2.shape[0], wq.shape[1]), dtype=bf16, device=gy2.device)
         gemm_fp8(gq, wq, gx, sg, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sw)
     if need_gw:
         tgt = ctx_w.grad if getattr(ctx_w, "_fuse_grad_accum", False) else None
         if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == ctx_w.shape:
             gemm_fp8(gq, xq, tgt, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
         else:
-            gw = torch.empty(ctx_w.shape, dtype=bf16, device=gy2.device)
+            gw = _alloc(ctx_w.shape, dtype=bf16, device=gy2.device)
             gemm_fp8(gq, xq, gw, sg, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
     return gx, gw
 
@@ -499,15 +580,15 @@ class _NormLinearFP8(torch.autograd.Function):
             _, _, a, y = _rmsnorm_fwd(x, wn, eps, form)
             xq, sx = quantize_fp8_site(y, E4M3, w, "x")
         else:
-            xq = torch.empty((T, D), dtype=torch.uint8, device=x.device)
-            a = torch.empty(T, dtype=torch.float32, device=x.device)
-            sx = torch.empty(1, dtype=torch.float32, device=x.device)
+            xq = _alloc((T, D), dtype=torch.uint8, device=x.device)
+            a = _alloc(T, dtype=torch.float32, device=x.device)
+            sx = _alloc(1, dtype=torch.float32, device=x.device)
             _check(lib.sb_rmsnorm_fwd_fp8(x2.data_ptr(), wnc.data_ptr(), xq.data_ptr(), a.data_ptr(), T, D, eps, form,
                                           h.buf.data_ptr(), h.buf.numel(), h.cur, sx.data_ptr(), _stream()), "rmsnorm_fwd_fp8")
             _count()
             h.cur = (h.cur + 1) % h.buf.numel()
         wq, sw = _fp8_weight(w)
-        out = torch.empty((T, w.shape[0]), dtype=bf16, device=x.device)
+        out = _alloc((T, w.shape[0]), dtype=bf16, device=x.device)
         gemm_fp8(xq, wq, out, sx, bias=bias, alpha2=sw)
         ctx.save_for_backward(x2, wnc, a, xq, sx, wq, sw)
         ctx.meta = (eps, form, x.shape, bias is not None)
@@ -539,19 +620,19 @@ class _GluLinearFP8(torch.autograd.Function):
         Fh = F2 // 2
         h = _site(w, "x", ab.device)
         if not h.primed:
-            hb = torch.empty((T, Fh), dtype=bf16, device=ab.device)
+            hb = _alloc((T, Fh), dtype=bf16, device=ab.device)
             _check(lib.sb_glu_fwd(ab2.data_ptr(), hb.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
             _count()
             xq, sx = quantize_fp8_site(hb, E4M3, w, "x")
         else:
-            xq = torch.empty((T, Fh), dtype=torch.uint8, device=ab.device)
-            sx = torch.empty(1, dtype=torch.float32, device=ab.device)
+            xq = _alloc((T, Fh), dtype=torch.uint8, device=ab.device)
+            sx = _alloc(1, dtype=torch.float32, device=ab.device)
             _check(lib.sb_glu_fwd_fp8(ab2.data_ptr(), xq.data_ptr(), T, Fh, act, h.buf.data_ptr(), h.buf.numel(), h.cur,
                                       sx.data_ptr(), _stream()), "glu_fwd_fp8")
             _count()
             h.cur = (h.cur + 1) % h.buf.numel()
         wq, sw = _fp8_weight(w)
-        out = torch.empty((T, w.shape[0]), dtype=bf16, device=ab.device)
+        out = _alloc((T, w.shape[0]), dtype=bf16, device=ab.device)
         r2 = _rows(residual) if residual is not None else None
         gemm_fp8(xq, wq, out, sx, bias=bias, residual=r2, alpha2=sw)
         ctx.save_for_backward(ab2, xq, sx, wq, sw)
@@ -568,7 +649,7 @@ class _GluLinearFP8(torch.autograd.Function):
         gh, gw = _fp8_backward_gemms(ctx.wref, g2, xq, sx, wq, sw, True, ctx.needs_input_grad[2])
         gb = colsum(g2).to(gy.dtype) if (has_bias and ctx.needs_input_grad[3]) else None
         T, F2 = ab2.shape
-        dab = torch.empty_like(ab2)
+        dab = _alloc_like(ab2)
         _check(lib.sb_glu_bwd(ab2.data_ptr(), gh.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
         _count()
         gr = gy if (has_res and ctx.needs_input_grad[4]) else None
@@ -595,30 +676,30 @@ class _MlpFP8(torch.autograd.Function):
             _, _, a, y = _rmsnorm_fwd(x, wn, eps, form)
             xq, sx = quantize_fp8_site(y, E4M3, w12, "x")
         else:
-            xq = torch.empty((T, D), dtype=torch.uint8, device=dev)
-            a = torch.empty(T, dtype=torch.float32, device=dev)
-            sx = torch.empty(1, dtype=torch.float32, device=dev)
+            xq = _alloc((T, D), dtype=torch.uint8, device=dev)
+            a = _alloc(T, dtype=torch.float32, device=dev)
+            sx = _alloc(1, dtype=torch.float32, device=dev)
             _check(lib.sb_rmsnorm_fwd_fp8(x2.data_ptr(), wnc.data_ptr(), xq.data_ptr(), a.data_ptr(), T, D, eps, form,
                                           hx.buf.data_ptr(), hx.buf.numel(), hx.cur, sx.data_ptr(), _stream()), "rmsnorm_fwd_fp8")
             _count()
             hx.cur = (hx.cur + 1) % hx.buf.numel()
         w12q, s12 = _fp8_weight(w12)
-        ab = torch.empty((T, F2), dtype=bf16, device=dev)
+        ab = _alloc((T, F2), dtype=bf16, device=dev)
         gemm_fp8(xq, w12q, ab, sx, alpha2=s12)
         if not hh.primed:
-            hb = torch.empty((T, Fh), dtype=bf16, device=dev)
+            hb = _alloc((T, Fh), dtype=bf16, device=dev)
             _check(lib.sb_glu_fwd(ab.data_ptr(), hb.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
             _count()
             hq, sh = quantize_fp8_site(hb, E4M3, w3, "x")
         else:
-            hq = torch.empty((T, Fh), dtype=torch.uint8, device=dev)
-            sh = torch.empty(1, dtype=torch.float32, device=dev)
+            hq = _alloc((T, Fh), dtype=torch.uint8, device=dev)
+            sh = _alloc(1, dtype=torch.float32, device=dev)
             _check(lib.sb_glu_fwd_fp8(ab.data_ptr(), hq.data_ptr(), T, Fh, act, hh.buf.data_ptr(), hh.buf.numel(), hh.cur,
                                       sh.data_ptr(), _stream()), "glu_fwd_fp8")
             _count()
             hh.cur = (hh.cur + 1) % hh.buf.numel()
         w3q, s3 = _fp8_weight(w3)
-        out = torch.empty((T, w3.shape[0]), dtype=bf16, device=dev)
+        out = _alloc((T, w3.shape[0]), dtype=bf16, device=dev)
         gemm_fp8(hq, w3q, out, sh, bias=b3, residual=x2, alpha2=s3)
         ctx.save_for_backward(x2, wnc, a, xq, sx, w12q, s12, ab, hq, sh, w3q, s3)
         ctx.meta = (eps, form, x.shape, act, b3 is not None)
@@ -638,18 +719,18 @@ class _MlpFP8(torch.autograd.Function):
         gb3 = colsum(g2).to(gy.dtype) if (has_b3 and ctx.needs_input_grad[6]) else None
         hg = _site(w12, "g", dev)
         if not hg.primed:
-            dab = torch.empty_like(ab)
+            dab = _alloc_like(ab)
             _check(lib.sb_glu_bwd(ab.data_ptr(), gh.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
             _count()
             dq, sd = quantize_fp8_site(dab, E5M2, w12, "g")
         else:
-            dq = torch.empty((T, F2), dtype=torch.uint8, device=dev)
-            sd = torch.empty(1, dtype=torch.float32, device=dev)
+            dq = _alloc((T, F2), dtype=torch.uint8, device=dev)
+            sd = _alloc(1, dtype=torch.float32, device=dev)
             _check(lib.sb_glu_bwd_fp8(ab.data_ptr(), gh.data_ptr(), dq.data_ptr(), T, F2 // 2, act, hg.buf.data_ptr(),
                                       hg.buf.numel(), hg.cur, sd.data_ptr(), _stream()), "glu_bwd_fp8")
             _count()
             hg.cur = (hg.cur + 1) % hg.buf.numel()
-        gxn = torch.empty((T, x2.shape[1]), dtype=bf16, device=dev)
+        gxn = _alloc((T, x2.shape[1]), dtype=bf16, device=dev)
         gemm_fp8(dq, w12q, gxn, sd, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=s12)
         gw12 = None
         if ctx.needs_input_grad[4]:
@@ -657,7 +738,7 @@ class _MlpFP8(torch.autograd.Function):
             if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == w12.shape:
                 gemm_fp8(dq, xq, tgt, sd, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, accumulate=True, alpha2=sx)
             else:
-                gw12 = torch.empty(w12.shape, dtype=bf16, device=dev)
+                gw12 = _alloc(w12.shape, dtype=bf16, device=dev)
                 gemm_fp8(dq, xq, gw12, sd, a_mn=True, b_mn=True, a_fmt=E5M2, b_fmt=E4M3, alpha2=sx)
         # the residual branch's gradient (gy itself) is added inside the norm's backward kernel
         dx, dwn = _rmsnorm_bwd(x2, wn, a, gxn, g2, eps, form)
@@ -716,7 +797,7 @@ class _GluPacked(torch.autograd.Function):
         ab2 = ab.reshape(-1, ab.shape[-1]).contiguous()
         T, F2 = ab2.shape
         Fh = F2 // 2
-        h = torch.empty((T, Fh), dtype=bf16, device=ab.device)
+        h = _alloc((T, Fh), dtype=bf16, device=ab.device)
         _check(lib.sb_glu_fwd(ab2.data_ptr(), h.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
         _count()
         ctx.save_for_backward(ab2)
@@ -730,7 +811,7 @@ class _GluPacked(torch.autograd.Function):
         act, shape = ctx.meta
         T, F2 = ab2.shape
         g2 = gh.reshape(T, F2 // 2).contiguous()
-        dab = torch.empty_like(ab2)
+        dab = _alloc_like(ab2)
         _check(lib.sb_glu_bwd(ab2.data_ptr(), g2.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
         _count()
         return dab.view(shape), None
@@ -771,7 +852,7 @@ def _rope_launch(x, cos, sin, inverse):
     if x.stride(3) != 1 or x.stride(1) != H * rs or x.stride(0) != L * H * rs or rs % 8 or x.data_ptr() % 16:
         x = x.contiguous()
         rs = hd
-    y = torch.empty((B, L, H, hd), dtype=bf16, device=x.device)
+    y = _alloc((B, L, H, hd), dtype=bf16, device=x.device)
     _check(lib.sb_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, L, H, hd, cos.shape[-1], rs, hd,
                        inverse, _stream()), "rope")
     _count()
@@ -800,8 +881,8 @@ class _CrossEntropy(torch.autograd.Function):
         l2 = logits.reshape(-1, V).contiguous()
         lab = labels.reshape(-1).contiguous()
         T = l2.shape[0]
-        loss = torch.empty(T, dtype=torch.float32, device=logits.device)
-        lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+        loss = _alloc(T, dtype=torch.float32, device=logits.device)
+        lse = _alloc(T, dtype=torch.float32, device=logits.device)
         _check(lib.sb_ce_fwd(l2.data_ptr(), lab.data_ptr(), loss.data_ptr(), lse.data_ptr(), T, V, _stream()), "ce_fwd")
         _count()
         ctx.save_for_backward(l2, lab, lse)
@@ -814,7 +895,7 @@ class _CrossEntropy(torch.autograd.Function):
         l2, lab, lse = ctx.saved_tensors
         T, V = l2.shape
         gc = g.reshape(-1).float().contiguous()
-        dl = torch.empty_like(l2)
+        dl = _alloc_like(l2)
         _check(lib.sb_ce_bwd(l2.data_ptr(), lab.data_ptr(), lse.data_ptr(), gc.data_ptr(), dl.data_ptr(), T, V, _stream()),
                "ce_bwd")
         _count()
@@ -835,7 +916,7 @@ def sq_norm(x, weight=None):
         xf = x.float()
         return (xf * xf * weight).sum() if weight is not None else (xf * xf).sum()
     lib = require()
-    out = torch.zeros((), dtype=torch.float32, device=x.device)
+    out = _zeros((), dtype=torch.float32, device=x.device)
     _check(lib.sb_sqnorm(x.data_ptr(), _ptr(weight), out.data_ptr(), x.numel(), int(x.dtype == bf16), _stream()), "sqnorm")
     _count()
     return out
@@ -876,10 +957,10 @@ class _DwConv(torch.autograd.Function):
         xc = x.contiguous()
         hc = halo.contiguous() if halo is not None else None
         wf = _f32c(w)
-        y = torch.empty_like(xc)
+        y = _alloc_like(xc)
         _check(lib.sb_dwconv_fwd(xc.data_ptr(), _ptr(hc), wf.data_ptr(), y.data_ptr(), B, L, C, K, _stream()), "dwconv_fwd")
         _count()
-        ctx.save_for_backward(xc, wf, hc if hc is not None else torch.empty(0, device=x.device))
+        ctx.save_for_backward(xc, wf, hc if hc is not None else _alloc(0, device=x.device))
         ctx.meta = (halo is not None, w.dtype)
         return y
 
@@ -891,9 +972,9 @@ class _DwConv(torch.autograd.Function):
         B, L, C = xc.shape
         K = wf.shape[-1]
         g = gy.contiguous()
-        dx = torch.empty_like(xc)
-        dh = torch.empty_like(hc) if has_halo else None
-        dw = torch.zeros_like(wf)
+        dx = _alloc_like(xc)
+        dh = _alloc_like(hc) if has_halo else None
+        dw = _zeros_like(wf)
         _check(lib.sb_dwconv_bwd(xc.data_ptr(), hc.data_ptr() if has_halo else None, wf.data_ptr(), g.data_ptr(),
                                  dx.data_ptr(), _ptr(dh), dw.data_ptr(), B, L, C, K, _stream()), "dwconv_bwd")
         _count()
@@ -917,11 +998,11 @@ class _HyenaSE(torch.autograd.Function):
         fc = feat.contiguous()
         hc = halo.contiguous() if halo is not None else None
         wf = _f32c(w)
-        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        z = _alloc((B, L, D), dtype=bf16, device=feat.device)
         _check(lib.sb_se_fwd(fc.data_ptr(), _ptr(hc), wf.data_ptr(), z.data_ptr(), B, L, D, G, K, int(pregate),
                              int(postgate), _stream()), "se_fwd")
         _count()
-        ctx.save_for_backward(fc, wf, hc if hc is not None else torch.empty(0, device=feat.device))
+        ctx.save_for_backward(fc, wf, hc if hc is not None else _alloc(0, device=feat.device))
         ctx.meta = (halo is not None, w.dtype, pregate, postgate)
         return z
 
@@ -934,9 +1015,9 @@ class _HyenaSE(torch.autograd.Function):
         D = C3 // 3
         G, K = wf.shape
         g = gz.contiguous()
-        df = torch.empty_like(fc)
-        dh = torch.empty_like(hc) if has_halo else None
-        dw = torch.zeros_like(wf)
+        df = _alloc_like(fc)
+        dh = _alloc_like(hc) if has_halo else None
+        dw = _zeros_like(wf)
         _check(lib.sb_se_bwd(fc.data_ptr(), hc.data_ptr() if has_halo else None, wf.data_ptr(), g.data_ptr(), df.data_ptr(),
                              _ptr(dh), dw.data_ptr(), B, L, D, G, K, int(pregate), int(postgate), _stream()), "se_bwd")
         _count()
@@ -964,18 +1045,18 @@ class _HyenaMR(torch.autograd.Function):
         fc = feat.contiguous()
         hc = halo.contiguous() if halo is not None else None
         hf, bf = _f32c(h), _f32c(bias)
-        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        z = _alloc((B, L, D), dtype=bf16, device=feat.device)
         tc = (D // G) % 16 == 0 and D % 8 == 0
         y = None
         if tc:
             _check(lib.sb_mr_tc_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), B, L, D, G, K,
                                     _stream()), "mr_tc_fwd")
         else:
-            y = torch.empty_like(z) if any(ctx.needs_input_grad) else None
+            y = _alloc_like(z) if any(ctx.needs_input_grad) else None
             _check(lib.sb_mr_fwd(fc.data_ptr(), _ptr(hc), hf.data_ptr(), bf.data_ptr(), z.data_ptr(), _ptr(y), B, L, D, G, K,
                                  _stream()), "mr_fwd")
         _count()
-        empty = torch.empty(0, device=feat.device)
+        empty = _alloc(0, device=feat.device)
         ctx.save_for_backward(fc, hf, bf, y if y is not None else empty, hc if hc is not None else empty)
         ctx.meta = (halo is not None, h.dtype, bias.dtype, tc)
         return z
@@ -989,10 +1070,10 @@ class _HyenaMR(torch.autograd.Function):
         D = C3 // 3
         G, K = hf.shape
         g = gz.contiguous()
-        df = torch.empty_like(fc)
-        dhalo = torch.zeros_like(hc) if has_halo else None
-        dh = torch.zeros_like(hf)
-        db = torch.zeros_like(bf)
+        df = _alloc_like(fc)
+        dhalo = _zeros_like(hc) if has_halo else None
+        dh = _zeros_like(hf)
+        db = _zeros_like(bf)
         hp = hc.data_ptr() if has_halo else None
         if tc:
             _check(lib.sb_mr_tc_bwd(fc.data_ptr(), hp, hf.data_ptr(), bf.data_ptr(), g.data_ptr(), df.data_ptr(), _ptr(dhalo),
@@ -1057,17 +1138,17 @@ class _HyenaLI(torch.autograd.Function):
         bf = _f32c(bias)
         sin = None
         if state_in is not None:
-            sin = torch.zeros((B, D, LI_ORDER), dtype=torch.float32, device=feat.device)
+            sin = _zeros((B, D, LI_ORDER), dtype=torch.float32, device=feat.device)
             sin[..., :O] = state_in.detach().float()
         tc = _li_chunk(B, L, D)
         NC = (L + tc - 1) // tc
-        S = torch.empty((B, NC, D, LI_ORDER), dtype=torch.float32, device=feat.device)
-        sout = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=feat.device) if want_state else None
-        z = torch.empty((B, L, D), dtype=bf16, device=feat.device)
+        S = _alloc((B, NC, D, LI_ORDER), dtype=torch.float32, device=feat.device)
+        sout = _alloc((B, D, LI_ORDER), dtype=torch.float32, device=feat.device) if want_state else None
+        z = _alloc((B, L, D), dtype=bf16, device=feat.device)
         _check(lib.sb_li_fwd(fc.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(), _ptr(sin), _ptr(sout), S.data_ptr(),
                              z.data_ptr(), B, L, D, tc, _stream()), "li_fwd")
         _count(3)
-        ctx.save_for_backward(fc, ll, Rp, bf, sin if sin is not None else torch.empty(0, device=feat.device))
+        ctx.save_for_backward(fc, ll, Rp, bf, sin if sin is not None else _alloc(0, device=feat.device))
         ctx.meta = (O, state_in is not None, gamma.dtype, R.dtype, p.dtype, bias.dtype, want_state)
         if want_state:
             return z, sout[..., :O].contiguous()
@@ -1085,16 +1166,16 @@ class _HyenaLI(torch.autograd.Function):
         NC = (L + tc - 1) // tc
         g = gz.contiguous()
         shape = (B, NC, D, LI_ORDER)
-        S, W, A, dRp, dLp = (torch.empty(shape, dtype=torch.float32, device=dev) for _ in range(5))
-        dBp = torch.empty((B, NC, D), dtype=torch.float32, device=dev)
-        tmp = torch.empty((B, L, D), dtype=bf16, device=dev)
-        df = torch.empty_like(fc)
+        S, W, A, dRp, dLp = (_alloc(shape, dtype=torch.float32, device=dev) for _ in range(5))
+        dBp = _alloc((B, NC, D), dtype=torch.float32, device=dev)
+        tmp = _alloc((B, L, D), dtype=bf16, device=dev)
+        df = _alloc_like(fc)
         dso = None
         if want_state and gstate is not None:
-            dso = torch.zeros((B, D, LI_ORDER), dtype=torch.float32, device=dev)
+            dso = _zeros((B, D, LI_ORDER), dtype=torch.float32, device=dev)
             dso[..., :O] = gstate.float()
-        w_end = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=dev) if dso is not None else None
-        dsi = torch.empty((B, D, LI_ORDER), dtype=torch.float32, device=dev) if has_sin else None
+        w_end = _alloc((B, D, LI_ORDER), dtype=torch.float32, device=dev) if dso is not None else None
+        dsi = _alloc((B, D, LI_ORDER), dtype=torch.float32, device=dev) if has_sin else None
         _check(lib.sb_li_bwd(fc.data_ptr(), g.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(),
                              sin.data_ptr() if has_sin else None, _ptr(dso), S.data_ptr(), W.data_ptr(), A.data_ptr(),
                              dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), tmp.data_ptr(), df.data_ptr(), _ptr(w_end),

@@ -14,6 +14,7 @@ import math
 import torch
 
 from . import cuda_ops
+from .cuda_ops import _alloc, _alloc_like, _zeros, _zeros_like
 
 _SIGS_SET = False
 _LL3 = ctypes.c_longlong * 3
@@ -76,8 +77,8 @@ def forward(q, k, v, causal: bool, scale: float):
     lib = _lib()
     B, Lq, H, _ = q.shape
     Lk = k.shape[1]
-    out = torch.empty((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty((B, H, Lq), dtype=torch.float32, device=q.device)
+    out = _alloc((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
+    lse = _alloc((B, H, Lq), dtype=torch.float32, device=q.device)
     rc = lib.sb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, H, Lq, Lk,
                          _str3(q), _str3(k), _str3(v), _str3(out), int(causal), float(scale),
                          cuda_ops.status_word(q.device).data_ptr(), cuda_ops._stream())
@@ -100,13 +101,13 @@ def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_ac
     go = go if _ok_layout(go) else go.contiguous()
     shared = dq_acc is not None
     if not shared:
-        dq_acc = torch.zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
-    stats = torch.empty(2 * B * H * ((Lq + 63) // 64 * 64), dtype=torch.float32, device=q.device)
-    dq = None if shared else torch.empty((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
+        dq_acc = _zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
+    stats = _alloc(2 * B * H * ((Lq + 63) // 64 * 64), dtype=torch.float32, device=q.device)
+    dq = None if shared else _alloc((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
     if dk is None:
-        dk = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
+        dk = _alloc((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     if dv is None:
-        dv = torch.empty((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
+        dv = _alloc((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     if glse is not None:
         glse = glse.contiguous().float()
     rc = lib.sb_attn_bwd(go.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
@@ -134,7 +135,7 @@ class _Flash(torch.autograd.Function):
     def backward(ctx, go, glse):
         q, k, v, out, lse = ctx.saved_tensors
         if go is None:
-            go = torch.zeros_like(out)
+            go = _zeros_like(out)
         dq, dk, dv = backward(go, q, k, v, out, lse, ctx.causal, ctx.scale, glse)
         return dq, dk, dv, None
 
@@ -177,8 +178,8 @@ def merge_forward(os_, lses):
     lib = _lib()
     S = len(os_)
     B, L, H, _ = os_[0].shape
-    out = torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
-    lse = torch.empty((B, H, L), dtype=torch.float32, device=os_[0].device)
+    out = _alloc((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
+    lse = _alloc((B, H, L), dtype=torch.float32, device=os_[0].device)
     optr, lptr, ostr, lstr = _merge_args(os_, lses)
     rc = lib.sb_attn_merge_fwd(optr, lptr, ostr, lstr, S, B, L, H, out.data_ptr(), lse.data_ptr(), cuda_ops._stream())
     if rc != 0:
@@ -196,8 +197,8 @@ class _Merge(torch.autograd.Function):
         os_, lses = ts[:S], ts[S:]
         lib = _lib()
         B, L, H, _ = os_[0].shape
-        out = torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
-        lse = torch.empty((B, H, L), dtype=torch.float32, device=os_[0].device)
+        out = _alloc((B, L, H, 128), dtype=torch.bfloat16, device=os_[0].device)
+        lse = _alloc((B, H, L), dtype=torch.float32, device=os_[0].device)
         optr, lptr, ostr, lstr = _merge_args(os_, lses)
         rc = lib.sb_attn_merge_fwd(optr, lptr, ostr, lstr, S, B, L, H, out.data_ptr(), lse.data_ptr(), cuda_ops._stream())
         if rc != 0:
@@ -219,8 +220,8 @@ class _Merge(torch.autograd.Function):
         B, L, H, _ = out.shape
         if gout.stride(-1) != 1 or any(st % 4 for st in gout.stride()[:3]) or gout.data_ptr() % 8:
             gout = gout.contiguous()
-        gos = [torch.empty((B, L, H, 128), dtype=torch.bfloat16, device=out.device) for _ in range(S)]
-        gls = [torch.empty((B, H, L), dtype=torch.float32, device=out.device) for _ in range(S)]
+        gos = [_alloc((B, L, H, 128), dtype=torch.bfloat16, device=out.device) for _ in range(S)]
+        gls = [_alloc((B, H, L), dtype=torch.float32, device=out.device) for _ in range(S)]
         optr, lptr, ostr, lstr = _merge_args(os_, lses)
         gstr = _LL3(gout.stride(0), gout.stride(1), gout.stride(2))
         goptr = (ctypes.c_void_p * S)(*[t.data_ptr() for t in gos])
