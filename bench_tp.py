@@ -37,7 +37,7 @@ def emulate(a):
     lib = cuda_ops.require()
     P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
     lib.sb_gemm_tp.restype = I
-    lib.sb_gemm_tp.argtypes = [P, I, P, I, I, P, I, P, I, I, I, I, I, P, P, P, I, I, I, I, P, P, P]
+    lib.sb_gemm_tp.argtypes = [P, I, P, I, I, P, I, P, I, I, I, I, I, P, P, I, I, I, I, P, P, P, I, I, I, I, P, P, P]
     lib.sb_zero_reduce_scatter.restype = I
     lib.sb_zero_reduce_scatter.argtypes = [P, I, I, LL, LL, P, P, P, P]
     lib.sb_zero_adam_allgather.restype = I
@@ -77,6 +77,7 @@ def emulate(a):
         def run():
             epoch[0] += 1
             rc = lib.sb_gemm_tp(shards[0].data_ptr(), K, w.data_ptr(), K, 0, out.data_ptr(), N // world, None, L, N // world, K,
+                                1, 2, None, None, 0, 0,
                                 world, 0, ptrs, gather.data_ptr(), flags.data_ptr(), epoch[0], 16, 0, 0, None,
                                 status.data_ptr(), st())
             assert rc == 0, rc
@@ -88,6 +89,27 @@ def emulate(a):
         print(json.dumps({"op": f"F1.ag_gemm.{name}.emulated_1gpu", "slots": world, "ms": round(ms, 4),
                           "tflops": round(fl / ms / 1e9, 1), "frac_of_gemm_peak": round(fl / (ms / 1e3) / peak, 3),
                           "rel_err": round(err, 5)}), flush=True)
+    for name, N, K in (() if a.only_zero else (("in_proj", 3 * D, D), ("mlp_w12", 2 * F_, D))):
+        # the same projection on one-byte e4m3 operands (unit scales: the timing does not depend on them)
+        shards = [torch.randint(0, 120, (l, K), device=dev, dtype=torch.uint8) for _ in range(world)]
+        w = torch.randint(0, 120, (N // world, K), device=dev, dtype=torch.uint8)
+        gather = torch.empty(L * K, dtype=torch.uint8, device=dev)
+        out = torch.empty(L, N // world, dtype=torch.bfloat16, device=dev)
+        ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in shards])
+        one = torch.ones(1, device=dev)
+
+        def run():
+            epoch[0] += 1
+            rc = lib.sb_gemm_tp(shards[0].data_ptr(), K, w.data_ptr(), K, 0, out.data_ptr(), N // world, None, L, N // world, K,
+                                1, 1, one.data_ptr(), one.data_ptr(), 0, 0,
+                                world, 0, ptrs, gather.data_ptr(), flags.data_ptr(), epoch[0], 16, 0, 0, None,
+                                status.data_ptr(), st())
+            assert rc == 0, rc
+        ms = timed(run)
+        cuda_ops.check_status()
+        fl = 2.0 * L * (N // world) * K
+        print(json.dumps({"op": f"F1.ag_gemm.{name}.fp8.emulated_1gpu", "slots": world, "ms": round(ms, 4),
+                          "tflops": round(fl / ms / 1e9, 1), "frac_of_bf16_gemm_peak": round(fl / (ms / 1e3) / peak, 3)}), flush=True)
     for name, N, K in (() if a.only_zero else (("out_proj", D, D), ("mlp_w3", D, F_))):
         x = torch.randn(L, K // world, device=dev).to(torch.bfloat16)
         w = (torch.randn(N, K // world, device=dev) * 0.02).to(torch.bfloat16)
@@ -96,6 +118,7 @@ def emulate(a):
 
         def run():
             rc = lib.sb_gemm_tp(x.data_ptr(), K // world, w.data_ptr(), K // world, 0, None, 0, None, L, N, K // world,
+                                1, 2, None, None, 0, 0,
                                 0, 0, None, None, flags.data_ptr(), 0, 16, world, 0, sp, status.data_ptr(), st())
             assert rc == 0, rc
         ms = timed(run)
@@ -135,6 +158,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=1, help="sequences per launch (micro-batch)")
+    ap.add_argument("--hidden", type=int, default=4096, help="model width (8192 with --ffn 21888 = the 40B shapes)")
+    ap.add_argument("--ffn", type=int, default=11264)
     ap.add_argument("--zero-elems", type=int, default=512 * 1024 * 1024,
                     help="elements of the flat group of the emulated ZeRO kernels (smaller for profiler captures)")
     ap.add_argument("--only-zero", action="store_true", help="emulation: run the ZeRO kernels only")
@@ -151,7 +177,7 @@ def main():
     assert fused_tp.setup()
     peak = float((measured_peaks() or {}).get("bf16_tflops", 1590.0)) * 1e12
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    D, F, L = 4096, 11264, a.seq
+    D, F, L = a.hidden, a.ffn, a.seq
     l = L // world
 
     def timed(fn):
@@ -170,34 +196,41 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def report(name, ms, flops, nvbytes):
-        roof = max(flops / peak, nvbytes / (NVLINK_GBS * 1e9)) * 1e3
+    def report(name, ms, flops, nvbytes, fp8=False):
+        # compute roofline: the measured cuBLAS bf16 burst peak; for one-byte operands twice that (the hardware ratio)
+        roof = max(flops / (peak * (2.0 if fp8 else 1.0)), nvbytes / (NVLINK_GBS * 1e9)) * 1e3
         if rank == 0:
             print(json.dumps({"op": name, "tp": world, "ms": round(ms, 4), "roofline_ms": round(roof, 4),
                               "frac_of_roofline": round(roof / ms, 3), "tflops_per_gpu": round(flops / ms / 1e9, 1),
                               "nvlink_bytes_per_gpu": nvbytes}), flush=True)
 
     ws = fused_tp._WS
+    Bn = a.batch
     for name, N, K in (("in_proj", 3 * D, D), ("mlp_w12", 2 * F, D)):
-        x = torch.randn(1, l, K, device=dev).to(torch.bfloat16)
+        x = torch.randn(Bn, l, K, device=dev).to(torch.bfloat16)
         w = (torch.randn(N // world, K, device=dev) * 0.02).to(torch.bfloat16)
-        fl = 2.0 * L * (N // world) * K
-        nb = (world - 1) * l * K * 2
-        with torch.no_grad():
-            fused_tp._WS = ws
-            report(f"F1.ag_gemm.{name}.fused", timed(lambda: ops.linear_allgather(x, w, None, 1)), fl, nb)
-            fused_tp._WS = None
-            report(f"F1.ag_gemm.{name}.nccl", timed(lambda: ops.linear_allgather(x, w, None, 1)), fl, nb)
+        fl = 2.0 * Bn * L * (N // world) * K
+        for fp8 in (False, True):
+            nb = (world - 1) * Bn * l * K * (1 if fp8 else 2)
+            tag = ".fp8" if fp8 else ""
+            with torch.no_grad():
+                fused_tp._WS = ws
+                report(f"F1.ag_gemm.{name}{tag}.fused", timed(lambda: ops.linear_allgather(x, w, None, 1, fp8=fp8)), fl, nb, fp8)
+                fused_tp._WS = None
+                nbn = (world - 1) * Bn * l * K * 2                     # the NCCL path gathers bf16
+                report(f"F1.ag_gemm.{name}{tag}.nccl", timed(lambda: ops.linear_allgather(x, w, None, 1, fp8=fp8)), fl, nbn, fp8)
     for name, N, K in (("out_proj", D, D), ("mlp_w3", D, F)):
-        x = torch.randn(1, L, K // world, device=dev).to(torch.bfloat16)
+        x = torch.randn(Bn, L, K // world, device=dev).to(torch.bfloat16)
         w = (torch.randn(N, K // world, device=dev) * 0.02).to(torch.bfloat16)
-        fl = 2.0 * L * N * (K // world)
-        nb = (world - 1) * l * N * 2
-        with torch.no_grad():
-            fused_tp._WS = ws
-            report(f"F2.gemm_rs.{name}.fused", timed(lambda: ops.linear_reducescatter(x, w, 1)), fl, nb)
-            fused_tp._WS = None
-            report(f"F2.gemm_rs.{name}.nccl", timed(lambda: ops.linear_reducescatter(x, w, 1)), fl, nb)
+        fl = 2.0 * Bn * L * N * (K // world)
+        nb = (world - 1) * Bn * l * N * 2
+        for fp8 in (False, True):
+            tag = ".fp8" if fp8 else ""
+            with torch.no_grad():
+                fused_tp._WS = ws
+                report(f"F2.gemm_rs.{name}{tag}.fused", timed(lambda: ops.linear_reducescatter(x, w, 1, fp8=fp8)), fl, nb, fp8)
+                fused_tp._WS = None
+                report(f"F2.gemm_rs.{name}{tag}.nccl", timed(lambda: ops.linear_reducescatter(x, w, 1, fp8=fp8)), fl, nb, fp8)
     fused_tp._WS = ws
     from savanna_b200.ops import cuda_ops
     cuda_ops.check_status()

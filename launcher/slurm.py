@@ -7,7 +7,12 @@ launcher/slurm_template.py:16-470, launcher/generate_distributed_launcher.py:35-
   2. `srun` starts one launcher per node — `torchrun` (default, with --max-restarts for relaunch after a failure),
      or one task per GPU with plain `srun` — which run `train.py` with those arguments.
 Options cover NUMA / CPU binding, environment exports (allocator configuration, NCCL settings), an optional
-profiler wrapper and automatic requeue (`--dependency=singleton` chains + relaunch loop).
+profiler wrapper (free-form, or the Nsight Systems preset of the reference's tuner), automatic requeue
+(`--dependency=singleton` chains + relaunch loop), configuration overrides written as an extra YAML file
+(`--override KEY=VALUE`, the reference's launcher/utils.py:341-394), a per-run checkpoint directory used for both `save`
+and `load` so that a requeued job resumes by itself (`--checkpoint-dir`), and the run-time health options
+(`--straggler-interval` turns the straggler report on, `--watchdog-timeout` the per-step watchdog with its heartbeat
+directory under the output directory).
 
     python -m launcher.slurm --job-name evo2 --nodes 2 --gpus-per-node 8 --config-dir configs model.yml data.yml \
         --output job.sbatch
@@ -42,11 +47,41 @@ def sbatch_header(job_name: str, nodes: int, gpus_per_node: int, time_limit: str
     return lines
 
 
+def nsys_command(output: str, warmup_steps: int = 3, num_steps: int = 2, trace: str = "cuda,nvtx,osrt,cudnn,cublas",
+                 gpu_metrics_device: str = "none", cuda_memory_usage: bool = True, capture_range: str = "cudaProfilerApi",
+                 extra: str = "") -> str:
+    """Nsight Systems wrapper in the shape of the reference's tuner preset (tuner/tuner.py:253-290): the capture is
+    bounded by the profiler API range that the training loop opens after `warmup_steps` and closes `num_steps` later
+    (config keys `nsys_warmup_steps` / `nsys_num_steps`)."""
+    return (f"nsys profile -o {shlex.quote(output)}-%q{{SLURM_PROCID}} --trace={trace} --gpu-metrics-device={gpu_metrics_device} "
+            f"--cuda-memory-usage={'true' if cuda_memory_usage else 'false'} --capture-range={capture_range} "
+            f"--capture-range-end=stop --force-overwrite=true --sample=process-tree {extra}").strip()
+
+
+def write_overrides(path: str, overrides: Dict[str, object]) -> str:
+    """YAML file of configuration overrides, handed to launch.py with `--overrides` (it replaces values of the model / data
+    files, which themselves may not set a key twice)."""
+    import yaml
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as fh:
+        yaml.safe_dump(overrides, fh, sort_keys=True)
+    return path
+
+
+def parse_override(kv: str):
+    import yaml
+    k, _, v = kv.partition("=")
+    if not k or not _:
+        raise ValueError(f"override {kv!r} is not KEY=VALUE")
+    return k.strip(), yaml.safe_load(v)
+
+
 def build_script(job_name: str, nodes: int, gpus_per_node: int, repo_dir: str, conf_dir: Optional[str], conf_files: List[str],
                  launcher: str = "torch", time_limit: str = "24:00:00", partition: Optional[str] = None,
                  account: Optional[str] = None, output_dir: str = "logs", env: Optional[Dict[str, str]] = None,
                  max_restarts: int = 0, numa_bind: bool = False, profile_cmd: Optional[str] = None, master_port: int = 29500,
-                 singleton: bool = False, container: Optional[str] = None, python: str = "python") -> str:
+                 singleton: bool = False, container: Optional[str] = None, python: str = "python",
+                 overrides_file: Optional[str] = None) -> str:
     if launcher not in ("torch", "srun"):
         raise ValueError("launcher must be 'torch' (one torchrun per node) or 'srun' (one task per GPU)")
     lines = sbatch_header(job_name, nodes, gpus_per_node, time_limit, partition, account, output_dir, singleton)
@@ -62,6 +97,8 @@ def build_script(job_name: str, nodes: int, gpus_per_node: int, repo_dir: str, c
               'export MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)',
               f"export MASTER_PORT={master_port}", 'TRAIN_ARGS_FILE="$PWD/' + output_dir + '/train_args-$SLURM_JOB_ID.txt"', ""]
     conf = (f"-d {shlex.quote(conf_dir)} " if conf_dir else "") + " ".join(shlex.quote(c) for c in conf_files)
+    if overrides_file:
+        conf += f" --overrides {shlex.quote(overrides_file)}"
     srun_pre = f"srun --container-image={shlex.quote(container)} " if container else "srun "
     lines += ["# step 1: parse the configuration once, on the first node",
               f"{srun_pre}--nodes=1 --ntasks=1 -w \"$MASTER_ADDR\" {python} launch.py train.py {conf} "
@@ -97,12 +134,35 @@ def main(argv=None):
     ap.add_argument("--container", default=None)
     ap.add_argument("--profile-cmd", default=None)
     ap.add_argument("--env", action="append", default=[], help="KEY=VALUE (repeatable)")
+    ap.add_argument("--override", action="append", default=[], metavar="KEY=VALUE", help="configuration override (repeatable)")
+    ap.add_argument("--checkpoint-dir", default=None, help="run directory used as both `save` and `load` (self-resuming requeue)")
+    ap.add_argument("--straggler-interval", type=int, default=0, help="report stragglers every N steps (0 = off)")
+    ap.add_argument("--watchdog-timeout", type=float, default=0.0, help="per-step watchdog deadline in seconds (0 = off)")
+    ap.add_argument("--nsys", action="store_true", help="wrap the workers in the Nsight Systems preset")
+    ap.add_argument("--nsys-warmup-steps", type=int, default=3)
+    ap.add_argument("--nsys-num-steps", type=int, default=2)
     ap.add_argument("--output", default=None)
     a = ap.parse_args(argv)
     env = dict(e.split("=", 1) for e in a.env)
+    over = dict(parse_override(kv) for kv in a.override)
+    if a.checkpoint_dir:
+        over.update({"save": a.checkpoint_dir, "load": a.checkpoint_dir})
+    if a.straggler_interval > 0:
+        over.update({"heimdall_log_straggler": True, "heimdall_log_interval": a.straggler_interval})
+    if a.watchdog_timeout > 0:
+        over.update({"watchdog_step_timeout": a.watchdog_timeout,
+                     "watchdog_heartbeat_dir": os.path.join(a.output_dir, f"heartbeat-{a.job_name}")})
+    profile_cmd = a.profile_cmd
+    if a.nsys:
+        over.update({"nsys_warmup_steps": a.nsys_warmup_steps, "nsys_num_steps": a.nsys_num_steps})
+        profile_cmd = nsys_command(os.path.join(a.output_dir, f"nsys-{a.job_name}"), a.nsys_warmup_steps, a.nsys_num_steps)
+    overrides_file = None
+    if over:
+        overrides_file = f"overrides-{a.job_name}.yml"
+        write_overrides(os.path.join(a.config_dir or ".", overrides_file), over)
     script = build_script(a.job_name, a.nodes, a.gpus_per_node, os.getcwd(), a.config_dir, a.conf_files, a.launcher, a.time,
-                          a.partition, a.account, a.output_dir, env, a.max_restarts, a.numa_bind, a.profile_cmd,
-                          singleton=a.singleton, container=a.container)
+                          a.partition, a.account, a.output_dir, env, a.max_restarts, a.numa_bind, profile_cmd,
+                          singleton=a.singleton, container=a.container, overrides_file=overrides_file)
     if a.output:
         with open(a.output, "w") as fh:
             fh.write(script)

@@ -436,6 +436,9 @@ class GlobalConfig:
         p.add_argument("--sample_input_file", "-i", type=str, default=None)
         p.add_argument("--sample_output_file", "-o", type=str, default=None)
         p.add_argument("--train-args-output", dest="train_args_output", type=str, default=None)
+        p.add_argument("--overrides", type=str, default=None,
+                       help="YAML file of KEY: VALUE pairs that replace values of the configuration files (the files "
+                            "themselves may not set a key twice)")
         a = p.parse_args(argv)
         paths = []
         for f in a.conf_file:
@@ -450,6 +453,14 @@ class GlobalConfig:
             if getattr(a, k) is not None
         }
         over["user_script"] = a.user_script
+        if a.overrides:
+            path = os.path.join(a.conf_dir, a.overrides) if a.conf_dir and not os.path.isabs(a.overrides) \
+                and not os.path.exists(a.overrides) else a.overrides
+            with open(path) as fh:
+                extra = yaml.load(fh, Loader=yaml.FullLoader) or {}
+            if not isinstance(extra, dict):
+                raise ConfigError(f"{path}: an overrides file holds a mapping of keys to values")
+            over = {**extra, **over}
         cfg = cls.from_ymls(paths, overwrite_values=over)
         cfg._train_args_output = a.train_args_output
         return cfg

@@ -317,6 +317,294 @@ li_bwd_apply_rev_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------------------------ tiled kernels
+// The kernels above walk the sequence with 2-byte loads at a stride of a whole row: a warp moves 192 useful bytes per
+// step with 96 load instructions, and the time loop waits on them.  The tiled kernels below (D % 8 == 0) stage
+// [rows x 128 channels] tiles of the interleaved features in shared memory with 16-byte asynchronous copies that are all
+// in flight at once, run the recurrences out of shared memory, and store their outputs as 16-byte chunks.
+//   forward   local / apply: sub-tiles of LT_ROWS steps, double buffered, any chunk length that is a multiple of LT_ROWS
+//   backward  one kernel per chunk of LB_TC steps holds the chunk's features, dz and dx1 in shared memory: the forward
+//             sweep (state, sensitivity: y, dx1, filter-gradient partials) and the reverse sweep (adjoint: du) run back
+//             to back, so dx1 never goes through global memory and the chunk is read once.
+constexpr int LT_ROWS = 16, LT_CH = 128;
+constexpr int LB_TC = 64;
+
+__device__ __forceinline__ void li_cp_async16(void* smem_dst, const void* src, int nbytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(nbytes) : "memory");
+}
+__device__ __forceinline__ void li_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void li_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Stage `rows` feature rows starting at time t_lo (rows beyond t_hi are zero-filled) for channels [c0, c0 + 128) into
+// tile[rows][3 * 128]; chunks of 8 bf16.  `ncv` = number of valid 16-byte chunks per row (channels beyond D: zeros).
+__device__ __forceinline__ void li_stage_feat(bf16 (*tile)[3 * LT_CH], const bf16* feat_b, int t_lo, int t_hi, int rows, int c0,
+                                              int D, int tid, int nthreads) {
+  constexpr int CHK = 3 * LT_CH / 8;                        // 48 chunks per row
+  const int ncv = min(CHK, (3 * (D - c0)) / 8);
+  for (int idx = tid; idx < rows * CHK; idx += nthreads) {
+    const int r = idx / CHK, ch = idx - r * CHK, t = t_lo + r;
+    const bool ok = t < t_hi && ch < ncv;
+    const bf16* src = ok ? feat_b + (size_t)t * 3 * D + 3 * c0 + ch * 8 : feat_b;
+    li_cp_async16(&tile[r][ch * 8], src, ok ? 16 : 0);
+  }
+}
+__device__ __forceinline__ void li_stage_d(bf16 (*tile)[LT_CH], const bf16* g_b, int t_lo, int t_hi, int rows, int c0, int D,
+                                           int tid, int nthreads) {
+  constexpr int CHK = LT_CH / 8;                            // 16 chunks per row
+  const int ncv = min(CHK, (D - c0) / 8);
+  for (int idx = tid; idx < rows * CHK; idx += nthreads) {
+    const int r = idx / CHK, ch = idx - r * CHK, t = t_lo + r;
+    const bool ok = t < t_hi && ch < ncv;
+    const bf16* src = ok ? g_b + (size_t)t * D + c0 + ch * 8 : g_b;
+    li_cp_async16(&tile[r][ch * 8], src, ok ? 16 : 0);
+  }
+}
+
+// pass 1 (tiled): chunk-local end state from a zero state
+__global__ void __launch_bounds__(LT_CH)
+li_local_tiled_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam, float* __restrict__ Sloc, LiDims d) {
+  __shared__ __align__(16) bf16 fS[2][LT_ROWS][3 * LT_CH];
+  const int tid = threadIdx.x, c0 = blockIdx.x * LT_CH, ch = c0 + tid;
+  const int n = blockIdx.y, b = blockIdx.z;
+  const bool live = ch < d.D;
+  float lam[LO], s[LO];
+  if (live) load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = live ? __expf(lam[o]) : 0.f; s[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* fb = feat + (size_t)b * d.L * 3 * d.D;
+  const int ntile = (t1 - t0 + LT_ROWS - 1) / LT_ROWS;
+  li_stage_feat(fS[0], fb, t0, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+  li_cp_commit();
+  for (int k = 0; k < ntile; ++k) {
+    if (k + 1 < ntile) li_stage_feat(fS[(k + 1) & 1], fb, t0 + (k + 1) * LT_ROWS, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+    li_cp_commit();
+    li_cp_wait<1>();
+    __syncthreads();
+    const bf16 (*T)[3 * LT_CH] = fS[k & 1];
+    const int rows = min(LT_ROWS, t1 - (t0 + k * LT_ROWS));
+#pragma unroll 8
+    for (int r = 0; r < rows; ++r) {
+      const float u = b2f(T[r][3 * tid + 1]) * b2f(T[r][3 * tid + 2]);
+#pragma unroll
+      for (int o = 0; o < LO; ++o) s[o] = lam[o] * s[o] + u;
+    }
+    __syncthreads();                                        // the buffer is refilled two iterations from now
+  }
+  if (live) store_vec16(Sloc + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+}
+
+// pass 3 (tiled): rerun each chunk from its entering state and emit z through a staged tile
+__global__ void __launch_bounds__(LT_CH)
+li_apply_tiled_kernel(const bf16* __restrict__ feat, const float* __restrict__ loglam, const float* __restrict__ R,
+                      const float* __restrict__ bias, const float* __restrict__ Sin, bf16* __restrict__ z, LiDims d) {
+  __shared__ __align__(16) bf16 fS[2][LT_ROWS][3 * LT_CH];
+  __shared__ __align__(16) bf16 zS[LT_ROWS][LT_CH];
+  const int tid = threadIdx.x, c0 = blockIdx.x * LT_CH, ch = c0 + tid;
+  const int n = blockIdx.y, b = blockIdx.z;
+  const bool live = ch < d.D;
+  float lam[LO], s[LO], rr[LO];
+  float be = 0.f;
+  if (live) {
+    load_vec16(loglam + (size_t)ch * LO, lam);
+    load_vec16(R + (size_t)ch * LO, rr);
+    load_vec16(Sin + (((size_t)b * d.NC + n) * d.D + ch) * LO, s);
+    be = bias[ch];
+  }
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = live ? __expf(lam[o]) : 0.f; if (!live) { s[o] = 0.f; rr[o] = 0.f; } }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* fb = feat + (size_t)b * d.L * 3 * d.D;
+  bf16* zb = z + (size_t)b * d.L * d.D;
+  const int ntile = (t1 - t0 + LT_ROWS - 1) / LT_ROWS;
+  const int zcv = min(LT_CH / 8, (d.D - c0) / 8);
+  li_stage_feat(fS[0], fb, t0, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+  li_cp_commit();
+  for (int k = 0; k < ntile; ++k) {
+    if (k + 1 < ntile) li_stage_feat(fS[(k + 1) & 1], fb, t0 + (k + 1) * LT_ROWS, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+    li_cp_commit();
+    li_cp_wait<1>();
+    __syncthreads();
+    const bf16 (*T)[3 * LT_CH] = fS[k & 1];
+    const int tt = t0 + k * LT_ROWS, rows = min(LT_ROWS, t1 - tt);
+#pragma unroll 8
+    for (int r = 0; r < rows; ++r) {
+      const float x1 = b2f(T[r][3 * tid]);
+      const float u = b2f(T[r][3 * tid + 1]) * b2f(T[r][3 * tid + 2]);
+      float y = be * u;
+#pragma unroll
+      for (int o = 0; o < LO; ++o) { s[o] = lam[o] * s[o] + u; y += rr[o] * s[o]; }
+      zS[r][tid] = __float2bfloat16_rn(x1 * y);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows * (LT_CH / 8); idx += LT_CH) {
+      const int r = idx / (LT_CH / 8), cv = idx - r * (LT_CH / 8);
+      if (cv < zcv) *reinterpret_cast<uint4*>(zb + (size_t)(tt + r) * d.D + c0 + cv * 8) = *reinterpret_cast<const uint4*>(&zS[r][cv * 8]);
+    }
+    __syncthreads();
+  }
+}
+
+// backward pass B1 (tiled): Sloc, Wloc, Aloc of a chunk (see li_bwd_local_kernel)
+__global__ void __launch_bounds__(LT_CH)
+li_bwd_local_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
+                          const float* __restrict__ R, float* __restrict__ Sloc, float* __restrict__ Wloc,
+                          float* __restrict__ Aloc, LiDims d) {
+  __shared__ __align__(16) bf16 fS[2][LT_ROWS][3 * LT_CH];
+  __shared__ __align__(16) bf16 gS[2][LT_ROWS][LT_CH];
+  const int tid = threadIdx.x, c0 = blockIdx.x * LT_CH, ch = c0 + tid;
+  const int n = blockIdx.y, b = blockIdx.z;
+  const bool live = ch < d.D;
+  float lam[LO], s[LO], w[LO], pw[LO], a[LO];
+  if (live) load_vec16(loglam + (size_t)ch * LO, lam);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = live ? __expf(lam[o]) : 0.f; s[o] = 0.f; w[o] = 0.f; pw[o] = 1.f; a[o] = 0.f; }
+  const int t0 = n * d.TC, t1 = min(t0 + d.TC, d.L);
+  const bf16* fb = feat + (size_t)b * d.L * 3 * d.D;
+  const bf16* gb = dz + (size_t)b * d.L * d.D;
+  const int ntile = (t1 - t0 + LT_ROWS - 1) / LT_ROWS;
+  li_stage_feat(fS[0], fb, t0, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+  li_stage_d(gS[0], gb, t0, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+  li_cp_commit();
+  for (int k = 0; k < ntile; ++k) {
+    if (k + 1 < ntile) {
+      li_stage_feat(fS[(k + 1) & 1], fb, t0 + (k + 1) * LT_ROWS, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+      li_stage_d(gS[(k + 1) & 1], gb, t0 + (k + 1) * LT_ROWS, t1, LT_ROWS, c0, d.D, tid, LT_CH);
+    }
+    li_cp_commit();
+    li_cp_wait<1>();
+    __syncthreads();
+    const bf16 (*T)[3 * LT_CH] = fS[k & 1];
+    const bf16 (*G)[LT_CH] = gS[k & 1];
+    const int rows = min(LT_ROWS, t1 - (t0 + k * LT_ROWS));
+#pragma unroll 4
+    for (int r = 0; r < rows; ++r) {
+      const float u = b2f(T[r][3 * tid + 1]) * b2f(T[r][3 * tid + 2]);
+      const float dy = b2f(G[r][tid]) * b2f(T[r][3 * tid]);
+#pragma unroll
+      for (int o = 0; o < LO; ++o) {
+        w[o] = s[o] + lam[o] * w[o];
+        s[o] = lam[o] * s[o] + u;
+        a[o] += pw[o] * dy;
+        pw[o] *= lam[o];
+      }
+    }
+    __syncthreads();
+  }
+  if (!live) return;
+  float rr[LO];
+  load_vec16(R + (size_t)ch * LO, rr);
+#pragma unroll
+  for (int o = 0; o < LO; ++o) a[o] *= rr[o];
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  store_vec16(Sloc + off, s);
+  store_vec16(Wloc + off, w);
+  store_vec16(Aloc + off, a);
+}
+
+// backward pass B3 + R3 in one kernel (chunk length LB_TC): the chunk's features and dz stay in shared memory between the
+// forward sweep (y, dx1 = dz y into shared memory, partial sums of dR / dlam / dbias) and the reverse sweep (adjoint scan,
+// du; the gradient tile overwrites the feature tile in place and leaves as 16-byte chunks).
+constexpr int LB_SMEM = LB_TC * (3 * LT_CH + LT_CH + LT_CH) * 2;     // features + dz + dx1
+__global__ void __launch_bounds__(LT_CH, 2)
+li_bwd_apply_tiled_kernel(const bf16* __restrict__ feat, const bf16* __restrict__ dz, const float* __restrict__ loglam,
+                          const float* __restrict__ R, const float* __restrict__ bias, const float* __restrict__ Sin,
+                          const float* __restrict__ Win, const float* __restrict__ Ain, bf16* __restrict__ dfeat,
+                          float* __restrict__ dRp, float* __restrict__ dLp, float* __restrict__ dBp,
+                          const float* __restrict__ dstate_out, LiDims d) {
+  extern __shared__ __align__(16) uint8_t li_smem[];
+  bf16 (*fS)[3 * LT_CH] = reinterpret_cast<bf16 (*)[3 * LT_CH]>(li_smem);
+  bf16 (*gS)[LT_CH] = reinterpret_cast<bf16 (*)[LT_CH]>(li_smem + LB_TC * 3 * LT_CH * 2);
+  bf16 (*xS)[LT_CH] = reinterpret_cast<bf16 (*)[LT_CH]>(li_smem + LB_TC * 4 * LT_CH * 2);
+  const int tid = threadIdx.x, c0 = blockIdx.x * LT_CH, ch = c0 + tid;
+  const int n = blockIdx.y, b = blockIdx.z;
+  const bool live = ch < d.D;
+  const int t0 = n * LB_TC, t1 = min(t0 + LB_TC, d.L), rows = t1 - t0;
+  const bf16* fb = feat + (size_t)b * d.L * 3 * d.D;
+  const bf16* gb = dz + (size_t)b * d.L * d.D;
+  li_stage_feat(fS, fb, t0, t1, LB_TC, c0, d.D, tid, LT_CH);
+  li_stage_d(gS, gb, t0, t1, LB_TC, c0, d.D, tid, LT_CH);
+  li_cp_commit();
+  float lam[LO], rr[LO];
+  float be = 0.f;
+  const size_t off = (((size_t)b * d.NC + n) * d.D + ch) * LO;
+  if (live) { load_vec16(loglam + (size_t)ch * LO, lam); load_vec16(R + (size_t)ch * LO, rr); be = bias[ch]; }
+#pragma unroll
+  for (int o = 0; o < LO; ++o) { lam[o] = live ? __expf(lam[o]) : 0.f; if (!live) rr[o] = 0.f; }
+  li_cp_wait<0>();
+  __syncthreads();
+  {
+    // ---- forward sweep
+    float s[LO], w[LO], dr[LO], dl[LO];
+    if (live) { load_vec16(Sin + off, s); load_vec16(Win + off, w); }
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { dr[o] = 0.f; dl[o] = 0.f; if (!live) { s[o] = 0.f; w[o] = 0.f; } }
+    float db = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < rows; ++r) {
+      const float x1 = b2f(fS[r][3 * tid]);
+      const float u = b2f(fS[r][3 * tid + 1]) * b2f(fS[r][3 * tid + 2]);
+      const float gz = b2f(gS[r][tid]);
+      const float dy = gz * x1;
+      float y = be * u;
+#pragma unroll
+      for (int o = 0; o < LO; ++o) {
+        w[o] = s[o] + lam[o] * w[o];
+        s[o] = lam[o] * s[o] + u;
+        y += rr[o] * s[o];
+        dr[o] += dy * s[o];
+        dl[o] += dy * w[o];
+      }
+      db += dy * u;
+      xS[r][tid] = __float2bfloat16_rn(gz * y);
+    }
+    if (live) {
+#pragma unroll
+      for (int o = 0; o < LO; ++o) dl[o] *= rr[o];
+      store_vec16(dRp + off, dr);
+      store_vec16(dLp + off, dl);
+      dBp[((size_t)b * d.NC + n) * d.D + ch] = db;
+    }
+  }
+  {
+    // ---- reverse sweep (each thread touches only its own three tile entries: no barrier needed in between)
+    float a[LO], gs[LO];
+    if (live) load_vec16(Ain + off, a);
+    const bool tail = dstate_out != nullptr && n == d.NC - 1 && live;
+    if (tail) load_vec16(dstate_out + ((size_t)b * d.D + ch) * LO, gs);
+#pragma unroll
+    for (int o = 0; o < LO; ++o) { if (!live) a[o] = 0.f; if (!tail) gs[o] = 0.f; }
+#pragma unroll 4
+    for (int r = rows - 1; r >= 0; --r) {
+      const float x1 = b2f(fS[r][3 * tid]), x2 = b2f(fS[r][3 * tid + 1]), v = b2f(fS[r][3 * tid + 2]);
+      const float dy = b2f(gS[r][tid]) * x1;
+      float du = be * dy;
+#pragma unroll
+      for (int o = 0; o < LO; ++o) a[o] = rr[o] * dy + lam[o] * a[o];
+      if (tail && r == rows - 1) {
+#pragma unroll
+        for (int o = 0; o < LO; ++o) a[o] += gs[o];
+      }
+#pragma unroll
+      for (int o = 0; o < LO; ++o) du += a[o];
+      fS[r][3 * tid] = xS[r][tid];
+      fS[r][3 * tid + 1] = __float2bfloat16_rn(du * v);
+      fS[r][3 * tid + 2] = __float2bfloat16_rn(du * x2);
+    }
+  }
+  __syncthreads();
+  constexpr int CHK = 3 * LT_CH / 8;
+  const int ncv = min(CHK, (3 * (d.D - c0)) / 8);
+  bf16* db_ = dfeat + (size_t)b * d.L * 3 * d.D;
+  for (int idx = tid; idx < rows * CHK; idx += LT_CH) {
+    const int r = idx / CHK, cv = idx - r * CHK;
+    if (cv < ncv) *reinterpret_cast<uint4*>(db_ + (size_t)(t0 + r) * 3 * d.D + 3 * c0 + cv * 8) = *reinterpret_cast<const uint4*>(&fS[r][cv * 8]);
+  }
+}
+
+static int g_li_tiled = 1;
+
 // ------------------------------------------------------------------------------------ context parallel: all-to-all inside the scan
 // Sequence-sharded ranks (zigzag: rank r holds natural chunks r and 2cp-1-r of `chunk_len` rows, [B, l, Dtot] with
 // l = 2 chunk_len) switch to a channel-sharded scan over the whole sequence (this rank: d = Dtot / cp channels) and back.
@@ -592,12 +880,24 @@ extern "C" int sb_li_fwd(const void* feat, const float* loglam, const float* R, 
   if (B * L == 0) return 0;
   LiDims d = li_dims(B, L, D, TC);
   dim3 grid((D + LI_THREADS - 1) / LI_THREADS, d.NC, B);
-  li_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, S_scratch, d);
   const size_t n = (size_t)B * D * LO;
+  if (g_li_tiled && D % 8 == 0 && TC % LT_ROWS == 0) {
+    li_local_tiled_kernel<<<grid, LT_CH, 0, st>>>((const bf16*)feat, loglam, S_scratch, d);
+    li_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S_scratch, loglam, state_in, state_out, d);
+    li_apply_tiled_kernel<<<grid, LT_CH, 0, st>>>((const bf16*)feat, loglam, R, bias, S_scratch, (bf16*)z, d);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
+  li_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, S_scratch, d);
   li_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S_scratch, loglam, state_in, state_out, d);
   li_apply_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, loglam, R, bias, S_scratch, (bf16*)z, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// 1 (default): shared-memory tiled scan kernels where the shape allows; 0: the per-thread streaming kernels
+extern "C" int sb_li_set_variant(int tiled) { sb::g_li_tiled = tiled ? 1 : 0; return 0; }
+// Chunk length the backward pass uses for a given forward choice: the tiled backward keeps a whole chunk in shared memory
+// and therefore fixes its own chunk length; callers size the scratch arrays with the value returned here.
+extern "C" int sb_li_bwd_chunk(int D, int TC) { return (sb::g_li_tiled && D % 8 == 0) ? sb::LB_TC : TC; }
 
 // Scratch: S, W, A, dRp, dLp each B*NC*D*16 floats; dBp B*NC*D floats; dx1_tmp B*L*D bf16.
 // Outputs: dfeat; per-chunk partials dRp/dLp/dBp (the caller sums over B and NC); w_end, dstate_in optional.
@@ -608,8 +908,20 @@ extern "C" int sb_li_bwd(const void* feat, const void* dz, const float* loglam, 
   if (B * L == 0) return 0;
   LiDims d = li_dims(B, L, D, TC);
   dim3 grid((D + LI_THREADS - 1) / LI_THREADS, d.NC, B);
-  li_bwd_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, S, W, A, d);
   const size_t n = (size_t)B * D * LO;
+  if (g_li_tiled && D % 8 == 0 && TC == LB_TC) {
+    static bool attr = false;
+    if (!attr) {
+      if (cudaFuncSetAttribute(li_bwd_apply_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LB_SMEM) != cudaSuccess) return -5;
+      attr = true;
+    }
+    li_bwd_local_tiled_kernel<<<grid, LT_CH, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, S, W, A, d);
+    li_bwd_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, W, A, loglam, state_in, dstate_out, w_end, dstate_in, d);
+    li_bwd_apply_tiled_kernel<<<grid, LT_CH, LB_SMEM, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, S, W, A,
+                                                           (bf16*)dfeat, dRp, dLp, dBp, dstate_out, d);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
+  li_bwd_local_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, S, W, A, d);
   li_bwd_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(S, W, A, loglam, state_in, dstate_out, w_end, dstate_in, d);
   li_bwd_apply_fwd_kernel<<<grid, LI_THREADS, 0, st>>>((const bf16*)feat, (const bf16*)dz, loglam, R, bias, S, W,
                                                       (bf16*)dx1_tmp, dRp, dLp, dBp, d);

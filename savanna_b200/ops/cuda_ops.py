@@ -81,6 +81,8 @@ class _Sig:
     sb_conv_set_fwd_variant = [I]
     sb_mr_tc_bwd = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
     sb_li_fwd = [P, P, P, P, P, P, P, P, I, I, I, I, P]
+    sb_li_set_variant = [I]
+    sb_li_bwd_chunk = [I, I]
     sb_li_bwd = [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]
 
 
@@ -1101,6 +1103,14 @@ LI_ORDER = 16
 
 
 LI_CHUNK_OVERRIDE = None      # tests set this to exercise a chunk length that their small shapes would not select
+LI_TILED = True
+
+
+def set_li_variant(tiled: bool) -> None:
+    """True (default): shared-memory tiled scan kernels; False: the per-thread streaming kernels (A/B measurements, tests)."""
+    global LI_TILED
+    LI_TILED = bool(tiled)
+    require().sb_li_set_variant(int(LI_TILED))
 
 
 def _li_chunk(B: int, L: int, D: int) -> int:
@@ -1162,13 +1172,16 @@ class _HyenaLI(torch.autograd.Function):
         B, L, C3 = fc.shape
         D = C3 // 3
         dev = fc.device
-        tc = _li_chunk(B, L, D)
+        # the shared-memory tiled backward keeps a whole chunk on chip and fixes the chunk length itself
+        tc_fwd = _li_chunk(B, L, D)
+        tc = int(lib.sb_li_bwd_chunk(D, tc_fwd))
         NC = (L + tc - 1) // tc
         g = gz.contiguous()
         shape = (B, NC, D, LI_ORDER)
         S, W, A, dRp, dLp = (_alloc(shape, dtype=torch.float32, device=dev) for _ in range(5))
         dBp = _alloc((B, NC, D), dtype=torch.float32, device=dev)
-        tmp = _alloc((B, L, D), dtype=bf16, device=dev)
+        tiled = tc != tc_fwd
+        tmp = None if tiled else _alloc((B, L, D), dtype=bf16, device=dev)     # dx1 round trip of the streaming kernels only
         df = _alloc_like(fc)
         dso = None
         if want_state and gstate is not None:
@@ -1178,7 +1191,7 @@ class _HyenaLI(torch.autograd.Function):
         dsi = _alloc((B, D, LI_ORDER), dtype=torch.float32, device=dev) if has_sin else None
         _check(lib.sb_li_bwd(fc.data_ptr(), g.data_ptr(), ll.data_ptr(), Rp.data_ptr(), bf.data_ptr(),
                              sin.data_ptr() if has_sin else None, _ptr(dso), S.data_ptr(), W.data_ptr(), A.data_ptr(),
-                             dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), tmp.data_ptr(), df.data_ptr(), _ptr(w_end),
+                             dRp.data_ptr(), dLp.data_ptr(), dBp.data_ptr(), _ptr(tmp), df.data_ptr(), _ptr(w_end),
                              _ptr(dsi), B, L, D, tc, _stream()), "li_bwd")
         _count(4)
         dR = dRp.sum((0, 1))[:, :O]

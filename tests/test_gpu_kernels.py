@@ -333,8 +333,16 @@ def li_chunk(request):
     cuda_ops.LI_CHUNK_OVERRIDE = None
 
 
+@pytest.fixture(params=[True, False], ids=["tiled", "streaming"])
+def li_variant(request):
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.set_li_variant(request.param)
+    yield request.param
+    cuda_ops.set_li_variant(True)
+
+
 @pytest.mark.parametrize("L,O,state", [(512, 16, False), (300, 8, False), (384, 16, True), (1300, 16, True)])
-def test_hyena_li(L, O, state, li_chunk):
+def test_hyena_li(L, O, state, li_chunk, li_variant):
     torch.manual_seed(13)
     B, D = 2, 128
     feat = (torch.randn(B, L, 3 * D, device=DEV) * 0.7).to(BF).requires_grad_()

@@ -1,4 +1,4 @@
-"""Tiny StripedHyena 2 on CPU (BASELINE config 1): trains, is deterministic, checkpoints and resumes."""
+"""Tiny StripedHyena 2 on CPU (configs/baseline/tiny_sh2_cpu.yml): trains, is deterministic, checkpoints and resumes."""
 import os
 
 import pytest
@@ -54,7 +54,7 @@ def test_loss_decreases_and_is_deterministic():
 
 
 def test_golden_loss_trace():
-    """The 10-step loss trace of BASELINE config 1 (seed 0) stays what it was when first recorded."""
+    """The 10-step loss trace of the tiny CPU model (seed 0) stays what it was when first recorded."""
     cfg = _cfg()
     tr = Trainer(cfg, load=False)
     d = _iter(cfg)

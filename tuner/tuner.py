@@ -1,7 +1,8 @@
 """Throughput tuner: generates the grid of (micro batch, accumulation, tensor / context parallel size,
 activation-checkpoint interval, ZeRO stage) variants of a base config that fit a GPU count, with one SLURM
-script per variant or a job array, and collects the `tokens/s/gpu` lines of their logs into a table
-(reference: tuner/tuner.py:34-218, tuner/utils.py:81-200).
+script per variant or ONE job-array script (`--array`: task i runs variant i, `--array-parallel` bounds how many run at
+once), optionally wrapped in the Nsight Systems preset (`--nsys`), and collects the `tokens/s/gpu` lines of their logs
+into a table (reference: tuner/tuner.py:34-340, tuner/utils.py:81-200).
 
     python -m tuner.tuner generate --base configs/baseline/evo2_7b_8k.yml --gpus 8 --out tuner_runs \
         --micro-batch 1 2 --tp 1 2 --checkpoint-num-layers 0 2 4
@@ -54,11 +55,32 @@ def cmd_generate(a):
         with open(path, "w") as fh:
             yaml.safe_dump(cfg, fh, sort_keys=False)
         names.append(tag)
-    from launcher.slurm import build_script
+    from launcher.slurm import build_script, nsys_command
     nodes = max(1, a.gpus // a.gpus_per_node)
+    logs = os.path.join(a.out, "logs")
+    prof = nsys_command(os.path.join(logs, "nsys-$TAG"), a.nsys_warmup_steps, a.nsys_num_steps) if a.nsys else None
+    if a.array and names:
+        # one script for all variants: the array index selects the configuration file
+        with open(os.path.join(a.out, "variants.txt"), "w") as fh:
+            fh.write("\n".join(names) + "\n")
+        script = build_script("tune", nodes, min(a.gpus, a.gpus_per_node), os.getcwd(), os.path.join(a.out, "configs"),
+                              ["$TAG.yml"], output_dir=logs, time_limit=a.time, profile_cmd=prof)
+        head, _, body = script.partition("\n\nset -euo pipefail")
+        limit = f"%{a.array_parallel}" if a.array_parallel else ""
+        head += f"\n#SBATCH --array=0-{len(names) - 1}{limit}"
+        head = head.replace("%x-%j", "%x-%A_%a")
+        pick = f'\nTAG=$(sed -n "$((SLURM_ARRAY_TASK_ID + 1))p" {os.path.join(a.out, "variants.txt")})\nexport TAG'
+        body = body.replace("'$TAG.yml'", '"$TAG.yml"')
+        with open(os.path.join(a.out, "array.sbatch"), "w") as fh:
+            fh.write(head + "\n\nset -euo pipefail" + pick + body)
+        with open(os.path.join(a.out, "submit_all.sh"), "w") as fh:
+            fh.write(f"#!/bin/bash\nsbatch {os.path.join(a.out, 'array.sbatch')}\n")
+        print(f"generated {len(names)} variants under {a.out} as one job array")
+        return
     for tag in names:
         script = build_script(f"tune_{tag}", nodes, min(a.gpus, a.gpus_per_node), os.getcwd(), os.path.join(a.out, "configs"),
-                              [f"{tag}.yml"], output_dir=os.path.join(a.out, "logs"), time_limit=a.time)
+                              [f"{tag}.yml"], output_dir=logs, time_limit=a.time,
+                              profile_cmd=prof.replace("$TAG", tag) if prof else None)
         with open(os.path.join(a.out, f"{tag}.sbatch"), "w") as fh:
             fh.write(script)
     with open(os.path.join(a.out, "submit_all.sh"), "w") as fh:
@@ -95,6 +117,11 @@ def main(argv=None):
     g.add_argument("--global-batch", type=int, default=None)
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--time", default="00:30:00")
+    g.add_argument("--array", action="store_true", help="one SLURM job array instead of one script per variant")
+    g.add_argument("--array-parallel", type=int, default=0, help="at most this many array tasks at once (0 = no limit)")
+    g.add_argument("--nsys", action="store_true", help="wrap the workers in the Nsight Systems preset")
+    g.add_argument("--nsys-warmup-steps", type=int, default=3)
+    g.add_argument("--nsys-num-steps", type=int, default=2)
     g.set_defaults(fn=cmd_generate)
     c = sub.add_parser("collect")
     c.add_argument("--logs", required=True)
