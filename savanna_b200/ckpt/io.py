@@ -87,6 +87,19 @@ def _split_by_layer(module_sd: Dict) -> Dict[int, Dict]:
     return out
 
 
+def _zero_rank(trainer) -> int:
+    """Index of this rank's optimizer shard in the file names: its position in the partition group (with MiCS sharding
+    that is the sub-group, whose replicas all hold the same shards)."""
+    opt = trainer.optimizer
+    if getattr(opt, "replica_world", 1) > 1:
+        return opt.rank
+    return state.get_sequence_data_parallel_rank()
+
+
+def _writes_optimizer(trainer) -> bool:
+    return getattr(trainer.optimizer, "replica_index", 0) == 0          # replicas of a MiCS sub-group hold identical shards
+
+
 def _barrier():
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
@@ -211,7 +224,9 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
     tp_rank = state.get_model_parallel_rank()
     mp_rank = _model_rank()
     pp = state.get_pipe_parallel_world_size()
-    zero_rank = state.get_sequence_data_parallel_rank()
+    zero_rank = _zero_rank(trainer)
+    if not _writes_optimizer(trainer):
+        zero_rank = -1 - zero_rank                # a replica of a MiCS sub-group: takes part in collectives, writes nothing
     bf16 = cfg.precision == "bfloat16"
     finalize_async_save(True)
     if _rank() == 0:
@@ -250,7 +265,7 @@ def save_checkpoint(trainer, iteration: Optional[int] = None) -> str:
         }
         ms.update(_client_state(trainer))
         files[os.path.join(d, model_states_name(mp_rank))] = ms
-    if not cfg.no_save_optim and hasattr(trainer.optimizer, "state_dict"):
+    if not cfg.no_save_optim and hasattr(trainer.optimizer, "state_dict") and _writes_optimizer(trainer):
         files[os.path.join(d, optim_states_name(zero_rank, mp_rank, bf16))] = {
             "optimizer_state_dict": trainer.optimizer.state_dict(),
             "ds_config": cfg.engine_config,
@@ -336,7 +351,7 @@ def load_checkpoint(trainer, iteration: Optional[int] = None) -> int:
     d = checkpoint_dir(load_dir, it)
     tp_rank = state.get_model_parallel_rank()
     mp_rank = _model_rank()
-    zero_rank = state.get_sequence_data_parallel_rank()
+    zero_rank = _zero_rank(trainer)
     path = os.path.join(d, model_states_name(mp_rank))
     if not os.path.isfile(path):
         raise FileNotFoundError(f"checkpoint file {path} not found")

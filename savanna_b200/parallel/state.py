@@ -218,3 +218,27 @@ def get_group_ranks(name: str) -> List[int]:
 
 def device() -> torch.device:
     return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
+def create_mics_groups(shard_size: int):
+    """Split the sequence-data-parallel group into contiguous sub-groups of `shard_size` ranks (state is partitioned
+    inside a sub-group) and the transposed replica groups (ranks holding the same shard).  Every rank calls this (the
+    group constructors are collective).  Returns (shard group, shard ranks, replica group, replica ranks) of this rank."""
+    ranks = get_sequence_data_parallel_ranks()
+    n = len(ranks)
+    if shard_size <= 0 or n % shard_size:
+        raise ValueError(f"mics_shard_size {shard_size} does not divide the data-parallel size {n}")
+    me = dist.get_rank() if _is_dist() else 0
+    mine = None
+    for s0 in range(0, n, shard_size):
+        rs = ranks[s0:s0 + shard_size]
+        g = dist.new_group(rs) if _is_dist() else None
+        if me in rs:
+            mine = (g, rs)
+    rep = None
+    for off in range(shard_size):
+        rs = ranks[off::shard_size]
+        g = dist.new_group(rs) if _is_dist() else None
+        if me in rs:
+            rep = (g, rs)
+    return mine[0], mine[1], rep[0], rep[1]

@@ -152,7 +152,7 @@ class PartitionedZeroOptimizer:
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = True,
                  clip_grad: float = 0.0, group=None, group_ranks: Optional[List[int]] = None,
                  grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
-                 sum_ranks: Optional[int] = None):
+                 sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
         self.stage = stage
@@ -161,7 +161,12 @@ class PartitionedZeroOptimizer:
         self.world = len(ranks)
         me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
         self.rank = ranks.index(me) if me in ranks else 0
-        self.reduce_world = self.world
+        # MiCS-style sharding (`zero_use_mics` + `mics_shard_size`): states are partitioned over a sub-group of the
+        # replicas (`group`, e.g. the GPUs of one node) and replicated across `replica_group` (the ranks that hold the
+        # same shard in the other sub-groups); a shard's gradient is reduce-scattered inside the sub-group and then
+        # all-reduced over the replica group, parameters are gathered inside the sub-group only.
+        self.replica_group, self.replica_world, self.replica_index = replica_group, max(1, replica_world), replica_index
+        self.reduce_world = self.world * self.replica_world
         # context-parallel ranks hold partial gradients of one replica (summed); replicas are averaged
         self.sum_ranks = int(sum_ranks) if sum_ranks else state.get_context_parallel_world_size()
         if self.reduce_world % max(1, self.sum_ranks) != 0:
@@ -311,6 +316,8 @@ class PartitionedZeroOptimizer:
             work, f, shard = self.pending.pop(0)
             if work is not None:
                 work.wait()
+            if self.replica_world > 1:
+                dist.all_reduce(shard, group=self.replica_group)      # the same shard of the other sub-groups
             f.grad_acc.add_(shard)
             if f.free_grads:
                 f.free_grad_buffer()

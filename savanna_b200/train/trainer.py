@@ -160,12 +160,19 @@ class Trainer:
             if cfg.zero_stage >= 2 and len(zranks) >= 1 and hasattr(model, "blocks") \
                     and not getattr(model, "is_pipeline_stage", False):
                 from ..parallel.zero_partitioned import PartitionedZeroOptimizer
+                zgroup, mics = state.get_sequence_data_parallel_group(), {}
+                shard = int((cfg.zero_optimization or {}).get("mics_shard_size", 0) or 0)
+                if cfg.zero_use_mics and 0 < shard < len(zranks):
+                    zgroup, zranks, rgroup, rranks = state.create_mics_groups(shard)
+                    me = dist.get_rank() if dist.is_initialized() else 0
+                    mics = {"replica_group": rgroup, "replica_world": len(rranks), "replica_index": rranks.index(me)}
+                    print_rank_0(f" > MiCS: optimizer state sharded over sub-groups of {shard} ranks, {len(rranks)} replicas")
                 optimizer = PartitionedZeroOptimizer(
                     groups, model.blocks(), stage=min(3, cfg.zero_stage), lr=cfg.lr,
                     betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8), weight_decay=cfg.weight_decay,
                     adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
-                    group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
-                    sync_replicated=bool(cfg.sequence_parallel))
+                    group=zgroup, group_ranks=zranks,
+                    sync_replicated=bool(cfg.sequence_parallel), **mics)
                 rep = optimizer.memory_report()
                 print_rank_0(f" > ZeRO stage {optimizer.stage}: {rep['persistent_bytes'] / 2**20:.0f} MiB of shards and "
                              f"optimizer state per rank, largest unit {rep['largest_unit_param_bytes'] / 2**20:.0f} MiB "

@@ -305,6 +305,38 @@ def test_zero23_data_parallel_equivalence(stage, ckpt_layers, tmp_path):
 
 
 @pytest.mark.slow
+@pytest.mark.parametrize("stage", [2, 3])
+def test_zero_mics_subgroup_sharding(stage, tmp_path):
+    """4 replicas, optimizer state sharded over sub-groups of 2 (MiCS) and replicated across the two sub-groups: the loss
+    trace equals the single-process run, and the checkpoint holds one set of shards (2 optimizer files), which reloads."""
+    ref_losses = _reference_losses(mb=4)
+    over = {"train_micro_batch_size_per_gpu": 1, "zero_use_mics": True,
+            "zero_optimization": {"stage": stage, "mics_shard_size": 2}}
+    run_distributed(_w_mics, 4, over, ref_losses, str(tmp_path))
+
+
+def _w_mics(rank, world, over, ref_losses, tmp):
+    import os
+    from savanna_b200.ckpt import load_checkpoint, save_checkpoint
+    cfg = _tiny_cfg(world, save=tmp, **over)
+    tr, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    opt = tr.optimizer
+    assert opt.world == 2 and opt.replica_world == 2 and opt.reduce_world == 4
+    d = save_checkpoint(tr)
+    dist.barrier()
+    files = sorted(f for f in os.listdir(d) if f.endswith("optim_states.pt"))
+    assert files == ["zero_pp_rank_0_mp_rank_00_optim_states.pt", "zero_pp_rank_1_mp_rank_00_optim_states.pt"], files
+    before = [p.detach().clone() for p in tr.model.parameters()] if opt.stage == 2 else None
+    cfg.load = tmp
+    load_checkpoint(tr)
+    if before is not None:
+        for a, b in zip(before, tr.model.parameters()):
+            assert torch.equal(a, b)
+
+
+@pytest.mark.slow
 def test_zero3_with_tensor_parallel():
     """Stage 3 over a one-rank partition group beside tp=2 + sequence parallelism (replicated-parameter gradients are
     summed per unit) reproduces the loss trace."""
