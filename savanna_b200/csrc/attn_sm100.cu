@@ -383,8 +383,9 @@ constexpr int BWD_SMEM = 2 * TILE_BYTES + 4 * QTILE_BYTES + 4 * PT_BYTES + STAGE
 
 struct BwdParams {
   const float* stats;        // [B, H, Lpad, 2]: (-lse * log2(e), scale * (rowsum(dO * O) - dlse)), Lpad = 64 * ceil(Lq / 64)
-  __nv_bfloat16* dk;         // [B, Lk, H, 128] contiguous
+  __nv_bfloat16* dk;         // [B, Lk, H, 128]; element strides of (batch, key, head) in dk_str / dv_str, unit inner stride
   __nv_bfloat16* dv;
+  long long dk_str[3], dv_str[3];
   int B, H, Lq, Lk;
   int causal;
   float scale_log2, scale;
@@ -644,7 +645,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok && mbar_wait(dkv_done, 0u, abort_flag, p.status, ST_ATTN + 24)) {
       tc_fence_after();
       // warpgroup 0 stores dV, warpgroup 1 stores dK: one key row (256 bytes) per thread
-      __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + (((long long)b * p.Lk + key) * p.H + h) * HD;
+      const long long* ds = wg == 0 ? p.dv_str : p.dk_str;
+      __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + (long long)b * ds[0] + (long long)key * ds[1] + (long long)h * ds[2];
       const uint32_t t_src = tmem_base + lane_off + (wg == 0 ? T_DV : T_DK);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
@@ -803,8 +805,8 @@ extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* ou
 extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const void* v, const void* out, const float* lse,
                            const float* glse, float* stats, float* dq_acc, void* dq, void* dk, int B, int H, int Lq, int Lk,
                            void* dv, const long long* g_str, const long long* q_str, const long long* k_str,
-                           const long long* v_str, const long long* o_str, const long long* dq_str, int causal, float scale,
-                           unsigned int* status, cudaStream_t stream) {
+                           const long long* v_str, const long long* o_str, const long long* dq_str, const long long* dk_str,
+                           const long long* dv_str, int causal, float scale, unsigned int* status, cudaStream_t stream) {
   using namespace sb;
   using namespace sb::attn;
   if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0) return 0;
@@ -814,7 +816,8 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(go) | reinterpret_cast<uintptr_t>(dq_acc) |
        reinterpret_cast<uintptr_t>(stats)) & 15) return -4;
-  for (int i = 0; i < 3; ++i) if ((dq_str[i] % 8) || (o_str[i] % 8) || (g_str[i] % 8)) return -4;
+  for (int i = 0; i < 3; ++i)
+    if ((dq_str[i] % 8) || (o_str[i] % 8) || (g_str[i] % 8) || (dk_str[i] % 8) || (dv_str[i] % 8)) return -4;
   CUtensorMap tq, tk, tv, tg, tdq;
   int rc;
   if ((rc = make_tmap(&tq, q, B, Lq, H, q_str[0], q_str[1], q_str[2], BQ2))) return rc;
@@ -844,7 +847,8 @@ extern "C" int sb_attn_bwd(const void* go, const void* q, const void* k, const v
   attn_stats_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)go, (const __nv_bfloat16*)out, lse, glse, stats, B, H, Lq, lpad, scale, g_str[0], g_str[1], g_str[2],
       o_str[0], o_str[1], o_str[2]);
-  BwdParams p{stats, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), B, H, Lq, Lk,
+  BwdParams p{stats, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv),
+              {dk_str[0], dk_str[1], dk_str[2]}, {dv_str[0], dv_str[1], dv_str[2]}, B, H, Lq, Lk,
               causal, scale * 1.4426950408889634f, scale, status};
   dim3 grid((Lk + BK - 1) / BK, H, B);
   if (g_p_tmem) attn_bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tg, tdq, p);

@@ -48,11 +48,17 @@ class SelfAttention(nn.Module):
     def forward(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         B, L, _ = qkv.shape
         qkv = qkv.view(B, L, self.heads, 3 * self.hd)
-        q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+        cp = state.get_context_parallel_world_size()
+        cos = sin = None
         if self._rotary:
             cos, sin = self._rotary[0](positions)
+        if cp == 1 or self.operator_type not in ("ring", "flash_te"):
+            o = ops.attention_packed(qkv, cos, sin, self.causal)      # one function: no slice / concatenate in autograd
+            if o is not None:
+                return o.reshape(B, L, self.heads * self.hd)
+        q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+        if self._rotary:
             q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
-        cp = state.get_context_parallel_world_size()
         comm = self.cp_comm_type if self.operator_type == "flash_te" else "p2p"
         if cp > 1 and self.operator_type in ("ring", "flash_te") and comm == "a2a":
             from ..parallel.cp_attention import ulysses_attention

@@ -172,6 +172,20 @@ def attention(q, k, v, causal=True, q_pos=None, k_pos=None, return_lse=False):
     return ref.attention(q, k, v, causal, q_pos, k_pos, return_lse)
 
 
+def attention_packed(qkv, cos, sin, causal=True):
+    """Self-attention on the packed projection qkv [B, L, H, 3*hd] with rotary embedding of q and k (cos / sin [L, rd] or
+    None).  Returns [B, L, H, hd], or None when the fused function does not cover the case (the caller then slices,
+    rotates and calls `attention`)."""
+    if not (qkv.is_cuda and _k(qkv)):
+        return None
+    from . import attention_cuda, flash_sm100
+    if not attention_cuda._OWN or not flash_sm100.packed_supported(qkv):
+        return None
+    if cos is not None and (cos.shape[-1] % 16 or cos.shape[-1] > 128 or cos.shape[0] != qkv.shape[1]):
+        return None
+    return flash_sm100.attention_packed(qkv, cos, sin, causal)
+
+
 # ----------------------------------------------------------------------------- loss / optimizer
 
 

@@ -846,7 +846,13 @@ class _Rope(torch.autograd.Function):
         return _rope_launch(gy, cos, sin, 1), None, None
 
 
-def _rope_launch(x, cos, sin, inverse):
+def _one_row_stride(t, L, H):
+    rs = t.stride(2)
+    return t.stride(3) == 1 and t.stride(1) == H * rs and t.stride(0) == L * H * rs and rs % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _rope_launch(x, cos, sin, inverse, out=None):
+    """`out`: a destination [B, L, H, hd] whose rows (b, l, h) are one stride apart (a slice of a packed buffer)."""
     lib = require()
     B, L, H, hd = x.shape
     # rows (b,l,h) must be addressable with one stride: true for a slice of the packed [B,L,H,3*hd] projection
@@ -854,8 +860,13 @@ def _rope_launch(x, cos, sin, inverse):
     if x.stride(3) != 1 or x.stride(1) != H * rs or x.stride(0) != L * H * rs or rs % 8 or x.data_ptr() % 16:
         x = x.contiguous()
         rs = hd
-    y = _alloc((B, L, H, hd), dtype=bf16, device=x.device)
-    _check(lib.sb_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, L, H, hd, cos.shape[-1], rs, hd,
+    if out is None:
+        y, ys = _alloc((B, L, H, hd), dtype=bf16, device=x.device), hd
+    else:
+        if not _one_row_stride(out, L, H):
+            raise ValueError("rope: destination rows must be one stride apart")
+        y, ys = out, out.stride(2)
+    _check(lib.sb_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, L, H, hd, cos.shape[-1], rs, ys,
                        inverse, _stream()), "rope")
     _count()
     return y

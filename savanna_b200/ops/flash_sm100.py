@@ -28,7 +28,7 @@ def _lib():
         lib.sb_attn_fwd.restype = I
         lib.sb_attn_fwd.argtypes = [P, P, P, P, P, I, I, I, I, P, P, P, P, I, F, P, P]
         lib.sb_attn_bwd.restype = I
-        lib.sb_attn_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P, P, P, P, P, P, I, F, P, P]
+        lib.sb_attn_bwd.argtypes = [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P, P, P, P, P, P, P, P, I, F, P, P]
         lib.sb_attn_last_encode_result.restype = I
         lib.sb_attn_last_encode_result.argtypes = []
         lib.sb_attn_set_bwd_variant.restype = I
@@ -89,12 +89,13 @@ def forward(q, k, v, causal: bool, scale: float):
     return out, lse
 
 
-def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_acc=None, dk=None, dv=None):
+def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_acc=None, dk=None, dv=None, dq=None):
     """Gradients (dq, dk, dv) in bf16.  `glse` [B, H, Lq] is the gradient that arrived at the log-sum-exp output (the
     merge step of ring attention differentiates through it); it enters as a shift of the row term delta.
     With `dq_acc` (fp32, contiguous [B, Lq, H, 128]) the query gradient is ADDED into that accumulator and no bf16 dq is
-    produced (returned as None): several calls over different key blocks share one accumulator.  `dk` / `dv` may be
-    given as contiguous [B, Lk, H, 128] bf16 destinations."""
+    produced (returned as None): several calls over different key blocks share one accumulator.  `dq` / `dk` / `dv`
+    may be given as bf16 destinations [B, L, H, 128] with a unit inner stride and the other strides multiples of 8
+    elements (slices of a packed gradient buffer)."""
     lib = _lib()
     B, Lq, H, _ = q.shape
     Lk = k.shape[1]
@@ -103,7 +104,13 @@ def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_ac
     if not shared:
         dq_acc = _zeros((B, Lq, H, 128), dtype=torch.float32, device=q.device)
     stats = _alloc(2 * B * H * ((Lq + 63) // 64 * 64), dtype=torch.float32, device=q.device)
-    dq = None if shared else _alloc((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
+    if shared:
+        dq = None
+    elif dq is None:
+        dq = _alloc((B, Lq, H, 128), dtype=torch.bfloat16, device=q.device)
+    for t in (dq, dk, dv):
+        if t is not None and not _ok_layout(t):
+            raise ValueError(f"attention backward: destination layout {tuple(t.shape)} {t.stride()} is not supported")
     if dk is None:
         dk = _alloc((B, Lk, H, 128), dtype=torch.bfloat16, device=q.device)
     if dv is None:
@@ -113,8 +120,8 @@ def backward(go, q, k, v, out, lse, causal: bool, scale: float, glse=None, dq_ac
     rc = lib.sb_attn_bwd(go.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                          cuda_ops._ptr(glse), stats.data_ptr(), dq_acc.data_ptr(), cuda_ops._ptr(dq), dk.data_ptr(),
                          B, H, Lq, Lk, dv.data_ptr(), _str3(go), _str3(q), _str3(k), _str3(v), _str3(out),
-                         _str3(dq if dq is not None else out), int(causal), float(scale), cuda_ops.status_word(q.device).data_ptr(),
-                         cuda_ops._stream())
+                         _str3(dq if dq is not None else out), _str3(dk), _str3(dv), int(causal), float(scale),
+                         cuda_ops.status_word(q.device).data_ptr(), cuda_ops._stream())
     if rc != 0:
         raise RuntimeError(f"attention backward failed (code {rc}, encode {lib.sb_attn_last_encode_result()})")
     cuda_ops._count(3)
@@ -138,6 +145,54 @@ class _Flash(torch.autograd.Function):
             go = _zeros_like(out)
         dq, dk, dv = backward(go, q, k, v, out, lse, ctx.causal, ctx.scale, glse)
         return dq, dk, dv, None
+
+
+class _FlashPacked(torch.autograd.Function):
+    """Attention on the packed projection qkv [B, L, H, 3*128] (per head: q, k, v) with rotary embedding of q and k inside
+    the function.  The backward writes dq, dk, dv straight into one packed gradient buffer: the slice / concatenate
+    bookkeeping of autograd (a zero fill, a strided copy and an add per slice) does not run."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, causal):
+        B, L, H, _ = qkv.shape
+        q, k, v = qkv[..., :128], qkv[..., 128:256], qkv[..., 256:]
+        if cos is not None:
+            q = cuda_ops._rope_launch(q, cos, sin, 0)
+            k = cuda_ops._rope_launch(k, cos, sin, 0)
+        scale = 1.0 / math.sqrt(128)
+        out, lse = forward(q, k, v, causal, scale)
+        ctx.save_for_backward(qkv, q if cos is not None else None, k if cos is not None else None, out, lse, cos, sin)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, go):
+        qkv, q, k, out, lse, cos, sin = ctx.saved_tensors
+        rot = cos is not None
+        if not rot:
+            q, k = qkv[..., :128], qkv[..., 128:256]
+        v = qkv[..., 256:]
+        dqkv = _alloc(tuple(qkv.shape), dtype=torch.bfloat16, device=qkv.device)
+        dq_dst, dk_dst, dv_dst = dqkv[..., :128], dqkv[..., 128:256], dqkv[..., 256:]
+        if rot:
+            dq, dk, _ = backward(go, q, k, v, out, lse, ctx.causal, ctx.scale, dv=dv_dst)
+            cuda_ops._rope_launch(dq, cos, sin, 1, out=dq_dst)
+            cuda_ops._rope_launch(dk, cos, sin, 1, out=dk_dst)
+        else:
+            backward(go, q, k, v, out, lse, ctx.causal, ctx.scale, dq=dq_dst, dk=dk_dst, dv=dv_dst)
+        return dqkv, None, None, None
+
+
+def packed_supported(qkv) -> bool:
+    return (qkv.dim() == 4 and qkv.dtype == torch.bfloat16 and qkv.is_cuda and qkv.shape[-1] == 384 and qkv.is_contiguous()
+            and qkv.data_ptr() % 16 == 0)
+
+
+def attention_packed(qkv, cos, sin, causal):
+    """qkv [B, L, H, 384] bf16 contiguous; cos / sin [L, rd] fp32 (or None for no rotary embedding) -> [B, L, H, 128]."""
+    if cos is not None:
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+    return _FlashPacked.apply(qkv, cos, sin, causal)
 
 
 def attention(q, k, v, causal, return_lse=False):

@@ -34,9 +34,10 @@ E4M3, E5M2 = 0, 1
 
 class TPWorkspace:
     def __init__(self, group, ranks):
-        import torch.distributed._symmetric_memory as symm_mem
+        from . import symm
         from ..ops import cuda_ops
-        self.symm_mem, self.cuda_ops = symm_mem, cuda_ops
+        symm_mem = symm.load()
+        self.symm_mem, self.cuda_ops, self._symm_api = symm_mem, cuda_ops, symm
         self.lib = cuda_ops.require()
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         self.lib.sb_gemm_tp.restype = I
@@ -63,7 +64,7 @@ class TPWorkspace:
         self.sig = symm_mem.empty(32, dtype=torch.int32, device=self.dev)
         self.sig.zero_()
         hs = symm_mem.rendezvous(self.sig, self.group)
-        self.sig_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hs.buffer_ptrs])
+        self.sig_ptrs = (ctypes.c_void_p * self.world)(*symm.peer_pointers(hs, self.world))
         self.bar_epoch = 0
         torch.cuda.synchronize()
         dist.barrier(group=self.group)               # every rank's signal words are zero before the first device barrier
@@ -88,7 +89,7 @@ class TPWorkspace:
         if key not in self.symm:
             t = self.symm_mem.empty(numel, dtype=bf16, device=self.dev)
             h = self.symm_mem.rendezvous(t, self.group)
-            ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs])
+            ptrs = (ctypes.c_void_p * self.world)(*self._symm_api.peer_pointers(h, self.world))
             self.symm[key] = (t, ptrs)
         return self.symm[key]
 

@@ -31,15 +31,15 @@ import torch
 import torch.distributed as dist
 
 from .. import print_rank_0
-from . import state
+from . import state, symm
 
 
 class SymmAllocator:
     """Allocates flat buffers in symmetric memory and remembers the handles for the later rendezvous."""
 
     def __init__(self, group):
-        import torch.distributed._symmetric_memory as symm_mem
-        self.symm_mem = symm_mem
+        from . import symm
+        self.symm_mem = symm.load()
         self.group = group
         self.tensors: List[torch.Tensor] = []
 
@@ -76,11 +76,11 @@ class FusedZeroStep:
                 continue
             hg = allocator.rendezvous(g.flat_grad)
             hp = allocator.rendezvous(g.flat_param)
-            gp = (ctypes.c_void_p * self.world)(*[int(p) for p in hg.buffer_ptrs])
-            pp = (ctypes.c_void_p * self.world)(*[int(p) for p in hp.buffer_ptrs])
+            gp = (ctypes.c_void_p * self.world)(*symm.peer_pointers(hg, self.world))
+            pp = (ctypes.c_void_p * self.world)(*symm.peer_pointers(hp, self.world))
             # NVLS: the buffers' multicast addresses (0 when the fabric offers none)
-            mcg = int(getattr(hg, "multicast_ptr", 0) or 0) if use_nvls else 0
-            mcp = int(getattr(hp, "multicast_ptr", 0) or 0) if use_nvls else 0
+            mcg = symm.multicast_pointer(hg) if use_nvls else 0
+            mcp = symm.multicast_pointer(hp) if use_nvls else 0
             self.handles[id(g)] = (hg, hp, gp, pp, mcg, mcp)
         self.nvls = bool(self.handles) and all(h[4] and h[5] for h in self.handles.values())
         dev = opt.groups[0].flat_param.device
@@ -101,7 +101,7 @@ class FusedZeroStep:
             self._sig = allocator.symm_mem.empty(32, dtype=torch.int32, device=dev)
             self._sig.zero_()
             hs = allocator.rendezvous(self._sig)
-            self._sig_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hs.buffer_ptrs])
+            self._sig_ptrs = (ctypes.c_void_p * self.world)(*symm.peer_pointers(hs, self.world))
             self._bar_epoch = 0
             torch.cuda.synchronize()
             dist.barrier(group=opt.group)    # every rank's signal words are zero before the first device barrier

@@ -100,6 +100,34 @@ def test_flash_lse_gradient():
     _case(1, 128, 256, 2, False, lse_grad=True, seed=9)
 
 
+@pytest.mark.parametrize("rotary_dim", [None, 128, 64])
+@pytest.mark.parametrize("L", [256, 333])
+def test_packed_projection_attention(L, rotary_dim):
+    """The one-function form on the packed projection [B, L, H, 3*128] (rotary embedding inside, gradients written
+    straight into one packed buffer) against slicing, rotating and attending in fp32."""
+    from savanna_b200 import ops
+    torch.manual_seed(21)
+    B, H = 2, 2
+    qkv = torch.randn(B, L, H, 384, device=DEV, dtype=BF, requires_grad=True)
+    cos = sin = None
+    if rotary_dim:
+        cos, sin = ref.rope_tables(torch.arange(L, device=DEV), rotary_dim)
+    o = ops.attention_packed(qkv, cos, sin, True)
+    assert o is not None
+    go = torch.randn_like(o)
+    (g,) = torch.autograd.grad((o.float() * go.float()).sum(), (qkv,))
+    _status_ok()
+    qr = qkv.detach().float().requires_grad_()
+    q, k, v = qr[..., :128], qr[..., 128:256], qr[..., 256:]
+    if rotary_dim:
+        q, k = ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
+    orf = ref.attention(q, k, v, True)
+    (gr,) = torch.autograd.grad((orf * go.float()).sum(), (qr,))
+    _rel(o, orf, 1e-2, "out")
+    for name, sl in (("dq", slice(0, 128)), ("dk", slice(128, 256)), ("dv", slice(256, 384))):
+        _rel(g[..., sl], gr[..., sl], 2e-2, name)
+
+
 def test_flash_long_sequence_statistics():
     """Scores with a large spread exercise the lazy rescaling of the output accumulator."""
     from savanna_b200.ops import flash_sm100

@@ -445,3 +445,26 @@ def test_ring_block_plan_covers_the_causal_mask():
             assert torch.equal(got, want), (me, src, got, want)
     # without causality a step is one dense block
     assert _block_plan(1, 2, False) == [("all", "all", False)]
+
+
+def test_symmetric_memory_door_reports_a_moved_api(monkeypatch):
+    """The private PyTorch API behind every peer mapping is checked in one place: a module without `rendezvous` (or no
+    module at all) gives one clear error, and the ZeRO allocator answers None so that the NCCL path runs."""
+    import sys
+    import types
+    from savanna_b200.parallel import fused_zero, symm
+    fake = types.ModuleType("fake_symm_without_rendezvous")
+    fake.empty = lambda *a, **k: None
+    sys.modules[fake.__name__] = fake
+    with pytest.raises(symm.SymmetricMemoryUnavailable, match="lacks rendezvous"):
+        symm.load(fake.__name__)
+    with pytest.raises(symm.SymmetricMemoryUnavailable, match="no importable"):
+        symm.load("savanna_b200_no_such_module")
+    handle = types.SimpleNamespace(buffer_ptrs=[16, 0])
+    with pytest.raises(symm.SymmetricMemoryUnavailable):
+        symm.peer_pointers(handle, 2)
+    assert symm.peer_pointers(types.SimpleNamespace(buffer_ptrs=[16, 32]), 2) == [16, 32]
+    assert symm.multicast_pointer(types.SimpleNamespace()) == 0
+    monkeypatch.setattr(symm, "_MODULE", fake.__name__)
+    monkeypatch.setattr(symm.load, "__defaults__", (fake.__name__,))
+    assert fused_zero.make_allocator(None) is None
