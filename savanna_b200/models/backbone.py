@@ -183,4 +183,43 @@ def param_groups(model: nn.Module, cfg):
         groups[1]["lr"] = cfg.wd_free_lr
     if medium:
         groups.append({"params": medium, "weight_decay": 0.0, "lr": cfg.lr_medium_hyena, "name": "medium_hyena"})
-    return [g for g in groups if g["params"]]
+    groups = [g for g in groups if g["params"]]
+    if cfg.use_mup:
+        groups = mup_param_groups(groups, model, cfg)
+    return groups
+
+
+def mup_param_groups(groups, model: nn.Module, cfg):
+    """Per-group learning rates of the maximal-update parametrisation (the reference's MuAdam / MuSGD,
+    savanna/training.py:1065-1185 with the `mup` package): parameters whose two dimensions both grow with the model
+    width ("matrix-like": the projection and MLP weights) are separated from the rest ("vector-like": embeddings,
+    norms, biases, filters).  Adam-type optimizers divide the matrix-like learning rate by the width multiplier
+    `mup_width_scale` (and multiply a coupled weight decay by it); SGD multiplies the vector-like learning rate by it.
+    A group that was split keeps its name with a `_matrix` suffix for the matrix-like half."""
+    matrix_ids = set()
+    for name, p in model.named_parameters():
+        if p.dim() == 2 and name.endswith(".weight") and any(k in name for k in (
+                "dense_projection.", "mixer.dense.", ".mlp.w1.", ".mlp.w2.", ".mlp.w3.", ".mlp.dense_", ".mlp.w12")):
+            matrix_ids.add(id(p))
+    mult = float(cfg.mup_width_scale)
+    sgd = str(cfg.optimizer_type).lower() in ("sgd", "musgd")
+    decoupled = bool(((cfg.optimizer or {}).get("params", {}) or {}).get("adam_w_mode", True))
+    out = []
+    for g in groups:
+        base_lr = g.get("lr", cfg.lr)
+        mat = [p for p in g["params"] if id(p) in matrix_ids]
+        vec = [p for p in g["params"] if id(p) not in matrix_ids]
+        if vec:
+            gv = dict(g, params=vec)
+            if sgd:
+                gv["lr"] = base_lr * mult
+                gv["weight_decay"] = g.get("weight_decay", 0.0) / mult
+            out.append(gv)
+        if mat:
+            gm = dict(g, params=mat, name=g.get("name", "group") + "_matrix")
+            if not sgd:
+                gm["lr"] = base_lr / mult
+                if not decoupled:
+                    gm["weight_decay"] = g.get("weight_decay", 0.0) * mult
+            out.append(gm)
+    return out

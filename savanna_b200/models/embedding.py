@@ -22,9 +22,17 @@ class SinusoidalPositionalEmbedding(nn.Module):
 
 
 class Embedding(nn.Module):
-    def __init__(self, cfg, init_method, dtype=None, device=None):
+    """Word embedding + optional learned / sinusoidal positions + optional token-type embeddings (`num_tokentypes`
+    segment ids, word_embeddings.py:88-136: built at construction or added later with `add_tokentype_embeddings`)."""
+
+    def __init__(self, cfg, init_method, dtype=None, device=None, num_tokentypes: int = 0):
         super().__init__()
         self.cfg = cfg
+        self._init_method, self._dtype = init_method, dtype
+        self.num_tokentypes = 0
+        self.tokentype_embeddings = None
+        if num_tokentypes > 0:
+            self._build_tokentypes(num_tokentypes, device)
         self.word_embeddings = VocabParallelEmbedding(cfg.padded_vocab_size, cfg.hidden_size, init_method, dtype, device)
         self.pos_kind = cfg.pos_emb
         if cfg.pos_emb == "learned":
@@ -36,8 +44,23 @@ class Embedding(nn.Module):
         self.sequence_parallel = cfg.sequence_parallel and state.get_model_parallel_world_size() > 1
         self.mup_mult = cfg.mup_embedding_mult if cfg.use_mup else 1.0
 
-    def forward(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    def _build_tokentypes(self, n: int, device) -> None:
+        self.num_tokentypes = n
+        self.tokentype_embeddings = nn.Embedding(n, self.cfg.hidden_size, dtype=self._dtype, device=device)
+        self._init_method(self.tokentype_embeddings.weight)
+
+    def add_tokentype_embeddings(self, num_tokentypes: int) -> None:
+        """Add token-type embeddings to a model that was built (or pretrained) without them."""
+        if self.tokentype_embeddings is not None:
+            raise RuntimeError("tokentype embeddings are already initialised")
+        self._build_tokentypes(num_tokentypes, self.word_embeddings.weight.device)
+
+    def forward(self, ids: torch.Tensor, positions: torch.Tensor, tokentype_ids: torch.Tensor = None) -> torch.Tensor:
         x = self.word_embeddings(ids)
+        if tokentype_ids is not None:
+            if self.tokentype_embeddings is None:
+                raise RuntimeError("tokentype ids given to a model without tokentype embeddings")
+            x = x + self.tokentype_embeddings(tokentype_ids)
         if self.pos_kind == "learned":
             x = x + self.position_embeddings(positions + self.cfg.opt_pos_emb_offset)[None]
         elif self.pos_kind == "sinusoidal":

@@ -6,6 +6,7 @@ into bias-dropout-add).
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -44,11 +45,33 @@ class SelfAttention(nn.Module):
             self._rotary.append(RotaryEmbedding(rd, cfg.rotary_emb_base, cfg.rotary_emb_scaling_factor,
                                                 "rotary" if cfg.pos_emb == "rotary2" else cfg.pos_emb,
                                                 cfg.rotary_emb_max_unscaled_seq_len, device=device))
+        # score biases (ALiBi slopes, bucketed relative positions): only the legacy `global` operator takes them; its
+        # scores are materialised (the flash kernels have no bias input), as in the reference's non-flash attention
+        self.score_bias = None
+        if cfg.pos_emb in ("alibi", "rpe"):
+            if operator_type != "global":
+                raise NotImplementedError(f"pos_emb={cfg.pos_emb!r} needs the `global` attention operator "
+                                          f"(got {operator_type!r}): the flash kernels take no score bias")
+            from .rope import AliBi, RelativePositionBias
+            rank = state.get_model_parallel_rank()
+            if cfg.pos_emb == "alibi":
+                self.score_bias = AliBi(cfg.num_attention_heads, tp, rank).to(device)
+            else:
+                self.score_bias = RelativePositionBias(math.sqrt(self.hd), self.causal,
+                                                       cfg.rpe_num_buckets, cfg.rpe_max_distance, cfg.num_attention_heads,
+                                                       tp, rank, dtype=torch.float32, device=device)
 
     def forward(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         B, L, _ = qkv.shape
         qkv = qkv.view(B, L, self.heads, 3 * self.hd)
         cp = state.get_context_parallel_world_size()
+        if self.score_bias is not None:
+            if cp > 1:
+                raise NotImplementedError("score-bias attention (alibi / rpe) does not run under context parallelism")
+            from ..ops import reference as ref
+            q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+            o = ref.attention(q, k, v, self.causal, positions, positions, bias=self.score_bias.bias(positions, positions))
+            return o.reshape(B, L, self.heads * self.hd)
         cos = sin = None
         if self._rotary:
             cos, sin = self._rotary[0](positions)

@@ -59,3 +59,47 @@ class AliBi(nn.Module):
     def bias(self, q_pos, k_pos):
         rel = (k_pos[None, :] - q_pos[:, None]).float()
         return self.slopes.view(-1, 1, 1) * rel[None]
+
+
+class RelativePositionBias(nn.Module):
+    """T5-style bucketed relative-position bias: a table [num_buckets, heads / tp] indexed by the bucket of
+    (key position - query position); half of the buckets are exact small distances, the rest grow logarithmically up
+    to `max_distance`.  `bias(q_pos, k_pos)` -> [heads / tp, Lq, Lk] * scale, added to the attention scores
+    (reference: savanna/mpu/layers.py:194-349 `ParallelRelativePositionBias`, heads split over tensor-parallel ranks)."""
+
+    def __init__(self, scale: float, causal: bool = True, num_buckets: int = 32, max_distance: int = 128, heads: int = 8,
+                 mp_size: int = 1, mp_rank: int = 0, init_method=None, dtype=None, device=None):
+        super().__init__()
+        import math
+        self.scale, self.causal, self.num_buckets, self.max_distance = scale, causal, num_buckets, max_distance
+        per = heads // mp_size
+        full = torch.empty(num_buckets, heads, dtype=torch.float32)
+        (init_method or nn.init.xavier_normal_)(full)              # the whole table, then this rank's head columns
+        self.weight = nn.Parameter(full[:, mp_rank * per:(mp_rank + 1) * per].to(dtype=dtype, device=device).contiguous())
+        self._log_ratio = math.log
+
+    def bucket(self, relative_position: torch.Tensor) -> torch.Tensor:
+        import math
+        nb = self.num_buckets
+        n = -relative_position
+        ret = torch.zeros_like(n)
+        if not self.causal:
+            nb //= 2
+            ret = ret + (n < 0).long() * nb
+            n = n.abs()
+        else:
+            n = n.clamp_min(0)
+        max_exact = nb // 2
+        large = max_exact + (torch.log(n.float().clamp_min(1) / max_exact) / math.log(self.max_distance / max_exact)
+                             * (nb - max_exact)).long()
+        large = large.clamp_max(nb - 1)
+        return ret + torch.where(n < max_exact, n, large)
+
+    def bias(self, q_pos: torch.Tensor, k_pos: torch.Tensor) -> torch.Tensor:
+        rel = k_pos[None, :].long() - q_pos[:, None].long()
+        values = nn.functional.embedding(self.bucket(rel), self.weight)          # [Lq, Lk, heads]
+        return values.permute(2, 0, 1) * self.scale
+
+    def forward(self, q_len: int, k_len: int) -> torch.Tensor:
+        dev = self.weight.device
+        return self.bias(torch.arange(q_len, device=dev) + (k_len - q_len), torch.arange(k_len, device=dev))

@@ -196,11 +196,14 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
               q_pos: Optional[torch.Tensor] = None, k_pos: Optional[torch.Tensor] = None,
-              return_lse: bool = False):
-    """softmax(q k^T / sqrt(hd)) v; q [B, Lq, H, hd], k/v [B, Lk, H, hd].  With q_pos/k_pos (global
-    positions) the causal mask is q_pos >= k_pos, which covers zigzag shards."""
+              return_lse: bool = False, bias: Optional[torch.Tensor] = None):
+    """softmax(q k^T / sqrt(hd) + bias) v; q [B, Lq, H, hd], k/v [B, Lk, H, hd], bias [H, Lq, Lk] (ALiBi or a
+    relative-position table).  With q_pos/k_pos (global positions) the causal mask is q_pos >= k_pos, which covers
+    zigzag shards."""
     B, Lq, H, hd = q.shape
     s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / math.sqrt(hd)
+    if bias is not None:
+        s = s + bias.float()[None]
     if causal:
         if q_pos is None:
             q_pos = torch.arange(Lq, device=q.device) + (k.shape[1] - Lq)

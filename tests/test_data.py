@@ -150,3 +150,45 @@ def test_dpo_preprocess_and_batch(tmp_path):
     batches = iter([{"text": rows}] * 4)
     l0 = float(tr.train_step(batches))
     assert l0 == l0
+
+
+def test_legacy_indexed_dataset_round_trip(tmp_path):
+    """The pre-mmap format: builder -> lazy reader -> cached reader; slices, documents, merge, implementation inferred
+    from the index magic."""
+    import numpy as np
+    from savanna_b200.data import indexed_dataset as ids
+    docs = [[np.arange(5), np.arange(3) + 10], [np.arange(7) + 100]]
+    prefix = str(tmp_path / "legacy")
+    b = ids.make_builder(prefix + ".bin", impl="cached")
+    for doc in docs:
+        for item in doc:
+            b.add_item(item)
+        b.end_document()
+    b.finalize(prefix + ".idx")
+    assert ids.infer_dataset_impl(prefix) == "cached"
+    lazy = ids.make_dataset(prefix, "lazy")
+    assert len(lazy) == 3 and list(lazy.doc_idx) == [0, 2, 3] and list(lazy.sizes) == [5, 3, 7]
+    assert np.array_equal(lazy[1], np.arange(3) + 10)
+    parts = lazy[0:3]
+    assert [len(p) for p in parts] == [5, 3, 7] and np.array_equal(parts[2], np.arange(7) + 100)
+    assert np.array_equal(lazy.get(2, 2, 3), np.arange(7)[2:5] + 100)
+    cached = ids.make_dataset(prefix, "infer")
+    assert isinstance(cached, ids.IndexedCachedDataset) and cached.supports_prefetch
+    cached.prefetch([2, 0])
+    assert np.array_equal(cached[2], np.arange(7) + 100) and np.array_equal(cached[1], np.arange(3) + 10)
+    # merge a second file behind the first
+    p2 = str(tmp_path / "merged")
+    b2 = ids.IndexedDatasetBuilder(p2 + ".bin")
+    b2.add_item(np.array([1, 2]))
+    b2.end_document()
+    b2.merge_file_(prefix)
+    b2.finalize(p2 + ".idx")
+    m = ids.IndexedDataset(p2)
+    assert len(m) == 4 and list(m.doc_idx) == [0, 1, 3, 4] and np.array_equal(m[3], np.arange(7) + 100)
+    # the mmap format is still told apart
+    p3 = str(tmp_path / "mm")
+    b3 = ids.make_builder(p3 + ".bin", vocab_size=512)
+    b3.add_item([1, 2, 3])
+    b3.end_document()
+    b3.finalize(p3 + ".idx")
+    assert ids.infer_dataset_impl(p3) == "mmap" and isinstance(ids.make_dataset(p3, "infer"), ids.MMapIndexedDataset)

@@ -71,3 +71,58 @@ def test_tuner_grid_and_job_array(tmp_path):
     cfg = yaml.safe_load((out / "configs" / "mb2_tp2_cp4_ac2_z1.yml").read_text())
     assert cfg["model_parallel_size"] == 2 and cfg["context_parallel_size"] == 4 and cfg["sequence_parallel"] and cfg["use_cp_hyena"]
     assert subprocess.run(["bash", "-n", str(out / "array.sbatch")]).returncode == 0          # the script parses
+
+
+def test_ops_scripts_config_diff_log_parse_checkpoint_summary_filter_lens(tmp_path):
+    import torch
+    from launcher.scripts import compare_configs, filter_lens, parse_logs, summarize_checkpoints
+    # config diff, raw and resolved
+    a, b = tmp_path / "a.yml", tmp_path / "b.yml"
+    a.write_text("{\n  \"hidden-size\": 64,\n  \"optimizer\": {\"type\": \"Adam\", \"params\": {\"lr\": 0.001}}\n}\n")
+    b.write_text("{\n  \"hidden_size\": 128,\n  \"optimizer\": {\"type\": \"Adam\", \"params\": {\"lr\": 0.002}},\n  \"seed\": 3\n}\n")
+    diffs = compare_configs.compare([str(a)], [str(b)])
+    assert any(d.startswith("hidden_size differs") for d in diffs)
+    assert any("optimizer/params/lr differs" in d for d in diffs) and any(d == "seed only in second" for d in diffs)
+    # log scraping
+    log = tmp_path / "train.log"
+    log.write_text(" iteration       10/    1000 | lm_loss: 2.345E+00 | tokens/s/gpu: 4.1E+04 | lr: 1.0E-04 |\n"
+                   "SAVE_CHECKPOINT: iteration: 10, ckpt saving takes 12.5 seconds\n"
+                   " iteration       20/    1000 | lm_loss: 2.1E+00 | tokens/s/gpu: 4.2E+04 |\n"
+                   "time (ms) | model and optimizer: 1234.5 | train/valid/test data iterators: 56.7\n")
+    lines = log.read_text().splitlines()
+    it = parse_logs.parse_iterations(lines)
+    assert [r["iteration"] for r in it] == [10, 20] and it[0]["lm_loss"] == 2.345 and it[1]["tokens/s/gpu"] == 4.2e4
+    ck = parse_logs.parse_checkpoint_times(lines)
+    assert ck == [{"iteration": 10, "checkpoint_time": 12.5}]
+    assert parse_logs.describe(ck, "checkpoint_time")["mean"] == 12.5
+    assert parse_logs.parse_startup(lines)[0]["model_and_optimizer"] == 1234.5
+    parse_logs.write_csv(it, str(tmp_path / "it.csv"))
+    assert (tmp_path / "it.csv").read_text().startswith("iteration,train_iters,lm_loss")
+    # checkpoint summary
+    save = tmp_path / "save"
+    for step, files in ((10, ["mp_rank_00_model_states.pt", "bf16_zero_pp_rank_0_mp_rank_00_optim_states.pt"]), (20, [])):
+        d = save / f"global_step{step}"
+        d.mkdir(parents=True)
+        for f in files:
+            (d / f).write_bytes(b"x" * 100)
+    (save / "latest").write_text("global_step10")
+    (save / "global_step10" / ".uploaded").write_text("")
+    res = summarize_checkpoints.summarize(str(save), expect_mp=1, expect_dp=1)
+    assert res["latest"] == "global_step10" and res["steps"][10]["complete"] and res["steps"][10]["uploaded"]
+    assert 20 not in res["steps"] or not res["steps"][20]["complete"]
+    # filter lengths: an un-padded checkpoint is reported, fixed, and then passes
+    ck_dir = tmp_path / "ext"
+    (ck_dir / "zero" / "sequential.3.mixer.mixer.filter.h").mkdir(parents=True)
+    h = torch.randn(4, 16)
+    torch.save({"module": {"sequential.3.mixer.mixer.filter.h": h.clone(), "other.weight": torch.ones(2)},
+                "param_shapes": [{"sequential.3.mixer.mixer.filter.h": h.shape}]}, ck_dir / "mp_rank_00_model_states.pt")
+    torch.save({"fp32": h.clone().flatten(), "exp_avg": torch.zeros(64)}, ck_dir / "zero" / "sequential.3.mixer.mixer.filter.h" / "fp32.pt")
+    probs = filter_lens.check(str(ck_dir), 4, 16, 64)
+    assert len(probs) >= 2
+    changed = filter_lens.fix(str(ck_dir), 4, 16, 64)
+    assert changed == {"model_tensors": 1, "zero_tensors": 2}
+    probs = filter_lens.check(str(ck_dir), 4, 16, 64)
+    assert probs == ["zero/sequential.3.mixer.mixer.filter.h/fp32.pt:exp_avg: only zeros in the filter region [0:16)"]
+    sd = torch.load(ck_dir / "mp_rank_00_model_states.pt", weights_only=False)
+    assert torch.equal(sd["module"]["sequential.3.mixer.mixer.filter.h"][:, :16], h) and sd["param_shapes"][0][
+        "sequential.3.mixer.mixer.filter.h"] == torch.Size([4, 64])

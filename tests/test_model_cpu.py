@@ -189,3 +189,79 @@ def test_warmstart_loads_state_but_restarts_the_count(tmp_path):
     assert t2.optimizer.step_count == tr.optimizer.step_count == 2
     for ga, gb in zip(tr.optimizer.groups, t2.optimizer.groups):
         assert torch.equal(ga.exp_avg, gb.exp_avg) and torch.equal(ga.master, gb.master)
+
+
+def test_score_bias_position_embeddings_on_the_global_operator():
+    """`pos_emb: alibi` and `pos_emb: rpe` add a per-head bias to the attention scores of the legacy `global` operator:
+    bucket law of the relative-position table, head split over tensor-parallel ranks, and a model step."""
+    from savanna_b200.models.rope import AliBi, RelativePositionBias
+    rpe = RelativePositionBias(2.0, causal=True, num_buckets=32, max_distance=128, heads=4)
+    rel = torch.tensor([[0, -1, -15, -16, -64, -127, -128, -5000, 3]])
+    b = rpe.bucket(rel)[0].tolist()
+    assert b[:3] == [0, 1, 15]                       # exact below num_buckets / 2
+    assert b[3] == 16 and b[4] > b[3] and b[5] <= 31 and b[6] == 31 and b[7] == 31
+    assert b[8] == 0                                 # future positions collapse to bucket 0 in the causal form
+    bias = rpe(6, 6)
+    assert bias.shape == (4, 6, 6)
+    assert torch.allclose(bias[:, 3, 1], rpe.weight[2].float() * 2.0)
+    half = RelativePositionBias(1.0, heads=4, mp_size=2, mp_rank=1)
+    assert half.weight.shape == (32, 2)
+    ali = AliBi(8)
+    assert torch.allclose(ali.bias(torch.arange(4), torch.arange(4))[0, 3, 1], ali.slopes[0] * -2.0)
+    for pe in ("alibi", "rpe"):
+        cfg = _cfg(operator_config=[[["global"], 2]], num_layers=2, pos_emb=pe)
+        tr = Trainer(cfg, load=False)
+        d = _iter(cfg)
+        losses = [float(tr.train_step(d)) for _ in range(4)]
+        assert losses[-1] < losses[0], (pe, losses)
+    with pytest.raises(NotImplementedError, match="global"):
+        Trainer(_cfg(operator_config=[[["flash_v2"], 2]], num_layers=2, pos_emb="alibi"), load=False)
+
+
+def test_tokentype_embeddings_can_be_added_after_construction():
+    from savanna_b200.models.embedding import Embedding
+    from savanna_b200.models.init_functions import get_init_methods
+    cfg = _cfg()
+    Trainer(cfg, load=False)                                   # brings up the (single-rank) parallel state
+    init, _ = get_init_methods(cfg)
+    emb = Embedding(cfg, init, dtype=torch.float32)
+    ids = torch.randint(0, 512, (2, 8))
+    pos = torch.arange(8)
+    base = emb(ids, pos)
+    with pytest.raises(RuntimeError):
+        emb(ids, pos, torch.zeros(2, 8, dtype=torch.long))
+    emb.add_tokentype_embeddings(3)
+    tt = torch.randint(0, 3, (2, 8))
+    emb.eval()
+    assert torch.allclose(emb(ids, pos, tt), emb(ids, pos) + emb.tokentype_embeddings(tt))
+    assert "tokentype_embeddings.weight" in emb.state_dict()
+    with pytest.raises(RuntimeError):
+        emb.add_tokentype_embeddings(2)
+    assert base.shape == (2, 8, cfg.hidden_size)
+
+
+def test_mup_optimizer_groups_scale_matrix_like_learning_rates():
+    """`use_mup`: projection / MLP weights get lr / mup_width_scale under Adam (MuAdam), vector-like parameters get
+    lr * mup_width_scale under SGD (MuSGD); every parameter stays in exactly one group."""
+    from savanna_b200.models.backbone import param_groups
+    cfg = _cfg(use_mup=True, mup_width_scale=4)
+    tr = Trainer(cfg, load=False)
+    groups = param_groups(tr.model, cfg)
+    names = {g["name"] for g in groups}
+    assert "decay_matrix" in names
+    n_params = sum(len(g["params"]) for g in groups)
+    assert n_params == len([p for p in tr.model.parameters() if p.requires_grad])
+    mat = next(g for g in groups if g["name"] == "decay_matrix")
+    assert abs(mat["lr"] - cfg.lr / 4) < 1e-12 and all(p.dim() == 2 for p in mat["params"])
+    vec = next(g for g in groups if g["name"] == "no_decay")
+    assert "lr" not in vec or vec["lr"] == cfg.lr
+    # the optimizer carries the ratio through the schedule
+    zg = [g for g in tr.optimizer.param_groups if g["name"] == "decay_matrix"][0]
+    assert abs(zg["lr_mult"] - 0.25) < 1e-9 and zg["fixed_lr"]
+    cfg2 = _cfg(use_mup=True, mup_width_scale=4, optimizer={"type": "sgd", "params": {"lr": 1e-3}})
+    assert cfg2.optimizer_type == "sgd"
+    tr2 = Trainer(cfg2, load=False)
+    g2 = param_groups(tr2.model, cfg2)
+    vec2 = next(g for g in g2 if g["name"] == "no_decay")
+    assert abs(vec2["lr"] - cfg2.lr * 4) < 1e-12
+    assert "lr" not in next(g for g in g2 if g["name"] == "decay_matrix")

@@ -1,6 +1,8 @@
 """Algebraic checks of the oracle operators themselves (the kernels are tested against these)."""
 import math
 
+import pytest
+
 import torch
 
 from savanna_b200.ops import reference as ref
@@ -82,3 +84,34 @@ def test_adam_matches_torch():
         opt.step()
         ref.adam_step(master, m, v, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, True)
     assert torch.allclose(master, q.detach(), atol=1e-6)
+
+
+def test_hippo_nplr_and_dplr_initialisers():
+    """HiPPO matrices: A + P^T P is normal for every measure; the kept half of the spectrum with its conjugate rebuilds
+    the matrix; LegS has the known diagonal; the DPLR layouts have the documented poles."""
+    from savanna_b200.models import ssm_init as si
+    N = 16
+    for measure in ("legs", "legt", "lagt", "fourier"):
+        A, B = si.transition(measure, N)
+        P = si.rank_correction(measure, N, rank=2 if measure == "legt" else 1)
+        AP = A + (P[:, :, None] * P[:, None, :]).sum(0)
+        assert torch.allclose(AP @ AP.t(), AP.t() @ AP, atol=1e-8), measure
+        w, Pc, Bc, V = si.nplr(measure, N, rank=P.shape[0], dtype=torch.float64)
+        assert w.shape == (N // 2,) and (w.imag >= -1e-9).all()
+        full = (V * w) @ V.conj().t()
+        rebuilt = 2 * full.real if measure != "lagt" else None
+        if rebuilt is not None and (w.imag.abs() > 1e-6).all():
+            assert torch.allclose(rebuilt, AP, atol=1e-6), measure
+    A, _ = si.transition("legs", 4)
+    assert torch.allclose(torch.diagonal(A), -torch.arange(1, 5, dtype=torch.float64))
+    assert float(A[2, 1]) == pytest.approx(-(5 ** 0.5) * (3 ** 0.5))
+    w, P, B, V = si.dplr("linear", N=8, H=3)
+    assert w.shape == (3, 4) and torch.allclose(w.real, torch.full((3, 4), -0.5))
+    assert torch.allclose(w.imag[0], math.pi * torch.arange(4.0))
+    assert float(P.abs().sum()) == 0.0 and V.shape == (3, 8, 4)
+    w2, *_ = si.ssm("diag-inv", 8, 1, 2)
+    assert w2.shape == (2, 4)
+    wc, Pc, Bc, Vc = si.combination("diag", 8, 1, 4)
+    assert wc.shape == (4, 4) and Pc.shape == (1, 4, 4) and Vc.shape == (4, 8, 4)
+    E = si.embed_c2r(torch.tensor([[1 + 2j]]))
+    assert torch.equal(E, torch.tensor([[1.0, -2.0], [2.0, 1.0]]))

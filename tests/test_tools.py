@@ -326,3 +326,73 @@ def test_zero3_layout_round_trips(tmp_path):
     t2 = Trainer(cfg2, load=True)
     assert t2.iteration == 2
     assert abs(float(t2.train_step(it(2))) - want_next) < 1e-6
+
+
+def test_train_tokenizer_round_trip(tmp_path):
+    """A BPE tokenizer trained on a few jsonl lines loads through the framework's HFTokenizer and round-trips text."""
+    import json
+    pytest.importorskip("tokenizers")
+    from savanna_b200.data.tokenizer import HFTokenizer
+    from savanna_b200.tools import train_tokenizer as tt
+    d = tmp_path / "corpus"
+    d.mkdir()
+    with open(d / "a.jsonl", "w") as fh:
+        for i in range(50):
+            fh.write(json.dumps({"text": f"the quick brown fox number {i} jumps over the lazy dog"}) + "\n")
+    out = str(tmp_path / "tok" / "tok.json")
+    tt.main(["--json_input_dir", str(d), "--tokenizer_output_path", out, "-v", "300"])
+    tok = HFTokenizer(out)
+    assert tok.eod == 0 and tok.pad_id == 1 and tok.vocab_size <= 300
+    ids = tok.tokenize("the quick brown fox")
+    assert tok.detokenize(ids).strip() == "the quick brown fox"
+    (tmp_path / "empty").mkdir()
+    with pytest.raises(FileNotFoundError):
+        list(tt.iter_texts(str(tmp_path / "empty")))
+
+
+def test_modal_distillation_recovers_a_modal_filter():
+    """Distilling a filter that is itself a sum of decaying modes: the real form reaches a small relative error and
+    exports parameters that the framework's modal filter statement reproduces."""
+    from savanna_b200.ops import reference as ref
+    from savanna_b200.tools import distill_filters as df
+    torch.manual_seed(0)
+    N, O, L = 3, 4, 96
+    gamma = torch.log(torch.rand(N, O) * 0.3 + 0.05)
+    R = torch.randn(N, O) * 0.3
+    p = -torch.ones(N, O)
+    target = ref.modal_filter(gamma, R, p, L)
+    models, logs = df.distill(target, order=8, form="real", epochs=1500, lr=2e-2)
+    assert logs[0][-1] < logs[0][0] * 0.05
+    err = df.relative_error(models[0], target)
+    assert err < 0.15, err
+    ex = df.export_implicit_modal(models[0])
+    again = ref.modal_filter(ex["gamma"], ex["R"], ex["p"], L)
+    assert torch.allclose(again, models[0].filter(L), atol=1e-5)
+    # the complex (recurrent) form keeps tap 0 as a pass-through and fits the rest
+    cm, clog = df.distill(target, order=8, form="complex", epochs=300, lr=1e-2)
+    assert torch.allclose(cm[0].filter(L)[:, 0], target[:, 0]) and clog[0][-1] < clog[0][0]
+    lam, Rc = cm[0].step_matrices()
+    assert lam.shape == (N, 8) and Rc.is_complex()
+
+
+def test_longeval_lines_task_scores_through_generation(tmp_path, monkeypatch):
+    """LongEval plumbing with a stand-in generator: test files are written and read back, answers are parsed as the last
+    integer, responses and accuracy land in the response file."""
+    from savanna_b200.inference import longeval as le
+    paths = le.write_testcases(str(tmp_path), "lines", sizes=[20, 30], num_cases=4, seed=1)
+    assert len(paths) == 2 and all(os.path.exists(p) for p in paths)
+    cases = le.load_testcases(paths[0])
+    assert len(cases) == 4 and cases[0]["correct_line"].endswith(f"<{cases[0]['expected_number']}>")
+    assert cases[0]["prompt"].count("REGISTER_CONTENT is") == 20
+    assert le.parse_number("the value is <123> or 456") == 456 and le.parse_number("none") == -1
+    answers = iter([f"it is {c['expected_number']}" if i % 2 == 0 else "unknown" for i, c in enumerate(cases)])
+    monkeypatch.setattr(le, "_answer", lambda model, tok, prompt, n, cache: (next(answers), len(prompt)))
+    out = str(tmp_path / "pred")
+    os.makedirs(out)
+    res = le.longeval_test(None, None, out, "lines", str(tmp_path), eval_shortest_only=True, sizes=[20, 30])
+    assert list(res) == [20] and res[20]["accuracy"] == 0.5
+    text = open(os.path.join(out, "20_response.txt")).read()
+    assert text.count("Label:") == 4 and text.rstrip().endswith("Accuracy: 0.5")
+    tp = le.write_testcases(str(tmp_path), "topics", sizes=[5], num_cases=2)
+    tc = le.load_testcases(tp[0])
+    assert len(tc[0]["topics"]) == 5 and tc[0]["topics"][0] in tc[0]["prompt"]
