@@ -396,3 +396,32 @@ def test_longeval_lines_task_scores_through_generation(tmp_path, monkeypatch):
     tp = le.write_testcases(str(tmp_path), "topics", sizes=[5], num_cases=2)
     tc = le.load_testcases(tp[0])
     assert len(tc[0]["topics"]) == 5 and tc[0]["topics"][0] in tc[0]["prompt"]
+
+
+def test_prepare_dataset_from_local_files_and_upload_to_a_posix_store(tmp_path):
+    """Corpora plumbing without network: a `file://` source is fetched, tokenised into .bin/.idx and read back; an
+    unreachable URL gives a clear error; the upload tool copies a directory into a posix store with its marker."""
+    from savanna_b200.data.indexed_dataset import make_dataset
+    from savanna_b200.tools import corpora, prepare_data, upload
+    src = tmp_path / "src.jsonl"
+    with open(src, "w") as fh:
+        for t in ("ACGTACGT", "GGCC", "TTTTAAAA"):
+            fh.write(json.dumps({"text": t}) + "\n")
+    prefix = prepare_data.main(["mygenomes", "-t", "CharLevelTokenizer", "-d", str(tmp_path / "data"), "--files", str(src),
+                                "--workers", "1"])
+    assert prefix.endswith(os.path.join("mygenomes", "mygenomes"))
+    found = [p for p in os.listdir(os.path.dirname(prefix)) if p.endswith(".idx")]
+    assert found, os.listdir(os.path.dirname(prefix))
+    ds = make_dataset(os.path.join(os.path.dirname(prefix), found[0][:-4]))
+    assert len(ds) == 3 and bytes(ds[1][:4].astype("uint8")) == b"GGCC"
+    assert corpora.prepare_dataset("pass") is None
+    with pytest.raises(NotImplementedError):
+        corpora.prepare_dataset("no_such_corpus", "CharLevelTokenizer", str(tmp_path / "data"))
+    with pytest.raises(RuntimeError, match="cannot download"):
+        corpora.fetch("file:///nonexistent/file.jsonl", str(tmp_path / "x.jsonl"))
+    ck = tmp_path / "global_step7"
+    ck.mkdir()
+    (ck / "mp_rank_00_model_states.pt").write_bytes(b"abc")
+    assert upload.main(["store", str(ck), "--store", "posix", "--root", str(tmp_path / "archive")])
+    assert (tmp_path / "archive" / "global_step7" / "mp_rank_00_model_states.pt").read_bytes() == b"abc"
+    assert (ck / ".uploaded").exists()
