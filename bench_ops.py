@@ -234,6 +234,11 @@ def bench_elementwise(T, iters, which):
         report("adam.ours", ms, None, n * 28, n=n)
 
 
+def cuda_ops_status():
+    from savanna_b200.ops import cuda_ops
+    cuda_ops.check_status()
+
+
 def bench_attention(L, iters, heads=32, small=False):
     """Causal attention of one 7B layer (32 heads x 128): this framework's tcgen05 kernels and the flash kernels that
     ship with PyTorch (library baseline).  FLOPs: 4 L^2 hd H / 2 forward, 2.5x that backward."""
@@ -251,6 +256,11 @@ def bench_attention(L, iters, heads=32, small=False):
     report("attention.fwd.ours_pingpong", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
     report("attention.fwd.ours_pingpong_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
     flash_sm100.set_forward_variant(False)
+    flash_sm100.set_forward_p_in_tmem(True)
+    report("attention.fwd.ours_p_in_tmem", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
+    report("attention.fwd.ours_p_in_tmem_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
+    flash_sm100.set_forward_p_in_tmem(False)
+    cuda_ops_status()
     report("attention.bwd.ours", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
     flash_sm100.set_backward_variant(False)
     report("attention.bwd.ours_p_in_smem", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)

@@ -80,6 +80,12 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kk) {
   return umma_smem_desc(tile + uint32_t(kk) * 2048u, BOX_BYTES, 1024u);
 }
 
+// P_TMEM: the probabilities go back into tensor memory as packed bf16 over the first 64 columns of their own score
+// buffer and enter the P V product as its TMEM operand: no P stores into shared memory and no A-operand reads from it
+// (a single-CTA M = 128 product with both operands in shared memory uses the whole shared-memory bandwidth of the SM).
+// The price is an ordering constraint: the scores of block j+1 overwrite P(j), so S_t(j+1) is issued behind P_t(j) V(j)
+// on the (in-order) tensor pipe instead of during softmax j; the other query tile fills the gap.
+template <bool P_TMEM>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -184,9 +190,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               tc_fence_after();
               const uint32_t sV = sKV + vslot * TILE_BYTES;
 #pragma unroll
-              for (int kk = 0; kk < 8; ++kk)
-                umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
-                          (jp | kk) ? 1u : 0u);
+              for (int kk = 0; kk < 8; ++kk) {
+                if (P_TMEM)      // 16 keys = 8 packed columns of the tile's score buffer
+                  umma_bf16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, desc_mnmajor(sV, kk), idesc_o,
+                               (jp | kk) ? 1u : 0u);
+                else
+                  umma_bf16(tmem_base + 256 + t * 128, desc_kmajor(sP + t * TILE_BYTES, kk), desc_mnmajor(sV, kk), idesc_o,
+                            (jp | kk) ? 1u : 0u);
+              }
               umma_commit(pv_done(t));
               pv_idx[t] = jp + 1;
               if (pv_idx[t ^ 1] > jp || jp >= nb[t ^ 1]) umma_commit(kv_free(vslot));   // both tiles are through with V(jp)
@@ -196,8 +207,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (s_idx[t] < nb[t]) {
             const int js = s_idx[t];
             const int kslot = (2 * js) % 3;
+            // P_TMEM: P(js-1) lives in the score buffer until its P V product, issued earlier on the in-order pipe, read it
             if (mbar_test(kv_full(kslot), uint32_t((2 * js) / 3) & 1u) &&
-                (js == 0 || mbar_test(s_free(t), uint32_t(js - 1) & 1u))) {
+                (js == 0 || (P_TMEM ? pv_idx[t] >= js : mbar_test(s_free(t), uint32_t(js - 1) & 1u)))) {
               tc_fence_after();
               const uint32_t sK = sKV + kslot * TILE_BYTES;
 #pragma unroll
@@ -304,9 +316,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             rs4[i] += ea + eb;
             w[i] = pack_bf16(ea, eb);
           }
-          st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
+          if (P_TMEM) {
+            // the score registers of these 8 keys are dead: keep the packed probabilities in their place
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[c][g * 4 + i] = w[i];
+          } else {
+            st_shared_v4(p_tile + swz_chunk(r, c * 4 + g), w[0], w[1], w[2], w[3]);
+          }
+        }
+        if (P_TMEM) {
+          uint32_t pw[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pw[i] = v[c][i];
+          tmem_st_32x16(t_s + c * 16, pw);                 // keys 32c .. 32c+31 -> packed columns 16c .. 16c+15
         }
       }
+      if (P_TMEM) tmem_wait_st();
       if (p.pingpong) mbar_arrive(turn(t ^ 1));               // hand the unit to the other warpgroup
       const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l = l * alpha + rs;
@@ -744,6 +769,7 @@ static EncodeTiledFn get_encode() {
 static int g_last_encode = 0;
 static int g_pingpong = 0;     // forward variant: softmax warpgroups take turns on the exponentials (1) or run freely (0)
 static int g_p_tmem = 1;       // backward variant: P^T in tensor memory (1) or in shared memory (0)
+static int g_fwd_p_tmem = 0;   // forward variant: P as the TMEM operand of P V (1) or through shared memory (0)
 
 // [B, L, H, 128] bf16 with element strides (sb, sl, sh); box = 64 columns x 1 head x box_rows rows x 1 batch
 static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, long long sb, long long sl, long long sh,
@@ -768,6 +794,7 @@ static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, lo
 extern "C" int sb_attn_last_encode_result() { return sb::attn::g_last_encode; }
 extern "C" int sb_attn_set_bwd_variant(int p_in_tmem) { sb::attn::g_p_tmem = p_in_tmem ? 1 : 0; return 0; }
 extern "C" int sb_attn_set_fwd_variant(int pingpong) { sb::attn::g_pingpong = pingpong ? 1 : 0; return 0; }
+extern "C" int sb_attn_set_fwd_p_tmem(int on) { sb::attn::g_fwd_p_tmem = on ? 1 : 0; return 0; }
 
 // Attention forward.  q [B, Lq, H, 128], k and v [B, Lk, H, 128], out like q: bf16, last dimension contiguous, the
 // other strides (in elements) multiples of 8.  lse [B, H, Lq] fp32.  causal needs Lq == Lk (row i sees keys 0..i).
@@ -788,13 +815,15 @@ extern "C" int sb_attn_fwd(const void* q, const void* k, const void* v, void* ou
   if ((rc = make_tmap(&tv, v, B, Lk, H, v_str[0], v_str[1], v_str[2]))) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
+    if (cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) return -5;
     attr_set = true;
   }
   FwdParams p{reinterpret_cast<__nv_bfloat16*>(out), lse, o_str[0], o_str[1], o_str[2], B, H, Lq, Lk, causal,
               scale * 1.4426950408889634f, scale, status, g_pingpong};
   dim3 grid((Lq + 2 * BQ - 1) / (2 * BQ), H, B);
-  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tk, tv, p);
+  if (g_fwd_p_tmem) attn_fwd_kernel<true><<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tk, tv, p);
+  else attn_fwd_kernel<false><<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;
 }
 

@@ -35,6 +35,8 @@ def _lib():
         lib.sb_attn_set_bwd_variant.argtypes = [I]
         lib.sb_attn_set_fwd_variant.restype = I
         lib.sb_attn_set_fwd_variant.argtypes = [I]
+        lib.sb_attn_set_fwd_p_tmem.restype = I
+        lib.sb_attn_set_fwd_p_tmem.argtypes = [I]
         lib.sb_attn_merge_fwd.restype = I
         lib.sb_attn_merge_fwd.argtypes = [P, P, P, P, I, I, I, I, P, P, P]
         lib.sb_attn_merge_bwd.restype = I
@@ -53,6 +55,12 @@ def set_forward_variant(pingpong: bool) -> None:
     """Forward kernel variant: the two softmax warpgroups of a CTA take turns on the exponentials (default), or run
     without coordination."""
     _lib().sb_attn_set_fwd_variant(int(bool(pingpong)))
+
+
+def set_forward_p_in_tmem(on: bool) -> None:
+    """Forward kernel variant: the probabilities as the tensor-memory operand of the P V product (packed bf16 over the
+    score columns), or through shared memory."""
+    _lib().sb_attn_set_fwd_p_tmem(int(bool(on)))
 
 
 def _ok_layout(t) -> bool:

@@ -128,6 +128,19 @@ def test_packed_projection_attention(L, rotary_dim):
         _rel(g[..., sl], gr[..., sl], 2e-2, name)
 
 
+@pytest.mark.parametrize("shape", [(1, 256, 256, 2, True), (2, 1024, 1024, 2, True), (1, 333, 333, 2, True),
+                                   (1, 384, 640, 2, False), (1, 2048, 2048, 4, True)])
+def test_flash_forward_with_probabilities_in_tensor_memory(shape):
+    """The forward variant that feeds P to the P V product from tensor memory: same cases, same tolerances."""
+    from savanna_b200.ops import flash_sm100
+    B, Lq, Lk, H, causal = shape
+    flash_sm100.set_forward_p_in_tmem(True)
+    try:
+        _case(B, Lq, Lk, H, causal, seed=31)
+    finally:
+        flash_sm100.set_forward_p_in_tmem(False)
+
+
 def test_flash_long_sequence_statistics():
     """Scores with a large spread exercise the lazy rescaling of the output accumulator."""
     from savanna_b200.ops import flash_sm100
