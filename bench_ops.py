@@ -256,10 +256,10 @@ def bench_attention(L, iters, heads=32, small=False):
     report("attention.fwd.ours_pingpong", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
     report("attention.fwd.ours_pingpong_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
     flash_sm100.set_forward_variant(False)
-    flash_sm100.set_forward_p_in_tmem(True)
-    report("attention.fwd.ours_p_in_tmem", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
-    report("attention.fwd.ours_p_in_tmem_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
     flash_sm100.set_forward_p_in_tmem(False)
+    report("attention.fwd.ours_p_in_smem", timeit(lambda: flash_sm100.forward(q, k, v, True, hd ** -0.5), iters), fl)
+    report("attention.fwd.ours_p_in_smem_noncausal", timeit(lambda: flash_sm100.forward(qn, kn, vn, False, hd ** -0.5), iters), 2 * fl)
+    flash_sm100.set_forward_p_in_tmem(True)
     cuda_ops_status()
     report("attention.bwd.ours", timeit(lambda: flash_sm100.backward(go, q, k, v, o, lse, True, hd ** -0.5), iters), 2.5 * fl)
     flash_sm100.set_backward_variant(False)

@@ -769,7 +769,7 @@ static EncodeTiledFn get_encode() {
 static int g_last_encode = 0;
 static int g_pingpong = 0;     // forward variant: softmax warpgroups take turns on the exponentials (1) or run freely (0)
 static int g_p_tmem = 1;       // backward variant: P^T in tensor memory (1) or in shared memory (0)
-static int g_fwd_p_tmem = 0;   // forward variant: P as the TMEM operand of P V (1) or through shared memory (0)
+static int g_fwd_p_tmem = 1;   // forward variant: P as the TMEM operand of P V (1, default) or through shared memory (0)
 
 // [B, L, H, 128] bf16 with element strides (sb, sl, sh); box = 64 columns x 1 head x box_rows rows x 1 batch
 static int make_tmap(CUtensorMap* out, const void* base, int B, int L, int H, long long sb, long long sl, long long sh,

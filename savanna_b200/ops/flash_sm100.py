@@ -59,7 +59,7 @@ def set_forward_variant(pingpong: bool) -> None:
 
 def set_forward_p_in_tmem(on: bool) -> None:
     """Forward kernel variant: the probabilities as the tensor-memory operand of the P V product (packed bf16 over the
-    score columns), or through shared memory."""
+    score columns; default), or through shared memory."""
     _lib().sb_attn_set_fwd_p_tmem(int(bool(on)))
 
 

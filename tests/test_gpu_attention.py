@@ -130,15 +130,16 @@ def test_packed_projection_attention(L, rotary_dim):
 
 @pytest.mark.parametrize("shape", [(1, 256, 256, 2, True), (2, 1024, 1024, 2, True), (1, 333, 333, 2, True),
                                    (1, 384, 640, 2, False), (1, 2048, 2048, 4, True)])
-def test_flash_forward_with_probabilities_in_tensor_memory(shape):
-    """The forward variant that feeds P to the P V product from tensor memory: same cases, same tolerances."""
+def test_flash_forward_with_probabilities_through_shared_memory(shape):
+    """The forward variant that stages P in shared memory (the default feeds it to the P V product from tensor memory):
+    same cases, same tolerances."""
     from savanna_b200.ops import flash_sm100
     B, Lq, Lk, H, causal = shape
-    flash_sm100.set_forward_p_in_tmem(True)
+    flash_sm100.set_forward_p_in_tmem(False)
     try:
         _case(B, Lq, Lk, H, causal, seed=31)
     finally:
-        flash_sm100.set_forward_p_in_tmem(False)
+        flash_sm100.set_forward_p_in_tmem(True)
 
 
 def test_flash_long_sequence_statistics():
