@@ -116,6 +116,15 @@ def bench_gemm(T, iters):
         report(f"gemm.{name}.fwd.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(xq, wq, out, al), iters), fl)
         report(f"gemm.{name}.dgrad.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(gq, wq, gx, al, b_mn=True, a_fmt=1), iters), fl)
         report(f"gemm.{name}.wgrad.ours_fp8_pair", timeit(lambda: cuda_ops.gemm_fp8(gq, xq, gw, al, a_mn=True, b_mn=True, a_fmt=1), iters), fl)
+        if N % 32 == 0 and K % 32 == 0 and M % 32 == 0:
+            # block-scaled fp8: the three products of a projection on operands quantised along their own contraction
+            xm, sxm = cuda_ops.mx_quantize(x); wm, swm = cuda_ops.mx_quantize(w); gm, sgm = cuda_ops.mx_quantize(gy)
+            wtm, swtm = cuda_ops.mx_quantize(w, True); xtm, sxtm = cuda_ops.mx_quantize(x, True); gtm, sgtm = cuda_ops.mx_quantize(gy, True)
+            report(f"gemm.{name}.fwd.ours_mxfp8", timeit(lambda: cuda_ops.gemm_mx(xm, sxm, wm, swm, out), iters), fl)
+            report(f"gemm.{name}.dgrad.ours_mxfp8", timeit(lambda: cuda_ops.gemm_mx(gm, sgm, wtm, swtm, gx), iters), fl)
+            report(f"gemm.{name}.wgrad.ours_mxfp8", timeit(lambda: cuda_ops.gemm_mx(gtm, sgtm, xtm, sxtm, gw), iters), fl)
+            report(f"quantize_mxfp8.{name}.x.rowwise", timeit(lambda: cuda_ops.mx_quantize(x), iters), None, M * K * 3)
+            report(f"quantize_mxfp8.{name}.x.transposed", timeit(lambda: cuda_ops.mx_quantize(x, True), iters), None, M * K * 3)
         report(f"quantize_fp8.{name}.x.current", timeit(lambda: cuda_ops.quantize_fp8(x, 0), iters), None, M * K * 5)
         site = torch.nn.Parameter(torch.zeros(1, device=x.device))
         report(f"quantize_fp8.{name}.x.delayed", timeit(lambda: cuda_ops.quantize_fp8_site(x, 0, site, "x"), iters), None, M * K * 3)

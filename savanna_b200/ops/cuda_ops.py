@@ -462,7 +462,123 @@ class _LinearFP8(torch.autograd.Function):
         return gx, gw, gb, gr
 
 
+# ----------------------------------------------------------------------------- block-scaled fp8 (MXFP8)
+FP8_RECIPE = "delayed"      # "delayed": per-tensor scaling (default); "mxfp8": one E8M0 scale per 32 elements of the contraction
+
+
+def set_fp8_recipe(name: str) -> None:
+    global FP8_RECIPE
+    if name not in ("delayed", "mxfp8"):
+        raise ValueError(f"unknown fp8 recipe {name!r}")
+    FP8_RECIPE = name
+
+
+def _mx_sigs(lib):
+    if getattr(lib, "_sb_mx_ready", False):
+        return
+    P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    lib.sb_mx_sf_bytes.restype = LL
+    lib.sb_mx_sf_bytes.argtypes = [LL, LL]
+    lib.sb_mx_quantize.restype = I
+    lib.sb_mx_quantize.argtypes = [P, P, P, LL, I, LL, I, P]
+    lib.sb_gemm_mx.restype = I
+    lib.sb_gemm_mx.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P]
+    lib._sb_mx_ready = True
+
+
+def mx_quantize(x2: torch.Tensor, transposed: bool = False):
+    """x2 [R, C] bf16 -> (q, sf): e4m3 bytes and E8M0 block scales (one per 32 elements of the contraction dimension) in
+    the layout the block-scaled tensor-core instruction reads.  transposed=False: q [R, C], scales along C (C % 32 == 0).
+    transposed=True: q [C, R], scales along R (R % 32 == 0): the operand form of a product contracted over the rows."""
+    lib = require()
+    _mx_sigs(lib)
+    R, C = x2.shape
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    rows, k = (C, R) if transposed else (R, C)
+    q = _alloc((rows, k), dtype=torch.uint8, device=x2.device)
+    sf = _zeros(lib.sb_mx_sf_bytes(rows, k), dtype=torch.uint8, device=x2.device)
+    _check(lib.sb_mx_quantize(x2.data_ptr(), q.data_ptr(), sf.data_ptr(), R, C, x2.stride(0), int(transposed), _stream()),
+           "mx_quantize")
+    _count(2)
+    return q, sf
+
+
+def gemm_mx(a, sfa, b, sfb, out, bias=None, residual=None, accumulate=False):
+    """out [M, N] bf16 (+)= a [M, K] b [N, K]^T with e4m3 operands and their block scales."""
+    lib = require()
+    _mx_sigs(lib)
+    M, K = a.shape
+    N = b.shape[0]
+    rc = lib.sb_gemm_mx(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual),
+                        M, N, K, a.stride(0), b.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                        int(accumulate), status_word(out.device).data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_mx failed (code {rc}): M={M} N={N} K={K}")
+    _count()
+    return out
+
+
+def _mx_weight(w):
+    """(row-wise quantised w [N, K], its scales, row-wise quantised w^T [K, N], its scales), cached per parameter update:
+    the forward contracts over K, the input-gradient product over N."""
+    cache = getattr(w, "_mx_cache", None)
+    if cache is None or cache[0] != PARAM_EPOCH:
+        wd = w.detach()
+        cache = (PARAM_EPOCH,) + mx_quantize(wd) + mx_quantize(wd, transposed=True)
+        w._mx_cache = cache
+    return cache[1:]
+
+
+class _LinearMX(torch.autograd.Function):
+    """Projection with block-scaled fp8 operands (MXFP8: e4m3 data, one power-of-two scale per 32 elements of the
+    contraction, applied inside `tcgen05.mma.kind::mxf8f6f4.block_scale`): every product gets operands quantised along
+    its own contraction dimension, so activations and output gradients are quantised twice (row-wise for the forward /
+    input-gradient products, transposed for the weight-gradient product) and weights twice per optimizer step.  No amax
+    history and no global scale: outliers only cost the 32 values that share their block."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = _rows(x)
+        xq, sx = mx_quantize(x2)
+        wq, sw, wtq, swt = _mx_weight(w)
+        out = _alloc((x2.shape[0], w.shape[0]), dtype=bf16, device=x.device)
+        r2 = _rows(residual) if residual is not None else None
+        gemm_mx(xq, sx, wq, sw, out, bias=bias, residual=r2)
+        xtq, sxt = mx_quantize(x2, transposed=True) if w.requires_grad else (None, None)
+        ctx.save_for_backward(xtq, sxt, wtq, swt)
+        ctx.has_bias, ctx.has_res, ctx.xshape, ctx.wref = bias is not None, residual is not None, x.shape, w
+        return out.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        xtq, sxt, wtq, swt = ctx.saved_tensors
+        g2 = _rows(gy)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gq, sg = mx_quantize(g2)
+            gx = _alloc((g2.shape[0], wtq.shape[0]), dtype=bf16, device=gy.device)
+            gemm_mx(gq, sg, wtq, swt, gx)                                   # dX = dY W: contraction over the outputs
+            gx = gx.view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            gtq, sgt = mx_quantize(g2, transposed=True)
+            wp = ctx.wref
+            tgt = wp.grad if getattr(wp, "_fuse_grad_accum", False) else None
+            if tgt is not None and tgt.dtype == bf16 and tgt.is_contiguous() and tgt.shape == wp.shape:
+                gemm_mx(gtq, sgt, xtq, sxt, tgt, accumulate=True)           # dW += dY^T X: contraction over the rows
+            else:
+                gw = _alloc(wp.shape, dtype=bf16, device=gy.device)
+                gemm_mx(gtq, sgt, xtq, sxt, gw)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = colsum(g2).to(gy.dtype)
+        gr = gy if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        return gx, gw, gb, gr
+
+
 def linear(x, w, bias=None, fp8: bool = False, residual=None):
+    if fp8 and FP8_RECIPE == "mxfp8" and _is_bf16(x, w, bias, residual) and w.shape[0] % 32 == 0 and w.shape[1] % 32 == 0 \
+            and (x.numel() // x.shape[-1]) % 32 == 0:
+        return _LinearMX.apply(x, w, bias, residual)
     if fp8 and _is_bf16(x, w, bias, residual) and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0:
         return _LinearFP8.apply(x, w, bias, residual)
     if not _is_bf16(x, w, bias, residual) or (w.shape[0] % 8) or (w.shape[1] % 8):
@@ -757,7 +873,8 @@ def mlp_gated(x, norm_weight, eps, form, w12, w3, b3, act, fp8):
 
 
 def _fp8_fusable(x, w, *others) -> bool:
-    return (FP8_HISTORY > 0 and _is_bf16(x, w, *others) and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0
+    # the norm / gate kernels write per-tensor (delayed-scaling) fp8 operands: not with the block-scaled recipe
+    return (FP8_HISTORY > 0 and FP8_RECIPE == "delayed" and _is_bf16(x, w, *others) and w.shape[0] % 16 == 0 and w.shape[1] % 16 == 0
             and x.shape[-1] % 16 == 0)
 
 

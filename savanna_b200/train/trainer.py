@@ -96,6 +96,7 @@ class Trainer:
         if self.device.type == "cuda":
             from ..ops import cuda_ops
             cuda_ops.set_fp8_history(cfg.fp8_amax_history_len)
+            cuda_ops.set_fp8_recipe(cfg.fp8_recipe)
             from ..ops import attention_cuda
             attention_cuda.set_allow_library(bool(cfg.allow_library_attention))
         if (self.device.type == "cuda" and cfg.comm_path == "symm" and cfg.sequence_parallel

@@ -664,3 +664,139 @@ def test_peer_barrier_wait_runs_out_and_reports():
     cuda_ops.check_status()                             # the word was cleared; the context still works
     a = torch.ones(8, device=DEV)
     assert float((a + a).sum()) == 16.0
+
+
+# ----------------------------------------------------------------------------- block-scaled fp8 (MXFP8)
+from savanna_b200.ops import cuda_ops  # noqa: E402
+
+
+def _done():
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+
+
+def _mx_reference_quantize(x, transposed=False):
+    """PyTorch statement of the MXFP8 quantiser: per 32 elements of the contraction e = ceil(log2(amax / 448)),
+    q = e4m3(x / 2^e).  Returns (q as float, e as int tensor, the de-quantised tensor) in operand orientation [rows, K]."""
+    xf = x.float().t().contiguous() if transposed else x.float()
+    R, K = xf.shape
+    blocks = xf.view(R, K // 32, 32)
+    amax = blocks.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax / 448.0)), torch.full_like(amax, -127.0)).clamp(-127, 127)
+    scale = torch.exp2(e)[..., None]
+    q = (blocks / scale).to(torch.float8_e4m3fn).float()
+    return q.view(R, K), e.to(torch.int32), (q * scale).view(R, K)
+
+
+def _mx_unpack_scales(sf, rows, k):
+    """E8M0 bytes of the kernel's atom layout -> [rows, k / 32] exponents."""
+    kb = (k + 127) // 128
+    atoms = sf.view((rows + 127) // 128, kb, 32, 4, 4)          # [row tile, k-block, r % 32, r // 32, k4]
+    full = atoms.permute(0, 3, 2, 1, 4).reshape(-1, kb * 4)      # rows = tile * 128 + (r // 32) * 32 + r % 32
+    return full[:rows, : k // 32].to(torch.int32) - 127
+
+
+@pytest.mark.parametrize("shape", [(256, 256), (192, 416), (64, 4096)])
+@pytest.mark.parametrize("transposed", [False, True])
+def test_mx_quantize_matches_the_block_scaling_rule(shape, transposed):
+    torch.manual_seed(41)
+    R, C = shape
+    x = (torch.randn(R, C, device=DEV) * torch.exp(torch.randn(R, 1, device=DEV) * 2)).to(BF)
+    x[3, :40] = 0
+    q, sf = cuda_ops.mx_quantize(x, transposed)
+    _done()
+    qr, er, _ = _mx_reference_quantize(x, transposed)
+    rows, k = (C, R) if transposed else (R, C)
+    assert q.shape == (rows, k)
+    e = _mx_unpack_scales(sf, rows, k)
+    assert torch.equal(e, er), (e - er).abs().max()
+    assert torch.equal(q.view(torch.float8_e4m3fn).float(), qr)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 512, 1024), (200, 328, 416), (1024, 4096, 4096)])
+def test_mx_gemm_against_dequantised_fp32(shape):
+    """The block-scaled tensor-core product against fp32 matmul of the de-quantised operands: only the summation order
+    differs, so the tolerance is tight."""
+    torch.manual_seed(42)
+    M, N, K = shape
+    a = (torch.randn(M, K, device=DEV) * torch.exp(torch.randn(M, 1, device=DEV))).to(BF)
+    b = (torch.randn(N, K, device=DEV) * 0.05 * torch.exp(torch.randn(1, K, device=DEV))).to(BF)
+    aq, sa = cuda_ops.mx_quantize(a)
+    bq, sb_ = cuda_ops.mx_quantize(b)
+    bias = torch.randn(N, device=DEV, dtype=BF)
+    res = torch.randn(M, N, device=DEV, dtype=BF)
+    out = torch.empty(M, N, device=DEV, dtype=BF)
+    cuda_ops.gemm_mx(aq, sa, bq, sb_, out, bias=bias, residual=res)
+    _done()
+    _, _, ad = _mx_reference_quantize(a)
+    _, _, bd = _mx_reference_quantize(b)
+    want = ad @ bd.t() + bias.float() + res.float()
+    _close(out, want, rtol=1e-2, atol=5e-3, what="mx gemm")
+    acc = out.clone()
+    cuda_ops.gemm_mx(aq, sa, bq, sb_, acc, accumulate=True)
+    _done()
+    _close(acc, out.float() + ad @ bd.t(), rtol=1e-2, atol=1e-2, what="mx gemm accumulate")
+
+
+def test_mx_linear_forward_and_gradients_track_bf16():
+    """`fp8_recipe: mxfp8` projection: output and all gradients against the fp32 statement, at the accuracy of e4m3
+    operands with per-32 scales (a few percent of the rms, no dependence on outliers elsewhere in the tensor)."""
+    torch.manual_seed(43)
+    T, K, N = 512, 1024, 768
+    x = torch.randn(2, T // 2, K, device=DEV, dtype=BF, requires_grad=True)
+    x.data[0, 0, 0] = 300.0                                      # an outlier only costs its own block
+    w = (torch.randn(N, K, device=DEV) * 0.03).to(BF).requires_grad_()
+    b = torch.randn(N, device=DEV, dtype=BF, requires_grad=True)
+    cuda_ops.set_fp8_recipe("mxfp8")
+    try:
+        y = cuda_ops.linear(x, w, b, fp8=True)
+        g = torch.randn_like(y)
+        y.backward(g)
+    finally:
+        cuda_ops.set_fp8_recipe("delayed")
+    _done()
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    _rel(y, yr, 4e-2, "mx linear fwd")
+    _rel(x.grad, xr.grad, 4e-2, "mx linear dx")
+    _rel(w.grad, wr.grad, 4e-2, "mx linear dw")
+    _rel(b.grad, br.grad, 1e-2, "mx linear db")
+
+
+def test_mxfp8_training_tracks_bf16():
+    """Same tiny model, same data: the loss trace with block-scaled fp8 projections (`fp8_recipe: mxfp8`) stays close to
+    the bf16 one, and the block-scaled function is what ran."""
+    import os
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    traces = []
+    calls = {"n": 0}
+    orig = cuda_ops.gemm_mx
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+    try:
+        for mx in (False, True):
+            over = {"global_num_gpus": 1}
+            if mx:
+                over.update({"use_fp8_linears": True, "use_fp8_input_projections": True, "use_fp8_output_projections": True,
+                             "use_fp8_mlp_projections": True, "fp8_recipe": "mxfp8"})
+                cuda_ops.gemm_mx = counting
+            cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_gpu.yml")], over)
+            tr = Trainer(cfg, load=False)
+            batches = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i).cuda()} for i in range(30)])
+            traces.append([float(tr.train_step(batches)) for _ in range(30)])
+            state.destroy_model_parallel()
+    finally:
+        cuda_ops.gemm_mx = orig
+        cuda_ops.set_fp8_recipe("delayed")
+    a, b = traces
+    assert calls["n"] > 0
+    assert b[-1] < b[0] - 1.5, b
+    assert abs(a[-1] - b[-1]) < 0.06 * a[-1], (a[-1], b[-1])
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.2, (a, b)
