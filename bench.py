@@ -201,7 +201,10 @@ def describe_metric(cfg, pstate, config_path: str) -> str:
 def describe_dtype(cfg, fused_tp_fp8) -> str:
     if not cfg.use_fp8_linears:
         return "bf16"
-    d = "bf16 + fp8 (e4m3/e5m2, per-tensor delayed scaling) projection GEMMs"
+    if getattr(cfg, "fp8_recipe", "delayed") == "mxfp8":
+        d = "bf16 + block-scaled fp8 (MXFP8: e4m3, one E8M0 scale per 32 elements) projection GEMMs"
+    else:
+        d = "bf16 + fp8 (e4m3/e5m2, per-tensor delayed scaling) projection GEMMs"
     if fused_tp_fp8 is False:
         d += " [fused tensor-parallel projections ran bf16 operands]"
     return d
@@ -458,6 +461,10 @@ def main():
     if not args.extra_only:
         main_res = measure(args.config, fp8_over if use_fp8 else {}, args.steps, args.warmup, not args.no_e2e)
         other = measure(args.config, {}, args.steps, args.warmup, False) if (use_fp8 and not args.skip_second) else None
+        # the block-scaled recipe on one GPU, beside the headline (its projections run without tensor parallelism only)
+        mx = None
+        if use_fp8 and not args.skip_second and world == 1 and not any(k == "fp8_recipe" for k in over):
+            mx = measure(args.config, dict(fp8_over, fp8_recipe="mxfp8"), args.steps, args.warmup, False)
         cfg = main_res["cfg"]
         L, B, gas = cfg.seq_length, cfg.train_micro_batch_size_per_gpu, cfg.gradient_accumulation_steps
         fpt = model_flops_per_token(cfg)
@@ -485,6 +492,8 @@ def main():
             "bf16_only": None if other is None else {"value": other["value"], "ms_per_step": other["ms_per_step"],
                                                      "loss": other["loss"], "dtype": "bf16",
                                                      "mfu_of_measured_peak": other["mfu_reference_accounting"]},
+            "mxfp8": None if mx is None else {"value": mx["value"], "ms_per_step": mx["ms_per_step"], "loss": mx["loss"],
+                                              "dtype": mx["dtype"]},
         }
     printed = threading.Event()
 
