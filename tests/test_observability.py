@@ -79,3 +79,65 @@ def test_alloc_stats_warns_when_the_allocator_goes_back_to_the_driver():
     counters["num_device_alloc"] = 12
     assert w.step(10) is True and w.changes == 1 and "rank=3" in lines[0]
     assert w.step(11) is False
+
+
+def test_torch_profiler_records_the_step_marks_with_expected_counts(tmp_path):
+    """A short CPU run under `profiler_type: torch`: one trace per schedule cycle is written, the key-averages table
+    exists, and the three training marks appear once per micro-batch / optimizer step of the active window
+    (role of the reference's tests/functional/test_profiler.py)."""
+    import glob
+    import gzip
+    import json
+    import os
+    import torch
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "prof")
+    active, gas = 2, 2
+    cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")], {
+        "global_num_gpus": 1, "train_iters": 5, "gradient_accumulation_steps": gas, "should_profile": True,
+        "profiler_type": "torch", "profiler_output_dir": out, "profile_cpu": True, "profile_cuda": False,
+        "profiler_schedule_wait": 1, "profiler_schedule_warmup": 1, "profiler_schedule_active": active,
+        "profiler_schedule_repeat": 1, "log_interval": 100, "eval_interval": 1000, "save": None, "load": None})
+    tr = Trainer(cfg, load=False)
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    tr.train(it())
+    traces = glob.glob(os.path.join(out, "rank0_step*.pt.trace.json.gz"))
+    assert len(traces) == 1, os.listdir(out)
+    assert glob.glob(os.path.join(out, "key_averages_step*.txt"))
+    with gzip.open(traces[0], "rt") as fh:
+        events = json.load(fh)["traceEvents"]
+    names = [e.get("name") for e in events if e.get("cat") in ("user_annotation", "cpu_op") or e.get("ph") == "X"]
+    count = lambda n: sum(1 for x in names if x == n)          # noqa: E731
+    assert count("TRAIN_STEP_FORWARD") == active * gas
+    assert count("TRAIN_STEP_BACKWARD") == active * gas
+    assert count("TRAIN_STEP_OPTIMIZER_STEP") == active
+
+
+def test_cuda_profiler_window_and_nsys_command():
+    """The capture-range profiler opens its window after `nsys_warmup_steps` steps and closes it `nsys_num_steps` later;
+    the nsys command line wraps the training command with the capture-range flags."""
+    import types
+    from savanna_b200.utils.profiler import CudaProfiler, EmptyProfiler, build_nsys_command, setup_profiler
+    cfg = types.SimpleNamespace(disable_autograd_multithreading=False, nsys_warmup_steps=2, nsys_num_steps=3, emit_nvtx=False,
+                                profile_record_shapes=False, should_profile=True, profiler_type="nsys", profile_ranks=[0],
+                                rank=0, nsys_stop_on_exit=True)
+    p = setup_profiler(cfg)
+    assert isinstance(p, CudaProfiler)
+    states = []
+    for _ in range(7):
+        p.step()
+        states.append(p.running)
+    assert states == [False, True, True, True, False, False, False]
+    cfg.rank = 1
+    assert type(setup_profiler(cfg)) is EmptyProfiler            # not a profiled rank
+    cmd = build_nsys_command(cfg, ["python", "train.py"], "out")
+    assert cmd[0] == "nsys" and "--capture-range=cudaProfilerApi" in cmd and "--capture-range-end=stop" in cmd
+    assert cmd[-2:] == ["python", "train.py"]
