@@ -459,7 +459,17 @@ def main():
     use_fp8 = not args.bf16_only and own
     out = {}
     if not args.extra_only:
-        main_res = measure(args.config, fp8_over if use_fp8 else {}, args.steps, args.warmup, not args.no_e2e)
+        try:
+            main_res = measure(args.config, fp8_over if use_fp8 else {}, args.steps, args.warmup, not args.no_e2e)
+        except torch.OutOfMemoryError as exc:
+            if args.impl != "torch":
+                raise
+            # the library stand-in keeps far more intermediates than this framework's operators
+            if rank == 0:
+                print(json.dumps({"impl": "torch", "unavailable": "the PyTorch / library operator stand-in runs out of "
+                                  "device memory at this configuration even with per-layer activation checkpointing "
+                                  f"({str(exc)[:120]}); compare both arms with the same --layers / --accum truncation"}), flush=True)
+            return
         other = measure(args.config, {}, args.steps, args.warmup, False) if (use_fp8 and not args.skip_second) else None
         # the block-scaled recipe on one GPU, beside the headline (its projections run without tensor parallelism only)
         mx = None
