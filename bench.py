@@ -432,7 +432,9 @@ def main():
         def trace_check():
             ops4 = ["hyena_se", "hyena_mr", "hyena", "ring"]
             Lc = 8192 * world
-            base = dict(fp8_over, num_layers=4, seq_length=Lc, max_position_embeddings=Lc, gradient_accumulation_steps=1,
+            # all-bf16 on both arms: the check is about the context-parallel paths (halo, all-to-all, ring), and fp8
+            # rounding noise is amplified many times over in the first steps, where the loss falls from ln(512) steeply
+            base = dict(num_layers=4, seq_length=Lc, max_position_embeddings=Lc, gradient_accumulation_steps=1,
                         checkpoint_activations=False)
             a = measure(cp_cfg, dict(base, context_parallel_size=world, operator_config=ops4), 2, 1, False,
                         same_data_on_all_ranks=True, keep_losses=True)
@@ -442,7 +444,7 @@ def main():
             gap = max(abs(x - y) / max(1.0, abs(y)) for x, y in zip(a["losses"], b["losses"]))
             return {"seq_len": Lc, "layers": ops4, "steps": len(a["losses"]), "cp_losses": a["losses"],
                     "single_shard_losses": b["losses"], "max_rel_gap": gap, "tolerance": 2e-2, "match": bool(gap < 2e-2),
-                    "paths": a["paths"]}
+                    "dtype": "bf16 (both arms)", "paths": a["paths"]}
 
         def tp_run():
             r = brief(measure(os.path.join(CFG_DIR, "evo2_40b_tp8.yml"), dict(fp8_over), 2, 1, False))

@@ -17,6 +17,8 @@
 //
 // All waits are bounded (sm100.cuh); on a timeout the kernel records a status word, every role unwinds,
 // TMEM is freed and the kernel returns.
+#include <cuda_fp8.h>
+
 #include "sm100.cuh"
 
 namespace sb {
@@ -41,6 +43,14 @@ struct GemmParams {
   const float* alpha;          // device scalar multiplied into the accumulator (fp8 de-quantisation), or null
   const float* alpha2;         // second device scalar (the other operand's de-quantisation factor), or null
   int a_fmt, b_fmt;            // fp8 operand formats for the instruction descriptor: 0 = e4m3, 1 = e5m2
+  // gated-MLP epilogue of the CTA-pair kernel (GLU mode): B = [w1 ; w2] with F rows each, C = [a | b] (ldc >= 2 F);
+  // besides C the epilogue writes q = e4m3(silu(a) * b) [M, F] under delayed scaling (ring `hist` of `slots` floats,
+  // this call's slot `cur`, de-quantisation factor to `scale_inv`)
+  uint8_t* glu_q;
+  int glu_F;
+  float* glu_hist;
+  int glu_slots, glu_cur;
+  float* glu_scale_inv;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
@@ -266,7 +276,12 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_ti
   nt = r / gsz;
 }
 
-template <int A_MN, int B_MN, int EB>
+// GLU = 1 (K-major one-byte operands only): output tile t covers features [128 t, 128 t + 128) of BOTH halves of the
+// packed gate projection: the even CTA stages the w1 rows of those features, the odd CTA the w2 rows, so accumulator
+// columns 0-127 hold a and 128-255 hold b of the same features, and the epilogue applies the gate on the spot: it
+// stores a and b (bf16, for the backward) and the e4m3 operand of the following projection, which the separate gate
+// kernel otherwise produces by re-reading [a | b] from memory.
+template <int A_MN, int B_MN, int EB, int GLU = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -284,7 +299,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();             // 0: issues the MMAs, 1: partner
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + BN - 1) / BN;
+  const int m_tiles = (p.M + 255) / 256, n_tiles = GLU ? p.glu_F / 128 : (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   constexpr int BKE = 128 / EB;
   constexpr int MNB = 128 / EB;
@@ -318,7 +333,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
         int mt, nt; pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
-        const int m0 = mt * 256 + int(rank) * 128, n0 = nt * BN + int(rank) * 128;
+        const int m0 = mt * 256 + int(rank) * 128;
+        const int n0 = GLU ? nt * 128 + int(rank) * p.glu_F : nt * BN + int(rank) * 128;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES;
@@ -388,6 +404,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int local = 0;
     bool ok = true;
     const float alpha = (p.alpha ? p.alpha[0] : 1.f) * (p.alpha2 ? p.alpha2[0] : 1.f);
+    float q_scale = 1.f, q_amax = 0.f;
+    if (GLU) {
+      // delayed scaling of the gated output: scale from the amax ring (all slots but this call's and the next one's)
+      const int nxt = p.glu_cur + 1 == p.glu_slots ? 0 : p.glu_cur + 1;
+      float a = 0.f;
+      for (int j = 0; j < p.glu_slots; ++j) {
+        if (j == p.glu_cur || j == nxt) continue;
+        const float h = p.glu_hist[j];
+        if (h > a && h < 3.0e38f) a = h;
+      }
+      if (!(a > 0.f)) a = 448.f;
+      if (blockIdx.x == 0 && warp == 2 && lane == 0) { p.glu_scale_inv[0] = a / 448.f; p.glu_hist[nxt] = 0.f; }
+      q_scale = 448.f / a;
+    }
     for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local) {
       const int acc = local & 1;
       int mt, nt; pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
@@ -398,6 +428,49 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nt * BN;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       __nv_bfloat16* crow = p.C + size_t(row) * p.ldc;
+      if (GLU) {
+        const int f0 = nt * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(t_row + c * 32, ra);
+          tmem_ld_32x32(t_row + 128 + c * 32, rb);
+          tmem_wait_ld();
+          if (row < p.M) {
+            const int f = f0 + c * 32;
+            uint32_t qw[8];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 oa, ob;
+              __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+              __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+              float o[8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                a2[j] = __floats2bfloat162_rn(__uint_as_float(ra[v * 8 + 2 * j]) * alpha, __uint_as_float(ra[v * 8 + 2 * j + 1]) * alpha);
+                b2[j] = __floats2bfloat162_rn(__uint_as_float(rb[v * 8 + 2 * j]) * alpha, __uint_as_float(rb[v * 8 + 2 * j + 1]) * alpha);
+                // the gate on the bf16-rounded a and b (what the backward re-reads), its result rounded to bf16 as the
+                // separate gate kernel's is
+                const float2 af = __bfloat1622float2(a2[j]), bf = __bfloat1622float2(b2[j]);
+                o[2 * j] = __bfloat162float(__float2bfloat16_rn(af.x * __fdividef(1.f, 1.f + __expf(-af.x)) * bf.x));
+                o[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(af.y * __fdividef(1.f, 1.f + __expf(-af.y)) * bf.y));
+                q_amax = fmaxf(q_amax, fmaxf(fabsf(o[2 * j]), fabsf(o[2 * j + 1])));
+              }
+              *reinterpret_cast<uint4*>(crow + f + v * 8) = oa;
+              *reinterpret_cast<uint4*>(crow + p.glu_F + f + v * 8) = ob;
+              const unsigned short h0 = __nv_cvt_float2_to_fp8x2(make_float2(o[0] * q_scale, o[1] * q_scale), __NV_SATFINITE, __NV_E4M3);
+              const unsigned short h1 = __nv_cvt_float2_to_fp8x2(make_float2(o[2] * q_scale, o[3] * q_scale), __NV_SATFINITE, __NV_E4M3);
+              const unsigned short h2 = __nv_cvt_float2_to_fp8x2(make_float2(o[4] * q_scale, o[5] * q_scale), __NV_SATFINITE, __NV_E4M3);
+              const unsigned short h3 = __nv_cvt_float2_to_fp8x2(make_float2(o[6] * q_scale, o[7] * q_scale), __NV_SATFINITE, __NV_E4M3);
+              qw[2 * v] = uint32_t(h0) | (uint32_t(h1) << 16);
+              qw[2 * v + 1] = uint32_t(h2) | (uint32_t(h3) << 16);
+            }
+            uint4* qd = reinterpret_cast<uint4*>(p.glu_q + size_t(row) * p.glu_F + f);
+            qd[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+            qd[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -405,10 +478,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_wait_ld();
         store_chunk(p, row, n0 + c * 32, r, alpha, crow);
       }
+      }
       tc_fence_before();
       __syncwarp();
       // the MMA thread of the even CTA waits for the four epilogue warps of both CTAs
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+    }
+    if (GLU) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) q_amax = fmaxf(q_amax, __shfl_xor_sync(0xffffffffu, q_amax, o));
+      if (lane == 0 && q_amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.glu_hist + p.glu_cur), __float_as_uint(q_amax));
     }
   }
   tc_fence_before();
@@ -569,6 +648,49 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   }
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}
+
+// Gate projection of the gated MLP with the gate in the epilogue (CTA-pair kernel, GLU mode): AB [M, 2 F] bf16 =
+// alpha * A [M, K] * W12 [2 F, K]^T with e4m3 operands, and Q [M, F] = e4m3(silu(a) * b) under delayed scaling (ring
+// protocol of sb_quantize_fp8_delayed: `hist` of `slots` floats, slot `cur` collects this call's amax, `scale_inv`
+// receives the de-quantisation factor).  F % 128 == 0, K % 16 == 0.
+extern "C" int sb_gemm_fp8_glu(const void* A, const void* W12, void* AB, void* Q, const float* alpha, const float* alpha2, int M,
+                               int F, int K, int lda, int ldb, int ldab, float* hist, int slots, int cur, float* scale_inv,
+                               unsigned int* status, cudaStream_t stream) {
+  using namespace sb;
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
+  if ((F % 128) || (K % 16) || (lda % 16) || (ldb % 16) || (ldab % 8) || ldab < 2 * F || slots < 3 || cur < 0 || cur >= slots) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W12) | reinterpret_cast<uintptr_t>(AB) |
+       reinterpret_cast<uintptr_t>(Q)) & 15) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if ((rc = make_tmap_2d_u8(&tmA, A, K, M, lda, 128, BM))) return rc;
+  if ((rc = make_tmap_2d_u8(&tmB, W12, K, 2 * F, ldb, 128, 128))) return rc;
+  if (!g_num_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev); }
+  GemmParams p{reinterpret_cast<__nv_bfloat16*>(AB), nullptr, nullptr, M, 2 * F, K, ldab, 0, 0, status, alpha, alpha2, 0, 0,
+               reinterpret_cast<uint8_t*>(Q), F, hist, slots, cur, scale_inv};
+  auto kern = gemm_pair_kernel<0, 0, 1, 1>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  const int tiles = ((M + 255) / 256) * (F / 128);
+  int pairs = g_num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? 0 : -6;
 }
 
 // fp8 GEMM: C[M,N] (bf16) = alpha * A * B^T (+bias) (+residual) (+C) with one-byte operands (e4m3 = 0 / e5m2 = 1) and

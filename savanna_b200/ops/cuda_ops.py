@@ -258,9 +258,14 @@ def set_conv_forward_variant(tiled: bool) -> None:
     require().sb_conv_set_fwd_variant(int(bool(tiled)))
 
 
+_PAIR_MODE = 2
+
+
 def set_gemm_pair_mode(mode: int) -> None:
     """0: one CTA per 128 x 256 tile; 1: CTA pairs (cta_group::2, 256 x 256 tiles) for fp8 operands; 2: for bf16 too."""
+    global _PAIR_MODE
     require().sb_gemm_set_pair_mode(int(mode))
+    _PAIR_MODE = int(mode)
 
 
 def colsum(x2: torch.Tensor) -> torch.Tensor:
@@ -408,6 +413,36 @@ def gemm_fp8(a, b, out, alpha, a_mn=False, b_mn=False, a_fmt=E4M3, b_fmt=E4M3, b
         raise RuntimeError(f"gemm_fp8 failed (code {rc}): M={M} N={N} K={K} a{tuple(a.shape)} b{tuple(b.shape)} a_mn={a_mn} b_mn={b_mn}")
     _count()
     return out
+
+
+# gated MLP: apply the gate in the epilogue of the w1|w2 projection (CTA-pair fp8 kernel); SAVANNA_B200_GLU_EPILOGUE=0
+# selects the separate gate kernel (A/B measurements)
+GLU_EPILOGUE = os.environ.get("SAVANNA_B200_GLU_EPILOGUE", "1") != "0"
+
+
+def set_glu_epilogue(on: bool) -> None:
+    global GLU_EPILOGUE
+    GLU_EPILOGUE = bool(on)
+
+
+def gemm_fp8_glu(xq, w12q, ab, hq, sx, s12, site, sh):
+    """ab [T, 2F] = (x w12^T) de-quantised, hq [T, F] = e4m3(silu(a) * b) under the delayed scaling of `site` (advances
+    its ring); sh receives hq's de-quantisation factor."""
+    lib = require()
+    if not getattr(lib, "_sb_glu_ready", False):
+        P, I = ctypes.c_void_p, ctypes.c_int
+        lib.sb_gemm_fp8_glu.restype = I
+        lib.sb_gemm_fp8_glu.argtypes = [P, P, P, P, P, P, I, I, I, I, I, I, P, I, I, P, P, P]
+        lib._sb_glu_ready = True
+    T, K = xq.shape
+    F = hq.shape[1]
+    rc = lib.sb_gemm_fp8_glu(xq.data_ptr(), w12q.data_ptr(), ab.data_ptr(), hq.data_ptr(), sx.data_ptr(), s12.data_ptr(), T, F, K,
+                             xq.stride(0), w12q.stride(0), ab.stride(0), site.buf.data_ptr(), site.buf.numel(), site.cur,
+                             sh.data_ptr(), status_word(ab.device).data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_fp8_glu failed (code {rc}): T={T} F={F} K={K}")
+    _count()
+    site.cur = (site.cur + 1) % site.buf.numel()
 
 
 def _fp8_weight(w):
@@ -803,8 +838,17 @@ class _MlpFP8(torch.autograd.Function):
             hx.cur = (hx.cur + 1) % hx.buf.numel()
         w12q, s12 = _fp8_weight(w12)
         ab = _alloc((T, F2), dtype=bf16, device=dev)
-        gemm_fp8(xq, w12q, ab, sx, alpha2=s12)
-        if not hh.primed:
+        fuse_gate = hh.primed and act == 0 and Fh % 128 == 0 and GLU_EPILOGUE and _PAIR_MODE >= 1
+        if fuse_gate:
+            # the gate runs in the epilogue of the w1|w2 projection: [a | b] and the e4m3 operand of w3 from one kernel
+            hq = _alloc((T, Fh), dtype=torch.uint8, device=dev)
+            sh = _alloc(1, dtype=torch.float32, device=dev)
+            gemm_fp8_glu(xq, w12q, ab, hq, sx, s12, hh, sh)
+        else:
+            gemm_fp8(xq, w12q, ab, sx, alpha2=s12)
+        if fuse_gate:
+            pass
+        elif not hh.primed:
             hb = _alloc((T, Fh), dtype=bf16, device=dev)
             _check(lib.sb_glu_fwd(ab.data_ptr(), hb.data_ptr(), T, Fh, act, _stream()), "glu_fwd")
             _count()

@@ -800,3 +800,39 @@ def test_mxfp8_training_tracks_bf16():
     assert b[-1] < b[0] - 1.5, b
     assert abs(a[-1] - b[-1]) < 0.06 * a[-1], (a[-1], b[-1])
     assert max(abs(x - y) for x, y in zip(a, b)) < 0.2, (a, b)
+
+
+def test_gate_in_the_projection_epilogue_matches_the_separate_gate_kernel():
+    """The gated MLP with the gate applied in the epilogue of the w1|w2 projection (CTA-pair fp8 kernel, GLU mode) against
+    the same function with the separate gate kernel: identical [a | b], identical e4m3 operand of w3 (same scale, same
+    rounding), same amax history, same output and gradients."""
+    torch.manual_seed(51)
+    T, D, F = 384, 512, 1024
+    x = torch.randn(1, T, D, device=DEV, dtype=BF)
+    wn = (1 + 0.1 * torch.randn(D, device=DEV)).to(BF)
+    w12 = (torch.randn(2 * F, D, device=DEV) * 0.05).to(BF)
+    w3 = (torch.randn(D, F, device=DEV) * 0.05).to(BF)
+    b3 = torch.randn(D, device=DEV, dtype=BF)
+    outs = []
+    for fused in (False, True):
+        cuda_ops.set_glu_epilogue(fused)
+        ps = [t.clone().requires_grad_() for t in (x, wn, w12, w3, b3)]
+        try:
+            for _ in range(3):                                   # the third call runs on primed amax histories
+                for t in ps:
+                    t.grad = None
+                before = cuda_ops.launch_count()
+                y = cuda_ops.mlp_gated(ps[0], ps[1], 1e-5, "te", ps[2], ps[3], ps[4], "silu", True)
+                launches = cuda_ops.launch_count() - before
+                y.backward(torch.ones_like(y) * 0.01)
+        finally:
+            cuda_ops.set_glu_epilogue(True)
+        _done()
+        outs.append((y.detach().float(), [t.grad.float() for t in ps], launches,
+                     ps[3]._fp8_sites["x"].buf.clone()))
+    (y0, g0, n0, h0), (y1, g1, n1, h1) = outs
+    assert n1 == n0 - 1, (n0, n1)                                 # one kernel fewer in the forward
+    assert torch.equal(h0, h1), (h0, h1)                          # same amax history of the gated activation
+    assert torch.equal(y0, y1)
+    for a, b, name in zip(g0, g1, ("dx", "dwn", "dw12", "dw3", "db3")):
+        assert torch.equal(a, b), name
