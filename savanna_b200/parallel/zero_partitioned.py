@@ -94,16 +94,36 @@ class UnitFlat:
         self.resident = True
         self.grads_live = True
         self.gather_work = None
+        # hpZ: a secondary copy of the parameters partitioned over a small sub-group (see the optimizer)
+        self.hpz_world, self.hpz_rank, self.hpz_group = 1, 0, None
+        self.hpz_shard: Optional[torch.Tensor] = None
+        self.hpz_fresh = False
+        self.hpz_gathers = 0
 
     def shard_slice(self, t: torch.Tensor) -> torch.Tensor:
         return t[self.rank * self.shard:(self.rank + 1) * self.shard]
 
     # -- parameters ----------------------------------------------------------------
-    def start_gather(self, group, async_op: bool) -> None:
+    def start_gather(self, group, async_op: bool, secondary: bool = False) -> None:
+        """`secondary`: gather from the hpZ copy over the sub-group when it is up to date (the backward pass)."""
         if self.resident or self.gather_work is not None:
             return
         self.full.untyped_storage().resize_(self.nbytes)
-        self.gather_work = _all_gather(self.full, self.param_shard, group, self.world, async_op) or True
+        if secondary and self.hpz_world > 1 and self.hpz_fresh:
+            self.hpz_gathers += 1
+            self.gather_work = _all_gather(self.full, self.hpz_shard, self.hpz_group, self.hpz_world, async_op) or True
+        else:
+            self.gather_work = _all_gather(self.full, self.param_shard, group, self.world, async_op) or True
+
+    def keep_secondary(self) -> None:
+        """Before the whole parameters are released after the forward pass: keep this rank's 1 / hpz_world slice."""
+        if self.hpz_world <= 1 or self.hpz_fresh or not self.resident or not self.free_params:
+            return
+        n = self.padded // self.hpz_world
+        if self.hpz_shard is None:
+            self.hpz_shard = torch.empty(n, dtype=self.full.dtype, device=self.full.device)
+        self.hpz_shard.copy_(self.full[self.hpz_rank * n:(self.hpz_rank + 1) * n])
+        self.hpz_fresh = True
 
     def wait_gather(self) -> None:
         if self.gather_work is not None:
@@ -152,7 +172,8 @@ class PartitionedZeroOptimizer:
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, adamw: bool = True,
                  clip_grad: float = 0.0, group=None, group_ranks: Optional[List[int]] = None,
                  grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
-                 sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0):
+                 sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0,
+                 hpz_group=None, hpz_ranks: Optional[List[int]] = None):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
         self.stage = stage
@@ -208,6 +229,16 @@ class PartitionedZeroOptimizer:
                              free_params=(stage == 3 and not root), free_grads=not root, tp=tp)
                 unit.flats.append(f)
                 self.groups.append(f)
+        # hpZ (`zero_hpz_partition_size`, stage 3): after a unit's forward all-gather over the whole group, every rank keeps
+        # its 1 / hpz slice of the whole parameters, partitioned over a small sub-group (the GPUs of one node); the
+        # backward (and recomputation) gathers then run inside the sub-group only.  Costs padded / hpz elements per rank
+        # and unit; the copies go stale when the optimizer updates the parameters.
+        self.hpz_world = len(hpz_ranks) if (hpz_ranks and stage == 3) else 1
+        if self.hpz_world > 1:
+            if self.world % self.hpz_world:
+                raise ValueError(f"zero_hpz_partition_size {self.hpz_world} does not divide the partition group size {self.world}")
+            for f in self.groups:
+                f.hpz_world, f.hpz_rank, f.hpz_group = self.hpz_world, hpz_ranks.index(me), hpz_group
         self.backward_phase = False
         self.pending: List = []                     # (work, flat, shard view) reductions in flight
         self._handles = []
@@ -225,7 +256,7 @@ class PartitionedZeroOptimizer:
 
     def _ensure_resident(self, u: Unit) -> None:
         for f in u.flats:
-            f.start_gather(self.group, False)
+            f.start_gather(self.group, False, secondary=self.backward_phase)
         for f in u.flats:
             f.wait_gather()
 
@@ -233,7 +264,7 @@ class PartitionedZeroOptimizer:
         if self.stage != 3 or not self._async() or idx < 1 or idx >= len(self.units):
             return
         for f in self.units[idx].flats:
-            f.start_gather(self.group, True)
+            f.start_gather(self.group, True, secondary=self.backward_phase)
 
     def _make_pre_forward(self, u: Unit):
         def hook(module, args):
@@ -255,6 +286,7 @@ class PartitionedZeroOptimizer:
                         o.register_hook(self._make_pre_backward(u))
                         break
             for f in u.flats:
+                f.keep_secondary()
                 f.release_params()
             return None
         return hook
@@ -377,6 +409,7 @@ class PartitionedZeroOptimizer:
             ops.adam_step(f.master, f.exp_avg, f.exp_avg_sq, f.grad_acc, f.hyper["lr"], b1, b2, self.eps,
                           f.hyper["weight_decay"], self.step_count, self.adamw, coef,
                           None if f.master_is_view else f.param_shard)
+            f.hpz_fresh = False                       # the secondary copies hold the old parameters
             if not f.free_params:
                 _all_gather(f.full, f.param_shard, self.group, self.world)
         return norm

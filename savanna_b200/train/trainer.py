@@ -168,6 +168,11 @@ class Trainer:
                     me = dist.get_rank() if dist.is_initialized() else 0
                     mics = {"replica_group": rgroup, "replica_world": len(rranks), "replica_index": rranks.index(me)}
                     print_rank_0(f" > MiCS: optimizer state sharded over sub-groups of {shard} ranks, {len(rranks)} replicas")
+                hpz = int((cfg.zero_optimization or {}).get("zero_hpz_partition_size", 1) or 1)
+                if hpz > 1 and cfg.zero_stage >= 3 and not mics and len(zranks) % hpz == 0 and hpz < len(zranks):
+                    hgroup, hranks, _, _ = state.create_mics_groups(hpz)
+                    mics = {"hpz_group": hgroup, "hpz_ranks": hranks}
+                    print_rank_0(f" > hpZ: secondary parameter partition over sub-groups of {hpz} ranks for the backward gathers")
                 optimizer = PartitionedZeroOptimizer(
                     groups, model.blocks(), stage=min(3, cfg.zero_stage), lr=cfg.lr,
                     betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8), weight_decay=cfg.weight_decay,

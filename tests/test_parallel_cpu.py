@@ -468,3 +468,29 @@ def test_symmetric_memory_door_reports_a_moved_api(monkeypatch):
     monkeypatch.setattr(symm, "_MODULE", fake.__name__)
     monkeypatch.setattr(symm.load, "__defaults__", (fake.__name__,))
     assert fused_zero.make_allocator(None) is None
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("ckpt_layers", [0, 1])
+def test_zero3_hpz_secondary_partition(ckpt_layers):
+    """Stage 3 over 4 ranks with `zero_hpz_partition_size: 2`: after a unit's forward gather every rank keeps its half of
+    the whole parameters, and the backward (and recomputation) gathers run inside the sub-group of 2; the loss trace
+    equals the single-process run and the secondary gathers are counted."""
+    ref_losses = _reference_losses(mb=4)
+    over = {"train_micro_batch_size_per_gpu": 1, "zero_optimization": {"stage": 3, "zero_hpz_partition_size": 2}}
+    if ckpt_layers:
+        over.update({"checkpoint_activations": True, "checkpoint_num_layers": ckpt_layers})
+    run_distributed(_w_hpz, 4, over, ref_losses)
+
+
+def _w_hpz(rank, world, over, ref_losses):
+    cfg = _tiny_cfg(world, **over)
+    tr, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    opt = tr.optimizer
+    assert opt.stage == 3 and opt.world == 4 and opt.hpz_world == 2
+    freed = [f for f in opt.groups if f.free_params]
+    assert freed and all(f.hpz_gathers > 0 for f in freed), [f.hpz_gathers for f in freed]
+    assert all(f.hpz_shard.numel() == f.padded // 2 for f in freed)
+    assert all(not f.hpz_fresh for f in freed)                  # stale after the optimizer step
