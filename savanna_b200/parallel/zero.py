@@ -33,8 +33,10 @@ def _pad_to(n: int, m: int) -> int:
 class FlatGroup:
     """One parameter group flattened into a parameter buffer and a gradient buffer."""
 
-    def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, allocator=None):
+    def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, allocator=None,
+                 offload: bool = False):
         self.params = params
+        self.offload = bool(offload)
         self.hyper = hyper
         dtype, device = params[0].dtype, params[0].device
         if any(p.dtype != dtype for p in params):
@@ -62,6 +64,16 @@ class FlatGroup:
         # fp32 parameters are their own master copy (the shard view is updated in place)
         self.master = self.flat_param[lo:hi] if dtype == torch.float32 else self.flat_param[lo:hi].float().clone()
         self.master_is_view = dtype == torch.float32
+        if self.offload:
+            # optimizer state in (pinned) host memory: the fp32 master copy of this rank's shard and both Adam moments;
+            # the step copies the reduced gradient shard to the host, updates there and copies the shard back
+            pin = device.type == "cuda"
+            self.master = self.flat_param[lo:hi].float().cpu()
+            if pin:
+                self.master = self.master.pin_memory()
+            self.master_is_view = False
+            self.host_grad = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
+            self.host_param = torch.zeros(self.shard, dtype=dtype, pin_memory=pin)
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.norm_weight: Optional[torch.Tensor] = None
@@ -89,8 +101,11 @@ class ZeroOptimizer:
                  weight_decay: float = 0.0, adamw: bool = True, clip_grad: float = 0.0,
                  group=None, group_ranks: Optional[List[int]] = None, comm_path: str = "nccl",
                  grad_divisor: Optional[float] = None, partition: bool = True, allocator=None,
-                 sum_ranks: Optional[int] = None):
+                 sum_ranks: Optional[int] = None, offload_optimizer: bool = False):
         self.group = group
+        # ZeRO-Offload (`zero_optimization.offload_optimizer.device: cpu`): master weights and Adam moments live in
+        # host memory and the update runs on the CPU; HBM then holds parameters, gradients and activations only
+        self.offload_optimizer = bool(offload_optimizer)
         ranks = group_ranks or [0]
         self.world = len(ranks) if partition else 1
         me = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
@@ -125,7 +140,7 @@ class ZeroOptimizer:
             for q in params:
                 by_dtype.setdefault(q.dtype, []).append(q)
             for dt, plist in by_dtype.items():
-                fg = FlatGroup(plist, self.world, self.rank, hyper, allocator)
+                fg = FlatGroup(plist, self.world, self.rank, hyper, allocator, offload=self.offload_optimizer)
                 fg.hyper = hyper                    # shared object: both flats follow the schedule
                 fg.build_norm_weight(tp)
                 self.groups.append(fg)
@@ -204,6 +219,21 @@ class ZeroOptimizer:
         else:
             coef = torch.full_like(norm, inv)
         b1, b2 = self.betas
+        if self.offload_optimizer:
+            from ..ops import reference as ref
+            coef_host = float(coef)                 # one synchronisation per step: the clip coefficient
+            for g, s in zip(self.groups, shards):
+                own = s if s.numel() == g.shard else g.shard_slice(s)
+                g.host_grad.copy_(own, non_blocking=True)
+            if self.groups and self.groups[0].flat_param.is_cuda:
+                torch.cuda.current_stream().synchronize()
+            for g in self.groups:
+                ref.adam_step(g.master, g.exp_avg, g.exp_avg_sq, g.host_grad, g.hyper["lr"], b1, b2, self.eps,
+                              g.hyper["weight_decay"], self.step_count, self.adamw, coef_host, None)
+                g.host_param.copy_(g.master)
+                g.shard_slice(g.flat_param).copy_(g.host_param, non_blocking=True)
+                self._all_gather(g)
+            return norm
         for g, s in zip(self.groups, shards):
             ops.adam_step(g.master, g.exp_avg, g.exp_avg_sq, s, g.hyper["lr"], b1, b2, self.eps,
                           g.hyper["weight_decay"], self.step_count, self.adamw, coef,

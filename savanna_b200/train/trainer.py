@@ -152,8 +152,12 @@ class Trainer:
         otype = cfg.optimizer_type
         if otype in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
             zranks = state.get_sequence_data_parallel_ranks()
+            off = (cfg.zero_optimization or {}).get("offload_optimizer") or {}
+            offload = isinstance(off, dict) and str(off.get("device", "none")).lower() == "cpu"
+            if offload and cfg.zero_stage >= 2:
+                raise NotImplementedError("offload_optimizer is implemented for ZeRO stages 0 and 1")
             use_symm = (self.device.type == "cuda" and cfg.comm_path == "symm" and len(zranks) > 1
-                        and cfg.zero_stage >= 1 and cfg.precision == "bfloat16")
+                        and cfg.zero_stage >= 1 and cfg.precision == "bfloat16" and not offload)
             allocator = None
             if use_symm:
                 from ..parallel import fused_zero
@@ -188,7 +192,9 @@ class Trainer:
                 groups, lr=cfg.lr, betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8),
                 weight_decay=cfg.weight_decay, adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
                 group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
-                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator)
+                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator, offload_optimizer=offload)
+            if offload:
+                print_rank_0(" > ZeRO-Offload: master weights and Adam moments in host memory, update on the CPU")
             if use_symm:
                 fused_zero.attach(optimizer, allocator, use_nvls=bool(cfg.use_nvls))
         else:

@@ -494,3 +494,31 @@ def _w_hpz(rank, world, over, ref_losses):
     assert freed and all(f.hpz_gathers > 0 for f in freed), [f.hpz_gathers for f in freed]
     assert all(f.hpz_shard.numel() == f.padded // 2 for f in freed)
     assert all(not f.hpz_fresh for f in freed)                  # stale after the optimizer step
+
+
+def test_zero_offload_keeps_state_on_the_host_and_matches():
+    """`zero_optimization.offload_optimizer.device: cpu`: the loss trace equals the run without offload (same Adam
+    arithmetic, fp32), master weights and moments are host tensors, and the optimizer state survives a state-dict
+    round trip."""
+    from savanna_b200.parallel import state
+    cfg = _tiny_cfg(1)
+    _, ref_losses = _run_steps(cfg)
+    state.destroy_model_parallel()
+    cfg2 = _tiny_cfg(1, zero_optimization={"stage": 1, "offload_optimizer": {"device": "cpu", "pin_memory": True}})
+    tr, losses = _run_steps(cfg2)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(b)), (losses, ref_losses)
+    opt = tr.optimizer
+    assert opt.offload_optimizer and opt.fused is None
+    for g in opt.groups:
+        assert g.master.device.type == "cpu" and g.exp_avg.device.type == "cpu" and not g.master_is_view
+        assert torch.allclose(g.master.to(g.flat_param.dtype), g.shard_slice(g.flat_param).cpu())
+    import copy
+    sd = copy.deepcopy(opt.state_dict())
+    m0 = [g.master.clone() for g in opt.groups]
+    for g in opt.groups:
+        g.master.zero_()
+    opt.load_state_dict(sd)
+    for a, g in zip(m0, opt.groups):
+        assert torch.equal(a, g.master)
+    state.destroy_model_parallel()
