@@ -43,10 +43,11 @@ class TPWorkspace:
         P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         self.lib.sb_gemm_tp.restype = I
         self.lib.sb_gemm_tp.argtypes = [P, I, P, I, I, P, I, P, I, I, I, I, I, P, P, I, I, I, I, P, P, P, I, I, I, I, P, P, P]
-        # CTA-pair variant of the fused kernels (cta_group::2): opt-in through SAVANNA_B200_TP_PAIR=1
+        # CTA-pair variant of the fused kernels (cta_group::2, 256 x 256 tiles per SM pair) where the shapes allow it
+        # (rows a multiple of 256); SAVANNA_B200_TP_PAIR=0 selects the single-CTA kernel (A/B measurements)
         self.lib.sb_gemm_tp_set_pair.restype = I
         self.lib.sb_gemm_tp_set_pair.argtypes = [I]
-        self.pair = os.environ.get("SAVANNA_B200_TP_PAIR", "0") == "1"
+        self.pair = os.environ.get("SAVANNA_B200_TP_PAIR", "1") == "1"
         self.lib.sb_gemm_tp_set_pair(int(self.pair))
         self.lib.sb_rs_reduce.restype = I
         self.lib.sb_rs_reduce.argtypes = [P, P, P, P, I, LL, I, P]
