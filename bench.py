@@ -476,7 +476,11 @@ def main():
         # the block-scaled recipe on one GPU, beside the headline (its projections run without tensor parallelism only)
         mx = None
         if use_fp8 and not args.skip_second and world == 1 and not any(k == "fp8_recipe" for k in over):
-            mx = measure(args.config, dict(fp8_over, fp8_recipe="mxfp8"), args.steps, args.warmup, False)
+            try:
+                mx = measure(args.config, dict(fp8_over, fp8_recipe="mxfp8"), args.steps, args.warmup, False)
+            except Exception as exc:  # noqa: BLE001  (a side measurement must not take the headline down)
+                mx = {"value": None, "ms_per_step": None, "loss": None, "dtype": f"mxfp8 run failed: {type(exc).__name__}: {exc}"[:300]}
+                release()
         cfg = main_res["cfg"]
         L, B, gas = cfg.seq_length, cfg.train_micro_batch_size_per_gpu, cfg.gradient_accumulation_steps
         fpt = model_flops_per_token(cfg)
