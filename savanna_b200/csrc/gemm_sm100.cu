@@ -51,6 +51,11 @@ struct GemmParams {
   float* glu_hist;
   int glu_slots, glu_cur;
   float* glu_scale_inv;
+  // gate backward in the epilogue of the w3 input-gradient product (GLU = 2): C is not written; with g = the product's
+  // result and [a | b] read from glu_ab (leading dimension glu_ld_ab), the epilogue writes q [M, 2 F] =
+  // e5m2(g * b * silu'(a) | g * silu(a)) under delayed scaling (same ring protocol)
+  const __nv_bfloat16* glu_ab;
+  int glu_ld_ab;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
@@ -299,7 +304,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();             // 0: issues the MMAs, 1: partner
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int m_tiles = (p.M + 255) / 256, n_tiles = GLU ? p.glu_F / 128 : (p.N + BN - 1) / BN;
+  const int m_tiles = (p.M + 255) / 256, n_tiles = GLU == 1 ? p.glu_F / 128 : (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   constexpr int BKE = 128 / EB;
   constexpr int MNB = 128 / EB;
@@ -334,7 +339,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
         int mt, nt; pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
         const int m0 = mt * 256 + int(rank) * 128;
-        const int n0 = GLU ? nt * 128 + int(rank) * p.glu_F : nt * BN + int(rank) * 128;
+        const int n0 = GLU == 1 ? nt * 128 + int(rank) * p.glu_F : nt * BN + int(rank) * 128;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES;
@@ -414,9 +419,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const float h = p.glu_hist[j];
         if (h > a && h < 3.0e38f) a = h;
       }
-      if (!(a > 0.f)) a = 448.f;
-      if (blockIdx.x == 0 && warp == 2 && lane == 0) { p.glu_scale_inv[0] = a / 448.f; p.glu_hist[nxt] = 0.f; }
-      q_scale = 448.f / a;
+      const float fmax_q = GLU == 2 ? 57344.f : 448.f;          // e5m2 gradients, e4m3 activations
+      if (!(a > 0.f)) a = fmax_q;
+      if (blockIdx.x == 0 && warp == 2 && lane == 0) { p.glu_scale_inv[0] = a / fmax_q; p.glu_hist[nxt] = 0.f; }
+      q_scale = fmax_q / a;
     }
     for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local) {
       const int acc = local & 1;
@@ -428,7 +434,61 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nt * BN;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       __nv_bfloat16* crow = p.C + size_t(row) * p.ldc;
-      if (GLU) {
+      if (GLU == 2) {
+        const int F = p.glu_F;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          const int f = n0 + c * 32;
+          const bool live = row < p.M && f < F;
+          uint4 av[4], bv[4];
+          if (live) {
+            const uint4* pa = reinterpret_cast<const uint4*>(p.glu_ab + size_t(row) * p.glu_ld_ab + f);
+            const uint4* pb = reinterpret_cast<const uint4*>(p.glu_ab + size_t(row) * p.glu_ld_ab + F + f);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) { av[v] = pa[v]; bv[v] = pb[v]; }
+          }
+          tmem_wait_ld();
+          if (live) {
+            uint32_t qa[8], qb[8];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av[v]);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv[v]);
+              float da[8], db[8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 af = __bfloat1622float2(a2[j]), bf = __bfloat1622float2(b2[j]);
+                // g as the separate product would have stored it (bf16), then the gate backward's arithmetic
+                const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha));
+                const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[v * 8 + 2 * j + 1]) * alpha));
+                const float s0 = __fdividef(1.f, 1.f + __expf(-af.x)), s1 = __fdividef(1.f, 1.f + __expf(-af.y));
+                const float f0 = af.x * s0, f1 = af.y * s1;
+                const float d0 = s0 + f0 * (1.f - s0), d1 = s1 + f1 * (1.f - s1);
+                da[2 * j] = __bfloat162float(__float2bfloat16_rn(g0 * bf.x * d0));
+                da[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(g1 * bf.y * d1));
+                db[2 * j] = __bfloat162float(__float2bfloat16_rn(g0 * f0));
+                db[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(g1 * f1));
+                q_amax = fmaxf(q_amax, fmaxf(fmaxf(fabsf(da[2 * j]), fabsf(da[2 * j + 1])), fmaxf(fabsf(db[2 * j]), fabsf(db[2 * j + 1]))));
+              }
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const unsigned short x0 = __nv_cvt_float2_to_fp8x2(make_float2(da[4 * h] * q_scale, da[4 * h + 1] * q_scale), __NV_SATFINITE, __NV_E5M2);
+                const unsigned short x1 = __nv_cvt_float2_to_fp8x2(make_float2(da[4 * h + 2] * q_scale, da[4 * h + 3] * q_scale), __NV_SATFINITE, __NV_E5M2);
+                const unsigned short y0 = __nv_cvt_float2_to_fp8x2(make_float2(db[4 * h] * q_scale, db[4 * h + 1] * q_scale), __NV_SATFINITE, __NV_E5M2);
+                const unsigned short y1 = __nv_cvt_float2_to_fp8x2(make_float2(db[4 * h + 2] * q_scale, db[4 * h + 3] * q_scale), __NV_SATFINITE, __NV_E5M2);
+                qa[2 * v + h] = uint32_t(x0) | (uint32_t(x1) << 16);
+                qb[2 * v + h] = uint32_t(y0) | (uint32_t(y1) << 16);
+              }
+            }
+            uint4* da_dst = reinterpret_cast<uint4*>(p.glu_q + size_t(row) * 2 * F + f);
+            uint4* db_dst = reinterpret_cast<uint4*>(p.glu_q + size_t(row) * 2 * F + F + f);
+            da_dst[0] = make_uint4(qa[0], qa[1], qa[2], qa[3]); da_dst[1] = make_uint4(qa[4], qa[5], qa[6], qa[7]);
+            db_dst[0] = make_uint4(qb[0], qb[1], qb[2], qb[3]); db_dst[1] = make_uint4(qb[4], qb[5], qb[6], qb[7]);
+          }
+        }
+      } else if (GLU) {
         const int f0 = nt * 128;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -678,6 +738,48 @@ extern "C" int sb_gemm_fp8_glu(const void* A, const void* W12, void* AB, void* Q
     attr_set = true;
   }
   const int tiles = ((M + 255) / 256) * (F / 128);
+  int pairs = g_num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? 0 : -6;
+}
+
+// Input-gradient product of the gated MLP's output projection with the gate backward in the epilogue (GLU = 2):
+// g [M, F] = alpha * G [M, D] (e5m2) * W3 [D, F] (e4m3, rows of F contiguous) is not stored; with [a | b] = AB [M, 2 F]
+// the epilogue writes Q [M, 2 F] = e5m2(g * b * silu'(a) | g * silu(a)) under delayed scaling.  F % 16 == 0, D % 16 == 0.
+extern "C" int sb_gemm_fp8_glu_bwd(const void* G, const void* W3, const void* AB, void* Q, const float* alpha, const float* alpha2,
+                                   int M, int F, int D, int ldg, int ldw, int ldab, float* hist, int slots, int cur,
+                                   float* scale_inv, unsigned int* status, cudaStream_t stream) {
+  using namespace sb;
+  if (M <= 0 || F <= 0 || D <= 0) return 0;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(0); ctx_bound = true; }
+  if ((F % 32) || (D % 16) || (ldg % 16) || (ldw % 16) || (ldab % 8) || ldab < 2 * F || slots < 3 || cur < 0 || cur >= slots) return -3;
+  if ((reinterpret_cast<uintptr_t>(G) | reinterpret_cast<uintptr_t>(W3) | reinterpret_cast<uintptr_t>(AB) |
+       reinterpret_cast<uintptr_t>(Q)) & 15) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if ((rc = make_tmap_2d_u8(&tmA, G, D, M, ldg, 128, BM))) return rc;
+  if ((rc = make_tmap_2d_u8(&tmB, W3, F, D, ldw, 128, 128))) return rc;          // MN-major operand: boxes of 128 x 128
+  if (!g_num_sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev); }
+  GemmParams p{nullptr, nullptr, nullptr, M, F, D, 0, 0, 0, status, alpha, alpha2, 1, 0,
+               reinterpret_cast<uint8_t*>(Q), F, hist, slots, cur, scale_inv, reinterpret_cast<const __nv_bfloat16*>(AB), ldab};
+  auto kern = gemm_pair_kernel<0, 1, 1, 2>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  const int tiles = ((M + 255) / 256) * ((F + BN - 1) / BN);
   int pairs = g_num_sms / 2;
   if (tiles < pairs) pairs = tiles;
   cudaLaunchConfig_t cfg = {};

@@ -420,9 +420,14 @@ def gemm_fp8(a, b, out, alpha, a_mn=False, b_mn=False, a_fmt=E4M3, b_fmt=E4M3, b
 GLU_EPILOGUE = os.environ.get("SAVANNA_B200_GLU_EPILOGUE", "1") != "0"
 
 
-def set_glu_epilogue(on: bool) -> None:
-    global GLU_EPILOGUE
+GLU_BWD_EPILOGUE = os.environ.get("SAVANNA_B200_GLU_BWD_EPILOGUE", "0") != "0"    # likewise for the gate backward (w3 dgrad)
+
+
+def set_glu_epilogue(on: bool, backward=None) -> None:
+    global GLU_EPILOGUE, GLU_BWD_EPILOGUE
     GLU_EPILOGUE = bool(on)
+    if backward is not None:
+        GLU_BWD_EPILOGUE = bool(backward)
 
 
 def gemm_fp8_glu(xq, w12q, ab, hq, sx, s12, site, sh):
@@ -441,6 +446,26 @@ def gemm_fp8_glu(xq, w12q, ab, hq, sx, s12, site, sh):
                              sh.data_ptr(), status_word(ab.device).data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"gemm_fp8_glu failed (code {rc}): T={T} F={F} K={K}")
+    _count()
+    site.cur = (site.cur + 1) % site.buf.numel()
+
+
+def gemm_fp8_glu_bwd(gq, w3q, ab, dq, sg, s3, site, sd):
+    """dq [T, 2F] = e5m2 gate gradients of [a | b] from g = (gq w3q) de-quantised, under the delayed scaling of `site`
+    (advances its ring); sd receives dq's de-quantisation factor.  g itself is not stored."""
+    lib = require()
+    if not getattr(lib, "_sb_glu_bwd_ready", False):
+        P, I = ctypes.c_void_p, ctypes.c_int
+        lib.sb_gemm_fp8_glu_bwd.restype = I
+        lib.sb_gemm_fp8_glu_bwd.argtypes = [P, P, P, P, P, P, I, I, I, I, I, I, P, I, I, P, P, P]
+        lib._sb_glu_bwd_ready = True
+    T, D = gq.shape
+    F = w3q.shape[1]
+    rc = lib.sb_gemm_fp8_glu_bwd(gq.data_ptr(), w3q.data_ptr(), ab.data_ptr(), dq.data_ptr(), sg.data_ptr(), s3.data_ptr(), T, F, D,
+                                 gq.stride(0), w3q.stride(0), ab.stride(0), site.buf.data_ptr(), site.buf.numel(), site.cur,
+                                 sd.data_ptr(), status_word(ab.device).data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"gemm_fp8_glu_bwd failed (code {rc}): T={T} F={F} D={D}")
     _count()
     site.cur = (site.cur + 1) % site.buf.numel()
 
@@ -700,9 +725,10 @@ class _RMSNormResidual(torch.autograd.Function):
         return dx.view(shape), dw, None, None
 
 
-def _fp8_backward_gemms(ctx_w, gy2, xq, sx, wq, sw, need_gx, need_gw):
-    """Shared by the fp8 projections: quantise the output gradient (e5m2), then dgrad and (in-place) wgrad."""
-    gq, sg = quantize_fp8_site(gy2, E5M2, ctx_w, "g")
+def _fp8_backward_gemms(ctx_w, gy2, xq, sx, wq, sw, need_gx, need_gw, quantised=None):
+    """Shared by the fp8 projections: quantise the output gradient (e5m2), then dgrad and (in-place) wgrad.
+    `quantised` = (gq, sg) when the caller has already quantised the gradient."""
+    gq, sg = quantised if quantised is not None else quantize_fp8_site(gy2, E5M2, ctx_w, "g")
     gx = gw = None
     if need_gx:
         gx = _alloc((gy2.shape[0], wq.shape[1]), dtype=bf16, device=gy2.device)
@@ -877,10 +903,22 @@ class _MlpFP8(torch.autograd.Function):
         g2 = _rows(gy)
         T, F2 = ab.shape
         dev = gy.device
-        gh, gw3 = _fp8_backward_gemms(w3, g2, hq, sh, w3q, s3, True, ctx.needs_input_grad[5])
-        gb3 = colsum(g2).to(gy.dtype) if (has_b3 and ctx.needs_input_grad[6]) else None
         hg = _site(w12, "g", dev)
-        if not hg.primed:
+        Fh = F2 // 2
+        fuse_gate = hg.primed and act == 0 and Fh % 32 == 0 and GLU_EPILOGUE and GLU_BWD_EPILOGUE and _PAIR_MODE >= 1
+        if fuse_gate:
+            # the gate backward runs in the epilogue of the w3 input-gradient product: its result [T, F] never exists
+            gq3, sg3 = quantize_fp8_site(g2, E5M2, w3, "g")
+            dq = _alloc((T, F2), dtype=torch.uint8, device=dev)
+            sd = _alloc(1, dtype=torch.float32, device=dev)
+            gemm_fp8_glu_bwd(gq3, w3q, ab, dq, sg3, s3, hg, sd)
+            _, gw3 = _fp8_backward_gemms(w3, g2, hq, sh, w3q, s3, False, ctx.needs_input_grad[5], quantised=(gq3, sg3))
+        else:
+            gh, gw3 = _fp8_backward_gemms(w3, g2, hq, sh, w3q, s3, True, ctx.needs_input_grad[5])
+        gb3 = colsum(g2).to(gy.dtype) if (has_b3 and ctx.needs_input_grad[6]) else None
+        if fuse_gate:
+            pass
+        elif not hg.primed:
             dab = _alloc_like(ab)
             _check(lib.sb_glu_bwd(ab.data_ptr(), gh.data_ptr(), dab.data_ptr(), T, F2 // 2, act, _stream()), "glu_bwd")
             _count()

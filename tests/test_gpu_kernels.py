@@ -802,6 +802,9 @@ def test_mxfp8_training_tracks_bf16():
     assert max(abs(x - y) for x, y in zip(a, b)) < 0.2, (a, b)
 
 
+GLU_BWD_DEFAULT = cuda_ops.GLU_BWD_EPILOGUE
+
+
 def test_gate_in_the_projection_epilogue_matches_the_separate_gate_kernel():
     """The gated MLP with the gate applied in the epilogue of the w1|w2 projection (CTA-pair fp8 kernel, GLU mode) against
     the same function with the separate gate kernel: identical [a | b], identical e4m3 operand of w3 (same scale, same
@@ -815,7 +818,7 @@ def test_gate_in_the_projection_epilogue_matches_the_separate_gate_kernel():
     b3 = torch.randn(D, device=DEV, dtype=BF)
     outs = []
     for fused in (False, True):
-        cuda_ops.set_glu_epilogue(fused)
+        cuda_ops.set_glu_epilogue(fused, backward=fused)
         ps = [t.clone().requires_grad_() for t in (x, wn, w12, w3, b3)]
         try:
             for _ in range(3):                                   # the third call runs on primed amax histories
@@ -826,7 +829,7 @@ def test_gate_in_the_projection_epilogue_matches_the_separate_gate_kernel():
                 launches = cuda_ops.launch_count() - before
                 y.backward(torch.ones_like(y) * 0.01)
         finally:
-            cuda_ops.set_glu_epilogue(True)
+            cuda_ops.set_glu_epilogue(True, backward=GLU_BWD_DEFAULT)
         _done()
         outs.append((y.detach().float(), [t.grad.float() for t in ps], launches,
                      ps[3]._fp8_sites["x"].buf.clone()))
