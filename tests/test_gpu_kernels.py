@@ -806,9 +806,10 @@ GLU_BWD_DEFAULT = cuda_ops.GLU_BWD_EPILOGUE
 
 
 def test_gate_in_the_projection_epilogue_matches_the_separate_gate_kernel():
-    """The gated MLP with the gate applied in the epilogue of the w1|w2 projection (CTA-pair fp8 kernel, GLU mode) against
-    the same function with the separate gate kernel: identical [a | b], identical e4m3 operand of w3 (same scale, same
-    rounding), same amax history, same output and gradients."""
+    """The gated MLP with the gate applied in the epilogue of the w1|w2 projection and the gate backward in the epilogue of
+    the w3 input-gradient product (CTA-pair fp8 kernel, GLU modes 1 and 2) against the same function with the separate gate
+    kernels: identical [a | b], identical e4m3 operand of w3 and e5m2 gradient of [a | b] (same scales, same rounding),
+    same amax history, same output and gradients, bit for bit."""
     torch.manual_seed(51)
     T, D, F = 384, 512, 1024
     x = torch.randn(1, T, D, device=DEV, dtype=BF)
