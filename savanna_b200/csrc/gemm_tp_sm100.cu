@@ -95,6 +95,96 @@ __device__ __forceinline__ void st_release(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Copy CTAs of the fused all-gather -> GEMM kernels (the lowest block indices of the grid): pull the remote 128-row tiles
+// of the gathered operand into the local gather buffer, next rank's shard first, and publish one flag per tile.  Whole
+// rows travel as a ring of untiled bulk copies (peer memory -> shared memory -> local memory) driven by one thread;
+// rows with a leading dimension larger than K go through registers.
+template <int EB>
+__device__ __forceinline__ void tp_copy_cta(const Params& p, uint8_t* smem_raw, int m_tiles, int n_copy_ctas) {
+  const int cid = blockIdx.x, n_copy = n_copy_ctas;
+  const int n_local = p.ag_batch * p.ag_tiles_per_rank;
+  const int n_remote = m_tiles - n_local;
+  const int row_bytes_i = p.K * EB;
+  const int vec_per_row = row_bytes_i >> 4;
+  const bool contiguous = p.ag_src_ld == p.K && row_bytes_i <= CP_CHUNK;   // whole rows per bulk chunk
+  const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
+  const uint32_t cbar = ring + CP_NB * CP_CHUNK;                       // CP_NB mbarriers
+  __shared__ int copy_abort;
+  if (threadIdx.x == 0) {
+    copy_abort = 0;
+    for (int b = 0; b < CP_NB; ++b) mbar_init(cbar + 8u * b, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  uint32_t issued = 0, done = 0;                                       // chunk counters over the whole CTA lifetime
+  for (int idx = cid; idx < n_remote; idx += n_copy) {
+    const int mt = ag_ordered_tile(p, n_local + idx);                   // rotated order: next rank's shard first
+    int src_rank, src_row0;
+    ag_tile_source(p, mt, src_rank, src_row0);
+    const int rows = min(BM, p.M - mt * BM);
+    if (contiguous) {
+      // one thread drives a ring of bulk copies: peer memory -> shared -> local gather buffer
+      if (threadIdx.x == 0) {
+        const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * row_bytes_i);
+        char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
+        const uint32_t row_bytes = (uint32_t)row_bytes_i;
+        const uint32_t rows_per_chunk = max(1u, CP_CHUNK / row_bytes);
+        const uint32_t chunk = rows_per_chunk * row_bytes;
+        const uint32_t total = (uint32_t)rows * row_bytes;
+        const uint32_t n_chunks = (total + chunk - 1) / chunk;
+        bool ok = chunk <= (uint32_t)CP_CHUNK;
+        for (uint32_t i = 0; ok && i < n_chunks + CP_LAG; ++i) {
+          if (i < n_chunks) {
+            const uint32_t b = issued % CP_NB;
+            bulk_wait_read<CP_NB - CP_LAG - 1>();                      // the store that last used this buffer has read it
+            const uint32_t off = i * chunk, sz = min(chunk, total - off);
+            mbar_expect_tx(cbar + 8u * b, sz);
+            bulk_load(ring + b * CP_CHUNK, src + off, sz, cbar + 8u * b);
+            ++issued;
+          }
+          if (i >= (uint32_t)CP_LAG) {
+            const uint32_t j = i - CP_LAG;
+            const uint32_t b = done % CP_NB, par = (done / CP_NB) & 1u;
+            if (!mbar_wait(cbar + 8u * b, par, &copy_abort, p.status, ST_TIMEOUT_PEER)) { ok = false; break; }
+            const uint32_t off = j * chunk, sz = min(chunk, total - off);
+            bulk_store(dst + off, ring + b * CP_CHUNK, sz);
+            bulk_commit();
+            ++done;
+          }
+        }
+        bulk_wait<0>();                                                // all stores of this tile have landed
+        if (ok) {
+          __threadfence();
+          fence_proxy_async();
+          st_release(p.ag_flags + mt, p.ag_epoch);
+        }
+      }
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld * EB);
+      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
+      const int total = rows * vec_per_row;
+      const int src_ld8 = (p.ag_src_ld * EB) >> 4;
+      for (int i = threadIdx.x; i < total; i += NUM_THREADS * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int j = i + u * NUM_THREADS;
+          if (j < total) { const int r = j / vec_per_row, c = j - r * vec_per_row; v[u] = src[(size_t)r * src_ld8 + c]; }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int j = i + u * NUM_THREADS;
+          if (j < total) dst[j] = v[u];
+        }
+      }
+      __threadfence();
+      fence_proxy_async();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release(p.ag_flags + mt, p.ag_epoch);
+    }
+  }
+}
+
 template <int B_MN, int EB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_constant__ CUtensorMap tmA_gather,
@@ -112,89 +202,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_const
   const int gemm_id = (int)blockIdx.x - n_copy_ctas;
 
   if (ag && (int)blockIdx.x < n_copy_ctas) {
-    // ------------------------------------------------------------------ copy CTAs: pull remote tiles, publish local flags
-    const int cid = blockIdx.x, n_copy = n_copy_ctas;
-    const int n_local = p.ag_batch * p.ag_tiles_per_rank;
-    const int n_remote = m_tiles - n_local;
-    const int row_bytes_i = p.K * EB;
-    const int vec_per_row = row_bytes_i >> 4;
-    const bool contiguous = p.ag_src_ld == p.K && row_bytes_i <= CP_CHUNK;   // whole rows per bulk chunk
-    const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
-    const uint32_t cbar = ring + CP_NB * CP_CHUNK;                       // CP_NB mbarriers
-    __shared__ int copy_abort;
-    if (threadIdx.x == 0) {
-      copy_abort = 0;
-      for (int b = 0; b < CP_NB; ++b) mbar_init(cbar + 8u * b, 1);
-      fence_barrier_init();
-    }
-    __syncthreads();
-    uint32_t issued = 0, done = 0;                                       // chunk counters over the whole CTA lifetime
-    for (int idx = cid; idx < n_remote; idx += n_copy) {
-      const int mt = ag_ordered_tile(p, n_local + idx);                   // rotated order: next rank's shard first
-      int src_rank, src_row0;
-      ag_tile_source(p, mt, src_rank, src_row0);
-      const int rows = min(BM, p.M - mt * BM);
-      if (contiguous) {
-        // one thread drives a ring of bulk copies: peer memory -> shared -> local gather buffer
-        if (threadIdx.x == 0) {
-          const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * row_bytes_i);
-          char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
-          const uint32_t row_bytes = (uint32_t)row_bytes_i;
-          const uint32_t rows_per_chunk = max(1u, CP_CHUNK / row_bytes);
-          const uint32_t chunk = rows_per_chunk * row_bytes;
-          const uint32_t total = (uint32_t)rows * row_bytes;
-          const uint32_t n_chunks = (total + chunk - 1) / chunk;
-          bool ok = chunk <= (uint32_t)CP_CHUNK;
-          for (uint32_t i = 0; ok && i < n_chunks + CP_LAG; ++i) {
-            if (i < n_chunks) {
-              const uint32_t b = issued % CP_NB;
-              bulk_wait_read<CP_NB - CP_LAG - 1>();                      // the store that last used this buffer has read it
-              const uint32_t off = i * chunk, sz = min(chunk, total - off);
-              mbar_expect_tx(cbar + 8u * b, sz);
-              bulk_load(ring + b * CP_CHUNK, src + off, sz, cbar + 8u * b);
-              ++issued;
-            }
-            if (i >= (uint32_t)CP_LAG) {
-              const uint32_t j = i - CP_LAG;
-              const uint32_t b = done % CP_NB, par = (done / CP_NB) & 1u;
-              if (!mbar_wait(cbar + 8u * b, par, &copy_abort, p.status, ST_TIMEOUT_PEER)) { ok = false; break; }
-              const uint32_t off = j * chunk, sz = min(chunk, total - off);
-              bulk_store(dst + off, ring + b * CP_CHUNK, sz);
-              bulk_commit();
-              ++done;
-            }
-          }
-          bulk_wait<0>();                                                // all stores of this tile have landed
-          if (ok) {
-            __threadfence();
-            fence_proxy_async();
-            st_release(p.ag_flags + mt, p.ag_epoch);
-          }
-        }
-      } else {
-        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld * EB);
-        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
-        const int total = rows * vec_per_row;
-        const int src_ld8 = (p.ag_src_ld * EB) >> 4;
-        for (int i = threadIdx.x; i < total; i += NUM_THREADS * 8) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int j = i + u * NUM_THREADS;
-            if (j < total) { const int r = j / vec_per_row, c = j - r * vec_per_row; v[u] = src[(size_t)r * src_ld8 + c]; }
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int j = i + u * NUM_THREADS;
-            if (j < total) dst[j] = v[u];
-          }
-        }
-        __threadfence();
-        fence_proxy_async();
-        __syncthreads();
-        if (threadIdx.x == 0) st_release(p.ag_flags + mt, p.ag_epoch);
-      }
-    }
+    tp_copy_cta<EB>(p, smem_raw, m_tiles, n_copy_ctas);
     return;
   }
 
@@ -420,79 +428,7 @@ gemm_tp_pair_kernel(const __grid_constant__ CUtensorMap tmA_local, const __grid_
   const int gemm_id = (int)blockIdx.x - n_copy_ctas;
 
   if (ag && (int)blockIdx.x < n_copy_ctas) {
-    // ------------------------------------------------------------------ copy CTAs (as in gemm_tp_kernel)
-    const int cid = blockIdx.x, n_copy = n_copy_ctas;
-    const int n_local = p.ag_batch * p.ag_tiles_per_rank;
-    const int n_remote = m_tiles - n_local;
-    const int row_bytes_i = p.K * EB;
-    const int vec_per_row = row_bytes_i >> 4;
-    const bool contiguous = p.ag_src_ld == p.K && row_bytes_i <= CP_CHUNK;
-    const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
-    const uint32_t cbar = ring + CP_NB * CP_CHUNK;
-    __shared__ int copy_abort;
-    if (threadIdx.x == 0) {
-      copy_abort = 0;
-      for (int b = 0; b < CP_NB; ++b) mbar_init(cbar + 8u * b, 1);
-      fence_barrier_init();
-    }
-    __syncthreads();
-    uint32_t issued = 0, done = 0;
-    for (int idx = cid; idx < n_remote; idx += n_copy) {
-      const int mt = ag_ordered_tile(p, n_local + idx);
-      int src_rank, src_row0;
-      ag_tile_source(p, mt, src_rank, src_row0);
-      const int rows = min(BM, p.M - mt * BM);
-      if (contiguous) {
-        if (threadIdx.x == 0) {
-          const char* src = reinterpret_cast<const char*>(p.ag_src[src_rank] + (size_t)src_row0 * row_bytes_i);
-          char* dst = reinterpret_cast<char*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
-          const uint32_t row_bytes = (uint32_t)row_bytes_i;
-          const uint32_t rows_per_chunk = max(1u, CP_CHUNK / row_bytes);
-          const uint32_t chunk = rows_per_chunk * row_bytes;
-          const uint32_t total = (uint32_t)rows * row_bytes;
-          const uint32_t n_chunks = (total + chunk - 1) / chunk;
-          bool ok = chunk <= (uint32_t)CP_CHUNK;
-          for (uint32_t i = 0; ok && i < n_chunks + CP_LAG; ++i) {
-            if (i < n_chunks) {
-              const uint32_t b = issued % CP_NB;
-              bulk_wait_read<CP_NB - CP_LAG - 1>();
-              const uint32_t off = i * chunk, sz = min(chunk, total - off);
-              mbar_expect_tx(cbar + 8u * b, sz);
-              bulk_load(ring + b * CP_CHUNK, src + off, sz, cbar + 8u * b);
-              ++issued;
-            }
-            if (i >= (uint32_t)CP_LAG) {
-              const uint32_t j = i - CP_LAG;
-              const uint32_t b = done % CP_NB, par = (done / CP_NB) & 1u;
-              if (!mbar_wait(cbar + 8u * b, par, &copy_abort, p.status, ST_TIMEOUT_PEER)) { ok = false; break; }
-              const uint32_t off = j * chunk, sz = min(chunk, total - off);
-              bulk_store(dst + off, ring + b * CP_CHUNK, sz);
-              bulk_commit();
-              ++done;
-            }
-          }
-          bulk_wait<0>();
-          if (ok) {
-            __threadfence();
-            fence_proxy_async();
-            st_release(p.ag_flags + mt, p.ag_epoch);
-          }
-        }
-      } else {
-        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[src_rank] + (size_t)src_row0 * p.ag_src_ld * EB);
-        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst + (size_t)mt * BM * row_bytes_i);
-        const int total = rows * vec_per_row;
-        const int src_ld8 = (p.ag_src_ld * EB) >> 4;
-        for (int i = threadIdx.x; i < total; i += NUM_THREADS) {
-          const int r = i / vec_per_row, c = i - r * vec_per_row;
-          dst[i] = src[(size_t)r * src_ld8 + c];
-        }
-        __threadfence();
-        fence_proxy_async();
-        __syncthreads();
-        if (threadIdx.x == 0) st_release(p.ag_flags + mt, p.ag_epoch);
-      }
-    }
+    tp_copy_cta<EB>(p, smem_raw, m_tiles, n_copy_ctas);
     return;
   }
 
