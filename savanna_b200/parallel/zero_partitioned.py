@@ -140,6 +140,8 @@ class UnitFlat:
         for p in self.params:                                  # quantised copies of the weights go with them
             if getattr(p, "_fp8_cache", None) is not None:
                 p._fp8_cache = None
+            if getattr(p, "_mx_cache", None) is not None:
+                p._mx_cache = None
 
     # -- gradients -----------------------------------------------------------------
     def alloc_grads(self) -> None:
