@@ -174,7 +174,8 @@ def reference_arm(args):
         why = f"reference not runnable offline: {type(exc).__name__}: {exc}".replace("\n", " ")[:300]
     if why is None:
         why = "reference imports resolved but no driver for its DeepSpeed launcher is wired on this box"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also when launched with one process per GPU
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
     return 0
 
 
