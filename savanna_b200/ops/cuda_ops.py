@@ -39,13 +39,50 @@ def require():
         raise RuntimeError(
             f"{_LIB_PATH} is missing: build the CUDA kernels with `python -m savanna_b200.csrc.build` "
             "(CUDA tensors never fall back to PyTorch ops silently; set SAVANNA_B200_BACKEND=torch to ask for that)")
-    _LIB = ctypes.CDLL(_LIB_PATH)
+    raw = ctypes.CDLL(_LIB_PATH)
     for name in dir(_Sig):
         if name.startswith("sb_"):
-            fn = getattr(_LIB, name)
+            fn = getattr(raw, name)
             fn.restype = c_int
             fn.argtypes = getattr(_Sig, name)
+    _LIB = _Library(raw)
     return _LIB
+
+
+NVTX = False        # one NVTX range per native entry point (named after it) while True; the capture-range profiler turns it on
+
+
+def set_nvtx(on: bool) -> None:
+    global NVTX
+    NVTX = bool(on)
+
+
+class _Library:
+    """The loaded native library.  Attribute access returns the C entry points unchanged (their `argtypes` / `restype` are
+    set on those objects); while `NVTX` is on, calls go through a wrapper that opens an NVTX range named after the entry
+    point, so that every kernel launcher shows up by name in an Nsight Systems timeline next to the step marks."""
+
+    def __init__(self, raw):
+        object.__setattr__(self, "_raw", raw)
+        object.__setattr__(self, "_wrapped", {})
+
+    def __getattr__(self, name):
+        fn = getattr(self._raw, name)
+        if not NVTX or not name.startswith("sb_"):
+            return fn
+        w = self._wrapped.get(name)
+        if w is None:
+            def w(*args, _fn=fn, _name=name):
+                torch.cuda.nvtx.range_push(_name)
+                try:
+                    return _fn(*args)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+            self._wrapped[name] = w
+        return w
+
+    def __setattr__(self, name, value):
+        setattr(self._raw, name, value)
 
 
 class _Sig:

@@ -98,6 +98,8 @@ class CudaProfiler(EmptyProfiler):
         if torch.cuda.is_available():
             torch.cuda.synchronize()
             torch.cuda.cudart().cudaProfilerStart()
+            from ..ops import cuda_ops
+            cuda_ops.set_nvtx(True)                  # one range per native kernel launcher inside the capture window
             if self.cfg.emit_nvtx:
                 self._nvtx_ctx = torch.autograd.profiler.emit_nvtx(record_shapes=self.cfg.profile_record_shapes)
                 self._nvtx_ctx.__enter__()
@@ -110,6 +112,8 @@ class CudaProfiler(EmptyProfiler):
                 self._nvtx_ctx.__exit__(None, None, None)
                 self._nvtx_ctx = None
             torch.cuda.cudart().cudaProfilerStop()
+            from ..ops import cuda_ops
+            cuda_ops.set_nvtx(False)
         self.running, self.done = False, True
 
     def step(self):

@@ -141,3 +141,33 @@ def test_cuda_profiler_window_and_nsys_command():
     cmd = build_nsys_command(cfg, ["python", "train.py"], "out")
     assert cmd[0] == "nsys" and "--capture-range=cudaProfilerApi" in cmd and "--capture-range-end=stop" in cmd
     assert cmd[-2:] == ["python", "train.py"]
+
+
+def test_native_library_proxy_opens_an_nvtx_range_per_entry_point(monkeypatch):
+    """While NVTX is on (the capture-range profiler's window) every native entry point runs inside a range named after it;
+    off, the raw C function objects are returned unchanged, and attribute writes reach the underlying library."""
+    import types
+    import torch
+    from savanna_b200.ops import cuda_ops
+    calls = []
+    raw = types.SimpleNamespace(sb_demo=lambda a, b: a + b, other=lambda: 7)
+    lib = cuda_ops._Library(raw)
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: calls.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: calls.append(("pop",)))
+    cuda_ops.set_nvtx(False)
+    assert lib.sb_demo is raw.sb_demo and lib.sb_demo(1, 2) == 3 and calls == []
+    lib.flag = 5
+    assert raw.flag == 5 and lib.flag == 5
+    cuda_ops.set_nvtx(True)
+    try:
+        assert lib.sb_demo(2, 3) == 5
+        assert calls == [("push", "sb_demo"), ("pop",)]
+        assert lib.other() == 7 and len(calls) == 2            # only sb_* entry points are wrapped
+        raw.sb_fail = lambda: (_ for _ in ()).throw(ValueError("x"))
+        try:
+            lib.sb_fail()
+        except ValueError:
+            pass
+        assert calls[-1] == ("pop",)                             # the range is closed on exceptions too
+    finally:
+        cuda_ops.set_nvtx(False)
