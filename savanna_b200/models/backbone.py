@@ -9,6 +9,7 @@ from __future__ import annotations
 from typing import List, Optional
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 import torch.utils.checkpoint as ckpt
 
@@ -122,8 +123,28 @@ class Backbone(nn.Module):
             return fn
         for s in range(0, len(blocks), n):
             e = min(s + n, len(blocks))
-            x = ckpt.checkpoint(chunk_fn(s, e), self._watch(x, e), positions, use_reentrant=False)
+            store = self._checkpoint_storage()
+            if store is None:
+                x = ckpt.checkpoint(chunk_fn(s, e), self._watch(x, e), positions, use_reentrant=False)
+            else:
+                with store:
+                    x = ckpt.checkpoint(chunk_fn(s, e), self._watch(x, e), positions, use_reentrant=True)
         return x
+
+    def _checkpoint_storage(self):
+        """Where the inputs of a checkpointed chunk live until its backward (the options of DeepSpeed's activation
+        checkpointing, reference: savanna/initialize.py:63-90): `checkpoint_in_cpu` moves them to pinned host memory and
+        back for the recomputation; `partition_activations` keeps 1 / tp of a tensor that is replicated over the
+        tensor-parallel group (no sequence parallelism) and all-gathers it for the recomputation.  Both are saved-tensor
+        hooks, so the chunk then runs through the re-entrant checkpoint, which hands its inputs to `save_for_backward`
+        (the non-re-entrant one keeps them in a closure that no hook sees).  None when neither option is on."""
+        cfg = self.cfg
+        if cfg.checkpoint_in_cpu:
+            return torch.autograd.graph.save_on_cpu(pin_memory=torch.cuda.is_available())
+        tp = state.get_model_parallel_world_size()
+        if cfg.partition_activations and tp > 1 and not self.sequence_parallel:
+            return _partitioned_saved_tensors(tp, state.get_model_parallel_rank(), state.get_model_parallel_group())
+        return None
 
     def logits(self, h: torch.Tensor) -> torch.Tensor:
         h = self.final_norm(h)
@@ -158,6 +179,25 @@ def build_model(cfg, device=None) -> Backbone:
     if cfg.padded_vocab_size is None:
         raise ValueError("padded_vocab_size is unset: build the tokenizer first (cfg.build_tokenizer())")
     return Backbone(cfg, device=device)
+
+
+def _partitioned_saved_tensors(tp: int, rank: int, group):
+    """Saved-tensor hooks that store this rank's 1 / tp slice (along the sequence dimension) of every saved floating-point
+    activation [B, L, D] whose length divides by tp, and rebuild the whole tensor with an all-gather when the backward
+    asks for it.  Every tensor-parallel rank saves and restores the same tensors in the same order."""
+    def pack(t):
+        if t.dim() == 3 and t.is_floating_point() and t.shape[1] % tp == 0 and t.shape[1] >= tp and not isinstance(t, nn.Parameter):
+            return ("part", t.chunk(tp, dim=1)[rank].contiguous(), t.shape)
+        return ("whole", t, None)
+
+    def unpack(packed):
+        kind, t, shape = packed
+        if kind == "whole":
+            return t
+        parts = [torch.empty_like(t) for _ in range(tp)]
+        dist.all_gather(parts, t, group=group)
+        return torch.cat(parts, dim=1).view(shape)
+    return torch.autograd.graph.saved_tensors_hooks(pack, unpack)
 
 
 def param_groups(model: nn.Module, cfg):

@@ -88,6 +88,29 @@ def test_activation_checkpointing_same_result():
     assert all(abs(a - b) < 1e-5 for a, b in zip(la, lb))
 
 
+def test_checkpoint_in_cpu_same_result_and_inputs_leave_through_the_hooks(monkeypatch):
+    """`checkpoint_in_cpu`: the chunk inputs pass through the host-offload hooks (counted) and training is unchanged."""
+    seen = []
+    real = torch.autograd.graph.save_on_cpu
+
+    class Counting(real):
+        def __init__(self, *a, **k):
+            super().__init__(*a, **k)
+            pack = self.pack_hook
+
+            def counted(t):
+                seen.append(tuple(t.shape))
+                return pack(t)
+            self.pack_hook = counted
+    monkeypatch.setattr(torch.autograd.graph, "save_on_cpu", Counting)
+    ca, cb = _cfg(), _cfg(checkpoint_activations=True, checkpoint_num_layers=2, checkpoint_in_cpu=True)
+    ta, tb = Trainer(ca, load=False), Trainer(cb, load=False)
+    la = [float(ta.train_step(_iter(ca))) for _ in range(2)]
+    lb = [float(tb.train_step(_iter(cb))) for _ in range(2)]
+    assert all(abs(a - b) < 1e-5 for a, b in zip(la, lb))
+    assert any(len(sh) == 3 and sh[-1] == cb.hidden_size for sh in seen), seen
+
+
 def test_checkpoint_resume_bit_exact(tmp_path):
     save = str(tmp_path / "ckpt")
     cfg = _cfg(save=save, train_iters=6)

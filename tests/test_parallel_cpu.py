@@ -192,6 +192,38 @@ def test_tensor_parallel_equivalence():
     run_distributed(_w_equiv, 2, {"model_parallel_size": 2}, ref_losses)
 
 
+def _w_partition_activations(rank, world, ref_losses):
+    """tp = 2 with checkpointed chunks whose saved inputs are cut to 1 / tp and gathered back for the recomputation."""
+    import savanna_b200.models.backbone as bb
+    stored = []
+    real = bb._partitioned_saved_tensors
+
+    def spy(tp, r, group):
+        ctx = real(tp, r, group)
+        pack = ctx.pack_hook
+
+        def counted(t):
+            out = pack(t)
+            stored.append((out[0], tuple(t.shape), tuple(out[1].shape)))
+            return out
+        ctx.pack_hook = counted
+        return ctx
+    bb._partitioned_saved_tensors = spy
+    cfg = _tiny_cfg(world, model_parallel_size=2, checkpoint_activations=True, checkpoint_num_layers=2,
+                    partition_activations=True)
+    tr, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    parts = [s for s in stored if s[0] == "part"]
+    assert parts and all(p[2][1] * 2 == p[1][1] for p in parts), stored
+
+
+@pytest.mark.slow
+def test_partition_activations_over_tensor_parallel_ranks():
+    ref_losses = _reference_losses()
+    run_distributed(_w_partition_activations, 2, ref_losses)
+
+
 @pytest.mark.slow
 def test_sequence_parallel_equivalence():
     ref_losses = _reference_losses()
