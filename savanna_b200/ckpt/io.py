@@ -309,7 +309,9 @@ def _publish(cfg, root: str, d: str, it: int) -> None:
             fh.write(f"global_step{it}")
         if cfg.keep_last_n_checkpoints:
             _delete_old(root, cfg.keep_last_n_checkpoints)
-        if cfg.checkpoint_stores:
+        # only every `save_retain_interval`-th iteration goes to the long-term stores; the others live (and are
+        # pruned) on the local disk alone (reference: savanna/checkpointing.py:338-346)
+        if cfg.checkpoint_stores and it % max(1, int(cfg.save_retain_interval or 1)) == 0:
             _upload(cfg, d)
     _barrier()
     print_rank_0(f"  saved checkpoint at iteration {it} to {d}")

@@ -203,7 +203,7 @@ def _partitioned_saved_tensors(tp: int, rank: int, group):
 def param_groups(model: nn.Module, cfg):
     """Weight-decay / no-weight-decay (+ optional per-group lr) parameter groups
     (reference: savanna/model/utils.py:28-109): no decay for norms, biases and Hyena filter
-    parameters; optional own lr for Hyena-MR filters (`lr_medium_hyena`) and for the no-decay group
+    parameters (filters are decayed when `hyena_filter_wd` is non-zero); optional own lr for Hyena-MR filters (`lr_medium_hyena`) and for the no-decay group
     (`wd_free_lr`)."""
     decay, no_decay, medium = [], [], []
     for name, p in model.named_parameters():
@@ -211,6 +211,8 @@ def param_groups(model: nn.Module, cfg):
             continue
         if cfg.lr_medium_hyena is not None and ".filter.h" in name:
             medium.append(p)
+        elif getattr(p, "is_filter_param", False) and cfg.hyena_filter_wd != 0.0 and not name.endswith(".bias"):
+            decay.append(p)       # `hyena_filter_wd` non-zero: filter parameters are decayed like the other weights
         elif getattr(p, "is_norm_param", False) or getattr(p, "is_filter_param", False) or name.endswith(".bias") \
                 or p.dim() == 1:
             no_decay.append(p)

@@ -130,21 +130,38 @@ class ParallelComplexModalFilter(nn.Module):
 
 class ParallelImplicitFreeformFilter(nn.Module):
     """Sine-activated MLP over a positional embedding, modulated by an exponential decay window
-    (parametrization/implicit_freeform.py:15-122, implicit_utils.py:12-111)."""
+    (parametrization/implicit_freeform.py:15-122, implicit_utils.py:12-111).
+
+    pos_emb "fourier_fixed": fixed features [t, cos(2 pi f t), sin(2 pi f t)] (emb_dim odd);  "random_fourier": a
+    learned frequency vector drawn from N(0, 2 pi omega_0), features [cos(w t), sin(w t)] on t in [-1, 1] (emb_dim
+    even, parameter `pos_emb.linear.weight`).  `normalized` applies a LayerNorm over the channels after the decay
+    window (`post_modulation_norm`)."""
 
     def __init__(self, d_model, emb_dim=33, order=64, num_inner_mlps=2, w=14, L_cache=8192, fast_decay=0.3,
-                 slow_decay=1.2, modulate=True, device=None):
+                 slow_decay=1.2, modulate=True, pos_emb="fourier_fixed", omega_0=1.0, normalized=False, device=None):
         super().__init__()
-        if emb_dim % 2 == 0 or emb_dim < 3:
-            raise ValueError("emb_dim must be odd and >= 3 (time + sine/cosine pairs)")
-        self.w, self.modulate = w, modulate
-        bands = (emb_dim - 1) // 2
-        t = torch.linspace(0, 1, L_cache, device=device)[:, None]
-        tr = torch.linspace(0, L_cache - 1, L_cache, device=device)[:, None]
-        f = torch.linspace(1e-4, bands - 1, bands, device=device)[None]
-        ang = 2 * math.pi * tr * f / L_cache
-        self.register_buffer("z", torch.cat([t, torch.cos(ang), torch.sin(ang)], dim=-1))
-        self.register_buffer("t", t)
+        self.w, self.modulate, self.pos_emb_type = w, modulate, pos_emb
+        if pos_emb == "fourier_fixed":
+            if emb_dim % 2 == 0 or emb_dim < 3:
+                raise ValueError("emb_dim must be odd and >= 3 (time + sine/cosine pairs)")
+            bands = (emb_dim - 1) // 2
+            t = torch.linspace(0, 1, L_cache, device=device)[:, None]
+            tr = torch.linspace(0, L_cache - 1, L_cache, device=device)[:, None]
+            f = torch.linspace(1e-4, bands - 1, bands, device=device)[None]
+            ang = 2 * math.pi * tr * f / L_cache
+            self.register_buffer("z", torch.cat([t, torch.cos(ang), torch.sin(ang)], dim=-1))
+            self.register_buffer("t", t)
+        elif pos_emb == "random_fourier":
+            if emb_dim % 2:
+                raise ValueError(f"emb_dim must be even for the random Fourier embedding (got {emb_dim})")
+            self.pos_emb = nn.Module()
+            self.pos_emb.linear = nn.Linear(1, emb_dim // 2, bias=False, device=device)
+            with torch.no_grad():
+                self.pos_emb.linear.weight.normal_(0.0, 2 * math.pi * omega_0)
+            self.register_buffer("t_sym", torch.linspace(-1, 1, L_cache, device=device)[:, None])
+            self.register_buffer("t", (self.t_sym + 1) / 2)
+        else:
+            raise ValueError(f"hyena_pos_emb {pos_emb!r} unknown (fourier_fixed | random_fourier)")
         layers = [nn.Linear(emb_dim, order, device=device)]
         for _ in range(num_inner_mlps):
             layers.append(nn.Linear(order, order, device=device))
@@ -154,16 +171,23 @@ class ParallelImplicitFreeformFilter(nn.Module):
         max_decay = math.log(1e-2) / fast_decay
         min_decay = math.log(1e-2) / slow_decay
         self.register_buffer("deltas", torch.linspace(min_decay, max_decay, d_model, device=device)[None])
+        self.post_modulation_norm = nn.LayerNorm(d_model, device=device) if normalized else None
         for q in self.parameters():
             q.is_filter_param = True
 
     def forward(self, L: int):
-        x = self.z[:L]
+        if self.pos_emb_type == "random_fourier":
+            ang = self.pos_emb.linear(self.t_sym[:L])
+            x = torch.cat([torch.cos(ang), torch.sin(ang)], dim=-1)
+        else:
+            x = self.z[:L]
         for lin in self.layers[:-1]:
             x = torch.sin(self.freq * lin(x))
         h = self.layers[-1](x)
         if self.modulate:
             h = h * torch.exp(-self.t[:L] * self.deltas.abs())
+        if self.post_modulation_norm is not None:
+            h = self.post_modulation_norm(h)
         return h.transpose(0, 1).float()
 
     filter = forward
@@ -183,10 +207,16 @@ def build_filter(cfg, operator_type: str, num_groups: int, device=None) -> nn.Mo
         return ImplicitRealModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length, cfg.hyena_filter_r_min,
                                        cfg.hyena_filter_r_max, cfg.modal_residue_factors, cfg.modal_pole_factors,
                                        device=device)
+    # a two-sided (`bidirectional`) operator asks its filter for a forward and a backward half: twice the rows
+    two_sided = 2 if cfg.bidirectional and operator_type == "hyena" else 1
+    if two_sided == 2 and cls not in ("implicit_complex_modal", "implicit", "implicit_freeform"):
+        raise ValueError(f"bidirectional needs an implicit free-form or complex modal filter (got {cls!r})")
     if cls == "implicit_complex_modal":
-        return ParallelComplexModalFilter(num_groups, cfg.hyena_filter_order, device=device)
+        return ParallelComplexModalFilter(num_groups * two_sided, cfg.hyena_filter_order, device=device)
     if cls in ("implicit", "implicit_freeform"):
-        return ParallelImplicitFreeformFilter(num_groups, cfg.hyena_filter_emb_dim, cfg.hyena_filter_order,
+        return ParallelImplicitFreeformFilter(num_groups * two_sided, cfg.hyena_filter_emb_dim, cfg.hyena_filter_order,
                                               cfg.hyena_filter_num_inner_mlps, cfg.hyena_filter_w, cfg.seq_length,
-                                              cfg.hyena_filter_fast_decay, cfg.hyena_filter_slow_decay, device=device)
+                                              cfg.hyena_filter_fast_decay, cfg.hyena_filter_slow_decay,
+                                              pos_emb=cfg.hyena_pos_emb, omega_0=cfg.hyena_filter_omega_0,
+                                              normalized=cfg.normalize_hyena_filters, device=device)
     raise ValueError(f"hyena filter class {cls!r} unknown")

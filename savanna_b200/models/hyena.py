@@ -134,8 +134,16 @@ class HyenaOperator(nn.Module):
         self.width, self.num_groups, self.group_dim = groups_per_rank(hidden_size, g, tp, cfg.hyena_width_expansion)
         self.hyena_mr_len = cfg.hyena_mr_len
         self.use_cp = cfg.use_cp_hyena
+        # the two PyTorch-level variants of the long operator: a two-sided filter, and outer-product heads with one
+        # filter and one bias per group.  They apply to the `hyena` (long) layers; hyena_mr layers of the same model keep
+        # their causal finite filter
+        self.bidirectional = bool(cfg.bidirectional) and not self.is_mr
+        self.slow_heads = bool(cfg.use_slow_heads) and not self.is_mr
+        if self.bidirectional and self.slow_heads:
+            raise ValueError("bidirectional and use_slow_heads exclude each other")
         self.filter = build_filter(cfg, operator_type, self.num_groups, device=device)
-        self.conv_bias = nn.Parameter(torch.full((self.width,), float(cfg.conv_bias_init), dtype=torch.float32, device=device))
+        bias_len = self.num_groups if self.slow_heads else self.width
+        self.conv_bias = nn.Parameter(torch.full((bias_len,), float(cfg.conv_bias_init), dtype=torch.float32, device=device))
         self.conv_bias.model_parallel = True
         self.conv_bias.partition_dim = 0
         self.conv_bias.is_filter_param = True
@@ -177,6 +185,12 @@ class HyenaOperator(nn.Module):
 
     def _forward_li(self, feat, cp):
         B, L, C = feat.shape
+        if self.bidirectional or self.slow_heads:
+            if cp > 1:
+                raise NotImplementedError("bidirectional / use_slow_heads do not run under context parallelism")
+            h = self.filter(L)
+            fn = ops.hyena_long_fft_bidirectional if self.bidirectional else ops.hyena_multihead
+            return fn(feat, h, self.conv_bias)
         modal = self._modal()
         if cp == 1:
             if modal is not None:

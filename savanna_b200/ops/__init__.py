@@ -157,6 +157,14 @@ def hyena_long_fft(feat, h, bias):
     return ref.hyena_long_fft(feat, h, bias)
 
 
+def hyena_long_fft_bidirectional(feat, h, bias):
+    return ref.hyena_long_fft_bidirectional(feat, h, bias)
+
+
+def hyena_multihead(feat, h, bias):
+    return ref.hyena_multihead(feat, h, bias)
+
+
 # ----------------------------------------------------------------------------- attention
 
 

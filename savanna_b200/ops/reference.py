@@ -120,6 +120,57 @@ def fft_causal_conv(u: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
     return y.transpose(1, 2)
 
 
+def fft_bidirectional_conv(u: torch.Tensor, h_fwd: torch.Tensor, h_bwd: torch.Tensor) -> torch.Tensor:
+    """The reference's `bidirectional` long convolution (fftconv.py:19-38), stated as it computes it: with U, K1, K2 the
+    size-2L real FFTs of the input and of the two filter halves,  y = irfft(U K1 + conj(U K2))[:L].  The first term is
+    the causal convolution with h_fwd; conjugating a spectrum reverses the (circular, length 2L) signal in time, so the
+    second term is c[(2L - t) mod 2L] with c the linear convolution of u and h_bwd: positions t >= 1 see c[2L - t], the
+    part of that convolution that extends past the end of the sequence.  u [B, L, C], filters [C, Lh]."""
+    L = u.shape[1]
+    n = 2 * L
+    uf = torch.fft.rfft(u.float().transpose(1, 2), n=n)
+    k1 = torch.fft.rfft(h_fwd.float()[..., :L], n=n)
+    k2 = torch.fft.rfft(h_bwd.float()[..., :L], n=n)
+    y = torch.fft.irfft(uf * k1 + (uf * k2).conj(), n=n)[..., :L]
+    return y.transpose(1, 2)
+
+
+def hyena_long_fft_bidirectional(feat: torch.Tensor, h: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """Hyena long convolution with a two-sided filter h [2*G, L]: rows [:G] act forward, rows [G:] through the
+    conjugate term of `fft_bidirectional_conv`."""
+    x1, x2, v = split_features(feat)
+    D = x1.shape[-1]
+    G = h.shape[0] // 2
+    hf, hb = h[:G], h[G:]
+    if G != D:
+        hf, hb = hf.repeat_interleave(D // G, dim=0), hb.repeat_interleave(D // G, dim=0)
+    u = (x2 * v).float()
+    y = fft_bidirectional_conv(u, hf, hb) + bias.float() * u
+    return (x1.float() * y).to(feat.dtype)
+
+
+def hyena_multihead(feat: torch.Tensor, h: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """Outer-product ("slow") heads of the Hyena operator (reference: operators/hyena/hyena.py:361-406).  The width D is
+    H heads of d channels (channel = head * d + i), one filter h [H, L] and one bias [H] per head:
+        kv[i, j] = x2[head, i] * v[head, j]                      (d x d per head and position)
+        o[i, j]  = causal_conv(kv[i, j], h[head]) + bias[head] * kv[i, j]
+        z[head, j] = sum_i x1[head, i] * o[i, j]
+    feat [B, L, 3D] interleaved -> [B, L, D]."""
+    x1, x2, v = split_features(feat)
+    B, L, D = x1.shape
+    H = h.shape[0]
+    d = D // H
+    q = x1.float().reshape(B, L, H, d)
+    k = x2.float().reshape(B, L, H, d)
+    vv = v.float().reshape(B, L, H, d)
+    kv = k.unsqueeze(-1) * vv.unsqueeze(-2)                                   # [B, L, H, d(i), d(j)]
+    hc = h.float().repeat_interleave(d * d, dim=0)                            # one filter row per (head, i, j)
+    o = fft_causal_conv(kv.reshape(B, L, H * d * d), hc).reshape(B, L, H, d, d)
+    o = o + bias.float().view(1, 1, H, 1, 1) * kv
+    z = (q.unsqueeze(-1) * o).sum(-2)                                         # [B, L, H, d(j)]
+    return z.reshape(B, L, D).to(feat.dtype)
+
+
 def modal_filter(gamma: torch.Tensor, R: torch.Tensor, p: torch.Tensor, L: int, t0: int = 0) -> torch.Tensor:
     """h[d, t] = sum_o R[d,o] exp(-exp(p[d,o]) exp(gamma[d,o]) t), t = t0..t0+L-1 (fp32) -> [D, L]."""
     t = torch.arange(t0, t0 + L, device=gamma.device, dtype=torch.float32)

@@ -127,7 +127,7 @@ class Trainer:
         self.profiler = None
         self.timers = None
         self.watchdog = None
-        self.straggler = self.comms_logger = self.alloc_stats = None
+        self.straggler = self.comms_logger = self.alloc_stats = self.mem_snapshots = None
         if load and cfg.load is not None:
             from ..ckpt import load_checkpoint
             self.iteration = load_checkpoint(self)
@@ -403,6 +403,8 @@ class Trainer:
         from ..utils import observability
         self.straggler, self.comms_logger, self.alloc_stats = observability.build_from_config(
             cfg, cfg.rank or 0, int(os.environ.get("WORLD_SIZE", "1")))
+        from ..utils.memory_stats import MemorySnapshotter
+        self.mem_snapshots = MemorySnapshotter.from_config(cfg, cfg.rank or 0, self.iteration)
         self.profiler.start()
         if cfg.save and self.iteration == 0 and cfg.save_iters and 0 in cfg.save_iters:
             with self._unwatched():
@@ -410,8 +412,15 @@ class Trainer:
         try:
             while self.iteration < cfg.train_iters:
                 t0 = time.time()
-                loss = self.train_step(train_iter)
+                try:
+                    loss = self.train_step(train_iter)
+                except torch.OutOfMemoryError:
+                    if self.mem_snapshots is not None:
+                        self.mem_snapshots.on_oom()      # the allocator history that led to the failure
+                    raise
                 self.profiler.step()
+                if self.mem_snapshots is not None:
+                    self.mem_snapshots.step()
                 logger.log_step(loss, time.time() - t0)
                 it = self.iteration
                 if self.straggler is not None:
@@ -447,6 +456,8 @@ class Trainer:
                     gc.collect(cfg.gc_collect_generation)
         finally:
             self.profiler.stop()
+            if self.mem_snapshots is not None:
+                self.mem_snapshots.close()
             if self.watchdog is not None:
                 self.watchdog.stop()
             if self.comms_logger is not None:

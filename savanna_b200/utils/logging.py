@@ -207,7 +207,7 @@ class TrainingLogger:
                 name = getattr(g, "name", None) or g.hyper.get("name", str(i))
                 self._log(f"optimizer_state_norms/{name}_{i}/exp_avg", float(g.exp_avg.float().norm()), it)
                 self._log(f"optimizer_state_norms/{name}_{i}/exp_avg_sq", float(g.exp_avg_sq.float().norm()), it)
-        if cfg.log_param_norm or cfg.log_grad_norm:
+        if cfg.log_param_norm or cfg.log_grad_norm or cfg.log_grad_pct_zeros:
             # ZeRO stage 2 / 3 keep no whole gradients after the step and (stage 3) no whole parameters: gather the
             # parameters for the read, skip the per-parameter gradient norms
             part = getattr(tr, "partitioned", False)
@@ -218,6 +218,9 @@ class TrainingLogger:
                         self._log(f"param_norm/{name}", float(p.detach().float().norm()), it)
                     if cfg.log_grad_norm and not part and p.grad is not None:
                         self._log(f"grad_norm/{name}", float(p.grad.detach().float().norm()), it)
+                    if cfg.log_grad_pct_zeros and not part and p.grad is not None:
+                        # share of exactly-zero gradient entries: dead units, saturated gates, underflow in low precision
+                        self._log(f"pct_grad_zeros/{name}", float((p.grad.detach() == 0).float().mean()) * 100.0, it)
         print_rank_0(line)
 
     def log_eval(self, results: Dict[str, float], it: int, prefix: str = "validation") -> None:

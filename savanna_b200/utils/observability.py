@@ -347,5 +347,7 @@ def build_from_config(cfg, rank: int, world: int):
                             verbose=bool(cfg.deepspeed_comms_logging_verbose))
         comms.install()
         comms.enabled = True
-    alloc = AllocStats(rank, enabled=True) if cfg.print_mem_alloc_stats else None
+    # every `mem_alloc_stats_ranks`-th rank reports (1 = all ranks); the others stay silent
+    every = max(1, int(cfg.mem_alloc_stats_ranks or 1))
+    alloc = AllocStats(rank, enabled=True) if cfg.print_mem_alloc_stats and rank % every == 0 else None
     return det, comms, alloc

@@ -179,6 +179,20 @@ def test_keep_last_n(tmp_path):
     assert dirs == ["global_step2", "global_step3"]
 
 
+def test_save_retain_interval_selects_the_uploaded_checkpoints(tmp_path):
+    """Every save lands on the local disk; only iterations that are multiples of `save_retain_interval` reach the stores."""
+    save, mirror = str(tmp_path / "c"), str(tmp_path / "mirror")
+    cfg = _cfg(save=save, save_retain_interval=2, checkpoint_stores=[{"storage_type": "posix", "location": mirror}])
+    tr = Trainer(cfg, load=False)
+    from savanna_b200.ckpt import save_checkpoint
+    d = _iter(cfg)
+    for _ in range(4):
+        tr.train_step(d)
+        save_checkpoint(tr)
+    assert sorted(p for p in os.listdir(save) if p.startswith("global_step")) == [f"global_step{i}" for i in (1, 2, 3, 4)]
+    assert sorted(os.listdir(mirror)) == ["global_step2", "global_step4"]
+
+
 def test_finetune_loads_module_only(tmp_path):
     save = str(tmp_path / "c")
     cfg = _cfg(save=save)
@@ -288,3 +302,25 @@ def test_mup_optimizer_groups_scale_matrix_like_learning_rates():
     vec2 = next(g for g in g2 if g["name"] == "no_decay")
     assert abs(vec2["lr"] - cfg2.lr * 4) < 1e-12
     assert "lr" not in next(g for g in g2 if g["name"] == "decay_matrix")
+
+
+@pytest.mark.parametrize("over", [
+    {"bidirectional": True, "hyena_filter_cls": "implicit_freeform", "hyena_filter_emb_dim": 5, "hyena_filter_order": 16},
+    {"use_slow_heads": True, "num_groups_hyena": 16},
+    {"hyena_filter_cls": "implicit_freeform", "hyena_pos_emb": "random_fourier", "hyena_filter_emb_dim": 8,
+     "hyena_filter_order": 16, "normalize_hyena_filters": True},
+])
+def test_long_operator_variants_train(over):
+    """Two-sided filters, outer-product heads and the free-form filter's options: the tiny model builds with them, trains,
+    and the loss falls."""
+    cfg = _cfg(**over)
+    tr = Trainer(cfg, load=False)
+    d = _iter(cfg)
+    losses = [float(tr.train_step(d)) for _ in range(6)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+    if over.get("use_slow_heads"):
+        li = [m for m in tr.model.modules() if getattr(m, "slow_heads", False)]
+        assert li and li[0].conv_bias.shape == (li[0].num_groups,)
+    if over.get("bidirectional"):
+        li = [m for m in tr.model.modules() if getattr(m, "bidirectional", False)]
+        assert li and li[0].filter(8).shape[0] == 2 * li[0].num_groups

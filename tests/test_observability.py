@@ -171,3 +171,78 @@ def test_native_library_proxy_opens_an_nvtx_range_per_entry_point(monkeypatch):
         assert calls[-1] == ("pop",)                             # the range is closed on exceptions too
     finally:
         cuda_ops.set_nvtx(False)
+
+
+def test_memory_snapshotter_writes_every_freq_steps_and_on_oom(tmp_path):
+    """The snapshot schedule, file layout and the out-of-memory dump, with the two allocator calls replaced."""
+    import pickle
+    from savanna_b200.utils.memory_stats import MemorySnapshotter
+    calls = []
+    snap = MemorySnapshotter(str(tmp_path), rank=3, step=10, freq=2, max_entries=77,
+                             recorder=lambda **kw: calls.append(kw), snapshot=lambda: {"segments": [1, 2]},
+                             printer=lambda *_: None)
+    assert calls == [{"max_entries": 77}]
+    for _ in range(4):
+        snap.step()                                   # steps 11 .. 14: snapshots at 12 and 14
+    snap.on_oom()
+    snap.close()
+    assert calls[-1] == {"enabled": None}
+    rel = [p.replace(str(tmp_path), "") for p in snap.written]
+    assert rel == ["/rank3/iteration_12/rank3_memory_snapshot.pickle", "/rank3/iteration_14/rank3_memory_snapshot.pickle",
+                   "/rank3/iteration_14_exit/rank3_memory_snapshot.pickle"]
+    with open(snap.written[0], "rb") as fh:
+        assert pickle.load(fh) == {"segments": [1, 2]}
+
+    class Cfg:
+        enable_memory_snapshot = False
+        memory_snapshot_rank0_only = True
+    assert MemorySnapshotter.from_config(Cfg, 0) is None
+
+
+def test_alloc_stats_reporting_ranks_and_gradient_zero_share(tmp_path):
+    """`mem_alloc_stats_ranks` picks every n-th rank; `log_grad_pct_zeros` logs the share of zero gradient entries."""
+    import os
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.utils import observability
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")],
+                                 {"global_num_gpus": 1, "print_mem_alloc_stats": True, "mem_alloc_stats_ranks": 4,
+                                  "log_grad_pct_zeros": True, "log_interval": 1})
+    assert observability.build_from_config(cfg, 0, 8)[2] is not None
+    assert observability.build_from_config(cfg, 4, 8)[2] is not None
+    assert observability.build_from_config(cfg, 5, 8)[2] is None
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train.trainer import Trainer
+    from savanna_b200.utils.logging import TrainingLogger
+    tr = Trainer(cfg, load=False)
+    logged = {}
+    lg = TrainingLogger(cfg, tr)
+    lg._log = lambda k, v, it: logged.__setitem__(k, v)
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    loss = tr.train_step(it())
+    lg.log_step(loss, 0.1)
+    keys = [k for k in logged if k.startswith("pct_grad_zeros/")]
+    assert keys and all(0.0 <= logged[k] <= 100.0 for k in keys)
+
+
+def test_hyena_filter_weight_decay_switch():
+    import os
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.models.backbone import param_groups
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    yml = [os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")]
+
+    def filters_in(group_name, **over):
+        cfg = GlobalConfig.from_ymls(yml, {"global_num_gpus": 1, **over})
+        tr = Trainer(cfg, load=False)
+        groups = {g["name"]: g for g in param_groups(tr.model, cfg)}
+        ids = {id(p) for p in groups[group_name]["params"]}
+        return [n for n, p in tr.model.named_parameters() if getattr(p, "is_filter_param", False) and id(p) in ids]
+    assert filters_in("decay") == [] and filters_in("no_decay")
+    assert filters_in("decay", hyena_filter_wd=0.1)

@@ -115,3 +115,75 @@ def test_hippo_nplr_and_dplr_initialisers():
     assert wc.shape == (4, 4) and Pc.shape == (1, 4, 4) and Vc.shape == (4, 8, 4)
     E = si.embed_c2r(torch.tensor([[1 + 2j]]))
     assert torch.equal(E, torch.tensor([[1.0, -2.0], [2.0, 1.0]]))
+
+
+def test_bidirectional_long_convolution_matches_its_time_domain_statement():
+    """y[t] = sum_{j<=t} h1[t-j] u[j] + c2[(2L - t) mod 2L], c2 the linear convolution of u with the second half."""
+    import torch
+    from savanna_b200.ops import reference as ref
+    torch.manual_seed(0)
+    B, L, D = 2, 12, 4
+    feat = torch.randn(B, L, 3 * D, dtype=torch.float64)
+    h = torch.randn(2 * D, L, dtype=torch.float64)
+    bias = torch.randn(D, dtype=torch.float64)
+    got = ref.hyena_long_fft_bidirectional(feat, h, bias).double()
+    x1, x2, v = ref.split_features(feat)
+    u = x2 * v
+    want = torch.zeros(B, L, D, dtype=torch.float64)
+    for d in range(D):
+        for b in range(B):
+            c1 = torch.zeros(2 * L, dtype=torch.float64)
+            c2 = torch.zeros(2 * L, dtype=torch.float64)
+            for j in range(L):
+                for k in range(L):
+                    c1[j + k] += u[b, j, d] * h[d, k]
+                    c2[j + k] += u[b, j, d] * h[D + d, k]
+            for t in range(L):
+                want[b, t, d] = c1[t] + c2[(2 * L - t) % (2 * L)]
+    want = x1 * (want + bias * u)
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+def test_multihead_hyena_matches_its_time_domain_statement():
+    import torch
+    from savanna_b200.ops import reference as ref
+    torch.manual_seed(1)
+    B, L, H, d = 2, 10, 3, 2
+    D = H * d
+    feat = torch.randn(B, L, 3 * D, dtype=torch.float64)
+    h = torch.randn(H, L, dtype=torch.float64)
+    bias = torch.randn(H, dtype=torch.float64)
+    got = ref.hyena_multihead(feat, h, bias).double()
+    x1, x2, v = ref.split_features(feat)
+    want = torch.zeros(B, L, D, dtype=torch.float64)
+    for hd in range(H):
+        for i in range(d):
+            for j in range(d):
+                kv = x2[:, :, hd * d + i] * v[:, :, hd * d + j]              # [B, L]
+                o = bias[hd] * kv
+                for t in range(L):
+                    for s in range(t + 1):
+                        o[:, t] = o[:, t] + h[hd, t - s] * kv[:, s]
+                want[:, :, hd * d + j] += x1[:, :, hd * d + i] * o
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+def test_freeform_filter_position_embeddings_and_normalisation():
+    import torch
+    from savanna_b200.models.filters import ParallelImplicitFreeformFilter
+    torch.manual_seed(0)
+    f = ParallelImplicitFreeformFilter(6, emb_dim=8, order=16, L_cache=64, pos_emb="random_fourier", omega_0=2.0,
+                                       normalized=True)
+    h = f(48)
+    assert h.shape == (6, 48)
+    assert torch.allclose(h.mean(0), torch.zeros(48), atol=1e-5)              # LayerNorm over the channels
+    names = dict(f.named_parameters())
+    assert "pos_emb.linear.weight" in names and "post_modulation_norm.weight" in names
+    assert 2.0 < float(names["pos_emb.linear.weight"].std()) < 40.0           # drawn at scale 2 pi omega_0
+    h.sum().backward()
+    assert names["pos_emb.linear.weight"].grad is not None
+    import pytest
+    with pytest.raises(ValueError):
+        ParallelImplicitFreeformFilter(6, emb_dim=9, pos_emb="random_fourier")
+    g = ParallelImplicitFreeformFilter(6, emb_dim=9, order=16, L_cache=64)(32)
+    assert g.shape == (6, 32) and float(g[:, -1].abs().max()) < float(g[:, 0].abs().max()) + 1.0
