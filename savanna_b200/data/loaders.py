@@ -57,23 +57,37 @@ def get_train_valid_test_split_(splits_string: str, size: int):
     return idx
 
 
+def _sample_format(cfg):
+    """(sample length, dtype, enforce exact length).  Direct-preference rows are float32 records of
+    `dpo_data_seq_length` + 1 values (two texts and their reference log-probabilities, written by
+    tools/preprocess_data_dpo.py) and must come back whole; everything else is seq_length + 1 int64 token ids
+    (reference: savanna/data/data_utils.py:211-221)."""
+    if cfg.alignment_method == "dpo":
+        if cfg.dpo_data_seq_length is None:
+            raise ValueError("alignment_method dpo: set dpo_data_seq_length (the record length of the preference data)")
+        return int(cfg.dpo_data_seq_length), np.float32, True
+    return cfg.seq_length, np.int64, bool(cfg.enforce_sample_length)
+
+
 def build_the_dataset(prefix, name, cfg, num_samples, seed, skip_warmup=True, build_index=True):
     ids = make_dataset(prefix, cfg.data_impl, skip_warmup)
     docs = np.arange(0, ids.sizes.shape[0], dtype=np.int32)
-    return SequenceDataset(name, prefix, docs, ids, num_samples, cfg.seq_length, seed, build_index=build_index,
-                           use_shared_fs=cfg.use_shared_fs, enforce_sample_length=cfg.enforce_sample_length)
+    length, dtype, enforce = _sample_format(cfg)
+    return SequenceDataset(name, prefix, docs, ids, num_samples, length, seed, build_index=build_index,
+                           use_shared_fs=cfg.use_shared_fs, enforce_sample_length=enforce, sample_dtype=dtype)
 
 
 def build_train_valid_test_datasets(prefix, cfg, splits_string, nums, seed, skip_warmup=True):
     ids = make_dataset(prefix, cfg.data_impl, skip_warmup)
     total = ids.sizes.shape[0]
     splits = get_train_valid_test_split_(splits_string, total)
+    length, dtype, enforce = _sample_format(cfg)
     out = []
     for i, name in enumerate(("train", "valid", "test")):
         if splits[i + 1] > splits[i] and nums[i] > 0:
             docs = np.arange(splits[i], splits[i + 1], dtype=np.int32)
-            out.append(SequenceDataset(name, prefix, docs, ids, nums[i], cfg.seq_length, seed,
-                                       use_shared_fs=cfg.use_shared_fs, enforce_sample_length=cfg.enforce_sample_length))
+            out.append(SequenceDataset(name, prefix, docs, ids, nums[i], length, seed, use_shared_fs=cfg.use_shared_fs,
+                                       enforce_sample_length=enforce, sample_dtype=dtype))
         else:
             out.append(None)
     return out

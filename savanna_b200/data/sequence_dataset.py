@@ -73,11 +73,17 @@ def build_index_mappings(name, data_prefix, documents, sizes, num_samples, seq_l
 
 class SequenceDataset(torch.utils.data.Dataset):
     def __init__(self, name, data_prefix, documents, indexed_dataset, num_samples, seq_length, seed,
-                 build_index=True, use_shared_fs=True, enforce_sample_length=False):
+                 build_index=True, use_shared_fs=True, enforce_sample_length=False, sample_dtype=np.int64):
         self.name, self.ds = name, indexed_dataset
         self.seq_length, self.enforce = seq_length, enforce_sample_length
+        self.sample_dtype = sample_dtype        # int64 token ids; float32 for preference rows (tokens + log-probabilities)
         if np.min(documents) < 0 or np.max(documents) >= len(indexed_dataset.sizes):
             raise ValueError("document ids out of range")
+        if enforce_sample_length and np.any(np.asarray(indexed_dataset.sizes) != seq_length):
+            # fixed-length records (preference rows): every sample is one whole record, so every document must be
+            # exactly `seq_length` long (sample i then starts at document i, offset 0)
+            raise ValueError(f"enforce_sample_length: {data_prefix} holds documents whose length is not {seq_length}; "
+                             "the data needs to be rewritten at that record length")
         if build_index:
             self.doc_idx, self.sample_idx, self.shuffle_idx = build_index_mappings(
                 name, data_prefix, documents, indexed_dataset.sizes, num_samples, seq_length, seed, use_shared_fs)
@@ -101,7 +107,7 @@ class SequenceDataset(torch.utils.data.Dataset):
                 parts.append(self.ds.get(int(self.doc_idx[i])))
             parts.append(self.ds.get(int(self.doc_idx[l_doc]), length=l_off + 1))
             sample = np.concatenate(parts)
-        sample = np.asarray(sample, dtype=np.int64)
+        sample = np.asarray(sample, dtype=self.sample_dtype)
         if self.enforce and len(sample) != self.seq_length + 1:
             raise ValueError(f"sample {idx} has {len(sample)} tokens, expected {self.seq_length + 1}")
         return {"text": sample}

@@ -55,6 +55,8 @@ class CachedDecoder:
         for b in self.blocks:
             if not isinstance(b.mlp, ParallelGLU):
                 raise NotImplementedError("cached generation supports the gated MLP")
+            if getattr(b.mixer, "tie_projections", False) or getattr(b.mixer, "proj_groups", 1) > 1:
+                raise NotImplementedError("cached generation expects the full-width (3 x hidden) in-projection")
             m = b.mixer.mixer
             if isinstance(m, HyenaOperator) and not m.is_mr and not isinstance(m.filter, ImplicitModalFilter):
                 raise NotImplementedError("cached generation needs the implicit modal filter for Hyena-LI")

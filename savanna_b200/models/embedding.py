@@ -43,6 +43,7 @@ class Embedding(nn.Module):
         self.dropout = nn.Dropout(cfg.hidden_dropout)
         self.sequence_parallel = cfg.sequence_parallel and state.get_model_parallel_world_size() > 1
         self.mup_mult = cfg.mup_embedding_mult if cfg.use_mup else 1.0
+        self.pos_mult = float(cfg.mup_rp_embedding_mult)      # multiplier of the position embeddings (word_embeddings.py:128)
 
     def _build_tokentypes(self, n: int, device) -> None:
         self.num_tokentypes = n
@@ -62,9 +63,9 @@ class Embedding(nn.Module):
                 raise RuntimeError("tokentype ids given to a model without tokentype embeddings")
             x = x + self.tokentype_embeddings(tokentype_ids)
         if self.pos_kind == "learned":
-            x = x + self.position_embeddings(positions + self.cfg.opt_pos_emb_offset)[None]
+            x = x + self.position_embeddings(positions + self.cfg.opt_pos_emb_offset)[None] * self.pos_mult
         elif self.pos_kind == "sinusoidal":
-            x = x + self.position_embeddings(positions, x.dtype)
+            x = x + self.position_embeddings(positions, x.dtype) * self.pos_mult
         if self.mup_mult != 1.0:
             x = x * self.mup_mult
         x = self.dropout(x)

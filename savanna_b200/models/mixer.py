@@ -112,7 +112,21 @@ class ParallelSequenceMixer(nn.Module):
         else:
             fp8_in = cfg.use_fp8_linears and cfg.use_fp8_input_projections
             fp8_out = cfg.use_fp8_linears and cfg.use_fp8_output_projections
-        self.dense_projection = ColumnParallelLinear(D, 3 * D, bias=False, gather_output=False, init_method=init_method,
+        # width of the in-projection: 3 D, or D when one projection serves as all three streams
+        # (`tie_projection_weights`), or D + 2 D / proj_groups for attention layers whose second and third stream are
+        # produced for one group of channels and repeated over the `proj_groups` groups
+        # (reference: savanna/model/block.py:213-236, 773-800)
+        self.tie_projections = bool(cfg.tie_projection_weights)
+        self.proj_groups = int(cfg.proj_groups or 1) if self.operator_type in ATTENTION_OPS else 1
+        if self.tie_projections:
+            proj_out = D
+        elif self.proj_groups > 1:
+            if (2 * D) % (self.proj_groups * tp):
+                raise ValueError(f"proj_groups={self.proj_groups}: 2 * hidden_size must divide by proj_groups * tensor-parallel size")
+            proj_out = D + 2 * D // self.proj_groups
+        else:
+            proj_out = 3 * D
+        self.dense_projection = ColumnParallelLinear(D, proj_out, bias=False, gather_output=False, init_method=init_method,
                                                      skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device,
                                                      fp8=fp8_in)
         if self.operator_type in HYENA_OPS:
@@ -144,6 +158,11 @@ class ParallelSequenceMixer(nn.Module):
             proj, _, residual = self.dense_projection.forward_normed(x, pre_norm)
         else:
             proj, _ = self.dense_projection(x)
+        if self.tie_projections:
+            proj = proj.repeat_interleave(3, dim=-1)              # every channel three times: its three streams are equal
+        elif self.proj_groups > 1:
+            own = proj.shape[-1] * self.proj_groups // (self.proj_groups + 2)          # this rank's D / tp first-stream columns
+            proj = torch.cat([proj[..., :own], proj[..., own:].repeat(1, 1, self.proj_groups)], dim=-1)
         if self.operator_type in HYENA_OPS:
             cp = state.get_context_parallel_world_size() if self.cfg.use_cp_hyena else 1
             if cp > 1:

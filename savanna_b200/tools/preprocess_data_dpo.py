@@ -4,7 +4,8 @@ frozen reference model, `ref_logprob_accept`, `ref_logprob_reject`.  A document 
 
     accept tokens, pad, reject tokens, pad, ref_logprob_accept, pad, ref_logprob_reject [, pad ... up to --seq-length]
 
-which `train/batch.py:build_batch_dpo` splits again.  The pad token must not occur inside the texts (the byte-level
+which `train/batch.py:build_batch_dpo` splits again.  Training reads one record per sample, so every row has to have
+the same length: give `--seq-length` and set the run's `dpo_data_seq_length` to the same number.  The pad token must not occur inside the texts (the byte-level
 tokenizer's pad id 1 never does for printable text).
 
     python -m savanna_b200.tools.preprocess_data_dpo --input pairs.jsonl --output-prefix out/pairs --seq-length 1024

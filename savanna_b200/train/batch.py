@@ -141,8 +141,9 @@ def build_batch_dpo(cfg, rows: torch.Tensor) -> Dict[str, torch.Tensor]:
             "ref_logps": torch.stack(lp_a + lp_r).float()}
 
 
-def get_batch(cfg, data_iterator, device) -> Dict[str, torch.Tensor]:
-    """Fetch from the iterator on the data-reading rank, broadcast to tensor/context peers, build."""
+def get_batch(cfg, data_iterator, device, max_len: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """Fetch from the iterator on the data-reading rank, broadcast to tensor/context peers, build.  `max_len` (the
+    sequence-length curriculum's current length) keeps the first `max_len` positions of every sample."""
     tp, cp = state.get_model_parallel_world_size(), state.get_context_parallel_world_size()
     data = next(data_iterator) if data_iterator is not None else None
     if cfg.alignment_method == "dpo":
@@ -155,4 +156,9 @@ def get_batch(cfg, data_iterator, device) -> Dict[str, torch.Tensor]:
         text = data["text"].to(device, non_blocking=True).long()
     else:
         text = broadcast_data(["text"], data, torch.int64)["text"].long()
+    if max_len is not None and max_len + 1 < text.shape[1]:
+        unit = 2 * cp * (tp if cfg.sequence_parallel else 1)
+        if max_len % unit:
+            raise ValueError(f"curriculum length {max_len} must divide by {unit} (zigzag context shards x sequence-parallel ranks)")
+        text = text[:, : max_len + 1]
     return build_batch(cfg, text)

@@ -124,6 +124,8 @@ class Trainer:
             self.noise_scale = CriticalBatchEstimator(cfg.train_micro_batch_size_per_gpu * cfg.gradient_accumulation_steps,
                                                       cfg.gradient_noise_scale_n_batches,
                                                       cpu_offload=bool(cfg.gradient_noise_scale_cpu_offload))
+        from . import curriculum as curriculum_mod
+        self.curriculum = curriculum_mod.from_config(cfg)          # sequence-length curriculum, or None
         self.profiler = None
         self.timers = None
         self.watchdog = None
@@ -296,6 +298,12 @@ class Trainer:
         self.model.train()
         self.optimizer.zero_grad()
         total = None
+        max_len = None
+        if self.curriculum is not None:
+            # iteration + 1: the length of the step that is about to run (a resumed run continues the schedule)
+            max_len = cfg.curriculum_seqlen = self.curriculum.update_difficulty(self.iteration + 1)
+            if max_len >= cfg.seq_length:
+                max_len = None
         for micro in range(self.gas):
             # the last micro-batch's forward plants the hooks through which its backward reports finished blocks
             overlap = self._zero_overlap if micro == self.gas - 1 else None
@@ -304,7 +312,7 @@ class Trainer:
                 self.model.grad_boundary_callback = lambda i: overlap.grads_final_from(opt, i)
             try:
                 with self._mark("TRAIN_STEP_FORWARD"):
-                    b = batch_mod.get_batch(cfg, data_iterator, self.device)
+                    b = batch_mod.get_batch(cfg, data_iterator, self.device, max_len)
                     loss = self.forward_step(b)
                 with self._mark("TRAIN_STEP_BACKWARD"):
                     if overlap is not None:
@@ -324,7 +332,7 @@ class Trainer:
             self.grad_norm = self.optimizer.step()
             self.lr_scheduler.step()
         self.iteration += 1
-        self.tokens_seen += cfg.train_batch_size * cfg.seq_length
+        self.tokens_seen += cfg.train_batch_size * (max_len or cfg.seq_length)
         if self.watchdog is not None:
             self.watchdog.beat(self.iteration)
         return self._reduce_loss(total / self.gas)

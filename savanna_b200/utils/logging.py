@@ -183,6 +183,8 @@ class TrainingLogger:
             self._log("runtime/mfu", m["mfu"], it)
             self._log("runtime/hfu", m["hfu"], it)
         self._log("train/tokens", tr.tokens_seen, it)
+        if getattr(tr, "curriculum", None) is not None:
+            self._log("train/curriculum_seqlen", cfg.curriculum_seqlen, it)
         line = (f" iteration {it:8d}/{cfg.train_iters:8d} | elapsed per iteration (ms): {dt * 1e3:.1f} | "
                 f"lr: {lr:.3E} | lm_loss: {lossv:.6E} | grad norm: {gn:.3f} | tokens/s/gpu: {tps_gpu:,.0f} | "
                 f"tokens: {tr.tokens_seen:,} | model {human_readable_flops(m['model_flops_per_sec'])}/gpu")

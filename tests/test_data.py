@@ -150,6 +150,20 @@ def test_dpo_preprocess_and_batch(tmp_path):
     batches = iter([{"text": rows}] * 4)
     l0 = float(tr.train_step(batches))
     assert l0 == l0
+    # through the sample index: one record of dpo_data_seq_length float32 values per sample (plus the first value of the
+    # next record, which the row parser never reaches), log-probabilities intact
+    from savanna_b200.data.loaders import build_the_dataset
+    cfg.dpo_data_seq_length = 64
+    sd = build_the_dataset(prefix + "_text_document", "train", cfg, num_samples=3, seed=1)
+    want = {(-12.5, -9.25), (-8.0, -20.0)}
+    for i in range(len(sd)):
+        r = sd[i]["text"]
+        assert r.dtype.name == "float32" and r.shape == (65,)
+        b2 = build_batch_dpo(cfg, torch.from_numpy(r.copy())[None])
+        assert tuple(b2["ref_logps"].tolist()) in want
+    cfg.dpo_data_seq_length = 48
+    with pytest.raises(ValueError):
+        build_the_dataset(prefix + "_text_document", "train", cfg, num_samples=3, seed=1)
 
 
 def test_legacy_indexed_dataset_round_trip(tmp_path):

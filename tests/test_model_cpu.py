@@ -324,3 +324,31 @@ def test_long_operator_variants_train(over):
     if over.get("bidirectional"):
         li = [m for m in tr.model.modules() if getattr(m, "bidirectional", False)]
         assert li and li[0].filter(8).shape[0] == 2 * li[0].num_groups
+
+
+def test_grouped_and_tied_in_projections():
+    """`proj_groups` narrows the attention layers' in-projection to D + 2 D / groups (second and third stream repeated
+    over the groups); `tie_projection_weights` narrows every in-projection to D (the three streams are equal)."""
+    D = _cfg().hidden_size
+    cfg = _cfg(proj_groups=2)
+    tr = Trainer(cfg, load=False)
+    widths = {n: p.shape[0] for n, p in tr.model.named_parameters() if n.endswith("dense_projection.weight")}
+    attn = [n for n in widths if cfg.operator_config[int(n.split(".")[1]) - 2] in ("flash_v2", "flash", "global", "ring")]
+    assert attn and all(widths[n] == 2 * D for n in attn)
+    assert all(w == 3 * D for n, w in widths.items() if n not in attn)
+    d = _iter(cfg)
+    l = [float(tr.train_step(d)) for _ in range(4)]
+    assert l[-1] < l[0]
+    # the repeated streams: the second half of the expanded projection equals the first
+    mixer = tr.model.get_submodule(".".join(attn[0].split(".")[:3]))
+    x = torch.randn(1, cfg.seq_length, D)
+    proj, _ = mixer.dense_projection(x)
+    own = proj.shape[-1] * 2 // 4
+    wide = torch.cat([proj[..., :own], proj[..., own:].repeat(1, 1, 2)], dim=-1)
+    assert wide.shape[-1] == 3 * D and torch.equal(wide[..., D:2 * D], wide[..., 2 * D:])
+    cfg = _cfg(tie_projection_weights=True)
+    tr = Trainer(cfg, load=False)
+    assert all(p.shape[0] == D for n, p in tr.model.named_parameters() if n.endswith("dense_projection.weight"))
+    d = _iter(cfg)
+    l = [float(tr.train_step(d)) for _ in range(4)]
+    assert l[-1] < l[0]

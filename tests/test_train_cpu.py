@@ -60,3 +60,45 @@ def test_optional_logging(monkeypatch, stage):
     if stage == 1:
         assert "train/noise_scale" in seen and any(k.startswith("grad_norm/") for k in seen)
     state.destroy_model_parallel()
+
+
+def test_sequence_length_curriculum_schedules_and_training():
+    """The three schedules' lengths, and a tiny run whose batches grow from 128 to the full 1024 tokens."""
+    import os
+    import torch
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train.curriculum import CurriculumScheduler
+    from savanna_b200.train.trainer import Trainer
+    lin = CurriculumScheduler({"min_difficulty": 8, "max_difficulty": 64, "schedule_type": "fixed_linear",
+                               "schedule_config": {"total_curriculum_step": 7, "difficulty_step": 8}})
+    assert [lin.difficulty(s) for s in (1, 2, 4, 7, 100)] == [16, 24, 40, 64, 64]
+    root = CurriculumScheduler({"min_difficulty": 8, "max_difficulty": 64, "schedule_type": "fixed_root",
+                                "schedule_config": {"total_curriculum_step": 16, "difficulty_step": 8, "root_degree": 2}})
+    assert [root.difficulty(s) for s in (1, 4, 16)] == [16, 32, 64]          # sqrt(1/16) = 1/4, sqrt(4/16) = 1/2
+    disc = CurriculumScheduler({"min_difficulty": 8, "max_difficulty": 64, "schedule_type": "fixed_discrete",
+                                "schedule_config": {"difficulty": [8, 32, 64], "max_step": [2, 5]}})
+    assert [disc.difficulty(s) for s in (1, 2, 3, 5, 6)] == [8, 8, 32, 32, 64]
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")], {
+        "global_num_gpus": 1,
+        "curriculum_learning": {"enabled": True, "curriculum_type": "seqlen", "min_difficulty": 128, "max_difficulty": 1024,
+                                "schedule_type": "fixed_discrete",
+                                "schedule_config": {"difficulty": [128, 256, 1024], "max_step": [1, 2]}}})
+    assert cfg.seq_length == 1024
+    tr = Trainer(cfg, load=False)
+    seen = []
+    real = tr.forward_step
+    tr.forward_step = lambda b, *a, **k: (seen.append(b["tokens"].shape[1]), real(b, *a, **k))[1]
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    d = it()
+    losses = [float(tr.train_step(d)) for _ in range(3)]
+    gas = cfg.gradient_accumulation_steps
+    assert seen == [128] * gas + [256] * gas + [1024] * gas
+    assert all(l == l for l in losses)
+    assert tr.tokens_seen == cfg.train_batch_size * (128 + 256 + 1024)
