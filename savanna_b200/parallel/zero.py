@@ -146,6 +146,8 @@ class ZeroOptimizer:
                 self.groups.append(fg)
         self.grad_divisor = grad_divisor
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self.loss_scaler = None                    # train/loss_scaler.py scaler for fp16 runs (set by the trainer)
+        self.overflow = False                      # the last step found inf / nan gradients and was skipped
         self.fused = None                          # set by parallel.fused_zero.attach() on CUDA with symmetric memory
 
     # ------------------------------------------------------------------ gradients
@@ -200,6 +202,9 @@ class ZeroOptimizer:
         inv = self.grad_scale() if (self.reduce_world > 1 and self.partition) else 1.0
         if self.grad_divisor:
             inv = inv / self.grad_divisor
+        scaler = self.loss_scaler
+        if scaler is not None:
+            inv = inv / scaler.scale                # the backward ran on loss * scale (fp16 training)
         sq = None
         for g, s in zip(self.groups, shards):
             part = ops.sq_norm(s, g.norm_weight)
@@ -214,6 +219,12 @@ class ZeroOptimizer:
             dist.all_reduce(sq, group=state.get_pipe_parallel_group())
         norm = sq.sqrt()
         self.last_grad_norm = norm
+        if scaler is not None:
+            # every rank holds the same reduced norm, so every rank takes the same branch
+            self.overflow = scaler.check(norm)
+            if self.overflow:
+                self.step_count -= 1                # inf / nan in the gradients: no update, the scaler has backed off
+                return norm
         if self.clip_grad > 0.0:
             coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0) * inv
         else:
@@ -250,9 +261,9 @@ class ZeroOptimizer:
         return {
             "zero_stage": 1,
             "partition_count": [self.world] * len(self.groups),
-            "loss_scaler": None,
-            "dynamic_loss_scale": False,
-            "overflow": False,
+            "loss_scaler": self.loss_scaler.state_dict() if self.loss_scaler is not None else None,
+            "dynamic_loss_scale": bool(self.loss_scaler is not None and self.loss_scaler.dynamic),
+            "overflow": bool(self.overflow),
             "clip_grad": self.clip_grad,
             "single_partition_of_fp32_groups": [g.master for g in self.groups],
             "group_paddings": [g.padded - g.numel if self.rank == self.world - 1 else 0 for g in self.groups],
@@ -280,6 +291,8 @@ class ZeroOptimizer:
             self.step_count = int(st[i]["step"])
             pg = sd["base_optimizer_state"]["param_groups"][i]
             g.hyper["lr"] = pg["lr"]
+        if self.loss_scaler is not None and isinstance(sd.get("loss_scaler"), dict):
+            self.loss_scaler.load_state_dict(sd["loss_scaler"])
 
     def refresh_master_from_params(self) -> None:
         for g in self.groups:

@@ -201,6 +201,8 @@ class PartitionedZeroOptimizer:
         self.prefetch = prefetch
         self.step_count = 0
         self.defaults = {"lr": lr, "weight_decay": weight_decay}
+        self.loss_scaler = None                    # train/loss_scaler.py scaler for fp16 runs (set by the trainer)
+        self.overflow = False
         self.fused = None
         self.last_grad_norm: Optional[torch.Tensor] = None
         tp = state.get_model_parallel_world_size()
@@ -391,6 +393,9 @@ class PartitionedZeroOptimizer:
         inv = float(self.sum_ranks) / float(self.reduce_world)
         if self.grad_divisor:
             inv = inv / self.grad_divisor
+        scaler = self.loss_scaler
+        if scaler is not None:
+            inv = inv / scaler.scale                # the backward ran on loss * scale (fp16 training)
         sq = None
         for f in self.groups:
             part = ops.sq_norm(f.grad_acc, f.norm_weight)
@@ -402,6 +407,11 @@ class PartitionedZeroOptimizer:
             dist.all_reduce(sq, group=state.get_model_parallel_group())
         norm = sq.sqrt()
         self.last_grad_norm = norm
+        if scaler is not None:
+            self.overflow = scaler.check(norm)      # the same reduced norm, hence the same branch, on every rank
+            if self.overflow:
+                self.step_count -= 1
+                return norm
         if self.clip_grad > 0.0:
             coef = torch.clamp(self.clip_grad / (norm + 1e-6), max=1.0) * inv
         else:
@@ -458,9 +468,9 @@ class PartitionedZeroOptimizer:
         return {
             "zero_stage": self.stage,
             "partition_count": [self.world] * len(self.groups),
-            "loss_scaler": None,
-            "dynamic_loss_scale": False,
-            "overflow": False,
+            "loss_scaler": self.loss_scaler.state_dict() if self.loss_scaler is not None else None,
+            "dynamic_loss_scale": bool(self.loss_scaler is not None and self.loss_scaler.dynamic),
+            "overflow": bool(self.overflow),
             "clip_grad": self.clip_grad,
             "single_partition_of_fp32_groups": [f.master for f in self.groups],
             "group_paddings": [f.padded - f.numel if self.rank == self.world - 1 else 0 for f in self.groups],
@@ -494,6 +504,8 @@ class PartitionedZeroOptimizer:
                 f.hyper["lr"] = sd["base_optimizer_state"]["param_groups"][i]["lr"]
                 if load_master and f.resident:
                     _all_gather(f.full, f.param_shard, self.group, self.world)
+        if self.loss_scaler is not None and isinstance(sd.get("loss_scaler"), dict):
+            self.loss_scaler.load_state_dict(sd["loss_scaler"])
 
     def memory_report(self) -> Dict[str, int]:
         """Bytes this rank holds persistently (shards and optimizer state) and transiently at most (one unit whole)."""

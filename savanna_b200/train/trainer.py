@@ -124,6 +124,17 @@ class Trainer:
             self.noise_scale = CriticalBatchEstimator(cfg.train_micro_batch_size_per_gpu * cfg.gradient_accumulation_steps,
                                                       cfg.gradient_noise_scale_n_batches,
                                                       cpu_offload=bool(cfg.gradient_noise_scale_cpu_offload))
+        # fp16 runs scale the loss; the ZeRO optimizers unscale, look for inf / nan and skip the step when they find one
+        from . import loss_scaler as loss_scaler_mod
+        from ..utils.watchdog import OverflowMonitor
+        self.loss_scaler = loss_scaler_mod.from_config(cfg)
+        self.overflow_monitor = OverflowMonitor(50)
+        if self.loss_scaler is not None:
+            if not hasattr(self.optimizer, "loss_scaler"):
+                raise NotImplementedError("fp16 loss scaling needs the Adam-family ZeRO optimizer (stages 0-3)")
+            if getattr(self.model, "is_pipeline_stage", False):
+                raise NotImplementedError("fp16 loss scaling is not wired into the pipeline schedule; use bf16")
+            self.optimizer.loss_scaler = self.loss_scaler
         from . import curriculum as curriculum_mod
         self.curriculum = curriculum_mod.from_config(cfg)          # sequence-length curriculum, or None
         self.profiler = None
@@ -317,7 +328,8 @@ class Trainer:
                 with self._mark("TRAIN_STEP_BACKWARD"):
                     if overlap is not None:
                         overlap.begin_overlap(self.optimizer)
-                    (loss / self.gas).backward()
+                    scale = self.loss_scaler.scale if self.loss_scaler is not None else 1.0
+                    (loss * (scale / self.gas)).backward()
                     if self.partitioned:
                         self.optimizer.finish_backward()
             finally:
@@ -330,7 +342,14 @@ class Trainer:
             self.noise_scale.update([p for p in self.model.parameters() if p.requires_grad])
         with self._mark("TRAIN_STEP_OPTIMIZER_STEP"):
             self.grad_norm = self.optimizer.step()
-            self.lr_scheduler.step()
+            if self.loss_scaler is not None and getattr(self.optimizer, "overflow", False):
+                # fp16: inf / nan gradients, no update was made; the learning-rate schedule does not advance either
+                self.skipped_iters += 1
+                self.overflow_monitor.check(True)
+            else:
+                if self.loss_scaler is not None:
+                    self.overflow_monitor.check(False)
+                self.lr_scheduler.step()
         self.iteration += 1
         self.tokens_seen += cfg.train_batch_size * (max_len or cfg.seq_length)
         if self.watchdog is not None:

@@ -183,6 +183,8 @@ class TrainingLogger:
             self._log("runtime/mfu", m["mfu"], it)
             self._log("runtime/hfu", m["hfu"], it)
         self._log("train/tokens", tr.tokens_seen, it)
+        if getattr(tr, "loss_scaler", None) is not None:
+            self._log("train/loss_scale", tr.loss_scaler.scale, it)
         if getattr(tr, "curriculum", None) is not None:
             self._log("train/curriculum_seqlen", cfg.curriculum_seqlen, it)
         line = (f" iteration {it:8d}/{cfg.train_iters:8d} | elapsed per iteration (ms): {dt * 1e3:.1f} | "
@@ -191,6 +193,8 @@ class TrainingLogger:
         if m["mfu"] is not None:
             line += f" | MFU {100 * m['mfu']:.1f}% HFU {100 * m['hfu']:.1f}%"
         line += f" | skipped: {tr.skipped_iters} | nan: {tr.nan_iters}"
+        if getattr(tr, "loss_scaler", None) is not None:
+            line += f" | loss scale: {tr.loss_scaler.scale:.1f}"
         if cfg.log_memory_stats and torch.cuda.is_available():
             st = mem.memory_stats()
             line += " | " + mem.format_memory_stats(st)

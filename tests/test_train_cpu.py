@@ -102,3 +102,66 @@ def test_sequence_length_curriculum_schedules_and_training():
     assert seen == [128] * gas + [256] * gas + [1024] * gas
     assert all(l == l for l in losses)
     assert tr.tokens_seen == cfg.train_batch_size * (128 + 256 + 1024)
+
+
+def test_dynamic_loss_scaler_policy():
+    from savanna_b200.train.loss_scaler import DynamicLossScaler, LossScaler
+    s = DynamicLossScaler(initial_scale_power=4, window=3, hysteresis=2, min_scale=2.0)
+    assert s.scale == 16.0
+    s.update(True)                       # first overflow spends the hysteresis budget
+    assert s.scale == 16.0
+    s.update(True)                       # second one halves
+    assert s.scale == 8.0
+    s.update(True); s.update(True); s.update(True)
+    assert s.scale == 2.0                # floor at min_scale
+    for _ in range(3):
+        s.update(False)
+    assert s.scale == 4.0                # doubled `window` clean steps after the last overflow
+    st = s.state_dict()
+    t = DynamicLossScaler(initial_scale_power=10, window=3)
+    t.load_state_dict(st)
+    assert t.scale == 4.0 and t.iter == s.iter
+    assert s.check(float("inf")) and s.check(float("nan")) and not s.check(1.5)
+    fixed = LossScaler(128.0)
+    assert fixed.check(float("inf")) and fixed.scale == 128.0
+
+
+@pytest.mark.parametrize("stage", [1, 2])
+def test_fp16_training_scales_the_loss_and_skips_overflowed_steps(stage):
+    """fp16 run of the tiny model: same updates as without scaling while the gradients are finite (the scale cancels),
+    and a step whose gradients overflow changes nothing but the scale."""
+    import os
+    import torch
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train.trainer import Trainer
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")], {
+        "global_num_gpus": 1, "precision": "fp16",
+        "fp16": {"enabled": True, "loss_scale": 0, "initial_scale_power": 8, "loss_scale_window": 2, "hysteresis": 1},
+        "zero_optimization": {"stage": stage}})
+    tr = Trainer(cfg, load=False)
+    assert tr.loss_scaler is not None and tr.loss_scaler.scale == 256.0 and tr.optimizer.loss_scaler is tr.loss_scaler
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)}
+            i += 1
+    d = it()
+    l0 = float(tr.train_step(d))
+    assert l0 == l0 and tr.skipped_iters == 0 and float(tr.grad_norm) < 100.0       # the norm is reported unscaled
+    before = [p.detach().clone() for p in tr.model.parameters()] if stage == 1 else None
+    lr_before = tr.optimizer.param_groups[0]["lr"]
+    tr.loss_scaler.scale = float("inf")                       # every gradient becomes inf / nan
+    tr.train_step(d)
+    assert tr.skipped_iters == 1 and tr.optimizer.overflow
+    assert tr.loss_scaler.scale == float("inf") / 2 or tr.loss_scaler.scale == float("inf")
+    if before is not None:
+        assert all(torch.equal(a, b.detach()) for a, b in zip(before, tr.model.parameters()))
+    assert tr.optimizer.param_groups[0]["lr"] == lr_before    # the schedule did not advance
+    tr.loss_scaler.scale = 256.0
+    l2 = float(tr.train_step(d))
+    assert l2 == l2 and tr.skipped_iters == 1 and not tr.optimizer.overflow
+    sd = tr.optimizer.state_dict()
+    assert sd["dynamic_loss_scale"] is True and sd["loss_scaler"]["cur_scale"] == tr.loss_scaler.scale
