@@ -231,19 +231,51 @@ def param_groups(model: nn.Module, cfg):
     return groups
 
 
+def _mup_shapes_path(cfg):
+    """`<base_shapes_file>.<rank>` (how the file is written) or the bare name, whichever exists; None without one."""
+    import os
+    base = cfg.base_shapes_file
+    if not base:
+        return None
+    rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+    for cand in (f"{base}.{rank}", f"{base}.0", base):
+        if os.path.exists(cand):
+            return cand
+    return None
+
+
 def mup_param_groups(groups, model: nn.Module, cfg):
     """Per-group learning rates of the maximal-update parametrisation (the reference's MuAdam / MuSGD,
     savanna/training.py:1065-1185 with the `mup` package): parameters whose two dimensions both grow with the model
     width ("matrix-like": the projection and MLP weights) are separated from the rest ("vector-like": embeddings,
     norms, biases, filters).  Adam-type optimizers divide the matrix-like learning rate by the width multiplier
     `mup_width_scale` (and multiply a coupled weight decay by it); SGD multiplies the vector-like learning rate by it.
-    A group that was split keeps its name with a `_matrix` suffix for the matrix-like half."""
+    With a `base_shapes_file` on disk the classification and the multiplier come from that file instead of from
+    parameter names and `mup_width_scale`.  A group that was split keeps its name with a `_matrix` suffix for the matrix-like half."""
     matrix_ids = set()
-    for name, p in model.named_parameters():
-        if p.dim() == 2 and name.endswith(".weight") and any(k in name for k in (
-                "dense_projection.", "mixer.dense.", ".mlp.w1.", ".mlp.w2.", ".mlp.w3.", ".mlp.dense_", ".mlp.w12")):
-            matrix_ids.add(id(p))
     mult = float(cfg.mup_width_scale)
+    shapes_file = _mup_shapes_path(cfg)
+    if shapes_file is not None:
+        # a base-shapes file says, per parameter, which dimensions grow with the width and by how much this model is
+        # wider than the base: matrix-like = two growing dimensions (train/mup_shapes.py)
+        from ..train import mup_shapes
+        widths = mup_shapes.width_multipliers(model, mup_shapes.load_base_shapes(shapes_file))
+        mults = set()
+        for name, p in model.named_parameters():
+            n_inf, m = widths[name]
+            if n_inf >= 2:
+                matrix_ids.add(id(p))
+                mults.add(round(m, 6))
+        if len(mults) > 1:
+            raise NotImplementedError(f"base shapes give different width multipliers for the matrix-like parameters ({sorted(mults)}); "
+                                      "one multiplier per model is supported")
+        if mults:
+            mult = mults.pop()
+    else:
+        for name, p in model.named_parameters():
+            if p.dim() == 2 and name.endswith(".weight") and any(k in name for k in (
+                    "dense_projection.", "mixer.dense.", ".mlp.w1.", ".mlp.w2.", ".mlp.w3.", ".mlp.dense_", ".mlp.w12")):
+                matrix_ids.add(id(p))
     sgd = str(cfg.optimizer_type).lower() in ("sgd", "musgd")
     decoupled = bool(((cfg.optimizer or {}).get("params", {}) or {}).get("adam_w_mode", True))
     out = []

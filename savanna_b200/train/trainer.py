@@ -506,6 +506,14 @@ class Trainer:
 def pretrain(cfg) -> Trainer:
     """Entry used by train.py: set up, build data iterators, train, final evaluation."""
     from ..data.loaders import build_train_valid_test_data_iterators
+    if cfg.use_mup and cfg.save_base_shapes:
+        from . import mup_shapes
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        path = f"{cfg.base_shapes_file or 'base-shapes'}.{rank}"
+        if cfg.padded_vocab_size is None:
+            cfg.build_tokenizer()
+        mup_shapes.save_base_shapes(cfg, path)
+        raise SystemExit(f"base shapes written to {path}; exiting (rerun without save_base_shapes to train)")
     if cfg.use_mup and cfg.coord_check:
         raise SystemExit("coord_check: run `python -m savanna_b200.train.mup_coord_check <model configs>`; it builds the "
                          "model at several widths itself (the reference also exits after its coordinate check)")

@@ -352,3 +352,25 @@ def test_grouped_and_tied_in_projections():
     d = _iter(cfg)
     l = [float(tr.train_step(d)) for _ in range(4)]
     assert l[-1] < l[0]
+
+
+def test_mup_base_shapes_file_drives_the_groups(tmp_path):
+    """Base shapes from two meta-device models; a model twice as wide as the base then gets multiplier 2 on exactly the
+    parameters with two growing dimensions."""
+    from savanna_b200.models.backbone import build_model, param_groups
+    from savanna_b200.train import mup_shapes
+    cfg = _cfg(use_mup=True, mup_width_scale=2, base_shapes_file=str(tmp_path / "shapes"))
+    cfg.build_tokenizer()
+    shapes = mup_shapes.save_base_shapes(cfg, str(tmp_path / "shapes") + ".0")
+    D = cfg.hidden_size
+    assert shapes["sequential.2.mixer.dense_projection.weight"] == {"shape": [3 * D, D], "infinite": [True, True]}
+    assert shapes["sequential.0.word_embeddings.weight"]["infinite"] == [False, True]
+    wide = _cfg(use_mup=True, mup_width_scale=7, hidden_size=2 * D, base_shapes_file=str(tmp_path / "shapes"),
+                optimizer={"type": "Adam", "params": {"lr": 1e-3}})
+    wide.build_tokenizer()
+    model = build_model(wide, device=torch.device("cpu"))
+    w = mup_shapes.width_multipliers(model, mup_shapes.load_base_shapes(str(tmp_path / "shapes") + ".0"))
+    assert w["sequential.2.mixer.dense_projection.weight"] == (2, 2.0) and w["sequential.0.word_embeddings.weight"][0] == 1
+    groups = param_groups(model, wide)
+    mat = [g for g in groups if g["name"].endswith("_matrix")]
+    assert mat and all(abs(g["lr"] - 1e-3 / 2.0) < 1e-12 for g in mat)          # 2 from the file, not mup_width_scale = 7
