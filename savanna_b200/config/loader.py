@@ -109,6 +109,22 @@ def _type_ok(value, typ) -> bool:
     return True
 
 
+_GIT_DESCRIBE = []
+
+
+def _git_describe() -> Optional[str]:
+    """`git describe --always` of the checkout that holds this package (None outside a repository); asked once."""
+    if not _GIT_DESCRIBE:
+        import subprocess
+        try:
+            out = subprocess.run(["git", "describe", "--always"], cwd=os.path.dirname(os.path.abspath(__file__)),
+                                 capture_output=True, text=True, timeout=10)
+            _GIT_DESCRIBE.append(out.stdout.strip() or None if out.returncode == 0 else None)
+        except Exception:
+            _GIT_DESCRIBE.append(None)
+    return _GIT_DESCRIBE[0]
+
+
 def _detect_num_gpus() -> int:
     if "WORLD_SIZE" in os.environ:
         return int(os.environ["WORLD_SIZE"])
@@ -272,6 +288,8 @@ class GlobalConfig:
         self.optimizer_type = str(opt.get("type", OPT_DEFAULT)).lower()
         self.lr = opt.get("params", {}).get("lr", OPT_PARAMS_DEFAULTS["lr"])
         self.dynamic_loss_scale = self.loss_scale is None
+        if self.git_hash is None:
+            self.git_hash = _git_describe()         # recorded in the saved configuration next to every checkpoint
 
         self.is_pipe_parallel = (self.pipe_parallel_size or 0) > 1
         self.is_context_parallel = cp > 1

@@ -153,7 +153,11 @@ def generate_samples_from_prompt(model, cfg, text, **kw) -> List[Dict]:
 
 
 def generate_samples_input_from_file(model, cfg, input_file: str, output_file: Optional[str] = None, **kw):
-    prompts = [ln.rstrip("\n") for ln in open(input_file) if ln.strip()]
+    # prompts are separated by `prompt_end` (a newline unless configured; other separators allow multi-line prompts)
+    sep = kw.pop("prompt_end", None) or cfg.prompt_end or "\n"
+    with open(input_file, encoding="utf-8") as fh:
+        prompts = [p.strip() for p in fh.read().split(sep)]
+    prompts = [p for p in prompts if p]
     results = generate_samples_from_prompt(model, cfg, prompts, **kw)
     if output_file:
         with open(output_file, "w") as fh:

@@ -39,7 +39,8 @@ class ParallelBlock(nn.Module):
                                            device=device)
         if cfg.identity_mlp:
             self.mlp = nn.Identity()
-        elif cfg.mlp_type == "regular":
+        elif cfg.mlp_type == "regular" or (cfg.safe and self.operator_type == "hyena"):
+            # `safe`: Hyena-LI layers take the plain two-layer MLP whatever `mlp_type` says (block.py:1074)
             self.mlp = ParallelMLP(cfg, init_method, output_layer_init_method, dtype=dtype, device=device)
         elif cfg.mlp_type == "short_hyena":
             self.mlp = ParallelSequenceMixer(cfg, init_method, output_layer_init_method, layer_number,

@@ -25,10 +25,64 @@ def stage_layer_range(num_layers: int, pp: int, stage: int) -> range:
     return range(start, start + base + (1 if stage < rem else 0))
 
 
+def balanced_layer_ranges(weights: List[float], pp: int, first_extra: float = 0.0, last_extra: float = 0.0) -> List[range]:
+    """Cut the layers into `pp` contiguous, non-empty runs so that the heaviest run is as light as possible
+    (`first_extra` / `last_extra`: what the first and the last stage carry besides their layers: embedding, final norm
+    and output head).  Dynamic programme over prefix sums; a few hundred layers at most."""
+    n = len(weights)
+    if pp > n:
+        raise ValueError(f"{pp} pipeline stages for {n} layers")
+    pre = [0.0]
+    for w in weights:
+        pre.append(pre[-1] + float(w))
+
+    def cost(a, b, k):                       # layers a..b-1 as stage k
+        return pre[b] - pre[a] + (first_extra if k == 0 else 0.0) + (last_extra if k == pp - 1 else 0.0)
+    inf = float("inf")
+    best = [[inf] * (n + 1) for _ in range(pp + 1)]
+    cut = [[0] * (n + 1) for _ in range(pp + 1)]
+    best[0][0] = 0.0
+    for k in range(1, pp + 1):
+        for b in range(k, n - (pp - k) + 1):
+            for a in range(k - 1, b):
+                if best[k - 1][a] == inf:
+                    continue
+                c = max(best[k - 1][a], cost(a, b, k - 1))
+                if c < best[k][b]:
+                    best[k][b], cut[k][b] = c, a
+    out, b = [], n
+    for k in range(pp, 0, -1):
+        a = cut[k][b]
+        out.append(range(a, b))
+        b = a
+    return out[::-1]
+
+
+def partition_layers(cfg, pp: int) -> List[range]:
+    """Layer range of every stage under `pipe_partition_method` (the methods of DeepSpeed's PipelineModule, which the
+    reference forwards this key to, savanna/model/backbone.py:281): `type:<class regex>` and `uniform` spread the blocks
+    evenly (the reference's default `type:ParallelBlockPipe` balances exactly the blocks); `parameters` balances the
+    parameter count, embedding and output head included, measured on a meta-device copy of the model."""
+    method = str(cfg.pipe_partition_method or "type:ParallelBlockPipe").lower()
+    if method.startswith("type:") or method == "uniform":
+        return [stage_layer_range(cfg.num_layers, pp, s) for s in range(pp)]
+    if method == "parameters":
+        from ..models.backbone import Backbone
+        meta = Backbone(cfg, device=torch.device("meta"))
+        per_block = [sum(p.numel() for p in b.parameters()) for b in meta.blocks()]
+        total = sum(p.numel() for p in meta.parameters())
+        emb = sum(p.numel() for p in meta.embedding.parameters())
+        tail = total - emb - sum(per_block)                       # final norm and, untied, the output head
+        if not cfg.no_weight_tying:
+            tail += emb                                           # the last stage holds a copy of the tied embedding
+        return balanced_layer_ranges(per_block, pp, first_extra=emb, last_extra=tail)
+    raise ValueError(f"pipe_partition_method {cfg.pipe_partition_method!r} unknown (type:<regex> | uniform | parameters)")
+
+
 def build_pipeline_stage(cfg, device):
     from ..models.backbone import Backbone
     pp, stage = state.get_pipe_parallel_world_size(), state.get_pipe_parallel_rank()
-    model = Backbone(cfg, device=device, layer_range=stage_layer_range(cfg.num_layers, pp, stage))
+    model = Backbone(cfg, device=device, layer_range=partition_layers(cfg, pp)[stage])
     model.is_pipeline_stage = True
     model.stage, model.num_stages = stage, pp
     return model

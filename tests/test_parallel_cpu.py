@@ -554,3 +554,27 @@ def test_zero_offload_keeps_state_on_the_host_and_matches():
     for a, g in zip(m0, opt.groups):
         assert torch.equal(a, g.master)
     state.destroy_model_parallel()
+
+
+def test_pipeline_partition_methods():
+    """Even block counts for `type:` / `uniform`; `parameters` balances the parameter count with the embedding on the
+    first and the head on the last stage."""
+    from savanna_b200.parallel.pipeline import balanced_layer_ranges, partition_layers
+    r = balanced_layer_ranges([1, 1, 1, 1, 1, 1], 3)
+    assert [list(x) for x in r] == [[0, 1], [2, 3], [4, 5]]
+    r = balanced_layer_ranges([1, 1, 1, 1, 1, 1], 2, first_extra=2.0)          # a heavy embedding: fewer blocks up front
+    assert [len(x) for x in r] == [2, 4]
+    r = balanced_layer_ranges([5, 1, 1, 1, 1, 1], 2)
+    assert [len(x) for x in r] == [1, 5]
+    with pytest.raises(ValueError):
+        balanced_layer_ranges([1, 1], 3)
+    cfg = _tiny_cfg(1)
+    cfg.build_tokenizer()
+    even = partition_layers(cfg, 2)
+    assert [len(x) for x in even] == [cfg.num_layers // 2, cfg.num_layers - cfg.num_layers // 2] or sum(len(x) for x in even) == cfg.num_layers
+    cfg.pipe_partition_method = "parameters"
+    by_params = partition_layers(cfg, 2)
+    assert by_params[0].start == 0 and by_params[-1].stop == cfg.num_layers and by_params[0].stop == by_params[1].start
+    cfg.pipe_partition_method = "nonsense"
+    with pytest.raises(ValueError):
+        partition_layers(cfg, 2)

@@ -99,6 +99,19 @@ def test_generation_greedy_is_deterministic():
     assert [r["text"] for r in a] == [r["text"] for r in b] and all(r["length"] >= 5 for r in a)
 
 
+def test_generation_from_file_splits_prompts_at_prompt_end(tmp_path):
+    from savanna_b200.inference.generation import generate_samples_input_from_file
+    cfg = GlobalConfig.from_ymls([TINY], {"global_num_gpus": 1, "prompt_end": "<|end|>", "maximum_tokens": 3})
+    tr = Trainer(cfg, load=False)
+    src = tmp_path / "prompts.txt"
+    src.write_text("ACGT\nACGT<|end|>GGCC<|end|>\n")
+    out = tmp_path / "out.jsonl"
+    res = generate_samples_input_from_file(tr.model, cfg, str(src), str(out))
+    assert [r["context"] for r in res] == ["ACGT\nACGT", "GGCC"]
+    assert len(out.read_text().strip().splitlines()) == 2
+    assert isinstance(cfg.git_hash, (str, type(None)))
+
+
 def test_convert_checkpoint_to_torch(tiny_ckpt, tmp_path):
     from savanna_b200.tools.convert_checkpoint_to_torch import convert
     tr, d = tiny_ckpt
