@@ -30,13 +30,24 @@ def _pad_to(n: int, m: int) -> int:
     return m * ((n + m - 1) // m)
 
 
+def _file_tensor(path: str, numel: int) -> torch.Tensor:
+    """fp32 tensor of `numel` elements whose storage is the file `path` (created or resized, shared mapping: writes go
+    to the file)."""
+    import os
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "ab") as fh:
+        fh.truncate(numel * 4)
+    return torch.from_file(path, shared=True, size=numel, dtype=torch.float32)
+
+
 class FlatGroup:
     """One parameter group flattened into a parameter buffer and a gradient buffer."""
 
     def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, allocator=None,
-                 offload: bool = False):
+                 offload: bool = False, nvme_prefix: Optional[str] = None):
         self.params = params
         self.offload = bool(offload)
+        self.nvme_prefix = nvme_prefix
         self.hyper = hyper
         dtype, device = params[0].dtype, params[0].device
         if any(p.dtype != dtype for p in params):
@@ -74,8 +85,20 @@ class FlatGroup:
             self.master_is_view = False
             self.host_grad = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
             self.host_param = torch.zeros(self.shard, dtype=dtype, pin_memory=pin)
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        if self.offload and nvme_prefix:
+            # `offload_optimizer.device: nvme`: the three fp32 state arrays are files under `nvme_path`, mapped into
+            # the address space; the CPU update walks them in place and the kernel's page cache moves the pages
+            # between the drive and memory, so resident host memory is bounded by what the update touches at a time
+            init = self.master
+            self.master = _file_tensor(nvme_prefix + "_master.bin", self.shard)
+            self.master.copy_(init)
+            self.exp_avg = _file_tensor(nvme_prefix + "_exp_avg.bin", self.shard)
+            self.exp_avg_sq = _file_tensor(nvme_prefix + "_exp_avg_sq.bin", self.shard)
+            self.exp_avg.zero_()
+            self.exp_avg_sq.zero_()
+        else:
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
         self.norm_weight: Optional[torch.Tensor] = None
 
     def shard_slice(self, t: torch.Tensor) -> torch.Tensor:
@@ -101,8 +124,9 @@ class ZeroOptimizer:
                  weight_decay: float = 0.0, adamw: bool = True, clip_grad: float = 0.0,
                  group=None, group_ranks: Optional[List[int]] = None, comm_path: str = "nccl",
                  grad_divisor: Optional[float] = None, partition: bool = True, allocator=None,
-                 sum_ranks: Optional[int] = None, offload_optimizer: bool = False):
+                 sum_ranks: Optional[int] = None, offload_optimizer: bool = False, nvme_path: Optional[str] = None):
         self.group = group
+        self.nvme_path = nvme_path                 # with offload_optimizer: directory of the file-backed state arrays
         # ZeRO-Offload (`zero_optimization.offload_optimizer.device: cpu`): master weights and Adam moments live in
         # host memory and the update runs on the CPU; HBM then holds parameters, gradients and activations only
         self.offload_optimizer = bool(offload_optimizer)
@@ -140,7 +164,12 @@ class ZeroOptimizer:
             for q in params:
                 by_dtype.setdefault(q.dtype, []).append(q)
             for dt, plist in by_dtype.items():
-                fg = FlatGroup(plist, self.world, self.rank, hyper, allocator, offload=self.offload_optimizer)
+                prefix = None
+                if self.offload_optimizer and nvme_path:
+                    import os
+                    prefix = os.path.join(nvme_path, f"zero_state_rank{me}_buf{len(self.groups)}")
+                fg = FlatGroup(plist, self.world, self.rank, hyper, allocator, offload=self.offload_optimizer,
+                               nvme_prefix=prefix)
                 fg.hyper = hyper                    # shared object: both flats follow the schedule
                 fg.build_norm_weight(tp)
                 self.groups.append(fg)

@@ -166,7 +166,13 @@ class Trainer:
         if otype in ("adam", "cpu_adam", "cpu_torch_adam", "onebitadam"):
             zranks = state.get_sequence_data_parallel_ranks()
             off = (cfg.zero_optimization or {}).get("offload_optimizer") or {}
-            offload = isinstance(off, dict) and str(off.get("device", "none")).lower() == "cpu"
+            off_dev = str(off.get("device", "none")).lower() if isinstance(off, dict) else "none"
+            offload = off_dev in ("cpu", "nvme")
+            nvme_path = None
+            if off_dev == "nvme":
+                nvme_path = off.get("nvme_path")
+                if not nvme_path:
+                    raise ValueError("offload_optimizer.device nvme needs offload_optimizer.nvme_path (a directory on the drive)")
             if offload and cfg.zero_stage >= 2:
                 raise NotImplementedError("offload_optimizer is implemented for ZeRO stages 0 and 1")
             use_symm = (self.device.type == "cuda" and cfg.comm_path == "symm" and len(zranks) > 1
@@ -205,9 +211,11 @@ class Trainer:
                 groups, lr=cfg.lr, betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8),
                 weight_decay=cfg.weight_decay, adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
                 group=state.get_sequence_data_parallel_group(), group_ranks=zranks,
-                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator, offload_optimizer=offload)
+                comm_path=cfg.comm_path, partition=cfg.zero_stage >= 1, allocator=allocator, offload_optimizer=offload,
+                nvme_path=nvme_path)
             if offload:
-                print_rank_0(" > ZeRO-Offload: master weights and Adam moments in host memory, update on the CPU")
+                where = f"files under {nvme_path}" if nvme_path else "host memory"
+                print_rank_0(f" > ZeRO-Offload: master weights and Adam moments in {where}, update on the CPU")
             if use_symm:
                 fused_zero.attach(optimizer, allocator, use_nvls=bool(cfg.use_nvls))
         else:
@@ -328,8 +336,10 @@ class Trainer:
                 with self._mark("TRAIN_STEP_BACKWARD"):
                     if overlap is not None:
                         overlap.begin_overlap(self.optimizer)
-                    scale = self.loss_scaler.scale if self.loss_scaler is not None else 1.0
-                    (loss * (scale / self.gas)).backward()
+                    if self.loss_scaler is not None:
+                        (loss * (self.loss_scaler.scale / self.gas)).backward()
+                    else:
+                        (loss / self.gas).backward()
                     if self.partitioned:
                         self.optimizer.finish_backward()
             finally:

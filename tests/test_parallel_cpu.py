@@ -556,6 +556,31 @@ def test_zero_offload_keeps_state_on_the_host_and_matches():
     state.destroy_model_parallel()
 
 
+def test_zero_offload_to_files_matches_and_persists_on_disk(tmp_path):
+    """`offload_optimizer.device: nvme`: same loss trace as without offload; master weights and moments are mapped
+    files of shard * 4 bytes under `nvme_path` whose contents follow the update."""
+    import numpy as np
+    from savanna_b200.parallel import state
+    cfg = _tiny_cfg(1)
+    _, ref_losses = _run_steps(cfg)
+    state.destroy_model_parallel()
+    cfg2 = _tiny_cfg(1, zero_optimization={"stage": 1, "offload_optimizer": {"device": "nvme", "nvme_path": str(tmp_path / "nv")}})
+    tr, losses = _run_steps(cfg2)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(b)), (losses, ref_losses)
+    files = sorted(os.listdir(tmp_path / "nv"))
+    assert len(files) == 3 * len(tr.optimizer.groups) and all(f.startswith("zero_state_rank0_buf") for f in files)
+    g = tr.optimizer.groups[0]
+    on_disk = np.fromfile(tmp_path / "nv" / "zero_state_rank0_buf0_master.bin", dtype=np.float32)
+    assert on_disk.shape[0] == g.shard and np.array_equal(on_disk, g.master.numpy())
+    moments = np.fromfile(tmp_path / "nv" / "zero_state_rank0_buf0_exp_avg_sq.bin", dtype=np.float32)
+    assert moments.max() > 0.0
+    state.destroy_model_parallel()
+    with pytest.raises(ValueError):
+        _run_steps(_tiny_cfg(1, zero_optimization={"stage": 1, "offload_optimizer": {"device": "nvme"}}))
+    state.destroy_model_parallel()
+
+
 def test_pipeline_partition_methods():
     """Even block counts for `type:` / `uniform`; `parameters` balances the parameter count with the embedding on the
     first and the head on the last stage."""
