@@ -53,7 +53,7 @@ class UnitFlat:
     """The parameters of one unit that share an optimizer group and a dtype, flattened and partitioned."""
 
     def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, name: str,
-                 free_params: bool, free_grads: bool, tp: int):
+                 free_params: bool, free_grads: bool, tp: int, offload_param: bool = False):
         self.params, self.hyper, self.name = params, hyper, name
         self.world, self.rank = world, rank
         self.free_params, self.free_grads = free_params, free_grads
@@ -80,6 +80,12 @@ class UnitFlat:
         self.param_shard = self.full[lo:hi].clone()
         self.master_is_view = dtype == torch.float32          # fp32 parameters are their own master copy
         self.master = self.param_shard if self.master_is_view else self.param_shard.float()
+        # `offload_param`: between uses the low-precision shard of a unit whose whole parameters are released lives in
+        # (pinned) host memory; gathers stage it to the device, the optimizer step writes it back
+        self.param_offloaded = bool(offload_param) and free_params and not self.master_is_view
+        if self.param_offloaded:
+            host = self.param_shard.cpu()
+            self.param_shard = host.pin_memory() if device.type == "cuda" else host
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_acc = torch.zeros(self.shard, dtype=torch.float32, device=device)
@@ -103,6 +109,12 @@ class UnitFlat:
     def shard_slice(self, t: torch.Tensor) -> torch.Tensor:
         return t[self.rank * self.shard:(self.rank + 1) * self.shard]
 
+    def shard_on_device(self) -> torch.Tensor:
+        """This rank's parameter shard as a device tensor (a staged copy when the shard is kept on the host)."""
+        if self.param_offloaded:
+            return self.param_shard.to(self.full.device, non_blocking=True)
+        return self.param_shard
+
     # -- parameters ----------------------------------------------------------------
     def start_gather(self, group, async_op: bool, secondary: bool = False) -> None:
         """`secondary`: gather from the hpZ copy over the sub-group when it is up to date (the backward pass)."""
@@ -113,7 +125,7 @@ class UnitFlat:
             self.hpz_gathers += 1
             self.gather_work = _all_gather(self.full, self.hpz_shard, self.hpz_group, self.hpz_world, async_op) or True
         else:
-            self.gather_work = _all_gather(self.full, self.param_shard, group, self.world, async_op) or True
+            self.gather_work = _all_gather(self.full, self.shard_on_device(), group, self.world, async_op) or True
 
     def keep_secondary(self) -> None:
         """Before the whole parameters are released after the forward pass: keep this rank's 1 / hpz_world slice."""
@@ -175,7 +187,7 @@ class PartitionedZeroOptimizer:
                  clip_grad: float = 0.0, group=None, group_ranks: Optional[List[int]] = None,
                  grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
                  sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0,
-                 hpz_group=None, hpz_ranks: Optional[List[int]] = None):
+                 hpz_group=None, hpz_ranks: Optional[List[int]] = None, offload_param: bool = False):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
         self.stage = stage
@@ -230,7 +242,8 @@ class PartitionedZeroOptimizer:
                 unit = self.units[ui]
                 root = ui == 0
                 f = UnitFlat(plist, self.world, self.rank, hyper, f"{unit.name}.{hyper['name']}.{dt}",
-                             free_params=(stage == 3 and not root), free_grads=not root, tp=tp)
+                             free_params=(stage == 3 and not root), free_grads=not root, tp=tp,
+                             offload_param=offload_param)
                 unit.flats.append(f)
                 self.groups.append(f)
         # hpZ (`zero_hpz_partition_size`, stage 3): after a unit's forward all-gather over the whole group, every rank keeps
@@ -418,12 +431,16 @@ class PartitionedZeroOptimizer:
             coef = torch.full_like(norm, inv)
         b1, b2 = self.betas
         for f in self.groups:
+            low = None if f.master_is_view else f.param_shard
+            if f.param_offloaded:
+                low = torch.empty(f.shard, dtype=f.param_shard.dtype, device=f.master.device)
             ops.adam_step(f.master, f.exp_avg, f.exp_avg_sq, f.grad_acc, f.hyper["lr"], b1, b2, self.eps,
-                          f.hyper["weight_decay"], self.step_count, self.adamw, coef,
-                          None if f.master_is_view else f.param_shard)
+                          f.hyper["weight_decay"], self.step_count, self.adamw, coef, low)
+            if f.param_offloaded:
+                f.param_shard.copy_(low, non_blocking=True)         # back to the host copy
             f.hpz_fresh = False                       # the secondary copies hold the old parameters
             if not f.free_params:
-                _all_gather(f.full, f.param_shard, self.group, self.world)
+                _all_gather(f.full, f.shard_on_device(), self.group, self.world)
         return norm
 
     # ------------------------------------------------------------------ whole parameters
@@ -458,7 +475,7 @@ class PartitionedZeroOptimizer:
                 if not f.master_is_view:
                     f.param_shard.copy_(f.master)
                 if f.resident:
-                    _all_gather(f.full, f.param_shard, self.group, self.world)
+                    _all_gather(f.full, f.shard_on_device(), self.group, self.world)
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> Dict:
@@ -503,13 +520,13 @@ class PartitionedZeroOptimizer:
                 self.step_count = int(st[i]["step"])
                 f.hyper["lr"] = sd["base_optimizer_state"]["param_groups"][i]["lr"]
                 if load_master and f.resident:
-                    _all_gather(f.full, f.param_shard, self.group, self.world)
+                    _all_gather(f.full, f.shard_on_device(), self.group, self.world)
         if self.loss_scaler is not None and isinstance(sd.get("loss_scaler"), dict):
             self.loss_scaler.load_state_dict(sd["loss_scaler"])
 
     def memory_report(self) -> Dict[str, int]:
         """Bytes this rank holds persistently (shards and optimizer state) and transiently at most (one unit whole)."""
-        persistent = sum(f.param_shard.numel() * f.param_shard.element_size() + f.grad_acc.numel() * 4
+        persistent = sum((0 if f.param_offloaded else f.param_shard.numel() * f.param_shard.element_size()) + f.grad_acc.numel() * 4
                          + (0 if f.master_is_view else f.master.numel() * 4) + 2 * f.exp_avg.numel() * 4
                          for f in self.groups)
         root = sum(2 * f.nbytes for f in self.units[0].flats)

@@ -196,12 +196,16 @@ class Trainer:
                     hgroup, hranks, _, _ = state.create_mics_groups(hpz)
                     mics = {"hpz_group": hgroup, "hpz_ranks": hranks}
                     print_rank_0(f" > hpZ: secondary parameter partition over sub-groups of {hpz} ranks for the backward gathers")
+                offp = (cfg.zero_optimization or {}).get("offload_param") or {}
+                offload_param = isinstance(offp, dict) and str(offp.get("device", "none")).lower() == "cpu" and cfg.zero_stage >= 3
+                if offload_param:
+                    print_rank_0(" > ZeRO-3 parameter offload: released units keep their parameter shard in host memory")
                 optimizer = PartitionedZeroOptimizer(
                     groups, model.blocks(), stage=min(3, cfg.zero_stage), lr=cfg.lr,
                     betas=tuple(p.get("betas", (0.9, 0.999))), eps=p.get("eps", 1e-8), weight_decay=cfg.weight_decay,
                     adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
                     group=zgroup, group_ranks=zranks,
-                    sync_replicated=bool(cfg.sequence_parallel), **mics)
+                    sync_replicated=bool(cfg.sequence_parallel), offload_param=offload_param, **mics)
                 rep = optimizer.memory_report()
                 print_rank_0(f" > ZeRO stage {optimizer.stage}: {rep['persistent_bytes'] / 2**20:.0f} MiB of shards and "
                              f"optimizer state per rank, largest unit {rep['largest_unit_param_bytes'] / 2**20:.0f} MiB "

@@ -336,6 +336,47 @@ def test_zero23_data_parallel_equivalence(stage, ckpt_layers, tmp_path):
     run_distributed(_w_partitioned, 2, over, ref_losses, str(tmp_path))
 
 
+def _w_offload_param(rank, world, over, ref_losses):
+    cfg = _tiny_cfg(world, **over)
+    tr, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    off = [f for f in tr.optimizer.groups if f.param_offloaded]
+    keep = [f for f in tr.optimizer.groups if not f.param_offloaded]
+    assert off and keep                       # block units are offloaded; the resident root unit and fp32 flats are not
+    assert all(f.free_params and f.param_shard.device.type == "cpu" for f in off)
+    rep = tr.optimizer.memory_report()
+    assert rep["persistent_bytes"] < sum(f.shard * 12 + f.shard * 2 + f.shard * 4 for f in tr.optimizer.groups) + 2 * sum(
+        f.nbytes for f in tr.optimizer.units[0].flats)
+    # the host copies follow the update: gathering from them reproduces the masters
+    with tr.optimizer.full_params():
+        for f in off:
+            assert torch.allclose(f.shard_slice(f.full).float(), f.master.to(f.full.dtype).float())
+
+
+def _w_write_losses(rank, world, over, out):
+    import json
+    cfg = _tiny_cfg(world, **over)
+    _, losses = _run_steps(cfg)
+    if rank == 0:
+        with open(out, "w") as fh:
+            json.dump(losses, fh)
+
+
+@pytest.mark.slow
+def test_zero3_parameter_offload_matches(tmp_path):
+    """`offload_param.device: cpu` with stage 3 in bf16: the shards of released units live on the host, the loss trace
+    equals the run without offload."""
+    import json
+    over = {"train_micro_batch_size_per_gpu": 1, "gradient_accumulation_steps": 2, "precision": "bfloat16",
+            "zero_optimization": {"stage": 3}}
+    out = str(tmp_path / "ref.json")
+    run_distributed(_w_write_losses, 2, over, out)
+    ref_losses = json.load(open(out))
+    over2 = dict(over, zero_optimization={"stage": 3, "offload_param": {"device": "cpu"}})
+    run_distributed(_w_offload_param, 2, over2, ref_losses)
+
+
 @pytest.mark.slow
 @pytest.mark.parametrize("stage", [2, 3])
 def test_zero_mics_subgroup_sharding(stage, tmp_path):
