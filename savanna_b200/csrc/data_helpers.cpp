@@ -121,4 +121,49 @@ int64_t sbd_build_mapping(const int64_t* docs, int64_t num_docs_plus1, const int
   return n;
 }
 
+// Block mapping for retrieval-style datasets (role of the reference's helpers.cpp build_blocks_mapping): every document
+// (a run of sentences docs[d] .. docs[d+1]) is cut into blocks of whole sentences whose token count reaches
+// max_seq_length minus the document's title length; a block is closed early enough that the rest of the document can
+// still form a block of `min_num_sent` sentences.  Documents with fewer than `min_num_sent` sentences, and documents
+// that hold a sentence longer than `long_sentence_len` tokens, are skipped.  Rows are (first sentence, one past the
+// last sentence, document, block id), block ids counting up over the whole pass.  With `maps` the rows are written and
+// then shuffled with a seeded Fisher-Yates pass; without it only the row count is returned.
+int64_t sbd_build_blocks_mapping(const int64_t* docs, int64_t num_docs_plus1, const int32_t* sizes, const int32_t* title_sizes,
+                                 int32_t num_epochs, int64_t max_num_samples, int32_t max_seq_length, int32_t seed,
+                                 int32_t min_num_sent, int32_t long_sentence_len, int64_t* maps /* [n * 4] or nullptr */) {
+  int64_t n = 0;
+  for (int32_t epoch = 0; epoch < num_epochs && n < max_num_samples; ++epoch) {
+    int64_t block_id = 0;
+    for (int64_t d = 0; d + 1 < num_docs_plus1 && n < max_num_samples; ++d) {
+      const int64_t first = docs[d], last = docs[d + 1];
+      if (last - first < min_num_sent) continue;
+      bool too_long = false;
+      for (int64_t s = first; s < last; ++s) too_long |= sizes[s] > long_sentence_len;
+      if (too_long) continue;
+      const int32_t target = max_seq_length - title_sizes[d];
+      int64_t start = first;
+      int32_t len = 0, nsent = 0;
+      for (int64_t s = first; s < last; ++s) {
+        len += sizes[s];
+        ++nsent;
+        const int64_t remain = last - s - 1;
+        if ((len >= target && remain >= min_num_sent && nsent >= min_num_sent) || remain == 0) {
+          if (maps) { maps[4 * n] = start; maps[4 * n + 1] = s + 1; maps[4 * n + 2] = d; maps[4 * n + 3] = block_id; }
+          ++n; ++block_id;
+          if (n >= max_num_samples) break;
+          start = s + 1; len = 0; nsent = 0;
+        }
+      }
+    }
+  }
+  if (maps) {
+    uint64_t ctr = (static_cast<uint64_t>(seed) << 32) + 1;
+    for (int64_t i = n - 1; i > 0; --i) {
+      const int64_t j = static_cast<int64_t>(mix64(ctr++) % static_cast<uint64_t>(i + 1));
+      for (int k = 0; k < 4; ++k) { const int64_t t = maps[4 * i + k]; maps[4 * i + k] = maps[4 * j + k]; maps[4 * j + k] = t; }
+    }
+  }
+  return n;
+}
+
 }  // extern "C"

@@ -21,6 +21,8 @@ def _lib():
         _LIB.sbd_build_blending_indices.argtypes = [P, P, P, I32, I64]
         _LIB.sbd_build_mapping.argtypes = [P, I64, P, I32, I64, I32, D, I32, I32, P]
         _LIB.sbd_build_mapping.restype = I64
+        _LIB.sbd_build_blocks_mapping.argtypes = [P, I64, P, P, I32, I64, I32, I32, I32, I32, P]
+        _LIB.sbd_build_blocks_mapping.restype = I64
     return _LIB
 
 
@@ -96,4 +98,28 @@ def build_mapping(docs: np.ndarray, sizes: np.ndarray, num_epochs: int, max_num_
     out = np.zeros((n, 3), dtype=np.int64)
     lib.sbd_build_mapping(_ptr(docs), len(docs), _ptr(sizes), num_epochs, max_num_samples, max_seq_length,
                           short_seq_prob, seed, min_num_sent, _ptr(out))
+    return out
+
+
+def build_blocks_mapping(docs: np.ndarray, sizes: np.ndarray, title_sizes: np.ndarray, num_epochs: int, max_num_samples: int,
+                         max_seq_length: int, seed: int, use_one_sent_blocks: bool = False,
+                         long_sentence_len: int = 512) -> np.ndarray:
+    """Rows (first sentence, one past the last sentence, document, block id), shuffled: the documents' sentences cut
+    into blocks of about `max_seq_length - title length` tokens (retrieval-style block datasets).  `docs` holds the
+    sentence offset of every document plus the end (len = documents + 1), `sizes` the sentence lengths, `title_sizes`
+    one length per document."""
+    lib = _lib()
+    if lib is None:
+        raise RuntimeError("build_blocks_mapping needs the native data library (python -m savanna_b200.csrc.build)")
+    docs = np.ascontiguousarray(docs, dtype=np.int64)
+    sizes = np.ascontiguousarray(sizes, dtype=np.int32)
+    title_sizes = np.ascontiguousarray(title_sizes, dtype=np.int32)
+    if len(title_sizes) != len(docs) - 1:
+        raise ValueError("one title length per document is needed")
+    min_sent = 1 if use_one_sent_blocks else 2
+    args = (_ptr(docs), len(docs), _ptr(sizes), _ptr(title_sizes), num_epochs, max_num_samples, max_seq_length, seed,
+            min_sent, long_sentence_len)
+    n = lib.sbd_build_blocks_mapping(*args, None)
+    out = np.zeros((n, 4), dtype=np.int64)
+    lib.sbd_build_blocks_mapping(*args, _ptr(out))
     return out

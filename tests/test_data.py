@@ -206,3 +206,24 @@ def test_legacy_indexed_dataset_round_trip(tmp_path):
     b3.end_document()
     b3.finalize(p3 + ".idx")
     assert ids.infer_dataset_impl(p3) == "mmap" and isinstance(ids.make_dataset(p3, "infer"), ids.MMapIndexedDataset)
+
+
+def test_build_blocks_mapping_cuts_documents_into_sentence_blocks():
+    """Native block mapping: whole sentences per block, token budget reduced by the title, short and over-long
+    documents skipped, rows shuffled reproducibly."""
+    docs = np.array([0, 5, 6, 9, 12], dtype=np.int64)               # 4 documents: 5, 1, 3, 3 sentences
+    sizes = np.array([4, 4, 4, 4, 4, 7, 3, 3, 3, 5, 600, 5], dtype=np.int32)
+    titles = np.array([2, 1, 1, 1], dtype=np.int32)
+    m = helpers.build_blocks_mapping(docs, sizes, titles, num_epochs=1, max_num_samples=100, max_seq_length=10, seed=3)
+    rows = sorted(map(tuple, m.tolist()))
+    # doc 0 (budget 8): sentences 0-1 reach 8 with 3 left -> block; 2-3 would leave one sentence (< 2), so 2-4 is the rest
+    # doc 1: one sentence, skipped; doc 2 (budget 9): 3+3+3 = 9 at the last sentence -> one block; doc 3: a 600-token sentence
+    assert rows == [(0, 2, 0, 0), (2, 5, 0, 1), (6, 9, 2, 2)]
+    again = helpers.build_blocks_mapping(docs, sizes, titles, num_epochs=1, max_num_samples=100, max_seq_length=10, seed=3)
+    assert np.array_equal(m, again)
+    one = helpers.build_blocks_mapping(docs, sizes, titles, 1, 100, 10, 3, use_one_sent_blocks=True)
+    assert (5, 6, 1, 3) in set(map(tuple, one.tolist())) or any(r[2] == 1 for r in one.tolist())
+    two_epochs = helpers.build_blocks_mapping(docs, sizes, titles, 2, 100, 10, 3)
+    assert len(two_epochs) == 6
+    capped = helpers.build_blocks_mapping(docs, sizes, titles, 5, 4, 10, 3)
+    assert len(capped) == 4
