@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import argparse
 import glob
+import re
 import os
 import shutil
 from typing import Dict, List
@@ -18,9 +19,31 @@ from .params import partition_dim
 
 
 def load_shards(step_dir: str) -> List[Dict]:
+    """One model-states dict per tensor-parallel rank.  Two layouts are read: `mp_rank_<TP>_model_states.pt` holding
+    the whole module, and the pipeline engine's one file per layer slot, `layer_<IDX>-model_<TP>-model_states.pt`
+    (role of the reference's savanna/loading.py raw per-layer load): the layer files are put back under
+    `sequential.<IDX>.` keys, one assembled module per tensor-parallel rank, whatever the number of stages was."""
+    layer_files = sorted(glob.glob(os.path.join(step_dir, "layer_*-model_*-model_states.pt")))
     files = sorted(glob.glob(os.path.join(step_dir, "mp_rank_*_model_states.pt")))
+    if layer_files:
+        by_tp: Dict[int, Dict[int, str]] = {}
+        for f in layer_files:
+            m = re.match(r"layer_(\d+)-model_(\d+)-model_states\.pt$", os.path.basename(f))
+            by_tp.setdefault(int(m.group(2)), {})[int(m.group(1))] = f
+        engine = torch.load(files[0], map_location="cpu", weights_only=False) if files else {}
+        out = []
+        for tp in sorted(by_tp):
+            module = {}
+            for idx in sorted(by_tp[tp]):
+                for k, v in torch.load(by_tp[tp][idx], map_location="cpu", weights_only=False).items():
+                    module[f"sequential.{idx}.{k}"] = v
+            shard = {k: v for k, v in engine.items() if k != "module"}
+            shard["module"] = module
+            shard["mp_world_size"] = len(by_tp)
+            out.append(shard)
+        return out
     if not files:
-        raise FileNotFoundError(f"no mp_rank_*_model_states.pt in {step_dir}")
+        raise FileNotFoundError(f"no mp_rank_*_model_states.pt and no layer_*-model_*-model_states.pt in {step_dir}")
     return [torch.load(f, map_location="cpu", weights_only=False) for f in files]
 
 

@@ -490,6 +490,22 @@ def test_pipeline_checkpoint_save_load_continue(tmp_path):
     from savanna_b200.parallel import state
     state.destroy_model_parallel()
     run_distributed(_w_pipeline_ckpt, 2, ref_losses, str(tmp_path))
+    # the per-layer files of the two stages load into one whole model (single process, for inference and the tools)
+    from savanna_b200.inference.load import load_for_inference
+    from savanna_b200.tools.reshard_model_parallel import load_shards
+    step = os.path.join(str(tmp_path), "global_step2")
+    shards = load_shards(step)
+    assert len(shards) == 1 and "sequential.0.word_embeddings.weight" in shards[0]["module"]
+    model, tok, cfg1 = load_for_inference(step, device="cpu")
+    sd = model.state_dict()
+    for k, v in shards[0]["module"].items():
+        if k in sd:
+            assert torch.equal(sd[k], v.to(sd[k].dtype)), k
+    ids = torch.tensor([list(tok.tokenize("ACGTACGT"))], dtype=torch.long)
+    with torch.no_grad():
+        logits = model(ids, torch.arange(ids.shape[1]))
+    assert logits.shape[:2] == ids.shape and torch.isfinite(logits).all()
+    state.destroy_model_parallel()
 
 
 def test_ring_block_plan_covers_the_causal_mask():
