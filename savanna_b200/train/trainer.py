@@ -135,6 +135,11 @@ class Trainer:
             if getattr(self.model, "is_pipeline_stage", False):
                 raise NotImplementedError("fp16 loss scaling is not wired into the pipeline schedule; use bf16")
             self.optimizer.loss_scaler = self.loss_scaler
+        if cfg.debug_dir:
+            # every leaf module's first inputs / outputs go to <debug_dir>/<layout tag>/ for an offline diff of two
+            # parallel layouts (python -m savanna_b200.utils.debug <dir a> <dir b>)
+            from ..utils.debug import register_debug_hooks
+            self._debug_hooks = register_debug_hooks(self.model, cfg)
         from . import curriculum as curriculum_mod
         self.curriculum = curriculum_mod.from_config(cfg)          # sequence-length curriculum, or None
         self.profiler = None
