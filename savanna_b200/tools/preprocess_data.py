@@ -15,7 +15,7 @@ import time
 
 import numpy as np
 
-from ..data.indexed_dataset import MMapIndexedDatasetBuilder, best_fitting_dtype
+from ..data.indexed_dataset import make_builder
 
 _TOK = None
 
@@ -26,10 +26,19 @@ class _Cfg:
         self.make_vocab_size_divisible_by, self.model_parallel_size, self.padded_vocab_size = 8, 1, None
 
 
+_FIX = None
+
+
 def _init(args):
-    global _TOK
+    global _TOK, _FIX
     from ..data.tokenizer import build_tokenizer
     _TOK = build_tokenizer(_Cfg(args))
+    if getattr(args, "ftfy", False):
+        try:
+            import ftfy
+        except ImportError as exc:
+            raise SystemExit("--ftfy needs the ftfy package, which is not installed") from exc
+        _FIX = ftfy.fix_text
 
 
 def _encode(payload):
@@ -40,7 +49,7 @@ def _encode(payload):
     doc = json.loads(line)
     out = {}
     for k in keys:
-        ids = list(_TOK.tokenize(doc[k]))
+        ids = list(_TOK.tokenize(_FIX(doc[k]) if _FIX is not None else doc[k]))
         if append_eod:
             ids.append(_TOK.eod)
         if enforce_len and len(ids) != enforce_len:
@@ -59,13 +68,18 @@ def main(argv=None):
     ap.add_argument("--merge-file", default=None)
     ap.add_argument("--append-eod", action="store_true")
     ap.add_argument("--enforce-sample-length", type=int, default=None)
+    ap.add_argument("--num-docs", type=int, default=None, help="number of input documents, if known: progress is then "
+                    "reported as a share of it")
+    ap.add_argument("--ftfy", action="store_true", help="repair mis-decoded text with ftfy before tokenizing")
+    ap.add_argument("--dataset-impl", default="mmap", choices=["mmap", "lazy", "cached"],
+                    help="on-disk format: memory-mapped (default) or the older index format read lazily / cached")
     ap.add_argument("--workers", type=int, default=1)
     ap.add_argument("--log-interval", type=int, default=10000)
     a = ap.parse_args(argv)
     _init(a)
     vocab = _TOK.vocab_size
     os.makedirs(os.path.dirname(os.path.abspath(a.output_prefix)), exist_ok=True)
-    builders = {k: MMapIndexedDatasetBuilder(f"{a.output_prefix}_{k}_document.bin", dtype=best_fitting_dtype(vocab))
+    builders = {k: make_builder(f"{a.output_prefix}_{k}_document.bin", impl=a.dataset_impl, vocab_size=vocab)
                 for k in a.jsonl_keys}
 
     def lines():
@@ -89,7 +103,8 @@ def main(argv=None):
         nbytes += nb
         if n % a.log_interval == 0:
             dt = time.time() - t0
-            print(f"processed {n} documents ({n / dt:.1f} docs/s, {nbytes / dt / 1e6:.2f} MB/s)", flush=True)
+            share = f" = {100.0 * n / a.num_docs:.1f} %" if a.num_docs else ""
+            print(f"processed {n} documents{share} ({n / dt:.1f} docs/s, {nbytes / dt / 1e6:.2f} MB/s)", flush=True)
     if pool is not None:
         pool.close()
     for k, b in builders.items():

@@ -88,6 +88,21 @@ def test_preprocess_and_load(tmp_path):
     main(["--input", str(src), "--output-prefix", str(tmp_path / "out"), "--append-eod"])
     ds = MMapIndexedDataset(str(tmp_path / "out_text_document"))
     assert len(ds) == 3 and ds[0].tolist() == [65, 67, 71, 84, 0] and ds[2].tolist() == [84, 0]
+    # uniform-length data: only documents of exactly --enforce-sample-length tokens are kept; the older index format
+    src2 = tmp_path / "u.jsonl"
+    src2.write_text("\n".join(json.dumps({"text": t}) for t in ("ACGTACG", "ACG", "TTTTGGG", "ACGTACGTAC")) + "\n")
+    main(["--input", str(src2), "--output-prefix", str(tmp_path / "uni"), "--append-eod", "--enforce-sample-length", "8",
+          "--dataset-impl", "lazy", "--num-docs", "4", "--log-interval", "1"])
+    from savanna_b200.data import indexed_dataset as ids
+    assert ids.infer_dataset_impl(str(tmp_path / "uni_text_document")) in ("lazy", "cached")
+    uni = ids.make_dataset(str(tmp_path / "uni_text_document"), "lazy")
+    assert len(uni) == 2 and all(len(uni[i]) == 8 for i in range(2))
+    # ... and trains as fixed-length samples: every sample is one whole document
+    from savanna_b200.data.sequence_dataset import SequenceDataset
+    import numpy as np
+    sd = SequenceDataset("train", str(tmp_path / "uni_text_document"), np.arange(2, dtype=np.int32), uni, 2, 8, 1,
+                         enforce_sample_length=True)
+    assert len(sd) >= 1 and sd[0]["text"].shape == (9,)
 
 
 def test_generation_greedy_is_deterministic():
