@@ -39,8 +39,17 @@ def main(argv=None):
     ap.add_argument("--tokenizer-type", default="CharLevelTokenizer")
     ap.add_argument("--vocab-file", default=None)
     ap.add_argument("--merge-file", default=None)
-    ap.add_argument("--seq-length", type=int, default=None, help="pad every row to this many entries")
+    ap.add_argument("--seq-length", "--enforce-sample-length", dest="seq_length", type=int, default=None,
+                    help="pad every row to this many entries (set the run's dpo_data_seq_length to the same number)")
+    ap.add_argument("--ftfy", action="store_true", help="repair mis-decoded text with ftfy before tokenizing")
     a = ap.parse_args(argv)
+    fix = None
+    if a.ftfy:
+        try:
+            import ftfy
+        except ImportError as exc:
+            raise SystemExit("--ftfy needs the ftfy package, which is not installed") from exc
+        fix = ftfy.fix_text
     from ..data.tokenizer import build_tokenizer
     from .preprocess_data import _Cfg
     tok = build_tokenizer(_Cfg(a))
@@ -54,7 +63,10 @@ def main(argv=None):
                 line = line.strip()
                 if not line:
                     continue
-                builder.add_item(encode_pair(json.loads(line), tok, a.seq_length))
+                doc = json.loads(line)
+                if fix is not None:
+                    doc = dict(doc, text_accept=fix(doc["text_accept"]), text_reject=fix(doc["text_reject"]))
+                builder.add_item(encode_pair(doc, tok, a.seq_length))
                 builder.end_document()
                 n += 1
     builder.finalize(a.output_prefix + "_text_document.idx")
