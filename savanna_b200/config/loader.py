@@ -323,10 +323,6 @@ class GlobalConfig:
                     raise ConfigError("pipeline and context parallelism cannot be combined")
             self.operator_config = oc
 
-        if self.fp8_recipe == "mxfp8" and self.use_fp8_linears and (self.model_parallel_size or 1) > 1 and self.sequence_parallel:
-            raise ConfigError("fp8_recipe 'mxfp8' (block-scaled projections) is not available with tensor + sequence "
-                              "parallelism: the fused all-gather / reduce-scatter projections use per-tensor scales; "
-                              "use fp8_recipe 'delayed' there")
         self.causal = self.pretraining_strategy == "AR"
         if self.sparsity_config is None:
             self.sparsity_config = {}

@@ -686,11 +686,15 @@ def linear(x, w, bias=None, fp8: bool = False, residual=None):
 
 def linear_allgather(x, w, bias, seq_dim, fp8):
     from ..parallel import fused_tp
+    if fp8 and FP8_RECIPE == "mxfp8":
+        return None                 # block-scaled operands: the caller gathers with NCCL and runs the MXFP8 projection
     return fused_tp.linear_allgather(x, w, bias, seq_dim, fp8=bool(fp8) and _is_bf16(x, w, bias))
 
 
 def linear_reducescatter(x, w, seq_dim, fp8):
     from ..parallel import fused_tp
+    if fp8 and FP8_RECIPE == "mxfp8":
+        return None                 # as above: MXFP8 projection, then an NCCL reduce-scatter
     return fused_tp.linear_reducescatter(x, w, seq_dim, fp8=bool(fp8) and _is_bf16(x, w))
 
 

@@ -366,6 +366,46 @@ def test_tensor_sequence_parallel_training_fused():
     _spawn(_w_tp_train, 2)
 
 
+def _w_tp_train_mx(rank, world):
+    """Block-scaled fp8 projections under tensor + sequence parallelism: NCCL all-gather / reduce-scatter around the
+    MXFP8 GEMMs (the fused peer-memory projections take per-tensor scales only)."""
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.ops import cuda_ops
+    from savanna_b200.train.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_gpu.yml")],
+                                 {"global_num_gpus": world, "model_parallel_size": world, "sequence_parallel": True,
+                                  "train_micro_batch_size_per_gpu": 1, "use_fp8_linears": True, "fp8_recipe": "mxfp8",
+                                  "use_fp8_input_projections": True, "use_fp8_output_projections": True,
+                                  "use_fp8_mlp_projections": True})
+    tr = Trainer(cfg, load=False)
+    assert cuda_ops.FP8_RECIPE == "mxfp8"
+    calls = []
+    real = cuda_ops.gemm_mx
+    cuda_ops.gemm_mx = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+
+    def it():
+        i = 0
+        while True:
+            yield {"text": acgt_batch(1, cfg.seq_length, seed=i, pin=True)}
+            i += 1
+    d = it()
+    try:
+        losses = [float(tr.train_step(d)) for _ in range(8)]
+    finally:
+        cuda_ops.gemm_mx = real
+        cuda_ops.set_fp8_recipe("delayed")
+    cuda_ops.check_status()
+    assert calls, "no block-scaled GEMM ran"
+    assert losses[-1] < losses[0] - 0.5, losses
+
+
+@needs2
+def test_tensor_sequence_parallel_training_block_scaled_fp8():
+    _spawn(_w_tp_train_mx, 2)
+
+
 # ------------------------------------------------------------------------------------------ context parallelism
 # 128-wide heads so that the tcgen05 attention kernels and the peer-memory ring are the ones that run
 _WIDE = {"hidden_size": 512, "num_attention_heads": 4, "num_groups_hyena": 512, "num_groups_hyena_medium": 32,
