@@ -77,3 +77,27 @@ def test_partitioned_stages_match_stage1_two_gpus(stage):
     over = dict(_WIDE, **_FP8)
     _spawn_args(_w_two_gpus, 2, over, {"zero_optimization": {"stage": stage}, "checkpoint_activations": True,
                                        "checkpoint_num_layers": 2})
+
+
+@pytest.mark.parametrize("over", [
+    {"zero_optimization": {"stage": 1, "offload_optimizer": {"device": "cpu", "pin_memory": True}}},
+    {"zero_optimization": {"stage": 3, "offload_param": {"device": "cpu"}}},
+    {"zero_optimization": {"stage": 1}, "checkpoint_activations": True, "checkpoint_num_layers": 2, "checkpoint_in_cpu": True},
+], ids=["offload_optimizer", "offload_param", "checkpoint_in_cpu"])
+def test_host_offload_paths_match_the_resident_run(over):
+    """Optimizer state on the host (update on the CPU), parameter shards on the host (stage 3) and checkpointed chunk
+    inputs on the host: same loss trace as the all-on-device ZeRO-1 run."""
+    want = _losses(1, 0, dict(_WIDE, zero_optimization={"stage": 1}))
+    got = _losses(1, 0, dict(_WIDE, **over))
+    _close(got, want)
+
+
+def test_fp16_precision_with_dynamic_loss_scale_on_the_gpu():
+    """fp16 parameters and activations (the operators then run their PyTorch statements: the own kernels are bf16 / fp32)
+    with the dynamic loss scaler: starts at the bf16 run's loss and trains."""
+    want = _losses(1, 0, dict(_WIDE, zero_optimization={"stage": 1}), n=4)
+    got = _losses(1, 0, dict(_WIDE, zero_optimization={"stage": 1}, precision="fp16",
+                             fp16={"enabled": True, "loss_scale": 0, "initial_scale_power": 10, "loss_scale_window": 100,
+                                   "hysteresis": 2}), n=4)
+    assert abs(got[0] - want[0]) < 0.05, (got, want)
+    assert got[-1] < got[0] - 0.2, got
