@@ -19,9 +19,15 @@ def build_command(cfg, nproc=None):
     script_idx = args.index(cfg.user_script)
     worker_args = args[script_idx + 1:]
     nproc = nproc or cfg.global_num_gpus
+    rank_logs = []
+    if cfg.enable_each_rank_log:
+        # one stdout / stderr file per rank (and still on the terminal), under <log_dir or .>/rank_logs
+        log_dir = os.path.join(cfg.log_dir or ".", "rank_logs")
+        os.makedirs(log_dir, exist_ok=True)
+        rank_logs = ["--log-dir", log_dir, "--redirects", "3", "--tee", "3"]
     return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-            "--master-addr", cfg.master_addr or "127.0.0.1", "--master-port", str(cfg.master_port),
-            cfg.user_script] + worker_args
+            "--master-addr", cfg.master_addr or "127.0.0.1", "--master-port", str(cfg.master_port)] + rank_logs + \
+           [cfg.user_script] + worker_args
 
 
 def main(argv=None):

@@ -126,3 +126,23 @@ def test_ops_scripts_config_diff_log_parse_checkpoint_summary_filter_lens(tmp_pa
     sd = torch.load(ck_dir / "mp_rank_00_model_states.pt", weights_only=False)
     assert torch.equal(sd["module"]["sequential.3.mixer.mixer.filter.h"][:, :16], h) and sd["param_shapes"][0][
         "sequential.3.mixer.mixer.filter.h"] == torch.Size([4, 64])
+
+
+def test_launch_command_with_per_rank_logs(tmp_path, monkeypatch):
+    """`enable_each_rank_log`: the worker command redirects every rank's output into its own file under rank_logs."""
+    import importlib.util
+    from savanna_b200.config import GlobalConfig
+    spec = importlib.util.spec_from_file_location("launch_mod", os.path.join(ROOT, "launch.py"))
+    launch = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(launch)
+    tiny = os.path.join(ROOT, "configs", "baseline", "tiny_sh2_cpu.yml")
+    cfg = GlobalConfig.consume_deepy_args(["train.py", tiny, "--num_gpus", "2"])
+    cmd = launch.build_command(cfg)
+    assert "--log-dir" not in cmd and cmd[cmd.index("train.py") - 1] != "3"
+    cfg.enable_each_rank_log = True
+    cfg.log_dir = str(tmp_path / "logs")
+    cmd = launch.build_command(cfg)
+    i = cmd.index("--log-dir")
+    assert cmd[i + 1] == os.path.join(str(tmp_path / "logs"), "rank_logs") and os.path.isdir(cmd[i + 1])
+    assert cmd[i + 2: i + 6] == ["--redirects", "3", "--tee", "3"] and cmd.index("train.py") > i
+    assert "--nproc-per-node=2" in cmd
