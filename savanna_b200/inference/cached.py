@@ -60,6 +60,8 @@ class CachedDecoder:
             m = b.mixer.mixer
             if isinstance(m, HyenaOperator) and not m.is_mr and not isinstance(m.filter, ImplicitModalFilter):
                 raise NotImplementedError("cached generation needs the implicit modal filter for Hyena-LI")
+            if getattr(m, "sparse", False):
+                raise NotImplementedError("cached generation does not cover the block-sparse attention operators")
             if isinstance(m, HyenaOperator) and (m.bidirectional or m.slow_heads):
                 raise NotImplementedError("cached generation does not cover two-sided filters or outer-product heads")
         self.states: List[Dict] = []

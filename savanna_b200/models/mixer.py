@@ -19,7 +19,8 @@ from .hyena import CausalDepthwiseConv1d, HyenaOperator, ShortHyenaOperator, _as
 from .rope import RotaryEmbedding
 
 HYENA_OPS = ("hyena", "hyena_mr", "hyena_se")
-ATTENTION_OPS = ("flash_v2", "flash", "global", "ring", "flash_te")
+ATTENTION_OPS = ("flash_v2", "flash", "global", "ring", "flash_te", "local", "sparse_fixed", "sparse_variable", "bigbird",
+                 "bslongformer")
 
 
 class SelfAttention(nn.Module):
@@ -39,6 +40,13 @@ class SelfAttention(nn.Module):
         self.operator_type = operator_type
         # context-parallel exchange of `flash_te` layers: "p2p" = ring of K/V shards, "a2a" = head exchange, "all_gather"
         self.cp_comm_type = cfg.flash_te_comm_type or "p2p"
+        # legacy block-sparse operators: a layout mask over materialised scores (models/sparse_layouts.py)
+        from .sparse_layouts import SPARSE_OPERATORS
+        self.sparse = operator_type in SPARSE_OPERATORS
+        self.sparsity_config = dict(cfg.sparsity_config or {})
+        self._sparse_masks = {}
+        if self.sparse and not cfg.causal:
+            raise NotImplementedError("block-sparse attention operators are built for causal models (unidirectional layouts)")
         self._rotary = []          # the module itself is registered by the owning mixer as `rotary_emb`
         if cfg.pos_emb in ("rotary", "rotary_linear_scaled", "rotary_ntk_scaled", "rotary2"):
             rd = int(self.hd * cfg.rotary_pct)
@@ -61,10 +69,30 @@ class SelfAttention(nn.Module):
                                                        cfg.rpe_num_buckets, cfg.rpe_max_distance, cfg.num_attention_heads,
                                                        tp, rank, dtype=torch.float32, device=device)
 
+    def _sparse_mask(self, L: int, device) -> torch.Tensor:
+        m = self._sparse_masks.get(L)
+        if m is None or m.device != device:
+            from .sparse_layouts import additive_mask
+            tp, r = state.get_model_parallel_world_size(), state.get_model_parallel_rank()
+            m = additive_mask(self.operator_type, self.heads * tp, L, self.sparsity_config)      # layouts of all heads ...
+            m = m[r * self.heads:(r + 1) * self.heads].to(device)                                 # ... this rank's slice
+            self._sparse_masks = {L: m}                 # one length at a time: the mask is [heads, L, L]
+        return m
+
     def forward(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         B, L, _ = qkv.shape
         qkv = qkv.view(B, L, self.heads, 3 * self.hd)
         cp = state.get_context_parallel_world_size()
+        if self.sparse:
+            if cp > 1:
+                raise NotImplementedError("block-sparse attention operators do not run under context parallelism")
+            from ..ops import reference as ref
+            q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+            if self._rotary:
+                cos, sin = self._rotary[0](positions)
+                q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+            o = ref.attention(q, k, v, True, positions, positions, bias=self._sparse_mask(L, qkv.device))
+            return o.reshape(B, L, self.heads * self.hd)
         if self.score_bias is not None:
             if cp > 1:
                 raise NotImplementedError("score-bias attention (alibi / rpe) does not run under context parallelism")

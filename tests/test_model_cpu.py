@@ -374,3 +374,61 @@ def test_mup_base_shapes_file_drives_the_groups(tmp_path):
     groups = param_groups(model, wide)
     mat = [g for g in groups if g["name"].endswith("_matrix")]
     assert mat and all(abs(g["lr"] - 1e-3 / 2.0) < 1e-12 for g in mat)          # 2 from the file, not mup_width_scale = 7
+
+
+def test_block_sparse_layouts_follow_their_rules():
+    from savanna_b200.models.sparse_layouts import additive_mask, block_layout
+    nb = 8
+    loc = block_layout("local", 2, nb, {"num_sliding_window_blocks": 5})[0]
+    for r in range(nb):
+        for c in range(nb):
+            assert bool(loc[r, c]) == (r - 2 <= c <= r), (r, c)
+    fx = block_layout("sparse_fixed", 1, nb, {"num_local_blocks": 4, "num_global_blocks": 1})[0]
+    assert bool(fx[2, 0]) and bool(fx[3, 3]) and not bool(fx[1, 2])           # inside window 0, lower triangle
+    assert bool(fx[6, 4]) and not bool(fx[6, 2])                              # window 1 sees itself, not window 0 ...
+    assert bool(fx[6, 3]) and bool(fx[7, 3]) and bool(fx[7, 7])               # ... except the global column 3 (and 7)
+    var = block_layout("sparse_variable", 1, nb, {"local_window_blocks": [2, 3], "global_block_indices": [1]})[0]
+    assert bool(var[1, 0]) and not bool(var[2, 0]) and bool(var[4, 2]) and bool(var[7, 5]) and not bool(var[5, 4])
+    assert all(bool(var[r, 1]) for r in range(1, nb))
+    bb = block_layout("bigbird", 1, nb, {"num_random_blocks": 1, "num_sliding_window_blocks": 3, "num_global_blocks": 1})[0]
+    assert all(bool(bb[r, 0]) and bool(bb[r, r]) and (r == 0 or bool(bb[r, r - 1])) for r in range(nb))
+    assert int(bb.sum()) >= int(block_layout("bigbird", 1, nb, {"num_random_blocks": 0})[0].sum())
+    lf = block_layout("bslongformer", 1, nb, {"num_sliding_window_blocks": 3, "global_block_indices": [0, 4],
+                                               "global_block_end_indices": [1, 6]})[0]
+    assert bool(lf[7, 4]) and bool(lf[7, 5]) and not bool(lf[7, 3]) and bool(lf[7, 0]) and bool(lf[7, 6])
+    for lay in (loc, fx, var, bb, lf):
+        assert not bool(torch.triu(lay, 1).any()) and bool(torch.diagonal(lay).all())
+    heads = block_layout("sparse_fixed", 4, nb, {"num_local_blocks": 4, "num_global_blocks": 1, "different_layout_per_head": True,
+                                                  "num_different_global_patterns": 2})
+    assert not torch.equal(heads[0], heads[1]) and torch.equal(heads[0], heads[2])
+    m = additive_mask("local", 2, 64, {"block": 16, "num_sliding_window_blocks": 3})
+    assert m.shape == (2, 64, 64) and m[0, 40, 20] == 0 and m[0, 40, 10] == float("-inf")
+    with pytest.raises(ValueError):
+        additive_mask("local", 2, 60, {"block": 16})
+
+
+def test_block_sparse_attention_operators_train_and_match_a_masked_softmax():
+    cfg = _cfg(operator_config=[[["hyena_se", "local", "hyena_mr", "bigbird"], 1]], num_layers=4,
+               sparsity_config={"block": 16, "num_sliding_window_blocks": 3, "num_random_blocks": 1})
+    tr = Trainer(cfg, load=False)
+    d = _iter(cfg)
+    losses = [float(tr.train_step(d)) for _ in range(5)]
+    assert losses[-1] < losses[0], losses
+    layer = [m for m in tr.model.modules() if getattr(m, "sparse", False) and m.operator_type == "local"][0]
+    B, L, H, hd = 1, 64, layer.heads, layer.hd
+    torch.manual_seed(0)
+    qkv = torch.randn(B, L, H * 3 * hd)
+    pos = torch.arange(L)
+    got = layer(qkv, pos).view(B, L, H, hd)
+    q3 = qkv.view(B, L, H, 3 * hd)
+    q, k, v = q3[..., :hd], q3[..., hd:2 * hd], q3[..., 2 * hd:]
+    if layer._rotary:
+        from savanna_b200 import ops
+        cos, sin = layer._rotary[0](pos)
+        q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+    s = torch.einsum("bqhd,bkhd->bhqk", q, k) / hd ** 0.5
+    blk = torch.arange(L) // 16
+    keep = (blk[None, :] >= blk[:, None] - 1) & (pos[None, :] <= pos[:, None])
+    s = s.masked_fill(~keep[None, None], float("-inf"))
+    want = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v)
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
