@@ -154,18 +154,18 @@ def pad_vocab_size(n: int, divisible_by: int, tp: int) -> int:
 
 
 def build_tokenizer(cfg):
-    t = cfg.tokenizer_type
-    if t == "CharLevelTokenizer":
+    t = str(cfg.tokenizer_type).lower()                 # names compare without case, as in the reference
+    if t == "charleveltokenizer":
         tok = CharLevelTokenizer(512)
-    elif t == "GPT2BPETokenizer":
+    elif t == "gpt2bpetokenizer":
         tok = GPT2BPETokenizer(cfg.vocab_file, cfg.merge_file)
-    elif t in ("HFTokenizer", "HFGPT2Tokenizer"):
+    elif t in ("hftokenizer", "hfgpt2tokenizer"):
         tok = HFTokenizer(cfg.vocab_file)
-    elif t == "SPMTokenizer":
+    elif t == "spmtokenizer":
         tok = SentencePieceTokenizer(cfg.vocab_file)
-    elif t == "TiktokenTokenizer":
+    elif t == "tiktokentokenizer":
         tok = TiktokenTokenizer(cfg.vocab_file)
     else:
-        raise NotImplementedError(f"tokenizer {t!r} not implemented")
+        raise NotImplementedError(f"tokenizer {cfg.tokenizer_type!r} not implemented")
     cfg.padded_vocab_size = pad_vocab_size(tok.vocab_size, cfg.make_vocab_size_divisible_by, cfg.model_parallel_size)
     return tok
