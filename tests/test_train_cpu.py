@@ -165,3 +165,75 @@ def test_fp16_training_scales_the_loss_and_skips_overflowed_steps(stage):
     assert l2 == l2 and tr.skipped_iters == 1 and not tr.optimizer.overflow
     sd = tr.optimizer.state_dict()
     assert sd["dynamic_loss_scale"] is True and sd["loss_scaler"]["cur_scale"] == tr.loss_scaler.scale
+
+
+def _tag_mask_by_loop(row, eod):
+    """Row-by-row statement of the tag rule: pieces between '|' / end-of-document / row ends that hold '_', ';' or ' '."""
+    L = len(row)
+    keep = [1] * L
+    cuts = sorted({0, L - 1} | {i for i, t in enumerate(row) if t in (124, eod)})
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        if any(t in (95, 59, 32) for t in row[a:b]):
+            lo = a + 1 if row[a] == eod else a
+            hi = b - 1 if row[b] == eod else b
+            for i in range(lo, hi + 1):
+                keep[i] = 0
+    for i, t in enumerate(row):
+        if t in (64, 35):
+            keep[i] = 0
+    return keep
+
+
+def test_control_and_phylogenetic_tag_loss_mask():
+    import torch
+    from savanna_b200.train.batch import mask_control_tags
+    enc = lambda s: [0 if c == "$" else ord(c) for c in s]             # '$' stands for end-of-document (token 0)
+    rows = [
+        "ACGT|d__Bacteria;p__Firmicutes|ACGTACGT$ACGT@ACGT",            # a whole tag, a control character
+        "teria;s__coli|ACGTACGTACGT#ACGT|d__Archaea;p__Eury",            # tags cut by both sample boundaries
+        "ACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTAC",            # plain sequence
+        "ACGT$|d__B;c__X|ACGT$ACGT|r__Z|$ACGTACGTACGTACGT|ACG",          # tags next to end-of-document tokens, a lone bar
+    ]
+    L = max(len(r) for r in rows)
+    rows = [r.ljust(L, "A") for r in rows]
+    tok = torch.tensor([enc(r) for r in rows])
+    got = mask_control_tags(tok, torch.ones(tok.shape), eod=0)
+    want = torch.tensor([_tag_mask_by_loop(enc(r), 0) for r in rows], dtype=torch.float32)
+    assert torch.equal(got, want), (got - want).nonzero().tolist()
+    assert got[0, :4].sum() == 4 and got[0, 4:31].sum() == 0 and got[0, 31:39].sum() == 8      # DNA kept, tag dropped
+    assert got[1, :14].sum() == 0 and got[1, 14] == 1                                           # leading partial tag
+    assert got[2].sum() == L
+
+
+def test_masked_strategies_follow_their_rules_and_train():
+    import math
+    import os
+    import torch
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.train import batch as bm
+    from savanna_b200.train.trainer import Trainer
+    g = torch.Generator().manual_seed(0)
+    clean = acgt_batch(4, 199, seed=3)[:, :200]
+    clean[:, 50] = 0                                                     # an end-of-document token per row
+    out, sel = bm._mlm_corrupt(clean, 512, eod=0, eod_mask_loss=True, gen=g)
+    n = math.ceil(0.15 * 200)
+    assert all(n - 1 <= int(s) <= n for s in sel.sum(1)) and float(sel[:, 50].sum()) == 0
+    changed = out != clean
+    assert bool((changed <= sel.bool()).all()) and float((out[sel.bool()] == bm.MASK_TOKEN_ID).float().mean()) > 0.6
+    out, sel = bm._span_corrupt(clean.clone(), 512, randomize=False, gen=g)
+    assert all(10 <= int(s) <= 30 for s in sel.sum(1)) and bool((out[sel.bool()] == bm.MASK_TOKEN_ID).all())
+    assert bool((out[~sel.bool()] == bm._dna_only(clean)[~sel.bool()]).all())
+    runs = (sel[:, 1:] > sel[:, :-1]).sum(1) + sel[:, 0]
+    assert all(int(r) >= 2 for r in runs)                                # several spans, not one block
+    out, sel, t = bm._oadm_corrupt(clean, gen=g)
+    assert torch.equal(sel.sum(1).long(), (200 - t + 1).clamp(max=200)) and bool((out[sel.bool()] == bm.MASK_TOKEN_ID).all())
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for strategy in ("MLM", "SPAN", "SPAN_R", "OADM"):
+        cfg = GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")],
+                                     {"global_num_gpus": 1, "pretraining_strategy": strategy, "mask_loss_control_tags": True})
+        assert cfg.causal is False
+        tr = Trainer(cfg, load=False)
+        d = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)} for i in range(64)])
+        losses = [float(tr.train_step(d)) for _ in range(4)]
+        assert all(l == l for l in losses) and losses[-1] < losses[0], (strategy, losses)
