@@ -58,20 +58,26 @@ def lowercase_weights(labels, loss_mask, lowercase_weight: float = 0.1):
 
 def reweighted_cross_entropy(logits, labels, loss_mask, lowercase_weight: float = 0.1, normalize_per_batch: bool = True,
                              vocab_parallel: bool = False):
-    losses = vocab_parallel_cross_entropy(logits, labels) if vocab_parallel else ops.cross_entropy(logits, labels)
+    # the target is the upper-case letter (the model never sees case); the case of the label only sets the weight
+    lower = (labels >= 97) & (labels <= 122)
+    target = torch.where(lower, labels - 32, labels)
+    losses = vocab_parallel_cross_entropy(logits, target) if vocab_parallel else ops.cross_entropy(logits, target)
     if normalize_per_batch:
         w = lowercase_weights(labels, loss_mask, lowercase_weight)
     else:
-        lower = (labels >= 97) & (labels <= 122)
         w = torch.where(lower, lowercase_weight, 1.0) * loss_mask.float()
     return _masked_mean(losses, w, loss_mask)
 
 
-def oadm_loss(logits, labels, loss_mask, t_frac):
-    """Order-agnostic diffusion: CE on masked positions reweighted by 1/(number masked) per row."""
-    losses = ops.cross_entropy(logits, labels) * loss_mask.float()
-    n_masked = loss_mask.float().sum(-1).clamp(min=1.0)
-    return (losses.sum(-1) / n_masked).mean()
+def oadm_loss(logits, labels, loss_mask, t_frac=None, pad_token: int = 1):
+    """Order-agnostic autoregressive diffusion (reference: savanna/model/backbone.py:151-171): the cross-entropy of a
+    row's masked positions is weighted by (non-pad tokens of the row) / (masked positions of the row), the term of the
+    diffusion bound for the row's time step, and the batch is normalised by its number of masked positions."""
+    mask = loss_mask.float()
+    losses = ops.cross_entropy(logits, labels).float() * mask
+    n_masked = mask.sum(-1).clamp(min=1.0)
+    non_pad = (labels != pad_token).sum(-1).float()
+    return ((non_pad / n_masked)[:, None] * losses).sum() / mask.sum().clamp(min=1.0)
 
 
 def dpo_loss(policy_chosen_logps, policy_rejected_logps, ref_chosen_logps, ref_rejected_logps, beta: float = 1.0):
@@ -84,5 +90,8 @@ def dpo_loss(policy_chosen_logps, policy_rejected_logps, ref_chosen_logps, ref_r
 
 
 def sequence_logps(logits, labels, loss_mask):
+    """Per-row log-probability as the reference's preference loss measures it (savanna/model/backbone.py:190-197): the
+    masked token log-probabilities summed and divided by the row length (a mean over all positions, the masked-out ones
+    counting as zero).  The stored reference log-probabilities have to be on the same scale."""
     lp = -ops.cross_entropy(logits, labels)
-    return (lp * loss_mask.float()).sum(-1)
+    return (lp * loss_mask.float()).sum(-1) / float(lp.shape[-1])

@@ -187,3 +187,36 @@ def test_freeform_filter_position_embeddings_and_normalisation():
         ParallelImplicitFreeformFilter(6, emb_dim=9, pos_emb="random_fourier")
     g = ParallelImplicitFreeformFilter(6, emb_dim=9, order=16, L_cache=64)(32)
     assert g.shape == (6, 32) and float(g[:, -1].abs().max()) < float(g[:, 0].abs().max()) + 1.0
+
+
+def test_losses_match_their_plain_statements():
+    """Lower-case reweighting (target upper-cased, weight from the case), diffusion reweighting and the preference loss's
+    per-row log-probability, each against a few lines of plain PyTorch."""
+    import torch
+    import torch.nn.functional as F
+    from savanna_b200.models import losses
+    torch.manual_seed(0)
+    B, L, V = 3, 12, 128
+    logits = torch.randn(B, L, V)
+    labels = torch.randint(65, 91, (B, L))
+    lower = torch.rand(B, L) < 0.4
+    labels = torch.where(lower, labels + 32, labels)
+    mask = (torch.rand(B, L) < 0.8).float()
+    upper = torch.where(lower, labels - 32, labels)
+    ce = F.cross_entropy(logits.view(-1, V), upper.view(-1), reduction="none").view(B, L)
+    w = torch.where(lower, 0.1, 1.0) * mask
+    got = losses.reweighted_cross_entropy(logits, labels, mask, 0.1, normalize_per_batch=False)
+    assert torch.allclose(got, (ce * w).sum() / mask.sum(), atol=1e-6)
+    wn = mask.sum() * w / w.sum()
+    got = losses.reweighted_cross_entropy(logits, labels, mask, 0.1, normalize_per_batch=True)
+    assert torch.allclose(got, (ce * wn).sum() / mask.sum(), atol=1e-6)
+    ce_plain = F.cross_entropy(logits.view(-1, V), labels.view(-1), reduction="none").view(B, L)
+    labels_p = labels.clone()
+    labels_p[0, -3:] = 1                                                  # pad tokens shorten row 0
+    ce_p = F.cross_entropy(logits.view(-1, V), labels_p.view(-1), reduction="none").view(B, L)
+    want = sum((labels_p[b] != 1).sum() / mask[b].sum() * (ce_p[b] * mask[b]).sum() for b in range(B)) / mask.sum()
+    assert torch.allclose(losses.oadm_loss(logits, labels_p, mask), want, atol=1e-5)
+    lp = losses.sequence_logps(logits, labels, mask)
+    assert torch.allclose(lp, -(ce_plain * mask).mean(-1), atol=1e-6)
+    loss, _, _ = losses.dpo_loss(lp[:1], lp[1:2], torch.tensor([-1.0]), torch.tensor([-2.0]), beta=0.5)
+    assert torch.allclose(loss, -F.logsigmoid(0.5 * ((lp[0] + 1.0) - (lp[1] + 2.0))), atol=1e-6)
