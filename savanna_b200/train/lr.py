@@ -27,8 +27,10 @@ class AnnealingLR:
         self.step(self.num_iters)
 
     def factor(self) -> float:
-        it = min(self.num_iters, self.end_iter)
-        if self.warmup_iter > 0 and it <= self.warmup_iter:
+        # as the reference counts (learning_rates.py:47-52): the step count saturates at end_iter - warmup_iter, so the
+        # decay runs over end_iter - 2 * warmup_iter steps after the warm-up and then holds its value
+        it = min(self.num_iters, self.end_iter - self.warmup_iter)
+        if self.warmup_iter > 0 and self.num_iters <= self.warmup_iter:
             return it / self.warmup_iter
         it = it - self.warmup_iter
         if self.decay_style == "linear":
@@ -41,8 +43,13 @@ class AnnealingLR:
             f = 1.0
         return f
 
+    def in_warmup(self) -> bool:
+        return self.warmup_iter > 0 and self.num_iters <= self.warmup_iter
+
     def get_lr(self, base: float = None) -> float:
         base = self.start_lr if base is None else base
+        if self.in_warmup():
+            return base * self.factor()             # the floor applies to the decay only: warm-up starts at zero
         return max(base * self.factor(), self.min_lr)
 
     def step(self, step_num: int = None) -> None:

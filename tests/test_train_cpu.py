@@ -237,3 +237,33 @@ def test_masked_strategies_follow_their_rules_and_train():
         d = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)} for i in range(64)])
         losses = [float(tr.train_step(d)) for _ in range(4)]
         assert all(l == l for l in losses) and losses[-1] < losses[0], (strategy, losses)
+
+
+def test_annealing_lr_values_including_the_saturated_tail():
+    import math
+    from savanna_b200.train.lr import AnnealingLR
+
+    class Opt:
+        param_groups = [{"lr": 0.0}, {"lr": 0.0, "fixed_lr": True, "lr_mult": 0.5}]
+    s = AnnealingLR(Opt, start_lr=1.0, warmup_iter=10, total_iters=100, decay_style="cosine", min_lr=0.1)
+
+    def want(i):
+        n = min(i, 90)
+        if i <= 10:
+            return max(n / 10, 0.0) if i else 0.0
+        return max(0.5 * (math.cos(math.pi * (n - 10) / 100) + 1), 0.1)
+    for i in (0, 1, 5, 10, 11, 50, 90, 95, 100, 150):
+        s.step(i)
+        got = Opt.param_groups[0]["lr"]
+        ref = want(i) if i > 10 else i / 10
+        assert abs(got - ref) < 1e-12, (i, got, ref)
+        assert abs(Opt.param_groups[1]["lr"] - 0.5 * s.factor()) < 1e-12
+    s.step(95)
+    a = Opt.param_groups[0]["lr"]
+    s.step(100)
+    assert Opt.param_groups[0]["lr"] == a                     # held over the last `warmup_iter` steps
+    for style, f in (("linear", lambda n: (100 - n) / 100), ("exponential", lambda n: math.exp(-0.693 * n / 100)),
+                     ("constant", lambda n: 1.0)):
+        t = AnnealingLR(Opt, 2.0, 10, 100, style, min_lr=0.0)
+        t.step(60)
+        assert abs(Opt.param_groups[0]["lr"] - 2.0 * f(50)) < 1e-12
