@@ -56,7 +56,7 @@ class AnnealingLR:
         self.num_iters = self.num_iters + 1 if step_num is None else step_num
         for g in self.optimizer.param_groups:
             if g.get("fixed_lr", False):
-                g["lr"] = max(self.start_lr * g.get("lr_mult", 1.0) * self.factor(), 0.0)
+                g["lr"] = self.get_lr(self.start_lr * g.get("lr_mult", 1.0))     # same shape and floor, own peak
             else:
                 g["lr"] = self.get_lr()
 
