@@ -178,7 +178,17 @@ class Backbone(nn.Module):
 def build_model(cfg, device=None) -> Backbone:
     if cfg.padded_vocab_size is None:
         raise ValueError("padded_vocab_size is unset: build the tokenizer first (cfg.build_tokenizer())")
-    return Backbone(cfg, device=device)
+    model = Backbone(cfg, device=device)
+    if cfg.use_mup and (device is None or torch.device(device).type != "meta"):
+        # muP initialisation: tensors whose two dimensions grow with the width start 1 / sqrt(width multiplier) smaller
+        # (what `mup.init.normal_` does in the reference's re-initialisation pass, savanna/training.py:1053-1056)
+        ids, mult = _mup_matrix_like(model, cfg)
+        if mult != 1.0:
+            with torch.no_grad():
+                for p in model.parameters():
+                    if id(p) in ids:
+                        p.mul_(mult ** -0.5)
+    return model
 
 
 def _partitioned_saved_tensors(tp: int, rank: int, group):
@@ -244,20 +254,14 @@ def _mup_shapes_path(cfg):
     return None
 
 
-def mup_param_groups(groups, model: nn.Module, cfg):
-    """Per-group learning rates of the maximal-update parametrisation (the reference's MuAdam / MuSGD,
-    savanna/training.py:1065-1185 with the `mup` package): parameters whose two dimensions both grow with the model
-    width ("matrix-like": the projection and MLP weights) are separated from the rest ("vector-like": embeddings,
-    norms, biases, filters).  Adam-type optimizers divide the matrix-like learning rate by the width multiplier
-    `mup_width_scale` (and multiply a coupled weight decay by it); SGD multiplies the vector-like learning rate by it.
-    With a `base_shapes_file` on disk the classification and the multiplier come from that file instead of from
-    parameter names and `mup_width_scale`.  A group that was split keeps its name with a `_matrix` suffix for the matrix-like half."""
+def _mup_matrix_like(model: nn.Module, cfg):
+    """(ids of the matrix-like parameters, width multiplier).  With a base-shapes file on disk both come from it: matrix-
+    like = two dimensions that grow with the width, multiplier = how much wider this model is than the base
+    (train/mup_shapes.py).  Without one: the projection and MLP weights by name, and `mup_width_scale`."""
     matrix_ids = set()
     mult = float(cfg.mup_width_scale)
     shapes_file = _mup_shapes_path(cfg)
     if shapes_file is not None:
-        # a base-shapes file says, per parameter, which dimensions grow with the width and by how much this model is
-        # wider than the base: matrix-like = two growing dimensions (train/mup_shapes.py)
         from ..train import mup_shapes
         widths = mup_shapes.width_multipliers(model, mup_shapes.load_base_shapes(shapes_file))
         mults = set()
@@ -276,6 +280,18 @@ def mup_param_groups(groups, model: nn.Module, cfg):
             if p.dim() == 2 and name.endswith(".weight") and any(k in name for k in (
                     "dense_projection.", "mixer.dense.", ".mlp.w1.", ".mlp.w2.", ".mlp.w3.", ".mlp.dense_", ".mlp.w12")):
                 matrix_ids.add(id(p))
+    return matrix_ids, mult
+
+
+def mup_param_groups(groups, model: nn.Module, cfg):
+    """Per-group learning rates of the maximal-update parametrisation (the reference's MuAdam / MuSGD,
+    savanna/training.py:1065-1185 with the `mup` package): parameters whose two dimensions both grow with the model
+    width ("matrix-like": the projection and MLP weights) are separated from the rest ("vector-like": embeddings,
+    norms, biases, filters).  Adam-type optimizers divide the matrix-like learning rate by the width multiplier
+    `mup_width_scale` (and multiply a coupled weight decay by it); SGD multiplies the vector-like learning rate by it.
+    With a `base_shapes_file` on disk the classification and the multiplier come from that file instead of from
+    parameter names and `mup_width_scale`.  A group that was split keeps its name with a `_matrix` suffix for the matrix-like half."""
+    matrix_ids, mult = _mup_matrix_like(model, cfg)
     sgd = str(cfg.optimizer_type).lower() in ("sgd", "musgd")
     decoupled = bool(((cfg.optimizer or {}).get("params", {}) or {}).get("adam_w_mode", True))
     out = []

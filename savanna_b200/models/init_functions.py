@@ -27,7 +27,7 @@ def scaled_init_method_normal(sigma, num_layers):
 
 def orthogonal_init_method(n_layers=1):
     def f(t):
-        return torch.nn.init.orthogonal_(t, gain=math.sqrt(2.0 / n_layers) if n_layers > 1 else 1.0)
+        return torch.nn.init.orthogonal_(t, gain=math.sqrt(2.0 / n_layers))      # sqrt(2) for the unscaled method
     return f
 
 

@@ -16,7 +16,7 @@ import math
 from typing import Dict, Iterable, List, Optional
 
 
-def _records_for_width(paths, over, width: int, use_mup: bool, steps: int, seed: int) -> List[Dict]:
+def _records_for_width(paths, over, width: int, use_mup: bool, steps: int, seed: int, base_width: Optional[int] = None) -> List[Dict]:
     import torch
     from ..config import GlobalConfig
     from ..data.synthetic import acgt_batch
@@ -26,6 +26,9 @@ def _records_for_width(paths, over, width: int, use_mup: bool, steps: int, seed:
     o = dict(over)
     o.update({"hidden_size": width, "use_mup": use_mup, "coord_check": False, "load": None, "save": None,
               "num_groups_hyena": width})
+    if base_width:
+        # the width multiplier of muP is this model's width over the narrowest one's (the base model of the sweep)
+        o["mup_width_scale"] = max(1, width // base_width)
     for k in ("num_groups_hyena_medium", "num_groups_hyena_short"):
         g = getattr(base, k, None)
         if g:
@@ -74,9 +77,11 @@ def coord_check(paths, over: Optional[Dict] = None, powers: Iterable[int] = rang
     over.setdefault("global_num_gpus", 1)
     heads = GlobalConfig.from_ymls(paths, dict(over)).num_attention_heads
     out: List[Dict] = []
+    powers = list(powers)
+    base_width = heads * (2 ** min(powers))
     for use_mup in (True, False):
         for p in powers:
-            out += _records_for_width(list(paths), over, heads * (2 ** p), use_mup, steps, seed)
+            out += _records_for_width(list(paths), over, heads * (2 ** p), use_mup, steps, seed, base_width)
     return out
 
 
