@@ -147,3 +147,152 @@ def test_explicit_single_decay_filter_follows_the_reference_law():
         h = f(Lc)
         assert torch.allclose(h, f.h * want, atol=1e-6)
         assert abs(float(f.h.detach().std()) - 1.0 / math.sqrt(Lc)) < 0.02        # h ~ N(0, 1/L_cache) as in the reference
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Functions of files that cannot be imported (they pull in DeepSpeed, requests, ...) are taken out of the source text by
+# name: the file is parsed, the wanted `def` / `class` nodes (methods included) are compiled unchanged in a namespace
+# that offers torch, math and whatever stand-ins the code asks for, and then called.
+
+
+def _extract(rel, names, namespace):
+    import ast
+    path = os.path.join(REF, *rel)
+    tree = ast.parse(open(path).read(), filename=path)
+    wanted = []
+    for node in ast.walk(tree):
+        if isinstance(node, (ast.FunctionDef, ast.ClassDef)) and node.name in names:
+            node.decorator_list = []                   # e.g. torch.jit.script: the plain function is what is compared
+            wanted.append(node)
+    assert {n.name for n in wanted} == set(names), (names, [n.name for n in wanted])
+    mod = ast.Module(body=sorted(wanted, key=lambda n: n.lineno), type_ignores=[])
+    ns = dict(namespace)
+    exec(compile(mod, path, "exec"), ns)
+    return ns
+
+
+def test_bidirectional_fftconv_matches_reference():
+    fc = _load("savanna_ref_fftconv_bi", "savanna", "ops", "fftconv.py")
+    torch.manual_seed(0)
+    B, D, L = 2, 6, 40
+    u = torch.randn(B, D, L)
+    k = torch.randn(1, 2 * D, L)                           # forward half and backward half along the channel dimension
+    bias = torch.randn(D)
+    want = fc.fftconv_func(u, k, bias, None, gelu=False, bidirectional=True)
+    got = ref.fft_bidirectional_conv(u.transpose(1, 2), k[0, :D], k[0, D:]).transpose(1, 2) + bias[None, :, None] * u
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+def test_annealing_lr_matches_reference():
+    from savanna_b200.train.lr import AnnealingLR
+    ns = _extract(("savanna", "learning_rates.py"), ["AnnealingLR"], {"math": math, "print_rank_0": lambda *a, **k: None})
+
+    class Opt:
+        def __init__(self):
+            self.param_groups = [{"lr": 0.0}]
+    for style in ("cosine", "linear", "exponential", "constant"):
+        for warm, total, floor in ((10, 100, 0.1), (0, 50, 0.0), (25, 60, 0.05)):
+            a, b = Opt(), Opt()
+            theirs = ns["AnnealingLR"](a, 1.0, warm, total, style, 0, min_lr=floor)
+            ours = AnnealingLR(b, 1.0, warm, total, style, 0, min_lr=floor)
+            for step in range(0, total + 20):
+                theirs.step(step)
+                ours.step(step)
+                assert abs(a.param_groups[0]["lr"] - b.param_groups[0]["lr"]) < 1e-12, (style, warm, total, step)
+
+
+def test_tag_loss_mask_matches_reference():
+    from savanna_b200.train.batch import mask_control_tags
+    ns = _extract(("savanna", "utils.py"), ["mask_control_tags", "mask_phylogenetic_tags"], {"torch": torch})
+    enc = lambda s: [0 if c == "$" else ord(c) for c in s]
+    rows = [
+        "ACGT|d__Bacteria;p__Firmicutes|ACGTACGT$ACGT@ACGTAC",
+        "teria;s__coli|ACGTACGTACGT#ACGT|d__Archaea;p__Eurya",
+        "ACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTACGTACG",
+        "ACGT$|d__B;c__X|ACGT$ACGT|r__Z|ACGTACGTACGTACGT|ACGT",
+        "|d__A;p__B|ACGTACGTACGTACGTACGTACGTACGT|d__C;p__D|AC",
+    ]
+    L = max(len(r) for r in rows)
+    tok = torch.tensor([enc(r.ljust(L, "A")) for r in rows])
+    want = ns["mask_control_tags"]((tok.clone(), torch.ones(tok.shape)), 0)
+    got = mask_control_tags(tok, torch.ones(tok.shape), eod=0)
+    assert torch.equal(got, want.float()), (got - want.float()).nonzero().tolist()
+    g = torch.Generator().manual_seed(1)
+    for _ in range(20):                                    # random rows over the alphabet that matters
+        alphabet = torch.tensor([65, 67, 71, 84, 124, 95, 59, 32, 64, 35, 0, 100])
+        tok = alphabet[torch.randint(0, len(alphabet), (4, 48), generator=g)]
+        tok[:, 0] = 65                                     # the loop's restart quirk needs an open tag before an eod at
+        want = ns["mask_control_tags"]((tok.clone(), torch.ones(tok.shape)), 0).float()
+        got = mask_control_tags(tok, torch.ones(tok.shape), eod=0)
+        # rows where a masked piece ends at an end-of-document token may differ by the reference's one-position restart
+        for b in range(4):
+            if not torch.equal(got[b], want[b]):
+                assert bool((tok[b] == 0).any()), (tok[b].tolist(), got[b].tolist(), want[b].tolist())
+                assert float((want[b] <= got[b]).float().mean()) == 1.0      # the quirk only ever masks more
+
+
+def test_losses_match_reference():
+    from savanna_b200.models import losses
+    import torch.nn.functional as F
+
+    class Mpu:
+        @staticmethod
+        def vocab_parallel_cross_entropy(logits, labels):
+            return F.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), reduction="none").view(labels.shape)
+
+        @staticmethod
+        def get_sequence_parallel_world_size():
+            return 1
+    up = _extract(("savanna", "utils.py"), ["make_upper_case"], {"torch": torch})
+    ns = _extract(("savanna", "model", "backbone.py"), ["cross_entropy", "reweighted_cross_entropy", "oadm_loss", "dpo_loss"],
+                  {"torch": torch, "mpu": Mpu, "make_upper_case": up["make_upper_case"]})
+    torch.manual_seed(0)
+    B, L, V = 4, 16, 128
+    logits = torch.randn(B, L, V)
+    labels = torch.randint(65, 91, (B, L))
+    lower = torch.rand(B, L) < 0.4
+    labels = torch.where(lower, labels + 32, labels)
+    mask = (torch.rand(B, L) < 0.8).float()
+    assert torch.allclose(losses.cross_entropy(logits, labels, mask), ns["cross_entropy"](logits, (labels, mask)), atol=1e-6)
+    for norm in (False, True):
+        want = ns["reweighted_cross_entropy"](logits, (labels.clone(), mask.clone()), lowercase_weight=0.1, normalize_per_batch=norm)
+        got = losses.reweighted_cross_entropy(logits, labels, mask, 0.1, normalize_per_batch=norm)
+        assert torch.allclose(got, want, atol=1e-6), (norm, got, want)
+    # the reference's oadm_loss cannot run: its cross_entropy(..., reduce=False) falls off the end and returns None
+    # (backbone.py:101-108), so the diffusion loss is pinned to its formula in tests/test_ops_reference.py instead
+    with pytest.raises(TypeError):
+        ns["oadm_loss"](logits, (labels, mask))
+    # preference pairs: rows [accepted..., rejected...], reference log-probabilities in the labels' last column
+    ref_lp = torch.tensor([-1.0, -2.0, -1.5, -0.5])
+    packed = torch.cat([labels.float(), ref_lp[:, None]], dim=1)
+    want = ns["dpo_loss"](logits, (packed, mask), beta=0.7)
+    mine = losses.sequence_logps(logits, labels, mask)
+    got, _, _ = losses.dpo_loss(mine[:2], mine[2:], ref_lp[:2], ref_lp[2:], beta=0.7)
+    assert torch.allclose(got, want, atol=1e-6), (got, want)
+
+
+def test_multihead_long_operator_matches_reference():
+    from einops import rearrange
+    ns = _extract(("savanna", "model", "operators", "hyena", "hyena.py"), ["multihead_forward"],
+                  {"torch": torch, "rearrange": rearrange, "_mul_sum": lambda y, q: (y * q).sum(dim=1),
+                   "log_norm": lambda *a, **k: None})
+    torch.manual_seed(0)
+    B, L, H, d = 2, 24, 3, 4
+    D = H * d
+
+    class Self:
+        group_dim, num_groups, use_flashfft, log_hyena_norms = d, H, False, False
+        conv_bias = torch.randn(H)
+    torch.distributed_get_rank = None
+    import torch.distributed as tdist
+    real = tdist.get_rank
+    tdist.get_rank = lambda *a, **k: 1
+    try:
+        x1, x2, v = torch.randn(B, D, L), torch.randn(B, D, L), torch.randn(B, D, L)
+        h = torch.randn(1, H, L)
+        want = ns["multihead_forward"](Self, x1, x2, v, h)                     # [B, D, L]
+    finally:
+        tdist.get_rank = real
+    feat = torch.stack([x1, x2, v], dim=-1).permute(0, 2, 1, 3).reshape(B, L, 3 * D)   # interleaved (channel, stream)
+    got = ref.hyena_multihead(feat, h[0], Self.conv_bias).transpose(1, 2)
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
