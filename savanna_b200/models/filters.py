@@ -128,67 +128,107 @@ class ParallelComplexModalFilter(nn.Module):
     filter = forward
 
 
+class _Sin(nn.Module):
+    """sin(freq * x) with one trainable frequency per feature (reference: savanna/model/activations.py:12-19)."""
+
+    def __init__(self, dim, w, device=None):
+        super().__init__()
+        self.freq = nn.Parameter(w * torch.ones(1, dim, device=device))
+
+    def forward(self, x):
+        return torch.sin(self.freq * x)
+
+
+class _FixedFourierEmbedding(nn.Module):
+    """Buffers `z` [1, L, emb_dim] = [t, Re e^{-i f w}, Im e^{-i f w}] and `t` [1, L, 1] in [0, 1]
+    (implicit_utils.py:12-38); w = 2 pi n / L, f = `bands` frequencies from 1e-4 to bands - 1."""
+
+    def __init__(self, emb_dim, seq_len, device=None):
+        super().__init__()
+        if emb_dim % 2 == 0 or emb_dim < 3:
+            raise ValueError("emb_dim must be odd and >= 3 (time + sine/cosine pairs)")
+        bands = (emb_dim - 1) // 2
+        t = torch.linspace(0, 1, seq_len, device=device)[None, :, None]
+        w = 2 * math.pi * torch.linspace(0, seq_len - 1, seq_len, device=device)[None, :, None] / seq_len
+        f = torch.linspace(1e-4, bands - 1, bands, device=device)[None, None]
+        self.register_buffer("t", t)
+        self.register_buffer("z", torch.cat([t, torch.cos(f * w), -torch.sin(f * w)], dim=-1))
+
+    def forward(self, L):
+        return self.z[:, :L], self.t[:, :L]
+
+
+class _RandomFourierEmbedding(nn.Module):
+    """Learned frequencies drawn from N(0, 2 pi omega_0): features [cos(w t), sin(w t)] on t in [-1, 1]; the decay
+    window sees (t + 1) / 2 (implicit_utils.py:39-67)."""
+
+    def __init__(self, emb_dim, seq_len, omega_0, device=None):
+        super().__init__()
+        if emb_dim % 2:
+            raise ValueError(f"emb_dim must be even for the random Fourier embedding (got {emb_dim})")
+        self.linear = nn.Linear(1, emb_dim // 2, bias=False, device=device)
+        with torch.no_grad():
+            self.linear.weight.normal_(0.0, 2 * math.pi * omega_0)
+        self.register_buffer("t", torch.linspace(-1, 1, seq_len, device=device)[None, :, None])
+
+    def forward(self, L):
+        out = self.linear(self.t[:, :L])
+        return torch.cat([torch.cos(out), torch.sin(out)], dim=-1), (self.t[:, :L] + 1) / 2
+
+
+class _ExponentialModulation(nn.Module):
+    """h * exp(-t |weight|): per-channel decay rates, spread linearly between a slow and a fast one that reach 1e-2 at
+    `slow_decay` / `fast_decay` of the sequence; trainable, as in the reference (implicit_utils.py:70-111)."""
+
+    def __init__(self, d_model, fast_decay=0.3, slow_decay=1.5, target=1e-2, device=None):
+        super().__init__()
+        max_decay, min_decay = math.log(target) / fast_decay, math.log(target) / slow_decay
+        self.weight = nn.Parameter(torch.linspace(min_decay, max_decay, d_model, device=device)[None, None])
+
+    def forward(self, t, x):
+        return x * torch.exp(-t * self.weight.abs())
+
+
 class ParallelImplicitFreeformFilter(nn.Module):
     """Sine-activated MLP over a positional embedding, modulated by an exponential decay window
-    (parametrization/implicit_freeform.py:15-122, implicit_utils.py:12-111).
+    (parametrization/implicit_freeform.py:15-122).  Sub-module and parameter names are the reference's, so its
+    checkpoints load: `pos_emb.{z,t}` (or `pos_emb.linear.weight`), `act.freq`, `implicit_filter.<2i>.{weight,bias}`
+    (the shared activation sits at the odd positions), `final_filter.weight`, `modulation.weight`,
+    `post_modulation_norm.*`.
 
-    pos_emb "fourier_fixed": fixed features [t, cos(2 pi f t), sin(2 pi f t)] (emb_dim odd);  "random_fourier": a
-    learned frequency vector drawn from N(0, 2 pi omega_0), features [cos(w t), sin(w t)] on t in [-1, 1] (emb_dim
-    even, parameter `pos_emb.linear.weight`).  `normalized` applies a LayerNorm over the channels after the decay
-    window (`post_modulation_norm`)."""
+    pos_emb "fourier_fixed": fixed complex-exponential features (emb_dim odd); "random_fourier": learned frequencies
+    (emb_dim even, scale `omega_0`).  `normalized` applies a LayerNorm over the channels after the decay window."""
 
     def __init__(self, d_model, emb_dim=33, order=64, num_inner_mlps=2, w=14, L_cache=8192, fast_decay=0.3,
                  slow_decay=1.2, modulate=True, pos_emb="fourier_fixed", omega_0=1.0, normalized=False, device=None):
         super().__init__()
         self.w, self.modulate, self.pos_emb_type = w, modulate, pos_emb
         if pos_emb == "fourier_fixed":
-            if emb_dim % 2 == 0 or emb_dim < 3:
-                raise ValueError("emb_dim must be odd and >= 3 (time + sine/cosine pairs)")
-            bands = (emb_dim - 1) // 2
-            t = torch.linspace(0, 1, L_cache, device=device)[:, None]
-            tr = torch.linspace(0, L_cache - 1, L_cache, device=device)[:, None]
-            f = torch.linspace(1e-4, bands - 1, bands, device=device)[None]
-            ang = 2 * math.pi * tr * f / L_cache
-            self.register_buffer("z", torch.cat([t, torch.cos(ang), torch.sin(ang)], dim=-1))
-            self.register_buffer("t", t)
+            self.pos_emb = _FixedFourierEmbedding(emb_dim, L_cache, device=device)
         elif pos_emb == "random_fourier":
-            if emb_dim % 2:
-                raise ValueError(f"emb_dim must be even for the random Fourier embedding (got {emb_dim})")
-            self.pos_emb = nn.Module()
-            self.pos_emb.linear = nn.Linear(1, emb_dim // 2, bias=False, device=device)
-            with torch.no_grad():
-                self.pos_emb.linear.weight.normal_(0.0, 2 * math.pi * omega_0)
-            self.register_buffer("t_sym", torch.linspace(-1, 1, L_cache, device=device)[:, None])
-            self.register_buffer("t", (self.t_sym + 1) / 2)
+            self.pos_emb = _RandomFourierEmbedding(emb_dim, L_cache, omega_0, device=device)
         else:
             raise ValueError(f"hyena_pos_emb {pos_emb!r} unknown (fourier_fixed | random_fourier)")
-        layers = [nn.Linear(emb_dim, order, device=device)]
+        self.act = _Sin(order, w, device=device)
+        layers = [nn.Linear(emb_dim, order, device=device), self.act]
         for _ in range(num_inner_mlps):
-            layers.append(nn.Linear(order, order, device=device))
-        layers.append(nn.Linear(order, d_model, bias=False, device=device))
-        self.layers = nn.ModuleList(layers)
-        self.freq = nn.Parameter(w * torch.ones(1, order, device=device))
-        max_decay = math.log(1e-2) / fast_decay
-        min_decay = math.log(1e-2) / slow_decay
-        self.register_buffer("deltas", torch.linspace(min_decay, max_decay, d_model, device=device)[None])
+            layers += [nn.Linear(order, order, device=device), self.act]
+        self.implicit_filter = nn.Sequential(*layers)
+        self.final_filter = nn.Linear(order, d_model, bias=False, device=device)
+        nn.init.xavier_normal_(self.final_filter.weight, gain=1)
+        self.modulation = _ExponentialModulation(d_model, fast_decay, slow_decay, device=device)
         self.post_modulation_norm = nn.LayerNorm(d_model, device=device) if normalized else None
         for q in self.parameters():
             q.is_filter_param = True
 
     def forward(self, L: int):
-        if self.pos_emb_type == "random_fourier":
-            ang = self.pos_emb.linear(self.t_sym[:L])
-            x = torch.cat([torch.cos(ang), torch.sin(ang)], dim=-1)
-        else:
-            x = self.z[:L]
-        for lin in self.layers[:-1]:
-            x = torch.sin(self.freq * lin(x))
-        h = self.layers[-1](x)
+        z, t = self.pos_emb(L)
+        h = self.final_filter(self.implicit_filter(z))
         if self.modulate:
-            h = h * torch.exp(-self.t[:L] * self.deltas.abs())
+            h = self.modulation(t, h)
         if self.post_modulation_norm is not None:
             h = self.post_modulation_norm(h)
-        return h.transpose(0, 1).float()
+        return h[0].transpose(0, 1).float()
 
     filter = forward
 

@@ -296,3 +296,38 @@ def test_multihead_long_operator_matches_reference():
     feat = torch.stack([x1, x2, v], dim=-1).permute(0, 2, 1, 3).reshape(B, L, 3 * D)   # interleaved (channel, stream)
     got = ref.hyena_multihead(feat, h[0], Self.conv_bias).transpose(1, 2)
     assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+def test_freeform_filter_pieces_match_reference():
+    """Positional embedding, decay window and sine activation of the implicit free-form filter against the reference's
+    classes; the parameter names are the ones its checkpoints hold."""
+    import torch.nn as nn
+    from savanna_b200.models.filters import ParallelImplicitFreeformFilter
+
+    class Mpu:
+        get_model_parallel_rank = staticmethod(lambda: 0)
+        get_model_parallel_world_size = staticmethod(lambda: 1)
+
+    class Cfg:
+        params_dtype = torch.float32
+    ns = _extract(("savanna", "model", "operators", "hyena", "parametrization", "implicit_utils.py"),
+                  ["PositionalEmbedding", "ParallelExponentialModulation"],
+                  {"torch": torch, "math": math, "nn": nn, "Parameter": nn.Parameter, "mpu": Mpu,
+                   "get_dtype_from_string": lambda s: torch.float32})
+    d, emb, order, L = 6, 9, 16, 64
+    torch.manual_seed(0)
+    ours = ParallelImplicitFreeformFilter(d, emb_dim=emb, order=order, num_inner_mlps=2, w=14, L_cache=L, fast_decay=0.3,
+                                          slow_decay=1.2)
+    pe = ns["PositionalEmbedding"](emb, L, "float32")
+    assert torch.allclose(ours.pos_emb.z, pe.z, atol=1e-6) and torch.allclose(ours.pos_emb.t, pe.t)
+    mod = ns["ParallelExponentialModulation"](Cfg, d, d, 0, fast_decay_pct=0.3, slow_decay_pct=1.2)
+    assert torch.allclose(ours.modulation.weight, mod.weight, atol=1e-6)
+    z, t = pe(48)
+    x = z
+    for i, layer in enumerate(ours.implicit_filter):
+        x = layer(x) if isinstance(layer, nn.Linear) else torch.sin(ours.act.freq * x)
+    want = mod(t, ours.final_filter(x))[0].transpose(0, 1)
+    assert torch.allclose(ours(48), want, atol=1e-4)       # sines of large arguments amplify the 1e-7 differences of z
+    keys = set(ours.state_dict())
+    assert {"pos_emb.z", "pos_emb.t", "act.freq", "implicit_filter.0.weight", "implicit_filter.0.bias",
+            "implicit_filter.2.weight", "implicit_filter.4.bias", "final_filter.weight", "modulation.weight"} <= keys
