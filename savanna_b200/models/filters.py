@@ -78,52 +78,88 @@ class ImplicitModalFilter(nn.Module):
     filter = forward
 
 
-class ImplicitRealModalFilter(nn.Module):
-    """h[d,t] = sum_o residue[d,o] * pole[d,o]^t with real poles in (r_min, r_max)
-    (parametrization/implicit_modal.py:11-83)."""
+def _tp_slice_dim(full: torch.Tensor, dim: int) -> torch.Tensor:
+    """As `_tp_slice`, along another dimension."""
+    tp, rank = state.get_model_parallel_world_size(), state.get_model_parallel_rank()
+    return full.chunk(tp, dim=dim)[rank].contiguous() if tp > 1 else full
 
-    def __init__(self, d_model, order=64, L_cache=None, r_min=0.5, r_max=0.99, residue_factors=3, pole_factors=3,
+
+class ImplicitRealModalFilter(nn.Module):
+    """Real decaying modes with factored poles and residues (reference: parametrization/implicit_modal.py:11-83):
+
+        h[d, t] = sum_o (prod_f R[o, d, f]) * pole[o, d] ^ (dt[o, d] * t),   pole = exp(-exp(prod_f p[o, d, f]))
+
+    with dt clamped to [dt_min, dt_max] and t = linspace(0, L, L) (L points from 0 to L inclusive, the reference's time
+    grid).  Parameters as in the reference: `dt` [order, d], `p` [order, d, pole_factors] (one draw per mode, shared by
+    the channels at start), `R` [order, d, residue_factors] ~ N(0, 1 / order), and the unused `residues_norm`."""
+
+    def __init__(self, d_model, order=64, L_cache=None, dt_min=0.001, dt_max=0.1, residue_factors=4, pole_factors=4,
                  device=None):
         super().__init__()
-        self.order = order
+        self.order, self.d_model, self.dt_min, self.dt_max = order, d_model, dt_min, dt_max
         tp_ = state.get_model_parallel_world_size()
-        poles = _tp_slice(torch.rand(d_model * tp_, order, device=device)) * (r_max - r_min) + r_min
-        self.log_poles = nn.Parameter(poles.log())
-        self.residues = nn.Parameter(_tp_slice(torch.randn(d_model * tp_, order, device=device)) / math.sqrt(order))
-        self.log_poles.is_filter_param = True
-        self.residues.is_filter_param = True
+        dt = torch.rand(order, d_model * tp_, device=device) * (dt_max - dt_min) + dt_min
+        self.dt = nn.Parameter(_tp_slice_dim(dt, 1))
+        start = torch.randn(order, pole_factors, device=device)
+        self.p = nn.Parameter(start[:, None, :].repeat(1, d_model, 1))
+        R = torch.randn(order, d_model * tp_, residue_factors, device=device) / math.sqrt(order)
+        self.R = nn.Parameter(_tp_slice_dim(R, 1))
+        self.residues_norm = nn.LayerNorm(d_model, device=device)
+        for q in self.parameters():
+            q.is_filter_param = True
 
     def forward(self, L: int):
-        t = torch.arange(L, device=self.log_poles.device, dtype=torch.float32)
-        return (self.residues.float().unsqueeze(-1) * torch.exp(self.log_poles.float().unsqueeze(-1) * t)).sum(1)
+        R = self.R.float().prod(dim=-1)
+        dt = torch.clamp(self.dt.float(), min=self.dt_min, max=self.dt_max)[..., None]
+        log_pole = -torch.exp(self.p.float().prod(dim=-1))          # log of the pole, without forming a pole that underflows
+        t = torch.linspace(0, L, L, device=R.device)[None, None]
+        return torch.sum(R.unsqueeze(-1) * torch.exp(t * dt * log_pole.unsqueeze(-1)), dim=0)
 
     filter = forward
 
 
+class _ComplexModalParameters(nn.Module):
+    """Holder of the complex modal filter's parameters under the reference's names (`inner_cls.*`,
+    parametrization/implicit_complex.py:11-30): C and B as real views of complex tensors, A = -exp(inv_A_real) + i A_imag."""
+
+    def __init__(self, A, B, C, log_dt):
+        super().__init__()
+        self.C = nn.Parameter(torch.view_as_real(C.conj().resolve_conj()))
+        self.log_dt = nn.Parameter(log_dt)
+        self.inv_A_real = nn.Parameter(torch.log(-A.real))
+        self.A_imag = nn.Parameter(A.imag)
+        self.B = nn.Parameter(torch.view_as_real(B.conj().resolve_conj()))
+
+
 class ParallelComplexModalFilter(nn.Module):
-    """S4D-style complex diagonal filter: h[t] = Re( sum_o C_o exp(dt*A_o t) * (exp(dt*A_o)-1)/A_o )
-    (parametrization/implicit_complex.py:35-97)."""
+    """Complex diagonal modes (reference: parametrization/implicit_complex.py:35-97):
+
+        h[d, t] = 2 Re sum_n C[d, n] exp(dt[d] * A[d, n] * t),   A = -exp(inv_A_real) + i A_imag
+
+    started at A = -1/2 + i pi n, dt log-uniform in [dt_min, dt_max], C complex normal; B is carried (all ones) and, as
+    in the reference, does not enter the filter."""
 
     def __init__(self, d_model, order=64, dt_min=0.001, dt_max=0.1, device=None):
         super().__init__()
+        self.d_model, self.order = d_model, order
         half = max(1, order // 2)
-        log_dt = torch.rand(d_model, device=device) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min)
-        self.log_dt = nn.Parameter(log_dt)
-        self.C = nn.Parameter(torch.view_as_real(torch.randn(d_model, half, dtype=torch.cfloat, device=device)))
-        self.log_A_real = nn.Parameter(torch.log(0.5 * torch.ones(d_model, half, device=device)))
-        self.A_imag = nn.Parameter(math.pi * torch.arange(half, device=device, dtype=torch.float32).repeat(d_model, 1))
-        for q in (self.log_dt, self.C, self.log_A_real, self.A_imag):
+        tp_ = state.get_model_parallel_world_size()
+        log_dt = _tp_slice(torch.rand(d_model * tp_, device=device)) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min)
+        A = -0.5 * torch.ones(d_model, half, device=device) + 1j * math.pi * torch.arange(half, device=device).repeat(d_model, 1)
+        B = torch.ones(d_model, half, dtype=torch.cfloat, device=device)
+        C = _tp_slice_dim(torch.randn(1, d_model * tp_, half, dtype=torch.cfloat, device=device), 1)
+        self.inner_cls = _ComplexModalParameters(A, B, C, log_dt)
+        for q in self.parameters():
             q.is_filter_param = True
 
     def forward(self, L: int):
-        dt = torch.exp(self.log_dt.float())
-        C = torch.view_as_complex(self.C.float())
-        A = -torch.exp(self.log_A_real.float()) + 1j * self.A_imag.float()
+        m = self.inner_cls
+        dt = torch.exp(m.log_dt.float())
+        C = torch.view_as_complex(m.C.float().contiguous())[0]                     # [d, n]
+        A = -torch.exp(m.inv_A_real.float()) + 1j * m.A_imag.float()
         dtA = A * dt.unsqueeze(-1)
         t = torch.arange(L, device=dt.device)
-        K = dtA.unsqueeze(-1) * t
-        Cb = C * (torch.exp(dtA) - 1.0) / A
-        return 2 * torch.einsum("dn,dnl->dl", Cb, torch.exp(K)).real
+        return 2 * torch.einsum("dn,dnl->dl", C, torch.exp(dtA.unsqueeze(-1) * t)).real
 
     filter = forward
 
@@ -244,8 +280,8 @@ def build_filter(cfg, operator_type: str, num_groups: int, device=None) -> nn.Mo
         return ImplicitModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length, cfg.modal_gamma_min,
                                    cfg.modal_gamma_max, device=device)
     if cls == "implicit_real_modal":
-        return ImplicitRealModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length, cfg.hyena_filter_r_min,
-                                       cfg.hyena_filter_r_max, cfg.modal_residue_factors, cfg.modal_pole_factors,
+        return ImplicitRealModalFilter(num_groups, cfg.hyena_filter_order, cfg.seq_length,
+                                       residue_factors=cfg.modal_residue_factors, pole_factors=cfg.modal_pole_factors,
                                        device=device)
     # a two-sided (`bidirectional`) operator asks its filter for a forward and a backward half: twice the rows
     two_sided = 2 if cfg.bidirectional and operator_type == "hyena" else 1

@@ -12,7 +12,10 @@ _RULES = [
     (r"mixer\.dense_projection\.bias$", 0),
     (r"hyena_proj_conv\.short_conv_weight$", 0),
     (r"mixer\.mixer\.conv_bias$", 0),
-    (r"mixer\.mixer\.filter\.(h|decay|gamma|R|p|log_poles|residues)$", 0),
+    (r"mixer\.mixer\.filter\.(h|decay|gamma|R|p)$", 0),           # 3-d R / p of the real modal filter: see partition_dim
+    (r"mixer\.mixer\.filter\.dt$", 1),
+    (r"mixer\.mixer\.filter\.inner_cls\.(log_dt|inv_A_real|A_imag|B)$", 0),
+    (r"mixer\.mixer\.filter\.inner_cls\.C$", 1),
     (r"mixer\.mixer\.filter\.t$", None),
     (r"mixer\.mixer\.short_conv\.short_conv_weight$", 0),
     (r"rotary_emb\.inv_freq$", None),
@@ -33,7 +36,11 @@ _RULES = [
 ]
 
 
-def partition_dim(key: str) -> Optional[int]:
+def partition_dim(key: str, ndim: Optional[int] = None) -> Optional[int]:
+    """`ndim` (the tensor's rank, when the caller has it) tells the factored real modal filter's `R` / `p`
+    [order, channels, factors], split along dimension 1, from the modal filter's [channels, order]."""
+    if ndim == 3 and re.search(r"mixer\.mixer\.filter\.(R|p)$", key):
+        return 1
     for pat, dim in _RULES:
         if re.search(pat, key):
             return dim

@@ -50,8 +50,8 @@ def load_shards(step_dir: str) -> List[Dict]:
 def merge_module(shards: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
     out = {}
     for k in shards[0]:
-        d = partition_dim(k)
         ts = [s[k] for s in shards]
+        d = partition_dim(k, ts[0].dim() if isinstance(ts[0], torch.Tensor) else None)
         if d is None or not isinstance(ts[0], torch.Tensor) or ts[0].dim() == 0 or len(ts) == 1:
             out[k] = ts[0]
         else:
@@ -62,7 +62,7 @@ def merge_module(shards: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tenso
 def split_module(full: Dict[str, torch.Tensor], target_mp: int) -> List[Dict[str, torch.Tensor]]:
     outs = [dict() for _ in range(target_mp)]
     for k, t in full.items():
-        d = partition_dim(k)
+        d = partition_dim(k, t.dim() if isinstance(t, torch.Tensor) else None)
         if d is None or not isinstance(t, torch.Tensor) or t.dim() == 0 or target_mp == 1:
             for o in outs:
                 o[k] = t

@@ -331,3 +331,40 @@ def test_freeform_filter_pieces_match_reference():
     keys = set(ours.state_dict())
     assert {"pos_emb.z", "pos_emb.t", "act.freq", "implicit_filter.0.weight", "implicit_filter.0.bias",
             "implicit_filter.2.weight", "implicit_filter.4.bias", "final_filter.weight", "modulation.weight"} <= keys
+
+
+def test_real_and_complex_modal_filters_match_reference():
+    """Same parameters, same filter: the factored real modal filter and the complex diagonal filter against the
+    reference's classes (state dicts are exchanged key by key)."""
+    import torch.nn as nn
+    from einops import repeat
+    from savanna_b200.models.filters import ImplicitRealModalFilter, ParallelComplexModalFilter
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    ns = _extract(("savanna", "model", "operators", "hyena", "parametrization", "implicit_modal.py"),
+                  ["ImplicitRealModalFilter"], {"torch": torch, "nn": nn, "math": math})
+    torch.manual_seed(0)
+    theirs = ns["ImplicitRealModalFilter"](d_model=6, order=8, L_cache=64, residue_factors=3, pole_factors=3)
+    ours = ImplicitRealModalFilter(6, order=8, L_cache=64, residue_factors=3, pole_factors=3)
+    assert set(ours.state_dict()) == set(theirs.state_dict())
+    ours.load_state_dict(theirs.state_dict())
+    with torch.no_grad():
+        ours.dt[0, 0], ours.dt[1, 1] = 0.5, 1e-5                  # outside the clamp range on both sides
+        theirs.dt.copy_(ours.dt)
+    t = theirs.get_t(40)
+    want = ns["ImplicitRealModalFilter"].compute_filter.__wrapped__(theirs, 40, t) if hasattr(
+        ns["ImplicitRealModalFilter"].compute_filter, "__wrapped__") else theirs.compute_filter(40, t)
+    got = ours(40)
+    ok = torch.isfinite(want)            # a pole that underflows to 0 gives the reference 0 * log(0) = nan at t = 0
+    assert bool(torch.isfinite(got).all()) and float(ok.float().mean()) > 0.9
+    assert torch.allclose(got[ok], want[ok], atol=1e-5), (got[ok] - want[ok]).abs().max()
+    cs = _extract(("savanna", "model", "operators", "hyena", "parametrization", "implicit_complex.py"),
+                  ["ImplicitComplexModalFilter", "ParallelComplexModalFilter"],
+                  {"torch": torch, "nn": nn, "math": math, "repeat": repeat})
+    theirs = cs["ParallelComplexModalFilter"](d_model=6, order=8)
+    ours = ParallelComplexModalFilter(6, order=8)
+    assert set(ours.state_dict()) == set(theirs.state_dict())
+    assert all(ours.state_dict()[k].shape == v.shape for k, v in theirs.state_dict().items())
+    ours.load_state_dict(theirs.state_dict())
+    want, _ = theirs(40)
+    assert torch.allclose(ours(40), want[0], atol=1e-5), (ours(40) - want[0]).abs().max()
