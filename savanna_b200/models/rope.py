@@ -2,7 +2,7 @@
 
 `RotaryEmbedding` covers the reference's `rotary`, `rotary_linear_scaled` (position interpolation:
 positions divided by the scaling factor, optionally with a larger base) and `rotary_ntk_scaled`
-(base stretched by factor^(d/(d-2))) variants (savanna/model/operators/positional_embeddings.py:28-234).
+(dynamic NTK: beyond the unscaled length the base grows with the sequence length) variants (savanna/model/operators/positional_embeddings.py:28-234).
 Positions are always passed explicitly, so zigzag context-parallel shards get the right angles for
 every variant (the reference's plain variant overwrites them with arange, :74).
 """
@@ -12,6 +12,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import reference as ref
+from ..parallel import state
 
 
 class RotaryEmbedding(nn.Module):
@@ -19,10 +20,11 @@ class RotaryEmbedding(nn.Module):
                  max_unscaled_len: int = 8192, device=None):
         super().__init__()
         self.dim, self.kind = dim, kind
-        if kind == "rotary_ntk_scaled" and scaling_factor > 1.0:
-            base = base * scaling_factor ** (dim / (dim - 2))
-            scaling_factor = 1.0
-        if kind == "rotary":
+        # "rotary_ntk_scaled": the base grows with the sequence length once it exceeds `max_unscaled_len` (dynamic NTK
+        # scaling, positional_embeddings.py:194-237); "rotary_linear_scaled": positions are divided by the factor
+        self.ntk_factor = float(scaling_factor) if kind == "rotary_ntk_scaled" else 1.0
+        self.max_unscaled_len = int(max_unscaled_len or 2048)
+        if kind in ("rotary", "rotary_ntk_scaled"):
             scaling_factor = 1.0
         self.base, self.scaling_factor = float(base), float(scaling_factor)
         inv = 1.0 / (self.base ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
@@ -34,7 +36,13 @@ class RotaryEmbedding(nn.Module):
         key = (positions.data_ptr(), positions.shape[0], positions.device)
         if self._cache is not None and self._cache[0] == key:
             return self._cache[1], self._cache[2]
-        cos, sin = ref.rope_tables(positions, self.dim, self.base, self.scaling_factor)
+        base = self.base
+        if self.kind == "rotary_ntk_scaled":
+            seq_len = positions.shape[0] * state.get_context_parallel_world_size()
+            if seq_len > self.max_unscaled_len:
+                base = base * ((self.ntk_factor * seq_len / self.max_unscaled_len) - (self.ntk_factor - 1)) \
+                    ** (self.dim / (self.dim - 2))
+        cos, sin = ref.rope_tables(positions, self.dim, base, self.scaling_factor)
         self._cache = (key, cos, sin)
         return cos, sin
 

@@ -368,3 +368,94 @@ def test_real_and_complex_modal_filters_match_reference():
     ours.load_state_dict(theirs.state_dict())
     want, _ = theirs(40)
     assert torch.allclose(ours(40), want[0], atol=1e-5), (ours(40) - want[0]).abs().max()
+
+
+def test_rotary_variants_match_reference():
+    """cos / sin tables and the rotation itself for the plain, linearly scaled and dynamic-NTK rotary embeddings."""
+    import torch.nn as nn
+    from savanna_b200.models.rope import RotaryEmbedding
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+
+    class Mpu:
+        get_sequence_parallel_world_size = staticmethod(lambda: 1)
+        get_sequence_parallel_rank = staticmethod(lambda: 0)
+    ns = _extract(("savanna", "model", "operators", "positional_embeddings.py"),
+                  ["RotaryEmbedding2", "LinearlyScaledRotaryEmbedding", "NTKScaledRotaryEmbedding", "rotate_half",
+                   "apply_rotary_pos_emb_torch"], {"torch": torch, "mpu": Mpu, "ALLOC_DEVICE": None})
+    dim, L = 32, 48
+    x = torch.randn(L, 2, 3, dim)                                     # the reference rotates [L, B, H, hd]
+    pos = torch.arange(L)
+    cases = [
+        (ns["RotaryEmbedding2"](dim, base=10000.0, precision=torch.float32), RotaryEmbedding(dim, 10000.0, 1.0, "rotary")),
+        (ns["LinearlyScaledRotaryEmbedding"](dim, scaling_factor=4.0, base=1e6, precision=torch.float32),
+         RotaryEmbedding(dim, 1e6, 4.0, "rotary_linear_scaled")),
+        (ns["NTKScaledRotaryEmbedding"](dim, max_unscaled_seq_len=16, scaling_factor=2.0, base=10000.0, precision=torch.float32),
+         RotaryEmbedding(dim, 10000.0, 2.0, "rotary_ntk_scaled", max_unscaled_len=16)),
+        (ns["NTKScaledRotaryEmbedding"](dim, max_unscaled_seq_len=64, scaling_factor=2.0, base=10000.0, precision=torch.float32),
+         RotaryEmbedding(dim, 10000.0, 2.0, "rotary_ntk_scaled", max_unscaled_len=64)),     # short enough: no scaling
+    ]
+    for theirs, ours in cases:
+        cos_t, sin_t = theirs(x, seq_dim=0)
+        cos_o, sin_o = ours(pos)
+        assert torch.allclose(cos_o, cos_t[:, 0, 0, :], atol=1e-5) and torch.allclose(sin_o, sin_t[:, 0, 0, :], atol=1e-5)
+        q_t, k_t = ns["apply_rotary_pos_emb_torch"](x, x.flip(0), cos_t, sin_t)
+        q_o = ref.apply_rope(x.permute(1, 0, 2, 3), cos_o, sin_o).permute(1, 0, 2, 3)
+        k_o = ref.apply_rope(x.flip(0).permute(1, 0, 2, 3), cos_o, sin_o).permute(1, 0, 2, 3)
+        assert torch.allclose(q_o, q_t, atol=1e-5) and torch.allclose(k_o, k_t, atol=1e-5)
+
+
+def test_sample_index_helpers_match_reference():
+    """Document order, sample index (native helper against the reference's Python fallback), shuffle order, split
+    boundaries and blending weights: same inputs, same arrays."""
+    import numpy as np
+    from savanna_b200.data import helpers, loaders, sequence_dataset as sd
+    ns = _extract(("savanna", "data", "sequence_dataset.py"),
+                  ["_num_tokens", "_num_epochs", "_build_doc_idx", "_build_sample_idx", "_build_shuffle_idx"], {"np": np})
+    rng = np.random.RandomState(3)
+    sizes = rng.randint(5, 60, size=40).astype(np.int32)
+    docs = np.arange(5, 35, dtype=np.int32)
+    seq_length, num_samples = 32, 70
+    tokens = ns["_num_tokens"](docs, sizes)
+    assert tokens == sd._num_tokens(docs, sizes)
+    epochs = ns["_num_epochs"](tokens, seq_length, num_samples)
+    assert epochs == sd._num_epochs(tokens, seq_length, num_samples)
+    a = ns["_build_doc_idx"](docs, epochs, np.random.RandomState(11))
+    b = sd._build_doc_idx(docs, epochs, np.random.RandomState(11))
+    assert np.array_equal(a, b)
+    want = ns["_build_sample_idx"](sizes, a, seq_length, epochs, tokens)
+    got = helpers.build_sample_idx(sizes, b, seq_length, epochs, tokens)
+    assert np.array_equal(np.asarray(got), want)
+    n = want.shape[0] - 1
+    assert np.array_equal(ns["_build_shuffle_idx"](n, np.random.RandomState(5)), sd._build_shuffle_idx(n, np.random.RandomState(5)))
+    du = _extract(("savanna", "data", "data_utils.py"),
+                  ["get_train_valid_test_split_", "get_normalized_weights_and_num_samples", "weights_by_num_docs"],
+                  {"np": np, "math": math, "List": list, "Tuple": tuple})
+    for spec, size in (("969,30,1", 1000), ("0.8,0.2", 77), ("1", 10), ("3/1/1", 123)):
+        assert list(du["get_train_valid_test_split_"](spec, size)) == list(loaders.get_train_valid_test_split_(spec, size))
+    w, ns_ = du["get_normalized_weights_and_num_samples"]([1.0, 3.0, 0.5], 1000)
+    w2, ns2 = loaders.get_normalized_weights_and_num_samples([1.0, 3.0, 0.5], 1000)
+    assert np.allclose(w, w2) and list(ns_) == list(ns2)
+    assert np.allclose(du["weights_by_num_docs"]([10, 200, 3000]), loaders.weights_by_num_docs([10, 200, 3000]))
+
+
+def test_logit_filter_and_operator_expansion_match_reference():
+    from savanna_b200.config.loader import expand_operator_types
+    from savanna_b200.inference.generation import filter_logits
+    import torch.nn.functional as F
+    tg = _extract(("savanna", "text_generation_utils.py"), ["filter_logits"], {"torch": torch, "F": F})
+    torch.manual_seed(0)
+    logits = torch.randn(3, 50)
+    for k, p in ((0, 0.0), (5, 0.0), (0, 0.7), (10, 0.9), (1, 0.0)):
+        want = tg["filter_logits"](logits.clone(), top_k=k, top_p=p)
+        got = filter_logits(logits.clone(), top_k=k, top_p=p)
+        assert torch.equal(torch.isinf(got), torch.isinf(want)), (k, p)
+        assert torch.allclose(got[~torch.isinf(got)], want[~torch.isinf(want)])
+    ut = _extract(("savanna", "utils.py"), ["expand_operator_types"], {})
+    for spec, n in (([[["hyena_se", "hyena_mr", "hyena"], 2], [["flash_v2"], 1]], 7), ([[["global"], 4]], 4),
+                    ([[["hyena", "flash_v2"], "all"]], 6)):
+        try:
+            want = ut["expand_operator_types"](spec, n)
+        except Exception:
+            continue
+        assert list(expand_operator_types(spec, n)) == list(want), (spec, n)
