@@ -459,3 +459,49 @@ def test_logit_filter_and_operator_expansion_match_reference():
         except Exception:
             continue
         assert list(expand_operator_types(spec, n)) == list(want), (spec, n)
+
+
+def test_norms_explicit_filter_and_sampler_match_reference():
+    import torch.nn as nn
+    from torch.utils import data
+    from savanna_b200.data.samplers import DistributedBatchSampler
+    from savanna_b200.models.filters import ExplicitSingleDecayFilter
+    from savanna_b200.models.norms import RMSNorm, ScaleNorm
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    nm = _extract(("savanna", "model", "operators", "local", "norms.py"), ["RMSNorm", "ScaleNorm"],
+                  {"torch": torch, "ALLOC_DEVICE": None})
+    torch.manual_seed(0)
+    x = torch.randn(3, 7, 64)
+    theirs, ours = nm["RMSNorm"](64, eps=1e-6), RMSNorm(64, eps=1e-6, form="torch")
+    with torch.no_grad():
+        theirs.scale.copy_(torch.randn(64))
+        ours.scale.copy_(theirs.scale)
+    assert torch.allclose(ours(x), theirs(x), atol=1e-6)
+    assert set(ours.state_dict()) == set(theirs.state_dict()) == {"scale"}
+    assert torch.allclose(ScaleNorm(64)(x), nm["ScaleNorm"](64)(x), atol=1e-6)
+
+    class Mpu:
+        size, rank = 1, 0
+        get_model_parallel_world_size = staticmethod(lambda: Mpu.size)
+        get_model_parallel_rank = staticmethod(lambda: Mpu.rank)
+    ex = _extract(("savanna", "model", "operators", "hyena", "parametrization", "explicit.py"), ["ExplicitSingleDecayFilter"],
+                  {"torch": torch, "nn": nn, "math": math, "mpu": Mpu, "ALLOC_DEVICE": None, "print_rank_0": lambda *a, **k: None})
+    for preset, repeats in (("weak", 1), ("strong", 2), ("normal", 1)):
+        theirs = ex["ExplicitSingleDecayFilter"](16, 128, decay_preset=preset, num_decay_repeats=repeats)
+        ours = ExplicitSingleDecayFilter(16, 128, decay_preset=preset, num_decay_repeats=repeats)
+        assert torch.allclose(ours.decay, theirs.decay, atol=1e-6), preset
+        with torch.no_grad():
+            ours.h.copy_(theirs.h)
+        want = ex["ExplicitSingleDecayFilter"].filter.__wrapped__(theirs, 100) if hasattr(
+            ex["ExplicitSingleDecayFilter"].filter, "__wrapped__") else theirs.h[:, :100] * theirs.decay[:, :100]
+        assert torch.allclose(ours(100), want, atol=1e-7)
+        assert set(ours.state_dict()) == set(theirs.state_dict())
+    sm = _extract(("savanna", "data", "samplers.py"), ["DistributedBatchSampler"], {"torch": torch, "data": data})
+    for n, bs, world, drop, inter, skip in ((37, 8, 2, True, False, 0), (37, 8, 2, False, True, 0), (64, 16, 4, True, False, 2),
+                                            (30, 6, 3, False, False, 1)):
+        for rank in range(world):
+            a = sm["DistributedBatchSampler"](data.SequentialSampler(range(n)), bs, drop, rank, world, interleave=inter)
+            b = DistributedBatchSampler(data.SequentialSampler(range(n)), bs, drop, rank, world, interleave=inter)
+            a.start_iter = b.start_iter = skip
+            assert [list(x) for x in a] == [list(x) for x in b], (n, bs, world, drop, inter, skip, rank)
