@@ -53,7 +53,8 @@ class UnitFlat:
     """The parameters of one unit that share an optimizer group and a dtype, flattened and partitioned."""
 
     def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, name: str,
-                 free_params: bool, free_grads: bool, tp: int, offload_param: bool = False):
+                 free_params: bool, free_grads: bool, tp: int, offload_param: bool = False,
+                 offload_optimizer: bool = False):
         self.params, self.hyper, self.name = params, hyper, name
         self.world, self.rank = world, rank
         self.free_params, self.free_grads = free_params, free_grads
@@ -86,6 +87,16 @@ class UnitFlat:
         if self.param_offloaded:
             host = self.param_shard.cpu()
             self.param_shard = host.pin_memory() if device.type == "cuda" else host
+        # `offload_optimizer`: fp32 master copy and Adam moments of this rank's shard live in (pinned) host memory and the
+        # update runs on the CPU; the reduced gradient shard is copied down, the new low-precision shard copied up
+        self.optimizer_offloaded = bool(offload_optimizer)
+        self.host_grad = None
+        if self.optimizer_offloaded:
+            pin = device.type == "cuda"
+            host = self.master.detach().float().cpu().clone()
+            self.master = host.pin_memory() if pin else host
+            self.master_is_view = False
+            self.host_grad = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_acc = torch.zeros(self.shard, dtype=torch.float32, device=device)
@@ -187,9 +198,11 @@ class PartitionedZeroOptimizer:
                  clip_grad: float = 0.0, group=None, group_ranks: Optional[List[int]] = None,
                  grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
                  sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0,
-                 hpz_group=None, hpz_ranks: Optional[List[int]] = None, offload_param: bool = False):
+                 hpz_group=None, hpz_ranks: Optional[List[int]] = None, offload_param: bool = False,
+                 offload_optimizer: bool = False):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
+        self.offload_optimizer = bool(offload_optimizer)
         self.stage = stage
         self.group = group
         ranks = group_ranks or [0]
@@ -243,7 +256,7 @@ class PartitionedZeroOptimizer:
                 root = ui == 0
                 f = UnitFlat(plist, self.world, self.rank, hyper, f"{unit.name}.{hyper['name']}.{dt}",
                              free_params=(stage == 3 and not root), free_grads=not root, tp=tp,
-                             offload_param=offload_param)
+                             offload_param=offload_param, offload_optimizer=offload_optimizer)
                 unit.flats.append(f)
                 self.groups.append(f)
         # hpZ (`zero_hpz_partition_size`, stage 3): after a unit's forward all-gather over the whole group, every rank keeps
@@ -430,6 +443,21 @@ class PartitionedZeroOptimizer:
         else:
             coef = torch.full_like(norm, inv)
         b1, b2 = self.betas
+        if self.offload_optimizer:
+            from ..ops import reference as ref
+            coef_host = float(coef)                 # one synchronisation per step: the clip coefficient
+            for f in self.groups:
+                f.host_grad.copy_(f.grad_acc, non_blocking=True)
+            if self.groups and self.groups[0].grad_acc.is_cuda:
+                torch.cuda.current_stream().synchronize()
+            for f in self.groups:
+                ref.adam_step(f.master, f.exp_avg, f.exp_avg_sq, f.host_grad, f.hyper["lr"], b1, b2, self.eps,
+                              f.hyper["weight_decay"], self.step_count, self.adamw, coef_host, None)
+                f.param_shard.copy_(f.master, non_blocking=True)
+                f.hpz_fresh = False
+                if not f.free_params:
+                    _all_gather(f.full, f.shard_on_device(), self.group, self.world)
+            return norm
         for f in self.groups:
             low = None if f.master_is_view else f.param_shard
             if f.param_offloaded:
@@ -527,7 +555,8 @@ class PartitionedZeroOptimizer:
     def memory_report(self) -> Dict[str, int]:
         """Bytes this rank holds persistently (shards and optimizer state) and transiently at most (one unit whole)."""
         persistent = sum((0 if f.param_offloaded else f.param_shard.numel() * f.param_shard.element_size()) + f.grad_acc.numel() * 4
-                         + (0 if f.master_is_view else f.master.numel() * 4) + 2 * f.exp_avg.numel() * 4
+                         + (0 if (f.master_is_view or f.optimizer_offloaded) else f.master.numel() * 4)
+                         + (0 if f.optimizer_offloaded else 2 * f.exp_avg.numel() * 4)
                          for f in self.groups)
         root = sum(2 * f.nbytes for f in self.units[0].flats)
         unit = max((sum(f.nbytes for f in u.flats) for u in self.units[1:]), default=0)

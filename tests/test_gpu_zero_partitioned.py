@@ -82,8 +82,9 @@ def test_partitioned_stages_match_stage1_two_gpus(stage):
 @pytest.mark.parametrize("over", [
     {"zero_optimization": {"stage": 1, "offload_optimizer": {"device": "cpu", "pin_memory": True}}},
     {"zero_optimization": {"stage": 3, "offload_param": {"device": "cpu"}}},
+    {"zero_optimization": {"stage": 3, "offload_optimizer": {"device": "cpu"}, "offload_param": {"device": "cpu"}}},
     {"zero_optimization": {"stage": 1}, "checkpoint_activations": True, "checkpoint_num_layers": 2, "checkpoint_in_cpu": True},
-], ids=["offload_optimizer", "offload_param", "checkpoint_in_cpu"])
+], ids=["offload_optimizer", "offload_param", "offload_both_stage3", "checkpoint_in_cpu"])
 def test_host_offload_paths_match_the_resident_run(over):
     """Optimizer state on the host (update on the CPU), parameter shards on the host (stage 3) and checkpointed chunk
     inputs on the host: same loss trace as the all-on-device ZeRO-1 run."""

@@ -363,6 +363,32 @@ def _w_write_losses(rank, world, over, out):
             json.dump(losses, fh)
 
 
+def _w_offload_optimizer_partitioned(rank, world, over, ref_losses):
+    cfg = _tiny_cfg(world, **over)
+    tr, losses = _run_steps(cfg)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    opt = tr.optimizer
+    assert opt.offload_optimizer and all(f.optimizer_offloaded and f.master.device.type == "cpu" and not f.master_is_view
+                                         for f in opt.groups)
+    with opt.full_params():
+        for f in opt.groups:
+            assert torch.allclose(f.shard_slice(f.full).float(), f.master.to(f.full.dtype).float())
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("stage", [2, 3])
+def test_zero23_optimizer_offload_matches(stage, tmp_path):
+    """`offload_optimizer.device: cpu` with the partitioned optimizer (fp32 and bf16 flats alike): same loss trace."""
+    import json
+    over = {"train_micro_batch_size_per_gpu": 1, "gradient_accumulation_steps": 2, "zero_optimization": {"stage": stage}}
+    out = str(tmp_path / "ref.json")
+    run_distributed(_w_write_losses, 2, over, out)
+    ref_losses = json.load(open(out))
+    over2 = dict(over, zero_optimization={"stage": stage, "offload_optimizer": {"device": "cpu"}})
+    run_distributed(_w_offload_optimizer_partitioned, 2, over2, ref_losses)
+
+
 @pytest.mark.slow
 def test_zero3_parameter_offload_matches(tmp_path):
     """`offload_param.device: cpu` with stage 3 in bf16: the shards of released units live on the host, the loss trace
