@@ -27,6 +27,7 @@ resident and is handled like a stage-1 group.
 from __future__ import annotations
 
 import contextlib
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -54,7 +55,7 @@ class UnitFlat:
 
     def __init__(self, params: List[torch.nn.Parameter], world: int, rank: int, hyper: Dict, name: str,
                  free_params: bool, free_grads: bool, tp: int, offload_param: bool = False,
-                 offload_optimizer: bool = False):
+                 offload_optimizer: bool = False, nvme_prefix: Optional[str] = None):
         self.params, self.hyper, self.name = params, hyper, name
         self.world, self.rank = world, rank
         self.free_params, self.free_grads = free_params, free_grads
@@ -97,8 +98,17 @@ class UnitFlat:
             self.master = host.pin_memory() if pin else host
             self.master_is_view = False
             self.host_grad = torch.zeros(self.shard, dtype=torch.float32, pin_memory=pin)
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        if self.optimizer_offloaded and nvme_prefix:
+            # `device: nvme`: the three state arrays are mapped files under `nvme_path` (see parallel/zero.py)
+            from .zero import _file_tensor
+            init = self.master
+            self.master = _file_tensor(nvme_prefix + "_master.bin", self.shard)
+            self.master.copy_(init)
+            self.exp_avg = _file_tensor(nvme_prefix + "_exp_avg.bin", self.shard).zero_()
+            self.exp_avg_sq = _file_tensor(nvme_prefix + "_exp_avg_sq.bin", self.shard).zero_()
+        else:
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_acc = torch.zeros(self.shard, dtype=torch.float32, device=device)
         self.norm_weight: Optional[torch.Tensor] = None
         if tp > 1 and not all(getattr(p, "model_parallel", False) for p in params):
@@ -199,7 +209,7 @@ class PartitionedZeroOptimizer:
                  grad_divisor: Optional[float] = None, sync_replicated: bool = False, prefetch: bool = True,
                  sum_ranks: Optional[int] = None, replica_group=None, replica_world: int = 1, replica_index: int = 0,
                  hpz_group=None, hpz_ranks: Optional[List[int]] = None, offload_param: bool = False,
-                 offload_optimizer: bool = False):
+                 offload_optimizer: bool = False, nvme_path: Optional[str] = None):
         if stage not in (2, 3):
             raise ValueError("PartitionedZeroOptimizer implements ZeRO stages 2 and 3")
         self.offload_optimizer = bool(offload_optimizer)
@@ -256,7 +266,9 @@ class PartitionedZeroOptimizer:
                 root = ui == 0
                 f = UnitFlat(plist, self.world, self.rank, hyper, f"{unit.name}.{hyper['name']}.{dt}",
                              free_params=(stage == 3 and not root), free_grads=not root, tp=tp,
-                             offload_param=offload_param, offload_optimizer=offload_optimizer)
+                             offload_param=offload_param, offload_optimizer=offload_optimizer,
+                             nvme_prefix=(os.path.join(nvme_path, f"zero_state_rank{me}_buf{len(self.groups)}")
+                                          if (offload_optimizer and nvme_path) else None))
                 unit.flats.append(f)
                 self.groups.append(f)
         # hpZ (`zero_hpz_partition_size`, stage 3): after a unit's forward all-gather over the whole group, every rank keeps

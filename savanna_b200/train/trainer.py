@@ -178,8 +178,6 @@ class Trainer:
                 nvme_path = off.get("nvme_path")
                 if not nvme_path:
                     raise ValueError("offload_optimizer.device nvme needs offload_optimizer.nvme_path (a directory on the drive)")
-            if nvme_path and cfg.zero_stage >= 2:
-                raise NotImplementedError("offload_optimizer.device nvme is implemented for ZeRO stages 0 and 1 (cpu: all stages)")
             use_symm = (self.device.type == "cuda" and cfg.comm_path == "symm" and len(zranks) > 1
                         and cfg.zero_stage >= 1 and cfg.precision == "bfloat16" and not offload)
             allocator = None
@@ -211,7 +209,7 @@ class Trainer:
                     adamw=p.get("adam_w_mode", True), clip_grad=cfg.gradient_clipping or 0.0,
                     group=zgroup, group_ranks=zranks,
                     sync_replicated=bool(cfg.sequence_parallel), offload_param=offload_param, offload_optimizer=offload,
-                    **mics)
+                    nvme_path=nvme_path, **mics)
                 rep = optimizer.memory_report()
                 print_rank_0(f" > ZeRO stage {optimizer.stage}: {rep['persistent_bytes'] / 2**20:.0f} MiB of shards and "
                              f"optimizer state per rank, largest unit {rep['largest_unit_param_bytes'] / 2**20:.0f} MiB "

@@ -387,6 +387,12 @@ def test_zero23_optimizer_offload_matches(stage, tmp_path):
     ref_losses = json.load(open(out))
     over2 = dict(over, zero_optimization={"stage": stage, "offload_optimizer": {"device": "cpu"}})
     run_distributed(_w_offload_optimizer_partitioned, 2, over2, ref_losses)
+    if stage == 3:                                         # ... and with the state arrays as mapped files
+        nv = str(tmp_path / "nv")
+        over3 = dict(over, zero_optimization={"stage": stage, "offload_optimizer": {"device": "nvme", "nvme_path": nv}})
+        run_distributed(_w_offload_optimizer_partitioned, 2, over3, ref_losses)
+        files = os.listdir(nv)
+        assert files and len(files) % 3 == 0 and any(f.startswith("zero_state_rank1_") for f in files)
 
 
 @pytest.mark.slow
