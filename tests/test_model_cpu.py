@@ -193,6 +193,26 @@ def test_save_retain_interval_selects_the_uploaded_checkpoints(tmp_path):
     assert sorted(os.listdir(mirror)) == ["global_step2", "global_step4"]
 
 
+def test_checkpoint_validation_with_forward_pass(tmp_path):
+    """The logits of a fixed input are stored with the checkpoint and reproduced after loading; a checkpoint whose
+    stored logits do not belong to its weights is refused."""
+    from savanna_b200.ckpt import load_checkpoint, save_checkpoint
+    save = str(tmp_path / "c")
+    cfg = _cfg(save=save, load=save, checkpoint_validation_with_forward_pass=True)
+    tr = Trainer(cfg, load=False)
+    tr.train_step(_iter(cfg))
+    d = save_checkpoint(tr)
+    path = os.path.join(d, "mp_rank_00_model_states.pt")
+    ms = torch.load(path, weights_only=False)
+    assert ms["checkpoint_validation_logits"].shape == (cfg.seq_length, cfg.padded_vocab_size)
+    t2 = Trainer(cfg, load=True)                                  # validates while loading
+    assert t2.iteration == 1
+    ms["checkpoint_validation_logits"] = ms["checkpoint_validation_logits"] + 1.0      # what another model would have stored
+    torch.save(ms, path)
+    with pytest.raises(RuntimeError, match="does not reproduce"):
+        Trainer(cfg, load=True)
+
+
 def test_finetune_loads_module_only(tmp_path):
     save = str(tmp_path / "c")
     cfg = _cfg(save=save)
