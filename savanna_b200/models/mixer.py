@@ -47,6 +47,9 @@ class SelfAttention(nn.Module):
         self._sparse_masks = {}
         if self.sparse and not cfg.causal:
             raise NotImplementedError("block-sparse attention operators are built for causal models (unidirectional layouts)")
+        # dropout on the attention probabilities (0 in every Evo 2 configuration): the own kernels have none, so a
+        # training step with a non-zero rate runs PyTorch's fused attention, which has
+        self.attn_dropout = float(cfg.attention_dropout or 0.0)
         self._rotary = []          # the module itself is registered by the owning mixer as `rotary_emb`
         if cfg.pos_emb in ("rotary", "rotary_linear_scaled", "rotary_ntk_scaled", "rotary2"):
             rd = int(self.hd * cfg.rotary_pct)
@@ -103,6 +106,16 @@ class SelfAttention(nn.Module):
         cos = sin = None
         if self._rotary:
             cos, sin = self._rotary[0](positions)
+        if self.attn_dropout > 0.0 and self.training:
+            if cp > 1:
+                raise NotImplementedError("attention_dropout does not run under context parallelism")
+            import torch.nn.functional as F
+            q, k, v = qkv[..., : self.hd], qkv[..., self.hd: 2 * self.hd], qkv[..., 2 * self.hd:]
+            if self._rotary:
+                q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               dropout_p=self.attn_dropout, is_causal=self.causal)
+            return o.transpose(1, 2).reshape(B, L, self.heads * self.hd)
         if cp == 1 or self.operator_type not in ("ring", "flash_te"):
             o = ops.attention_packed(qkv, cos, sin, self.causal)      # one function: no slice / concatenate in autograd
             if o is not None:

@@ -452,3 +452,21 @@ def test_block_sparse_attention_operators_train_and_match_a_masked_softmax():
     s = s.masked_fill(~keep[None, None], float("-inf"))
     want = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v)
     assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+
+
+def test_attention_dropout_is_applied_in_training_only():
+    cfg = _cfg(attention_dropout=0.5, hidden_dropout=0.0)
+    tr = Trainer(cfg, load=False)
+    layer = [m for m in tr.model.modules() if hasattr(m, "attn_dropout")][0]
+    assert layer.attn_dropout == 0.5
+    torch.manual_seed(0)
+    qkv = torch.randn(1, 64, layer.heads * 3 * layer.hd)
+    pos = torch.arange(64)
+    layer.train()
+    a, b = layer(qkv, pos), layer(qkv, pos)
+    assert not torch.allclose(a, b)                       # two draws of the dropout mask
+    layer.eval()
+    c, d = layer(qkv, pos), layer(qkv, pos)
+    assert torch.equal(c, d)
+    losses = [float(tr.train_step(_iter(cfg))) for _ in range(3)]
+    assert all(l == l for l in losses)
