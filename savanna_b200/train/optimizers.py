@@ -120,12 +120,17 @@ class MadgradWD(torch.optim.Optimizer):
                     st["s"] = torch.zeros_like(grad)
                     st["x0"] = p.detach().float().clone()
                 if g["weight_decay"] != 0:
-                    p.mul_(1 - g["lr"] * g["weight_decay"])
-                    st["x0"].mul_(1 - g["lr"] * g["weight_decay"])
+                    # decoupled decay of the iterate only, with the eps-shifted rate; the anchor x0 is left alone
+                    # (reference: savanna/optimizers/madgrad.py:131-133)
+                    p.mul_(1 - lr * g["weight_decay"])
+                if mom > 0:
+                    x0 = st["x0"]
+                else:                                   # without momentum the anchor is recovered from the iterate
+                    x0 = p.float() + st["s"] / st["sum_sq"].pow(1 / 3).add_(g["eps"])
                 st["sum_sq"].addcmul_(grad, grad, value=lamb)
                 st["s"].add_(grad, alpha=lamb)
                 rms = st["sum_sq"].pow(1 / 3).add_(g["eps"])
-                z = st["x0"] - st["s"] / rms
+                z = x0 - st["s"] / rms
                 p.copy_((p.float() * mom + z * (1 - mom)).to(p.dtype)) if mom > 0 else p.copy_(z.to(p.dtype))
             g["k"] = k + 1
 

@@ -505,3 +505,47 @@ def test_norms_explicit_filter_and_sampler_match_reference():
             b = DistributedBatchSampler(data.SequentialSampler(range(n)), bs, drop, rank, world, interleave=inter)
             a.start_iter = b.start_iter = skip
             assert [list(x) for x in a] == [list(x) for x in b], (n, bs, world, drop, inter, skip, rank)
+
+
+def test_extra_optimizers_match_reference():
+    """SophiaG, SM3, MADGRAD with weight decay and schedule-free AdamW: the reference's optimizer files are plain PyTorch and
+    load as they are; both sides take the same gradients for several steps and must hold the same parameters."""
+    from savanna_b200.train import optimizers as ours
+    soph = _load("savanna_ref_sophia", "savanna", "optimizers", "sophia.py")
+    sm3 = _load("savanna_ref_sm3", "savanna", "optimizers", "sm3.py")
+    mad = _load("savanna_ref_madgrad", "savanna", "optimizers", "madgrad.py")
+    sfree = _load("savanna_ref_schedulefree", "savanna", "optimizers", "adam_schedulefree.py")
+
+    def run(make_theirs, make_ours, steps=5, hessian_every=0, switch_modes=False):
+        torch.manual_seed(0)
+        shapes = [(6, 5), (7,), (3, 4, 2)]
+        pa = [torch.nn.Parameter(torch.randn(s)) for s in shapes]
+        pb = [torch.nn.Parameter(p.detach().clone()) for p in pa]
+        a, b = make_theirs(pa), make_ours(pb)
+        for i in range(steps):
+            grads = [torch.randn(s) for s in shapes]
+            for p, q, g in zip(pa, pb, grads):
+                p.grad, q.grad = g.clone(), g.clone()
+            if hessian_every and i % hessian_every == 0:
+                a.update_hessian()
+                b.update_hessian()
+            a.step()
+            b.step()
+            if switch_modes and i == 2:
+                a.eval(); b.eval()
+                for p, q in zip(pa, pb):
+                    assert torch.allclose(p, q, atol=1e-6), "evaluation iterate"
+                a.train(); b.train()
+        for p, q in zip(pa, pb):
+            assert torch.allclose(p, q, atol=1e-6, rtol=1e-5), (p - q).abs().max()
+
+    run(lambda p: soph.SophiaG(p, lr=1e-2, betas=(0.9, 0.95), rho=0.05, weight_decay=0.1, batch_size=4),
+        lambda p: ours.SophiaG(p, lr=1e-2, betas=(0.9, 0.95), rho=0.05, weight_decay=0.1, bs=4), hessian_every=2)
+    run(lambda p: sm3.SM3(p, lr=0.1, momentum=0.9, beta=0.5), lambda p: ours.SM3(p, lr=0.1, momentum=0.9, beta=0.5))
+    run(lambda p: sm3.SM3(p, lr=0.1), lambda p: ours.SM3(p, lr=0.1))
+    run(lambda p: mad.madgrad_wd(p, lr=1e-2, momentum=0.9, weight_decay=0.01),
+        lambda p: ours.MadgradWD(p, lr=1e-2, momentum=0.9, weight_decay=0.01))
+    run(lambda p: mad.madgrad_wd(p, lr=1e-2, momentum=0.0, weight_decay=0.0),
+        lambda p: ours.MadgradWD(p, lr=1e-2, momentum=0.0, weight_decay=0.0))
+    run(lambda p: sfree.AdamWScheduleFree(p, lr=1e-2, weight_decay=0.01, warmup_steps=2, foreach=False),
+        lambda p: ours.AdamWScheduleFree(p, lr=1e-2, weight_decay=0.01, warmup_steps=2), switch_modes=True)
