@@ -549,3 +549,28 @@ def test_extra_optimizers_match_reference():
         lambda p: ours.MadgradWD(p, lr=1e-2, momentum=0.0, weight_decay=0.0))
     run(lambda p: sfree.AdamWScheduleFree(p, lr=1e-2, weight_decay=0.01, warmup_steps=2, foreach=False),
         lambda p: ours.AdamWScheduleFree(p, lr=1e-2, weight_decay=0.01, warmup_steps=2), switch_modes=True)
+
+
+def test_gradient_noise_scale_matches_reference():
+    from savanna_b200.train.critical_batch import CriticalBatchEstimator
+    ns = _extract(("savanna", "scaling", "critical_batch.py"), ["ema", "CriticalBatchEstimator"],
+                  {"torch": torch, "safe_get_full_grad": lambda p: p.grad})
+
+    class Cfg:
+        is_pipe_parallel = False
+    model = torch.nn.Linear(6, 4)
+    theirs = ns["CriticalBatchEstimator"](model, batch_size_small=8, n_batches=3, beta=0.9, global_config=Cfg)
+    ours = CriticalBatchEstimator(8, n_batches=3, beta=0.9)
+    torch.manual_seed(0)
+    base = [torch.randn_like(p) for p in model.parameters()]
+    seen = 0
+    for step in range(12):
+        for p, b in zip(model.parameters(), base):
+            p.grad = b + 0.5 * torch.randn_like(p)            # a common direction plus per-batch noise
+        theirs.update()
+        ours.update(list(model.parameters()))
+        if theirs.noise_scale is not None:
+            seen += 1
+            assert ours.noise_scale is not None
+            assert abs(ours.noise_scale - theirs.noise_scale) < 1e-4 * max(1.0, abs(theirs.noise_scale)), (step, ours.noise_scale, theirs.noise_scale)
+    assert seen >= 9
