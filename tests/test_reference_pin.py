@@ -574,3 +574,34 @@ def test_gradient_noise_scale_matches_reference():
             assert ours.noise_scale is not None
             assert abs(ours.noise_scale - theirs.noise_scale) < 1e-4 * max(1.0, abs(theirs.noise_scale)), (step, ours.noise_scale, theirs.noise_scale)
     assert seen >= 9
+
+
+def test_alibi_bias_matches_reference():
+    from savanna_b200.models.rope import AliBi
+    ns = _extract(("savanna", "model", "operators", "positional_embeddings.py"), ["AliBi"], {"torch": torch, "math": math})
+    for heads, mp, rank in ((8, 1, 0), (12, 1, 0), (8, 2, 1), (6, 2, 0)):
+        theirs = ns["AliBi"](heads, mp, rank)
+        ours = AliBi(heads, mp, rank)
+        L = 24
+        want = theirs(torch.zeros(1, heads // mp, L, L))[0]                  # [heads / mp, L, L]
+        pos = torch.arange(L)
+        got = ours.bias(pos, pos)
+        keep = torch.tril(torch.ones(L, L, dtype=torch.bool))                 # above the diagonal the causal mask decides
+        assert torch.allclose(got[:, keep], want[:, keep], atol=1e-6), (heads, mp, rank)
+
+
+def test_relative_position_buckets_match_reference():
+    from savanna_b200.models.rope import RelativePositionBias
+    from savanna_b200.parallel import state
+    state.destroy_model_parallel()
+    ns = _extract(("savanna", "mpu", "layers.py"), ["_relative_position_bucket"], {"torch": torch, "math": math})
+    rel = torch.arange(-300, 300)[None, :] - torch.arange(0, 40)[:, None]
+    for causal in (True, False):
+        for buckets, dist_ in ((32, 128), (16, 64)):
+            class Self:
+                pass
+            me = Self()
+            me.causal = causal
+            want = ns["_relative_position_bucket"](me, rel, num_buckets=buckets, max_distance=dist_)
+            ours = RelativePositionBias(1.0, causal, buckets, dist_, heads=4)
+            assert torch.equal(ours.bucket(rel), want), (causal, buckets, dist_)
