@@ -605,3 +605,35 @@ def test_relative_position_buckets_match_reference():
             want = ns["_relative_position_bucket"](me, rel, num_buckets=buckets, max_distance=dist_)
             ours = RelativePositionBias(1.0, causal, buckets, dist_, heads=4)
             assert torch.equal(ours.bucket(rel), want), (causal, buckets, dist_)
+
+
+def test_flop_model_terms_match_reference():
+    """Per-layer FLOP terms of the reference's counter (projections, featuriser conv, short / medium depthwise convs, FFT long
+    conv, attention, logits) summed with the right layer counts equal this framework's per-token model FLOPs; the gated
+    MLP is counted at its real inner size here (the reference's counter rounds 8/3 D to a multiple of 64 whatever the
+    configured multiple is)."""
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.utils import mfu
+    names = ["dense_projection_flops_per_layer", "hyena_conv_proj_flops_per_layer", "attention_out_proj_flops_per_layer",
+             "logits_flops_per_batch", "depthwise_conv_flops_per_layer", "fft_conv_flops_per_layer",
+             "attention_flops_per_layer", "ffn_flops_per_layer", "round_to_next_multiple"]
+    ns = _extract(("savanna", "mfu.py"), names, {"math": math, "FFN_EXPANSION_FACTOR": 8 / 3, "FFN_DIM_MULTIPLE": 64})
+    cfg = GlobalConfig.from_ymls([os.path.join(ROOT, "configs", "baseline", "tiny_sh2_cpu.yml")], {"global_num_gpus": 1})
+    cfg.build_tokenizer()
+    bs, L, D, V = 1, cfg.seq_length, cfg.hidden_size, cfg.padded_vocab_size
+    ops_ = list(cfg.operator_config)
+    n = len(ops_)
+    n_se, n_mr, n_li = ops_.count("hyena_se"), ops_.count("hyena_mr"), ops_.count("hyena")
+    n_attn = n - n_se - n_mr - n_li
+    total = (n * ns["dense_projection_flops_per_layer"](bs, L, D) + n * ns["attention_out_proj_flops_per_layer"](bs, L, D)
+             + n * 2 * 3 * bs * L * cfg.ffn_size * D
+             + (n_se + n_mr + n_li) * ns["hyena_conv_proj_flops_per_layer"](bs, L, D, kernel_size=cfg.short_conv_L)
+             + n_se * ns["depthwise_conv_flops_per_layer"](bs, L, D, cfg.hyena_se_len)
+             + n_mr * ns["depthwise_conv_flops_per_layer"](bs, L, D, min(cfg.hyena_mr_len, L))
+             + n_li * ns["fft_conv_flops_per_layer"](bs, L, D)
+             + n_attn * ns["attention_flops_per_layer"](bs, L, D)
+             + ns["logits_flops_per_batch"](bs, L, D, V))
+    ours = mfu.model_flops_per_token(cfg, backward=False) * bs * L
+    assert abs(ours - total) < 1e-9 * total, (ours, total)
+    # the reference's own inner size for this width, for the record of the difference
+    assert ns["ffn_flops_per_layer"](bs, L, D) == 2 * 3 * bs * L * ns["round_to_next_multiple"](int(D * 8 / 3), 64) * D
