@@ -22,14 +22,16 @@ from .filters import ExplicitSingleDecayFilter, ImplicitModalFilter, build_filte
 
 
 def groups_per_rank(hidden: int, num_groups: Optional[int], tp: int, expansion: float = 1.0):
-    width = int(hidden * expansion)
+    """(width, filter groups, channels per group) on one tensor-parallel rank.  `hidden` is the operator's width, already
+    expanded by the mixer; the group count is scaled by `expansion` here, as the reference does
+    (operators/hyena/hyena.py:184-188: groups per rank = int(groups / tp * hyena_width_expansion))."""
     if num_groups is None:
-        num_groups = width
-    if width % tp or num_groups % tp:
+        num_groups = hidden
+    if hidden % tp or num_groups % tp:
         raise ValueError("hyena width and group count must be divisible by the tensor-parallel size")
-    w, g = width // tp, num_groups // tp
-    if w % g:
-        raise ValueError("hyena width per rank must be divisible by the groups per rank")
+    w, g = hidden // tp, int(num_groups // tp * expansion)
+    if g <= 0 or w % g:
+        raise ValueError(f"hyena width per rank {w} must be divisible by the groups per rank {g}")
     return w, g, w // g
 
 

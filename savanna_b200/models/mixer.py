@@ -147,6 +147,16 @@ class ParallelSequenceMixer(nn.Module):
         D = cfg.hidden_size
         tp = state.get_model_parallel_world_size()
         sp = cfg.sequence_parallel
+        # Hyena layers may run wider than the residual stream (`hyena_width_expansion`, or `hyena_mlp_expansion_factor`
+        # for the short-Hyena MLP): projections go D -> 3 H and H -> D, H rounded up to a multiple of 32 when expanded
+        # (reference: savanna/model/block.py:178-201)
+        H = D
+        if self.operator_type in HYENA_OPS:
+            e = float(cfg.hyena_mlp_expansion_factor if is_mlp else cfg.hyena_width_expansion)
+            H = int(D * e)
+            if e > 1:
+                H = 32 * ((H + 31) // 32)
+        self.inner_size = H
         if is_mlp:
             fp8_in = cfg.use_fp8_linears and cfg.use_fp8_hyena_mlp_input_projections
             fp8_out = cfg.use_fp8_linears and cfg.use_fp8_hyena_mlp_output_projections
@@ -160,25 +170,25 @@ class ParallelSequenceMixer(nn.Module):
         self.tie_projections = bool(cfg.tie_projection_weights)
         self.proj_groups = int(cfg.proj_groups or 1) if self.operator_type in ATTENTION_OPS else 1
         if self.tie_projections:
-            proj_out = D
+            proj_out = H
         elif self.proj_groups > 1:
             if (2 * D) % (self.proj_groups * tp):
                 raise ValueError(f"proj_groups={self.proj_groups}: 2 * hidden_size must divide by proj_groups * tensor-parallel size")
             proj_out = D + 2 * D // self.proj_groups
         else:
-            proj_out = 3 * D
+            proj_out = 3 * H
         self.dense_projection = ColumnParallelLinear(D, proj_out, bias=False, gather_output=False, init_method=init_method,
                                                      skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device,
                                                      fp8=fp8_in)
         if self.operator_type in HYENA_OPS:
-            width = 3 * D // tp
+            width = 3 * H // tp
             self.short_conv_L = cfg.short_conv_L
             self.hyena_proj_conv = CausalDepthwiseConv1d(width, cfg, cfg.short_conv_L, num_groups=width,
                                                          fast=cfg.fast_conv_proj, dtype=dtype, device=device)
             if self.operator_type == "hyena_se":
-                self.mixer = ShortHyenaOperator(D, cfg, is_mlp=is_mlp, dtype=dtype, device=device)
+                self.mixer = ShortHyenaOperator(H, cfg, is_mlp=is_mlp, dtype=dtype, device=device)
             else:
-                self.mixer = HyenaOperator(D, cfg, layer_number, self.operator_type, dtype=dtype, device=device)
+                self.mixer = HyenaOperator(H, cfg, layer_number, self.operator_type, dtype=dtype, device=device)
             if not cfg.interleave_projections:
                 raise NotImplementedError("non-interleaved projections: convert the checkpoint with "
                                           "tools/interleave_model_states.py and set interleave_projections")
@@ -188,7 +198,7 @@ class ParallelSequenceMixer(nn.Module):
                 self.rotary_emb = self.mixer._rotary[0]
         else:
             raise NotImplementedError(f"operator {self.operator_type!r} has no implementation in this framework")
-        self.dense = RowParallelLinear(D, D, bias=True, input_is_parallel=True, init_method=output_layer_init_method,
+        self.dense = RowParallelLinear(H, D, bias=True, input_is_parallel=True, init_method=output_layer_init_method,
                                        skip_bias_add=True, sequence_parallel=sp, dtype=dtype, device=device, fp8=fp8_out)
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor, residual: Optional[torch.Tensor] = None, pre_norm=None):

@@ -470,3 +470,25 @@ def test_attention_dropout_is_applied_in_training_only():
     assert torch.equal(c, d)
     losses = [float(tr.train_step(_iter(cfg))) for _ in range(3)]
     assert all(l == l for l in losses)
+
+
+def test_hyena_width_expansion_widens_the_operators_not_the_stream():
+    """`hyena_mlp_expansion_factor` 2 on the short-Hyena MLP and `hyena_width_expansion` 2 on the mixers: projections go
+    D -> 3 H -> D with H a multiple of 32, groups scale with the width, and the model trains."""
+    cfg = _cfg(mlp_type="short_hyena", hyena_mlp_expansion_factor=2, hyena_width_expansion=2, num_groups_hyena=256,
+               num_groups_hyena_medium=16, num_groups_hyena_short=16, num_groups_hyena_mlp=16)
+    D = cfg.hidden_size
+    tr = Trainer(cfg, load=False)
+    shapes = {n: tuple(p.shape) for n, p in tr.model.named_parameters()}
+    Hm, Hx = 2 * D, 32 * ((int(2 * D) + 31) // 32)
+    assert shapes["sequential.2.mlp.dense_projection.weight"] == (3 * Hm, D)
+    assert shapes["sequential.2.mlp.dense.weight"] == (D, Hm)
+    assert shapes["sequential.2.mixer.dense_projection.weight"] == (3 * Hx, D)
+    assert shapes["sequential.2.mixer.dense.weight"] == (D, Hx)
+    attn = [n for n in shapes if n.endswith("mixer.dense_projection.weight")
+            and cfg.operator_config[int(n.split(".")[1]) - 2] == "flash_v2"]
+    assert attn and all(shapes[n] == (3 * D, D) for n in attn)           # attention keeps the stream's width
+    se = tr.model.get_submodule("sequential.2.mlp.mixer")
+    assert se.width == Hm and se.num_groups == int(int(16 * 2) * 2) and se.width % se.num_groups == 0
+    losses = [float(tr.train_step(_iter(cfg))) for _ in range(4)]
+    assert losses[-1] < losses[0], losses
