@@ -637,3 +637,39 @@ def test_flop_model_terms_match_reference():
     assert abs(ours - total) < 1e-9 * total, (ours, total)
     # the reference's own inner size for this width, for the record of the difference
     assert ns["ffn_flops_per_layer"](bs, L, D) == 2 * 3 * bs * L * ns["round_to_next_multiple"](int(D * 8 / 3), 64) * D
+
+
+def test_checkpoint_surgery_tools_match_reference():
+    """Projection interleave and context-extension surgery against the reference's tool functions."""
+    from einops import rearrange
+    from savanna_b200.tools.extend_filter import extend_module
+    from savanna_b200.tools.interleave_model_states import deinterleave_rows, interleave_rows
+    il = _extract(("tools", "7b", "conversion", "interleave_model_states.py"), ["reshape_to_interleaved"], {"torch": torch})
+    torch.manual_seed(0)
+    w = torch.randn(3 * 8, 5)
+    with torch.no_grad():
+        want = il["reshape_to_interleaved"](w, dim=8).detach()
+    got = interleave_rows(w)
+    assert torch.equal(got, want) and torch.equal(deinterleave_rows(got), w)
+    conv = torch.randn(3 * 8, 1, 3)
+    with torch.no_grad():
+        want = il["reshape_to_interleaved"](conv.view(24, 3), dim=8).detach().view(24, 1, 3)
+    assert torch.equal(interleave_rows(conv), want)
+    ex = _extract(("tools", "7b", "conversion", "extend_filter.py"), ["extend_model_state"],
+                  {"torch": torch, "rearrange": rearrange, "hyena_mr_LEN": 128, "print": lambda *a, **k: None,
+                   "EXPLICIT_FILTER_PATTERNS": ["mixer.mixer.filter.h", "mixer.mixer.filter.decay"],
+                   "IMPLICIT_FILTER_PATTERN": "mixer.mixer.filter.t"})
+    G, old, new = 16, 256, 1024
+    module = {"sequential.3.mixer.mixer.filter.h": torch.randn(G, old),
+              "sequential.3.mixer.mixer.filter.decay": torch.rand(G, old),
+              "sequential.4.mixer.mixer.filter.t": torch.arange(old, dtype=torch.float32).view(1, 1, -1),
+              "sequential.4.mixer.mixer.filter.gamma": torch.randn(G, 4)}
+    want = ex["extend_model_state"]({k: v.clone() for k, v in module.items()}, G, old, new)
+    got = extend_module(module, new, taps=128)
+    for k in module:
+        assert got[k].shape == want[k].shape, k
+    assert torch.equal(got["sequential.3.mixer.mixer.filter.h"], want["sequential.3.mixer.mixer.filter.h"])
+    assert torch.equal(got["sequential.4.mixer.mixer.filter.t"], want["sequential.4.mixer.mixer.filter.t"])
+    # the decay window: the 128 taps that the operator reads are carried over unchanged by both; past them the reference
+    # writes zeros and this tool a fresh window, neither of which is ever read (hyena_mr_len = 128)
+    assert torch.equal(got["sequential.3.mixer.mixer.filter.decay"][:, :128], want["sequential.3.mixer.mixer.filter.decay"][:, :128])
