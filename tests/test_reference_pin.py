@@ -673,3 +673,14 @@ def test_checkpoint_surgery_tools_match_reference():
     # the decay window: the 128 taps that the operator reads are carried over unchanged by both; past them the reference
     # writes zeros and this tool a fresh window, neither of which is ever read (hyena_mr_len = 128)
     assert torch.equal(got["sequential.3.mixer.mixer.filter.decay"][:, :128], want["sequential.3.mixer.mixer.filter.decay"][:, :128])
+
+
+def test_partition_table_matches_reference():
+    """Every entry of the reference's Evo 2 parameter table has the same tensor-parallel split dimension here."""
+    from savanna_b200.tools.params import partition_dim
+    mod = _load("savanna_ref_params", "tools", "7b", "conversion", "params.py")
+    assert len(mod.EVO2_PARAMS) >= 20
+    for prm in mod.EVO2_PARAMS:
+        for prefix in ("sequential.0.", "sequential.7.", "sequential.33."):
+            key = prefix + prm.name
+            assert partition_dim(key) == prm.partition_dim, (key, partition_dim(key), prm.partition_dim)
