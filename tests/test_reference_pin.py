@@ -684,3 +684,55 @@ def test_partition_table_matches_reference():
         for prefix in ("sequential.0.", "sequential.7.", "sequential.33."):
             key = prefix + prm.name
             assert partition_dim(key) == prm.partition_dim, (key, partition_dim(key), prm.partition_dim)
+
+
+def test_depthwise_conv_and_short_operator_match_reference(monkeypatch):
+    """The featuriser / Hyena-SE depthwise convolution (weights shared per group, cross-correlation tap order, causal
+    padding) and the gate-conv-gate composition around it, against the reference's module."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+    from einops import rearrange
+    from functools import partial
+
+    class Mpu:
+        get_sequence_parallel_world_size = staticmethod(lambda: 1)
+        get_model_parallel_world_size = staticmethod(lambda: 1)
+        get_model_parallel_rank = staticmethod(lambda: 0)
+
+        class _Fork:
+            def __enter__(self):
+                return self
+
+            def __exit__(self, *a):
+                return False
+
+        @staticmethod
+        def get_cuda_rng_tracker():
+            class T:
+                fork = staticmethod(lambda: Mpu._Fork())
+            return T
+
+    class Cfg:
+        use_cp_hyena, use_depthwise_short_conv_grouping, params_dtype, short_conv_L = False, False, torch.float32, 3
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: "cpu")
+    ns = _extract(("savanna", "model", "operators", "hyena", "hyena.py"),
+                  ["initialize_affine_weight_gpu", "ParallelCausalDepthwiseConv1d"],
+                  {"torch": torch, "nn": nn, "F": F, "math": math, "mpu": Mpu, "partial": partial, "rearrange": rearrange,
+                   "causal_conv1d_fn": None})
+    torch.manual_seed(0)
+    B, L = 2, 40
+    for width, groups, k in ((24, 24, 3), (32, 4, 7)):
+        Cfg.use_depthwise_short_conv_grouping = groups != width      # the reference's PyTorch path for shared group weights
+        conv = ns["ParallelCausalDepthwiseConv1d"](width, Cfg, kernel_size=k, init_method=None, num_groups=groups,
+                                                   repeat_h_dg=False)
+        w = conv.short_conv_weight.detach()                                   # [groups, 1, k]
+        x = torch.randn(B, width, L)
+        want = conv(x)                                                        # [B, width, L]
+        got = ref.causal_conv1d(x.transpose(1, 2), w[:, 0, :].repeat_interleave(width // groups, dim=0)).transpose(1, 2)
+        assert torch.allclose(got, want, atol=1e-5), (width, groups, k)
+        # gate - conv - gate on interleaved features, as the short operator composes it
+        x1, x2, v = torch.randn(B, width, L), torch.randn(B, width, L), torch.randn(B, width, L)
+        want = x1 * conv(x2 * v)
+        feat = torch.stack([x1, x2, v], dim=-1).permute(0, 2, 1, 3).reshape(B, L, 3 * width)
+        got = ref.hyena_se_inner(feat, w[:, 0, :], None, True, True).transpose(1, 2)
+        assert torch.allclose(got, want, atol=1e-5)
