@@ -211,23 +211,42 @@ def _partitioned_saved_tensors(tp: int, rank: int, group):
 
 
 def param_groups(model: nn.Module, cfg):
-    """Weight-decay / no-weight-decay (+ optional per-group lr) parameter groups
-    (reference: savanna/model/utils.py:28-109): no decay for norms, biases and Hyena filter
-    parameters (filters are decayed when `hyena_filter_wd` is non-zero); optional own lr for Hyena-MR filters (`lr_medium_hyena`) and for the no-decay group
-    (`wd_free_lr`)."""
+    """Weight-decay / no-weight-decay (+ optional per-group lr) parameter groups, decided module by module on each
+    module's own parameters exactly as the reference decides them (savanna/model/utils.py:28-109):
+
+      * norm layers: no decay (and everything when `weight_decay` is 0);
+      * with `hyena_filter_wd` = 0, the own parameters of the free-form, complex modal and factored real modal filter
+        modules and of the short Hyena operator: no decay; the explicit Hyena-MR filter `h`: no decay, in its own group
+        when `lr_medium_hyena` differs from the learning rate;
+      * every other module: parameters named `bias` are not decayed, all the others are.
+
+    The last rule is what the reference applies to the modal Hyena-LI filter (`gamma`, `R`, `p`), to `conv_bias`, to
+    the depthwise convolution weights and to the layers inside the free-form filter's MLP, whose classes its list does not
+    name: they are decayed, and so they are here.  `wd_free_lr` gives the no-decay group its own learning rate."""
+    from .filters import (ExplicitSingleDecayFilter, ImplicitRealModalFilter, ParallelComplexModalFilter,
+                          ParallelImplicitFreeformFilter)
+    from .hyena import ShortHyenaOperator
+    from .norms import LayerNorm, RMSNorm, ScaleNorm
     decay, no_decay, medium = [], [], []
-    for name, p in model.named_parameters():
-        if not p.requires_grad:
+    seen = set()
+    wd_off = cfg.weight_decay == 0.0
+    filters_free = cfg.hyena_filter_wd == 0.0
+    own_medium = cfg.lr_medium_hyena is not None and cfg.lr_medium_hyena != cfg.lr
+    for module in model.modules():
+        own = [(n, p) for n, p in module._parameters.items() if p is not None and p.requires_grad and id(p) not in seen]
+        if not own:
             continue
-        if cfg.lr_medium_hyena is not None and ".filter.h" in name:
-            medium.append(p)
-        elif getattr(p, "is_filter_param", False) and cfg.hyena_filter_wd != 0.0 and not name.endswith(".bias"):
-            decay.append(p)       # `hyena_filter_wd` non-zero: filter parameters are decayed like the other weights
-        elif getattr(p, "is_norm_param", False) or getattr(p, "is_filter_param", False) or name.endswith(".bias") \
-                or p.dim() == 1:
-            no_decay.append(p)
+        seen.update(id(p) for _, p in own)
+        if isinstance(module, (LayerNorm, RMSNorm, ScaleNorm, nn.LayerNorm)) or wd_off:
+            no_decay += [p for _, p in own]
+        elif filters_free and isinstance(module, (ParallelImplicitFreeformFilter, ParallelComplexModalFilter,
+                                                  ImplicitRealModalFilter, ShortHyenaOperator)):
+            no_decay += [p for _, p in own]
+        elif filters_free and isinstance(module, ExplicitSingleDecayFilter):
+            (medium if own_medium else no_decay).extend(p for _, p in own)
         else:
-            decay.append(p)
+            decay += [p for n, p in own if n != "bias"]
+            no_decay += [p for n, p in own if n == "bias"]
     wd = cfg.weight_decay
     groups = [{"params": decay, "weight_decay": wd, "name": "decay"},
               {"params": no_decay, "weight_decay": 0.0, "name": "no_decay"}]

@@ -301,7 +301,7 @@ def test_mup_optimizer_groups_scale_matrix_like_learning_rates():
     """`use_mup`: projection / MLP weights get lr / mup_width_scale under Adam (MuAdam), vector-like parameters get
     lr * mup_width_scale under SGD (MuSGD); every parameter stays in exactly one group."""
     from savanna_b200.models.backbone import param_groups
-    cfg = _cfg(use_mup=True, mup_width_scale=4)
+    cfg = _cfg(use_mup=True, mup_width_scale=4, weight_decay=0.1)
     tr = Trainer(cfg, load=False)
     groups = param_groups(tr.model, cfg)
     names = {g["name"] for g in groups}
@@ -315,7 +315,7 @@ def test_mup_optimizer_groups_scale_matrix_like_learning_rates():
     # the optimizer carries the ratio through the schedule
     zg = [g for g in tr.optimizer.param_groups if g["name"] == "decay_matrix"][0]
     assert abs(zg["lr_mult"] - 0.25) < 1e-9 and zg["fixed_lr"]
-    cfg2 = _cfg(use_mup=True, mup_width_scale=4, optimizer={"type": "sgd", "params": {"lr": 1e-3}})
+    cfg2 = _cfg(use_mup=True, mup_width_scale=4, weight_decay=0.1, optimizer={"type": "sgd", "params": {"lr": 1e-3}})
     assert cfg2.optimizer_type == "sgd"
     tr2 = Trainer(cfg2, load=False)
     g2 = param_groups(tr2.model, cfg2)
@@ -386,7 +386,7 @@ def test_mup_base_shapes_file_drives_the_groups(tmp_path):
     assert shapes["sequential.2.mixer.dense_projection.weight"] == {"shape": [3 * D, D], "infinite": [True, True]}
     assert shapes["sequential.0.word_embeddings.weight"]["infinite"] == [False, True]
     wide = _cfg(use_mup=True, mup_width_scale=7, hidden_size=2 * D, base_shapes_file=str(tmp_path / "shapes"),
-                optimizer={"type": "Adam", "params": {"lr": 1e-3}})
+                weight_decay=0.1, optimizer={"type": "Adam", "params": {"lr": 1e-3}})
     wide.build_tokenizer()
     model = build_model(wide, device=torch.device("cpu"))
     w = mup_shapes.width_multipliers(model, mup_shapes.load_base_shapes(str(tmp_path / "shapes") + ".0"))

@@ -230,7 +230,11 @@ def test_alloc_stats_reporting_ranks_and_gradient_zero_share(tmp_path):
     assert keys and all(0.0 <= logged[k] <= 100.0 for k in keys)
 
 
-def test_hyena_filter_weight_decay_switch():
+def test_weight_decay_groups_follow_the_reference_rules():
+    """Module-by-module grouping: norms and `bias` parameters are never decayed; the explicit Hyena-MR filter is free of
+    decay only while `hyena_filter_wd` is 0 (then in its own group when `lr_medium_hyena` differs); the modal Hyena-LI
+    filter, `conv_bias` and the depthwise convolution weights are decayed, as the reference's class list leaves them;
+    with `weight_decay` 0 there is one group."""
     import os
     from savanna_b200.config import GlobalConfig
     from savanna_b200.models.backbone import param_groups
@@ -238,76 +242,22 @@ def test_hyena_filter_weight_decay_switch():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     yml = [os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")]
 
-    def filters_in(group_name, **over):
+    def groups_of(**over):
         cfg = GlobalConfig.from_ymls(yml, {"global_num_gpus": 1, **over})
         tr = Trainer(cfg, load=False)
-        groups = {g["name"]: g for g in param_groups(tr.model, cfg)}
-        ids = {id(p) for p in groups[group_name]["params"]}
-        return [n for n, p in tr.model.named_parameters() if getattr(p, "is_filter_param", False) and id(p) in ids]
-    assert filters_in("decay") == [] and filters_in("no_decay")
-    assert filters_in("decay", hyena_filter_wd=0.1)
-
-
-def test_flop_model_matches_the_closed_form_for_an_attention_only_model(monkeypatch):
-    """Attention-only model with a plain MLP: 24 D^2 + 4 L D per layer and token (forward), x3 with the backward, x4 with
-    recomputation: the Megatron formula.  The peak comes from the configuration, the measured file or the device name."""
-    import os
-    from savanna_b200.config import GlobalConfig
-    from savanna_b200.utils import mfu
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")],
-                                 {"global_num_gpus": 1, "operator_config": [[["flash_v2"], 4]], "num_layers": 4,
-                                  "mlp_type": "regular"})
-    cfg.build_tokenizer()
-    D, L, V, N = cfg.hidden_size, cfg.seq_length, cfg.padded_vocab_size, 4
-    fwd = N * (24 * D * D + 4 * L * D) + 2 * D * V
-    assert mfu.model_flops_per_token(cfg, backward=False) == fwd
-    assert mfu.model_flops_per_token(cfg, backward=True) == 3 * fwd
-    assert mfu.model_flops_per_token(cfg, backward=True, recompute=True) == 4 * fwd
-    assert mfu.layer_flops_per_token(cfg, "flash_v2", executed=True) == 24 * D * D + 2 * L * D
-    monkeypatch.setattr(mfu, "measured_peaks", lambda: None)
-    assert mfu.peak_flops(None, device_name="NVIDIA H100 PCIe") == mfu.DEVICE_PEAKS["H100 PCIe"]
-    assert mfu.peak_flops(None, device_name="NVIDIA B200") == 2.25e15
-    assert mfu.peak_flops(None, device_name="Some Other GPU") is None
-    monkeypatch.setattr(mfu, "measured_peaks", lambda: {"bf16_tflops": 1640.0, "bf16_tflops_sustained": 1329.5})
-    assert mfu.peak_flops(None) == 1329.5e12 and mfu.peak_flops(None, sustained=False) == 1640.0e12
-    cfg.peak_tflops = 1000.0
-    r = mfu.mfu(1000.0, cfg, recompute=True)
-    assert abs(r["mfu"] - 1000.0 * 3 * fwd / 1e15) < 1e-12 and abs(r["hfu"] / r["mfu"] - 4 / 3) < 1e-12
-
-
-def test_memory_stats_format_and_alloc_count_summary(monkeypatch):
-    from savanna_b200.utils import memory_stats as ms
-    assert ms.format_memory_stats({}) == "mem: n/a"
-    st = {"allocated_gb": 1.0, "max_allocated_gb": 2.5, "reserved_gb": 3.0, "max_reserved_gb": 4.0, "num_alloc_retries": 2,
-          "num_ooms": 0, "alloc_count": 10, "free_count": 7}
-    line = ms.format_memory_stats(st)
-    assert "alloc 1.0 (max 2.5) GB" in line and "retries 2" in line
-    monkeypatch.setattr(ms, "memory_stats", lambda device=None: st)
-    assert ms.gather_alloc_counts() == {"min": 10.0, "max": 10.0, "mean": 10.0}
-
-
-def test_debug_dumps_of_two_runs_are_compared_module_by_module(tmp_path):
-    """`debug_dir`: the trainer dumps every leaf module's first call; two runs with the same seed agree everywhere, a
-    run with another seed is flagged."""
-    import os
-    from savanna_b200.config import GlobalConfig
-    from savanna_b200.data.synthetic import acgt_batch
-    from savanna_b200.parallel import state
-    from savanna_b200.train.trainer import Trainer
-    from savanna_b200.utils.debug import diff_dumps
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    dirs = []
-    for name, seed in (("a", 7), ("b", 7), ("c", 8)):
-        cfg = GlobalConfig.from_ymls([os.path.join(root, "configs", "baseline", "tiny_sh2_cpu.yml")],
-                                     {"global_num_gpus": 1, "debug_dir": str(tmp_path / name), "seed": seed})
-        tr = Trainer(cfg, load=False)
-        tr.train_step(iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=0)}] * 8))
-        for h in tr._debug_hooks:
-            h.remove()
-        dirs.append(os.path.join(str(tmp_path / name), os.listdir(tmp_path / name)[0]))
-        state.destroy_model_parallel()
-    same = diff_dumps(dirs[0], dirs[1])
-    assert len(same) > 8 and all(status == "equal" for _, _, status in same)
-    other = diff_dumps(dirs[0], dirs[2])
-    assert any(status == "DIFFERENT" for _, _, status in other)
+        names = {id(p): n for n, p in tr.model.named_parameters()}
+        out = {g["name"]: sorted(names[id(p)] for p in g["params"]) for g in param_groups(tr.model, cfg)}
+        assert sum(len(v) for v in out.values()) == len(names)            # every parameter in exactly one group
+        return out
+    g = groups_of(weight_decay=0.1)
+    assert any(n.endswith("filter.h") for n in g["no_decay"]) and not any(n.endswith("filter.h") for n in g["decay"])
+    assert all(("layernorm" not in n and not n.endswith(".bias") and not n.endswith("norm.weight")) for n in g["decay"])
+    for tail in ("filter.gamma", "filter.R", "filter.p", "mixer.conv_bias", "short_conv_weight", "word_embeddings.weight"):
+        assert any(n.endswith(tail) for n in g["decay"]), tail
+    assert any(n.endswith("mixer.dense.bias") for n in g["no_decay"])
+    g = groups_of(weight_decay=0.1, hyena_filter_wd=0.1)
+    assert any(n.endswith("filter.h") for n in g["decay"])
+    g = groups_of(weight_decay=0.1, lr_medium_hyena=1e-5)
+    assert all(n.endswith("filter.h") for n in g["medium_hyena"]) and g["medium_hyena"]
+    g = groups_of(weight_decay=0.0)
+    assert set(g) == {"no_decay"}

@@ -292,6 +292,18 @@ def test_zero1_data_parallel_equivalence():
     run_distributed(_w_equiv, 2, {"train_micro_batch_size_per_gpu": 1, "zero_optimization": {"stage": 1}}, ref_losses)
 
 
+@pytest.mark.slow
+@pytest.mark.parametrize("stage", [1, 3])
+def test_zero_with_weight_decay_groups_matches_one_process(stage):
+    """With weight decay on there are several parameter groups (decayed weights incl. the fp32 modal filter parameters,
+    undecayed norms and biases, the Hyena-MR filter at its own learning rate): partitioned training still reproduces
+    the single-process trace and gradient norms."""
+    over = {"weight_decay": 0.1, "lr_medium_hyena": 1e-4}
+    ref_losses, ref_norms = _reference_losses(mb=2, with_norms=True, **over)
+    run_distributed(_w_equiv, 2, dict(over, train_micro_batch_size_per_gpu=1, zero_optimization={"stage": stage}),
+                    ref_losses, ref_norms)
+
+
 def _w_partitioned(rank, world, over, ref_losses, tmp):
     """Stage 2 / 3 training reproduces the loss trace; between steps a stage-3 rank holds no whole block; a checkpoint
     written from shards reloads into an identical model."""
