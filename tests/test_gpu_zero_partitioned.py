@@ -102,3 +102,12 @@ def test_fp16_precision_with_dynamic_loss_scale_on_the_gpu():
                                    "hysteresis": 2}), n=4)
     assert abs(got[0] - want[0]) < 0.05, (got, want)
     assert got[-1] < got[0] - 0.2, got
+
+
+def test_weight_decay_groups_with_mixed_precision_flats():
+    """Weight decay on: the decayed group holds bf16 weights and fp32 filter parameters side by side, the undecayed one
+    norms and biases, the Hyena-MR filter has its own learning rate.  Stage 3 reproduces stage 1 and both train."""
+    over = dict(_WIDE, **_FP8, weight_decay=0.1, lr_medium_hyena=1e-4)
+    want = _losses(1, 0, dict(over, zero_optimization={"stage": 1}))
+    got = _losses(1, 0, dict(over, zero_optimization={"stage": 3}))
+    _close(got, want)
