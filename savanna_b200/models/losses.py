@@ -89,9 +89,11 @@ def dpo_loss(policy_chosen_logps, policy_rejected_logps, ref_chosen_logps, ref_r
     return losses.mean(), chosen_r, rejected_r
 
 
-def sequence_logps(logits, labels, loss_mask):
+def sequence_logps(logits, labels, loss_mask, positions=None):
     """Per-row log-probability as the reference's preference loss measures it (savanna/model/backbone.py:190-197): the
-    masked token log-probabilities summed and divided by the row length (a mean over all positions, the masked-out ones
-    counting as zero).  The stored reference log-probabilities have to be on the same scale."""
+    masked token log-probabilities summed and divided by the number of label positions (a mean over all positions, the
+    masked-out ones counting as zero).  `positions` is that count; the reference's preference batches hold
+    seq_length - 1 labels (training.py:680-712: rows are padded to seq_length, then shifted), which is what the trainer
+    passes so that stored reference log-probabilities are on the same scale.  Default: the row length."""
     lp = -ops.cross_entropy(logits, labels)
-    return (lp * loss_mask.float()).sum(-1) / float(lp.shape[-1])
+    return (lp * loss_mask.float()).sum(-1) / float(positions or lp.shape[-1])

@@ -258,7 +258,7 @@ class Trainer:
             labels = batch_mod.to_upper_bytes(labels)
         if cfg.alignment_method == "dpo":
             # rows 0..B-1 are the accepted texts, B..2B-1 the rejected ones (train/batch.py:build_batch_dpo)
-            lp = losses.sequence_logps(logits, labels, mask)
+            lp = losses.sequence_logps(logits, labels, mask, positions=max(1, cfg.seq_length - 1))
             B = lp.shape[0] // 2
             ref = b["ref_logps"]
             loss, _, _ = losses.dpo_loss(lp[:B], lp[B:], ref[:B], ref[B:], beta=cfg.dpo_beta)
