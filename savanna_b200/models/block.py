@@ -92,17 +92,22 @@ class ParallelBlock(nn.Module):
             u, a_res = _norm_and_residual(self.pre_mlp_layernorm, a) if self.pre_mlp_norm else (a, a)
             y, _ = self._mlp(u, positions, a_res)
             return y
+        # the general order of the reference (savanna/model/block.py:1105-1212): the post-norm acts on the MLP output,
+        # the outer norm on the sum of the gated MLP's output and its residual, and the gated MLP's branch has no dropout
         u = self.input_layernorm(x) if self.prenorm else x
         m, mb = self.mixer(u, positions)
         if mb is not None:
             m = m + mb
-        if self.postnorm:
-            m = self.post_attention_layernorm(m)
         a = residual + self._drop(m)
+        if isinstance(self.mlp, nn.Identity):
+            return a
         u = self.pre_mlp_layernorm(a) if self.pre_mlp_norm else a
         f, fb = self._mlp(u, positions)
+        if self.postnorm:
+            f = self.post_attention_layernorm(f)
+        if isinstance(self.mlp, ParallelGLU):
+            out = a + f
+            return self.outer_mlp_layernorm(out) if self.outer_mlp_norm else out
         if fb is not None:
             f = f + fb
-        if self.outer_mlp_norm:
-            f = self.outer_mlp_layernorm(f)
         return a + self._drop(f)

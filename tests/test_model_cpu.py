@@ -492,3 +492,32 @@ def test_hyena_width_expansion_widens_the_operators_not_the_stream():
     assert se.width == Hm and se.num_groups == int(int(16 * 2) * 2) and se.width % se.num_groups == 0
     losses = [float(tr.train_step(_iter(cfg))) for _ in range(4)]
     assert losses[-1] < losses[0], losses
+
+
+@pytest.mark.parametrize("over", [{"postnorm": True, "pre_mlp_norm": False}, {"outer_mlp_norm": True},
+                                  {"prenorm": False, "pre_mlp_norm": False, "postnorm": True}])
+def test_block_norm_placements_follow_the_reference_order(over):
+    """Post-norm on the MLP output, outer norm on (residual + gated-MLP output), written out with the block's own
+    sub-modules."""
+    cfg = _cfg(hidden_dropout=0.0, **over)
+    tr = Trainer(cfg, load=False)
+    blk = tr.model.blocks()[0]
+    blk.eval()
+    torch.manual_seed(0)
+    x = torch.randn(1, cfg.seq_length, cfg.hidden_size)
+    pos = torch.arange(cfg.seq_length)
+    with torch.no_grad():
+        got = blk(x, pos)
+        u = blk.input_layernorm(x) if cfg.prenorm else x
+        m, mb = blk.mixer(u, pos)
+        a = x + (m + mb if mb is not None else m)
+        u = blk.pre_mlp_layernorm(a) if cfg.pre_mlp_norm else a
+        f, _ = blk.mlp(u, None)
+        if cfg.postnorm:
+            f = blk.post_attention_layernorm(f)
+        want = a + f
+        if cfg.outer_mlp_norm:
+            want = blk.outer_mlp_layernorm(want)
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+    losses = [float(tr.train_step(_iter(cfg))) for _ in range(3)]
+    assert losses[-1] < losses[0]
