@@ -736,3 +736,18 @@ def test_depthwise_conv_and_short_operator_match_reference(monkeypatch):
         feat = torch.stack([x1, x2, v], dim=-1).permute(0, 2, 1, 3).reshape(B, L, 3 * width)
         got = ref.hyena_se_inner(feat, w[:, 0, :], None, True, True).transpose(1, 2)
         assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_left_to_right_masks_match_reference():
+    from savanna_b200.train.batch import ltor_masks_and_position_ids, to_upper_bytes
+    ns = _extract(("savanna", "utils.py"), ["get_ltor_masks_and_position_ids", "get_attn_mask", "make_upper_case"],
+                  {"torch": torch})
+    torch.manual_seed(0)
+    tok = torch.randint(0, 6, (3, 20))
+    for eod_mask, pad_mask in ((False, False), (True, False), (True, True)):
+        _, want_mask, want_pos = ns["get_ltor_masks_and_position_ids"](tok, 0, 1, eod_mask, pad_mask, materialize_attn_mask=False)
+        got_mask, got_pos = ltor_masks_and_position_ids(tok, 0, eod_mask, 1, pad_mask)
+        assert torch.equal(got_mask, want_mask) and torch.equal(got_pos, want_pos[0])
+    letters = torch.randint(60, 125, (2, 30))
+    want, _ = ns["make_upper_case"](letters)
+    assert torch.equal(to_upper_bytes(letters), want)
