@@ -751,3 +751,14 @@ def test_left_to_right_masks_match_reference():
     letters = torch.randint(60, 125, (2, 30))
     want, _ = ns["make_upper_case"](letters)
     assert torch.equal(to_upper_bytes(letters), want)
+
+
+def test_vocab_padding_matches_reference():
+    from savanna_b200.data.tokenizer import pad_vocab_size
+    ns = _extract(("savanna", "tokenizer", "tokenizer.py"), ["_vocab_size_with_padding"], {})
+
+    class Args:
+        rank = 1
+    for vocab, by, tp in ((512, 8, 1), (50257, 128, 2), (32000, 128, 8), (259, 8, 4), (1000, 1, 1)):
+        Args.make_vocab_size_divisible_by, Args.model_parallel_size = by, tp
+        assert pad_vocab_size(vocab, by, tp) == ns["_vocab_size_with_padding"](vocab, Args), (vocab, by, tp)
