@@ -50,8 +50,17 @@ class CharLevelTokenizer(AbstractTokenizer):
             text = text.encode("utf-8")
         return list(np.frombuffer(text, dtype=np.uint8))
 
+    def tokenize_batch(self, text_batch):
+        """A list of strings -> a list of id lists; a single string is tokenized as such."""
+        if isinstance(text_batch, list):
+            return [self.tokenize(s) for s in text_batch]
+        return self.tokenize(text_batch)
+
+    def decode_token(self, token: int) -> str:
+        return chr(self.clamp(int(token)))
+
     def detokenize(self, ids) -> str:
-        return "".join(chr(self.clamp(int(t))) for t in ids)
+        return "".join(self.decode_token(t) for t in ids)
 
     def detokenize_batch(self, batch):
         return [self.detokenize(row) for row in batch]
