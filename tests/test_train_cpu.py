@@ -268,3 +268,28 @@ def test_annealing_lr_values_including_the_saturated_tail():
         t = AnnealingLR(Opt, 2.0, 10, 100, style, min_lr=0.0)
         t.step(60)
         assert abs(Opt.param_groups[0]["lr"] - 2.0 * f(50)) < 1e-12
+
+
+def test_fp16_loss_scale_survives_checkpoint_resume(tmp_path):
+    """The dynamic scaler's state travels in the optimizer checkpoint: a resumed run continues at the saved scale."""
+    import os
+    from savanna_b200.ckpt import save_checkpoint
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    save = str(tmp_path / "ck")
+    over = {"global_num_gpus": 1, "precision": "fp16", "save": save, "load": save,
+            "fp16": {"enabled": True, "loss_scale": 0, "initial_scale_power": 8, "loss_scale_window": 2, "hysteresis": 1}}
+    cfg = GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")], over)
+    tr = Trainer(cfg, load=False)
+    d = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)} for i in range(16)])
+    for _ in range(4):
+        tr.train_step(d)                                   # two clean windows: 256 -> 512 -> 1024
+    scale, it = tr.loss_scaler.scale, tr.loss_scaler.iter
+    assert scale > 256.0
+    save_checkpoint(tr)
+    state.destroy_model_parallel()
+    t2 = Trainer(GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")], over), load=True)
+    assert t2.iteration == 4 and t2.loss_scaler.scale == scale and t2.loss_scaler.iter == it
