@@ -293,3 +293,35 @@ def test_fp16_loss_scale_survives_checkpoint_resume(tmp_path):
     state.destroy_model_parallel()
     t2 = Trainer(GlobalConfig.from_ymls([os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")], over), load=True)
     assert t2.iteration == 4 and t2.loss_scaler.scale == scale and t2.loss_scaler.iter == it
+
+
+def test_curriculum_continues_after_resume(tmp_path):
+    """The curriculum length depends on the iteration only: a resumed run picks the schedule up where it stopped."""
+    import os
+    from savanna_b200.ckpt import save_checkpoint
+    from savanna_b200.config import GlobalConfig
+    from savanna_b200.data.synthetic import acgt_batch
+    from savanna_b200.parallel import state
+    from savanna_b200.train.trainer import Trainer
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    save = str(tmp_path / "ck")
+    over = {"global_num_gpus": 1, "save": save, "load": save,
+            "curriculum_learning": {"enabled": True, "curriculum_type": "seqlen", "min_difficulty": 128, "max_difficulty": 1024,
+                                    "schedule_type": "fixed_discrete",
+                                    "schedule_config": {"difficulty": [128, 512, 1024], "max_step": [2, 4]}}}
+    yml = [os.path.join(here, "configs", "baseline", "tiny_sh2_cpu.yml")]
+    cfg = GlobalConfig.from_ymls(yml, over)
+    tr = Trainer(cfg, load=False)
+    d = iter([{"text": acgt_batch(cfg.train_micro_batch_size_per_gpu, cfg.seq_length, seed=i)} for i in range(32)])
+    for _ in range(3):
+        tr.train_step(d)
+    assert cfg.curriculum_seqlen == 512 and tr.tokens_seen == cfg.train_batch_size * (128 + 128 + 512)
+    save_checkpoint(tr)
+    state.destroy_model_parallel()
+    cfg2 = GlobalConfig.from_ymls(yml, over)
+    t2 = Trainer(cfg2, load=True)
+    assert t2.iteration == 3 and t2.tokens_seen == tr.tokens_seen
+    t2.train_step(d)
+    assert cfg2.curriculum_seqlen == 512
+    t2.train_step(d)
+    assert cfg2.curriculum_seqlen == 1024
