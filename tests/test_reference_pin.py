@@ -762,3 +762,60 @@ def test_vocab_padding_matches_reference():
     for vocab, by, tp in ((512, 8, 1), (50257, 128, 2), (32000, 128, 8), (259, 8, 4), (1000, 1, 1)):
         Args.make_vocab_size_divisible_by, Args.model_parallel_size = by, tp
         assert pad_vocab_size(vocab, by, tp) == ns["_vocab_size_with_padding"](vocab, Args), (vocab, by, tp)
+
+
+def _reference_native_helpers():
+    import glob
+    found = glob.glob(os.path.join(REF, "savanna", "data", "helpers*.so"))
+    if not found:
+        pytest.skip("the reference ships no built helpers module for this interpreter")
+    spec = importlib.util.spec_from_file_location("helpers", found[0])
+    mod = importlib.util.module_from_spec(spec)
+    try:
+        spec.loader.exec_module(mod)
+    except ImportError as exc:
+        pytest.skip(f"the reference's built helpers module does not load here: {exc}")
+    return mod
+
+
+def test_native_index_builders_match_the_reference_binary():
+    """This framework's C++ data helpers against the helpers module the reference ships built: sample index (both
+    widths), blending indices, and the block mapping (same set of rows; the two shuffle with different generators)."""
+    import numpy as np
+    from savanna_b200.data import helpers
+    theirs = _reference_native_helpers()
+    rng = np.random.RandomState(0)
+    sizes = rng.randint(3, 90, size=64).astype(np.int32)
+    doc_idx = np.concatenate([rng.permutation(64) for _ in range(3)]).astype(np.int32)
+    tokens_per_epoch = int(sizes.sum())
+    for seq_length in (16, 100):
+        want = theirs.build_sample_idx_int32(sizes, doc_idx, seq_length, 3, tokens_per_epoch)
+        got = helpers.build_sample_idx(sizes, doc_idx, seq_length, 3, tokens_per_epoch)
+        assert np.array_equal(np.asarray(got), np.asarray(want)), seq_length
+        want64 = theirs.build_sample_idx_int64(sizes, doc_idx.astype(np.int64), seq_length, 3, tokens_per_epoch)
+        assert np.array_equal(np.asarray(got, dtype=np.int64), np.asarray(want64))
+    weights = np.array([0.5, 0.3, 0.2])
+    ds, ds_sample = np.zeros(500, dtype=np.uint8), np.zeros(500, dtype=np.int64)
+    theirs.build_blending_indices(ds, ds_sample, weights, 3, 500, False)
+    got_ds, got_sample = helpers.build_blending_indices(weights, 500)
+    assert np.array_equal(got_ds, ds) and np.array_equal(got_sample, ds_sample)
+    docs = np.array([0, 5, 6, 9, 14, 20], dtype=np.int64)
+    sent = rng.randint(2, 9, size=20).astype(np.int32)
+    titles = np.array([2, 1, 1, 3, 2], dtype=np.int32)
+    for one_sent in (False, True):
+        want = theirs.build_blocks_mapping(docs, sent, titles, 2, 1000, 16, 7, False, one_sent)
+        got = helpers.build_blocks_mapping(docs, sent, titles, 2, 1000, 16, 7, use_one_sent_blocks=one_sent)
+        assert sorted(map(tuple, np.asarray(want).tolist())) == sorted(map(tuple, got.tolist())), one_sent
+
+
+def test_native_sentence_mapping_matches_the_reference_binary():
+    """Sentence-pair style mapping without short sequences (the only random part): same rows as the reference's binary."""
+    import numpy as np
+    from savanna_b200.data import helpers
+    theirs = _reference_native_helpers()
+    rng = np.random.RandomState(1)
+    docs = np.array([0, 4, 5, 11, 13, 20], dtype=np.int64)
+    sent = rng.randint(2, 12, size=20).astype(np.int32)
+    want = theirs.build_mapping(docs, sent, 2, 1000, 24, 0.0, 5, False)        # the built module fixes two sentences minimum
+    got = helpers.build_mapping(docs, sent, 2, 1000, 24, 0.0, 5, min_num_sent=2)
+    assert sorted(map(tuple, np.asarray(want).tolist())) == sorted(map(tuple, got.tolist()))
